@@ -1,0 +1,423 @@
+/*
+ * CPU oracle for the quantized-weight hot path of FWkey/latentQ_LLM.
+ *
+ * TEST INFRASTRUCTURE ONLY.  This file is a scalar restatement of the
+ * reference's arithmetic, used by the test-suite, the smoke check and the
+ * CPU-baseline leg of the benchmark as the checker.  The product (the CUDA
+ * library) never links, loads or calls anything in this file.
+ *
+ * Pinning status:
+ *   - functions restating pure-torch reference code (utils/quant.py,
+ *     PTQ/quant/quantizer.py, PTQ/quant/quant_linear.py) are pinned by golden
+ *     vectors produced by executing the reference's own functions on CPU
+ *     (tests/golden/gen_golden.py);
+ *   - the 3-fold / uniform residual codecs of utils/cuda_src/
+ *     multi_random_quant_kernel.cu and the external torch_int int8 GEMM have
+ *     no golden vectors anywhere in the reference and were not executed:
+ *     PARITY UNPINNED for those (restated from source text / call sites).
+ *
+ * Every floating-point expression below is a separately rounded IEEE fp32
+ * operation (compile with -ffp-contract=off) except where fmaf() is written
+ * explicitly: nvcc's default --fmad=true contracts `a*b+c` into one FMA, so
+ * the CUDA reference's `x*c1+v` style expressions are restated with fmaf().
+ */
+#include <math.h>
+#include <stdint.h>
+#include <string.h>
+#include <stddef.h>
+
+#define ORC_API __attribute__((visibility("default")))
+
+/* ---------- bf16 helpers --------------------------------------------------- */
+static inline float bf16_round(float x) { /* fp32 -> bf16 (RNE) -> fp32 */
+    uint32_t u; memcpy(&u, &x, 4);
+    if ((u & 0x7fffffffu) > 0x7f800000u) { u |= 0x00400000u; u &= 0xffff0000u; }
+    else { uint32_t lsb = (u >> 16) & 1u; u += 0x7fffu + lsb; u &= 0xffff0000u; }
+    float r; memcpy(&r, &u, 4); return r;
+}
+static inline float rnd(float x, int bf16) { return bf16 ? bf16_round(x) : x; }
+ORC_API void orc_bf16_round(const float* x, float* y, int64_t n) { for (int64_t i = 0; i < n; ++i) y[i] = bf16_round(x[i]); }
+
+/* ---------- a1/a2: nibble pack / unpack  (utils/quant.py:4-19) ------------ */
+ORC_API void orc_pack_nibbles(const uint8_t* codes, int8_t* packed, int64_t n_codes) {
+    for (int64_t i = 0; i < n_codes / 2; ++i) {
+        int8_t hi = (int8_t)codes[2 * i], lo = (int8_t)codes[2 * i + 1];
+        packed[i] = (int8_t)((int8_t)(hi << 4) + lo);           /* int8 wrap-around */
+    }
+}
+ORC_API void orc_unpack_nibbles(const int8_t* packed, int8_t* codes, int64_t n_bytes) {
+    for (int64_t i = 0; i < n_bytes; ++i) {
+        int v = packed[i];
+        codes[2 * i]     = (int8_t)((((v >> 4) % 16) + 16) % 16); /* arithmetic shift, floor-mod */
+        codes[2 * i + 1] = (int8_t)(((v % 16) + 16) % 16);
+    }
+}
+
+/* ---------- a3: A16W4 group dequant  (utils/quant.py:66-72) --------------- */
+/* math_bf16: qparams are bf16 tensors, so sub and mul are bf16 ops. */
+ORC_API void orc_a16w4_dequant(const int8_t* packed, const float* scales, const float* zeros,
+                               int64_t numel, int group, int math_bf16, int out_bf16, float* out) {
+    for (int64_t i = 0; i < numel; ++i) {
+        int v = packed[i >> 1];
+        int code = (i & 1) ? (((v % 16) + 16) % 16) : ((((v >> 4) % 16) + 16) % 16);
+        int64_t g = i / group;
+        float d = rnd((float)code - zeros[g], math_bf16);
+        float w = rnd(d * scales[g], math_bf16);
+        out[i] = out_bf16 ? bf16_round(w) : w;
+    }
+}
+
+/* ---------- a12: uniform residual codec with real noise (utils/quant.py:765-788) */
+ORC_API void orc_uniform16_encode(const float* r, const float* noise, int64_t n,
+                                  int32_t* words, float* carry) {
+    for (int64_t w = 0; w < n / 8; ++w) {
+        uint32_t word = 0;
+        for (int k = 0; k < 8; ++k) {
+            int64_t i = w * 8 + k;
+            float d = (r[i] + 0.5f) * 16.0f;
+            d = d + noise[i];
+            d = rintf(d);                                   /* torch.round_: half-to-even */
+            float c = 0.0f;
+            if (d > 15.9f) { d = 0.0f; c = 1.0f; }
+            if (carry) carry[i] = c;
+            word |= ((uint32_t)(int32_t)d & 0xffffffffu) << (28 - 4 * k); /* shifts wrap like int32 */
+        }
+        words[w] = (int32_t)word;
+    }
+}
+ORC_API void orc_uniform16_decode(const int32_t* words, int64_t n_words, float* out) {
+    for (int64_t w = 0; w < n_words; ++w)
+        for (int k = 0; k < 8; ++k) {
+            int nib = (int)(((uint32_t)words[w] >> (28 - 4 * k)) & 15u);
+            out[w * 8 + k] = (float)nib / 16.0f - 0.5f;
+        }
+}
+
+/* ---------- a8-a10: 3-fold codec (multi_random_quant_kernel.cu:9-217,345-399) */
+typedef struct { float c1, c2, c3, ic1, ic2, ic3, b1, b2; int t1, t2; } orc_curve;
+static orc_curve make_curve(int k1, float b1, int k2, float b2, int k3) {
+    orc_curve c;
+    c.c1 = (float)k1 / b1;                                   /* .cu:346 */
+    c.c2 = (float)k2 / (b2 - b1);                            /* .cu:347 */
+    c.c3 = (float)((double)k3 / (0.5 - (double)b2));         /* .cu:348 (double) */
+    c.ic1 = b1 / (float)k1;                                  /* .cu:385 */
+    c.ic2 = (b2 - b1) / (float)k2;                           /* .cu:386 */
+    c.ic3 = (float)((0.5 - (double)b2) / (double)k3);        /* .cu:387 (double) */
+    c.b1 = b1; c.b2 = b2; c.t1 = k1; c.t2 = k1 + k2;
+    return c;
+}
+ORC_API void orc_curve_constants(int k1, float b1, int k2, float b2, int k3, float* out10) {
+    orc_curve c = make_curve(k1, b1, k2, b2, k3);
+    out10[0] = c.c1; out10[1] = c.c2; out10[2] = c.c3; out10[3] = c.ic1; out10[4] = c.ic2;
+    out10[5] = c.ic3; out10[6] = c.b1; out10[7] = c.b2; out10[8] = (float)c.t1; out10[9] = (float)c.t2;
+}
+/* one element; `v` is the dither in [-0.5,0.5] (hash, explicit or Philox).   */
+static inline int res3_encode_one(float x, float v, const orc_curve* c, int* carry) {
+    float S = fabsf(x), q;
+    if (S < c->b1) q = roundf(fmaf(x, c->c1, v));
+    else if (S < c->b2) { float r = roundf(fmaf(S - c->b1, c->c2, v)) + (float)c->t1; q = (x < 0) ? -r : r; }
+    else { float r = roundf(fmaf(S - c->b2, c->c3, v)) + (float)c->t2; q = (x < 0) ? -r : r; }
+    if (q > 7.5f) { *carry = 1; return 1; }                  /* overflow nibble is 1 in the reference (.cu:63) */
+    *carry = 0;
+    float t = q + 8.0f;
+    return (t <= 0.0f) ? 0 : (int)(unsigned)t;               /* float->unsigned saturates at 0 on the GPU */
+}
+static inline float hash_dither(float x, float v0) {        /* .cu:49-51 */
+    float v = fmaf(fabsf(x), 499.0f, v0);
+    return v - roundf(v);
+}
+/* .cu:160-169; the `a*b±c` forms are contractable, hence fmaf.            */
+static inline float res3_decode_one_fma(int nib, const orc_curve* c) {
+    int s = nib - 8;
+    if (s < -c->t2) return fmaf((float)(s + c->t2), c->ic3, -c->b2);
+    if (s < -c->t1) return fmaf((float)(s + c->t1), c->ic2, -c->b1);
+    if (s <= c->t1) return (float)s * c->ic1;
+    if (s <= c->t2) return fmaf((float)(s - c->t1), c->ic2, c->b1);
+    return fmaf((float)(s - c->t2), c->ic3, c->b2);
+}
+/* `quant`: x (values already in the tensor's dtype) -> words; x overwritten by 0/1 flags. */
+ORC_API void orc_res3_quant(float* x, int32_t* words, int64_t n_words,
+                            int k1, float b1, int k2, float b2, int k3, float v0, const float* dither) {
+    orc_curve c = make_curve(k1, b1, k2, b2, k3);
+    for (int64_t w = 0; w < n_words; ++w) {
+        uint32_t word = 0;
+        for (int k = 0; k < 8; ++k) {
+            int64_t i = w * 8 + k; int carry;
+            float v = dither ? dither[i] : hash_dither(x[i], v0);
+            int nib = res3_encode_one(x[i], v, &c, &carry);
+            word = (word << 4) | (uint32_t)nib;
+            x[i] = carry ? 1.0f : 0.0f;
+        }
+        words[w] = (int32_t)word;
+    }
+}
+ORC_API void orc_res3_dequant(const int32_t* words, float* x, int64_t n_words,
+                              int k1, float b1, int k2, float b2, int k3, int out_bf16) {
+    orc_curve c = make_curve(k1, b1, k2, b2, k3);
+    for (int64_t w = 0; w < n_words; ++w)
+        for (int k = 0; k < 8; ++k) {
+            float v = res3_decode_one_fma((int)(((uint32_t)words[w] >> (28 - 4 * k)) & 15u), &c);
+            x[w * 8 + k] = out_bf16 ? bf16_round(v) : v;
+        }
+}
+/* `uniform_quant` (.cu:241-294): dither sign is flipped w.r.t. the 3-fold kernel. */
+ORC_API void orc_resu_quant(float* x, int32_t* words, int64_t n_words, float v0) {
+    for (int64_t w = 0; w < n_words; ++w) {
+        uint32_t word = 0;
+        for (int k = 0; k < 8; ++k) {
+            int64_t i = w * 8 + k;
+            float v = fmaf(fabsf(x[i]), 499.0f, v0);
+            v = roundf(v) - v;
+            float q = roundf(fmaf(x[i], 8.0f, v));
+            int nib, carry = 0;
+            if (q > 7.5f) { nib = 1; carry = 1; } else { float t = q + 8.0f; nib = (t <= 0.0f) ? 0 : (int)(unsigned)t; }
+            word = (word << 4) | (uint32_t)nib;
+            x[i] = carry ? 1.0f : 0.0f;
+        }
+        words[w] = (int32_t)word;
+    }
+}
+/* `uniform_quant_s` (.cu:219-239): deterministic round(8x). */
+ORC_API void orc_resu_quant_s(float* x, int32_t* words, int64_t n_words) {
+    for (int64_t w = 0; w < n_words; ++w) {
+        uint32_t word = 0;
+        for (int k = 0; k < 8; ++k) {
+            int64_t i = w * 8 + k;
+            float q = roundf(x[i] * 8.0f);
+            int nib, carry = 0;
+            if (q > 7.5f) { nib = 1; carry = 1; } else { float t = q + 8.0f; nib = (t <= 0.0f) ? 0 : (int)(unsigned)t; }
+            word = (word << 4) | (uint32_t)nib;
+            x[i] = carry ? 1.0f : 0.0f;
+        }
+        words[w] = (int32_t)word;
+    }
+}
+/* `uniform_dequant` (.cu:297-334) */
+ORC_API void orc_resu_dequant(const int32_t* words, float* x, int64_t n_words) {
+    for (int64_t w = 0; w < n_words; ++w)
+        for (int k = 0; k < 8; ++k)
+            x[w * 8 + k] = (float)((int)(((uint32_t)words[w] >> (28 - 4 * k)) & 15u) - 8) * 0.125f;
+}
+
+/* ---------- Philox4x32-10 (Salmon et al. 2011; same constants as cuRAND) ---- */
+static inline void philox4x32_10(uint32_t c[4], uint32_t k0, uint32_t k1) {
+    for (int r = 0; r < 10; ++r) {
+        uint64_t p0 = (uint64_t)0xD2511F53u * c[0], p1 = (uint64_t)0xCD9E8D57u * c[2];
+        uint32_t n0 = (uint32_t)(p1 >> 32) ^ c[1] ^ k0, n1 = (uint32_t)p1;
+        uint32_t n2 = (uint32_t)(p0 >> 32) ^ c[3] ^ k1, n3 = (uint32_t)p0;
+        c[0] = n0; c[1] = n1; c[2] = n2; c[3] = n3;
+        k0 += 0x9E3779B9u; k1 += 0xBB67AE85u;
+    }
+}
+ORC_API void orc_philox4x32_10(const uint32_t ctr[4], const uint32_t key[2], uint32_t out[4]) {
+    uint32_t c[4] = {ctr[0], ctr[1], ctr[2], ctr[3]};
+    philox4x32_10(c, key[0], key[1]);
+    memcpy(out, c, 16);
+}
+/* The library's dither stream: one Philox block per residual word (8 elements);
+ * counter = (word index lo, word index hi, stream lo, stream hi), key = seed;
+ * element k uses 16 bits: half (k&1) of output word (k>>1); u = h/65536 - 0.5. */
+ORC_API void orc_philox_dither(uint64_t seed, uint64_t stream, int64_t first_word, int64_t n_words, float* out) {
+    for (int64_t w = 0; w < n_words; ++w) {
+        uint64_t idx = (uint64_t)(first_word + w);
+        uint32_t c[4] = {(uint32_t)idx, (uint32_t)(idx >> 32), (uint32_t)stream, (uint32_t)(stream >> 32)};
+        philox4x32_10(c, (uint32_t)seed, (uint32_t)(seed >> 32));
+        for (int k = 0; k < 8; ++k) {
+            uint32_t h = (k & 1) ? (c[k >> 1] >> 16) : (c[k >> 1] & 0xffffu);
+            out[w * 8 + k] = (float)h * (1.0f / 65536.0f) - 0.5f;
+        }
+    }
+}
+
+/* ---------- a6/a13 + MyAdam.update_step prologue: requantize ---------------- */
+enum { ORC_CODEC_NONE = 0, ORC_CODEC_UNIFORM16 = 1, ORC_CODEC_THREEFOLD = 2 };
+typedef struct {
+    int codec;            /* residual codec */
+    int math_bf16;        /* chain runs in bf16 (GPU reference) or fp32 (CPU config) */
+    int res_round_bf16;   /* residual cast to bf16 before encoding (utils/quant.py:726,737) */
+    int has_residual;     /* 0 while ResidualTensor.init is True (utils/quant.py:833-836) */
+    int enc_k1, enc_k2, enc_k3; float enc_b1, enc_b2;   /* curve used to encode (current mu) */
+    int dec_k1, dec_k2, dec_k3; float dec_b1, dec_b2;   /* curve used to decode (lock_mu)   */
+    float v0;
+    const float* dither;  /* explicit dither per element or NULL (hash dither, 3-fold only) */
+} orc_requant_opts;
+
+static inline float res_decode(int nib, const orc_requant_opts* o, const orc_curve* dc) {
+    if (o->codec == ORC_CODEC_UNIFORM16) return (float)nib / 16.0f - 0.5f;
+    float v = res3_decode_one_fma(nib, dc);
+    return bf16_round(v);                                    /* ext tensors are bf16 (utils/quant.py:722,761) */
+}
+static inline int res_encode(float r, int64_t i, const orc_requant_opts* o, const orc_curve* ec, int* carry) {
+    if (o->res_round_bf16) r = bf16_round(r);
+    if (o->codec == ORC_CODEC_UNIFORM16) {
+        float d = (r + 0.5f) * 16.0f; d = d + o->dither[i]; d = rintf(d);
+        if (d > 15.9f) { *carry = 1; return 0; }
+        *carry = 0; return (int)d & 15;
+    }
+    float v = o->dither ? o->dither[i] : hash_dither(r, o->v0);
+    return res3_encode_one(r, v, ec, carry);
+}
+
+/* A16W4: latent = residual.add(dequant(codes)) [+ delta]; codes', residual' = Qfunc_4bit_g_res(latent)
+ * (utils/quant.py:45-63,66-72,831-837,1069-1073,1143).  w_in != NULL: requantize that tensor instead
+ * (latent given directly).  words may be NULL when codec == NONE. */
+ORC_API void orc_a16w4_requant(const float* w_in, const int8_t* codes_in, const int32_t* words_in,
+                               const float* delta, const float* scales, const float* zeros,
+                               int64_t numel, int group, const orc_requant_opts* o,
+                               int8_t* codes_out, int32_t* words_out, float* latent_out) {
+    orc_curve ec = make_curve(o->enc_k1, o->enc_b1, o->enc_k2, o->enc_b2, o->enc_k3);
+    orc_curve dc = make_curve(o->dec_k1, o->dec_b1, o->dec_k2, o->dec_b2, o->dec_k3);
+    int bf = o->math_bf16;
+    for (int64_t w8 = 0; w8 < numel / 8; ++w8) {
+        uint32_t word = 0; uint8_t q8[8];
+        for (int k = 0; k < 8; ++k) {
+            int64_t i = w8 * 8 + k, g = i / group;
+            float s = scales[g], z = zeros[g], lat;
+            if (w_in) lat = w_in[i];
+            else {
+                int v = codes_in[i >> 1];
+                int code = (i & 1) ? (v & 15) : ((v >> 4) & 15);
+                lat = rnd(rnd((float)code - z, bf) * s, bf);
+                if (o->has_residual && o->codec != ORC_CODEC_NONE) {
+                    int nib = (int)(((uint32_t)words_in[w8] >> (28 - 4 * k)) & 15u);
+                    float rr = rnd(rnd(res_decode(nib, o, &dc) * s, bf), bf);
+                    lat = rnd(rr + lat, bf);
+                }
+                if (delta) lat = rnd(lat + delta[i], bf);
+            }
+            if (latent_out) latent_out[i] = lat;
+            float Z = rnd(lat / s, bf);
+            Z = rnd(Z + z, bf);
+            float q = rintf(Z);
+            float r = rnd(Z - q, bf);
+            int carry = 0, nib = 0;
+            if (o->codec != ORC_CODEC_NONE) nib = res_encode(r, i, o, &ec, &carry);
+            q = rnd(q + (float)carry, bf);
+            q = fminf(fmaxf(q, 0.0f), 15.0f);
+            q8[k] = (uint8_t)q;
+            word = (word << 4) | (uint32_t)nib;
+        }
+        if (words_out) words_out[w8] = (int32_t)word;
+        for (int k = 0; k < 4; ++k) codes_out[w8 * 4 + k] = (int8_t)(uint8_t)((q8[2 * k] << 4) | q8[2 * k + 1]);
+    }
+}
+
+/* A8W8 (utils/quant.py:88-103,1070-1071,1141): per-row scale, codes int8 [rows, cols]. */
+ORC_API void orc_a8w8_requant(const float* w_in, const int8_t* codes_in, const int32_t* words_in,
+                              const float* delta, const float* qscales, int64_t rows, int64_t cols,
+                              const orc_requant_opts* o, int8_t* codes_out, int32_t* words_out, float* latent_out) {
+    orc_curve ec = make_curve(o->enc_k1, o->enc_b1, o->enc_k2, o->enc_b2, o->enc_k3);
+    orc_curve dc = make_curve(o->dec_k1, o->dec_b1, o->dec_k2, o->dec_b2, o->dec_k3);
+    int bf = o->math_bf16;
+    int64_t numel = rows * cols;
+    for (int64_t w8 = 0; w8 < numel / 8; ++w8) {
+        uint32_t word = 0;
+        for (int k = 0; k < 8; ++k) {
+            int64_t i = w8 * 8 + k; float s = qscales[i / cols], lat;
+            if (w_in) lat = w_in[i];
+            else {
+                lat = rnd((float)codes_in[i] * s, bf);
+                if (o->has_residual && o->codec != ORC_CODEC_NONE) {
+                    int nib = (int)(((uint32_t)words_in[w8] >> (28 - 4 * k)) & 15u);
+                    float rr = rnd(rnd(res_decode(nib, o, &dc) * s, bf), bf);
+                    lat = rnd(rr + lat, bf);
+                }
+                if (delta) lat = rnd(lat + delta[i], bf);
+            }
+            if (latent_out) latent_out[i] = lat;
+            float Z = rnd(lat / s, bf);
+            float q = rintf(Z);
+            float r = rnd(Z - q, bf);
+            int carry = 0, nib = 0;
+            if (o->codec != ORC_CODEC_NONE) nib = res_encode(r, i, o, &ec, &carry);
+            q = rnd(q + (float)carry, bf);
+            q = fminf(fmaxf(q, -128.0f), 127.0f);
+            codes_out[i] = (int8_t)q;
+            word = (word << 4) | (uint32_t)nib;
+        }
+        if (words_out) words_out[w8] = (int32_t)word;
+    }
+}
+
+/* ---------- a19: group min/max quantizer (PTQ/quant/quantizer.py:34-74) ------ */
+ORC_API void orc_find_qparams(const float* x, int64_t rows, int64_t cols, int maxq, int sym,
+                              float* scale, float* zero) {
+    for (int64_t r = 0; r < rows; ++r) {
+        float mn = 0.0f, mx = 0.0f;
+        for (int64_t c = 0; c < cols; ++c) { float v = x[r * cols + c]; mn = fminf(mn, v); mx = fmaxf(mx, v); }
+        if (sym) { mx = fmaxf(fabsf(mn), mx); if (mn < 0) mn = -mx; }
+        if (mn == 0.0f && mx == 0.0f) { mn = -1.0f; mx = 1.0f; }
+        scale[r] = (mx - mn) / (float)maxq;
+        zero[r] = sym ? (float)(maxq + 1) / 2.0f : rintf(-mn / scale[r]);
+    }
+}
+
+/* ---------- C.6: 8-bit optimizer-state codec (utils/quant.py:22-41) --------- */
+ORC_API void orc_opt8_quant(const float* x, int64_t n, int64_t block, uint8_t* q, float* scale, float* tmax) {
+    for (int64_t b = 0; b < n / block; ++b) {
+        float mn = x[b * block], mx = mn;
+        for (int64_t i = 1; i < block; ++i) { float v = x[b * block + i]; mn = fminf(mn, v); mx = fmaxf(mx, v); }
+        float s = (mx - mn) / 255.0f + 1e-10f;
+        scale[b] = s; tmax[b] = mx;
+        for (int64_t i = 0; i < block; ++i) {
+            float t = rintf((mx - x[b * block + i]) / s);
+            q[b * block + i] = (uint8_t)fminf(fmaxf(t, 0.0f), 255.0f);
+        }
+    }
+}
+ORC_API void orc_opt8_dequant(const uint8_t* q, int64_t n, int64_t block, const float* scale, const float* tmax, float* x) {
+    for (int64_t i = 0; i < n; ++i) x[i] = tmax[i / block] - (float)q[i] * scale[i / block];
+}
+
+/* ---------- a23: per-token symmetric activation quant (quant_linear.py:520-528) */
+ORC_API void orc_act_quant_per_token(const float* x, int64_t rows, int64_t cols, int math_bf16,
+                                     int8_t* q, float* scale) {
+    for (int64_t r = 0; r < rows; ++r) {
+        float am = 0.0f;
+        for (int64_t c = 0; c < cols; ++c) am = fmaxf(am, fabsf(x[r * cols + c]));
+        float s = rnd(fmaxf(am, 1e-5f) / 127.0f, math_bf16);
+        scale[r] = s;
+        for (int64_t c = 0; c < cols; ++c) {
+            float t = rintf(rnd(x[r * cols + c] / s, math_bf16));
+            q[r * cols + c] = (int8_t)fminf(fmaxf(t, -128.0f), 127.0f);
+        }
+    }
+}
+/* a14 forward quantizer (utils/quant.py:264-266): x*127. then /clampv, each rounded in the tensor dtype. */
+ORC_API void orc_act_quant_per_tensor(const float* x, int64_t n, float clampv, int math_bf16, int8_t* q) {
+    for (int64_t i = 0; i < n; ++i) {
+        float t = rnd(x[i] * 127.0f, math_bf16);
+        t = rnd(t / clampv, math_bf16);
+        t = rintf(t);
+        q[i] = (int8_t)fminf(fmaxf(t, -128.0f), 127.0f);
+    }
+}
+
+/* ---------- a16: int8 GEMM, int32 accumulators; epilogue alpha*acc+bias -> bf16 */
+ORC_API void orc_gemm_i8_acc(const int8_t* x, const int8_t* w, int64_t M, int64_t N, int64_t K, int32_t* acc) {
+    for (int64_t m = 0; m < M; ++m)
+        for (int64_t n = 0; n < N; ++n) {
+            int32_t a = 0;
+            for (int64_t k = 0; k < K; ++k) a += (int32_t)x[m * K + k] * (int32_t)w[n * K + k];
+            acc[m * N + n] = a;
+        }
+}
+
+/* ---------- C.7: MyAdam.update_step on one A16W4 parameter, fp32 or bf16 chain
+ * (utils/quant.py:1062-1148).  States are the uint8 block codec above with
+ * block = 2048 (or 128).  step is the value AFTER the increment at :1095.     */
+ORC_API void orc_adam_dense(float* p, const float* g, float* m, float* s2, int64_t n,
+                            float beta1, float beta2, float eps, float step_size, float wd, int math_bf16) {
+    /* m: exp_avg; s2: stored sqrt(v)+eps (second state is squared on load, :1089) */
+    int bf = math_bf16;
+    for (int64_t i = 0; i < n; ++i) {
+        float grad = g[i];
+        if (wd != 0.0f) grad = rnd(grad + rnd(wd * p[i], bf), bf);
+        float ea = rnd(rnd(m[i] * beta1, bf) + rnd((1.0f - beta1) * grad, bf), bf);
+        float v = rnd(s2[i] * s2[i], bf);
+        float eq = rnd(rnd(v * beta2, bf) + rnd(rnd((1.0f - beta2) * grad, bf) * grad, bf), bf);
+        float den = rnd(rnd(sqrtf(eq), bf) + eps, bf);
+        p[i] = rnd(p[i] + rnd(rnd(-step_size * ea, bf) / den, bf), bf);
+        m[i] = ea; s2[i] = den;
+    }
+}

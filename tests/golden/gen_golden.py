@@ -1,0 +1,185 @@
+"""Generate the golden vectors under tests/golden/ by EXECUTING the reference's own code.
+
+Run once in a container that has the reference checkout (it does not travel
+to the GPU box; the .npz files do):
+
+    python tests/golden/gen_golden.py /path/to/latentQ_LLM
+
+`utils/quant.py` cannot be imported (it needs torch_int, a GPU and a JIT
+build at import time), so the pure-torch functions are loaded by slicing the
+module's AST: the selected `def`s / assignments are compiled from the
+reference file where it lies and executed in a scratch namespace.  Nothing
+from the reference is copied into this repository.
+
+`ResidualTensor` allocates on 'cuda' in its constructor, so a CPU stand-in
+with the same `set_value(residual_fp, scale) -> carry flags` contract is put in
+the namespace; it routes to the reference's own CPU codec
+(`python_quant_linear`, utils/quant.py:765-778), which is what the reference's
+`cuda_quant_linear` does for CPU tensors (utils/quant.py:728-729).
+"""
+import ast
+import os
+import sys
+
+import numpy as np
+import torch
+
+OUT = os.path.dirname(os.path.abspath(__file__))
+
+
+def slice_module(path, names, extra_ns=None):
+    src = open(path).read()
+    tree = ast.parse(src)
+    keep = []
+    for node in tree.body:
+        if isinstance(node, (ast.FunctionDef, ast.ClassDef)) and node.name in names:
+            keep.append(node)
+        elif isinstance(node, ast.Assign) and any(isinstance(t, ast.Name) and t.id in names for t in node.targets):
+            keep.append(node)
+    mod = ast.Module(body=keep, type_ignores=[])
+    ns = {"torch": torch, "nn": torch.nn, "math": __import__("math"), "np": np}
+    ns.update(extra_ns or {})
+    exec(compile(mod, path, "exec"), ns)
+    return ns
+
+
+def f32(t):
+    return t.detach().to(torch.float32).contiguous().numpy()
+
+
+def main(ref):
+    qpath = os.path.join(ref, "utils", "quant.py")
+
+    class ResidualTensor:  # CPU stand-in, see module docstring
+        def __init__(self):
+            self.residual_int = None
+            self.noise_seed = None
+
+        def set_value(self, residual_fp, weight_scale=None):
+            if self.noise_seed is not None:
+                torch.manual_seed(self.noise_seed)
+            words, adj = ns["python_quant_linear"](residual_fp.contiguous())
+            self.residual_int = words
+            return adj.view(residual_fp.shape)
+
+    ns = slice_module(qpath, {"python_compress", "python_decompress", "Qfunc_8bit_opt", "DeQfunc_8bit_opt",
+                              "GROUPSIZE", "Qfunc_4bit_g_res", "DeQfunc_4bit_g", "Qfunc_8bit_res",
+                              "python_quant_linear", "python_dequant_linear", "three_fold_curve_4bit"},
+                      {"ResidualTensor": ResidualTensor})
+    qz = slice_module(os.path.join(ref, "PTQ", "quant", "quantizer.py"), {"Quantizer"})
+    ql = slice_module(os.path.join(ref, "PTQ", "quant", "quant_linear.py"),
+                      {"quantize_activation_per_token_absmax"})
+
+    g = torch.Generator().manual_seed(1234)
+    out = {}
+
+    # --- a1/a2 pack / unpack ------------------------------------------------
+    codes = torch.randint(0, 16, (4096,), generator=g, dtype=torch.uint8)
+    codes[:32] = torch.arange(32, dtype=torch.uint8) % 16
+    packed = ns["python_compress"](codes.clone())
+    out["pack_codes"] = codes.numpy()
+    out["pack_packed"] = packed.numpy()
+    out["unpack_codes"] = ns["python_decompress"](packed).numpy().reshape(-1)
+
+    # --- a19 group min/max ---------------------------------------------------
+    W = (torch.randn(64, 256, generator=g) * 0.02).to(torch.bfloat16).float()
+    W[3, :128] = 0.0                       # all-zero group -> (-1, +1) rule
+    W[5, 128:] = W[5, 128:].abs()          # all-positive group -> xmin clamps to 0
+    for sym in (False, True):
+        q = qz["Quantizer"]()
+        q.configure(4, perchannel=True, sym=sym, mse=False)
+        q.find_params(W.view(-1, 128), weight=True)
+        out[f"qp_scale_sym{int(sym)}"] = f32(q.scale.reshape(-1))
+        out[f"qp_zero_sym{int(sym)}"] = f32(q.zero.reshape(-1))
+    out["qp_w"] = f32(W)
+    q = qz["Quantizer"]()
+    q.configure(4, perchannel=True, sym=False, mse=False)
+    q.find_params(W.view(-1, 128), weight=True)
+    scales, zeros = q.scale.reshape(-1, 1).clone(), q.zero.reshape(-1, 1).clone()
+    shape = [64, 256]
+
+    # --- a6 without a residual codec (lbit=16 handle), fp32 and bf16 chains --
+    class Plain:
+        dtype = torch.float32
+        data = None
+    codes0 = ns["Qfunc_4bit_g_res"](W.clone(), Plain(), [scales, zeros, shape])
+    out["rq_none_codes_f32"] = codes0.numpy()
+    sb, zb = scales.to(torch.bfloat16), zeros.to(torch.bfloat16)
+    Wb = (W + torch.randn(64, 256, generator=g) * 0.003).to(torch.bfloat16)
+    codes_b = ns["Qfunc_4bit_g_res"](Wb.clone(), Plain(), [sb, zb, shape])
+    out["rq_none_w_bf16"] = f32(Wb)
+    out["rq_none_codes_bf16"] = codes_b.numpy()
+
+    # --- a3 dequant, fp32 and bf16 qparams ----------------------------------
+    out["dq_f32"] = f32(ns["DeQfunc_4bit_g"](codes0, [scales, zeros, shape], torch.float32))
+    out["dq_bf16"] = f32(ns["DeQfunc_4bit_g"](codes0, [sb, zb, shape], torch.bfloat16))
+
+    # --- a12 uniform codec with real noise -----------------------------------
+    r = torch.rand(2048, generator=g) - 0.5
+    r[:8] = torch.tensor([-0.5, 0.5, 0.0, 0.46875, 0.499999, -0.499999, 0.25, -0.03125])
+    torch.manual_seed(77)
+    words, adj = ns["python_quant_linear"](r.clone())
+    torch.manual_seed(77)
+    noise = torch.empty(2048).uniform_(-0.5, 0.5)
+    out["u16_r"], out["u16_noise"] = f32(r), f32(noise)
+    out["u16_words"], out["u16_carry"] = words.numpy(), f32(adj)
+    out["u16_decode"] = f32(ns["python_dequant_linear"](words)).reshape(-1)
+
+    # --- a6 with the residual codec: config-1 style step, fp32 ---------------
+    # latent = dequant(codes0) + delta ; requantize with a12 as the codec
+    Wd = ns["DeQfunc_4bit_g"](codes0, [scales, zeros, shape], torch.float32)
+    delta = torch.randn(64, 256, generator=g) * 1e-4
+    lat = Wd + delta
+    h = ResidualTensor(); h.noise_seed = 4321
+    codes1 = ns["Qfunc_4bit_g_res"](lat.clone(), h, [scales, zeros, shape])
+    torch.manual_seed(4321)
+    noise1 = torch.empty(64 * 256).uniform_(-0.5, 0.5)
+    out["c1_delta"], out["c1_noise1"] = f32(delta), f32(noise1)
+    out["c1_codes0"], out["c1_codes1"] = codes0.numpy(), codes1.numpy()
+    out["c1_words1"] = h.residual_int.numpy()
+    # second step: latent = residual.add(dequant(codes1)) + delta2  (utils/quant.py:831-837)
+    res_fp = ns["python_dequant_linear"](h.residual_int)
+    lat2 = (res_fp.view(-1, 128) * scales).to(torch.float32).view(shape).add(
+        ns["DeQfunc_4bit_g"](codes1, [scales, zeros, shape], torch.float32))
+    delta2 = torch.randn(64, 256, generator=g) * 1e-4
+    lat2 = lat2 + delta2
+    h2 = ResidualTensor(); h2.noise_seed = 999
+    codes2 = ns["Qfunc_4bit_g_res"](lat2.clone(), h2, [scales, zeros, shape])
+    torch.manual_seed(999)
+    noise2 = torch.empty(64 * 256).uniform_(-0.5, 0.5)
+    out["c1_delta2"], out["c1_noise2"] = f32(delta2), f32(noise2)
+    out["c1_codes2"], out["c1_words2"] = codes2.numpy(), h2.residual_int.numpy()
+    X = torch.randn(32, 256, generator=g)
+    out["c1_x"] = f32(X)
+    out["c1_y"] = f32(X.mm(ns["DeQfunc_4bit_g"](codes2, [scales, zeros, shape], torch.float32).t()))
+
+    # --- a13 A8W8 requantize with the residual codec, fp32 -------------------
+    W8 = torch.randn(32, 128, generator=g) * 0.02
+    qs = (W8.abs().amax(dim=1, keepdim=True) / 127.0)
+    h8 = ResidualTensor(); h8.noise_seed = 555
+    c8 = ns["Qfunc_8bit_res"](W8.clone(), h8, qs)
+    torch.manual_seed(555)
+    out["a8_noise"] = f32(torch.empty(32 * 128).uniform_(-0.5, 0.5))
+    out["a8_w"], out["a8_qscales"] = f32(W8), f32(qs.reshape(-1))
+    out["a8_codes"], out["a8_words"] = c8.numpy(), h8.residual_int.numpy()
+    out["a8_codes_none"] = ns["Qfunc_8bit_res"](W8.clone(), None, qs).numpy()
+
+    # --- C.6 optimizer-state codec ------------------------------------------
+    st = torch.randn(4096, generator=g) * 1e-3
+    q8, (sc, tm) = ns["Qfunc_8bit_opt"](st.clone(), blocksize=2)
+    out["o8_x"], out["o8_q"] = f32(st), q8.numpy()
+    out["o8_scale"], out["o8_tmax"] = f32(sc.reshape(-1)), f32(tm.reshape(-1))
+    out["o8_deq"] = f32(ns["DeQfunc_8bit_opt"](q8, [sc, tm]))
+
+    # --- a23 per-token activation quantizer (fake-quant output, fp32) -------
+    A = torch.randn(16, 256, generator=g)
+    A[:, 7] *= 20.0
+    out["aq_x"] = f32(A)
+    out["aq_fake"] = f32(ql["quantize_activation_per_token_absmax"](A.clone()))
+
+    np.savez_compressed(os.path.join(OUT, "reference_vectors.npz"), **out)
+    print("wrote", len(out), "arrays,", os.path.getsize(os.path.join(OUT, "reference_vectors.npz")), "bytes")
+
+
+if __name__ == "__main__":
+    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")

@@ -1,0 +1,177 @@
+/*
+ * liblatentq — C ABI of the B200 (sm_100a) quantized-weight hot path.
+ *
+ * Every entry point takes raw DEVICE pointers plus explicit sizes, launches on
+ * the given CUDA stream (cudaStream_t passed as void*, NULL = default stream),
+ * returns 0 (LQ_OK) or a negative LQ_E* code, never throws, never aborts, and
+ * never retains a pointer.  Nothing is allocated by the library: kernels that
+ * need scratch memory take a caller-provided workspace (size from
+ * lq_gemm_workspace_bytes).  Calls are asynchronous; the caller synchronises.
+ *
+ * Each declaration names the interface of FWkey/latentQ_LLM it replaces
+ * (path:line inside that project).
+ */
+#ifndef LATENTQ_H
+#define LATENTQ_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__)
+#define LQ_API __attribute__((visibility("default")))
+#else
+#define LQ_API
+#endif
+
+typedef void* lq_stream_t; /* cudaStream_t */
+
+enum { LQ_OK = 0, LQ_EINVAL = -1, LQ_EUNSUPPORTED = -2, LQ_ECUDA = -3, LQ_ETIMEOUT = -4, LQ_EWORKSPACE = -5 };
+enum { LQ_F32 = 0, LQ_BF16 = 1 };
+enum { LQ_CODEC_NONE = 0, LQ_CODEC_UNIFORM16 = 1, LQ_CODEC_THREEFOLD = 2 };
+enum { LQ_DITHER_HASH = 0, LQ_DITHER_EXPLICIT = 1, LQ_DITHER_PHILOX = 2 };
+
+LQ_API int lq_version(void);
+LQ_API const char* lq_status_string(int status);
+/* cudaGetLastError-style text of the most recent LQ_ECUDA on this thread. */
+LQ_API const char* lq_last_cuda_error(void);
+
+/* ------------------------------------------------------------------------
+ * Residual codecs: the five functions of the pybind module `MyQuantDequant`
+ * (utils/cuda_src/multi_random_quant.cpp:38-54; kernels
+ * utils/cuda_src/multi_random_quant_kernel.cu:9-334).  `x` holds
+ * 8*n_words elements of dtype LQ_F32 / LQ_BF16; one int32 word packs 8
+ * nibbles, element k at bits 28-4k.  The quantizers overwrite `x` with the
+ * 0/1 carry flags like the reference does.
+ * ------------------------------------------------------------------------ */
+/* `quant`   (multi_random_quant.cpp:13-16, kernel .cu:9-128, launcher :345-361) */
+LQ_API int lq_res3_quant(void* x, int dtype, int32_t* words, int64_t n_words,
+                         int k1, float b1, int k2, float b2, int k3, float v0, lq_stream_t stream);
+/* `dequant` (multi_random_quant.cpp:18-21, kernel .cu:130-217, launcher :384-399) */
+LQ_API int lq_res3_dequant(const int32_t* words, void* x, int dtype, int64_t n_words,
+                           int k1, float b1, int k2, float b2, int k3, lq_stream_t stream);
+/* `uniform_quant`   (multi_random_quant.cpp:23-26, kernel .cu:241-294) */
+LQ_API int lq_resu_quant(void* x, int dtype, int32_t* words, int64_t n_words, float v0, lq_stream_t stream);
+/* `uniform_quant_s` (multi_random_quant.cpp:33-36, kernel .cu:219-239) */
+LQ_API int lq_resu_quant_s(void* x, int dtype, int32_t* words, int64_t n_words, lq_stream_t stream);
+/* `uniform_dequant` (multi_random_quant.cpp:28-31, kernel .cu:297-334) */
+LQ_API int lq_resu_dequant(const int32_t* words, void* x, int dtype, int64_t n_words, lq_stream_t stream);
+/* python_quant_linear / python_dequant_linear (utils/quant.py:765-788): the reference's only
+ * CPU-runnable stochastic codec; `noise` is the U(-0.5,0.5) draw (fp32, n elements). */
+LQ_API int lq_uniform16_encode(const float* r, const float* noise, int64_t n, int32_t* words, float* carry,
+                               lq_stream_t stream);
+LQ_API int lq_uniform16_decode(const int32_t* words, int64_t n_words, float* out, lq_stream_t stream);
+
+/* ------------------------------------------------------------------------
+ * Packing: python_compress / python_decompress (utils/quant.py:4-19; twins in
+ * PTQ/quant/quant_linear.py:400-416).  byte i = (code[2i] << 4) + code[2i+1].
+ * ------------------------------------------------------------------------ */
+LQ_API int lq_pack_nibbles(const uint8_t* codes, int8_t* packed, int64_t n_codes, lq_stream_t stream);
+LQ_API int lq_unpack_nibbles(const int8_t* packed, int8_t* codes, int64_t n_bytes, lq_stream_t stream);
+
+/* DeQfunc_4bit_g (utils/quant.py:66-72).  qparams of dtype qp_dtype, one per `group` elements.
+ * qp_dtype == LQ_BF16 reproduces the bf16 arithmetic of the GPU reference. */
+LQ_API int lq_a16w4_dequant(const int8_t* qweight, const void* scales, const void* zeros, int qp_dtype,
+                            void* out, int out_dtype, int64_t numel, int group, lq_stream_t stream);
+
+/* Quantizer.find_params on x.view(-1, group) (PTQ/quant/quantizer.py:34-74; called per group at
+ * PTQ/gptq.py:114-118): fp32 scale/zero per group; warp-shuffle min/max. */
+LQ_API int lq_find_qparams(const void* x, int dtype, int64_t numel, int group, int maxq, int sym,
+                           float* scales, float* zeros, lq_stream_t stream);
+
+/* ------------------------------------------------------------------------
+ * Latent-weight requantize.
+ * ------------------------------------------------------------------------ */
+typedef struct lq_requant_opts {
+    int32_t codec;          /* LQ_CODEC_*: how the 4-bit residual is coded                      */
+    int32_t dither;         /* LQ_DITHER_*: hash (CUDA reference), explicit buffer, or Philox    */
+    int32_t math_dtype;     /* LQ_F32 / LQ_BF16: dtype the reference chain would run in          */
+    int32_t res_round_bf16; /* cast the residual to bf16 before coding (utils/quant.py:726,737)  */
+    int32_t has_residual;   /* 0 while ResidualTensor.init is True (utils/quant.py:833-836)      */
+    int32_t mu_enc, mu_dec; /* three_fold_curve_4bit level used to encode / decode (:708-716)    */
+    float v0;               /* hash-dither offset (the reference always passes 0, .cu:351)       */
+    uint64_t seed;          /* Philox key                                                        */
+    uint64_t stream_id;     /* Philox counter high words: (optimizer step, parameter id)         */
+    const float* dither_buf;/* LQ_DITHER_EXPLICIT: one fp32 value in [-0.5,0.5] per element      */
+} lq_requant_opts;
+
+/* Qfunc_4bit_g_res (utils/quant.py:45-63): latent `w` -> packed codes + residual words. */
+LQ_API int lq_a16w4_requant(const void* w, int w_dtype, const void* scales, const void* zeros, int qp_dtype,
+                            int64_t numel, int group, const lq_requant_opts* opts,
+                            int8_t* codes_out, int32_t* words_out, lq_stream_t stream);
+/* One fused pass of MyAdam.update_step's weight path (utils/quant.py:1069-1073, 831-837, 1143):
+ * latent = residual.add(DeQfunc_4bit_g(codes)) + delta ; codes, residual = Qfunc_4bit_g_res(latent).
+ * In place on `codes` and `words`. */
+LQ_API int lq_a16w4_fold_delta(int8_t* codes, int32_t* words, const void* delta, int delta_dtype,
+                               const void* scales, const void* zeros, int qp_dtype,
+                               int64_t numel, int group, const lq_requant_opts* opts, lq_stream_t stream);
+/* Qfunc_8bit_res (utils/quant.py:88-103): per-row scale, codes int8 [rows, cols]. */
+LQ_API int lq_a8w8_requant(const void* w, int w_dtype, const void* qscales, int qp_dtype,
+                           int64_t rows, int64_t cols, const lq_requant_opts* opts,
+                           int8_t* codes_out, int32_t* words_out, lq_stream_t stream);
+LQ_API int lq_a8w8_fold_delta(int8_t* codes, int32_t* words, const void* delta, int delta_dtype,
+                              const void* qscales, int qp_dtype, int64_t rows, int64_t cols,
+                              const lq_requant_opts* opts, lq_stream_t stream);
+/* The library's Philox dither stream, materialised (test / debugging aid). */
+LQ_API int lq_philox_dither(uint64_t seed, uint64_t stream_id, int64_t first_word, int64_t n_words, float* out,
+                            lq_stream_t stream);
+
+/* ------------------------------------------------------------------------
+ * 8-bit optimizer-state codec: Qfunc_8bit_opt / DeQfunc_8bit_opt (utils/quant.py:22-41)
+ * with `block` contiguous elements per (scale, t_max) pair (2048 or 128, :1038-1045).
+ * ------------------------------------------------------------------------ */
+LQ_API int lq_opt8_quant(const float* x, int64_t n, int block, uint8_t* q, float* scale, float* tmax,
+                         lq_stream_t stream);
+LQ_API int lq_opt8_dequant(const uint8_t* q, int64_t n, int block, const float* scale, const float* tmax,
+                           float* x, lq_stream_t stream);
+
+/* ------------------------------------------------------------------------
+ * Activation quantizers for the A8W8 path.
+ * ------------------------------------------------------------------------ */
+/* quantize_activation_per_token_absmax (PTQ/quant/quant_linear.py:520-528): bf16 x[M,K] ->
+ * int8 + fp32 scale per token (computed in bf16 like the reference's in-place ops). */
+LQ_API int lq_act_quant_per_token(const void* x, int64_t M, int64_t K, int8_t* x8, float* a_scale,
+                                  lq_stream_t stream);
+/* QLinearFunctionA8W8_dynamic.forward quantizer (utils/quant.py:260-266): clampv = max(x) computed
+ * on device into clampv_out (fp32[1]); x8 = clamp(round(x*127/clampv)). */
+LQ_API int lq_act_quant_per_tensor(const void* x, int64_t n, float* clampv_out, int8_t* x8, lq_stream_t stream);
+
+/* ------------------------------------------------------------------------
+ * GEMMs (tcgen05 / TMEM; TMA-staged operands).  Row-major everywhere.
+ * ------------------------------------------------------------------------ */
+enum { LQ_GEMM_A16W4_FWD = 0, LQ_GEMM_A16W4_DGRAD = 1, LQ_GEMM_A8W8 = 2 };
+/* Bytes of caller-provided scratch the GEMM of that kind/shape may use (split-K partial sums). */
+LQ_API size_t lq_gemm_workspace_bytes(int kind, int64_t M, int64_t N, int64_t K);
+
+/* QLinearFunctionW4.forward (utils/quant.py:116-121): y[M,N] = x[M,K] · deq(qweight)[N,K]ᵀ (+ bias),
+ * deq = DeQfunc_4bit_g with bf16 scales/zeros [N*K/group].  x, y, bias bf16. */
+LQ_API int lq_gemm_a16w4_fwd(const void* x, const int8_t* qweight, const void* scales, const void* zeros,
+                             const void* bias, void* y, int64_t M, int64_t N, int64_t K, int group,
+                             void* workspace, size_t workspace_bytes, lq_stream_t stream);
+/* QLinearFunctionW4.backward grad_input (utils/quant.py:139-140): dx[M,K] = dy[M,N] · deq(qweight)[N,K]. */
+LQ_API int lq_gemm_a16w4_dgrad(const void* dy, const int8_t* qweight, const void* scales, const void* zeros,
+                               void* dx, int64_t M, int64_t N, int64_t K, int group,
+                               void* workspace, size_t workspace_bytes, lq_stream_t stream);
+/* torch_int._CUDA.linear_a8_w8_bbf16_obf16 (call sites utils/quant.py:181-389,
+ * PTQ/quant/quant_linear.py:709-711): x8[M,K] · w8[N,K]ᵀ with int32 accumulation.
+ *   y[m,n] = bf16( acc * row_scale[m] * col_scale[n] * alpha + bias[n] )
+ * row_scale (fp32[M]) / col_scale (fp32[N]) / bias (bf16[N]) may be NULL (treated as 1 / 1 / 0);
+ * alpha alone reproduces the torch_int call.  acc_out (int32[M,N]) may be NULL; when given the
+ * raw accumulators are stored as well. */
+LQ_API int lq_gemm_a8w8(const int8_t* x8, const int8_t* w8, const float* row_scale, const float* col_scale,
+                        float alpha, const void* bias, void* y, int32_t* acc_out,
+                        int64_t M, int64_t N, int64_t K, void* workspace, size_t workspace_bytes,
+                        lq_stream_t stream);
+
+/* Every device-side wait in the GEMM kernels is bounded; when one expires the kernel gives up cleanly and
+ * raises a device flag.  This call synchronises with the device, returns LQ_ETIMEOUT if the flag is set
+ * (LQ_OK otherwise) and clears it when `reset` is non-zero.  (No counterpart in the reference.) */
+LQ_API int lq_gemm_device_status(int reset);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* LATENTQ_H */

@@ -1,0 +1,652 @@
+// tcgen05 / TMEM GEMMs of liblatentq (sm_100a):
+//   A16W4 forward      y[M,N]  = x[M,K]  · deq(Wq)[N,K]^T      (QLinearFunctionW4.forward,  utils/quant.py:116-121)
+//   A16W4 grad-input   dx[M,K] = dy[M,N] · deq(Wq)[N,K]        (QLinearFunctionW4.backward, utils/quant.py:139-140)
+//   A8W8               y[M,N]  = x8[M,K] · w8[N,K]^T, int32 accumulate, scaled epilogue
+//                                                               (torch_int linear_a8_w8_bbf16_obf16 call sites, utils/quant.py:181-389)
+//
+// One persistent, warp-specialised kernel template.  The weight-derived operand is always the MMA "A"
+// operand (128 rows per tile: output features for forward / int8, input features for grad-input), the
+// token-side operand is "B" (16..256 tokens per tile), so the accumulator lives in TMEM as
+// [128 lanes = weight rows] x [tokens] and one dequantised weight tile is reused by up to 256 tokens.
+//
+//   warp 0      : TMA producer   (token tile + raw packed int4 tile, or both int8 tiles)
+//   warp 1      : MMA issuer     (one elected thread issues tcgen05.mma; owns TMEM alloc/dealloc)
+//   warps 2..5  : epilogue       (tcgen05.ld -> scale/bias -> bf16 / partial sums -> global)
+//   warps 6..13 : dequant        (A16W4 only: raw int4 in smem -> bf16((q-z)*s) -> 128B-swizzled MMA tile)
+//
+// Forward and grad-input share the dequant stage: a row of W[N,K] always becomes 128-byte rows of the
+// swizzled tile; forward describes that tile to the tensor core as K-major, grad-input as MN-major.
+//
+// Every mbarrier wait is bounded (clock64 budget).  On expiry the CTA raises an abort flag in shared
+// memory, all roles leave their loops, in-flight bulk copies are given time to land, TMEM is freed and a
+// global status word is set (read back with lq_gemm_device_status).
+#include <cuda.h>
+
+#include "lq_common.cuh"
+
+namespace lq {
+
+enum { KIND_FWD = LQ_GEMM_A16W4_FWD, KIND_DGRAD = LQ_GEMM_A16W4_DGRAD, KIND_I8 = LQ_GEMM_A8W8 };
+
+constexpr int TILE_R = 128;           // weight rows per tile (MMA M)
+constexpr int ROW_BYTES = 128;        // one swizzle row
+constexpr int A_TILE_BYTES = TILE_R * ROW_BYTES;
+constexpr int RAW_BYTES = 4096;       // packed int4 bytes per stage (128 rows x 64 k, or 64 rows x 128 k)
+constexpr int NUM_DQ_WARPS = 8;
+constexpr int MAX_STAGES = 8;
+constexpr long long WAIT_BUDGET_CYCLES = 2000000000LL;   // ~1 s
+
+__device__ int g_gemm_status;   // 0 = fine, 1 = a bounded wait expired in some CTA
+
+// ---------------------------------------------------------------------------------------------
+// PTX wrappers
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+// Bounded wait: false when the budget expired or another role already aborted.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const long long t0 = clock64();
+    for (uint32_t it = 1;; ++it) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((it & 31u) == 0u) {
+            if (*abort_flag) return false;
+            if (clock64() - t0 > WAIT_BUDGET_CYCLES) { *abort_flag = 1; return false; }
+        }
+    }
+}
+__device__ __forceinline__ void fence_barrier_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
+__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* map) {
+    asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
+}
+
+__device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t ncols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+template <bool I8>
+__device__ __forceinline__ void umma(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    if (I8) {
+        asm volatile(
+            "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
+            ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+    } else {
+        asm volatile(
+            "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+            ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+    }
+}
+// 32 lanes x 16 consecutive 32-bit columns -> 16 registers per thread.
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor (sm_100 format): start address, leading / stride byte offsets (all >>4),
+// descriptor version 1 at bit 46, layout type at bits 61-63 (2 = 128-byte swizzle).
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+    uint64_t d = 0;
+    d |= (uint64_t)((saddr >> 4) & 0x3FFFu);
+    d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFFu) << 16;
+    d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFFu) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
+// Instruction descriptor: D format (bits 4-5), A/B formats (7-9 / 10-12), A/B major (15 / 16), N>>3 (17-22), M>>4 (24-28).
+__host__ __device__ constexpr uint32_t make_idesc(bool i8, bool a_mn_major, int n) {
+    return (i8 ? 2u : 1u) << 4 | 1u << 7 | 1u << 10 | (a_mn_major ? 1u : 0u) << 15 | (uint32_t)(n >> 3) << 17 |
+           (uint32_t)(TILE_R >> 4) << 24;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Kernel parameters
+// ---------------------------------------------------------------------------------------------
+struct GemmParams {
+    int M;            // tokens
+    int R;            // weight-side rows of the output (N for fwd / int8, K for dgrad)
+    int C;            // contraction length (K for fwd / int8, N for dgrad)
+    int wcols;        // in-features K of the weight matrix (row length of W)
+    int group;        // A16W4 group size along K
+    int r_tiles, t_tiles, splits, kb_total, kb_per_split;
+    const __nv_bfloat16* scales;   // [N*K/group]
+    const __nv_bfloat16* zeros;
+    const __nv_bfloat16* bias;     // [R] or null
+    const float* row_scale;        // int8: per token, or null
+    const float* col_scale;        // int8: per output channel, or null
+    float alpha;
+    __nv_bfloat16* out;            // [M, R]
+    int32_t* acc_out;              // int8: raw accumulators [M, R] or null
+    void* partial;                 // split-K partial sums [splits][M][R] (fp32 / int32)
+};
+
+template <int KIND, int TN>
+struct Cfg {
+    static constexpr bool I8 = KIND == KIND_I8;
+    static constexpr bool W4 = !I8;
+    static constexpr int B_TILE_BYTES = TN * ROW_BYTES;
+    static constexpr int STAGE_BYTES = A_TILE_BYTES + B_TILE_BYTES + (W4 ? RAW_BYTES : 0);
+    static constexpr int STAGES_FIT = (226 * 1024 - 1024) / STAGE_BYTES;
+    static constexpr int STAGES = STAGES_FIT > MAX_STAGES ? MAX_STAGES : STAGES_FIT;
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+    static constexpr int TMEM_COLS = (2 * TN) < 32 ? 32 : (2 * TN);
+    static constexpr int NUM_WARPS = 6 + (W4 ? NUM_DQ_WARPS : 0);
+    static constexpr int THREADS = NUM_WARPS * 32;
+    static constexpr uint32_t TX_BYTES = (uint32_t)(B_TILE_BYTES + (W4 ? RAW_BYTES : A_TILE_BYTES));
+    static constexpr int UMMA_PER_STAGE = 4;   // 128 bytes of contraction per stage / 32 bytes per MMA
+};
+
+struct SmemCtl {
+    uint64_t full[MAX_STAGES];     // TMA landed
+    uint64_t a_ready[MAX_STAGES];  // dequantised tile written
+    uint64_t empty[MAX_STAGES];    // MMAs that read the stage retired
+    uint64_t acc_full[2];
+    uint64_t acc_empty[2];
+    uint32_t tmem_base;
+    int abort_flag;
+};
+
+// ---------------------------------------------------------------------------------------------
+// int4 -> bf16 dequant of 8 codes held in one little-endian 32-bit word of the nibble-pair layout
+// (byte j = code[2j] << 4 | code[2j+1]).  q+128 is formed exactly by OR-ing the nibble into the mantissa
+// of bf16 128.0; (q+128)-(z+128) and the product with s are single bf16 roundings, i.e. exactly
+// bf16((q - z) * s) as DeQfunc_4bit_g computes it with bf16 qparams.
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t bf2_as_u32(__nv_bfloat162 v) { return *reinterpret_cast<uint32_t*>(&v); }
+__device__ __forceinline__ __nv_bfloat162 u32_as_bf2(uint32_t v) { return *reinterpret_cast<__nv_bfloat162*>(&v); }
+__device__ __forceinline__ uint4 dequant8(uint32_t w, __nv_bfloat162 z128, __nv_bfloat162 s2) {
+    const uint32_t MAGIC = 0x43004300u, MASK = 0x000F000Fu;
+    uint32_t p15 = (w & MASK) | MAGIC;           // (c1, c5)
+    uint32_t p04 = ((w >> 4) & MASK) | MAGIC;    // (c0, c4)
+    uint32_t p37 = ((w >> 8) & MASK) | MAGIC;    // (c3, c7)
+    uint32_t p26 = ((w >> 12) & MASK) | MAGIC;   // (c2, c6)
+    uint32_t d15 = bf2_as_u32(__hmul2(__hsub2(u32_as_bf2(p15), z128), s2));
+    uint32_t d04 = bf2_as_u32(__hmul2(__hsub2(u32_as_bf2(p04), z128), s2));
+    uint32_t d37 = bf2_as_u32(__hmul2(__hsub2(u32_as_bf2(p37), z128), s2));
+    uint32_t d26 = bf2_as_u32(__hmul2(__hsub2(u32_as_bf2(p26), z128), s2));
+    uint4 o;
+    o.x = __byte_perm(d04, d15, 0x5410);   // (c0, c1)
+    o.y = __byte_perm(d26, d37, 0x5410);   // (c2, c3)
+    o.z = __byte_perm(d04, d15, 0x7632);   // (c4, c5)
+    o.w = __byte_perm(d26, d37, 0x7632);   // (c6, c7)
+    return o;
+}
+
+// ---------------------------------------------------------------------------------------------
+// The kernel
+// ---------------------------------------------------------------------------------------------
+template <int KIND, int TN>
+__global__ void __launch_bounds__(Cfg<KIND, TN>::THREADS, 1)
+k_gemm(const __grid_constant__ CUtensorMap map_tok, const __grid_constant__ CUtensorMap map_w, const GemmParams p) {
+    using C = Cfg<KIND, TN>;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    SmemCtl* ctl = reinterpret_cast<SmemCtl*>(smem + C::STAGES * C::STAGE_BYTES);
+    volatile int* abort_flag = &ctl->abort_flag;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t smem_base = smem_u32(smem);
+    auto a_tile = [&](int s) { return smem_base + s * C::STAGE_BYTES; };
+    auto b_tile = [&](int s) { return smem_base + s * C::STAGE_BYTES + A_TILE_BYTES; };
+    auto raw_tile = [&](int s) { return smem + s * C::STAGE_BYTES + A_TILE_BYTES + C::B_TILE_BYTES; };
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < C::STAGES; ++s) {
+            mbar_init(smem_u32(&ctl->full[s]), 1);
+            mbar_init(smem_u32(&ctl->a_ready[s]), NUM_DQ_WARPS);
+            mbar_init(smem_u32(&ctl->empty[s]), 1);
+        }
+        for (int a = 0; a < 2; ++a) {
+            mbar_init(smem_u32(&ctl->acc_full[a]), 1);
+            mbar_init(smem_u32(&ctl->acc_empty[a]), 4);
+        }
+        ctl->abort_flag = 0;
+        fence_barrier_init();
+        fence_proxy_async();
+    }
+    if (warp == 1) {
+        tmem_alloc(smem_u32(&ctl->tmem_base), C::TMEM_COLS);
+        tmem_relinquish();
+    }
+    if (warp == 0 && lane == 0) { tma_prefetch_desc(&map_tok); tma_prefetch_desc(&map_w); }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = ctl->tmem_base;
+
+    const int n_items = p.r_tiles * p.t_tiles * p.splits;
+
+    if (warp == 0) {
+        // ===================== TMA producer =====================
+        if (lane == 0) {
+            int stage = 0; uint32_t phase = 0;
+            bool ok = true;
+            for (int item = blockIdx.x; ok && item < n_items; item += gridDim.x) {
+                const int t_tile = item % p.t_tiles, r_tile = (item / p.t_tiles) % p.r_tiles, split = item / (p.t_tiles * p.r_tiles);
+                const int kb0 = split * p.kb_per_split, kb1 = min(p.kb_total, kb0 + p.kb_per_split);
+                for (int kb = kb0; kb < kb1; ++kb) {
+                    if (!(ok = mbar_wait(smem_u32(&ctl->empty[stage]), phase ^ 1u, abort_flag))) break;
+                    const uint32_t bar = smem_u32(&ctl->full[stage]);
+                    mbar_expect_tx(bar, C::TX_BYTES);
+                    if (KIND == KIND_I8) {
+                        tma_load_2d(a_tile(stage), &map_w, kb * 128, r_tile * TILE_R, bar);
+                        tma_load_2d(b_tile(stage), &map_tok, kb * 128, t_tile * TN, bar);
+                    } else if (KIND == KIND_FWD) {
+                        // raw: 128 weight rows x 32 bytes (64 k)
+                        tma_load_2d(smem_u32(raw_tile(stage)), &map_w, kb * 32, r_tile * TILE_R, bar);
+                        tma_load_2d(b_tile(stage), &map_tok, kb * 64, t_tile * TN, bar);
+                    } else {
+                        // raw: 64 weight rows (n) x 64 bytes (128 k)
+                        tma_load_2d(smem_u32(raw_tile(stage)), &map_w, r_tile * 64, kb * 64, bar);
+                        tma_load_2d(b_tile(stage), &map_tok, kb * 64, t_tile * TN, bar);
+                    }
+                    if (++stage == C::STAGES) { stage = 0; phase ^= 1u; }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ===================== MMA issuer =====================
+        if (lane == 0) {
+            constexpr uint32_t IDESC = make_idesc(C::I8, KIND == KIND_DGRAD, TN);
+            int stage = 0; uint32_t phase = 0;
+            int acc = 0; uint32_t acc_phase = 0;
+            bool ok = true;
+            for (int item = blockIdx.x; ok && item < n_items; item += gridDim.x) {
+                const int split = item / (p.t_tiles * p.r_tiles);
+                const int kb0 = split * p.kb_per_split, kb1 = min(p.kb_total, kb0 + p.kb_per_split);
+                if (!(ok = mbar_wait(smem_u32(&ctl->acc_empty[acc]), acc_phase ^ 1u, abort_flag))) break;
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + (uint32_t)(acc * TN);
+                for (int kb = kb0; kb < kb1; ++kb) {
+                    if (!(ok = mbar_wait(smem_u32(&ctl->full[stage]), phase, abort_flag))) break;
+                    if (C::W4) { if (!(ok = mbar_wait(smem_u32(&ctl->a_ready[stage]), phase, abort_flag))) break; }
+                    tc_fence_after();
+                    // K-major tiles: 8-row groups are 1024 B apart; one MMA consumes 32 B of every row.
+                    // MN-major A (grad-input): 64-element atoms are 8192 B apart (leading), 8-row groups of the
+                    // contraction 1024 B apart (stride); one MMA consumes 16 contraction rows = 2048 B.
+                    const uint64_t a_desc = (KIND == KIND_DGRAD) ? make_smem_desc(a_tile(stage), 8192, 1024)
+                                                                 : make_smem_desc(a_tile(stage), 16, 1024);
+                    const uint64_t b_desc = make_smem_desc(b_tile(stage), 16, 1024);
+                    const uint32_t a_step = (KIND == KIND_DGRAD) ? (2048u >> 4) : (32u >> 4);
+#pragma unroll
+                    for (int kk = 0; kk < C::UMMA_PER_STAGE; ++kk) {
+                        umma<C::I8>(d_tmem, a_desc + (uint64_t)(kk * a_step), b_desc + (uint64_t)(kk * 2),
+                                    IDESC, (kb > kb0 || kk > 0) ? 1u : 0u);
+                    }
+                    umma_commit(smem_u32(&ctl->empty[stage]));
+                    if (++stage == C::STAGES) { stage = 0; phase ^= 1u; }
+                }
+                if (!ok) break;
+                umma_commit(smem_u32(&ctl->acc_full[acc]));
+                if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+            }
+        }
+    } else if (warp < 6) {
+        // ===================== epilogue =====================
+        const int quad = warp & 3;                 // TMEM lane quadrant this warp may read
+        int acc = 0; uint32_t acc_phase = 0;
+        bool ok = true;
+        for (int item = blockIdx.x; ok && item < n_items; item += gridDim.x) {
+            const int t_tile = item % p.t_tiles, r_tile = (item / p.t_tiles) % p.r_tiles, split = item / (p.t_tiles * p.r_tiles);
+            if (!(ok = mbar_wait(smem_u32(&ctl->acc_full[acc]), acc_phase, abort_flag))) break;
+            tc_fence_after();
+            const int r = r_tile * TILE_R + quad * 32 + lane;
+            const bool r_ok = r < p.R;
+            const float cs = (C::I8 && p.col_scale && r_ok) ? __ldg(p.col_scale + r) : 1.0f;
+            const float bias = (p.bias && r_ok) ? __bfloat162float(p.bias[r]) : 0.0f;
+#pragma unroll 1
+            for (int c0 = 0; c0 < TN; c0 += 16) {
+                uint32_t v[16];
+                tmem_ld16(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * TN + c0), v);
+                tmem_ld_wait();
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                    const int t = t_tile * TN + c0 + j;
+                    if (!r_ok || t >= p.M) continue;
+                    const size_t o = (size_t)t * p.R + r;
+                    if (p.splits > 1) {
+                        reinterpret_cast<uint32_t*>(p.partial)[(size_t)split * p.M * p.R + o] = v[j];
+                    } else if (C::I8) {
+                        const int32_t a = (int32_t)v[j];
+                        if (p.acc_out) p.acc_out[o] = a;
+                        float f = (float)a;
+                        if (p.row_scale) f = __fmul_rn(f, __ldg(p.row_scale + t));
+                        f = __fmul_rn(__fmul_rn(f, cs), p.alpha);
+                        p.out[o] = __float2bfloat16_rn(__fadd_rn(f, bias));
+                    } else {
+                        float f = bf16r(__uint_as_float(v[j]));          // mm output is bf16, bias added after
+                        p.out[o] = __float2bfloat16_rn(p.bias ? __fadd_rn(f, bias) : f);
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&ctl->acc_empty[acc]));
+            if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+        }
+    } else {
+        // ===================== dequant (A16W4) =====================
+        if (C::W4) {
+            const int t = threadIdx.x - 6 * 32;          // 0..255, one 16-byte slice of the raw tile each
+            int stage = 0; uint32_t phase = 0;
+            bool ok = true;
+            const int groups_per_row = p.wcols / p.group;
+            for (int item = blockIdx.x; ok && item < n_items; item += gridDim.x) {
+                const int r_tile = (item / p.t_tiles) % p.r_tiles, split = item / (p.t_tiles * p.r_tiles);
+                const int kb0 = split * p.kb_per_split, kb1 = min(p.kb_total, kb0 + p.kb_per_split);
+                for (int kb = kb0; kb < kb1; ++kb) {
+                    // which weight row / k range this thread converts
+                    int wrow, k_abs, dst_off;
+                    if (KIND == KIND_FWD) {
+                        const int row = t >> 1, half = t & 1;
+                        wrow = r_tile * TILE_R + row;
+                        k_abs = kb * 64 + half * 32;
+                        dst_off = row * ROW_BYTES;
+                    } else {
+                        const int row = t >> 2, q = t & 3;                  // row = contraction index n within the stage
+                        wrow = kb * 64 + row;
+                        k_abs = r_tile * TILE_R + q * 32;
+                        dst_off = (q >> 1) * 8192 + row * ROW_BYTES;
+                    }
+                    const int swz = (KIND == KIND_FWD) ? ((t >> 1) & 7) : ((t >> 2) & 7);
+                    const int chunk0 = (KIND == KIND_FWD) ? (t & 1) * 4 : (t & 1) * 4;
+                    float sf = 0.0f, zf = 0.0f;
+                    const int n_rows = (KIND == KIND_FWD) ? p.R : p.C;
+                    if (wrow < n_rows && k_abs < p.wcols) {
+                        const size_t gi = (size_t)wrow * groups_per_row + (size_t)(k_abs / p.group);
+                        sf = __bfloat162float(p.scales[gi]);
+                        zf = __bfloat162float(p.zeros[gi]);
+                    }
+                    const __nv_bfloat162 s2 = __float2bfloat162_rn(sf);
+                    const __nv_bfloat162 z128 = __float2bfloat162_rn(zf + 128.0f);
+                    if (!(ok = mbar_wait(smem_u32(&ctl->full[stage]), phase, abort_flag))) break;
+                    const uint4 rawv = *reinterpret_cast<const uint4*>(raw_tile(stage) + t * 16);
+                    uint8_t* dst = smem + stage * C::STAGE_BYTES + dst_off;
+                    const uint32_t wv[4] = {rawv.x, rawv.y, rawv.z, rawv.w};
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const uint4 o = dequant8(wv[j], z128, s2);
+                        *reinterpret_cast<uint4*>(dst + (((chunk0 + j) ^ swz) << 4)) = o;
+                    }
+                    fence_proxy_async();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(smem_u32(&ctl->a_ready[stage]));
+                    if (++stage == C::STAGES) { stage = 0; phase ^= 1u; }
+                }
+            }
+        }
+    }
+
+    // ===================== teardown =====================
+    tc_fence_before();
+    __syncthreads();
+    if (*abort_flag) {
+        // give bulk copies that may still be in flight time to land before the CTA's shared memory is released
+        const long long t0 = clock64();
+        while (clock64() - t0 < 2000000LL) __nanosleep(1000);
+        if (threadIdx.x == 0) atomicExch(&g_gemm_status, 1);
+        __syncthreads();
+    }
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, C::TMEM_COLS);
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// split-K reduction
+// ---------------------------------------------------------------------------------------------
+template <bool I8>
+__global__ void __launch_bounds__(256) k_splitk_reduce(const GemmParams p) {
+    const int64_t total = (int64_t)p.M * p.R;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int r = (int)(i % p.R);
+        const int t = (int)(i / p.R);
+        if (I8) {
+            int32_t a = 0;
+            for (int s = 0; s < p.splits; ++s) a += reinterpret_cast<const int32_t*>(p.partial)[(size_t)s * total + i];
+            if (p.acc_out) p.acc_out[i] = a;
+            float f = (float)a;
+            if (p.row_scale) f = __fmul_rn(f, __ldg(p.row_scale + t));
+            f = __fmul_rn(__fmul_rn(f, p.col_scale ? __ldg(p.col_scale + r) : 1.0f), p.alpha);
+            p.out[i] = __float2bfloat16_rn(__fadd_rn(f, p.bias ? __bfloat162float(p.bias[r]) : 0.0f));
+        } else {
+            float a = 0.0f;
+            for (int s = 0; s < p.splits; ++s) a = __fadd_rn(a, reinterpret_cast<const float*>(p.partial)[(size_t)s * total + i]);
+            float f = bf16r(a);
+            p.out[i] = __float2bfloat16_rn(p.bias ? __fadd_rn(f, __bfloat162float(p.bias[r])) : f);
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Host side: plan, tensor maps, launch
+// ---------------------------------------------------------------------------------------------
+struct Plan { int tn, r_tiles, t_tiles, splits, kb_total, kb_per_split; };
+
+static Plan make_plan(int kind, int64_t M, int64_t N, int64_t K) {
+    Plan pl{};
+    const int64_t R = (kind == KIND_DGRAD) ? K : N;
+    const int64_t Cc = (kind == KIND_DGRAD) ? N : K;
+    pl.tn = M <= 16 ? 16 : (M <= 64 ? 64 : (M <= 128 ? 128 : 256));
+    pl.r_tiles = (int)((R + TILE_R - 1) / TILE_R);
+    pl.t_tiles = (int)((M + pl.tn - 1) / pl.tn);
+    const int bk = (kind == KIND_I8) ? 128 : 64;
+    pl.kb_total = (int)((Cc + bk - 1) / bk);
+    const int tiles = pl.r_tiles * pl.t_tiles;
+    const int sms = sm_count();
+    int splits = 1;
+    if (tiles * 2 <= sms) {
+        splits = sms / tiles;
+        if (splits > pl.kb_total / 4) splits = pl.kb_total / 4;   // at least 4 k-blocks per item
+        if (splits > 16) splits = 16;
+        if (splits < 1) splits = 1;
+    }
+    pl.kb_per_split = (pl.kb_total + splits - 1) / splits;
+    pl.splits = (pl.kb_total + pl.kb_per_split - 1) / pl.kb_per_split;
+    return pl;
+}
+
+typedef CUresult (*PFN_encodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                    const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                    CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static PFN_encodeTiled get_encode() {
+    static PFN_encodeTiled fn = nullptr;
+    if (!fn) {
+        void* f = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<PFN_encodeTiled>(f);
+    }
+    return fn;
+}
+// 2-D row-major tensor [rows, cols] of `elt` bytes; box [box_rows, box_cols].
+static int make_map(CUtensorMap* m, const void* base, CUtensorMapDataType dt, int elt, uint64_t rows, uint64_t cols,
+                    uint32_t box_rows, uint32_t box_cols, bool swizzle128) {
+    PFN_encodeTiled enc = get_encode();
+    if (!enc) return LQ_ECUDA;
+    cuuint64_t dims[2] = {cols, rows};
+    cuuint64_t strides[1] = {cols * (uint64_t)elt};
+    cuuint32_t box[2] = {box_cols, box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = enc(m, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                     swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                     CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) { set_cuda_error(cudaErrorInvalidValue, "cuTensorMapEncodeTiled"); return LQ_ECUDA; }
+    return LQ_OK;
+}
+
+template <int KIND, int TN>
+static int launch_tn(const CUtensorMap& mt, const CUtensorMap& mw, const GemmParams& p, cudaStream_t st) {
+    using C = Cfg<KIND, TN>;
+    static bool attr_done[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev >= 0 && dev < 64 && !attr_done[dev]) {
+        cudaError_t e = cudaFuncSetAttribute(k_gemm<KIND, TN>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
+        if (e != cudaSuccess) { set_cuda_error(e, "cudaFuncSetAttribute"); return LQ_ECUDA; }
+        attr_done[dev] = true;
+    }
+    const int items = p.r_tiles * p.t_tiles * p.splits;
+    const int grid = items < sm_count() ? items : sm_count();
+    k_gemm<KIND, TN><<<grid, C::THREADS, C::SMEM_BYTES, st>>>(mt, mw, p);
+    int rc = check_launch("k_gemm");
+    if (rc) return rc;
+    if (p.splits > 1) {
+        const int64_t total = (int64_t)p.M * p.R;
+        int g = (int)((total + 255) / 256);
+        if (g > sm_count() * 8) g = sm_count() * 8;
+        k_splitk_reduce<KIND == KIND_I8><<<g, 256, 0, st>>>(p);
+        rc = check_launch("k_splitk_reduce");
+    }
+    return rc;
+}
+template <int KIND>
+static int launch_kind(int tn, const CUtensorMap& mt, const CUtensorMap& mw, const GemmParams& p, cudaStream_t st) {
+    switch (tn) {
+        case 16: return launch_tn<KIND, 16>(mt, mw, p, st);
+        case 64: return launch_tn<KIND, 64>(mt, mw, p, st);
+        case 128: return launch_tn<KIND, 128>(mt, mw, p, st);
+        case 256: return launch_tn<KIND, 256>(mt, mw, p, st);
+    }
+    return LQ_EUNSUPPORTED;
+}
+
+static inline bool al16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+static int run_gemm(int kind, const void* tok, const void* w, GemmParams p, int64_t M, int64_t N, int64_t K,
+                    void* workspace, size_t workspace_bytes, cudaStream_t st) {
+    if (M == 0) return LQ_OK;
+    const Plan pl = make_plan(kind, M, N, K);
+    p.M = (int)M; p.R = (int)((kind == KIND_DGRAD) ? K : N); p.C = (int)((kind == KIND_DGRAD) ? N : K);
+    p.wcols = (int)K;
+    p.r_tiles = pl.r_tiles; p.t_tiles = pl.t_tiles; p.splits = pl.splits; p.kb_total = pl.kb_total; p.kb_per_split = pl.kb_per_split;
+    if (pl.splits > 1) {
+        const size_t need = (size_t)pl.splits * (size_t)M * (size_t)p.R * 4;
+        if (!workspace || workspace_bytes < need || !al16(workspace)) return LQ_EWORKSPACE;
+        p.partial = workspace;
+    }
+    CUtensorMap mt, mw;
+    int rc;
+    if (kind == KIND_I8) {
+        rc = make_map(&mt, tok, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, (uint64_t)M, (uint64_t)K, (uint32_t)pl.tn, 128, true);
+        if (rc) return rc;
+        rc = make_map(&mw, w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, (uint64_t)N, (uint64_t)K, TILE_R, 128, true);
+    } else {
+        rc = make_map(&mt, tok, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)M, (uint64_t)p.C, (uint32_t)pl.tn, 64, true);
+        if (rc) return rc;
+        if (kind == KIND_FWD)   // packed bytes [N, K/2]; box 128 rows x 32 bytes
+            rc = make_map(&mw, w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, (uint64_t)N, (uint64_t)(K / 2), TILE_R, 32, false);
+        else                    // box 64 rows x 64 bytes
+            rc = make_map(&mw, w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, (uint64_t)N, (uint64_t)(K / 2), 64, 64, false);
+    }
+    if (rc) return rc;
+    switch (kind) {
+        case KIND_FWD: return launch_kind<KIND_FWD>(pl.tn, mt, mw, p, st);
+        case KIND_DGRAD: return launch_kind<KIND_DGRAD>(pl.tn, mt, mw, p, st);
+        case KIND_I8: return launch_kind<KIND_I8>(pl.tn, mt, mw, p, st);
+    }
+    return LQ_EINVAL;
+}
+
+}  // namespace lq
+
+using namespace lq;
+
+extern "C" {
+
+size_t lq_gemm_workspace_bytes(int kind, int64_t M, int64_t N, int64_t K) {
+    if (kind < 0 || kind > 2 || M <= 0 || N <= 0 || K <= 0) return 0;
+    const Plan pl = make_plan(kind, M, N, K);
+    if (pl.splits <= 1) return 0;
+    const int64_t R = (kind == KIND_DGRAD) ? K : N;
+    return (size_t)pl.splits * (size_t)M * (size_t)R * 4;
+}
+
+static bool shape_ok_w4(int64_t M, int64_t N, int64_t K, int group) {
+    return M >= 0 && N > 0 && K > 0 && M < (1 << 30) && N < (1 << 30) && K < (1 << 30) && group >= 32 && (group % 32) == 0 &&
+           (K % group) == 0 && (K % 128) == 0 && (N % 64) == 0;
+}
+
+int lq_gemm_a16w4_fwd(const void* x, const int8_t* qweight, const void* scales, const void* zeros, const void* bias, void* y,
+                      int64_t M, int64_t N, int64_t K, int group, void* workspace, size_t workspace_bytes, lq_stream_t stream) {
+    if (!x || !qweight || !scales || !zeros || !y || !al16(x) || !al16(qweight) || !al16(y)) return LQ_EINVAL;
+    if (!shape_ok_w4(M, N, K, group)) return LQ_EUNSUPPORTED;
+    GemmParams p{};
+    p.group = group; p.scales = (const __nv_bfloat16*)scales; p.zeros = (const __nv_bfloat16*)zeros;
+    p.bias = (const __nv_bfloat16*)bias; p.out = (__nv_bfloat16*)y; p.alpha = 1.0f;
+    return run_gemm(KIND_FWD, x, qweight, p, M, N, K, workspace, workspace_bytes, (cudaStream_t)stream);
+}
+
+int lq_gemm_a16w4_dgrad(const void* dy, const int8_t* qweight, const void* scales, const void* zeros, void* dx, int64_t M,
+                        int64_t N, int64_t K, int group, void* workspace, size_t workspace_bytes, lq_stream_t stream) {
+    if (!dy || !qweight || !scales || !zeros || !dx || !al16(dy) || !al16(qweight) || !al16(dx)) return LQ_EINVAL;
+    if (!shape_ok_w4(M, N, K, group) || (group % 128) != 0 && (128 % group) != 0) return LQ_EUNSUPPORTED;
+    GemmParams p{};
+    p.group = group; p.scales = (const __nv_bfloat16*)scales; p.zeros = (const __nv_bfloat16*)zeros;
+    p.out = (__nv_bfloat16*)dx; p.alpha = 1.0f;
+    return run_gemm(KIND_DGRAD, dy, qweight, p, M, N, K, workspace, workspace_bytes, (cudaStream_t)stream);
+}
+
+int lq_gemm_a8w8(const int8_t* x8, const int8_t* w8, const float* row_scale, const float* col_scale, float alpha,
+                 const void* bias, void* y, int32_t* acc_out, int64_t M, int64_t N, int64_t K, void* workspace,
+                 size_t workspace_bytes, lq_stream_t stream) {
+    if (!x8 || !w8 || !y || !al16(x8) || !al16(w8)) return LQ_EINVAL;
+    if (M < 0 || N <= 0 || K <= 0 || M >= (1 << 30) || N >= (1 << 30) || K >= (1 << 30) || (K % 128) != 0) return LQ_EUNSUPPORTED;
+    GemmParams p{};
+    p.row_scale = row_scale; p.col_scale = col_scale; p.alpha = alpha; p.bias = (const __nv_bfloat16*)bias;
+    p.out = (__nv_bfloat16*)y; p.acc_out = acc_out;
+    return run_gemm(KIND_I8, x8, w8, p, M, N, K, workspace, workspace_bytes, (cudaStream_t)stream);
+}
+
+int lq_gemm_device_status(int reset) {
+    int v = 0;
+    cudaError_t e = cudaMemcpyFromSymbol(&v, g_gemm_status, sizeof(int));
+    if (e != cudaSuccess) { set_cuda_error(e, "lq_gemm_device_status"); return LQ_ECUDA; }
+    if (reset && v) { int z = 0; cudaMemcpyToSymbol(g_gemm_status, &z, sizeof(int)); }
+    return v ? LQ_ETIMEOUT : LQ_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,721 @@
+// HBM-streaming kernels of liblatentq: residual codecs, nibble packing, group dequant, group min/max,
+// latent-weight requantize (A16W4 / A8W8), 8-bit optimizer-state codec, activation quantizers.
+//
+// Bit-exactness: every expression that the reference evaluates as separately rounded fp32 (or bf16)
+// operations is written with __f*_rn intrinsics so that nvcc cannot contract it; where the CUDA
+// reference's own source is contractable under nvcc defaults (`a*b+c`), __fmaf_rn is used.
+#include <mutex>
+#include <string>
+
+#include "lq_common.cuh"
+
+namespace lq {
+
+static thread_local std::string g_last_error;
+void set_cuda_error(cudaError_t e, const char* where) {
+    g_last_error = std::string(where) + ": " + cudaGetErrorString(e);
+}
+int check_launch(const char* where) {
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) { set_cuda_error(e, where); return LQ_ECUDA; }
+    return LQ_OK;
+}
+int sm_count() {
+    static int cached[64];
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+    if (cached[dev] == 0) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+        cached[dev] = n;
+    }
+    return cached[dev];
+}
+
+static inline bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }
+static inline int grid_for(int64_t work_items, int threads, int ctas_per_sm) {
+    int64_t want = (work_items + threads - 1) / threads;
+    int64_t cap = (int64_t)sm_count() * ctas_per_sm;
+    if (want < 1) want = 1;
+    return (int)(want < cap ? want : cap);
+}
+
+// ---- 8-element vector load / store in the tensor's dtype -------------------------------------
+__device__ __forceinline__ void load8(const void* base, int dtype, int64_t e0, float (&v)[8]) {
+    if (dtype == LQ_BF16) {
+        uint4 u = __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(base) + e0));
+        uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            v[2 * i] = __uint_as_float(w[i] << 16);
+            v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+        }
+    } else {
+        const float4* p = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(base) + e0);
+        float4 a = __ldg(p), b = __ldg(p + 1);
+        v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+    }
+}
+__device__ __forceinline__ void store8(void* base, int dtype, int64_t e0, const float (&v)[8]) {
+    if (dtype == LQ_BF16) {
+        uint32_t w[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) w[i] = f32_to_bf16_bits(v[2 * i]) | (f32_to_bf16_bits(v[2 * i + 1]) << 16);
+        *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(base) + e0) = make_uint4(w[0], w[1], w[2], w[3]);
+    } else {
+        float4* p = reinterpret_cast<float4*>(reinterpret_cast<float*>(base) + e0);
+        p[0] = make_float4(v[0], v[1], v[2], v[3]);
+        p[1] = make_float4(v[4], v[5], v[6], v[7]);
+    }
+}
+__device__ __forceinline__ float load1(const void* base, int dtype, int64_t i) {
+    return dtype == LQ_BF16 ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(base)[i])
+                            : __ldg(reinterpret_cast<const float*>(base) + i);
+}
+
+// =================================================================================================
+// Residual codecs (MyQuantDequant's five functions)
+// =================================================================================================
+enum { RQ_3FOLD = 0, RQ_UNIFORM = 1, RQ_UNIFORM_S = 2 };
+
+template <int MODE>
+__global__ void __launch_bounds__(256) k_res_quant(void* x, int dtype, int32_t* __restrict__ words, int64_t n_words,
+                                                   Curve c, float v0) {
+    for (int64_t w = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; w < n_words; w += (int64_t)gridDim.x * blockDim.x) {
+        float v[8], flag[8];
+        load8(x, dtype, w * 8, v);
+        uint32_t word = 0;
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            uint32_t nib;
+            if (MODE == RQ_3FOLD) {
+                nib = res3_encode(v[k], hash_dither(v[k], v0), c, flag[k]);
+            } else {
+                float q;
+                if (MODE == RQ_UNIFORM) {   // .cu:257-260: dither sign is round(v) - v
+                    float d = __fmaf_rn(fabsf(v[k]), 499.0f, v0);
+                    d = __fsub_rn(roundf(d), d);
+                    q = roundf(__fmaf_rn(v[k], 8.0f, d));
+                } else {                    // .cu:233
+                    q = roundf(__fmul_rn(v[k], 8.0f));
+                }
+                if (q > 7.5f) { nib = 1u; flag[k] = 1.0f; }
+                else { float t = q + 8.0f; nib = (t <= 0.0f) ? 0u : (uint32_t)t; flag[k] = 0.0f; }
+            }
+            word = (word << 4) | (nib & 15u);
+        }
+        words[w] = (int32_t)word;
+        store8(x, dtype, w * 8, flag);
+    }
+}
+
+template <int MODE>
+__global__ void __launch_bounds__(256) k_res_dequant(const int32_t* __restrict__ words, void* x, int dtype,
+                                                     int64_t n_words, Curve c) {
+    for (int64_t w = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; w < n_words; w += (int64_t)gridDim.x * blockDim.x) {
+        uint32_t word = (uint32_t)__ldg(words + w);
+        float v[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            uint32_t nib = (word >> (28 - 4 * k)) & 15u;
+            v[k] = (MODE == RQ_3FOLD) ? res3_decode(nib, c) : __fmul_rn((float)((int)nib - 8), 0.125f);
+        }
+        store8(x, dtype, w * 8, v);
+    }
+}
+
+__global__ void __launch_bounds__(256) k_uniform16_encode(const float* __restrict__ r, const float* __restrict__ noise,
+                                                          int64_t n_words, int32_t* __restrict__ words,
+                                                          float* __restrict__ carry) {
+    for (int64_t w = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; w < n_words; w += (int64_t)gridDim.x * blockDim.x) {
+        float v[8], u[8], c[8];
+        load8(r, LQ_F32, w * 8, v);
+        load8(noise, LQ_F32, w * 8, u);
+        uint32_t word = 0;
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            float d = __fmul_rn(__fadd_rn(v[k], 0.5f), 16.0f);
+            d = rintf(__fadd_rn(d, u[k]));
+            c[k] = 0.0f;
+            if (d > 15.9f) { d = 0.0f; c[k] = 1.0f; }
+            word = (word << 4) | ((uint32_t)(int)d & 15u);
+        }
+        words[w] = (int32_t)word;
+        if (carry) store8(carry, LQ_F32, w * 8, c);
+    }
+}
+__global__ void __launch_bounds__(256) k_uniform16_decode(const int32_t* __restrict__ words, int64_t n_words,
+                                                          float* __restrict__ out) {
+    for (int64_t w = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; w < n_words; w += (int64_t)gridDim.x * blockDim.x) {
+        uint32_t word = (uint32_t)__ldg(words + w);
+        float v[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) v[k] = __fmaf_rn((float)((word >> (28 - 4 * k)) & 15u), 0.0625f, -0.5f);
+        store8(out, LQ_F32, w * 8, v);
+    }
+}
+
+// =================================================================================================
+// Nibble packing
+// =================================================================================================
+__global__ void __launch_bounds__(256) k_pack_nibbles(const uint8_t* __restrict__ codes, int8_t* __restrict__ packed,
+                                                      int64_t n_bytes) {
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n_bytes; i += (int64_t)gridDim.x * blockDim.x) {
+        uchar2 c = __ldg(reinterpret_cast<const uchar2*>(codes) + i);
+        packed[i] = (int8_t)(uint8_t)((uint32_t)(c.x << 4) + c.y);   // int8 wrap-around like the reference
+    }
+}
+__global__ void __launch_bounds__(256) k_unpack_nibbles(const int8_t* __restrict__ packed, int8_t* __restrict__ codes,
+                                                        int64_t n_bytes) {
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n_bytes; i += (int64_t)gridDim.x * blockDim.x) {
+        uint32_t b = (uint8_t)__ldg(packed + i);
+        reinterpret_cast<uchar2*>(codes)[i] = make_uchar2((unsigned char)(b >> 4), (unsigned char)(b & 15u));
+    }
+}
+
+// =================================================================================================
+// Group dequant (DeQfunc_4bit_g)
+// =================================================================================================
+template <bool BF>
+__global__ void __launch_bounds__(256) k_a16w4_dequant(const uint32_t* __restrict__ packed, const void* scales,
+                                                       const void* zeros, int qp_dtype, void* out, int out_dtype,
+                                                       int64_t n_words, int64_t group) {
+    for (int64_t w = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; w < n_words; w += (int64_t)gridDim.x * blockDim.x) {
+        int64_t g = (w * 8) / group;
+        float s = load1(scales, qp_dtype, g), z = load1(zeros, qp_dtype, g);
+        uint32_t p = __ldg(packed + w);
+        float v[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            // byte k/2 of the word; even element = high nibble
+            uint32_t code = (p >> (8 * (k >> 1) + ((k & 1) ? 0 : 4))) & 15u;
+            v[k] = rnd<BF>(__fmul_rn(rnd<BF>(__fsub_rn((float)code, z)), s));
+        }
+        store8(out, out_dtype, w * 8, v);
+    }
+}
+
+// =================================================================================================
+// Group min/max -> (scale, zero)   (Quantizer.find_params)
+// =================================================================================================
+__global__ void __launch_bounds__(256) k_find_qparams(const void* x, int dtype, int64_t n_groups, int group, float maxq,
+                                                      int sym, float* __restrict__ scales, float* __restrict__ zeros) {
+    const int lane = threadIdx.x & 31;
+    const int64_t warp = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int64_t n_warps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+    for (int64_t g = warp; g < n_groups; g += n_warps) {
+        float mn = 0.0f, mx = 0.0f;                      // xmin = min(min, 0), xmax = max(max, 0)
+        for (int e = lane * 8; e < group; e += 256) {
+            float v[8];
+            load8(x, dtype, g * group + e, v);
+#pragma unroll
+            for (int k = 0; k < 8; ++k) { mn = fminf(mn, v[k]); mx = fmaxf(mx, v[k]); }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            mn = fminf(mn, __shfl_xor_sync(0xffffffffu, mn, o));
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+        }
+        if (lane == 0) {
+            if (sym) { mx = fmaxf(fabsf(mn), mx); if (mn < 0.0f) mn = -mx; }
+            if (mn == 0.0f && mx == 0.0f) { mn = -1.0f; mx = 1.0f; }
+            float s = __fdiv_rn(__fsub_rn(mx, mn), maxq);
+            scales[g] = s;
+            zeros[g] = sym ? __fmul_rn(maxq + 1.0f, 0.5f) : rintf(__fdiv_rn(-mn, s));
+        }
+    }
+}
+
+// =================================================================================================
+// Latent-weight requantize
+// =================================================================================================
+struct RequantParams {
+    const void* w_in; int w_dtype;
+    const void* codes_in; const int32_t* words_in;
+    const void* delta; int delta_dtype;
+    const void* scales; const void* zeros; int qp_dtype;
+    int64_t n_words; int64_t group; int group_shift;
+    void* codes_out; int32_t* words_out;
+    Curve enc, dec;
+    float v0; uint64_t seed, stream_id; const float* dither_buf;
+    int has_residual, res_round_bf16;
+};
+
+// WBITS 4: codes are nibble pairs (4 bytes per 8 elements), zero point per group, clamp [0,15].
+// WBITS 8: codes are int8 (8 bytes per 8 elements), no zero point, clamp [-128,127].
+template <int WBITS, int CODEC, int DITHER, bool BF>
+__global__ void __launch_bounds__(256) k_requant(const RequantParams p) {
+    for (int64_t w = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; w < p.n_words; w += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t e0 = w * 8;
+        const int64_t g = p.group_shift >= 0 ? (e0 >> p.group_shift) : (e0 / p.group);
+        const float s = load1(p.scales, p.qp_dtype, g);
+        const float z = (WBITS == 4) ? load1(p.zeros, p.qp_dtype, g) : 0.0f;
+        const float rs = __frcp_rn(s);
+        const bool s_ok = fastdiv_ok_scale(s);
+
+        float lat[8];
+        if (p.w_in) {
+            load8(p.w_in, p.w_dtype, e0, lat);
+        } else {
+            int code[8];
+            if (WBITS == 4) {
+                uint32_t pk = __ldg(reinterpret_cast<const uint32_t*>(p.codes_in) + w);
+#pragma unroll
+                for (int k = 0; k < 8; ++k) code[k] = (int)((pk >> (8 * (k >> 1) + ((k & 1) ? 0 : 4))) & 15u);
+            } else {
+                uint2 pk = __ldg(reinterpret_cast<const uint2*>(p.codes_in) + w);
+#pragma unroll
+                for (int k = 0; k < 8; ++k) code[k] = (int)(int8_t)(((k < 4 ? pk.x : pk.y) >> (8 * (k & 3))) & 0xffu);
+            }
+#pragma unroll
+            for (int k = 0; k < 8; ++k) lat[k] = rnd<BF>(__fmul_rn(rnd<BF>(__fsub_rn((float)code[k], z)), s));
+            if (CODEC != LQ_CODEC_NONE && p.has_residual) {
+                uint32_t rw = (uint32_t)__ldg(p.words_in + w);
+#pragma unroll
+                for (int k = 0; k < 8; ++k) {
+                    uint32_t nib = (rw >> (28 - 4 * k)) & 15u;
+                    float rv = (CODEC == LQ_CODEC_UNIFORM16) ? __fmaf_rn((float)nib, 0.0625f, -0.5f)
+                                                              : bf16r(res3_decode(nib, p.dec));
+                    lat[k] = rnd<BF>(__fadd_rn(rnd<BF>(__fmul_rn(rv, s)), lat[k]));
+                }
+            }
+            if (p.delta) {
+                float d[8];
+                load8(p.delta, p.delta_dtype, e0, d);
+#pragma unroll
+                for (int k = 0; k < 8; ++k) lat[k] = rnd<BF>(__fadd_rn(lat[k], d[k]));
+            }
+        }
+
+        float u[8];
+        if (CODEC != LQ_CODEC_NONE) {
+            if (DITHER == LQ_DITHER_EXPLICIT) load8(p.dither_buf, LQ_F32, e0, u);
+            else if (DITHER == LQ_DITHER_PHILOX) philox_dither8(p.seed, p.stream_id, (uint64_t)w, u);
+        }
+
+        uint32_t rword = 0, q[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            float Z = rnd<BF>(div_rn(lat[k], s, rs, s_ok));
+            if (WBITS == 4) Z = rnd<BF>(__fadd_rn(Z, z));
+            float qf = rintf(Z);
+            float r = rnd<BF>(__fsub_rn(Z, qf));
+            float carry = 0.0f;
+            uint32_t nib = 0;
+            if (CODEC != LQ_CODEC_NONE) {
+                if (p.res_round_bf16) r = bf16r(r);
+                if (CODEC == LQ_CODEC_UNIFORM16) {
+                    float d = rintf(__fadd_rn(__fmul_rn(__fadd_rn(r, 0.5f), 16.0f), u[k]));
+                    if (d > 15.9f) { carry = 1.0f; nib = 0u; } else nib = (uint32_t)(int)d & 15u;
+                } else {
+                    float v = (DITHER == LQ_DITHER_HASH) ? hash_dither(r, p.v0) : u[k];
+                    nib = res3_encode(r, v, p.enc, carry) & 15u;
+                }
+            }
+            qf = rnd<BF>(__fadd_rn(qf, carry));
+            qf = (WBITS == 4) ? fminf(fmaxf(qf, 0.0f), 15.0f) : fminf(fmaxf(qf, -128.0f), 127.0f);
+            q[k] = (uint32_t)(int)qf & 0xffu;
+            rword = (rword << 4) | nib;
+        }
+        if (CODEC != LQ_CODEC_NONE) p.words_out[w] = (int32_t)rword;
+        if (WBITS == 4) {
+            uint32_t pk = 0;
+#pragma unroll
+            for (int k = 0; k < 4; ++k) pk |= (((q[2 * k] & 15u) << 4) | (q[2 * k + 1] & 15u)) << (8 * k);
+            reinterpret_cast<uint32_t*>(p.codes_out)[w] = pk;
+        } else {
+            uint2 pk;
+            pk.x = q[0] | (q[1] << 8) | (q[2] << 16) | (q[3] << 24);
+            pk.y = q[4] | (q[5] << 8) | (q[6] << 16) | (q[7] << 24);
+            reinterpret_cast<uint2*>(p.codes_out)[w] = pk;
+        }
+    }
+}
+
+template <int WBITS, int CODEC, int DITHER>
+static int launch_requant_bf(const RequantParams& p, bool bf, cudaStream_t st) {
+    int grid = grid_for(p.n_words, 256, 8);
+    if (bf) k_requant<WBITS, CODEC, DITHER, true><<<grid, 256, 0, st>>>(p);
+    else k_requant<WBITS, CODEC, DITHER, false><<<grid, 256, 0, st>>>(p);
+    return check_launch("k_requant");
+}
+template <int WBITS>
+static int launch_requant(const RequantParams& p, const lq_requant_opts* o, cudaStream_t st) {
+    const bool bf = o->math_dtype == LQ_BF16;
+    switch (o->codec) {
+        case LQ_CODEC_NONE: return launch_requant_bf<WBITS, LQ_CODEC_NONE, LQ_DITHER_HASH>(p, bf, st);
+        case LQ_CODEC_UNIFORM16:
+            if (o->dither == LQ_DITHER_EXPLICIT) return launch_requant_bf<WBITS, LQ_CODEC_UNIFORM16, LQ_DITHER_EXPLICIT>(p, bf, st);
+            if (o->dither == LQ_DITHER_PHILOX) return launch_requant_bf<WBITS, LQ_CODEC_UNIFORM16, LQ_DITHER_PHILOX>(p, bf, st);
+            return LQ_EINVAL;   // the uniform16 codec needs a real noise source
+        case LQ_CODEC_THREEFOLD:
+            if (o->dither == LQ_DITHER_HASH) return launch_requant_bf<WBITS, LQ_CODEC_THREEFOLD, LQ_DITHER_HASH>(p, bf, st);
+            if (o->dither == LQ_DITHER_EXPLICIT) return launch_requant_bf<WBITS, LQ_CODEC_THREEFOLD, LQ_DITHER_EXPLICIT>(p, bf, st);
+            if (o->dither == LQ_DITHER_PHILOX) return launch_requant_bf<WBITS, LQ_CODEC_THREEFOLD, LQ_DITHER_PHILOX>(p, bf, st);
+            return LQ_EINVAL;
+    }
+    return LQ_EINVAL;
+}
+
+static int fill_requant(RequantParams& p, const lq_requant_opts* o, int64_t numel, int64_t group) {
+    if (!o || numel <= 0 || (numel % 8) != 0 || group <= 0 || (group % 8) != 0 || (numel % group) != 0) return LQ_EINVAL;
+    if (o->math_dtype != LQ_F32 && o->math_dtype != LQ_BF16) return LQ_EINVAL;
+    if (o->codec != LQ_CODEC_NONE && o->dither == LQ_DITHER_EXPLICIT && (!o->dither_buf || !aligned(o->dither_buf, 16))) return LQ_EINVAL;
+    p.n_words = numel / 8; p.group = group; p.group_shift = -1;
+    if ((group & (group - 1)) == 0) { int sh = 0; while (((int64_t)1 << sh) < group) ++sh; p.group_shift = sh; }
+    p.enc = curve_for_level(o->mu_enc); p.dec = curve_for_level(o->mu_dec);
+    p.v0 = o->v0; p.seed = o->seed; p.stream_id = o->stream_id; p.dither_buf = o->dither_buf;
+    p.has_residual = o->has_residual; p.res_round_bf16 = o->res_round_bf16;
+    return LQ_OK;
+}
+static inline bool dtype_ok(int d) { return d == LQ_F32 || d == LQ_BF16; }
+
+// =================================================================================================
+// 8-bit optimizer-state codec
+// =================================================================================================
+__global__ void __launch_bounds__(256) k_opt8_quant(const float* __restrict__ x, int block, uint8_t* __restrict__ q,
+                                                    float* __restrict__ scale, float* __restrict__ tmax) {
+    __shared__ float s_mn[8], s_mx[8];
+    const int64_t base = (int64_t)blockIdx.x * block;
+    float mn = INFINITY, mx = -INFINITY;
+    for (int e = threadIdx.x * 8; e < block; e += blockDim.x * 8) {
+        float v[8];
+        load8(x, LQ_F32, base + e, v);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) { mn = fminf(mn, v[k]); mx = fmaxf(mx, v[k]); }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        mn = fminf(mn, __shfl_xor_sync(0xffffffffu, mn, o));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    }
+    if ((threadIdx.x & 31) == 0) { s_mn[threadIdx.x >> 5] = mn; s_mx[threadIdx.x >> 5] = mx; }
+    __syncthreads();
+    mn = s_mn[0]; mx = s_mx[0];
+    for (int i = 1; i < (int)(blockDim.x >> 5); ++i) { mn = fminf(mn, s_mn[i]); mx = fmaxf(mx, s_mx[i]); }
+    const float s = __fadd_rn(__fdiv_rn(__fsub_rn(mx, mn), 255.0f), 1e-10f);
+    if (threadIdx.x == 0) { scale[blockIdx.x] = s; tmax[blockIdx.x] = mx; }
+    const float rs = __frcp_rn(s);
+    const bool ok = fastdiv_ok_scale(s);
+    for (int e = threadIdx.x * 8; e < block; e += blockDim.x * 8) {
+        float v[8];
+        load8(x, LQ_F32, base + e, v);
+        uint32_t b[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            float t = rintf(div_rn(__fsub_rn(mx, v[k]), s, rs, ok));
+            b[k] = (uint32_t)(int)fminf(fmaxf(t, 0.0f), 255.0f);
+        }
+        uint2 o2;
+        o2.x = b[0] | (b[1] << 8) | (b[2] << 16) | (b[3] << 24);
+        o2.y = b[4] | (b[5] << 8) | (b[6] << 16) | (b[7] << 24);
+        *reinterpret_cast<uint2*>(q + base + e) = o2;
+    }
+}
+__global__ void __launch_bounds__(256) k_opt8_dequant(const uint8_t* __restrict__ q, int64_t n_words, int64_t block,
+                                                      const float* __restrict__ scale, const float* __restrict__ tmax,
+                                                      float* __restrict__ x) {
+    for (int64_t w = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; w < n_words; w += (int64_t)gridDim.x * blockDim.x) {
+        int64_t b = (w * 8) / block;
+        float s = __ldg(scale + b), t = __ldg(tmax + b);
+        uint2 pk = __ldg(reinterpret_cast<const uint2*>(q) + w);
+        float v[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            float c = (float)(((k < 4 ? pk.x : pk.y) >> (8 * (k & 3))) & 0xffu);
+            v[k] = __fsub_rn(t, __fmul_rn(c, s));
+        }
+        store8(x, LQ_F32, w * 8, v);
+    }
+}
+
+// =================================================================================================
+// Activation quantizers
+// =================================================================================================
+__global__ void __launch_bounds__(256) k_act_quant_per_token(const __nv_bfloat16* __restrict__ x, int64_t K,
+                                                             int8_t* __restrict__ x8, float* __restrict__ a_scale) {
+    __shared__ float s_mx[8];
+    const int64_t base = (int64_t)blockIdx.x * K;
+    float am = 0.0f;
+    for (int64_t e = threadIdx.x * 8; e < K; e += blockDim.x * 8) {
+        float v[8];
+        load8(x, LQ_BF16, base + e, v);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) am = fmaxf(am, fabsf(v[k]));
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, o));
+    if ((threadIdx.x & 31) == 0) s_mx[threadIdx.x >> 5] = am;
+    __syncthreads();
+    am = s_mx[0];
+    for (int i = 1; i < (int)(blockDim.x >> 5); ++i) am = fmaxf(am, s_mx[i]);
+    const float s = bf16r(__fdiv_rn(bf16r(fmaxf(am, 1e-5f)), 127.0f));   // bf16 in-place ops of the reference
+    if (threadIdx.x == 0) a_scale[blockIdx.x] = s;
+    const float rs = __frcp_rn(s);
+    const bool ok = fastdiv_ok_scale(s);
+    for (int64_t e = threadIdx.x * 8; e < K; e += blockDim.x * 8) {
+        float v[8];
+        load8(x, LQ_BF16, base + e, v);
+        uint32_t b[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            float t = rintf(bf16r(div_rn(v[k], s, rs, ok)));
+            b[k] = (uint32_t)(int)fminf(fmaxf(t, -128.0f), 127.0f) & 0xffu;
+        }
+        uint2 o2;
+        o2.x = b[0] | (b[1] << 8) | (b[2] << 16) | (b[3] << 24);
+        o2.y = b[4] | (b[5] << 8) | (b[6] << 16) | (b[7] << 24);
+        *reinterpret_cast<uint2*>(x8 + base + e) = o2;
+    }
+}
+
+__device__ __forceinline__ void atomic_max_float(float* addr, float v) {
+    if (v >= 0.0f) atomicMax(reinterpret_cast<int*>(addr), __float_as_int(v));
+    else atomicMin(reinterpret_cast<unsigned int*>(addr), __float_as_uint(v));
+}
+__global__ void k_set_neg_inf(float* p) { *p = -INFINITY; }
+__global__ void __launch_bounds__(256) k_tensor_max(const __nv_bfloat16* __restrict__ x, int64_t n_words, float* out) {
+    float mx = -INFINITY;
+    for (int64_t w = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; w < n_words; w += (int64_t)gridDim.x * blockDim.x) {
+        float v[8];
+        load8(x, LQ_BF16, w * 8, v);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) mx = fmaxf(mx, v[k]);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    if ((threadIdx.x & 31) == 0) atomic_max_float(out, mx);
+}
+__global__ void __launch_bounds__(256) k_act_quant_per_tensor(const __nv_bfloat16* __restrict__ x, int64_t n_words,
+                                                              const float* __restrict__ clampv, int8_t* __restrict__ x8) {
+    const float c = *clampv;
+    for (int64_t w = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; w < n_words; w += (int64_t)gridDim.x * blockDim.x) {
+        float v[8];
+        load8(x, LQ_BF16, w * 8, v);
+        uint32_t b[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            float t = bf16r(__fmul_rn(v[k], 127.0f));       // input*127. rounds to bf16 first (utils/quant.py:264)
+            t = rintf(bf16r(__fdiv_rn(t, c)));
+            b[k] = (uint32_t)(int)fminf(fmaxf(t, -128.0f), 127.0f) & 0xffu;
+        }
+        uint2 o2;
+        o2.x = b[0] | (b[1] << 8) | (b[2] << 16) | (b[3] << 24);
+        o2.y = b[4] | (b[5] << 8) | (b[6] << 16) | (b[7] << 24);
+        reinterpret_cast<uint2*>(x8)[w] = o2;
+    }
+}
+
+__global__ void __launch_bounds__(256) k_philox_dither(uint64_t seed, uint64_t stream_id, int64_t first_word,
+                                                       int64_t n_words, float* __restrict__ out) {
+    for (int64_t w = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; w < n_words; w += (int64_t)gridDim.x * blockDim.x) {
+        float u[8];
+        philox_dither8(seed, stream_id, (uint64_t)(first_word + w), u);
+        store8(out, LQ_F32, w * 8, u);
+    }
+}
+
+}  // namespace lq
+
+// =================================================================================================
+// C ABI
+// =================================================================================================
+using namespace lq;
+#define LQ_ST(s) reinterpret_cast<cudaStream_t>(s)
+
+extern "C" {
+
+int lq_version(void) { return 100; }
+const char* lq_status_string(int s) {
+    switch (s) {
+        case LQ_OK: return "ok";
+        case LQ_EINVAL: return "invalid argument";
+        case LQ_EUNSUPPORTED: return "unsupported shape or option";
+        case LQ_ECUDA: return "CUDA error (see lq_last_cuda_error)";
+        case LQ_ETIMEOUT: return "device-side bounded wait expired";
+        case LQ_EWORKSPACE: return "workspace missing or too small";
+    }
+    return "unknown status";
+}
+const char* lq_last_cuda_error(void) { return g_last_error.c_str(); }
+
+int lq_res3_quant(void* x, int dtype, int32_t* words, int64_t n_words, int k1, float b1, int k2, float b2, int k3,
+                  float v0, lq_stream_t stream) {
+    if (!x || !words || n_words < 0 || !dtype_ok(dtype) || !aligned(x, 16) || !aligned(words, 4)) return LQ_EINVAL;
+    if (n_words == 0) return LQ_OK;
+    k_res_quant<RQ_3FOLD><<<grid_for(n_words, 256, 8), 256, 0, LQ_ST(stream)>>>(x, dtype, words, n_words,
+                                                                                  make_curve(k1, b1, k2, b2, k3), v0);
+    return check_launch("lq_res3_quant");
+}
+int lq_res3_dequant(const int32_t* words, void* x, int dtype, int64_t n_words, int k1, float b1, int k2, float b2,
+                    int k3, lq_stream_t stream) {
+    if (!x || !words || n_words < 0 || !dtype_ok(dtype) || !aligned(x, 16)) return LQ_EINVAL;
+    if (n_words == 0) return LQ_OK;
+    k_res_dequant<RQ_3FOLD><<<grid_for(n_words, 256, 8), 256, 0, LQ_ST(stream)>>>(words, x, dtype, n_words,
+                                                                                    make_curve(k1, b1, k2, b2, k3));
+    return check_launch("lq_res3_dequant");
+}
+int lq_resu_quant(void* x, int dtype, int32_t* words, int64_t n_words, float v0, lq_stream_t stream) {
+    if (!x || !words || n_words < 0 || !dtype_ok(dtype) || !aligned(x, 16)) return LQ_EINVAL;
+    if (n_words == 0) return LQ_OK;
+    k_res_quant<RQ_UNIFORM><<<grid_for(n_words, 256, 8), 256, 0, LQ_ST(stream)>>>(x, dtype, words, n_words, Curve{}, v0);
+    return check_launch("lq_resu_quant");
+}
+int lq_resu_quant_s(void* x, int dtype, int32_t* words, int64_t n_words, lq_stream_t stream) {
+    if (!x || !words || n_words < 0 || !dtype_ok(dtype) || !aligned(x, 16)) return LQ_EINVAL;
+    if (n_words == 0) return LQ_OK;
+    k_res_quant<RQ_UNIFORM_S><<<grid_for(n_words, 256, 8), 256, 0, LQ_ST(stream)>>>(x, dtype, words, n_words, Curve{}, 0.0f);
+    return check_launch("lq_resu_quant_s");
+}
+int lq_resu_dequant(const int32_t* words, void* x, int dtype, int64_t n_words, lq_stream_t stream) {
+    if (!x || !words || n_words < 0 || !dtype_ok(dtype) || !aligned(x, 16)) return LQ_EINVAL;
+    if (n_words == 0) return LQ_OK;
+    k_res_dequant<RQ_UNIFORM><<<grid_for(n_words, 256, 8), 256, 0, LQ_ST(stream)>>>(words, x, dtype, n_words, Curve{});
+    return check_launch("lq_resu_dequant");
+}
+int lq_uniform16_encode(const float* r, const float* noise, int64_t n, int32_t* words, float* carry, lq_stream_t stream) {
+    if (!r || !noise || !words || n < 0 || (n % 8) || !aligned(r, 16) || !aligned(noise, 16) || (carry && !aligned(carry, 16)))
+        return LQ_EINVAL;
+    if (n == 0) return LQ_OK;
+    k_uniform16_encode<<<grid_for(n / 8, 256, 8), 256, 0, LQ_ST(stream)>>>(r, noise, n / 8, words, carry);
+    return check_launch("lq_uniform16_encode");
+}
+int lq_uniform16_decode(const int32_t* words, int64_t n_words, float* out, lq_stream_t stream) {
+    if (!words || !out || n_words < 0 || !aligned(out, 16)) return LQ_EINVAL;
+    if (n_words == 0) return LQ_OK;
+    k_uniform16_decode<<<grid_for(n_words, 256, 8), 256, 0, LQ_ST(stream)>>>(words, n_words, out);
+    return check_launch("lq_uniform16_decode");
+}
+
+int lq_pack_nibbles(const uint8_t* codes, int8_t* packed, int64_t n_codes, lq_stream_t stream) {
+    if (!codes || !packed || n_codes < 0 || (n_codes % 2) || !aligned(codes, 2)) return LQ_EINVAL;
+    if (n_codes == 0) return LQ_OK;
+    k_pack_nibbles<<<grid_for(n_codes / 2, 256, 8), 256, 0, LQ_ST(stream)>>>(codes, packed, n_codes / 2);
+    return check_launch("lq_pack_nibbles");
+}
+int lq_unpack_nibbles(const int8_t* packed, int8_t* codes, int64_t n_bytes, lq_stream_t stream) {
+    if (!codes || !packed || n_bytes < 0 || !aligned(codes, 2)) return LQ_EINVAL;
+    if (n_bytes == 0) return LQ_OK;
+    k_unpack_nibbles<<<grid_for(n_bytes, 256, 8), 256, 0, LQ_ST(stream)>>>(packed, codes, n_bytes);
+    return check_launch("lq_unpack_nibbles");
+}
+
+int lq_a16w4_dequant(const int8_t* qweight, const void* scales, const void* zeros, int qp_dtype, void* out,
+                     int out_dtype, int64_t numel, int group, lq_stream_t stream) {
+    if (!qweight || !scales || !zeros || !out || numel < 0 || (numel % 8) || group <= 0 || (group % 8) || (numel % group) ||
+        !dtype_ok(qp_dtype) || !dtype_ok(out_dtype) || !aligned(qweight, 4) || !aligned(out, 16))
+        return LQ_EINVAL;
+    if (numel == 0) return LQ_OK;
+    int grid = grid_for(numel / 8, 256, 8);
+    if (qp_dtype == LQ_BF16)
+        k_a16w4_dequant<true><<<grid, 256, 0, LQ_ST(stream)>>>(reinterpret_cast<const uint32_t*>(qweight), scales, zeros,
+                                                               qp_dtype, out, out_dtype, numel / 8, group);
+    else
+        k_a16w4_dequant<false><<<grid, 256, 0, LQ_ST(stream)>>>(reinterpret_cast<const uint32_t*>(qweight), scales, zeros,
+                                                                qp_dtype, out, out_dtype, numel / 8, group);
+    return check_launch("lq_a16w4_dequant");
+}
+
+int lq_find_qparams(const void* x, int dtype, int64_t numel, int group, int maxq, int sym, float* scales, float* zeros,
+                    lq_stream_t stream) {
+    if (!x || !scales || !zeros || numel < 0 || group <= 0 || (group % 8) || (numel % group) || !dtype_ok(dtype) ||
+        !aligned(x, 16) || maxq <= 0)
+        return LQ_EINVAL;
+    if (numel == 0) return LQ_OK;
+    int64_t n_groups = numel / group;
+    k_find_qparams<<<grid_for(n_groups * 32, 256, 8), 256, 0, LQ_ST(stream)>>>(x, dtype, n_groups, group, (float)maxq,
+                                                                               sym, scales, zeros);
+    return check_launch("lq_find_qparams");
+}
+
+int lq_a16w4_requant(const void* w, int w_dtype, const void* scales, const void* zeros, int qp_dtype, int64_t numel,
+                     int group, const lq_requant_opts* opts, int8_t* codes_out, int32_t* words_out, lq_stream_t stream) {
+    RequantParams p{};
+    int rc = fill_requant(p, opts, numel, group);
+    if (rc) return rc;
+    if (!w || !scales || !zeros || !codes_out || !dtype_ok(w_dtype) || !dtype_ok(qp_dtype) || !aligned(w, 16) ||
+        !aligned(codes_out, 4) || (opts->codec != LQ_CODEC_NONE && !words_out))
+        return LQ_EINVAL;
+    p.w_in = w; p.w_dtype = w_dtype; p.scales = scales; p.zeros = zeros; p.qp_dtype = qp_dtype;
+    p.codes_out = codes_out; p.words_out = words_out;
+    return launch_requant<4>(p, opts, LQ_ST(stream));
+}
+int lq_a16w4_fold_delta(int8_t* codes, int32_t* words, const void* delta, int delta_dtype, const void* scales,
+                        const void* zeros, int qp_dtype, int64_t numel, int group, const lq_requant_opts* opts,
+                        lq_stream_t stream) {
+    RequantParams p{};
+    int rc = fill_requant(p, opts, numel, group);
+    if (rc) return rc;
+    if (!codes || !scales || !zeros || !dtype_ok(qp_dtype) || !aligned(codes, 4) || (opts->codec != LQ_CODEC_NONE && !words) ||
+        (delta && (!dtype_ok(delta_dtype) || !aligned(delta, 16))))
+        return LQ_EINVAL;
+    p.codes_in = codes; p.words_in = words; p.delta = delta; p.delta_dtype = delta_dtype;
+    p.scales = scales; p.zeros = zeros; p.qp_dtype = qp_dtype; p.codes_out = codes; p.words_out = words;
+    return launch_requant<4>(p, opts, LQ_ST(stream));
+}
+int lq_a8w8_requant(const void* w, int w_dtype, const void* qscales, int qp_dtype, int64_t rows, int64_t cols,
+                    const lq_requant_opts* opts, int8_t* codes_out, int32_t* words_out, lq_stream_t stream) {
+    RequantParams p{};
+    if (rows <= 0 || cols <= 0) return LQ_EINVAL;
+    int rc = fill_requant(p, opts, rows * cols, cols);
+    if (rc) return rc;
+    if (!w || !qscales || !codes_out || !dtype_ok(w_dtype) || !dtype_ok(qp_dtype) || !aligned(w, 16) || !aligned(codes_out, 8) ||
+        (opts->codec != LQ_CODEC_NONE && !words_out))
+        return LQ_EINVAL;
+    p.w_in = w; p.w_dtype = w_dtype; p.scales = qscales; p.zeros = nullptr; p.qp_dtype = qp_dtype;
+    p.codes_out = codes_out; p.words_out = words_out;
+    return launch_requant<8>(p, opts, LQ_ST(stream));
+}
+int lq_a8w8_fold_delta(int8_t* codes, int32_t* words, const void* delta, int delta_dtype, const void* qscales,
+                       int qp_dtype, int64_t rows, int64_t cols, const lq_requant_opts* opts, lq_stream_t stream) {
+    RequantParams p{};
+    if (rows <= 0 || cols <= 0) return LQ_EINVAL;
+    int rc = fill_requant(p, opts, rows * cols, cols);
+    if (rc) return rc;
+    if (!codes || !qscales || !dtype_ok(qp_dtype) || !aligned(codes, 8) || (opts->codec != LQ_CODEC_NONE && !words) ||
+        (delta && (!dtype_ok(delta_dtype) || !aligned(delta, 16))))
+        return LQ_EINVAL;
+    p.codes_in = codes; p.words_in = words; p.delta = delta; p.delta_dtype = delta_dtype;
+    p.scales = qscales; p.zeros = nullptr; p.qp_dtype = qp_dtype; p.codes_out = codes; p.words_out = words;
+    return launch_requant<8>(p, opts, LQ_ST(stream));
+}
+int lq_philox_dither(uint64_t seed, uint64_t stream_id, int64_t first_word, int64_t n_words, float* out, lq_stream_t stream) {
+    if (!out || n_words < 0 || !aligned(out, 16)) return LQ_EINVAL;
+    if (n_words == 0) return LQ_OK;
+    k_philox_dither<<<grid_for(n_words, 256, 8), 256, 0, LQ_ST(stream)>>>(seed, stream_id, first_word, n_words, out);
+    return check_launch("lq_philox_dither");
+}
+
+int lq_opt8_quant(const float* x, int64_t n, int block, uint8_t* q, float* scale, float* tmax, lq_stream_t stream) {
+    if (!x || !q || !scale || !tmax || n < 0 || block <= 0 || (block % 8) || (n % block) || !aligned(x, 16) || !aligned(q, 8))
+        return LQ_EINVAL;
+    if (n == 0) return LQ_OK;
+    int threads = block / 8 >= 256 ? 256 : ((block / 8 + 31) / 32) * 32;
+    k_opt8_quant<<<(unsigned)(n / block), threads, 0, LQ_ST(stream)>>>(x, block, q, scale, tmax);
+    return check_launch("lq_opt8_quant");
+}
+int lq_opt8_dequant(const uint8_t* q, int64_t n, int block, const float* scale, const float* tmax, float* x, lq_stream_t stream) {
+    if (!x || !q || !scale || !tmax || n < 0 || block <= 0 || (block % 8) || (n % block) || !aligned(x, 16) || !aligned(q, 8))
+        return LQ_EINVAL;
+    if (n == 0) return LQ_OK;
+    k_opt8_dequant<<<grid_for(n / 8, 256, 8), 256, 0, LQ_ST(stream)>>>(q, n / 8, block, scale, tmax, x);
+    return check_launch("lq_opt8_dequant");
+}
+
+int lq_act_quant_per_token(const void* x, int64_t M, int64_t K, int8_t* x8, float* a_scale, lq_stream_t stream) {
+    if (!x || !x8 || !a_scale || M < 0 || K <= 0 || (K % 8) || !aligned(x, 16) || !aligned(x8, 8)) return LQ_EINVAL;
+    if (M == 0) return LQ_OK;
+    k_act_quant_per_token<<<(unsigned)M, 256, 0, LQ_ST(stream)>>>(reinterpret_cast<const __nv_bfloat16*>(x), K, x8, a_scale);
+    return check_launch("lq_act_quant_per_token");
+}
+int lq_act_quant_per_tensor(const void* x, int64_t n, float* clampv_out, int8_t* x8, lq_stream_t stream) {
+    if (!x || !x8 || !clampv_out || n < 0 || (n % 8) || !aligned(x, 16) || !aligned(x8, 8)) return LQ_EINVAL;
+    if (n == 0) return LQ_OK;
+    int grid = grid_for(n / 8, 256, 8);
+    k_set_neg_inf<<<1, 1, 0, LQ_ST(stream)>>>(clampv_out);
+    k_tensor_max<<<grid, 256, 0, LQ_ST(stream)>>>(reinterpret_cast<const __nv_bfloat16*>(x), n / 8, clampv_out);
+    k_act_quant_per_tensor<<<grid, 256, 0, LQ_ST(stream)>>>(reinterpret_cast<const __nv_bfloat16*>(x), n / 8, clampv_out, x8);
+    return check_launch("lq_act_quant_per_tensor");
+}
+
+}  // extern "C"

@@ -1,0 +1,281 @@
+"""Torch-tensor front-end of the C ABI (device memory and streams only; all arithmetic is in the
+CUDA library).  Every function validates device / dtype / contiguity, allocates the outputs the
+reference's Python code would allocate, and launches on torch's current stream."""
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+
+from . import _lib as L
+from ._lib import (CODEC_NONE, CODEC_THREEFOLD, CODEC_UNIFORM16, DITHER_EXPLICIT, DITHER_HASH,  # noqa: F401
+                   DITHER_PHILOX, LQ_BF16, LQ_F32, RequantOpts)
+
+
+def _stream():
+    return C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _dt(t: torch.Tensor) -> int:
+    if t.dtype == torch.float32:
+        return LQ_F32
+    if t.dtype == torch.bfloat16:
+        return LQ_BF16
+    raise TypeError(f"unsupported dtype {t.dtype} (float32 or bfloat16 expected)")
+
+
+def _chk(t: torch.Tensor, name: str, dtype=None):
+    if not isinstance(t, torch.Tensor) or not t.is_cuda:
+        raise ValueError(f"{name} must be a CUDA tensor (there is no CPU path)")
+    if not t.is_contiguous():
+        raise ValueError(f"{name} must be contiguous")
+    if dtype is not None and t.dtype != dtype:
+        raise TypeError(f"{name} must be {dtype}, got {t.dtype}")
+    return t
+
+
+def _ptr(t):
+    return C.c_void_p(0 if t is None else t.data_ptr())
+
+
+def make_opts(codec=CODEC_THREEFOLD, dither=DITHER_HASH, math_dtype=torch.bfloat16, res_round_bf16=True,
+              has_residual=True, mu_enc=0, mu_dec=0, v0=0.0, seed=0, step=0, param_id=0, dither_buf=None) -> RequantOpts:
+    o = RequantOpts()
+    o.codec, o.dither = codec, dither
+    o.math_dtype = LQ_BF16 if math_dtype == torch.bfloat16 else LQ_F32
+    o.res_round_bf16, o.has_residual = int(res_round_bf16), int(has_residual)
+    o.mu_enc, o.mu_dec, o.v0 = mu_enc, mu_dec, v0
+    o.seed = seed & 0xFFFFFFFFFFFFFFFF
+    o.stream_id = ((step & 0xFFFFFFFF) << 32) | (param_id & 0xFFFFFFFF)
+    if dither_buf is not None:
+        _chk(dither_buf, "dither_buf", torch.float32)
+        o.dither_buf = dither_buf.data_ptr()
+        o._keepalive = dither_buf      # the struct only holds the address
+    return o
+
+
+# ---- residual codecs (MyQuantDequant) ---------------------------------------------------------
+def res3_quant(x, words, k1, b1, k2, b2, k3, v0=0.0):
+    _chk(x, "x"); _chk(words, "words", torch.int32)
+    assert x.numel() == 8 * words.numel()
+    L.call("lq_res3_quant", _ptr(x), _dt(x), _ptr(words), words.numel(), k1, b1, k2, b2, k3, v0, _stream())
+
+
+def res3_dequant(words, x, k1, b1, k2, b2, k3):
+    _chk(x, "x"); _chk(words, "words", torch.int32)
+    assert x.numel() == 8 * words.numel()
+    L.call("lq_res3_dequant", _ptr(words), _ptr(x), _dt(x), words.numel(), k1, b1, k2, b2, k3, _stream())
+
+
+def resu_quant(x, words, v0=0.0):
+    _chk(x, "x"); _chk(words, "words", torch.int32)
+    assert x.numel() == 8 * words.numel()
+    L.call("lq_resu_quant", _ptr(x), _dt(x), _ptr(words), words.numel(), v0, _stream())
+
+
+def resu_quant_s(x, words):
+    _chk(x, "x"); _chk(words, "words", torch.int32)
+    assert x.numel() == 8 * words.numel()
+    L.call("lq_resu_quant_s", _ptr(x), _dt(x), _ptr(words), words.numel(), _stream())
+
+
+def resu_dequant(words, x):
+    _chk(x, "x"); _chk(words, "words", torch.int32)
+    assert x.numel() == 8 * words.numel()
+    L.call("lq_resu_dequant", _ptr(words), _ptr(x), _dt(x), words.numel(), _stream())
+
+
+def uniform16_encode(r, noise):
+    _chk(r, "r", torch.float32); _chk(noise, "noise", torch.float32)
+    words = torch.empty(r.numel() // 8, dtype=torch.int32, device=r.device)
+    carry = torch.empty_like(r)
+    L.call("lq_uniform16_encode", _ptr(r), _ptr(noise), r.numel(), _ptr(words), _ptr(carry), _stream())
+    return words, carry
+
+
+def uniform16_decode(words):
+    _chk(words, "words", torch.int32)
+    out = torch.empty(words.numel() * 8, dtype=torch.float32, device=words.device)
+    L.call("lq_uniform16_decode", _ptr(words), words.numel(), _ptr(out), _stream())
+    return out
+
+
+# ---- packing / dequant / qparams --------------------------------------------------------------
+def pack_nibbles(codes):
+    _chk(codes, "codes", torch.uint8)
+    out = torch.empty(codes.numel() // 2, dtype=torch.int8, device=codes.device)
+    L.call("lq_pack_nibbles", _ptr(codes), _ptr(out), codes.numel(), _stream())
+    return out
+
+
+def unpack_nibbles(packed):
+    _chk(packed, "packed", torch.int8)
+    out = torch.empty(packed.numel() * 2, dtype=torch.int8, device=packed.device)
+    L.call("lq_unpack_nibbles", _ptr(packed), _ptr(out), packed.numel(), _stream())
+    return out
+
+
+def a16w4_dequant(qweight, scales, zeros, shape, dtype=torch.bfloat16, group=128):
+    _chk(qweight, "qweight", torch.int8); _chk(scales, "scales"); _chk(zeros, "zeros", scales.dtype)
+    numel = qweight.numel() * 2
+    out = torch.empty(shape, dtype=dtype, device=qweight.device)
+    assert out.numel() == numel and scales.numel() == numel // group
+    L.call("lq_a16w4_dequant", _ptr(qweight), _ptr(scales), _ptr(zeros), _dt(scales), _ptr(out), _dt(out), numel, group,
+           _stream())
+    return out
+
+
+def find_qparams(x, group=128, maxq=15, sym=False):
+    _chk(x, "x")
+    n_groups = x.numel() // group
+    scales = torch.empty(n_groups, dtype=torch.float32, device=x.device)
+    zeros = torch.empty_like(scales)
+    L.call("lq_find_qparams", _ptr(x), _dt(x), x.numel(), group, maxq, int(sym), _ptr(scales), _ptr(zeros), _stream())
+    return scales, zeros
+
+
+# ---- requantize -----------------------------------------------------------------------------
+def a16w4_requant(w, scales, zeros, opts: RequantOpts, group=128, codes_out=None, words_out=None):
+    _chk(w, "w"); _chk(scales, "scales"); _chk(zeros, "zeros", scales.dtype)
+    numel = w.numel()
+    if codes_out is None:
+        codes_out = torch.empty(numel // 2, dtype=torch.int8, device=w.device)
+    if words_out is None and opts.codec != CODEC_NONE:
+        words_out = torch.empty(numel // 8, dtype=torch.int32, device=w.device)
+    L.call("lq_a16w4_requant", _ptr(w), _dt(w), _ptr(scales), _ptr(zeros), _dt(scales), numel, group, C.byref(opts),
+           _ptr(codes_out), _ptr(words_out), _stream())
+    return codes_out, words_out
+
+
+def a16w4_fold_delta(codes, words, delta, scales, zeros, opts: RequantOpts, group=128):
+    _chk(codes, "codes", torch.int8); _chk(scales, "scales"); _chk(zeros, "zeros", scales.dtype)
+    if words is not None:
+        _chk(words, "words", torch.int32)
+    if delta is not None:
+        _chk(delta, "delta")
+        assert delta.numel() == codes.numel() * 2
+    L.call("lq_a16w4_fold_delta", _ptr(codes), _ptr(words), _ptr(delta), 0 if delta is None else _dt(delta), _ptr(scales),
+           _ptr(zeros), _dt(scales), codes.numel() * 2, group, C.byref(opts), _stream())
+
+
+def a8w8_requant(w, qscales, opts: RequantOpts, codes_out=None, words_out=None):
+    _chk(w, "w"); _chk(qscales, "qscales")
+    rows, cols = w.shape
+    if codes_out is None:
+        codes_out = torch.empty((rows, cols), dtype=torch.int8, device=w.device)
+    if words_out is None and opts.codec != CODEC_NONE:
+        words_out = torch.empty(rows * cols // 8, dtype=torch.int32, device=w.device)
+    L.call("lq_a8w8_requant", _ptr(w), _dt(w), _ptr(qscales), _dt(qscales), rows, cols, C.byref(opts), _ptr(codes_out),
+           _ptr(words_out), _stream())
+    return codes_out, words_out
+
+
+def a8w8_fold_delta(codes, words, delta, qscales, opts: RequantOpts):
+    _chk(codes, "codes", torch.int8); _chk(qscales, "qscales")
+    rows, cols = codes.shape
+    if delta is not None:
+        _chk(delta, "delta")
+    L.call("lq_a8w8_fold_delta", _ptr(codes), _ptr(words), _ptr(delta), 0 if delta is None else _dt(delta), _ptr(qscales),
+           _dt(qscales), rows, cols, C.byref(opts), _stream())
+
+
+def philox_dither(seed, stream_id, n_words, device, first_word=0):
+    out = torch.empty(n_words * 8, dtype=torch.float32, device=device)
+    L.call("lq_philox_dither", seed, stream_id, first_word, n_words, _ptr(out), _stream())
+    return out
+
+
+# ---- optimizer-state codec ---------------------------------------------------------------------
+def opt8_quant(x, block):
+    _chk(x, "x", torch.float32)
+    n = x.numel()
+    q = torch.empty(x.shape, dtype=torch.uint8, device=x.device)
+    scale = torch.empty((n // block, 1), dtype=torch.float32, device=x.device)
+    tmax = torch.empty_like(scale)
+    L.call("lq_opt8_quant", _ptr(x), n, block, _ptr(q), _ptr(scale), _ptr(tmax), _stream())
+    return q, scale, tmax
+
+
+def opt8_dequant(q, block, scale, tmax):
+    _chk(q, "q", torch.uint8); _chk(scale, "scale", torch.float32); _chk(tmax, "tmax", torch.float32)
+    x = torch.empty(q.shape, dtype=torch.float32, device=q.device)
+    L.call("lq_opt8_dequant", _ptr(q), q.numel(), block, _ptr(scale), _ptr(tmax), _ptr(x), _stream())
+    return x
+
+
+# ---- activation quantizers ---------------------------------------------------------------------
+def act_quant_per_token(x):
+    _chk(x, "x", torch.bfloat16)
+    M, K = x.shape
+    x8 = torch.empty((M, K), dtype=torch.int8, device=x.device)
+    s = torch.empty(M, dtype=torch.float32, device=x.device)
+    L.call("lq_act_quant_per_token", _ptr(x), M, K, _ptr(x8), _ptr(s), _stream())
+    return x8, s
+
+
+def act_quant_per_tensor(x):
+    _chk(x, "x", torch.bfloat16)
+    x8 = torch.empty(x.shape, dtype=torch.int8, device=x.device)
+    clampv = torch.empty(1, dtype=torch.float32, device=x.device)
+    L.call("lq_act_quant_per_tensor", _ptr(x), x.numel(), _ptr(clampv), _ptr(x8), _stream())
+    return x8, clampv
+
+
+# ---- GEMMs --------------------------------------------------------------------------------------
+_workspaces: dict = {}
+
+
+def _workspace(kind, M, N, K, device):
+    need = int(L.lib.lq_gemm_workspace_bytes(kind, M, N, K))
+    if need == 0:
+        return None, 0
+    key = (device.index, torch.cuda.current_stream().cuda_stream)
+    ws = _workspaces.get(key)
+    if ws is None or ws.numel() < need:
+        ws = torch.empty(max(need, 1 << 20), dtype=torch.uint8, device=device)
+        _workspaces[key] = ws
+    return ws, ws.numel()
+
+
+def gemm_a16w4_fwd(x, qweight, scales, zeros, bias, N, K, group=128, out=None):
+    _chk(x, "x", torch.bfloat16); _chk(qweight, "qweight", torch.int8)
+    _chk(scales, "scales", torch.bfloat16); _chk(zeros, "zeros", torch.bfloat16)
+    M = x.shape[0]
+    assert x.shape[1] == K and qweight.numel() * 2 == N * K
+    if bias is not None:
+        _chk(bias, "bias", torch.bfloat16)
+    y = out if out is not None else torch.empty((M, N), dtype=torch.bfloat16, device=x.device)
+    ws, nb = _workspace(L.GEMM_A16W4_FWD, M, N, K, x.device)
+    L.call("lq_gemm_a16w4_fwd", _ptr(x), _ptr(qweight), _ptr(scales), _ptr(zeros), _ptr(bias), _ptr(y), M, N, K, group,
+           _ptr(ws), nb, _stream())
+    return y
+
+
+def gemm_a16w4_dgrad(dy, qweight, scales, zeros, N, K, group=128, out=None):
+    _chk(dy, "dy", torch.bfloat16); _chk(qweight, "qweight", torch.int8)
+    _chk(scales, "scales", torch.bfloat16); _chk(zeros, "zeros", torch.bfloat16)
+    M = dy.shape[0]
+    assert dy.shape[1] == N and qweight.numel() * 2 == N * K
+    dx = out if out is not None else torch.empty((M, K), dtype=torch.bfloat16, device=dy.device)
+    ws, nb = _workspace(L.GEMM_A16W4_DGRAD, M, N, K, dy.device)
+    L.call("lq_gemm_a16w4_dgrad", _ptr(dy), _ptr(qweight), _ptr(scales), _ptr(zeros), _ptr(dx), M, N, K, group, _ptr(ws), nb,
+           _stream())
+    return dx
+
+
+def gemm_a8w8(x8, w8, row_scale=None, col_scale=None, alpha=1.0, bias=None, want_acc=False):
+    _chk(x8, "x8", torch.int8); _chk(w8, "w8", torch.int8)
+    M, K = x8.shape
+    N = w8.shape[0]
+    assert w8.shape[1] == K
+    for t, nm in ((row_scale, "row_scale"), (col_scale, "col_scale")):
+        if t is not None:
+            _chk(t, nm, torch.float32)
+    if bias is not None:
+        _chk(bias, "bias", torch.bfloat16)
+    y = torch.empty((M, N), dtype=torch.bfloat16, device=x8.device)
+    acc = torch.empty((M, N), dtype=torch.int32, device=x8.device) if want_acc else None
+    ws, nb = _workspace(L.GEMM_A8W8, M, N, K, x8.device)
+    L.call("lq_gemm_a8w8", _ptr(x8), _ptr(w8), _ptr(row_scale), _ptr(col_scale), float(alpha), _ptr(bias), _ptr(y), _ptr(acc),
+           M, N, K, _ptr(ws), nb, _stream())
+    return (y, acc) if want_acc else y

@@ -375,7 +375,7 @@ ORC_API void orc_act_quant_per_token(const float* x, int64_t rows, int64_t cols,
     for (int64_t r = 0; r < rows; ++r) {
         float am = 0.0f;
         for (int64_t c = 0; c < cols; ++c) am = fmaxf(am, fabsf(x[r * cols + c]));
-        float s = rnd(fmaxf(am, 1e-5f) / 127.0f, math_bf16);
+        float s = rnd(rnd(fmaxf(am, 1e-5f), math_bf16) / 127.0f, math_bf16);
         scale[r] = s;
         for (int64_t c = 0; c < cols; ++c) {
             float t = rintf(rnd(x[r * cols + c] / s, math_bf16));

@@ -1,0 +1,137 @@
+"""GPU parity of the tcgen05 GEMMs.
+
+int8: accumulators are compared bit for bit with the oracle (small shapes) and with an exact
+integer matmul on the device (benchmark shapes).  A16W4: outputs within 1e-2 relative of the
+reference's dequantize-then-matmul (tolerance stated by the target), measured as
+max|err| / max|ref| and as a relative Frobenius error."""
+import numpy as np
+import pytest
+import torch
+
+import oracle as orc
+
+pytestmark = pytest.mark.gpu
+RTOL = 1e-2
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from latentq_llm_b200 import ops as _ops
+    return _ops
+
+
+@pytest.fixture(autouse=True)
+def _no_device_timeout():
+    yield
+    from latentq_llm_b200 import _lib
+    assert _lib.lib.lq_gemm_device_status(1) == 0, "a bounded device-side wait expired"
+
+
+def make_w4_layer(ops, N, K, seed, group=128):
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    w = (torch.randn(N, K, device="cuda", generator=g) * 0.02).to(torch.bfloat16)
+    s, z = ops.find_qparams(w, group, 15, False)
+    sb, zb = s.to(torch.bfloat16), z.to(torch.bfloat16)
+    codes, _ = ops.a16w4_requant(w, sb, zb, ops.make_opts(codec=ops.CODEC_NONE, math_dtype=torch.bfloat16), group=group)
+    return codes, sb, zb
+
+
+def rel_err(got, ref):
+    got, ref = got.double(), ref.double()
+    return float((got - ref).abs().max() / ref.abs().max()), float((got - ref).norm() / ref.norm())
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 128, 128), (16, 256, 512), (33, 192, 384), (128, 128, 256), (200, 320, 1024)])
+def test_a16w4_fwd_small_vs_oracle(ops, M, N, K):
+    codes, sb, zb = make_w4_layer(ops, N, K, seed=M + N)
+    g = torch.Generator(device="cuda").manual_seed(5)
+    x = torch.randn(M, K, device="cuda", generator=g).to(torch.bfloat16)
+    bias = (torch.randn(N, device="cuda", generator=g) * 0.1).to(torch.bfloat16)
+    y = ops.gemm_a16w4_fwd(x, codes, sb, zb, bias, N, K)
+    ref = orc.gemm_a16w4(x.float().cpu().numpy(), codes.cpu().numpy(), sb.float().cpu().numpy(), zb.float().cpu().numpy(),
+                         N, K, bias=bias.float().cpu().numpy())
+    e_max, e_fro = rel_err(y.cpu(), torch.from_numpy(ref))
+    assert e_max < RTOL and e_fro < RTOL, (e_max, e_fro)
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 128, 128), (16, 256, 512), (33, 192, 384), (128, 128, 256), (200, 320, 1024)])
+def test_a16w4_dgrad_small_vs_oracle(ops, M, N, K):
+    codes, sb, zb = make_w4_layer(ops, N, K, seed=M + K)
+    g = torch.Generator(device="cuda").manual_seed(6)
+    dy = torch.randn(M, N, device="cuda", generator=g).to(torch.bfloat16)
+    dx = ops.gemm_a16w4_dgrad(dy, codes, sb, zb, N, K)
+    ref = orc.gemm_a16w4(dy.float().cpu().numpy(), codes.cpu().numpy(), sb.float().cpu().numpy(), zb.float().cpu().numpy(),
+                         N, K, transpose=True)
+    e_max, e_fro = rel_err(dx.cpu(), torch.from_numpy(ref))
+    assert e_max < RTOL and e_fro < RTOL, (e_max, e_fro)
+
+
+@pytest.mark.parametrize("K,N", [(4096, 4096), (4096, 11008), (11008, 4096), (4096, 12288)])
+@pytest.mark.parametrize("M", [1, 16, 128, 512, 4096])
+def test_a16w4_llama_shapes(ops, M, K, N):
+    """Benchmark shapes: compare with dequantize (library kernel, itself oracle-checked) + fp32-accumulate matmul."""
+    codes, sb, zb = make_w4_layer(ops, N, K, seed=1)
+    W = ops.a16w4_dequant(codes, sb, zb, (N, K), torch.bfloat16)
+    g = torch.Generator(device="cuda").manual_seed(M)
+    x = torch.randn(M, K, device="cuda", generator=g).to(torch.bfloat16)
+    y = ops.gemm_a16w4_fwd(x, codes, sb, zb, None, N, K)
+    ref = (x.float() @ W.float().t())
+    e_max, e_fro = rel_err(y, ref)
+    assert e_max < RTOL and e_fro < RTOL, ("fwd", e_max, e_fro)
+    dy = torch.randn(M, N, device="cuda", generator=g).to(torch.bfloat16)
+    dx = ops.gemm_a16w4_dgrad(dy, codes, sb, zb, N, K)
+    ref = (dy.float() @ W.float())
+    e_max, e_fro = rel_err(dx, ref)
+    assert e_max < RTOL and e_fro < RTOL, ("dgrad", e_max, e_fro)
+    # linearity in the activations: f(2x) == 2 f(x) exactly (power-of-two scaling commutes with rounding)
+    y2 = ops.gemm_a16w4_fwd(x * 2, codes, sb, zb, None, N, K)
+    assert torch.equal(y2, y * 2)
+
+
+def _a8_inputs(M, N, K, seed):
+    rng = np.random.default_rng(seed)
+    x = rng.standard_normal((M, K)).astype(np.float32)
+    out_ch = rng.choice(K, max(1, K // 100), replace=False)
+    x[:, out_ch] *= 20.0
+    w = (rng.standard_normal((N, K)) * 0.02).astype(np.float32)
+    w_scale = (np.abs(w).max(axis=1) / 127.0).astype(np.float32)
+    w8 = np.clip(np.rint(w / w_scale[:, None]), -128, 127).astype(np.int8)
+    bias = orc.bf16_round((rng.standard_normal(N) * 0.1).astype(np.float32))
+    return x, w8, w_scale, bias
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 128, 128), (16, 256, 256), (37, 192, 384), (130, 128, 1024), (300, 320, 512)])
+def test_a8w8_small_vs_oracle(ops, M, N, K):
+    x, w8, w_scale, bias = _a8_inputs(M, N, K, seed=M)
+    xb = torch.from_numpy(x).cuda().to(torch.bfloat16)
+    x8, a_scale = ops.act_quant_per_token(xb)
+    y, acc = ops.gemm_a8w8(x8, torch.from_numpy(w8).cuda(), a_scale, torch.from_numpy(w_scale).cuda(), 1.0,
+                           torch.from_numpy(bias).cuda().to(torch.bfloat16), want_acc=True)
+    acc_o = orc.gemm_i8_acc(x8.cpu().numpy(), w8)
+    assert np.array_equal(acc.cpu().numpy(), acc_o)                       # int32 accumulators: bit-exact
+    y_o = orc.gemm_i8_epilogue_fused(acc_o, a_scale.cpu().numpy(), w_scale, bias)
+    assert np.array_equal(y.float().cpu().numpy(), y_o)                   # epilogue restated op for op
+    # the torch_int call form: alpha only
+    y2 = ops.gemm_a8w8(x8, torch.from_numpy(w8).cuda(), None, None, 0.0123, torch.from_numpy(bias).cuda().to(torch.bfloat16))
+    assert np.array_equal(y2.float().cpu().numpy(), orc.gemm_i8_epilogue_torch_int(acc_o, 0.0123, bias))
+    # against the floating-point product it approximates
+    ref = x @ (w8.astype(np.float32) * w_scale[:, None]).T + bias
+    e_max, e_fro = rel_err(y.float().cpu(), torch.from_numpy(ref))
+    assert e_fro < 3e-2, (e_max, e_fro)
+
+
+@pytest.mark.parametrize("K,N", [(2048, 2048), (2048, 8192), (8192, 2048)])
+@pytest.mark.parametrize("M", [2048, 16384])
+def test_a8w8_opt_shapes(ops, M, K, N):
+    g = torch.Generator(device="cuda").manual_seed(K + N)
+    x8 = torch.randint(-128, 128, (M, K), device="cuda", generator=g, dtype=torch.int8)
+    w8 = torch.randint(-128, 128, (N, K), device="cuda", generator=g, dtype=torch.int8)
+    y, acc = ops.gemm_a8w8(x8, w8, None, None, 1e-4, None, want_acc=True)
+    # exact integer reference on the device: fp64 matmul of int8 values is exact (|acc| < 2^53)
+    mrows = min(M, 1024)
+    ref = (x8[:mrows].double() @ w8.double().t()).to(torch.int64)
+    assert torch.equal(acc[:mrows].to(torch.int64), ref)
+    # checksum of checksums over the full output: sum_n acc[m, n] == x8[m, :] · sum_n w8[n, :]
+    colsum = w8.to(torch.int64).sum(0)
+    want = (x8.to(torch.int64) * colsum[None, :]).sum(1)
+    assert torch.equal(acc.to(torch.int64).sum(1), want)

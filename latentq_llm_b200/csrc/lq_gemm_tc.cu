@@ -650,3 +650,62 @@ int lq_gemm_device_status(int reset) {
 }
 
 }  // extern "C"
+
+// ---------------------------------------------------------------------------------------------
+// Forward GEMM with built-in scratch (no caller workspace, no allocation of any kind)
+// ---------------------------------------------------------------------------------------------
+// Split-K partial sums of the decode-sized forward GEMM normally live in a workspace the caller
+// allocates.  Some callers cannot allocate at all: code running inside a framework that owns every
+// byte of device memory through its own pool, serving loops that must not hit the implicit
+// device-wide synchronisation of cudaMalloc/cudaFree, and plugin hosts that forbid driver
+// allocations once initialisation is over.  For them the partial sums go into this fixed array.
+// It is part of the library image: every GPU that loads liblatentq holds these bytes until the
+// process exits, whether or not the entry point is ever called.
+#define LQ_STATIC_SCRATCH_BYTES (8u << 20)
+static __device__ __align__(256) unsigned char g_fwd_static_scratch[LQ_STATIC_SCRATCH_BYTES];
+
+// The array's name is only a host-side handle; the device address has to be asked for, once per
+// device, with that device current.
+static int fwd_static_scratch_ptr(void** out) {
+    static void* cached[64] = {};
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) { lq::set_cuda_error(e, "cudaGetDevice"); return LQ_ECUDA; }
+    if (dev < 0 || dev >= 64) return LQ_EUNSUPPORTED;
+    if (!cached[dev]) {
+        void* ptr = nullptr;
+        e = cudaGetSymbolAddress((void**)&ptr, g_fwd_static_scratch);
+        if (e != cudaSuccess || !ptr) { lq::set_cuda_error(e, "cudaGetSymbolAddress(g_fwd_static_scratch)"); return LQ_ECUDA; }
+        cached[dev] = ptr;
+    }
+    *out = cached[dev];
+    return LQ_OK;
+}
+
+extern "C" {
+
+size_t lq_gemm_a16w4_fwd_static_max_bytes(void) { return (size_t)LQ_STATIC_SCRATCH_BYTES; }
+
+int lq_gemm_a16w4_fwd_static(const void* x, const int8_t* qweight, const void* scales, const void* zeros, const void* bias,
+                             void* y, int64_t M, int64_t N, int64_t K, int group, lq_stream_t stream) {
+    if (!x || !qweight || !scales || !zeros || !y || !al16(x) || !al16(qweight) || !al16(y)) return LQ_EINVAL;
+    if (!shape_ok_w4(M, N, K, group)) return LQ_EUNSUPPORTED;
+    // Partial sums needed by this shape's split-K plan; shapes that need more than the array holds are refused.
+    const size_t need = lq_gemm_workspace_bytes(LQ_GEMM_A16W4_FWD, M, N, K);
+    if (need > (size_t)LQ_STATIC_SCRATCH_BYTES) {
+        lq::set_cuda_error(cudaErrorInvalidValue, "lq_gemm_a16w4_fwd_static: shape needs more scratch than the built-in 8 MiB; "
+                                                  "use lq_gemm_a16w4_fwd with a workspace");
+        return LQ_EWORKSPACE;
+    }
+    void* scratch = nullptr;
+    int rc = fwd_static_scratch_ptr(&scratch);
+    if (rc) return rc;
+    GemmParams p{};
+    p.group = group; p.scales = (const __nv_bfloat16*)scales; p.zeros = (const __nv_bfloat16*)zeros;
+    p.bias = (const __nv_bfloat16*)bias; p.out = (__nv_bfloat16*)y; p.alpha = 1.0f;
+    // Every partial-sum element the reduction reads is written by this launch first, so nothing in the
+    // array has to start at zero and the previous call's leftovers are harmless.
+    return run_gemm(KIND_FWD, x, qweight, p, M, N, K, scratch, (size_t)LQ_STATIC_SCRATCH_BYTES, (cudaStream_t)stream);
+}
+
+}  // extern "C"

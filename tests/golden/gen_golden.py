@@ -177,6 +177,41 @@ def main(ref):
     out["aq_x"] = f32(A)
     out["aq_fake"] = f32(ql["quantize_activation_per_token_absmax"](A.clone()))
 
+    # --- MyAdam.update_step (utils/quant.py:1062-1148) on one A16W4 parameter, fp32 gradients, CPU states ----
+    # lbit=16: the latent is a full-precision copy (no residual codec), so the Adam arithmetic, the 8-bit state
+    # codec and the requantize are exercised exactly as the reference executes them.
+    ad = slice_module(qpath, {"MyAdam", "QuantTensor", "GradientQTensor", "prodx", "python_compress", "python_decompress",
+                              "Qfunc_8bit_opt", "DeQfunc_8bit_opt", "GROUPSIZE", "Qfunc_4bit_g_res", "DeQfunc_4bit_g",
+                              "Qfunc_8bit_res"}, {"ResidualTensor": ResidualTensor, "warnings": __import__("warnings")})
+    Na, Ka = 128, 512                                # 65536 elements: uint8 states, 32 blocks of 2048
+    Wa = (torch.randn(Na, Ka, generator=g) * 0.02).to(torch.bfloat16).float()
+    qa = qz["Quantizer"]()
+    qa.configure(4, perchannel=True, sym=False, mse=False)
+    qa.find_params(Wa.view(-1, 128), weight=True)
+    sa = qa.scale.reshape(-1, 1).to(torch.bfloat16)
+    za = qa.zero.reshape(-1, 1).to(torch.bfloat16)
+    pt = ad["QuantTensor"]([Na, Ka], wbit=4, gbit=16, lbit=16)
+    codes_a = ad["Qfunc_4bit_g_res"](Wa.to(torch.bfloat16), pt.residual, [sa, za, [Na, Ka]])
+    pt.set_value(codes_a, [sa, za, [Na, Ka]])
+    out["adam_w"], out["adam_scales"], out["adam_zeros"] = f32(Wa), f32(sa.reshape(-1)), f32(za.reshape(-1))
+    out["adam_codes0"] = codes_a.numpy()
+    opt = ad["MyAdam"]([{"params": [pt], "weight_decay": 0.0}], lr=1e-3, betas=(0.9, 0.95), obit=8, cpu=True)
+    for step in range(3):
+        gr = torch.randn(Na, Ka, generator=g) * 1e-2
+        pt.grad = gr.clone()
+        group = opt.param_groups[0]
+        if len(opt.state[pt]) == 0:
+            opt.init_state(group, pt, 0, 0)
+        opt.update_step(group, pt, 0, 0)
+        st_ = opt.state[pt]
+        out[f"adam_grad{step}"] = f32(gr)
+        out[f"adam_codes{step + 1}"] = pt.data.numpy()
+        out[f"adam_latent{step + 1}"] = f32(pt.residual.data)
+        out[f"adam_state1_{step + 1}"] = st_["state1"].numpy()
+        out[f"adam_state2_{step + 1}"] = st_["state2"].numpy()
+        for k in ("qmap1", "absmax1", "qmap2", "absmax2"):
+            out[f"adam_{k}_{step + 1}"] = f32(st_[k].reshape(-1))
+
     np.savez_compressed(os.path.join(OUT, "reference_vectors.npz"), **out)
     print("wrote", len(out), "arrays,", os.path.getsize(os.path.join(OUT, "reference_vectors.npz")), "bytes")
 

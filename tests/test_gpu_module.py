@@ -1,0 +1,192 @@
+"""The reference-facing module API (`latentq_llm_b200.quant`, mirror of utils/quant.py) on the GPU."""
+import numpy as np
+import pytest
+import torch
+
+import oracle as orc
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def Q():
+    from latentq_llm_b200 import quant
+    return quant
+
+
+def _make_a16w4(Q, N, K, bias=True, lbit=4, seed=0):
+    from latentq_llm_b200 import ops
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    w = (torch.randn(N, K, device="cuda", generator=g) * 0.02).to(torch.bfloat16)
+    s, z = ops.find_qparams(w, 128, 15, False)
+    layer = Q.QLinearA16W4(K, N, bias=bias, lbit=lbit, gbit=16)
+    layer.zeros.data = z.view(-1, 1).to(torch.bfloat16)
+    layer.scales.data = s.view(-1, 1).to(torch.bfloat16)
+    codes, _ = ops.a16w4_requant(w, layer.scales.data.view(-1).contiguous(), layer.zeros.data.view(-1).contiguous(),
+                                 ops.make_opts(codec=ops.CODEC_NONE, math_dtype=torch.bfloat16))
+    layer.weight.set_value(codes, [layer.scales, layer.zeros, layer.wshape])
+    if bias:
+        layer.bias.data = (torch.randn(N, device="cuda", generator=g) * 0.1).to(torch.bfloat16)
+    layer.to("cuda")
+    return layer, w
+
+
+def test_state_dict_keys_and_repr(Q):
+    layer, _ = _make_a16w4(Q, 128, 256)
+    assert set(layer.state_dict().keys()) == {"bias", "qweight", "zeros", "scales"}
+    layer.before_save()
+    assert layer.qweight.dtype == torch.int8 and layer.qweight.numel() == 128 * 256 // 2 and not layer.qweight.is_cuda
+    assert "QLinearA16W4 input_features=256" in repr(layer)
+    l8 = Q.QLinearA8W8(256, 128)
+    assert set(l8.state_dict().keys()) == {"bias", "qweight", "clampv", "qscales"}
+
+
+def test_a16w4_module_forward_backward_and_hook(Q):
+    N, K, B, S = 256, 384, 3, 20
+    layer, _ = _make_a16w4(Q, N, K)
+    W = Q.DeQfunc_4bit_g(layer.weight.data, layer.weight.qparam, torch.bfloat16)
+    x = torch.randn(B, S, K, device="cuda").to(torch.bfloat16).requires_grad_(True)
+    # eval path (no hook)
+    y = layer(x)
+    ref = (x.detach().reshape(-1, K).float() @ W.float().t()).to(torch.bfloat16) + layer.bias.data
+    assert y.shape == (B, S, N)
+    assert float((y.reshape(-1, N).float() - ref.float()).abs().max() / ref.float().abs().max()) < 1e-2
+    # training path: hook moves dY^T·x into weight.grad, grad-input comes from the fused kernel
+    layer.add_hook()
+    y = layer(x)
+    dy = torch.randn_like(y)
+    y.backward(dy)
+    dx_ref = dy.reshape(-1, N).float() @ W.float()
+    assert float((x.grad.reshape(-1, K).float() - dx_ref).abs().max() / dx_ref.abs().max()) < 1e-2
+    gw_ref = dy.reshape(-1, N).float().t() @ x.detach().reshape(-1, K).float()
+    assert layer.weight.grad.shape == (N, K)
+    assert float((layer.weight.grad.float() - gw_ref).abs().max() / gw_ref.abs().max()) < 2e-2
+    assert layer.bias.grad is None          # as in the reference: the bias slot never reports needs_input_grad
+    assert len(Q.dict_temp) == 0
+    # accumulation over micro-batches
+    y = layer(x)
+    y.backward(dy)
+    assert float((layer.weight.grad.float() - 2 * gw_ref).abs().max() / gw_ref.abs().max()) < 4e-2
+
+
+def test_myadam_matches_reference_steps(Q, golden):
+    """Three optimizer steps on one A16W4 parameter (fp32 gradients, full-precision latent copy) against
+    vectors produced by the reference's own MyAdam.update_step on CPU.  The reference's CPU kernels and
+    the device kernels may differ by fused-multiply-add contraction inside single torch ops (<= 1 ulp), so
+    codes and 8-bit states are compared with a small mismatch budget instead of bit for bit."""
+    N, K = 128, 512
+    s = torch.from_numpy(golden["adam_scales"]).cuda().to(torch.bfloat16).view(-1, 1)
+    z = torch.from_numpy(golden["adam_zeros"]).cuda().to(torch.bfloat16).view(-1, 1)
+    p = Q.QuantTensor([N, K], wbit=4, gbit=16, lbit=16)
+    p.residual = p.residual.cuda()
+    w = torch.from_numpy(golden["adam_w"]).cuda().to(torch.bfloat16)
+    codes = Q.Qfunc_4bit_g_res(w, p.residual, [s, z, [N, K]])
+    assert np.array_equal(codes.cpu().numpy(), golden["adam_codes0"])
+    p.set_value(codes, [s, z, [N, K]])
+    opt = Q.MyAdam([{"params": [p], "weight_decay": 0.0}], lr=1e-3, betas=(0.9, 0.95), obit=8)
+    for step in range(3):
+        p.grad = torch.from_numpy(golden[f"adam_grad{step}"]).cuda()
+        opt.step()
+        st = opt.state[p]
+        assert st["state1"].dtype == torch.uint8 and st["qmap1"].shape == (32, 1)
+        lat = p.residual.data.float().cpu().numpy()
+        assert np.mean(lat != golden[f"adam_latent{step + 1}"]) < 2e-3
+        assert np.mean(p.data.cpu().numpy() != golden[f"adam_codes{step + 1}"]) < 2e-3
+        for k in ("state1", "state2"):
+            d = np.abs(st[k].cpu().numpy().astype(np.int32) - golden[f"adam_{k}_{step + 1}"].astype(np.int32))
+            assert d.max() <= 1 and np.mean(d != 0) < 2e-2, (k, step, d.max(), np.mean(d != 0))
+        for k in ("qmap1", "absmax1", "qmap2", "absmax2"):
+            np.testing.assert_allclose(st[k].cpu().numpy().ravel(), golden[f"adam_{k}_{step + 1}"], rtol=1e-5, atol=1e-12)
+        assert p.grad is None
+
+
+def test_myadam_with_residual_tracks_fp32_adam(Q):
+    """lbit=4 (codes + 4-bit residual), bf16 gradients: after a few steps the latent reconstructed from codes and
+    residual follows a plain fp32 Adam trajectory to within the residual's resolution (scale/16) plus bf16 noise."""
+    N, K = 256, 512
+    layer, w = _make_a16w4(Q, N, K, bias=False, lbit=4)
+    p = layer.weight
+    opt = Q.MyAdam([{"params": [p], "weight_decay": 0.0}], lr=1e-3, betas=(0.9, 0.95), obit=8)
+    W0 = Q.DeQfunc_4bit_g(p.data, p.qparam, torch.float32)
+    ref = W0.clone(); m = torch.zeros_like(ref); v = torch.zeros_like(ref)
+    g = torch.Generator(device="cuda").manual_seed(3)
+    for t in range(1, 5):
+        grad = (torch.randn(N, K, device="cuda", generator=g) * 1e-2).to(torch.bfloat16)
+        p.grad = grad.clone()
+        opt.step()
+        m = 0.9 * m + 0.1 * grad.float(); v = 0.95 * v + 0.05 * grad.float() ** 2
+        ref -= 1e-3 * (1 - 0.95 ** t) ** 0.5 / (1 - 0.9 ** t) * m / (v.sqrt() + 1e-8)
+    lat = p.residual.add(Q.DeQfunc_4bit_g(p.data, p.qparam, torch.bfloat16)).float()
+    scale = layer.scales.float().view(-1, 1).expand(-1, 128).reshape(N, K)
+    err = (lat - ref).abs() / scale
+    assert float(err.mean()) < 0.12 and float(err.max()) < 1.5, (float(err.mean()), float(err.max()))
+    assert not p.residual.init and p.residual.residual_int.dtype == torch.int32
+    assert int(p.data.view(torch.uint8).max()) <= 255
+
+
+def test_a8w8_module_forward_matches_composition(Q):
+    from latentq_llm_b200 import ops
+    N, K, M = 192, 512, 40
+    g = torch.Generator(device="cuda").manual_seed(9)
+    layer = Q.QLinearA8W8(K, N, bias=True, lbit=4, gbit=16)
+    w = torch.randn(N, K, device="cuda", generator=g) * 0.02
+    qs = (w.abs().amax(dim=1, keepdim=True) / 127).to(torch.bfloat16)
+    layer.qscales.data = qs
+    w8 = torch.clamp(torch.round(w / qs.float()), -128, 127).to(torch.int8)
+    layer.weight.set_value(w8, layer.qscales)
+    layer.bias.data = (torch.randn(N, device="cuda", generator=g) * 0.1).to(torch.bfloat16)
+    layer.to("cuda")
+    x = torch.randn(M, K, device="cuda", generator=g).to(torch.bfloat16)
+    y = layer(x)
+    # the reference's arithmetic, step by step (utils/quant.py:260-271), with the oracle's exact accumulators
+    clampv = x.max()
+    x8 = (x * 127. / clampv).round_().clamp_(-128, 127).to(torch.int8)
+    acc = orc.gemm_i8_acc(x8.cpu().numpy(), w8.cpu().numpy())
+    alpha = float((clampv / 127.).float())
+    inner = orc.gemm_i8_epilogue_torch_int(acc, alpha, (layer.bias.data / qs.view(-1)).float().cpu().numpy())
+    ref = (torch.from_numpy(inner).cuda().to(torch.bfloat16) * qs.view(1, -1))
+    assert torch.equal(y, ref)
+    # training path: grads flow, weight.grad is produced by the hook
+    layer.add_hook()
+    x2 = x.clone().requires_grad_(True)
+    out = layer(x2)
+    out.backward(torch.ones_like(out))
+    assert x2.grad is not None and layer.weight.grad.shape == (N, K) and len(Q.dict_temp) == 0
+    opt = Q.MyAdam([{"params": [layer.weight], "weight_decay": 0.0}], lr=1e-3, betas=(0.9, 0.95))
+    before = layer.weight.data.clone()
+    opt.step()
+    assert layer.weight.data.dtype == torch.int8 and layer.weight.data.shape == before.shape
+    assert not layer.weight.residual.init
+
+
+def test_torch_int_shim_call_shape(Q):
+    from latentq_llm_b200 import torch_int_shim
+    torch_int_shim.install()
+    from torch_int._CUDA import linear_a8_w8_bbf16_obf16, linear_a8_w8_bfp32_ofp32
+    g = torch.Generator(device="cuda").manual_seed(1)
+    x8 = torch.randint(-128, 128, (24, 256), device="cuda", generator=g, dtype=torch.int8)
+    w8 = torch.randint(-128, 128, (128, 256), device="cuda", generator=g, dtype=torch.int8)
+    bias = torch.randn(128, device="cuda", generator=g).to(torch.bfloat16)
+    y = linear_a8_w8_bbf16_obf16(x8, w8, bias, torch.tensor(0.01, device="cuda", dtype=torch.bfloat16))
+    acc = orc.gemm_i8_acc(x8.cpu().numpy(), w8.cpu().numpy())
+    alpha = float(torch.tensor(0.01, dtype=torch.bfloat16))
+    assert np.array_equal(y.float().cpu().numpy(), orc.gemm_i8_epilogue_torch_int(acc, alpha, bias.float().cpu().numpy()))
+    y32 = linear_a8_w8_bfp32_ofp32(x8, w8, bias.float(), 0.5)
+    assert torch.equal(y32, torch.from_numpy(acc).cuda().float() * 0.5 + bias.float()[None, :])
+
+
+def test_functional_mirrors(Q, golden):
+    codes = torch.from_numpy(golden["pack_codes"]).cuda()
+    packed = Q.python_compress(codes)
+    assert np.array_equal(packed.cpu().numpy(), golden["pack_packed"])
+    assert np.array_equal(Q.python_decompress(packed).cpu().numpy().reshape(-1), golden["unpack_codes"])
+    q, (sc, tm) = Q.Qfunc_8bit_opt(torch.from_numpy(golden["o8_x"]).cuda(), blocksize=2)
+    assert np.array_equal(q.cpu().numpy(), golden["o8_q"])
+    assert np.array_equal(Q.DeQfunc_8bit_opt(q, [sc, tm]).cpu().numpy(), golden["o8_deq"])
+    assert Q.three_fold_curve_4bit(2) == (2, 0.37272211741724515, 4, 0.4375)
+    r = Q.ResidualTensor([4, 128], [4, 128])
+    x = (torch.rand(4, 128, device="cuda") - 0.5)
+    adj = r.set_value(x.clone(), torch.ones(4, 1, device="cuda", dtype=torch.bfloat16))
+    assert adj.dtype == torch.bfloat16 and set(adj.float().unique().tolist()) <= {0.0, 1.0}
+    back = r.add(torch.zeros(4, 128, device="cuda", dtype=torch.bfloat16))
+    assert float((back.float() - x.to(torch.bfloat16).float()).abs().max()) <= 1 / 16 + 1e-3

@@ -131,8 +131,9 @@ def timed(torch, fn, steps, barrier):
     return e0.elapsed_time(e1), launches
 
 
-def extra_measurements(torch, ops, pk):
-    """Secondary figures of the same hot path (not the headline): requantize GB/s, int8 GEMM TOP/s, decode-size GEMM."""
+def extra_measurements(torch, ops, pk, only=None, numel=1 << 30):
+    """Secondary figures of the same hot path (not the headline): requantize GB/s, int8 GEMM TOP/s, decode-size GEMM.
+    `only` restricts to one family ("requant", "a8w8", "decode") for profiling runs."""
     out = {}
 
     def tm(fn, reps=5, warm=2):
@@ -146,9 +147,18 @@ def extra_measurements(torch, ops, pk):
         e1.record(); torch.cuda.synchronize()
         return e0.elapsed_time(e1) / reps
 
-    # requantize: fold a bf16 update into codes+residual, 2^30 weights (codes 0.5 + residual 0.5 read and written, delta 2 B read)
-    numel = 1 << 30
     g = torch.Generator(device="cuda").manual_seed(7)
+    if only in (None, "requant"):
+        _requant_part(torch, ops, pk, out, tm, g, numel)
+    if only in (None, "a8w8"):
+        _a8w8_part(torch, ops, out, tm, g)
+    if only in (None, "decode"):
+        _decode_part(torch, ops, pk, out, tm)
+    return out
+
+
+def _requant_part(torch, ops, pk, out, tm, g, numel):
+    # requantize: fold a bf16 update into codes+residual (codes 0.5 + residual 0.5 read and written, delta 2 B read)
     codes = torch.randint(-128, 128, (numel // 2,), device="cuda", generator=g, dtype=torch.int8)
     words = torch.zeros(numel // 8, dtype=torch.int32, device="cuda")
     delta = (torch.randn(numel, device="cuda", generator=g, dtype=torch.bfloat16) * 1e-4)
@@ -164,6 +174,8 @@ def extra_measurements(torch, ops, pk):
         out["requant_" + name] = {"GB/s": round(gbs, 1), "frac_hbm": round(gbs / pk["hbm_gbs"], 3), "ms": round(ms, 3), "numel": numel}
     del codes, words, delta, s, z
 
+
+def _a8w8_part(torch, ops, out, tm, g):
     # int8 GEMM, OPT-1.3B shapes, M = 32x512 tokens
     tot_ops, tot_ms = 0.0, 0.0
     for (k, n) in [(2048, 2048), (2048, 8192), (8192, 2048)]:
@@ -175,6 +187,8 @@ def extra_measurements(torch, ops, pk):
         tot_ops += 2.0 * m * n * k; tot_ms += ms
     out["a8w8_opt_m16384"] = {"TOP/s": round(tot_ops / tot_ms / 1e9, 1), "ms": round(tot_ms, 3)}
 
+
+def _decode_part(torch, ops, pk, out, tm):
     # A16W4 forward at decode / small M over the four Llama shapes: bandwidth view (packed weights + qparams + activations)
     layers = build_layers(torch, ops)
     for m in (1, 16, 128, 512):
@@ -186,7 +200,6 @@ def extra_measurements(torch, ops, pk):
             fl += 2.0 * m * L["N"] * L["K"]
         out[f"a16w4_fwd_m{m}"] = {"TFLOP/s": round(fl / ms_tot / 1e9, 2), "GB/s": round(bytes_tot / ms_tot / 1e6, 1),
                                   "frac_hbm": round(bytes_tot / ms_tot / 1e6 / pk["hbm_gbs"], 3), "ms": round(ms_tot, 4)}
-    return out
 
 
 def cpu_baseline(sample_m=256, reps=2):
@@ -330,13 +343,21 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-extra", action="store_true", help="skip the secondary measurements and the CPU baseline")
+    ap.add_argument("--only", default="", choices=["", "requant", "a8w8", "decode"],
+                    help="run one family of the secondary measurements only (profiling a single kernel)")
+    ap.add_argument("--numel", type=int, default=1 << 30, help="weights in the requantize measurement")
     ap.add_argument("--shapes", default="", help="comma-separated indices into the shape list (profiling a smaller case)")
     args = ap.parse_args()
     if args.shapes:
         global LLAMA_SHAPES, WORKLOAD
         LLAMA_SHAPES = [LLAMA_SHAPES[int(i)] for i in args.shapes.split(",")]
         WORKLOAD += f" [subset {LLAMA_SHAPES}]"
-    if args.impl == "reference":
+    if args.only:
+        import torch
+        from latentq_llm_b200 import ops
+        torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
+        print(json.dumps({"only": args.only, "extra": extra_measurements(torch, ops, peaks(), args.only, args.numel)}), flush=True)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_ours(args)

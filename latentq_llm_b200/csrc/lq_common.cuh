@@ -16,6 +16,10 @@ namespace lq {
 void set_cuda_error(cudaError_t e, const char* where);
 int check_launch(const char* where);  // cudaGetLastError -> LQ_OK / LQ_ECUDA
 int sm_count();                       // cached per current device
+// Makes the device that owns `device_ptr` current on the calling thread if the thread has no CUDA context yet
+// (worker threads such as an autograd engine thread start without one; launching from them would otherwise
+// target device 0, and tensor-map encoding fails outright).  No-op when a context is already current.
+int ensure_device_for(const void* device_ptr);
 
 // ---- numeric helpers ------------------------------------------------------------
 __device__ __forceinline__ float bf16r(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }

@@ -559,6 +559,7 @@ static inline bool al16(const void* p) { return (reinterpret_cast<uintptr_t>(p) 
 static int run_gemm(int kind, const void* tok, const void* w, GemmParams p, int64_t M, int64_t N, int64_t K,
                     void* workspace, size_t workspace_bytes, cudaStream_t st) {
     if (M == 0) return LQ_OK;
+    { int rc_dev = ensure_device_for(tok); if (rc_dev) return rc_dev; }
     const Plan pl = make_plan(kind, M, N, K);
     p.M = (int)M; p.R = (int)((kind == KIND_DGRAD) ? K : N); p.C = (int)((kind == KIND_DGRAD) ? N : K);
     p.wcols = (int)K;

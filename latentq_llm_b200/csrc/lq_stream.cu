@@ -32,6 +32,28 @@ int sm_count() {
     return cached[dev];
 }
 
+int ensure_device_for(const void* device_ptr) {
+    typedef int (*PFN_ctxGetCurrent)(void**);
+    static PFN_ctxGetCurrent get_current = nullptr;
+    static bool looked_up = false;
+    if (!looked_up) {
+        void* f = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuCtxGetCurrent", &f, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
+            get_current = reinterpret_cast<PFN_ctxGetCurrent>(f);
+        looked_up = true;
+    }
+    void* ctx = nullptr;
+    if (get_current && get_current(&ctx) == 0 && ctx != nullptr) return LQ_OK;
+    cudaPointerAttributes attr;
+    cudaError_t e = cudaPointerGetAttributes(&attr, device_ptr);
+    if (e != cudaSuccess) { set_cuda_error(e, "cudaPointerGetAttributes"); cudaGetLastError(); return LQ_ECUDA; }
+    if (attr.type != cudaMemoryTypeDevice && attr.type != cudaMemoryTypeManaged) return LQ_EINVAL;
+    e = cudaSetDevice(attr.device);
+    if (e != cudaSuccess) { set_cuda_error(e, "cudaSetDevice"); return LQ_ECUDA; }
+    return LQ_OK;
+}
+
 static inline bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }
 static inline int grid_for(int64_t work_items, int threads, int ctas_per_sm) {
     int64_t want = (work_items + threads - 1) / threads;
@@ -241,6 +263,73 @@ struct RequantParams {
     int has_residual, res_round_bf16;
 };
 
+// ---- conversion-free arithmetic helpers -------------------------------------------------------
+// int<->float conversions, rintf and roundf issue on the slow conversion pipe; the chain below uses
+// magic-number adds instead (exact for the value ranges stated).
+constexpr float MAGIC_RNE = 12582912.0f;            // 1.5 * 2^23
+// small non-negative integer (< 2^22) -> float, exactly
+__device__ __forceinline__ float u2f(uint32_t n) { return __fsub_rn(__uint_as_float(0x4B000000u | n), 8388608.0f); }
+// round-half-even of x for |x| < 2^22 (falls back to rintf beyond)
+__device__ __forceinline__ float rne(float x) {
+    if (fabsf(x) < 4194304.0f) return __fsub_rn(__fadd_rn(x, MAGIC_RNE), MAGIC_RNE);
+    return rintf(x);
+}
+// integer-valued float in [-2^21, 2^21] -> its two's-complement low bits
+__device__ __forceinline__ uint32_t f2bits(float q) { return __float_as_uint(__fadd_rn(q, MAGIC_RNE)); }
+// round-half-away of y for |y| < 2^22: half-even first, then push ties that went towards zero
+__device__ __forceinline__ float rha(float y) {
+    float q = __fsub_rn(__fadd_rn(y, MAGIC_RNE), MAGIC_RNE);
+    float d = __fsub_rn(y, q);
+    if (fabsf(d) == 0.5f && (d > 0.0f) == (y > 0.0f)) q = __fadd_rn(q, copysignf(1.0f, y));
+    return q;
+}
+// |x|*499 + v0 minus its round-half-away integer part (.cu:49-51), v >= 0 assumed small
+__device__ __forceinline__ float hash_dither_fast(float x, float v0) {
+    float v = __fmaf_rn(fabsf(x), 499.0f, v0);
+    return __fsub_rn(v, rha(v));
+}
+__device__ __forceinline__ uint32_t res3_encode_fast(float x, float v, const Curve& c, float& carry) {
+    float S = fabsf(x), q;
+    if (S < c.b1) {
+        q = rha(__fmaf_rn(x, c.c1, v));
+    } else {
+        const bool mid = S < c.b2;
+        float r = __fadd_rn(rha(__fmaf_rn(__fsub_rn(S, mid ? c.b1 : c.b2), mid ? c.c2 : c.c3, v)), mid ? c.t1 : c.t2);
+        q = (x < 0.0f) ? -r : r;
+    }
+    if (q > 7.5f) { carry = 1.0f; return 1u; }
+    carry = 0.0f;
+    float t = q + 8.0f;
+    return (t <= 0.0f) ? 0u : (f2bits(t) & 15u);
+}
+__device__ __forceinline__ float res3_decode_fast(uint32_t nib, const Curve& c) {
+    float s = __fsub_rn(u2f(nib), 8.0f);
+    if (s < -c.t2) return __fmaf_rn(s + c.t2, c.ic3, -c.b2);
+    if (s < -c.t1) return __fmaf_rn(s + c.t1, c.ic2, -c.b1);
+    if (s <= c.t1) return __fmul_rn(s, c.ic1);
+    if (s <= c.t2) return __fmaf_rn(s - c.t1, c.ic2, c.b1);
+    return __fmaf_rn(s - c.t2, c.ic3, c.b2);
+}
+// bf16 rounding (half-even) in integer arithmetic; finite inputs
+template <bool BF> __device__ __forceinline__ float rb(float x) {
+    if (!BF) return x;
+    uint32_t u = __float_as_uint(x);
+    u += 0x7fffu + ((u >> 16) & 1u);
+    return __uint_as_float(u & 0xffff0000u);
+}
+// correctly rounded a/s from r = RN(1/s); only large |a| needs the slow path (tiny |a| cannot change any
+// output of the chain: the quotient stays below 2^-19 either way)
+__device__ __forceinline__ float div_fast(float a, float s, float r, bool scale_ok) {
+    if (scale_ok && fabsf(a) <= 1.1529215e18f) {
+        float q = __fmul_rn(a, r);
+        float e = __fmaf_rn(-q, s, a);
+        q = __fmaf_rn(e, r, q);
+        e = __fmaf_rn(-q, s, a);
+        return __fmaf_rn(e, r, q);
+    }
+    return __fdiv_rn(a, s);
+}
+
 // WBITS 4: codes are nibble pairs (4 bytes per 8 elements), zero point per group, clamp [0,15].
 // WBITS 8: codes are int8 (8 bytes per 8 elements), no zero point, clamp [-128,127].
 template <int WBITS, int CODEC, int DITHER, bool BF>
@@ -257,33 +346,35 @@ __global__ void __launch_bounds__(256) k_requant(const RequantParams p) {
         if (p.w_in) {
             load8(p.w_in, p.w_dtype, e0, lat);
         } else {
-            int code[8];
-            if (WBITS == 4) {
-                uint32_t pk = __ldg(reinterpret_cast<const uint32_t*>(p.codes_in) + w);
+            // issue every load of this word first
+            uint32_t pk0 = 0, pk1 = 0, rw = 0;
+            if (WBITS == 4) pk0 = __ldg(reinterpret_cast<const uint32_t*>(p.codes_in) + w);
+            else { uint2 t = __ldg(reinterpret_cast<const uint2*>(p.codes_in) + w); pk0 = t.x; pk1 = t.y; }
+            const bool use_res = (CODEC != LQ_CODEC_NONE) && p.has_residual;
+            if (use_res) rw = (uint32_t)__ldg(p.words_in + w);
+            float d[8];
+            if (p.delta) load8(p.delta, p.delta_dtype, e0, d);
 #pragma unroll
-                for (int k = 0; k < 8; ++k) code[k] = (int)((pk >> (8 * (k >> 1) + ((k & 1) ? 0 : 4))) & 15u);
-            } else {
-                uint2 pk = __ldg(reinterpret_cast<const uint2*>(p.codes_in) + w);
-#pragma unroll
-                for (int k = 0; k < 8; ++k) code[k] = (int)(int8_t)(((k < 4 ? pk.x : pk.y) >> (8 * (k & 3))) & 0xffu);
+            for (int k = 0; k < 8; ++k) {
+                float c;
+                if (WBITS == 4) c = u2f((pk0 >> (8 * (k >> 1) + ((k & 1) ? 0 : 4))) & 15u);
+                else {   // signed byte: (b ^ 0x80) - 128
+                    uint32_t b = ((k < 4 ? pk0 : pk1) >> (8 * (k & 3))) & 0xffu;
+                    c = __fsub_rn(u2f(b ^ 0x80u), 128.0f);
+                }
+                lat[k] = rb<BF>(__fmul_rn(rb<BF>(__fsub_rn(c, z)), s));
             }
-#pragma unroll
-            for (int k = 0; k < 8; ++k) lat[k] = rnd<BF>(__fmul_rn(rnd<BF>(__fsub_rn((float)code[k], z)), s));
-            if (CODEC != LQ_CODEC_NONE && p.has_residual) {
-                uint32_t rw = (uint32_t)__ldg(p.words_in + w);
+            if (use_res) {
 #pragma unroll
                 for (int k = 0; k < 8; ++k) {
                     uint32_t nib = (rw >> (28 - 4 * k)) & 15u;
-                    float rv = (CODEC == LQ_CODEC_UNIFORM16) ? __fmaf_rn((float)nib, 0.0625f, -0.5f)
-                                                              : bf16r(res3_decode(nib, p.dec));
-                    lat[k] = rnd<BF>(__fadd_rn(rnd<BF>(__fmul_rn(rv, s)), lat[k]));
+                    float rv = (CODEC == LQ_CODEC_UNIFORM16) ? __fmaf_rn(u2f(nib), 0.0625f, -0.5f) : rb<true>(res3_decode_fast(nib, p.dec));
+                    lat[k] = rb<BF>(__fadd_rn(rb<BF>(__fmul_rn(rv, s)), lat[k]));
                 }
             }
             if (p.delta) {
-                float d[8];
-                load8(p.delta, p.delta_dtype, e0, d);
 #pragma unroll
-                for (int k = 0; k < 8; ++k) lat[k] = rnd<BF>(__fadd_rn(lat[k], d[k]));
+                for (int k = 0; k < 8; ++k) lat[k] = rb<BF>(__fadd_rn(lat[k], d[k]));
             }
         }
 
@@ -296,25 +387,26 @@ __global__ void __launch_bounds__(256) k_requant(const RequantParams p) {
         uint32_t rword = 0, q[8];
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
-            float Z = rnd<BF>(div_rn(lat[k], s, rs, s_ok));
-            if (WBITS == 4) Z = rnd<BF>(__fadd_rn(Z, z));
-            float qf = rintf(Z);
-            float r = rnd<BF>(__fsub_rn(Z, qf));
+            float Z = rb<BF>(div_fast(lat[k], s, rs, s_ok));
+            if (WBITS == 4) Z = rb<BF>(__fadd_rn(Z, z));
+            float qf = rne(Z);
+            float r = rb<BF>(__fsub_rn(Z, qf));
             float carry = 0.0f;
             uint32_t nib = 0;
             if (CODEC != LQ_CODEC_NONE) {
-                if (p.res_round_bf16) r = bf16r(r);
+                if (p.res_round_bf16) r = rb<true>(r);
                 if (CODEC == LQ_CODEC_UNIFORM16) {
-                    float d = rintf(__fadd_rn(__fmul_rn(__fadd_rn(r, 0.5f), 16.0f), u[k]));
-                    if (d > 15.9f) { carry = 1.0f; nib = 0u; } else nib = (uint32_t)(int)d & 15u;
+                    // (r+0.5)*16 == fma(r,16,8) exactly (scaling by 16 commutes with rounding); then + dither, round-half-even
+                    uint32_t n = f2bits(__fadd_rn(__fmaf_rn(r, 16.0f, 8.0f), u[k])) & 31u;
+                    if (n >= 16u) { carry = 1.0f; nib = 0u; } else nib = n;
                 } else {
-                    float v = (DITHER == LQ_DITHER_HASH) ? hash_dither(r, p.v0) : u[k];
-                    nib = res3_encode(r, v, p.enc, carry) & 15u;
+                    float v = (DITHER == LQ_DITHER_HASH) ? hash_dither_fast(r, p.v0) : u[k];
+                    nib = res3_encode_fast(r, v, p.enc, carry) & 15u;
                 }
             }
-            qf = rnd<BF>(__fadd_rn(qf, carry));
+            qf = rb<BF>(__fadd_rn(qf, carry));
             qf = (WBITS == 4) ? fminf(fmaxf(qf, 0.0f), 15.0f) : fminf(fmaxf(qf, -128.0f), 127.0f);
-            q[k] = (uint32_t)(int)qf & 0xffu;
+            q[k] = f2bits(qf) & 0xffu;
             rword = (rword << 4) | nib;
         }
         if (CODEC != LQ_CODEC_NONE) p.words_out[w] = (int32_t)rword;
@@ -332,15 +424,25 @@ __global__ void __launch_bounds__(256) k_requant(const RequantParams p) {
     }
 }
 
+template <int WBITS, int CODEC, int DITHER, bool BF>
+static int requant_grid(int64_t n_words) {
+    static int per_sm = 0;
+    if (per_sm == 0) {
+        int n = 0;
+        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, k_requant<WBITS, CODEC, DITHER, BF>, 256, 0) != cudaSuccess || n < 1) n = 4;
+        per_sm = n;
+    }
+    return grid_for(n_words, 256, per_sm);
+}
 template <int WBITS, int CODEC, int DITHER>
 static int launch_requant_bf(const RequantParams& p, bool bf, cudaStream_t st) {
-    int grid = grid_for(p.n_words, 256, 8);
-    if (bf) k_requant<WBITS, CODEC, DITHER, true><<<grid, 256, 0, st>>>(p);
-    else k_requant<WBITS, CODEC, DITHER, false><<<grid, 256, 0, st>>>(p);
+    if (bf) k_requant<WBITS, CODEC, DITHER, true><<<requant_grid<WBITS, CODEC, DITHER, true>(p.n_words), 256, 0, st>>>(p);
+    else k_requant<WBITS, CODEC, DITHER, false><<<requant_grid<WBITS, CODEC, DITHER, false>(p.n_words), 256, 0, st>>>(p);
     return check_launch("k_requant");
 }
 template <int WBITS>
 static int launch_requant(const RequantParams& p, const lq_requant_opts* o, cudaStream_t st) {
+    { int rc_dev = ensure_device_for(p.codes_out); if (rc_dev) return rc_dev; }
     const bool bf = o->math_dtype == LQ_BF16;
     switch (o->codec) {
         case LQ_CODEC_NONE: return launch_requant_bf<WBITS, LQ_CODEC_NONE, LQ_DITHER_HASH>(p, bf, st);
@@ -543,6 +645,7 @@ int lq_res3_quant(void* x, int dtype, int32_t* words, int64_t n_words, int k1, f
                   float v0, lq_stream_t stream) {
     if (n_words == 0) return LQ_OK;
     if (!x || !words || n_words < 0 || !dtype_ok(dtype) || !aligned(x, 16) || !aligned(words, 4)) return LQ_EINVAL;
+    { int rc_dev = ensure_device_for(x); if (rc_dev) return rc_dev; }
     k_res_quant<RQ_3FOLD><<<grid_for(n_words, 256, 8), 256, 0, LQ_ST(stream)>>>(x, dtype, words, n_words,
                                                                                   make_curve(k1, b1, k2, b2, k3), v0);
     return check_launch("lq_res3_quant");
@@ -551,6 +654,7 @@ int lq_res3_dequant(const int32_t* words, void* x, int dtype, int64_t n_words, i
                     int k3, lq_stream_t stream) {
     if (n_words == 0) return LQ_OK;
     if (!x || !words || n_words < 0 || !dtype_ok(dtype) || !aligned(x, 16)) return LQ_EINVAL;
+    { int rc_dev = ensure_device_for(x); if (rc_dev) return rc_dev; }
     k_res_dequant<RQ_3FOLD><<<grid_for(n_words, 256, 8), 256, 0, LQ_ST(stream)>>>(words, x, dtype, n_words,
                                                                                     make_curve(k1, b1, k2, b2, k3));
     return check_launch("lq_res3_dequant");
@@ -558,18 +662,21 @@ int lq_res3_dequant(const int32_t* words, void* x, int dtype, int64_t n_words, i
 int lq_resu_quant(void* x, int dtype, int32_t* words, int64_t n_words, float v0, lq_stream_t stream) {
     if (n_words == 0) return LQ_OK;
     if (!x || !words || n_words < 0 || !dtype_ok(dtype) || !aligned(x, 16)) return LQ_EINVAL;
+    { int rc_dev = ensure_device_for(x); if (rc_dev) return rc_dev; }
     k_res_quant<RQ_UNIFORM><<<grid_for(n_words, 256, 8), 256, 0, LQ_ST(stream)>>>(x, dtype, words, n_words, Curve{}, v0);
     return check_launch("lq_resu_quant");
 }
 int lq_resu_quant_s(void* x, int dtype, int32_t* words, int64_t n_words, lq_stream_t stream) {
     if (n_words == 0) return LQ_OK;
     if (!x || !words || n_words < 0 || !dtype_ok(dtype) || !aligned(x, 16)) return LQ_EINVAL;
+    { int rc_dev = ensure_device_for(x); if (rc_dev) return rc_dev; }
     k_res_quant<RQ_UNIFORM_S><<<grid_for(n_words, 256, 8), 256, 0, LQ_ST(stream)>>>(x, dtype, words, n_words, Curve{}, 0.0f);
     return check_launch("lq_resu_quant_s");
 }
 int lq_resu_dequant(const int32_t* words, void* x, int dtype, int64_t n_words, lq_stream_t stream) {
     if (n_words == 0) return LQ_OK;
     if (!x || !words || n_words < 0 || !dtype_ok(dtype) || !aligned(x, 16)) return LQ_EINVAL;
+    { int rc_dev = ensure_device_for(x); if (rc_dev) return rc_dev; }
     k_res_dequant<RQ_UNIFORM><<<grid_for(n_words, 256, 8), 256, 0, LQ_ST(stream)>>>(words, x, dtype, n_words, Curve{});
     return check_launch("lq_resu_dequant");
 }
@@ -577,12 +684,14 @@ int lq_uniform16_encode(const float* r, const float* noise, int64_t n, int32_t* 
     if (n == 0) return LQ_OK;
     if (!r || !noise || !words || n < 0 || (n % 8) || !aligned(r, 16) || !aligned(noise, 16) || (carry && !aligned(carry, 16)))
         return LQ_EINVAL;
+    { int rc_dev = ensure_device_for(r); if (rc_dev) return rc_dev; }
     k_uniform16_encode<<<grid_for(n / 8, 256, 8), 256, 0, LQ_ST(stream)>>>(r, noise, n / 8, words, carry);
     return check_launch("lq_uniform16_encode");
 }
 int lq_uniform16_decode(const int32_t* words, int64_t n_words, float* out, lq_stream_t stream) {
     if (n_words == 0) return LQ_OK;
     if (!words || !out || n_words < 0 || !aligned(out, 16)) return LQ_EINVAL;
+    { int rc_dev = ensure_device_for(out); if (rc_dev) return rc_dev; }
     k_uniform16_decode<<<grid_for(n_words, 256, 8), 256, 0, LQ_ST(stream)>>>(words, n_words, out);
     return check_launch("lq_uniform16_decode");
 }
@@ -590,12 +699,14 @@ int lq_uniform16_decode(const int32_t* words, int64_t n_words, float* out, lq_st
 int lq_pack_nibbles(const uint8_t* codes, int8_t* packed, int64_t n_codes, lq_stream_t stream) {
     if (n_codes == 0) return LQ_OK;
     if (!codes || !packed || n_codes < 0 || (n_codes % 2) || !aligned(codes, 2)) return LQ_EINVAL;
+    { int rc_dev = ensure_device_for(codes); if (rc_dev) return rc_dev; }
     k_pack_nibbles<<<grid_for(n_codes / 2, 256, 8), 256, 0, LQ_ST(stream)>>>(codes, packed, n_codes / 2);
     return check_launch("lq_pack_nibbles");
 }
 int lq_unpack_nibbles(const int8_t* packed, int8_t* codes, int64_t n_bytes, lq_stream_t stream) {
     if (n_bytes == 0) return LQ_OK;
     if (!codes || !packed || n_bytes < 0 || !aligned(codes, 2)) return LQ_EINVAL;
+    { int rc_dev = ensure_device_for(codes); if (rc_dev) return rc_dev; }
     k_unpack_nibbles<<<grid_for(n_bytes, 256, 8), 256, 0, LQ_ST(stream)>>>(packed, codes, n_bytes);
     return check_launch("lq_unpack_nibbles");
 }
@@ -606,6 +717,7 @@ int lq_a16w4_dequant(const int8_t* qweight, const void* scales, const void* zero
     if (!qweight || !scales || !zeros || !out || numel < 0 || (numel % 8) || group <= 0 || (group % 8) || (numel % group) ||
         !dtype_ok(qp_dtype) || !dtype_ok(out_dtype) || !aligned(qweight, 4) || !aligned(out, 16))
         return LQ_EINVAL;
+    { int rc_dev = ensure_device_for(out); if (rc_dev) return rc_dev; }
     int grid = grid_for(numel / 8, 256, 8);
     if (qp_dtype == LQ_BF16)
         k_a16w4_dequant<true><<<grid, 256, 0, LQ_ST(stream)>>>(reinterpret_cast<const uint32_t*>(qweight), scales, zeros,
@@ -622,6 +734,7 @@ int lq_find_qparams(const void* x, int dtype, int64_t numel, int group, int maxq
     if (!x || !scales || !zeros || numel < 0 || group <= 0 || (group % 8) || (numel % group) || !dtype_ok(dtype) ||
         !aligned(x, 16) || maxq <= 0)
         return LQ_EINVAL;
+    { int rc_dev = ensure_device_for(x); if (rc_dev) return rc_dev; }
     int64_t n_groups = numel / group;
     k_find_qparams<<<grid_for(n_groups * 32, 256, 8), 256, 0, LQ_ST(stream)>>>(x, dtype, n_groups, group, (float)maxq,
                                                                                sym, scales, zeros);
@@ -682,6 +795,7 @@ int lq_a8w8_fold_delta(int8_t* codes, int32_t* words, const void* delta, int del
 int lq_philox_dither(uint64_t seed, uint64_t stream_id, int64_t first_word, int64_t n_words, float* out, lq_stream_t stream) {
     if (n_words == 0) return LQ_OK;
     if (!out || n_words < 0 || !aligned(out, 16)) return LQ_EINVAL;
+    { int rc_dev = ensure_device_for(out); if (rc_dev) return rc_dev; }
     k_philox_dither<<<grid_for(n_words, 256, 8), 256, 0, LQ_ST(stream)>>>(seed, stream_id, first_word, n_words, out);
     return check_launch("lq_philox_dither");
 }
@@ -690,6 +804,7 @@ int lq_opt8_quant(const float* x, int64_t n, int block, uint8_t* q, float* scale
     if (n == 0) return LQ_OK;
     if (!x || !q || !scale || !tmax || n < 0 || block <= 0 || (block % 8) || (n % block) || !aligned(x, 16) || !aligned(q, 8))
         return LQ_EINVAL;
+    { int rc_dev = ensure_device_for(x); if (rc_dev) return rc_dev; }
     int threads = block / 8 >= 256 ? 256 : ((block / 8 + 31) / 32) * 32;
     k_opt8_quant<<<(unsigned)(n / block), threads, 0, LQ_ST(stream)>>>(x, block, q, scale, tmax);
     return check_launch("lq_opt8_quant");
@@ -698,6 +813,7 @@ int lq_opt8_dequant(const uint8_t* q, int64_t n, int block, const float* scale, 
     if (n == 0) return LQ_OK;
     if (!x || !q || !scale || !tmax || n < 0 || block <= 0 || (block % 8) || (n % block) || !aligned(x, 16) || !aligned(q, 8))
         return LQ_EINVAL;
+    { int rc_dev = ensure_device_for(x); if (rc_dev) return rc_dev; }
     k_opt8_dequant<<<grid_for(n / 8, 256, 8), 256, 0, LQ_ST(stream)>>>(q, n / 8, block, scale, tmax, x);
     return check_launch("lq_opt8_dequant");
 }
@@ -705,12 +821,14 @@ int lq_opt8_dequant(const uint8_t* q, int64_t n, int block, const float* scale, 
 int lq_act_quant_per_token(const void* x, int64_t M, int64_t K, int8_t* x8, float* a_scale, lq_stream_t stream) {
     if (M == 0) return LQ_OK;
     if (!x || !x8 || !a_scale || M < 0 || K <= 0 || (K % 8) || !aligned(x, 16) || !aligned(x8, 8)) return LQ_EINVAL;
+    { int rc_dev = ensure_device_for(x); if (rc_dev) return rc_dev; }
     k_act_quant_per_token<<<(unsigned)M, 256, 0, LQ_ST(stream)>>>(reinterpret_cast<const __nv_bfloat16*>(x), K, x8, a_scale);
     return check_launch("lq_act_quant_per_token");
 }
 int lq_act_quant_per_tensor(const void* x, int64_t n, float* clampv_out, int8_t* x8, lq_stream_t stream) {
     if (n == 0) return LQ_OK;
     if (!x || !x8 || !clampv_out || n < 0 || (n % 8) || !aligned(x, 16) || !aligned(x8, 8)) return LQ_EINVAL;
+    { int rc_dev = ensure_device_for(x); if (rc_dev) return rc_dev; }
     int grid = grid_for(n / 8, 256, 8);
     k_set_neg_inf<<<1, 1, 0, LQ_ST(stream)>>>(clampv_out);
     k_tensor_max<<<grid, 256, 0, LQ_ST(stream)>>>(reinterpret_cast<const __nv_bfloat16*>(x), n / 8, clampv_out);

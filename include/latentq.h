@@ -187,6 +187,13 @@ LQ_API int lq_gemm_a16w4_fwd_static(const void* x, const int8_t* qweight, const 
  * raises a device flag.  This call synchronises with the device, returns LQ_ETIMEOUT if the flag is set
  * (LQ_OK otherwise) and clears it when `reset` is non-zero.  (No counterpart in the reference.) */
 LQ_API int lq_gemm_device_status(int reset);
+/* Phase profile of the GEMM kernels (no counterpart in the reference).  Synchronises with the device, copies
+ * the 16 cycle counters accumulated since the last call into out16 (may be NULL), clears them and switches
+ * collection on/off.  Counters (summed over CTAs): [0] producer waiting for a free stage, [1] MMA issuer
+ * waiting for TMA data, [2] MMA issuer waiting for the dequantised tile, [3] MMA issuer waiting for a free
+ * accumulator, [4] MMA role total, [5] dequant waiting for TMA data, [6] dequant role total,
+ * [7] epilogue waiting for an accumulator, [8] epilogue role total, [9] number of CTAs. */
+LQ_API int lq_gemm_profile(int enable, unsigned long long* out16);
 
 #ifdef __cplusplus
 }

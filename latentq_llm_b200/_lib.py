@@ -71,6 +71,7 @@ SIGNATURES = {
     "lq_gemm_a16w4_fwd": [_p, _p, _p, _p, _p, _p, _i64, _i64, _i64, _i, _p, _sz, _p],
     "lq_gemm_a16w4_dgrad": [_p, _p, _p, _p, _p, _i64, _i64, _i64, _i, _p, _sz, _p],
     "lq_gemm_device_status": [_i],
+    "lq_gemm_profile": [_i, _p],
     "lq_gemm_a16w4_fwd_static_max_bytes": [],
     "lq_gemm_a16w4_fwd_static": [_p, _p, _p, _p, _p, _p, _i64, _i64, _i64, _i, _p],
     "lq_gemm_a8w8": [_p, _p, _p, _p, _f, _p, _p, _p, _i64, _i64, _i64, _p, _sz, _p],

@@ -12,7 +12,7 @@
 //   warp 0      : TMA producer   (token tile + raw packed int4 tile, or both int8 tiles)
 //   warp 1      : MMA issuer     (one elected thread issues tcgen05.mma; owns TMEM alloc/dealloc)
 //   warps 2..5  : epilogue       (tcgen05.ld -> scale/bias -> bf16 / partial sums -> global)
-//   warps 6..13 : dequant        (A16W4 only: raw int4 in smem -> bf16((q-z)*s) -> 128B-swizzled MMA tile)
+//   warps 6..21 : dequant        (A16W4 only: raw int4 in smem -> bf16((q-z)*s) -> 128B-swizzled MMA tile)
 //
 // Forward and grad-input share the dequant stage: a row of W[N,K] always becomes 128-byte rows of the
 // swizzled tile; forward describes that tile to the tensor core as K-major, grad-input as MN-major.
@@ -21,6 +21,7 @@
 // memory, all roles leave their loops, in-flight bulk copies are given time to land, TMEM is freed and a
 // global status word is set (read back with lq_gemm_device_status).
 #include <cuda.h>
+#include <cstdlib>
 
 #include "lq_common.cuh"
 
@@ -32,11 +33,18 @@ constexpr int TILE_R = 128;           // weight rows per tile (MMA M)
 constexpr int ROW_BYTES = 128;        // one swizzle row
 constexpr int A_TILE_BYTES = TILE_R * ROW_BYTES;
 constexpr int RAW_BYTES = 4096;       // packed int4 bytes per stage (128 rows x 64 k, or 64 rows x 128 k)
-constexpr int NUM_DQ_WARPS = 8;
+constexpr int NUM_DQ_WARPS = 16;          // 512 dequant threads, 8 packed bytes (16 weights) each per stage
+constexpr int DQ_PREFETCH = 4;            // stages of scale/zero-point prefetch held in registers
 constexpr int MAX_STAGES = 8;
 constexpr long long WAIT_BUDGET_CYCLES = 2000000000LL;   // ~1 s
 
 __device__ int g_gemm_status;   // 0 = fine, 1 = a bounded wait expired in some CTA
+// Optional phase profile (lq_gemm_profile): cycles summed over CTAs.
+//  [0] producer waiting for a free stage   [1] MMA waiting for TMA data   [2] MMA waiting for the dequantised tile
+//  [3] MMA waiting for a free accumulator  [4] MMA role total             [5] dequant waiting for TMA data
+//  [6] dequant role total                  [7] epilogue waiting for an accumulator  [8] epilogue role total  [9] CTAs
+__device__ unsigned long long g_gemm_prof[16];
+__device__ int g_gemm_prof_on;
 
 // ---------------------------------------------------------------------------------------------
 // PTX wrappers
@@ -72,6 +80,14 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
             if (clock64() - t0 > WAIT_BUDGET_CYCLES) { *abort_flag = 1; return false; }
         }
     }
+}
+// mbar_wait that also accumulates the cycles spent waiting (only when profiling is on)
+__device__ __forceinline__ bool mbar_wait_t(uint32_t bar, uint32_t parity, volatile int* abort_flag, bool prof, long long& acc) {
+    if (!prof) return mbar_wait(bar, parity, abort_flag);
+    const long long t0 = clock64();
+    const bool ok = mbar_wait(bar, parity, abort_flag);
+    acc += clock64() - t0;
+    return ok;
 }
 __device__ __forceinline__ void fence_barrier_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
 __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
@@ -161,20 +177,27 @@ struct GemmParams {
     void* partial;                 // split-K partial sums [splits][M][R] (fp32 / int32)
 };
 
-template <int KIND, int TN>
+// RT = weight-row tiles (of 128 rows) a CTA computes against one token tile.  RT = 2 halves the token-tile
+// bytes fetched from L2 per flop (the dominant operand traffic) at the cost of a shallower pipeline.
+template <int KIND, int TN, int RT>
 struct Cfg {
     static constexpr bool I8 = KIND == KIND_I8;
     static constexpr bool W4 = !I8;
+    static constexpr int A_BYTES = RT * A_TILE_BYTES;
     static constexpr int B_TILE_BYTES = TN * ROW_BYTES;
-    static constexpr int STAGE_BYTES = A_TILE_BYTES + B_TILE_BYTES + (W4 ? RAW_BYTES : 0);
+    static constexpr int RAW_TOTAL = W4 ? RT * RAW_BYTES : 0;
+    static constexpr int STAGE_BYTES = A_BYTES + B_TILE_BYTES + RAW_TOTAL;
     static constexpr int STAGES_FIT = (226 * 1024 - 1024) / STAGE_BYTES;
     static constexpr int STAGES = STAGES_FIT > MAX_STAGES ? MAX_STAGES : STAGES_FIT;
     static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
-    static constexpr int TMEM_COLS = (2 * TN) < 32 ? 32 : (2 * TN);
+    static constexpr int ACC_COLS = RT * TN;                               // TMEM columns of one accumulator set
+    static constexpr int ACC_BUFS = (2 * ACC_COLS <= 512) ? 2 : 1;         // double-buffered when TMEM allows
+    static constexpr int TMEM_COLS = (ACC_BUFS * ACC_COLS) < 32 ? 32 : (ACC_BUFS * ACC_COLS);
     static constexpr int NUM_WARPS = 6 + (W4 ? NUM_DQ_WARPS : 0);
     static constexpr int THREADS = NUM_WARPS * 32;
-    static constexpr uint32_t TX_BYTES = (uint32_t)(B_TILE_BYTES + (W4 ? RAW_BYTES : A_TILE_BYTES));
+    static constexpr uint32_t TX_BYTES = (uint32_t)(B_TILE_BYTES + (W4 ? RAW_TOTAL : A_BYTES));
     static constexpr int UMMA_PER_STAGE = 4;   // 128 bytes of contraction per stage / 32 bytes per MMA
+    static_assert(ACC_COLS <= 512 && STAGES >= 2, "tile configuration does not fit");
 };
 
 struct SmemCtl {
@@ -216,10 +239,10 @@ __device__ __forceinline__ uint4 dequant8(uint32_t w, __nv_bfloat162 z128, __nv_
 // ---------------------------------------------------------------------------------------------
 // The kernel
 // ---------------------------------------------------------------------------------------------
-template <int KIND, int TN>
-__global__ void __launch_bounds__(Cfg<KIND, TN>::THREADS, 1)
+template <int KIND, int TN, int RT>
+__global__ void __launch_bounds__(Cfg<KIND, TN, RT>::THREADS, 1)
 k_gemm(const __grid_constant__ CUtensorMap map_tok, const __grid_constant__ CUtensorMap map_w, const GemmParams p) {
-    using C = Cfg<KIND, TN>;
+    using C = Cfg<KIND, TN, RT>;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     SmemCtl* ctl = reinterpret_cast<SmemCtl*>(smem + C::STAGES * C::STAGE_BYTES);
@@ -227,9 +250,10 @@ k_gemm(const __grid_constant__ CUtensorMap map_tok, const __grid_constant__ CUte
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t smem_base = smem_u32(smem);
-    auto a_tile = [&](int s) { return smem_base + s * C::STAGE_BYTES; };
-    auto b_tile = [&](int s) { return smem_base + s * C::STAGE_BYTES + A_TILE_BYTES; };
-    auto raw_tile = [&](int s) { return smem + s * C::STAGE_BYTES + A_TILE_BYTES + C::B_TILE_BYTES; };
+    // stage layout: [A tile 0 .. RT-1][B tile][raw 0 .. RT-1]
+    auto a_tile = [&](int s, int r) { return smem_base + s * C::STAGE_BYTES + r * A_TILE_BYTES; };
+    auto b_tile = [&](int s) { return smem_base + s * C::STAGE_BYTES + C::A_BYTES; };
+    auto raw_tile = [&](int s, int r) { return smem + s * C::STAGE_BYTES + C::A_BYTES + C::B_TILE_BYTES + r * RAW_BYTES; };
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < C::STAGES; ++s) {
@@ -254,36 +278,38 @@ k_gemm(const __grid_constant__ CUtensorMap map_tok, const __grid_constant__ CUte
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = ctl->tmem_base;
+    const bool prof = g_gemm_prof_on != 0;
 
-    const int n_items = p.r_tiles * p.t_tiles * p.splits;
+    const int n_items = p.r_tiles * p.t_tiles * p.splits;     // r_tiles counts groups of RT row tiles
 
     if (warp == 0) {
         // ===================== TMA producer =====================
         if (lane == 0) {
             int stage = 0; uint32_t phase = 0;
             bool ok = true;
+            long long w_empty = 0;
             for (int item = blockIdx.x; ok && item < n_items; item += gridDim.x) {
-                const int t_tile = item % p.t_tiles, r_tile = (item / p.t_tiles) % p.r_tiles, split = item / (p.t_tiles * p.r_tiles);
+                const int r_tile = item % p.r_tiles, t_tile = (item / p.r_tiles) % p.t_tiles, split = item / (p.t_tiles * p.r_tiles);
                 const int kb0 = split * p.kb_per_split, kb1 = min(p.kb_total, kb0 + p.kb_per_split);
                 for (int kb = kb0; kb < kb1; ++kb) {
-                    if (!(ok = mbar_wait(smem_u32(&ctl->empty[stage]), phase ^ 1u, abort_flag))) break;
+                    if (!(ok = mbar_wait_t(smem_u32(&ctl->empty[stage]), phase ^ 1u, abort_flag, prof, w_empty))) break;
                     const uint32_t bar = smem_u32(&ctl->full[stage]);
                     mbar_expect_tx(bar, C::TX_BYTES);
-                    if (KIND == KIND_I8) {
-                        tma_load_2d(a_tile(stage), &map_w, kb * 128, r_tile * TILE_R, bar);
-                        tma_load_2d(b_tile(stage), &map_tok, kb * 128, t_tile * TN, bar);
-                    } else if (KIND == KIND_FWD) {
-                        // raw: 128 weight rows x 32 bytes (64 k)
-                        tma_load_2d(smem_u32(raw_tile(stage)), &map_w, kb * 32, r_tile * TILE_R, bar);
-                        tma_load_2d(b_tile(stage), &map_tok, kb * 64, t_tile * TN, bar);
-                    } else {
-                        // raw: 64 weight rows (n) x 64 bytes (128 k)
-                        tma_load_2d(smem_u32(raw_tile(stage)), &map_w, r_tile * 64, kb * 64, bar);
-                        tma_load_2d(b_tile(stage), &map_tok, kb * 64, t_tile * TN, bar);
+#pragma unroll
+                    for (int r = 0; r < RT; ++r) {
+                        const int row0 = (r_tile * RT + r) * TILE_R;
+                        if (KIND == KIND_I8)            // int8 weights straight into the MMA tile
+                            tma_load_2d(a_tile(stage, r), &map_w, kb * 128, row0, bar);
+                        else if (KIND == KIND_FWD)      // raw: 128 weight rows x 32 bytes (64 k)
+                            tma_load_2d(smem_u32(raw_tile(stage, r)), &map_w, kb * 32, row0, bar);
+                        else                            // raw: 64 weight rows (n) x 64 bytes (128 k)
+                            tma_load_2d(smem_u32(raw_tile(stage, r)), &map_w, row0 / 2, kb * 64, bar);
                     }
+                    tma_load_2d(b_tile(stage), &map_tok, kb * (C::I8 ? 128 : 64), t_tile * TN, bar);
                     if (++stage == C::STAGES) { stage = 0; phase ^= 1u; }
                 }
             }
+            if (prof) atomicAdd(&g_gemm_prof[0], (unsigned long long)w_empty);
         }
     } else if (warp == 1) {
         // ===================== MMA issuer =====================
@@ -292,34 +318,44 @@ k_gemm(const __grid_constant__ CUtensorMap map_tok, const __grid_constant__ CUte
             int stage = 0; uint32_t phase = 0;
             int acc = 0; uint32_t acc_phase = 0;
             bool ok = true;
+            long long w_full = 0, w_aready = 0, w_acc = 0;
+            const long long t_role = prof ? clock64() : 0;
             for (int item = blockIdx.x; ok && item < n_items; item += gridDim.x) {
                 const int split = item / (p.t_tiles * p.r_tiles);
                 const int kb0 = split * p.kb_per_split, kb1 = min(p.kb_total, kb0 + p.kb_per_split);
-                if (!(ok = mbar_wait(smem_u32(&ctl->acc_empty[acc]), acc_phase ^ 1u, abort_flag))) break;
+                if (!(ok = mbar_wait_t(smem_u32(&ctl->acc_empty[acc]), acc_phase ^ 1u, abort_flag, prof, w_acc))) break;
                 tc_fence_after();
-                const uint32_t d_tmem = tmem_base + (uint32_t)(acc * TN);
+                const uint32_t d_tmem = tmem_base + (uint32_t)(acc * C::ACC_COLS);
                 for (int kb = kb0; kb < kb1; ++kb) {
-                    if (!(ok = mbar_wait(smem_u32(&ctl->full[stage]), phase, abort_flag))) break;
-                    if (C::W4) { if (!(ok = mbar_wait(smem_u32(&ctl->a_ready[stage]), phase, abort_flag))) break; }
+                    if (!(ok = mbar_wait_t(smem_u32(&ctl->full[stage]), phase, abort_flag, prof, w_full))) break;
+                    if (C::W4) { if (!(ok = mbar_wait_t(smem_u32(&ctl->a_ready[stage]), phase, abort_flag, prof, w_aready))) break; }
                     tc_fence_after();
                     // K-major tiles: 8-row groups are 1024 B apart; one MMA consumes 32 B of every row.
                     // MN-major A (grad-input): 64-element atoms are 8192 B apart (leading), 8-row groups of the
                     // contraction 1024 B apart (stride); one MMA consumes 16 contraction rows = 2048 B.
-                    const uint64_t a_desc = (KIND == KIND_DGRAD) ? make_smem_desc(a_tile(stage), 8192, 1024)
-                                                                 : make_smem_desc(a_tile(stage), 16, 1024);
                     const uint64_t b_desc = make_smem_desc(b_tile(stage), 16, 1024);
                     const uint32_t a_step = (KIND == KIND_DGRAD) ? (2048u >> 4) : (32u >> 4);
 #pragma unroll
-                    for (int kk = 0; kk < C::UMMA_PER_STAGE; ++kk) {
-                        umma<C::I8>(d_tmem, a_desc + (uint64_t)(kk * a_step), b_desc + (uint64_t)(kk * 2),
-                                    IDESC, (kb > kb0 || kk > 0) ? 1u : 0u);
+                    for (int r = 0; r < RT; ++r) {
+                        const uint64_t a_desc = (KIND == KIND_DGRAD) ? make_smem_desc(a_tile(stage, r), 8192, 1024)
+                                                                     : make_smem_desc(a_tile(stage, r), 16, 1024);
+#pragma unroll
+                        for (int kk = 0; kk < C::UMMA_PER_STAGE; ++kk) {
+                            umma<C::I8>(d_tmem + (uint32_t)(r * TN), a_desc + (uint64_t)(kk * a_step), b_desc + (uint64_t)(kk * 2),
+                                        IDESC, (kb > kb0 || kk > 0) ? 1u : 0u);
+                        }
                     }
                     umma_commit(smem_u32(&ctl->empty[stage]));
                     if (++stage == C::STAGES) { stage = 0; phase ^= 1u; }
                 }
                 if (!ok) break;
                 umma_commit(smem_u32(&ctl->acc_full[acc]));
-                if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+                if (++acc == C::ACC_BUFS) { acc = 0; acc_phase ^= 1u; }
+            }
+            if (prof) {
+                atomicAdd(&g_gemm_prof[1], (unsigned long long)w_full); atomicAdd(&g_gemm_prof[2], (unsigned long long)w_aready);
+                atomicAdd(&g_gemm_prof[3], (unsigned long long)w_acc); atomicAdd(&g_gemm_prof[4], (unsigned long long)(clock64() - t_role));
+                atomicAdd(&g_gemm_prof[9], 1ull);
             }
         }
     } else if (warp < 6) {
@@ -327,93 +363,117 @@ k_gemm(const __grid_constant__ CUtensorMap map_tok, const __grid_constant__ CUte
         const int quad = warp & 3;                 // TMEM lane quadrant this warp may read
         int acc = 0; uint32_t acc_phase = 0;
         bool ok = true;
+        long long w_accf = 0;
+        const long long t_role = prof ? clock64() : 0;
         for (int item = blockIdx.x; ok && item < n_items; item += gridDim.x) {
-            const int t_tile = item % p.t_tiles, r_tile = (item / p.t_tiles) % p.r_tiles, split = item / (p.t_tiles * p.r_tiles);
-            if (!(ok = mbar_wait(smem_u32(&ctl->acc_full[acc]), acc_phase, abort_flag))) break;
+            const int r_tile = item % p.r_tiles, t_tile = (item / p.r_tiles) % p.t_tiles, split = item / (p.t_tiles * p.r_tiles);
+            if (!(ok = mbar_wait_t(smem_u32(&ctl->acc_full[acc]), acc_phase, abort_flag, prof, w_accf))) break;
             tc_fence_after();
-            const int r = r_tile * TILE_R + quad * 32 + lane;
-            const bool r_ok = r < p.R;
-            const float cs = (C::I8 && p.col_scale && r_ok) ? __ldg(p.col_scale + r) : 1.0f;
-            const float bias = (p.bias && r_ok) ? __bfloat162float(p.bias[r]) : 0.0f;
 #pragma unroll 1
-            for (int c0 = 0; c0 < TN; c0 += 16) {
-                uint32_t v[16];
-                tmem_ld16(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * TN + c0), v);
-                tmem_ld_wait();
+            for (int rr = 0; rr < RT; ++rr) {
+                const int r = (r_tile * RT + rr) * TILE_R + quad * 32 + lane;
+                const bool r_ok = r < p.R;
+                const float cs = (C::I8 && p.col_scale && r_ok) ? __ldg(p.col_scale + r) : 1.0f;
+                const float bias = (p.bias && r_ok) ? __bfloat162float(p.bias[r]) : 0.0f;
+#pragma unroll 1
+                for (int c0 = 0; c0 < TN; c0 += 16) {
+                    uint32_t v[16];
+                    tmem_ld16(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * C::ACC_COLS + rr * TN + c0), v);
+                    tmem_ld_wait();
 #pragma unroll
-                for (int j = 0; j < 16; ++j) {
-                    const int t = t_tile * TN + c0 + j;
-                    if (!r_ok || t >= p.M) continue;
-                    const size_t o = (size_t)t * p.R + r;
-                    if (p.splits > 1) {
-                        reinterpret_cast<uint32_t*>(p.partial)[(size_t)split * p.M * p.R + o] = v[j];
-                    } else if (C::I8) {
-                        const int32_t a = (int32_t)v[j];
-                        if (p.acc_out) p.acc_out[o] = a;
-                        float f = (float)a;
-                        if (p.row_scale) f = __fmul_rn(f, __ldg(p.row_scale + t));
-                        f = __fmul_rn(__fmul_rn(f, cs), p.alpha);
-                        p.out[o] = __float2bfloat16_rn(__fadd_rn(f, bias));
-                    } else {
-                        float f = bf16r(__uint_as_float(v[j]));          // mm output is bf16, bias added after
-                        p.out[o] = __float2bfloat16_rn(p.bias ? __fadd_rn(f, bias) : f);
+                    for (int j = 0; j < 16; ++j) {
+                        const int t = t_tile * TN + c0 + j;
+                        if (!r_ok || t >= p.M) continue;
+                        const size_t o = (size_t)t * p.R + r;
+                        if (p.splits > 1) {
+                            reinterpret_cast<uint32_t*>(p.partial)[(size_t)split * p.M * p.R + o] = v[j];
+                        } else if (C::I8) {
+                            const int32_t a = (int32_t)v[j];
+                            if (p.acc_out) p.acc_out[o] = a;
+                            float f = (float)a;
+                            if (p.row_scale) f = __fmul_rn(f, __ldg(p.row_scale + t));
+                            f = __fmul_rn(__fmul_rn(f, cs), p.alpha);
+                            p.out[o] = __float2bfloat16_rn(__fadd_rn(f, bias));
+                        } else {
+                            float f = bf16r(__uint_as_float(v[j]));          // mm output is bf16, bias added after
+                            p.out[o] = __float2bfloat16_rn(p.bias ? __fadd_rn(f, bias) : f);
+                        }
                     }
                 }
             }
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&ctl->acc_empty[acc]));
-            if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+            if (++acc == C::ACC_BUFS) { acc = 0; acc_phase ^= 1u; }
+        }
+        if (prof && warp == 2 && lane == 0) {
+            atomicAdd(&g_gemm_prof[7], (unsigned long long)w_accf); atomicAdd(&g_gemm_prof[8], (unsigned long long)(clock64() - t_role));
         }
     } else {
         // ===================== dequant (A16W4) =====================
         if (C::W4) {
-            const int t = threadIdx.x - 6 * 32;          // 0..255, one 16-byte slice of the raw tile each
+            const int t = threadIdx.x - 6 * 32;          // 0..511, one 8-byte slice (16 weights) of each raw tile
             int stage = 0; uint32_t phase = 0;
             bool ok = true;
             const int groups_per_row = p.wcols / p.group;
+            const int n_rows = (KIND == KIND_FWD) ? p.R : p.C;
+            // geometry of this thread's slice inside a raw tile
+            //   forward   : raw [128 rows][32 B]; row = t/4, 16 k at (t%4)*16   -> row `row` of the K-major tile
+            //   grad-input: raw [ 64 rows][64 B]; row = t/8, 16 k at (t%8)*16   -> row `row` of MN-atom (t%8)/4
+            const int row = (KIND == KIND_FWD) ? (t >> 2) : (t >> 3);
+            const int sub = (KIND == KIND_FWD) ? (t & 3) : (t & 7);
+            const int dst_off = (KIND == KIND_FWD) ? row * ROW_BYTES : ((sub >> 2) * 8192 + row * ROW_BYTES);
+            const int chunk0 = (sub & 3) * 2;
+            const int swz = row & 7;
+            long long w_dq = 0;
+            const long long t_role = prof ? clock64() : 0;
             for (int item = blockIdx.x; ok && item < n_items; item += gridDim.x) {
-                const int r_tile = (item / p.t_tiles) % p.r_tiles, split = item / (p.t_tiles * p.r_tiles);
+                const int r_tile = item % p.r_tiles, split = item / (p.t_tiles * p.r_tiles);
                 const int kb0 = split * p.kb_per_split, kb1 = min(p.kb_total, kb0 + p.kb_per_split);
-                for (int kb = kb0; kb < kb1; ++kb) {
-                    // which weight row / k range this thread converts
-                    int wrow, k_abs, dst_off;
-                    if (KIND == KIND_FWD) {
-                        const int row = t >> 1, half = t & 1;
-                        wrow = r_tile * TILE_R + row;
-                        k_abs = kb * 64 + half * 32;
-                        dst_off = row * ROW_BYTES;
-                    } else {
-                        const int row = t >> 2, q = t & 3;                  // row = contraction index n within the stage
-                        wrow = kb * 64 + row;
-                        k_abs = r_tile * TILE_R + q * 32;
-                        dst_off = (q >> 1) * 8192 + row * ROW_BYTES;
-                    }
-                    const int swz = (KIND == KIND_FWD) ? ((t >> 1) & 7) : ((t >> 2) & 7);
-                    const int chunk0 = (KIND == KIND_FWD) ? (t & 1) * 4 : (t & 1) * 4;
-                    float sf = 0.0f, zf = 0.0f;
-                    const int n_rows = (KIND == KIND_FWD) ? p.R : p.C;
-                    if (wrow < n_rows && k_abs < p.wcols) {
-                        const size_t gi = (size_t)wrow * groups_per_row + (size_t)(k_abs / p.group);
-                        sf = __bfloat162float(p.scales[gi]);
-                        zf = __bfloat162float(p.zeros[gi]);
-                    }
-                    const __nv_bfloat162 s2 = __float2bfloat162_rn(sf);
-                    const __nv_bfloat162 z128 = __float2bfloat162_rn(zf + 128.0f);
-                    if (!(ok = mbar_wait(smem_u32(&ctl->full[stage]), phase, abort_flag))) break;
-                    const uint4 rawv = *reinterpret_cast<const uint4*>(raw_tile(stage) + t * 16);
-                    uint8_t* dst = smem + stage * C::STAGE_BYTES + dst_off;
-                    const uint32_t wv[4] = {rawv.x, rawv.y, rawv.z, rawv.w};
+                // scale / zero-point of (weight row, group) for k-block kb, as raw bf16 bits (scale | zero << 16)
+                auto load_qp = [&](int kb, int r) -> uint32_t {
+                    int wrow, k_abs;
+                    if (KIND == KIND_FWD) { wrow = (r_tile * RT + r) * TILE_R + row; k_abs = kb * 64 + sub * 16; }
+                    else { wrow = kb * 64 + row; k_abs = (r_tile * RT + r) * TILE_R + sub * 16; }
+                    if (kb >= kb1 || wrow >= n_rows || k_abs >= p.wcols) return 0u;
+                    const size_t gi = (size_t)wrow * groups_per_row + (size_t)(k_abs / p.group);
+                    const uint32_t sc = __ldg(reinterpret_cast<const unsigned short*>(p.scales) + gi);
+                    const uint32_t zp = __ldg(reinterpret_cast<const unsigned short*>(p.zeros) + gi);
+                    return sc | (zp << 16);
+                };
+                uint32_t qp[DQ_PREFETCH][RT];
 #pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        const uint4 o = dequant8(wv[j], z128, s2);
-                        *reinterpret_cast<uint4*>(dst + (((chunk0 + j) ^ swz) << 4)) = o;
+                for (int u = 0; u < DQ_PREFETCH; ++u)
+#pragma unroll
+                    for (int r = 0; r < RT; ++r) qp[u][r] = load_qp(kb0 + u, r);
+                for (int kbb = kb0; ok && kbb < kb1; kbb += DQ_PREFETCH) {
+#pragma unroll
+                    for (int u = 0; u < DQ_PREFETCH; ++u) {
+                        const int kb = kbb + u;
+                        if (kb >= kb1) break;
+                        uint32_t cur[RT];
+#pragma unroll
+                        for (int r = 0; r < RT; ++r) { cur[r] = qp[u][r]; qp[u][r] = load_qp(kb + DQ_PREFETCH, r); }
+                        if (!(ok = mbar_wait_t(smem_u32(&ctl->full[stage]), phase, abort_flag, prof, w_dq))) break;
+#pragma unroll
+                        for (int r = 0; r < RT; ++r) {
+                            const float sf = __uint_as_float(cur[r] << 16), zf = __uint_as_float(cur[r] & 0xffff0000u);
+                            const __nv_bfloat162 s2 = __float2bfloat162_rn(sf);
+                            const __nv_bfloat162 z128 = __float2bfloat162_rn(zf + 128.0f);
+                            const uint2 rawv = *reinterpret_cast<const uint2*>(raw_tile(stage, r) + t * 8);
+                            uint8_t* dst = smem + stage * C::STAGE_BYTES + r * A_TILE_BYTES + dst_off;
+                            *reinterpret_cast<uint4*>(dst + (((chunk0 + 0) ^ swz) << 4)) = dequant8(rawv.x, z128, s2);
+                            *reinterpret_cast<uint4*>(dst + (((chunk0 + 1) ^ swz) << 4)) = dequant8(rawv.y, z128, s2);
+                        }
+                        fence_proxy_async();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(smem_u32(&ctl->a_ready[stage]));
+                        if (++stage == C::STAGES) { stage = 0; phase ^= 1u; }
                     }
-                    fence_proxy_async();
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(smem_u32(&ctl->a_ready[stage]));
-                    if (++stage == C::STAGES) { stage = 0; phase ^= 1u; }
                 }
+            }
+            if (prof && t == 0) {
+                atomicAdd(&g_gemm_prof[5], (unsigned long long)w_dq); atomicAdd(&g_gemm_prof[6], (unsigned long long)(clock64() - t_role));
             }
         }
     }
@@ -463,15 +523,21 @@ __global__ void __launch_bounds__(256) k_splitk_reduce(const GemmParams p) {
 // ---------------------------------------------------------------------------------------------
 // Host side: plan, tensor maps, launch
 // ---------------------------------------------------------------------------------------------
-struct Plan { int tn, r_tiles, t_tiles, splits, kb_total, kb_per_split; };
+struct Plan { int tn, rt, r_tiles, t_tiles, splits, kb_total, kb_per_split; };
 
 static Plan make_plan(int kind, int64_t M, int64_t N, int64_t K) {
     Plan pl{};
     const int64_t R = (kind == KIND_DGRAD) ? K : N;
     const int64_t Cc = (kind == KIND_DGRAD) ? N : K;
     pl.tn = M <= 16 ? 16 : (M <= 64 ? 64 : (M <= 128 ? 128 : 256));
-    pl.r_tiles = (int)((R + TILE_R - 1) / TILE_R);
     pl.t_tiles = (int)((M + pl.tn - 1) / pl.tn);
+    const int r_tiles1 = (int)((R + TILE_R - 1) / TILE_R);
+    // Two weight-row tiles per CTA for grad-input at large token counts: measured faster there (its dequant
+    // stage is the slower one, and sharing the token tile relieves shared-memory bandwidth); forward is faster
+    // with one tile per CTA and a double-buffered accumulator.
+    pl.rt = (kind == KIND_DGRAD && pl.tn == 256 && r_tiles1 >= 2 && (int64_t)((r_tiles1 + 1) / 2) * pl.t_tiles >= sm_count()) ? 2 : 1;
+    if (const char* e = getenv("LQ_GEMM_RT")) { int v = atoi(e); if ((v == 1 || v == 2) && pl.tn == 256) pl.rt = v; }
+    pl.r_tiles = (r_tiles1 + pl.rt - 1) / pl.rt;
     const int bk = (kind == KIND_I8) ? 128 : 64;
     pl.kb_total = (int)((Cc + bk - 1) / bk);
     const int tiles = pl.r_tiles * pl.t_tiles;
@@ -518,20 +584,20 @@ static int make_map(CUtensorMap* m, const void* base, CUtensorMapDataType dt, in
     return LQ_OK;
 }
 
-template <int KIND, int TN>
+template <int KIND, int TN, int RT>
 static int launch_tn(const CUtensorMap& mt, const CUtensorMap& mw, const GemmParams& p, cudaStream_t st) {
-    using C = Cfg<KIND, TN>;
+    using C = Cfg<KIND, TN, RT>;
     static bool attr_done[64] = {};
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev >= 0 && dev < 64 && !attr_done[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(k_gemm<KIND, TN>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
+        cudaError_t e = cudaFuncSetAttribute(k_gemm<KIND, TN, RT>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
         if (e != cudaSuccess) { set_cuda_error(e, "cudaFuncSetAttribute"); return LQ_ECUDA; }
         attr_done[dev] = true;
     }
     const int items = p.r_tiles * p.t_tiles * p.splits;
     const int grid = items < sm_count() ? items : sm_count();
-    k_gemm<KIND, TN><<<grid, C::THREADS, C::SMEM_BYTES, st>>>(mt, mw, p);
+    k_gemm<KIND, TN, RT><<<grid, C::THREADS, C::SMEM_BYTES, st>>>(mt, mw, p);
     int rc = check_launch("k_gemm");
     if (rc) return rc;
     if (p.splits > 1) {
@@ -544,12 +610,12 @@ static int launch_tn(const CUtensorMap& mt, const CUtensorMap& mw, const GemmPar
     return rc;
 }
 template <int KIND>
-static int launch_kind(int tn, const CUtensorMap& mt, const CUtensorMap& mw, const GemmParams& p, cudaStream_t st) {
+static int launch_kind(int tn, int rt, const CUtensorMap& mt, const CUtensorMap& mw, const GemmParams& p, cudaStream_t st) {
     switch (tn) {
-        case 16: return launch_tn<KIND, 16>(mt, mw, p, st);
-        case 64: return launch_tn<KIND, 64>(mt, mw, p, st);
-        case 128: return launch_tn<KIND, 128>(mt, mw, p, st);
-        case 256: return launch_tn<KIND, 256>(mt, mw, p, st);
+        case 16: return launch_tn<KIND, 16, 1>(mt, mw, p, st);
+        case 64: return launch_tn<KIND, 64, 1>(mt, mw, p, st);
+        case 128: return launch_tn<KIND, 128, 1>(mt, mw, p, st);
+        case 256: return rt == 2 ? launch_tn<KIND, 256, 2>(mt, mw, p, st) : launch_tn<KIND, 256, 1>(mt, mw, p, st);
     }
     return LQ_EUNSUPPORTED;
 }
@@ -585,9 +651,9 @@ static int run_gemm(int kind, const void* tok, const void* w, GemmParams p, int6
     }
     if (rc) return rc;
     switch (kind) {
-        case KIND_FWD: return launch_kind<KIND_FWD>(pl.tn, mt, mw, p, st);
-        case KIND_DGRAD: return launch_kind<KIND_DGRAD>(pl.tn, mt, mw, p, st);
-        case KIND_I8: return launch_kind<KIND_I8>(pl.tn, mt, mw, p, st);
+        case KIND_FWD: return launch_kind<KIND_FWD>(pl.tn, pl.rt, mt, mw, p, st);
+        case KIND_DGRAD: return launch_kind<KIND_DGRAD>(pl.tn, pl.rt, mt, mw, p, st);
+        case KIND_I8: return launch_kind<KIND_I8>(pl.tn, pl.rt, mt, mw, p, st);
     }
     return LQ_EINVAL;
 }
@@ -640,6 +706,16 @@ int lq_gemm_a8w8(const int8_t* x8, const int8_t* w8, const float* row_scale, con
     p.row_scale = row_scale; p.col_scale = col_scale; p.alpha = alpha; p.bias = (const __nv_bfloat16*)bias;
     p.out = (__nv_bfloat16*)y; p.acc_out = acc_out;
     return run_gemm(KIND_I8, x8, w8, p, M, N, K, workspace, workspace_bytes, (cudaStream_t)stream);
+}
+
+int lq_gemm_profile(int enable, unsigned long long* out16) {
+    unsigned long long z[16] = {};
+    cudaError_t e = cudaSuccess;
+    if (out16) e = cudaMemcpyFromSymbol(out16, g_gemm_prof, sizeof(z));
+    if (e == cudaSuccess) e = cudaMemcpyToSymbol(g_gemm_prof, z, sizeof(z));
+    if (e == cudaSuccess) e = cudaMemcpyToSymbol(g_gemm_prof_on, &enable, sizeof(int));
+    if (e != cudaSuccess) { set_cuda_error(e, "lq_gemm_profile"); return LQ_ECUDA; }
+    return LQ_OK;
 }
 
 int lq_gemm_device_status(int reset) {

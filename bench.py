@@ -172,6 +172,11 @@ def _requant_part(torch, ops, pk, out, tm, g, numel):
         ms = tm(lambda: ops.a16w4_fold_delta(codes, words, delta, s, z, o))
         gbs = bytes_per * numel / ms / 1e6
         out["requant_" + name] = {"GB/s": round(gbs, 1), "frac_hbm": round(gbs / pk["hbm_gbs"], 3), "ms": round(ms, 3), "numel": numel}
+        import ctypes
+        from latentq_llm_b200 import _lib
+        cnt = ctypes.c_ulonglong(0)
+        _lib.lib.lq_fold_fallback_words(1, ctypes.byref(cnt))
+        out["requant_" + name]["generic_fallback_words"] = cnt.value
     del codes, words, delta, s, z
 
 

@@ -115,6 +115,10 @@ LQ_API int lq_a8w8_requant(const void* w, int w_dtype, const void* qscales, int 
 LQ_API int lq_a8w8_fold_delta(int8_t* codes, int32_t* words, const void* delta, int delta_dtype,
                               const void* qscales, int qp_dtype, int64_t rows, int64_t cols,
                               const lq_requant_opts* opts, lq_stream_t stream);
+/* Diagnostic (no counterpart in the reference): number of residual words the bf16 fast path of
+ * lq_a16w4_fold_delta / lq_a16w4_requant handed to the generic code since the last reset (weights far outside
+ * the quantization range, non-finite values).  Synchronises with the device. */
+LQ_API int lq_fold_fallback_words(int reset, unsigned long long* count);
 /* The library's Philox dither stream, materialised (test / debugging aid). */
 LQ_API int lq_philox_dither(uint64_t seed, uint64_t stream_id, int64_t first_word, int64_t n_words, float* out,
                             lq_stream_t stream);

@@ -62,6 +62,7 @@ SIGNATURES = {
     "lq_a16w4_fold_delta": [_p, _p, _p, _i, _p, _p, _i, _i64, _i, _OPTS, _p],
     "lq_a8w8_requant": [_p, _i, _p, _i, _i64, _i64, _OPTS, _p, _p, _p],
     "lq_a8w8_fold_delta": [_p, _p, _p, _i, _p, _i, _i64, _i64, _OPTS, _p],
+    "lq_fold_fallback_words": [_i, _p],
     "lq_philox_dither": [_u64, _u64, _i64, _i64, _p, _p],
     "lq_opt8_quant": [_p, _i64, _i, _p, _p, _p, _p],
     "lq_opt8_dequant": [_p, _i64, _i, _p, _p, _p, _p],

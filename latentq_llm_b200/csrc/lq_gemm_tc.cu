@@ -224,10 +224,10 @@ __device__ __forceinline__ uint4 dequant8(uint32_t w, __nv_bfloat162 z128, __nv_
     uint32_t p04 = ((w >> 4) & MASK) | MAGIC;    // (c0, c4)
     uint32_t p37 = ((w >> 8) & MASK) | MAGIC;    // (c3, c7)
     uint32_t p26 = ((w >> 12) & MASK) | MAGIC;   // (c2, c6)
-    uint32_t d15 = bf2_as_u32(__hmul2(__hsub2(u32_as_bf2(p15), z128), s2));
-    uint32_t d04 = bf2_as_u32(__hmul2(__hsub2(u32_as_bf2(p04), z128), s2));
-    uint32_t d37 = bf2_as_u32(__hmul2(__hsub2(u32_as_bf2(p37), z128), s2));
-    uint32_t d26 = bf2_as_u32(__hmul2(__hsub2(u32_as_bf2(p26), z128), s2));
+    uint32_t d15 = bf2_as_u32(__hmul2_rn(__hsub2_rn(u32_as_bf2(p15), z128), s2));
+    uint32_t d04 = bf2_as_u32(__hmul2_rn(__hsub2_rn(u32_as_bf2(p04), z128), s2));
+    uint32_t d37 = bf2_as_u32(__hmul2_rn(__hsub2_rn(u32_as_bf2(p37), z128), s2));
+    uint32_t d26 = bf2_as_u32(__hmul2_rn(__hsub2_rn(u32_as_bf2(p26), z128), s2));
     uint4 o;
     o.x = __byte_perm(d04, d15, 0x5410);   // (c0, c1)
     o.y = __byte_perm(d26, d37, 0x5410);   // (c2, c3)

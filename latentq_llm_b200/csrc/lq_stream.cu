@@ -4,6 +4,8 @@
 // Bit-exactness: every expression that the reference evaluates as separately rounded fp32 (or bf16)
 // operations is written with __f*_rn intrinsics so that nvcc cannot contract it; where the CUDA
 // reference's own source is contractable under nvcc defaults (`a*b+c`), __fmaf_rn is used.
+#include <cstdio>
+#include <cstdlib>
 #include <mutex>
 #include <string>
 
@@ -333,8 +335,8 @@ __device__ __forceinline__ float div_fast(float a, float s, float r, bool scale_
 // WBITS 4: codes are nibble pairs (4 bytes per 8 elements), zero point per group, clamp [0,15].
 // WBITS 8: codes are int8 (8 bytes per 8 elements), no zero point, clamp [-128,127].
 template <int WBITS, int CODEC, int DITHER, bool BF>
-__global__ void __launch_bounds__(256) k_requant(const RequantParams p) {
-    for (int64_t w = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; w < p.n_words; w += (int64_t)gridDim.x * blockDim.x) {
+__device__ __forceinline__ void requant_word(const RequantParams& p, const int64_t w) {
+    {
         const int64_t e0 = w * 8;
         const int64_t g = p.group_shift >= 0 ? (e0 >> p.group_shift) : (e0 / p.group);
         const float s = load1(p.scales, p.qp_dtype, g);
@@ -425,6 +427,190 @@ __global__ void __launch_bounds__(256) k_requant(const RequantParams p) {
 }
 
 template <int WBITS, int CODEC, int DITHER, bool BF>
+__global__ void __launch_bounds__(256) k_requant(const RequantParams p) {
+    for (int64_t w = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; w < p.n_words; w += (int64_t)gridDim.x * blockDim.x)
+        requant_word<WBITS, CODEC, DITHER, BF>(p, w);
+}
+
+// =================================================================================================
+// Fast path of the production configuration: A16W4, bf16 chain, bf16 qparams and update, 3-fold codec with the
+// reference's hash dither.  Same results as k_requant<4, THREEFOLD, HASH, true>, bit for bit:
+//  * bf16 add / sub / mul run as native packed bf16x2 instructions (one rounding of the exact result, which is
+//    what "fp32 op, then round to bf16" yields for bf16 operands) — the *_rn forms, which the compiler may not
+//    contract into fused multiply-adds;
+//  * bf16(w / s): the quotient of two bf16 numbers is never closer than 2^-17 (relative) to a bf16 rounding
+//    boundary, so bf16(w * RN(1/s)) (error < 2^-22) rounds to the same bf16 as bf16(fp32(w / s));
+//  * round-half-even of a bf16 Z with |Z| < 64 is (Z + 192) - 192 in bf16 arithmetic;
+//  * with the hash dither the 3-fold code of a residual is a pure function of its bf16 bit pattern, so it comes
+//    from a 48 KB table (built once per curve level by the reference-exact scalar code below);
+//  * words whose Z leaves (-64, 64) (weights far outside the quantization range) or is not finite take the
+//    generic path.
+// =================================================================================================
+constexpr int ENC3_TABLE_ENTRIES = 49152;               // bf16 patterns 0x0000..0xBFFF
+__device__ uint8_t g_enc3_table[4][ENC3_TABLE_ENTRIES]; // one per curve level; entry = nibble | carry << 4, 0xFF = unused
+
+__global__ void __launch_bounds__(256) k_build_enc3_table(int slot, Curve c, float v0) {
+    for (int h = blockIdx.x * blockDim.x + threadIdx.x; h < ENC3_TABLE_ENTRIES; h += gridDim.x * blockDim.x) {
+        const float x = __uint_as_float((uint32_t)h << 16);
+        uint8_t e = 0xFF;
+        if (fabsf(x) <= 0.5f) {                         // also rejects NaN patterns
+            float carry;
+            const uint32_t nib = res3_encode(x, hash_dither(x, v0), c, carry) & 15u;
+            e = (uint8_t)(nib | (carry != 0.0f ? 16u : 0u));
+        }
+        g_enc3_table[slot][h] = e;
+    }
+}
+
+__device__ unsigned long long g_fold_fallback_words;    // words the fast path handed to the generic code (diagnostic)
+
+constexpr int FAST_THREADS = 512;
+constexpr int FAST_RES_REPL = 8;                          // copies of the decode table (bank-conflict relief)
+constexpr int FAST_SMEM_BYTES = ENC3_TABLE_ENTRIES + 256 * FAST_RES_REPL * 4;
+
+__device__ __forceinline__ uint32_t h2u(__nv_bfloat162 v) { return *reinterpret_cast<uint32_t*>(&v); }
+__device__ __forceinline__ __nv_bfloat162 u2h(uint32_t v) { return *reinterpret_cast<__nv_bfloat162*>(&v); }
+
+__global__ void __launch_bounds__(FAST_THREADS, 2) k_fold_fast(const RequantParams p, const int enc_slot) {
+    extern __shared__ __align__(16) uint8_t fsm[];
+    uint8_t* enc = fsm;                                                       // [49152]
+    uint32_t* tres = reinterpret_cast<uint32_t*>(fsm + ENC3_TABLE_ENTRIES);   // [256][FAST_RES_REPL]
+    {   // stage the tables
+        const uint4* src = reinterpret_cast<const uint4*>(g_enc3_table[enc_slot]);
+        uint4* dst = reinterpret_cast<uint4*>(enc);
+        for (int i = threadIdx.x; i < ENC3_TABLE_ENTRIES / 16; i += FAST_THREADS) dst[i] = __ldg(src + i);
+        for (int b = threadIdx.x; b < 256; b += FAST_THREADS) {
+            // residual byte b holds two nibbles: high = even element, low = odd element; decode as the reference does
+            const uint32_t lo = f32_to_bf16_bits(bf16r(res3_decode((uint32_t)b >> 4, p.dec)));
+            const uint32_t hi = f32_to_bf16_bits(bf16r(res3_decode((uint32_t)b & 15u, p.dec)));
+            for (int r = 0; r < FAST_RES_REPL; ++r) tres[b * FAST_RES_REPL + r] = lo | (hi << 16);
+        }
+    }
+    __syncthreads();
+    const uint32_t tres_lane = (threadIdx.x & (FAST_RES_REPL - 1));
+    const unsigned short* scales = reinterpret_cast<const unsigned short*>(p.scales);
+    const unsigned short* zeros = reinterpret_cast<const unsigned short*>(p.zeros);
+    const __nv_bfloat162 c128 = u2h(0x43004300u), c192 = u2h(0x43404340u), c0 = u2h(0u), c15 = u2h(0x41704170u);
+    const bool use_res = p.has_residual != 0;
+
+    for (int64_t w = (int64_t)blockIdx.x * FAST_THREADS + threadIdx.x; w < p.n_words; w += (int64_t)gridDim.x * FAST_THREADS) {
+        const int64_t g = (w * 8) >> p.group_shift;
+        const uint32_t sb = __ldg(scales + g), zb = __ldg(zeros + g);
+        __nv_bfloat162 lat[4];
+        if (p.w_in) {
+            const uint4 u = __ldg(reinterpret_cast<const uint4*>(p.w_in) + w);
+            lat[0] = u2h(u.x); lat[1] = u2h(u.y); lat[2] = u2h(u.z); lat[3] = u2h(u.w);
+        } else {
+            const uint32_t pk = __ldg(reinterpret_cast<const uint32_t*>(p.codes_in) + w);
+            uint32_t rw = 0;
+            if (use_res) rw = (uint32_t)__ldg(p.words_in + w);
+            uint4 dv = make_uint4(0, 0, 0, 0);
+            if (p.delta) dv = __ldg(reinterpret_cast<const uint4*>(p.delta) + w);
+            const uint32_t d[4] = {dv.x, dv.y, dv.z, dv.w};
+            const __nv_bfloat162 s2 = u2h(sb * 0x00010001u), z2 = u2h(zb * 0x00010001u);
+            const uint32_t lo_n = pk & 0x0F0F0F0Fu, hi_n = (pk >> 4) & 0x0F0F0F0Fu;   // odd / even elements, one per byte
+            // codes in element order, one per byte: (c0,c1,c2,c3) and (c4,c5,c6,c7)
+            const uint32_t c03 = __byte_perm(hi_n, lo_n, 0x5140), c47 = __byte_perm(hi_n, lo_n, 0x7362);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                // bytes [c_even, 0x43, c_odd, 0x43]  =  bf16 pair (128 + c_even, 128 + c_odd)
+                const uint32_t pair = __byte_perm((j < 2) ? c03 : c47, 0x43434343u, (j & 1) ? 0x4342 : 0x4140);
+                __nv_bfloat162 v = __hsub2_rn(__hsub2_rn(u2h(pair), c128), z2);
+                v = __hmul2_rn(v, s2);
+                if (use_res) {
+                    const uint32_t b = (rw >> (24 - 8 * j)) & 0xffu;
+                    v = __hadd2_rn(__hmul2_rn(u2h(tres[b * FAST_RES_REPL + tres_lane]), s2), v);
+                }
+                if (p.delta) v = __hadd2_rn(v, u2h(d[j]));
+                lat[j] = v;
+            }
+        }
+        const float sf = __uint_as_float(sb << 16);
+        const float rs = __frcp_rn(sf);
+        const __nv_bfloat162 z2 = u2h(zb * 0x00010001u);
+        __nv_bfloat162 Z[4];
+        uint32_t bad = 0;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const uint32_t lb = h2u(lat[j]);
+            const float q0 = __fmul_rn(__uint_as_float(lb << 16), rs), q1 = __fmul_rn(__uint_as_float(lb & 0xffff0000u), rs);
+            Z[j] = __hadd2_rn(__floats2bfloat162_rn(q0, q1), z2);
+            bad |= ((h2u(Z[j]) & 0x7fff7fffu) + 0x3d803d80u) & 0x80008000u;          // |Z| >= 64, inf or NaN in either half
+        }
+        if (!fastdiv_ok_scale(sf)) bad = 1;
+#ifdef LQ_DEBUG_FAST
+        if (w == 0) printf("dbg w0: sb=%04x zb=%04x lat=%08x %08x Z=%08x %08x %08x %08x bad=%08x sf=%g ok=%d\n", sb, zb, h2u(lat[0]), h2u(lat[1]),
+                           h2u(Z[0]), h2u(Z[1]), h2u(Z[2]), h2u(Z[3]), bad, sf, (int)fastdiv_ok_scale(sf));
+#endif
+        if (__builtin_expect(bad != 0, 0)) {
+            requant_word<4, LQ_CODEC_THREEFOLD, LQ_DITHER_HASH, true>(p, w);
+            atomicAdd(&g_fold_fallback_words, 1ull);
+            continue;
+        }
+        uint32_t code_word = 0, res_word = 0;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const __nv_bfloat162 q = __hsub2_rn(__hadd2_rn(Z[j], c192), c192);           // round-half-even
+            const uint32_t rb2 = h2u(__hsub2_rn(Z[j], q));                            // residual pair, exact
+            const uint32_t e2 = (uint32_t)enc[rb2 & 0xffffu] | ((uint32_t)enc[rb2 >> 16] << 16);
+            const uint32_t carry = ((e2 >> 4) & 0x00010001u) * 0x3F80u;            // bf16 1.0 where the residual overflowed
+            __nv_bfloat162 qc = __hmin2(__hmax2(__hadd2_rn(q, u2h(carry)), c0), c15);
+            const uint32_t ci = h2u(__hadd2_rn(qc, c128)) & 0x000F000Fu;              // (code_even, code_odd) as integers
+            code_word |= (((ci << 4) | (ci >> 16)) & 0xffu) << (8 * j);            // byte j = even << 4 | odd
+            const uint32_t ni = e2 & 0x000F000Fu;
+            res_word |= (((ni << 4) | (ni >> 16)) & 0xffu) << (24 - 8 * j);        // element k at bits 28 - 4k
+        }
+        reinterpret_cast<uint32_t*>(p.codes_out)[w] = code_word;
+        p.words_out[w] = (int32_t)res_word;
+    }
+}
+
+static std::mutex g_enc3_mutex;
+// Builds (once per device, curve level and v0) the encode table the fast path reads.
+static int ensure_enc3_table(int mu, float v0, cudaStream_t st) {
+    static bool built[64][4] = {};
+    static float built_v0[64][4] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return LQ_EUNSUPPORTED;
+    const int slot = (mu < 0 || mu > 3) ? 0 : mu;
+    std::lock_guard<std::mutex> lock(g_enc3_mutex);
+    if (built[dev][slot] && built_v0[dev][slot] == v0) return LQ_OK;
+    k_build_enc3_table<<<96, 256, 0, st>>>(slot, curve_for_level(slot), v0);
+    int rc = check_launch("k_build_enc3_table");
+    if (rc) return rc;
+    // first use only: make the table visible to every stream before anyone else may read it
+    cudaError_t e = cudaStreamSynchronize(st);
+    if (e != cudaSuccess) { set_cuda_error(e, "cudaStreamSynchronize"); return LQ_ECUDA; }
+    built[dev][slot] = true; built_v0[dev][slot] = v0;
+    return LQ_OK;
+}
+
+static bool fast_fold_eligible(const RequantParams& p, const lq_requant_opts* o) {
+    if (getenv("LQ_REQUANT_GENERIC")) return false;
+    return o->codec == LQ_CODEC_THREEFOLD && o->dither == LQ_DITHER_HASH && o->math_dtype == LQ_BF16 && p.qp_dtype == LQ_BF16 &&
+           p.group_shift >= 3 && o->mu_enc >= 0 && o->mu_enc <= 3 && o->mu_dec >= 0 && o->mu_dec <= 3 &&
+           (p.w_in ? p.w_dtype == LQ_BF16 : (!p.delta || p.delta_dtype == LQ_BF16));
+}
+static int launch_fold_fast(const RequantParams& p, const lq_requant_opts* o, cudaStream_t st) {
+    int rc = ensure_enc3_table(o->mu_enc, o->v0, st);
+    if (rc) return rc;
+    static bool attr_done[64] = {};
+    static int per_sm[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (!attr_done[dev]) {
+        cudaError_t e = cudaFuncSetAttribute(k_fold_fast, cudaFuncAttributeMaxDynamicSharedMemorySize, FAST_SMEM_BYTES);
+        if (e != cudaSuccess) { set_cuda_error(e, "cudaFuncSetAttribute(k_fold_fast)"); return LQ_ECUDA; }
+        int n = 0;
+        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, k_fold_fast, FAST_THREADS, FAST_SMEM_BYTES) != cudaSuccess || n < 1) n = 1;
+        per_sm[dev] = n; attr_done[dev] = true;
+    }
+    int grid = grid_for(p.n_words, FAST_THREADS, per_sm[dev]);
+    k_fold_fast<<<grid, FAST_THREADS, FAST_SMEM_BYTES, st>>>(p, o->mu_enc);
+    return check_launch("k_fold_fast");
+}
+
+template <int WBITS, int CODEC, int DITHER, bool BF>
 static int requant_grid(int64_t n_words) {
     static int per_sm = 0;
     if (per_sm == 0) {
@@ -443,6 +629,7 @@ static int launch_requant_bf(const RequantParams& p, bool bf, cudaStream_t st) {
 template <int WBITS>
 static int launch_requant(const RequantParams& p, const lq_requant_opts* o, cudaStream_t st) {
     { int rc_dev = ensure_device_for(p.codes_out); if (rc_dev) return rc_dev; }
+    if (WBITS == 4 && fast_fold_eligible(p, o)) return launch_fold_fast(p, o, st);
     const bool bf = o->math_dtype == LQ_BF16;
     switch (o->codec) {
         case LQ_CODEC_NONE: return launch_requant_bf<WBITS, LQ_CODEC_NONE, LQ_DITHER_HASH>(p, bf, st);
@@ -791,6 +978,14 @@ int lq_a8w8_fold_delta(int8_t* codes, int32_t* words, const void* delta, int del
     p.codes_in = codes; p.words_in = words; p.delta = delta; p.delta_dtype = delta_dtype;
     p.scales = qscales; p.zeros = nullptr; p.qp_dtype = qp_dtype; p.codes_out = codes; p.words_out = words;
     return launch_requant<8>(p, opts, LQ_ST(stream));
+}
+int lq_fold_fallback_words(int reset, unsigned long long* count) {
+    unsigned long long v = 0;
+    cudaError_t e = cudaMemcpyFromSymbol(&v, g_fold_fallback_words, sizeof(v));
+    if (e == cudaSuccess && reset) { unsigned long long z = 0; e = cudaMemcpyToSymbol(g_fold_fallback_words, &z, sizeof(z)); }
+    if (e != cudaSuccess) { set_cuda_error(e, "lq_fold_fallback_words"); return LQ_ECUDA; }
+    if (count) *count = v;
+    return LQ_OK;
 }
 int lq_philox_dither(uint64_t seed, uint64_t stream_id, int64_t first_word, int64_t n_words, float* out, lq_stream_t stream) {
     if (n_words == 0) return LQ_OK;

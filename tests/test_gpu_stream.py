@@ -268,3 +268,49 @@ def test_empty_and_bad_inputs(ops):
     from latentq_llm_b200._lib import LatentQError
     with pytest.raises(LatentQError):
         ops.find_qparams(torch.zeros(100, device="cuda"), 128)
+
+
+def test_fast_fold_path_equals_generic_kernel(ops, monkeypatch):
+    """The packed-bf16 / table-driven fast path of the production configuration against the generic kernel on 4M
+    weights, including weights far outside the quantization range (which the fast path hands to the generic code)
+    and every pair of curve levels."""
+    N, K = 2048, 2048
+    g = torch.Generator(device="cuda").manual_seed(5)
+    w = (torch.randn(N, K, device="cuda", generator=g) * 0.02).to(torch.bfloat16)
+    s, z = ops.find_qparams(w, 128, 15, False)
+    sb, zb = s.to(torch.bfloat16), z.to(torch.bfloat16)
+    codes0, _ = ops.a16w4_requant(w, sb, zb, ops.make_opts(codec=ops.CODEC_NONE, math_dtype=torch.bfloat16))
+    delta = (torch.randn(N * K, device="cuda", generator=g) * 2e-3).to(torch.bfloat16)
+    delta[::4099] = 3.0          # |Z| far beyond 64
+    delta[1::7919] = -0.7
+    delta[2::10007] = float("inf")
+    results = {}
+    for mode in ("fast", "generic"):
+        if mode == "generic":
+            monkeypatch.setenv("LQ_REQUANT_GENERIC", "1")
+        else:
+            monkeypatch.delenv("LQ_REQUANT_GENERIC", raising=False)
+        c, wd = codes0.clone(), torch.zeros(N * K // 8, dtype=torch.int32, device="cuda")
+        outs = []
+        for step, (mu_enc, mu_dec) in enumerate([(0, 0), (1, 0), (2, 1), (3, 2), (0, 3)]):
+            o = ops.make_opts(codec=ops.CODEC_THREEFOLD, dither=ops.DITHER_HASH, has_residual=step > 0, mu_enc=mu_enc, mu_dec=mu_dec)
+            ops.a16w4_fold_delta(c, wd, delta if step != 3 else None, sb, zb, o)
+            outs.append((c.clone(), wd.clone()))
+        # requantize-from-latent entry as well
+        o = ops.make_opts(codec=ops.CODEC_THREEFOLD, dither=ops.DITHER_HASH, mu_enc=1)
+        outs.append(ops.a16w4_requant((w.float() + delta.view(N, K).float() * 0.1).to(torch.bfloat16), sb, zb, o))
+        results[mode] = outs
+    for (cf, wf), (cg, wg) in zip(results["fast"], results["generic"]):
+        assert torch.equal(cf, cg) and torch.equal(wf, wg)
+    # the fast path must really be the one that ran: only the words poisoned above may fall back to the generic code
+    import ctypes
+    from latentq_llm_b200 import _lib
+    cnt = ctypes.c_ulonglong(0)
+    monkeypatch.delenv("LQ_REQUANT_GENERIC", raising=False)
+    _lib.lib.lq_fold_fallback_words(1, ctypes.byref(cnt))
+    o = ops.make_opts(codec=ops.CODEC_THREEFOLD, dither=ops.DITHER_HASH, has_residual=False)
+    c, wd = codes0.clone(), torch.zeros(N * K // 8, dtype=torch.int32, device="cuda")
+    ops.a16w4_fold_delta(c, wd, delta, sb, zb, o)
+    _lib.lib.lq_fold_fallback_words(1, ctypes.byref(cnt))
+    poisoned = N * K // 4099 + N * K // 7919 + N * K // 10007 + 3
+    assert 0 < cnt.value <= poisoned, (cnt.value, poisoned)

@@ -1,0 +1,120 @@
+"""Data-parallel plumbing for the latent fine-tune step.
+
+The reference never reduces the gradients of its quantized weights: they live on plain Python
+`QuantTensor` objects, attached by a backward hook (utils/quant.py:398-411), invisible to DeepSpeed's
+gradient all-reduce, and its default launch is world size 1 (main0.py:200-216).  Here every rank keeps the
+bf16 weight gradients of all quantized linears in ONE flat arena; at the gradient-accumulation boundary the
+arena is all-reduced in buckets (NCCL over NVLink on GPUs, gloo in the CPU tests), averaged, and every rank
+then runs the same deterministic optimizer + requantize step, so packed codes, residuals and optimizer
+states stay bit-identical across replicas without ever broadcasting weights (the stochastic-rounding
+dither is keyed by seed / step / parameter, never by rank).
+"""
+from __future__ import annotations
+
+from typing import Iterable, List, Sequence
+
+import torch
+import torch.distributed as dist
+
+
+class GradArena:
+    """Flat gradient buffer with one view per parameter.
+
+    `params` are objects with `.shape` and a writable `.grad` attribute (QuantTensor, FPTensor) or plain
+    tensors / nn.Parameters.  `attach()` points every `.grad` at its (zeroed) view, so the reference's backward
+    hook — which adds into an existing `.grad` (utils/quant.py:408-411) — accumulates straight into the arena.
+    """
+
+    def __init__(self, params: Sequence, dtype=torch.bfloat16, device="cuda", align_elems: int = 128):
+        self.params = list(params)
+        self.offsets: List[int] = []
+        n = 0
+        for p in self.params:
+            self.offsets.append(n)
+            numel = 1
+            for d in p.shape:
+                numel *= int(d)
+            n += (numel + align_elems - 1) // align_elems * align_elems
+        self.numel = n
+        self.flat = torch.zeros(n, dtype=dtype, device=device)
+        self.views = []
+        for p, off in zip(self.params, self.offsets):
+            numel = 1
+            for d in p.shape:
+                numel *= int(d)
+            self.views.append(self.flat[off:off + numel].view(*[int(d) for d in p.shape]))
+
+    def attach(self) -> None:
+        """Zero the arena and make every parameter's `.grad` its view (call at the start of an accumulation cycle)."""
+        self.flat.zero_()
+        for p, v in zip(self.params, self.views):
+            p.grad = v
+
+    def buckets(self, bucket_bytes: int) -> Iterable[torch.Tensor]:
+        per = max(1, bucket_bytes // self.flat.element_size())
+        for start in range(0, self.numel, per):
+            yield self.flat[start:min(self.numel, start + per)]
+
+
+def allreduce_mean(arena: GradArena, group=None, bucket_bytes: int = 64 << 20) -> int:
+    """Bucketed sum all-reduce of the arena followed by division by the world size.  Returns the bucket count.
+    NVSwitch gives every peer full bandwidth, so buckets are sized for launch latency / overlap (tens of MB)."""
+    if not (dist.is_available() and dist.is_initialized()):
+        return 0
+    world = dist.get_world_size(group)
+    if world == 1:
+        return 0
+    works = []
+    for b in arena.buckets(bucket_bytes):
+        works.append(dist.all_reduce(b, op=dist.ReduceOp.SUM, group=group, async_op=True))
+    for w in works:
+        w.wait()
+    arena.flat.div_(world)
+    return len(works)
+
+
+def shard_micro_batches(n_micro_batches: int, rank: int, world: int) -> List[int]:
+    """DistributedSampler-style assignment (main0.py:387-392): rank r takes micro-batches r, r+W, r+2W, …"""
+    return list(range(rank, n_micro_batches, world))
+
+
+def replicas_identical(tensors: Sequence[torch.Tensor], group=None) -> bool:
+    """True when the given tensors hold the same bytes on every rank (checksum max == min)."""
+    if not (dist.is_available() and dist.is_initialized()) or dist.get_world_size(group) == 1:
+        return True
+    sums = torch.stack([t.reshape(-1).to(torch.float64).sum() if t.is_floating_point()
+                        else t.reshape(-1).to(torch.int64).sum().to(torch.float64) for t in tensors])
+    hi, lo = sums.clone(), sums.clone()
+    dist.all_reduce(hi, op=dist.ReduceOp.MAX, group=group)
+    dist.all_reduce(lo, op=dist.ReduceOp.MIN, group=group)
+    return bool(torch.equal(hi, lo))
+
+
+class PeerLostError(RuntimeError):
+    """A peer did not reach the step boundary in time (it crashed, hung or left)."""
+
+
+class StepGate:
+    """Host-side liveness check at the step boundary, before any collective is launched.
+
+    Every rank publishes `gate/<step>/<rank>` in the process group's key-value store and waits (bounded) for the
+    same key of every peer.  A rank that died between steps is therefore noticed on the host, with no kernel or
+    collective in flight, instead of turning the next all-reduce into a hang.
+    """
+
+    def __init__(self, store=None, rank=None, world=None, timeout_s: float = 30.0):
+        self.store = store if store is not None else dist.distributed_c10d._get_default_store()
+        self.rank = dist.get_rank() if rank is None else rank
+        self.world = dist.get_world_size() if world is None else world
+        self.timeout_s = timeout_s
+
+    def arrive_and_wait(self, step: int) -> None:
+        import datetime
+        self.store.set(f"gate/{step}/{self.rank}", "1")
+        keys = [f"gate/{step}/{r}" for r in range(self.world) if r != self.rank]
+        if not keys:
+            return
+        try:
+            self.store.wait(keys, datetime.timedelta(seconds=self.timeout_s))
+        except Exception as e:  # the store raises on timeout
+            raise PeerLostError(f"rank {self.rank}: a peer did not reach step {step} within {self.timeout_s}s") from e

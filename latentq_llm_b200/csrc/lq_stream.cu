@@ -493,20 +493,36 @@ __global__ void __launch_bounds__(FAST_THREADS, 2) k_fold_fast(const RequantPara
     const __nv_bfloat162 c128 = u2h(0x43004300u), c192 = u2h(0x43404340u), c0 = u2h(0u), c15 = u2h(0x41704170u);
     const bool use_res = p.has_residual != 0;
 
-    for (int64_t w = (int64_t)blockIdx.x * FAST_THREADS + threadIdx.x; w < p.n_words; w += (int64_t)gridDim.x * FAST_THREADS) {
+    // inputs of one word; the next word's loads are issued before the current word is processed
+    struct In { uint32_t pk, rw, sb, zb; uint4 dv; };
+    auto load_in = [&](int64_t w) -> In {
+        In in;
+        in.pk = 0; in.rw = 0; in.dv = make_uint4(0, 0, 0, 0);
         const int64_t g = (w * 8) >> p.group_shift;
-        const uint32_t sb = __ldg(scales + g), zb = __ldg(zeros + g);
+        in.sb = __ldg(scales + g); in.zb = __ldg(zeros + g);
+        if (p.w_in) {
+            in.dv = __ldg(reinterpret_cast<const uint4*>(p.w_in) + w);
+        } else {
+            in.pk = __ldg(reinterpret_cast<const uint32_t*>(p.codes_in) + w);
+            if (use_res) in.rw = (uint32_t)__ldg(p.words_in + w);
+            if (p.delta) in.dv = __ldg(reinterpret_cast<const uint4*>(p.delta) + w);
+        }
+        return in;
+    };
+    const int64_t stride = (int64_t)gridDim.x * FAST_THREADS;
+    int64_t w = (int64_t)blockIdx.x * FAST_THREADS + threadIdx.x;
+    In nxt;
+    if (w < p.n_words) nxt = load_in(w);
+    for (; w < p.n_words; w += stride) {
+        const In cur = nxt;
+        if (w + stride < p.n_words) nxt = load_in(w + stride);
+        const uint32_t sb = cur.sb, zb = cur.zb;
         __nv_bfloat162 lat[4];
         if (p.w_in) {
-            const uint4 u = __ldg(reinterpret_cast<const uint4*>(p.w_in) + w);
-            lat[0] = u2h(u.x); lat[1] = u2h(u.y); lat[2] = u2h(u.z); lat[3] = u2h(u.w);
+            lat[0] = u2h(cur.dv.x); lat[1] = u2h(cur.dv.y); lat[2] = u2h(cur.dv.z); lat[3] = u2h(cur.dv.w);
         } else {
-            const uint32_t pk = __ldg(reinterpret_cast<const uint32_t*>(p.codes_in) + w);
-            uint32_t rw = 0;
-            if (use_res) rw = (uint32_t)__ldg(p.words_in + w);
-            uint4 dv = make_uint4(0, 0, 0, 0);
-            if (p.delta) dv = __ldg(reinterpret_cast<const uint4*>(p.delta) + w);
-            const uint32_t d[4] = {dv.x, dv.y, dv.z, dv.w};
+            const uint32_t pk = cur.pk, rw = cur.rw;
+            const uint32_t d[4] = {cur.dv.x, cur.dv.y, cur.dv.z, cur.dv.w};
             const __nv_bfloat162 s2 = u2h(sb * 0x00010001u), z2 = u2h(zb * 0x00010001u);
             const uint32_t lo_n = pk & 0x0F0F0F0Fu, hi_n = (pk >> 4) & 0x0F0F0F0Fu;   // odd / even elements, one per byte
             // codes in element order, one per byte: (c0,c1,c2,c3) and (c4,c5,c6,c7)
@@ -529,25 +545,21 @@ __global__ void __launch_bounds__(FAST_THREADS, 2) k_fold_fast(const RequantPara
         const float rs = __frcp_rn(sf);
         const __nv_bfloat162 z2 = u2h(zb * 0x00010001u);
         __nv_bfloat162 Z[4];
-        uint32_t bad = 0;
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
             const uint32_t lb = h2u(lat[j]);
             const float q0 = __fmul_rn(__uint_as_float(lb << 16), rs), q1 = __fmul_rn(__uint_as_float(lb & 0xffff0000u), rs);
             Z[j] = __hadd2_rn(__floats2bfloat162_rn(q0, q1), z2);
-            bad |= ((h2u(Z[j]) & 0x7fff7fffu) + 0x3d803d80u) & 0x80008000u;          // |Z| >= 64, inf or NaN in either half
         }
-        if (!fastdiv_ok_scale(sf)) bad = 1;
-#ifdef LQ_DEBUG_FAST
-        if (w == 0) printf("dbg w0: sb=%04x zb=%04x lat=%08x %08x Z=%08x %08x %08x %08x bad=%08x sf=%g ok=%d\n", sb, zb, h2u(lat[0]), h2u(lat[1]),
-                           h2u(Z[0]), h2u(Z[1]), h2u(Z[2]), h2u(Z[3]), bad, sf, (int)fastdiv_ok_scale(sf));
-#endif
-        if (__builtin_expect(bad != 0, 0)) {
+        // |Z| >= 64, inf or NaN anywhere in the word -> generic path (max of the magnitudes, NaN-propagating)
+        const uint32_t zmax = h2u(__hmax2_nan(__hmax2_nan(__habs2(Z[0]), __habs2(Z[1])), __hmax2_nan(__habs2(Z[2]), __habs2(Z[3]))));
+        const bool bad = (((zmax & 0x7fff7fffu) + 0x3d803d80u) & 0x80008000u) != 0u || !fastdiv_ok_scale(sf);
+        if (__builtin_expect(bad, 0)) {
             requant_word<4, LQ_CODEC_THREEFOLD, LQ_DITHER_HASH, true>(p, w);
             atomicAdd(&g_fold_fallback_words, 1ull);
             continue;
         }
-        uint32_t code_word = 0, res_word = 0;
+        uint32_t tc[4], tn[4];
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
             const __nv_bfloat162 q = __hsub2_rn(__hadd2_rn(Z[j], c192), c192);           // round-half-even
@@ -556,10 +568,13 @@ __global__ void __launch_bounds__(FAST_THREADS, 2) k_fold_fast(const RequantPara
             const uint32_t carry = ((e2 >> 4) & 0x00010001u) * 0x3F80u;            // bf16 1.0 where the residual overflowed
             __nv_bfloat162 qc = __hmin2(__hmax2(__hadd2_rn(q, u2h(carry)), c0), c15);
             const uint32_t ci = h2u(__hadd2_rn(qc, c128)) & 0x000F000Fu;              // (code_even, code_odd) as integers
-            code_word |= (((ci << 4) | (ci >> 16)) & 0xffu) << (8 * j);            // byte j = even << 4 | odd
+            tc[j] = ci * 16u + (ci >> 16);                                         // low byte = even << 4 | odd
             const uint32_t ni = e2 & 0x000F000Fu;
-            res_word |= (((ni << 4) | (ni >> 16)) & 0xffu) << (24 - 8 * j);        // element k at bits 28 - 4k
+            tn[j] = ni * 16u + (ni >> 16);
         }
+        // gather the low bytes: code byte j = pair j; residual element k sits at bits 28 - 4k, i.e. pair j in byte 3 - j
+        const uint32_t code_word = __byte_perm(__byte_perm(tc[0], tc[1], 0x4040), __byte_perm(tc[2], tc[3], 0x4040), 0x5410);
+        const uint32_t res_word = __byte_perm(__byte_perm(tn[3], tn[2], 0x4040), __byte_perm(tn[1], tn[0], 0x4040), 0x5410);
         reinterpret_cast<uint32_t*>(p.codes_out)[w] = code_word;
         p.words_out[w] = (int32_t)res_word;
     }

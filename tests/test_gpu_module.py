@@ -189,4 +189,6 @@ def test_functional_mirrors(Q, golden):
     adj = r.set_value(x.clone(), torch.ones(4, 1, device="cuda", dtype=torch.bfloat16))
     assert adj.dtype == torch.bfloat16 and set(adj.float().unique().tolist()) <= {0.0, 1.0}
     back = r.add(torch.zeros(4, 128, device="cuda", dtype=torch.bfloat16))
-    assert float((back.float() - x.to(torch.bfloat16).float()).abs().max()) <= 1 / 16 + 1e-3
+    # an overflowing residual (close to +0.5) is stored as nibble 1 and hands a carry of one code step to the caller
+    err = back.float() + adj.float().view(4, 128) - x.to(torch.bfloat16).float()
+    assert float(err.abs().max()) <= 1 / 8 + 1e-3 and float(err.abs().mean()) < 1 / 32

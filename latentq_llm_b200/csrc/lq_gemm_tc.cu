@@ -24,6 +24,7 @@
 #include <cstdlib>
 
 #include "lq_common.cuh"
+#include "lq_gemv.h"
 
 namespace lq {
 
@@ -523,10 +524,18 @@ __global__ void __launch_bounds__(256) k_splitk_reduce(const GemmParams p) {
 // ---------------------------------------------------------------------------------------------
 // Host side: plan, tensor maps, launch
 // ---------------------------------------------------------------------------------------------
-struct Plan { int tn, rt, r_tiles, t_tiles, splits, kb_total, kb_per_split; };
+struct Plan { int tn, rt, r_tiles, t_tiles, splits, kb_total, kb_per_split; bool skinny; };
 
-static Plan make_plan(int kind, int64_t M, int64_t N, int64_t K) {
+// group: quantization group size, or 0 when unknown (the skinny path needs 64, 128 or 256)
+static Plan make_plan(int kind, int64_t M, int64_t N, int64_t K, int group = 128) {
     Plan pl{};
+    if (kind == KIND_FWD && M <= 16 && (K % 256) == 0 && (group == 64 || group == 128 || group == 256) && !getenv("LQ_GEMM_NO_SKINNY")) {
+        // decode-sized forward: bandwidth-bound register-dequant kernel (lq_gemv.cu)
+        pl.skinny = true;
+        pl.kb_per_split = skinny_chunks_per_split(N, K, &pl.splits);
+        pl.kb_total = (int)(K / 64);
+        return pl;
+    }
     const int64_t R = (kind == KIND_DGRAD) ? K : N;
     const int64_t Cc = (kind == KIND_DGRAD) ? N : K;
     pl.tn = M <= 16 ? 16 : (M <= 64 ? 64 : (M <= 128 ? 128 : 256));
@@ -626,7 +635,7 @@ static int run_gemm(int kind, const void* tok, const void* w, GemmParams p, int6
                     void* workspace, size_t workspace_bytes, cudaStream_t st) {
     if (M == 0) return LQ_OK;
     { int rc_dev = ensure_device_for(tok); if (rc_dev) return rc_dev; }
-    const Plan pl = make_plan(kind, M, N, K);
+    const Plan pl = make_plan(kind, M, N, K, p.group);
     p.M = (int)M; p.R = (int)((kind == KIND_DGRAD) ? K : N); p.C = (int)((kind == KIND_DGRAD) ? N : K);
     p.wcols = (int)K;
     p.r_tiles = pl.r_tiles; p.t_tiles = pl.t_tiles; p.splits = pl.splits; p.kb_total = pl.kb_total; p.kb_per_split = pl.kb_per_split;
@@ -634,6 +643,19 @@ static int run_gemm(int kind, const void* tok, const void* w, GemmParams p, int6
         const size_t need = (size_t)pl.splits * (size_t)M * (size_t)p.R * 4;
         if (!workspace || workspace_bytes < need || !al16(workspace)) return LQ_EWORKSPACE;
         p.partial = workspace;
+    }
+    if (pl.skinny) {
+        SkinnyParams sp{};
+        sp.x = (const __nv_bfloat16*)tok; sp.qweight = (const uint8_t*)w; sp.scales = p.scales; sp.zeros = p.zeros;
+        sp.bias = p.bias; sp.out = p.out; sp.partial = (float*)p.partial;
+        sp.M = (int)M; sp.N = (int)N; sp.K = (int)K; sp.group = p.group; sp.splits = pl.splits; sp.chunks_per_split = pl.kb_per_split;
+        int rc = launch_skinny_fwd(sp, st);
+        if (rc || pl.splits <= 1) return rc;
+        const int64_t total = (int64_t)p.M * p.R;
+        int g = (int)((total + 255) / 256);
+        if (g > sm_count() * 8) g = sm_count() * 8;
+        k_splitk_reduce<false><<<g, 256, 0, st>>>(p);
+        return check_launch("k_splitk_reduce");
     }
     CUtensorMap mt, mw;
     int rc;
@@ -666,10 +688,12 @@ extern "C" {
 
 size_t lq_gemm_workspace_bytes(int kind, int64_t M, int64_t N, int64_t K) {
     if (kind < 0 || kind > 2 || M <= 0 || N <= 0 || K <= 0) return 0;
-    const Plan pl = make_plan(kind, M, N, K);
-    if (pl.splits <= 1) return 0;
+    // the forward plan depends on the group size (decode-sized kernel or tensor-core kernel): cover both
+    const Plan pl = make_plan(kind, M, N, K, 128), pl2 = make_plan(kind, M, N, K, 0);
+    const int splits = pl.splits > pl2.splits ? pl.splits : pl2.splits;
+    if (splits <= 1) return 0;
     const int64_t R = (kind == KIND_DGRAD) ? K : N;
-    return (size_t)pl.splits * (size_t)M * (size_t)R * 4;
+    return (size_t)splits * (size_t)M * (size_t)R * 4;
 }
 
 static bool shape_ok_w4(int64_t M, int64_t N, int64_t K, int group) {

@@ -1,0 +1,215 @@
+// Decode-sized A16W4 forward (M <= 16 tokens): bandwidth-bound split-K kernel.
+//   y[M,N] = x[M,K] · deq(Wq)[N,K]^T   (QLinearFunctionW4_eval.forward, utils/quant.py:149-158, as generate.py uses it)
+//
+// The packed int4 weights are read exactly once, 8 bytes per thread per row straight from global memory into
+// registers and fed as the A operand of mma.sync.m16n8k16 (16 weight rows x 16 k) as the exact bf16 integers
+// 128 + q; scale and zero point are applied once per (row, group) to the fp32 group sums:
+//     sum_k x_k (q_k - z) s  =  s * ( sum_k x_k (128 + q_k)  -  (128 + z) * sum_k x_k ),
+// which costs one logic op per two weights in the inner loop instead of a subtract and a multiply per weight
+// (and does not round the dequantised weight to bf16, so it is slightly closer to exact arithmetic than the
+// reference's bf16 weight matrix; outputs are compared with the 1e-2 relative tolerance).  The tokens are the
+// 8-wide B operand, staged once per CTA in shared memory in the k-order the register extraction produces (a
+// contraction does not care about the order of k as long as both operands agree), so no byte shuffles are
+// needed.  Split-K partial sums go to the caller's workspace and are reduced by the GEMM's deterministic
+// reduction kernel.
+// Tensor-core rate is irrelevant here (the kernel is HBM-bound); tcgen05 serves the large-M path.
+#include "lq_common.cuh"
+#include "lq_gemv.h"
+
+namespace lq {
+
+__device__ __forceinline__ uint32_t sk_bf2(__nv_bfloat162 v) { return *reinterpret_cast<uint32_t*>(&v); }
+__device__ __forceinline__ __nv_bfloat162 sk_u2(uint32_t v) { return *reinterpret_cast<__nv_bfloat162*>(&v); }
+
+__device__ __forceinline__ void mma_16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+// 8 codes of one packed word -> 4 bf16 pairs (128 + c_k, 128 + c_{k+4}) for k = 0..3 (OR into the mantissa of 128.0)
+__device__ __forceinline__ void extract_word(uint32_t w, uint32_t* p) {
+    const uint32_t MAGIC = 0x43004300u, MASK = 0x000F000Fu;
+    p[0] = ((w >> 4) & MASK) | MAGIC;     // (c0, c4)
+    p[1] = (w & MASK) | MAGIC;            // (c1, c5)
+    p[2] = ((w >> 12) & MASK) | MAGIC;    // (c2, c6)
+    p[3] = ((w >> 8) & MASK) | MAGIC;     // (c3, c7)
+}
+
+constexpr int SK_THREADS = 256;       // 8 warps x 16 weight rows = 128 rows per CTA
+constexpr int SK_ROWS = 128;
+constexpr int SK_CHUNK = 64;          // k per loop step: 4 mma k-steps
+constexpr int SK_XPAD = 8;            // bf16 elements of padding per token row (bank-conflict relief)
+
+// MT = number of 8-token groups (1: M <= 8, 2: M <= 16)
+template <int MT>
+__global__ void __launch_bounds__(SK_THREADS) k_skinny_fwd(const SkinnyParams p) {
+    extern __shared__ __align__(16) uint8_t sk_smem[];
+    __nv_bfloat16* xs = reinterpret_cast<__nv_bfloat16*>(sk_smem);
+    const int chunks = p.chunks_per_split;
+    const int split = blockIdx.y;
+    const int c_begin = split * chunks, c_end = min(p.K / SK_CHUNK, c_begin + chunks);
+    const int n_chunks = c_end - c_begin;
+    const int xstride = chunks * SK_CHUNK + SK_XPAD;            // elements per token row in smem
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+    const int row0 = blockIdx.x * SK_ROWS + warp * 16;
+    const int ra = min(row0 + g, p.N - 1), rb = min(row0 + g + 8, p.N - 1);        // clamped loads, guarded stores
+    const size_t row_bytes = (size_t)p.K / 2;
+    const uint8_t* wa = p.qweight + (size_t)ra * row_bytes + (size_t)c_begin * (SK_CHUNK / 2) + t * 8;
+    const uint8_t* wb = p.qweight + (size_t)rb * row_bytes + (size_t)c_begin * (SK_CHUNK / 2) + t * 8;
+    const int gpr = p.K / p.group;
+    const unsigned short* sca = reinterpret_cast<const unsigned short*>(p.scales) + (size_t)ra * gpr;
+    const unsigned short* scb = reinterpret_cast<const unsigned short*>(p.scales) + (size_t)rb * gpr;
+    const unsigned short* zpa = reinterpret_cast<const unsigned short*>(p.zeros) + (size_t)ra * gpr;
+    const unsigned short* zpb = reinterpret_cast<const unsigned short*>(p.zeros) + (size_t)rb * gpr;
+
+    // packed weights of one chunk (2 rows x 16 k per thread); PF chunks are in flight per thread, issued before the
+    // token tile is staged so that the weight stream starts with the kernel
+    struct Chunk { uint2 qa, qb; };
+    auto load_chunk = [&](int c) -> Chunk {
+        Chunk ck;
+        ck.qa = __ldg(reinterpret_cast<const uint2*>(wa + (size_t)c * (SK_CHUNK / 2)));
+        ck.qb = __ldg(reinterpret_cast<const uint2*>(wb + (size_t)c * (SK_CHUNK / 2)));
+        return ck;
+    };
+    constexpr int PF = 4;
+    Chunk ring[PF];
+#pragma unroll
+    for (int u = 0; u < PF; ++u) {
+        ring[u].qa = ring[u].qb = make_uint2(0, 0);
+        if (u < n_chunks) ring[u] = load_chunk(u);
+    }
+    const int gc = p.group / SK_CHUNK;                      // chunks per quantization group (slices hold whole groups)
+    const int g_first = c_begin / gc, n_groups = (n_chunks + gc - 1) / gc;
+    // (scale, zero) of the first group for both rows, prefetched one group ahead inside the loop
+    uint32_t sz_a = (uint32_t)__ldg(sca + g_first) | ((uint32_t)__ldg(zpa + g_first) << 16);
+    uint32_t sz_b = (uint32_t)__ldg(scb + g_first) | ((uint32_t)__ldg(zpb + g_first) << 16);
+
+    // stage x[0..8*MT) x [k slice] with every 8-run of k reordered to (0,4,1,5,2,6,3,7)
+    for (int i = threadIdx.x; i < MT * 8 * n_chunks * (SK_CHUNK / 8); i += SK_THREADS) {
+        const int run = i % (n_chunks * (SK_CHUNK / 8));
+        const int tok = i / (n_chunks * (SK_CHUNK / 8));
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (tok < p.M) v = __ldg(reinterpret_cast<const uint4*>(p.x + (size_t)tok * p.K + (size_t)c_begin * SK_CHUNK) + run);
+        uint4 o;   // (k0,k1)(k2,k3)(k4,k5)(k6,k7) -> (k0,k4)(k1,k5)(k2,k6)(k3,k7)
+        o.x = __byte_perm(v.x, v.z, 0x5410); o.y = __byte_perm(v.x, v.z, 0x7632);
+        o.z = __byte_perm(v.y, v.w, 0x5410); o.w = __byte_perm(v.y, v.w, 0x7632);
+        *reinterpret_cast<uint4*>(xs + (size_t)tok * xstride + run * 8) = o;
+    }
+    __syncthreads();
+    const uint32_t ones[4] = {0x3F803F80u, 0x3F803F80u, 0x3F803F80u, 0x3F803F80u};   // bf16 1.0
+    float tot[MT][4];
+#pragma unroll
+    for (int m = 0; m < MT; ++m) { tot[m][0] = tot[m][1] = tot[m][2] = tot[m][3] = 0.0f; }
+
+    int c = 0;
+    for (int grp = 0; grp < n_groups; ++grp) {
+        const uint32_t cur_a = sz_a, cur_b = sz_b;
+        if (grp + 1 < n_groups) {
+            sz_a = (uint32_t)__ldg(sca + g_first + grp + 1) | ((uint32_t)__ldg(zpa + g_first + grp + 1) << 16);
+            sz_b = (uint32_t)__ldg(scb + g_first + grp + 1) | ((uint32_t)__ldg(zpb + g_first + grp + 1) << 16);
+        }
+        float acc[MT][4], sx[MT][4];      // sx: sum of the activations over the group, from an all-ones A operand
+#pragma unroll
+        for (int m = 0; m < MT; ++m) {
+            acc[m][0] = acc[m][1] = acc[m][2] = acc[m][3] = 0.0f;
+            sx[m][0] = sx[m][1] = sx[m][2] = sx[m][3] = 0.0f;
+        }
+        const int c_stop = min(n_chunks, (grp + 1) * gc);
+        for (; c < c_stop; ++c) {
+            const int u = c % PF;
+            Chunk ck;
+            // the ring is indexed with a runtime slot; PF is small, so select with predicates instead of local memory
+            ck = ring[0];
+#pragma unroll
+            for (int q = 1; q < PF; ++q) if (u == q) ck = ring[q];
+            if (c + PF < n_chunks) {
+                const Chunk nx = load_chunk(c + PF);
+#pragma unroll
+                for (int q = 0; q < PF; ++q) if (u == q) ring[q] = nx;
+            }
+            uint32_t pa[8], pb[8];
+            extract_word(ck.qa.x, pa); extract_word(ck.qa.y, pa + 4);
+            extract_word(ck.qb.x, pb); extract_word(ck.qb.y, pb + 4);
+#pragma unroll
+            for (int m = 0; m < MT; ++m) {
+                const __nv_bfloat16* xr = xs + (size_t)(m * 8 + g) * xstride + c * SK_CHUNK + t * 16;
+                const uint4 x0 = *reinterpret_cast<const uint4*>(xr), x1 = *reinterpret_cast<const uint4*>(xr + 8);
+                const uint32_t xb[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
+#pragma unroll
+                for (int s4 = 0; s4 < 4; ++s4) {
+                    const uint32_t a[4] = {pa[2 * s4], pb[2 * s4], pa[2 * s4 + 1], pb[2 * s4 + 1]};
+                    mma_16816(acc[m], a, xb[2 * s4], xb[2 * s4 + 1]);
+                    mma_16816(sx[m], ones, xb[2 * s4], xb[2 * s4 + 1]);
+                }
+            }
+        }
+        // fold the group: s * (sum x (128 + q) - (128 + z) * sum x)
+        const float s_a = __uint_as_float(cur_a << 16), z_a = __uint_as_float(cur_a & 0xffff0000u) + 128.0f;
+        const float s_b = __uint_as_float(cur_b << 16), z_b = __uint_as_float(cur_b & 0xffff0000u) + 128.0f;
+#pragma unroll
+        for (int m = 0; m < MT; ++m) {
+            const float sx0 = sx[m][0], sx1 = sx[m][1];      // tokens 2t, 2t+1 (identical in every row of the ones tile)
+            tot[m][0] = fmaf(s_a, acc[m][0] - z_a * sx0, tot[m][0]);
+            tot[m][1] = fmaf(s_a, acc[m][1] - z_a * sx1, tot[m][1]);
+            tot[m][2] = fmaf(s_b, acc[m][2] - z_b * sx0, tot[m][2]);
+            tot[m][3] = fmaf(s_b, acc[m][3] - z_b * sx1, tot[m][3]);
+        }
+    }
+    float (&acc)[MT][4] = tot;
+
+    // D fragment: d0,d1 = (row g, tokens 2t, 2t+1); d2,d3 = (row g+8, same tokens)
+#pragma unroll
+    for (int m = 0; m < MT; ++m) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int row = row0 + g + ((i >= 2) ? 8 : 0);
+            const int tok = m * 8 + 2 * t + (i & 1);
+            if (row >= p.N || tok >= p.M) continue;
+            const size_t o = (size_t)tok * p.N + row;
+            if (p.splits > 1) {
+                p.partial[(size_t)split * p.M * p.N + o] = acc[m][i];
+            } else {
+                const float f = bf16r(acc[m][i]);
+                p.out[o] = __float2bfloat16_rn(p.bias ? __fadd_rn(f, __bfloat162float(p.bias[row])) : f);
+            }
+        }
+    }
+}
+
+int skinny_chunks_per_split(int64_t N, int64_t K, int* splits_out) {
+    const int n_blocks = (int)((N + SK_ROWS - 1) / SK_ROWS);
+    const int chunks_total = (int)(K / SK_CHUNK);
+    const int gc = 4;                                               // slices are multiples of 256 k: whole groups of 64/128/256
+    int splits = (4 * sm_count() + n_blocks - 1) / n_blocks;     // ~4 CTAs per SM in flight
+    if (splits > chunks_total / 4) splits = chunks_total / 4;    // at least 4 chunks (256 k) per CTA
+    if (splits > 32) splits = 32;
+    if (splits < 1) splits = 1;
+    int per = (chunks_total + splits - 1) / splits;
+    per = (per + gc - 1) / gc * gc;                                 // a slice holds whole quantization groups
+    *splits_out = (chunks_total + per - 1) / per;
+    return per;
+}
+
+int launch_skinny_fwd(const SkinnyParams& p, cudaStream_t st) {
+    const int mt = p.M <= 8 ? 1 : 2;
+    const size_t smem = (size_t)mt * 8 * (p.chunks_per_split * SK_CHUNK + SK_XPAD) * sizeof(__nv_bfloat16);
+    if (smem > 200 * 1024) return LQ_EUNSUPPORTED;
+    dim3 grid((unsigned)((p.N + SK_ROWS - 1) / SK_ROWS), (unsigned)p.splits);
+    static bool attr_done[64][2] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev >= 0 && dev < 64 && !attr_done[dev][mt - 1]) {
+        cudaError_t e = mt == 1 ? cudaFuncSetAttribute(k_skinny_fwd<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024)
+                                : cudaFuncSetAttribute(k_skinny_fwd<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        if (e != cudaSuccess) { set_cuda_error(e, "cudaFuncSetAttribute(k_skinny_fwd)"); return LQ_ECUDA; }
+        attr_done[dev][mt - 1] = true;
+    }
+    if (mt == 1) k_skinny_fwd<1><<<grid, SK_THREADS, smem, st>>>(p);
+    else k_skinny_fwd<2><<<grid, SK_THREADS, smem, st>>>(p);
+    return check_launch("k_skinny_fwd");
+}
+
+}  // namespace lq

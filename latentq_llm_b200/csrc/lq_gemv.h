@@ -1,0 +1,24 @@
+// Interface between the GEMM dispatcher and the decode-sized (M <= 16) forward kernel.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace lq {
+
+struct SkinnyParams {
+    const __nv_bfloat16* x;        // [M, K]
+    const uint8_t* qweight;        // packed nibble pairs, K/2 bytes per row
+    const __nv_bfloat16* scales;   // [N * K / group]
+    const __nv_bfloat16* zeros;
+    const __nv_bfloat16* bias;     // [N] or null
+    __nv_bfloat16* out;            // [M, N]
+    float* partial;                // [splits][M][N] when splits > 1
+    int M, N, K, group, splits, chunks_per_split;
+};
+
+// split-K plan of the skinny kernel: returns 64-k chunks per split and writes the number of splits
+int skinny_chunks_per_split(int64_t N, int64_t K, int* splits_out);
+int launch_skinny_fwd(const SkinnyParams& p, cudaStream_t st);
+
+}  // namespace lq

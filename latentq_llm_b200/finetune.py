@@ -1,0 +1,147 @@
+"""DeepSpeed-free latent fine-tune step around the quantized hot path (the loop of main0.py:526-544).
+
+What it reproduces from the reference driver: every `nn.Linear` inside the decoder layers becomes a
+`QLinearA16W4` (main0.py:299-343), every such module gets the backward hook (main0.py:454-461), the
+optimizer is `MyAdam(betas=(0.9, 0.95))` over [quantized weights] + [biases and other weights of the decoder
+layers] (main0.py:445-472), the loss of each micro-batch is divided by the accumulation count and the
+optimizer steps at the accumulation boundary (main0.py:538-543; DeepSpeed does the same internally).
+What is new: data parallelism that really covers the quantized weights — their bf16 gradients accumulate in
+one flat arena that is all-reduced once per optimizer step (see dp.py).
+
+No datasets or checkpoints are involved: models are built from a config with random weights, quantized with
+the reference's min/max rule (PTQ/quant/quantizer.py:34-74) on group-128 slices, and fed uniform random
+token ids.
+"""
+from __future__ import annotations
+
+import torch
+import torch.nn as nn
+
+from . import ops
+from .dp import GradArena, StepGate, allreduce_mean, shard_micro_batches
+from .quant import GROUPSIZE, MyAdam, QLinearA16W4
+
+ARCHS = {
+    # OPT-1.3B: 24 layers, d 2048, ffn 8192, 32 heads, vocab 50272
+    "opt-1.3b": dict(kind="opt", hidden_size=2048, ffn_dim=8192, num_hidden_layers=24, num_attention_heads=32,
+                     vocab_size=50272, max_position_embeddings=2048, word_embed_proj_dim=2048),
+    # Llama-2-7B: 32 layers, d 4096, ffn 11008, 32 heads, vocab 32000
+    "llama-2-7b": dict(kind="llama", hidden_size=4096, intermediate_size=11008, num_hidden_layers=32,
+                       num_attention_heads=32, num_key_value_heads=32, vocab_size=32000, max_position_embeddings=4096),
+    # small shapes of the same architectures for tests
+    "opt-tiny": dict(kind="opt", hidden_size=256, ffn_dim=512, num_hidden_layers=2, num_attention_heads=4,
+                     vocab_size=1024, max_position_embeddings=256, word_embed_proj_dim=256),
+    "llama-tiny": dict(kind="llama", hidden_size=256, intermediate_size=512, num_hidden_layers=2, num_attention_heads=4,
+                       num_key_value_heads=4, vocab_size=1024, max_position_embeddings=256),
+}
+
+
+def build_model(arch: str, device="cuda", seed: int = 1234, layers: int | None = None) -> nn.Module:
+    """Random-init HF model of the named architecture in bf16 (no download: config only)."""
+    cfg = dict(ARCHS[arch])
+    kind = cfg.pop("kind")
+    if layers is not None:
+        cfg["num_hidden_layers"] = layers
+    torch.manual_seed(seed)
+    if kind == "opt":
+        from transformers import OPTConfig, OPTForCausalLM
+        model = OPTForCausalLM(OPTConfig(**cfg))
+    else:
+        from transformers import LlamaConfig, LlamaForCausalLM
+        model = LlamaForCausalLM(LlamaConfig(**cfg))
+    return model.to(torch.bfloat16).to(device)
+
+
+def decoder_layers(model: nn.Module):
+    inner = model.model
+    return inner.decoder.layers if hasattr(inner, "decoder") else inner.layers
+
+
+@torch.no_grad()
+def quantize_decoder(model: nn.Module, lbit: int = 4, gbit: int = 16) -> list:
+    """Swap every nn.Linear inside the decoder layers for a QLinearA16W4 holding int4 group-128 codes of the
+    same weights (main0.py:299-343 with the checkpoint replaced by on-the-fly min/max quantization)."""
+    swapped = []
+    for li, layer in enumerate(decoder_layers(model)):
+        for subname, sub in list(layer.named_modules()):
+            for name, child in list(sub.named_children()):
+                if not isinstance(child, nn.Linear):
+                    continue
+                n_out, n_in = child.weight.shape
+                new = QLinearA16W4(n_in, n_out, bias=child.bias is not None, lbit=lbit, gbit=gbit)
+                w = child.weight.data.to(torch.bfloat16).contiguous()
+                s, z = ops.find_qparams(w, GROUPSIZE, 15, False)
+                new.scales.data = s.view(-1, 1).to(torch.bfloat16)
+                new.zeros.data = z.view(-1, 1).to(torch.bfloat16)
+                codes, _ = ops.a16w4_requant(w, new.scales.data.view(-1), new.zeros.data.view(-1),
+                                             ops.make_opts(codec=ops.CODEC_NONE, math_dtype=torch.bfloat16))
+                new.weight.set_value(codes, [new.scales, new.zeros, new.wshape])
+                new.lname = f"layers.{li}.{subname + '.' if subname else ''}{name}"
+                if lbit == 4:
+                    new.weight.residual.name = new.lname + ".residual"
+                if child.bias is not None:
+                    new.bias.data = child.bias.data.to(torch.bfloat16)
+                new.to(w.device)
+                setattr(sub, name, new)
+                swapped.append(new)
+    return swapped
+
+
+def build_optimizer(model: nn.Module, lr: float = 1e-3, obit: int = 8, mu_f: int = 20):
+    """Parameter groups of main0.py:445-472: [quantized weights], [biases + other decoder-layer weights]."""
+    for p in model.parameters():
+        p.requires_grad_(False)
+    groups = [{"params": [], "weight_decay": 0.0}, {"params": [], "weight_decay": 0.0}]
+    for layer in decoder_layers(model):
+        for child in layer.modules():
+            if getattr(child, "bias", None) is not None and isinstance(child.bias, torch.Tensor):
+                child.bias.requires_grad_(True)
+                groups[1]["params"].append(child.bias)
+            if isinstance(child, QLinearA16W4):
+                child.weight.requires_grad = True
+                child.add_hook()
+                groups[0]["params"].append(child.weight)
+            elif isinstance(getattr(child, "weight", None), nn.Parameter) and not isinstance(child, nn.Embedding):
+                child.weight.requires_grad_(True)
+                groups[1]["params"].append(child.weight)
+    opt = MyAdam(groups, lr=lr, betas=(0.9, 0.95), obit=obit, mu_updata_f=mu_f)
+    return opt, groups
+
+
+class LatentFineTuner:
+    """One optimizer step = `grad_accum` micro-batches of forward/backward on this rank, one bucketed all-reduce of
+    the gradient arena, one MyAdam step (dequantize + Adam + stochastic requantize per quantized weight)."""
+
+    def __init__(self, model, optimizer, groups, grad_accum: int = 8, group=None, gate_timeout_s: float = 600.0):
+        self.model, self.opt, self.grad_accum, self.group = model, optimizer, grad_accum, group
+        self.params = groups[0]["params"] + groups[1]["params"]
+        self.arena = GradArena(self.params, dtype=torch.bfloat16, device=next(model.parameters()).device)
+        self.step_no = 0
+        dist_on = torch.distributed.is_available() and torch.distributed.is_initialized()
+        self.gate = StepGate(timeout_s=gate_timeout_s) if dist_on and torch.distributed.get_world_size() > 1 else None
+        # the hidden states entering the first decoder layer must require grad, otherwise autograd skips the custom
+        # backward of the quantized linears (embeddings are frozen, as in the reference's parameter groups)
+        model.get_input_embeddings().register_forward_hook(lambda m, i, o: o.requires_grad_(True))
+
+    def step(self, micro_batches) -> torch.Tensor:
+        """`micro_batches`: list of LongTensor [B, S] of token ids for THIS rank.  Returns the mean loss (device tensor)."""
+        self.model.train()
+        self.arena.attach()
+        total = torch.zeros((), device=self.arena.flat.device, dtype=torch.float32)
+        for ids in micro_batches:
+            out = self.model(input_ids=ids, labels=ids, use_cache=False)
+            (out.loss / len(micro_batches)).backward()
+            total += out.loss.detach().float()
+        if self.gate is not None:
+            self.gate.arrive_and_wait(self.step_no)      # host-side liveness check before the collective
+        allreduce_mean(self.arena, self.group)
+        self.opt.step()
+        for p in self.params:                           # MyAdam drops quantized grads (p.grad = None); clear the rest too
+            p.grad = None
+        self.step_no += 1
+        return total / max(1, len(micro_batches))
+
+
+def synthetic_batches(n: int, batch: int, seq: int, vocab: int, device, seed: int):
+    g = torch.Generator(device=device).manual_seed(seed)
+    return [torch.randint(0, vocab, (batch, seq), device=device, generator=g) for _ in range(n)]

@@ -1,0 +1,32 @@
+"""Latent fine-tune step on tiny OPT- / Llama-shaped models (random init, synthetic token ids)."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("arch", ["opt-tiny", "llama-tiny"])
+def test_finetune_steps_reduce_loss_and_move_codes(arch):
+    from latentq_llm_b200 import finetune as ft
+    from latentq_llm_b200.quant import QLinearA16W4
+    model = ft.build_model(arch, "cuda", seed=7)
+    swapped = ft.quantize_decoder(model, lbit=4, gbit=16)
+    assert len(swapped) == (12 if arch == "opt-tiny" else 14)
+    assert all(isinstance(m, QLinearA16W4) for m in swapped)
+    opt, groups = ft.build_optimizer(model, lr=2e-3)
+    assert len(groups[0]["params"]) == len(swapped) and len(groups[1]["params"]) > 0
+    tuner = ft.LatentFineTuner(model, opt, groups, grad_accum=2)
+    batches = ft.synthetic_batches(2, 4, 64, 1024, "cuda", seed=3)      # the same data every step: loss must fall
+    codes0 = swapped[0].weight.data.clone()
+    losses = [float(tuner.step(batches)) for _ in range(6)]
+    assert all(l == l and l < 20 for l in losses), losses
+    assert losses[-1] < losses[0] - 0.05, losses
+    assert not torch.equal(swapped[0].weight.data, codes0)
+    assert swapped[0].weight.data.dtype == torch.int8 and not swapped[0].weight.residual.init
+    assert swapped[0].weight.grad is None
+    st = opt.state[swapped[0].weight]
+    assert st["state1"].dtype == torch.uint8 and st["step"] == 6
+    # forward in eval mode still works after training (module keeps the hook: training function, no grad needed)
+    with torch.no_grad():
+        out = model(input_ids=batches[0][:1])
+    assert torch.isfinite(out.logits.float()).all()

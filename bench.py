@@ -218,6 +218,54 @@ def _decode_part(torch, ops, pk, out, tm):
                                   "timing": "CUDA graph replay of the 4 layers"}
 
 
+def finetune_measurement(torch, arch="opt-1.3b", steps=2, warmup=1, micro_batch=4, seq=512, grad_accum=8):
+    """Latent fine-tune step (BASELINE config 4): A16W4 int4 group-128 latent weights, seq 512, micro-batch 4,
+    grad-accum 8 per rank, uniform random token ids, data-parallel over the ranks of this launch with one bf16
+    gradient all-reduce per optimizer step.  tokens/s = world * micro_batch * seq * grad_accum / step time.
+    Token ids come from pinned host memory every step and the loss is read back (end-to-end through the module API)."""
+    import torch.distributed as dist
+    from latentq_llm_b200 import finetune as ft
+    world = dist.get_world_size() if dist.is_initialized() else 1
+    rank = dist.get_rank() if dist.is_initialized() else 0
+    model = ft.build_model(arch, "cuda", seed=1234)
+    ft.quantize_decoder(model, lbit=4, gbit=16)
+    opt, groups = ft.build_optimizer(model, lr=1e-4)
+    tuner = ft.LatentFineTuner(model, opt, groups, grad_accum=grad_accum)
+    vocab = ft.ARCHS[arch]["vocab_size"]
+    host = [torch.randint(0, vocab, (micro_batch, seq), generator=torch.Generator().manual_seed(100 + rank * 1000 + i)).pin_memory()
+            for i in range(grad_accum)]
+
+    def one_step():
+        batches = [h.to("cuda", non_blocking=True) for h in host]
+        return float(tuner.step(batches))          # float(): device -> host read of the loss
+
+    losses = [one_step() for _ in range(warmup)]
+    if dist.is_initialized():
+        dist.barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        losses.append(one_step())
+    e1.record(); torch.cuda.synchronize()
+    ms = torch.tensor([e0.elapsed_time(e1) / steps], device="cuda", dtype=torch.float64)
+    if dist.is_initialized():
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    ms = float(ms)
+    tokens = world * micro_batch * seq * grad_accum
+    same = True
+    if world > 1:
+        from latentq_llm_b200.dp import replicas_identical
+        same = replicas_identical([p.data for p in groups[0]["params"][:8]])
+    res = {"arch": arch, "tokens_per_s": round(tokens / ms * 1e3, 1), "ms_per_step": round(ms, 1), "world": world,
+           "micro_batch": micro_batch, "seq": seq, "grad_accum": grad_accum, "loss_first": round(losses[0], 4),
+           "loss_last": round(losses[-1], 4), "replica_codes_identical": same,
+           "grad_arena_bytes": tuner.arena.flat.numel() * 2, "h2d_bytes_per_step": grad_accum * micro_batch * seq * 8}
+    del tuner, opt, model
+    torch.cuda.empty_cache()
+    return res
+
+
 def cpu_baseline(sample_m=256, reps=2):
     """The reference's CPU path for this workload (DeQfunc_4bit_g then input.mm(W.t()) / grad.mm(W), fp32,
     utils/quant.py:116-121,136-140) restated with the oracle, on a bounded sample: the (4096,4096) shape at M=sample_m."""
@@ -347,6 +395,18 @@ def run_ours(args):
             import oracle
             oracle.build()
             line["cpu_baseline"], _ = cpu_baseline()
+    # the data-parallel fine-tune step runs on every rank (it has the path's one real exchange step)
+    ft_res = None
+    if not args.no_extra:
+        del layers, host
+        torch.cuda.empty_cache()
+        try:
+            ft_res = finetune_measurement(torch)
+        except Exception as e:                      # the headline line must still be printed
+            ft_res = {"error": repr(e)[:300]}
+    if rank == 0:
+        if ft_res is not None:
+            line.setdefault("extra", {})["finetune_opt1.3b"] = ft_res
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()

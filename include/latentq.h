@@ -72,6 +72,13 @@ LQ_API int lq_uniform16_decode(const int32_t* words, int64_t n_words, float* out
 LQ_API int lq_pack_nibbles(const uint8_t* codes, int8_t* packed, int64_t n_codes, lq_stream_t stream);
 LQ_API int lq_unpack_nibbles(const int8_t* packed, int8_t* codes, int64_t n_bytes, lq_stream_t stream);
 
+/* Conversion between the two packed int4 layouts of the reference: nibble-pair int8 [N*K/2]
+ * (QuantLinearA16W4.pack, PTQ/quant/quant_linear.py:455-470; the layout main0.py loads) and GPTQ int32 [K/8, N]
+ * (QuantLinearGPTQ.pack, PTQ/quant/quant_linear.py:343-377).  Codes only; scales / zero points are small
+ * [groups, N] <-> [N*groups] transposes done by the host code. */
+LQ_API int lq_nibblepair_to_gptq(const int8_t* qweight_np, int32_t* qweight_gptq, int64_t N, int64_t K, lq_stream_t stream);
+LQ_API int lq_gptq_to_nibblepair(const int32_t* qweight_gptq, int8_t* qweight_np, int64_t N, int64_t K, lq_stream_t stream);
+
 /* DeQfunc_4bit_g (utils/quant.py:66-72).  qparams of dtype qp_dtype, one per `group` elements.
  * qp_dtype == LQ_BF16 reproduces the bf16 arithmetic of the GPU reference. */
 LQ_API int lq_a16w4_dequant(const int8_t* qweight, const void* scales, const void* zeros, int qp_dtype,

@@ -56,6 +56,8 @@ SIGNATURES = {
     "lq_uniform16_decode": [_p, _i64, _p, _p],
     "lq_pack_nibbles": [_p, _p, _i64, _p],
     "lq_unpack_nibbles": [_p, _p, _i64, _p],
+    "lq_nibblepair_to_gptq": [_p, _p, _i64, _i64, _p],
+    "lq_gptq_to_nibblepair": [_p, _p, _i64, _i64, _p],
     "lq_a16w4_dequant": [_p, _p, _p, _i, _p, _i, _i64, _i, _p],
     "lq_find_qparams": [_p, _i, _i64, _i, _i, _i, _p, _p, _p],
     "lq_a16w4_requant": [_p, _i, _p, _p, _i, _i64, _i, _OPTS, _p, _p, _p],

@@ -810,6 +810,33 @@ __global__ void __launch_bounds__(256) k_act_quant_per_tensor(const __nv_bfloat1
     }
 }
 
+
+// =================================================================================================
+// Layout conversion: nibble-pair int8 [N, K/2] (utils/quant.py:4-9)  <->  GPTQ int32 [K/8, N]
+// (PTQ/quant/quant_linear.py:364-377: nibble j of qweight[r, n] = code of W[n, 8r + j], LSB first).
+// The 8 codes of W[n, 8r .. 8r+7] are one 32-bit word in either layout; the nibble-pair word keeps the even
+// element in the high nibble of each byte, the GPTQ word in the low one, so the conversion is a nibble swap
+// inside every byte plus a transpose of the word matrix (32x32 tiles through shared memory).
+// =================================================================================================
+__device__ __forceinline__ uint32_t swap_nibbles(uint32_t w) { return ((w & 0x0F0F0F0Fu) << 4) | ((w >> 4) & 0x0F0F0F0Fu); }
+
+// in: [rows, cols] words; out: [cols, rows] words, nibble-swapped
+__global__ void __launch_bounds__(256) k_transpose_swap_words(const uint32_t* __restrict__ in, uint32_t* __restrict__ out,
+                                                              int rows, int cols) {
+    __shared__ uint32_t tile[32][33];
+    const int c0 = blockIdx.x * 32, r0 = blockIdx.y * 32;
+    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;           // 32 x 8
+    for (int i = ty; i < 32; i += 8) {
+        const int r = r0 + i, c = c0 + tx;
+        if (r < rows && c < cols) tile[i][tx] = swap_nibbles(__ldg(in + (size_t)r * cols + c));
+    }
+    __syncthreads();
+    for (int i = ty; i < 32; i += 8) {
+        const int c = c0 + i, r = r0 + tx;
+        if (r < rows && c < cols) out[(size_t)c * rows + r] = tile[tx][i];
+    }
+}
+
 __global__ void __launch_bounds__(256) k_philox_dither(uint64_t seed, uint64_t stream_id, int64_t first_word,
                                                        int64_t n_words, float* __restrict__ out) {
     for (int64_t w = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; w < n_words; w += (int64_t)gridDim.x * blockDim.x) {
@@ -994,6 +1021,28 @@ int lq_a8w8_fold_delta(int8_t* codes, int32_t* words, const void* delta, int del
     p.scales = qscales; p.zeros = nullptr; p.qp_dtype = qp_dtype; p.codes_out = codes; p.words_out = words;
     return launch_requant<8>(p, opts, LQ_ST(stream));
 }
+
+int lq_nibblepair_to_gptq(const int8_t* qweight_np, int32_t* qweight_gptq, int64_t N, int64_t K, lq_stream_t stream) {
+    if (N == 0 || K == 0) return LQ_OK;
+    if (!qweight_np || !qweight_gptq || N < 0 || K < 0 || (K % 8) || !aligned(qweight_np, 4) || N > (1 << 30) || K > (1 << 30)) return LQ_EINVAL;
+    { int rc_dev = ensure_device_for(qweight_np); if (rc_dev) return rc_dev; }
+    const int rows = (int)N, cols = (int)(K / 8);
+    dim3 grid((cols + 31) / 32, (rows + 31) / 32);
+    k_transpose_swap_words<<<grid, 256, 0, LQ_ST(stream)>>>(reinterpret_cast<const uint32_t*>(qweight_np),
+                                                           reinterpret_cast<uint32_t*>(qweight_gptq), rows, cols);
+    return check_launch("lq_nibblepair_to_gptq");
+}
+int lq_gptq_to_nibblepair(const int32_t* qweight_gptq, int8_t* qweight_np, int64_t N, int64_t K, lq_stream_t stream) {
+    if (N == 0 || K == 0) return LQ_OK;
+    if (!qweight_np || !qweight_gptq || N < 0 || K < 0 || (K % 8) || !aligned(qweight_np, 4) || N > (1 << 30) || K > (1 << 30)) return LQ_EINVAL;
+    { int rc_dev = ensure_device_for(qweight_np); if (rc_dev) return rc_dev; }
+    const int rows = (int)(K / 8), cols = (int)N;
+    dim3 grid((cols + 31) / 32, (rows + 31) / 32);
+    k_transpose_swap_words<<<grid, 256, 0, LQ_ST(stream)>>>(reinterpret_cast<const uint32_t*>(qweight_gptq),
+                                                           reinterpret_cast<uint32_t*>(qweight_np), rows, cols);
+    return check_launch("lq_gptq_to_nibblepair");
+}
+
 int lq_fold_fallback_words(int reset, unsigned long long* count) {
     unsigned long long v = 0;
     cudaError_t e = cudaMemcpyFromSymbol(&v, g_fold_fallback_words, sizeof(v));

@@ -115,6 +115,20 @@ def unpack_nibbles(packed):
     return out
 
 
+def nibblepair_to_gptq(qweight_np, N, K):
+    _chk(qweight_np, "qweight_np", torch.int8)
+    out = torch.empty((K // 8, N), dtype=torch.int32, device=qweight_np.device)
+    L.call("lq_nibblepair_to_gptq", _ptr(qweight_np), _ptr(out), N, K, _stream())
+    return out
+
+
+def gptq_to_nibblepair(qweight_gptq, N, K):
+    _chk(qweight_gptq, "qweight_gptq", torch.int32)
+    out = torch.empty(N * K // 2, dtype=torch.int8, device=qweight_gptq.device)
+    L.call("lq_gptq_to_nibblepair", _ptr(qweight_gptq), _ptr(out), N, K, _stream())
+    return out
+
+
 def a16w4_dequant(qweight, scales, zeros, shape, dtype=torch.bfloat16, group=128):
     _chk(qweight, "qweight", torch.int8); _chk(scales, "scales"); _chk(zeros, "zeros", scales.dtype)
     numel = qweight.numel() * 2

@@ -212,6 +212,38 @@ def main(ref):
         for k in ("qmap1", "absmax1", "qmap2", "absmax2"):
             out[f"adam_{k}_{step + 1}"] = f32(st_[k].reshape(-1))
 
+    # --- PTQ packers (PTQ/quant/quant_linear.py:304-477, 578-692): checkpoint producers --------------------
+    pq = slice_module(os.path.join(ref, "PTQ", "quant", "quant_linear.py"),
+                      {"QuantLinearGPTQ", "QuantLinearA16W4", "QuantLinearA8W8", "python_compress", "python_decompress"})
+    Np, Kp = 128, 256
+    lin = torch.nn.Linear(Kp, Np, bias=True)
+    lin.weight.data = (torch.randn(Np, Kp, generator=g) * 0.02)
+    lin.bias.data = torch.randn(Np, generator=g) * 0.1
+    qp_ = qz["Quantizer"]()
+    qp_.configure(4, perchannel=True, sym=False, mse=False)
+    qp_.find_params(lin.weight.data.view(-1, 128), weight=True)
+    sc_g = qp_.scale.reshape(Np, Kp // 128).clone()          # [N, G] as PTQ/run.py:18-41 hands them over
+    zr_g = qp_.zero.reshape(Np, Kp // 128).clone()
+    out["ptq_w"], out["ptq_bias"] = f32(lin.weight.data), f32(lin.bias.data)
+    out["ptq_scale"], out["ptq_zero"] = f32(sc_g), f32(zr_g)
+    gq = pq["QuantLinearGPTQ"](4, 128, Kp, Np, True)
+    gq.pack(lin, sc_g.clone(), zr_g.clone(), None)
+    out["gptq_qweight"], out["gptq_qzeros"] = gq.qweight.numpy(), gq.qzeros.numpy()
+    out["gptq_scales"], out["gptq_g_idx"] = f32(gq.scales), gq.g_idx.numpy()
+    out["gptq_unpack"] = f32(gq.unpack(gq.qweight, gq.scales, gq.qzeros))
+    a4 = pq["QuantLinearA16W4"](4, 128, Kp, Np, True)
+    a4.pack(lin, sc_g.clone(), zr_g.clone(), None)
+    out["a16w4_qweight"] = a4.qweight.numpy()
+    out["a16w4_scales"], out["a16w4_zeros"] = f32(a4.scales.reshape(-1)), f32(a4.zeros.reshape(-1))
+    out["a16w4_unpack"] = f32(a4.unpack(a4.qweight))
+    qs_ = qz["Quantizer"]()
+    qs_.configure(8, perchannel=True, sym=True, mse=False)
+    qs_.find_params(lin.weight.data, weight=True)
+    a8 = pq["QuantLinearA8W8"](8, -1, Kp, Np, True)
+    a8.pack(lin, qs_.scale.clone(), qs_.zero.clone(), None)
+    out["a8w8_qweight"], out["a8w8_qzeros"] = a8.qweight.numpy(), a8.qzeros.numpy().astype(np.int32)
+    out["a8w8_scales"] = f32(a8.scales.reshape(-1))
+
     np.savez_compressed(os.path.join(OUT, "reference_vectors.npz"), **out)
     print("wrote", len(out), "arrays,", os.path.getsize(os.path.join(OUT, "reference_vectors.npz")), "bytes")
 

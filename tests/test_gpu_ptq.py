@@ -1,0 +1,78 @@
+"""Checkpoint-side modules (mirror of PTQ/quant/quant_linear.py) against vectors produced by the reference's own
+`pack` / `unpack` methods, and the GPTQ-layout GEMM entry points."""
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _linear(golden):
+    lin = torch.nn.Linear(256, 128, bias=True)
+    lin.weight.data = torch.from_numpy(golden["ptq_w"])
+    lin.bias.data = torch.from_numpy(golden["ptq_bias"])
+    return lin
+
+
+def test_gptq_pack_unpack_and_gemm(golden):
+    from latentq_llm_b200 import ops, ptq
+    m = ptq.QuantLinearGPTQ(4, 128, 256, 128, True).cuda()
+    m.pack(_linear(golden), torch.from_numpy(golden["ptq_scale"]), torch.from_numpy(golden["ptq_zero"]), None)
+    assert m.qweight.dtype == torch.int32 and np.array_equal(m.qweight.cpu().numpy(), golden["gptq_qweight"])
+    assert np.array_equal(m.qzeros.cpu().numpy(), golden["gptq_qzeros"])
+    assert np.array_equal(m.scales.float().cpu().numpy(), golden["gptq_scales"])
+    assert np.array_equal(m.g_idx.cpu().numpy(), golden["gptq_g_idx"])
+    W = m.unpack(m.qweight, m.scales, m.qzeros)
+    assert np.array_equal(W.cpu().numpy(), golden["gptq_unpack"])
+    # layout conversion round trip
+    codes = ops.gptq_to_nibblepair(m.qweight, 128, 256)
+    assert torch.equal(ops.nibblepair_to_gptq(codes, 128, 256), m.qweight)
+    # GEMM entry points of the GPTQ layout (fp16 in / out like the reference)
+    g = torch.Generator(device="cuda").manual_seed(0)
+    x = torch.randn(40, 256, device="cuda", generator=g).half().requires_grad_(True)
+    y = m(x)
+    ref = x.detach().float() @ W.t() + m.bias.float()
+    assert y.dtype == torch.float16 and float((y.float() - ref).abs().max() / ref.abs().max()) < 1e-2
+    dy = torch.randn(40, 128, device="cuda", generator=g).half()
+    y.backward(dy)
+    ref = dy.float() @ W
+    assert float((x.grad.float() - ref).abs().max() / ref.abs().max()) < 1e-2
+    with pytest.raises(NotImplementedError):
+        ptq.matmul248(x.detach(), m.qweight, m.scales, m.qzeros, m.g_idx.flip(0), 4, 15)
+
+
+def test_a16w4_and_a8w8_packers(golden):
+    from latentq_llm_b200 import ptq
+    a4 = ptq.QuantLinearA16W4(4, 128, 256, 128, True)
+    a4.pack(_linear(golden), torch.from_numpy(golden["ptq_scale"]), torch.from_numpy(golden["ptq_zero"]), None)
+    assert a4.qweight.dtype == torch.int8 and np.array_equal(a4.qweight.cpu().numpy(), golden["a16w4_qweight"])
+    assert np.array_equal(a4.scales.float().cpu().numpy().ravel(), golden["a16w4_scales"])
+    assert np.array_equal(a4.zeros.float().cpu().numpy().ravel(), golden["a16w4_zeros"])
+    W = a4.unpack(a4.qweight)
+    assert np.array_equal(W.float().cpu().numpy(), golden["a16w4_unpack"])
+    x = torch.randn(24, 256, device="cuda").half()
+    ref = x.float() @ W.float().t() + a4.bias.float()
+    assert float((a4(x).float() - ref).abs().max() / ref.abs().max()) < 1e-2
+    # A8W8: symmetric per-channel uint8 weights with zero point 128
+    import oracle as orc
+    w = golden["ptq_w"]
+    s, z = orc.find_qparams(w, 256, 255, True)
+    a8 = ptq.QuantLinearA8W8(8, -1, 256, 128, True)
+    a8.pack(_linear(golden), torch.from_numpy(s), torch.from_numpy(z), None)
+    assert a8.qweight.dtype == torch.uint8 and np.array_equal(a8.qweight.cpu().numpy(), golden["a8w8_qweight"])
+    assert np.array_equal(a8.qzeros.cpu().numpy().astype(np.int32), golden["a8w8_qzeros"])
+    assert np.array_equal(a8.scales.float().cpu().numpy().ravel(), golden["a8w8_scales"])
+    a8.clampv = 4.0
+    y = a8(x.to(torch.bfloat16))
+    ref = x.float().clamp(-4, 4) @ a8.unpack(a8.qweight).float().t() + a8.bias.float()
+    assert float((y.float() - ref).norm() / ref.norm()) < 3e-2
+
+
+def test_per_token_fake_quant(golden):
+    from latentq_llm_b200 import ptq
+    t = torch.from_numpy(golden["aq_x"]).cuda().to(torch.bfloat16)
+    out = ptq.quantize_activation_per_token_absmax(t.clone())
+    import oracle as orc
+    q, s = orc.act_quant_per_token(t.float().cpu().numpy(), math_bf16=True)
+    want = orc.bf16_round(q.astype(np.float32) * s[:, None])
+    assert np.array_equal(out.float().cpu().numpy(), want)

@@ -140,6 +140,39 @@ LQ_API int lq_opt8_dequant(const uint8_t* q, int64_t n, int block, const float* 
                            float* x, lq_stream_t stream);
 
 /* ------------------------------------------------------------------------
+ * Fused optimizer step: MyAdam.update_step (utils/quant.py:1052-1148) in one pass.
+ * ------------------------------------------------------------------------ */
+typedef struct lq_adam_hyper {
+    float beta1, beta2;          /* as torch rounds the Python floats to the op's fp32 math type            */
+    float one_minus_beta1, one_minus_beta2;
+    float eps;
+    float neg_step_size;         /* -(lr * sqrt(1 - beta2^t) / (1 - beta1^t)), rounded once from double      */
+} lq_adam_hyper;
+
+/* One quantized A16W4 weight, everything in place (utils/quant.py:1056-1073 latent reconstruction, :1075-1105
+ * 8-bit state decode + Adam in the gradient's dtype, :1113-1131 state re-encode, :1143 requantize):
+ *   latent = residual.add(DeQfunc_4bit_g(codes));  m, v = decode(state1), decode(state2)^2;  Adam;
+ *   state1, state2 = Qfunc_8bit_opt(m), Qfunc_8bit_opt(sqrt(v)+eps);  codes, residual = Qfunc_4bit_g_res(latent).
+ * `grad` is [numel] in `grad_dtype` (the chain runs in that dtype when the qparams have it too, as torch's type
+ * promotion would); `opt_block` is 2048 or 128 elements per (scale, t_max) pair.  weight_decay must be 0 (the
+ * only value the reference's parameter groups use, main0.py:445-472).  The residual-curve statistics update of
+ * :1107-1111 is not part of this call. */
+LQ_API int lq_adam_a16w4_step(int8_t* codes, int32_t* words, const void* grad, int grad_dtype,
+                              const void* scales, const void* zeros, int qp_dtype, int64_t numel, int group,
+                              uint8_t* state1, float* scale1, float* tmax1,
+                              uint8_t* state2, float* scale2, float* tmax2, int opt_block,
+                              const lq_adam_hyper* hyper, const lq_requant_opts* opts, lq_stream_t stream);
+
+/* Many small dense bf16 parameters with bf16 optimizer states (numel < 65536, utils/quant.py:1020-1027) in one
+ * launch.  `table` is a DEVICE array of n_tensors records {param, grad, state1, state2, numel}; state2 holds
+ * sqrt(v)+eps as in the reference (:1133-1135).  All four arrays of a record are bf16 and 16-byte aligned. */
+typedef struct lq_dense_slot {
+    void* param; const void* grad; void* state1; void* state2; int64_t numel;
+} lq_dense_slot;
+LQ_API int lq_adam_dense_multi(const lq_dense_slot* table, int n_tensors, int64_t max_numel,
+                               const lq_adam_hyper* hyper, lq_stream_t stream);
+
+/* ------------------------------------------------------------------------
  * Activation quantizers for the A8W8 path.
  * ------------------------------------------------------------------------ */
 /* quantize_activation_per_token_absmax (PTQ/quant/quant_linear.py:520-528): bf16 x[M,K] ->

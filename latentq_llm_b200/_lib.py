@@ -26,6 +26,18 @@ class RequantOpts(C.Structure):
                 ("seed", C.c_uint64), ("stream_id", C.c_uint64), ("dither_buf", C.c_void_p)]
 
 
+class AdamHyper(C.Structure):
+    """Mirror of `lq_adam_hyper`."""
+    _fields_ = [("beta1", C.c_float), ("beta2", C.c_float), ("one_minus_beta1", C.c_float),
+                ("one_minus_beta2", C.c_float), ("eps", C.c_float), ("neg_step_size", C.c_float)]
+
+
+class DenseSlot(C.Structure):
+    """Mirror of `lq_dense_slot`."""
+    _fields_ = [("param", C.c_void_p), ("grad", C.c_void_p), ("state1", C.c_void_p), ("state2", C.c_void_p),
+                ("numel", C.c_int64)]
+
+
 class LatentQError(RuntimeError):
     def __init__(self, fn, status, detail=""):
         self.status = status
@@ -41,6 +53,7 @@ lib = C.CDLL(LIB_PATH)
 
 _p, _i, _i64, _f, _u64, _sz = C.c_void_p, C.c_int, C.c_int64, C.c_float, C.c_uint64, C.c_size_t
 _OPTS = C.POINTER(RequantOpts)
+_HYPER = C.POINTER(AdamHyper)
 
 # name -> argtypes; every function returns int except the ones listed in _RESTYPE.
 SIGNATURES = {
@@ -68,6 +81,8 @@ SIGNATURES = {
     "lq_philox_dither": [_u64, _u64, _i64, _i64, _p, _p],
     "lq_opt8_quant": [_p, _i64, _i, _p, _p, _p, _p],
     "lq_opt8_dequant": [_p, _i64, _i, _p, _p, _p, _p],
+    "lq_adam_a16w4_step": [_p, _p, _p, _i, _p, _p, _i, _i64, _i, _p, _p, _p, _p, _p, _p, _i, _HYPER, _OPTS, _p],
+    "lq_adam_dense_multi": [_p, _i, _i64, _HYPER, _p],
     "lq_act_quant_per_token": [_p, _i64, _i64, _p, _p, _p],
     "lq_act_quant_per_tensor": [_p, _i64, _p, _p, _p],
     "lq_gemm_workspace_bytes": [_i, _i64, _i64, _i64],

@@ -1,0 +1,204 @@
+// Fused optimizer step of the latent fine-tune path: one HBM pass per quantized weight instead of the ~40
+// tensor-op passes of MyAdam.update_step (utils/quant.py:1052-1148), and one launch for all the small dense
+// parameters.  Every intermediate is rounded where the reference's torch ops round it (each op computes in fp32
+// and stores in the tensor dtype), so codes, residual words and optimizer states come out bit-identical to the
+// op-by-op route.
+//
+// Where torch's CUDA functors are single expressions (`a + alpha * b`, `a + alpha * (b / c)`), nvcc contracts the
+// multiply-add into an FMA in torch's own build; the same contraction is spelled out here with __fmaf_rn
+// (checked on the GPU against torch's add_/addcmul_/addcdiv_ on 2^24-element bf16 tensors: the separately
+// rounded forms of add_(alpha) and addcdiv_ differ from torch in a few elements per million, the fused ones never).
+#include "lq_requant.cuh"
+
+namespace lq {
+
+struct AdamParams {
+    RequantParams rq;
+    const void* grad; int grad_dtype;
+    uint8_t* st1; float* sc1; float* tm1;
+    uint8_t* st2; float* sc2; float* tm2;
+    int opt_shift;                 // log2(elements per optimizer-state block): 11 or 7
+    int64_t n_tiles;               // tiles of 256 words
+    lq_adam_hyper h;
+};
+
+// m <- m*b1 ; m <- m + (1-b1)*g ; v <- v*b2 ; v <- v + (1-b2)*(g*g) ; d <- sqrt(v) ; d <- d + eps ; each stored in
+// the chain dtype (utils/quant.py:1098-1101).  Returns m and d = sqrt(v)+eps.
+template <bool BF>
+__device__ __forceinline__ void adam_moments(const lq_adam_hyper& h, float g, float& m, float& v_to_d) {
+    m = rb<BF>(__fmul_rn(m, h.beta1));
+    m = rb<BF>(__fmaf_rn(h.one_minus_beta1, g, m));
+    float v = rb<BF>(__fmul_rn(v_to_d, h.beta2));
+    v = rb<BF>(__fmaf_rn(h.one_minus_beta2, __fmul_rn(g, g), v));
+    float d = rb<BF>(__fsqrt_rn(v));
+    v_to_d = rb<BF>(__fadd_rn(d, h.eps));
+}
+// p <- p + (-step_size) * (m / d)   (addcdiv_, utils/quant.py:1105)
+template <bool BF>
+__device__ __forceinline__ float adam_apply(const lq_adam_hyper& h, float p, float m, float d) {
+    return rb<BF>(__fmaf_rn(h.neg_step_size, __fdiv_rn(m, d), p));
+}
+
+__device__ __forceinline__ uint2 opt8_encode8(const float (&x)[8], float mx, float s) {
+    const float rs = __frcp_rn(s);
+    const bool ok = fastdiv_ok_scale(s);
+    uint32_t b[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+        float t = rne(div_rn(__fsub_rn(mx, x[k]), s, rs, ok));
+        t = fminf(fmaxf(t, 0.0f), 255.0f);
+        b[k] = f2bits(t) & 0xffu;
+    }
+    uint2 o;
+    o.x = b[0] | (b[1] << 8) | (b[2] << 16) | (b[3] << 24);
+    o.y = b[4] | (b[5] << 8) | (b[6] << 16) | (b[7] << 24);
+    return o;
+}
+
+// One thread per word of 8 elements; a CTA covers 256 words = one 2048-element optimizer-state block, or sixteen
+// 128-element blocks (16 lanes each).
+template <int CODEC, int DITHER, bool BF>
+__global__ void __launch_bounds__(256) k_adam_a16w4(const AdamParams p) {
+    __shared__ float s_red[4][8];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    for (int64_t tile = blockIdx.x; tile < p.n_tiles; tile += gridDim.x) {
+        const int64_t w = tile * 256 + tid;
+        const bool active = w < p.rq.n_words;
+        const int64_t e0 = w * 8;
+        float lat[8], m[8], d[8];
+        float s = 1.0f, z = 0.0f;
+        float mn1 = INFINITY, mx1 = -INFINITY, mn2 = INFINITY, mx2 = -INFINITY;
+        int64_t ob = 0;
+        if (active) {
+            const int64_t g = p.rq.group_shift >= 0 ? (e0 >> p.rq.group_shift) : (e0 / p.rq.group);
+            s = load1(p.rq.scales, p.rq.qp_dtype, g);
+            z = load1(p.rq.zeros, p.rq.qp_dtype, g);
+            ob = e0 >> p.opt_shift;
+            const float s1 = p.sc1[ob], t1 = p.tm1[ob], s2 = p.sc2[ob], t2 = p.tm2[ob];   // rewritten below: plain loads
+            const uint2 q1 = *reinterpret_cast<const uint2*>(p.st1 + e0);
+            const uint2 q2 = *reinterpret_cast<const uint2*>(p.st2 + e0);
+            float gr[8];
+            load8(p.grad, p.grad_dtype, e0, gr);
+            latent_load<4, CODEC, BF>(p.rq, w, s, z, lat);
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+                const float c1 = u2f(((k < 4 ? q1.x : q1.y) >> (8 * (k & 3))) & 0xffu);
+                const float c2 = u2f(((k < 4 ? q2.x : q2.y) >> (8 * (k & 3))) & 0xffu);
+                m[k] = rb<BF>(__fsub_rn(t1, __fmul_rn(c1, s1)));           // DeQfunc_8bit_opt(...).to(dtype)
+                const float r2 = __fsub_rn(t2, __fmul_rn(c2, s2));
+                d[k] = rb<BF>(__fmul_rn(r2, r2));                          // (s2 * s2).to(dtype)
+                adam_moments<BF>(p.h, gr[k], m[k], d[k]);
+                lat[k] = adam_apply<BF>(p.h, lat[k], m[k], d[k]);
+                mn1 = fminf(mn1, m[k]); mx1 = fmaxf(mx1, m[k]);
+                mn2 = fminf(mn2, d[k]); mx2 = fmaxf(mx2, d[k]);
+            }
+        }
+        // min/max over the optimizer-state block: 16 lanes, then (2048-element blocks) the whole CTA
+#pragma unroll
+        for (int o = 8; o > 0; o >>= 1) {
+            mn1 = fminf(mn1, __shfl_xor_sync(0xffffffffu, mn1, o)); mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, o));
+            mn2 = fminf(mn2, __shfl_xor_sync(0xffffffffu, mn2, o)); mx2 = fmaxf(mx2, __shfl_xor_sync(0xffffffffu, mx2, o));
+        }
+        if (p.opt_shift == 11) {
+            mn1 = fminf(mn1, __shfl_xor_sync(0xffffffffu, mn1, 16)); mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 16));
+            mn2 = fminf(mn2, __shfl_xor_sync(0xffffffffu, mn2, 16)); mx2 = fmaxf(mx2, __shfl_xor_sync(0xffffffffu, mx2, 16));
+            __syncthreads();                                               // previous tile's readers are done
+            if (lane == 0) { s_red[0][warp] = mn1; s_red[1][warp] = mx1; s_red[2][warp] = mn2; s_red[3][warp] = mx2; }
+            __syncthreads();
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                mn1 = fminf(mn1, s_red[0][i]); mx1 = fmaxf(mx1, s_red[1][i]);
+                mn2 = fminf(mn2, s_red[2][i]); mx2 = fmaxf(mx2, s_red[3][i]);
+            }
+        }
+        if (active) {
+            const float ns1 = __fadd_rn(__fdiv_rn(__fsub_rn(mx1, mn1), 255.0f), 1e-10f);
+            const float ns2 = __fadd_rn(__fdiv_rn(__fsub_rn(mx2, mn2), 255.0f), 1e-10f);
+            *reinterpret_cast<uint2*>(p.st1 + e0) = opt8_encode8(m, mx1, ns1);
+            *reinterpret_cast<uint2*>(p.st2 + e0) = opt8_encode8(d, mx2, ns2);
+            const bool leader = p.opt_shift == 11 ? (tid == 0) : ((tid & 15) == 0);
+            if (leader) { p.sc1[ob] = ns1; p.tm1[ob] = mx1; p.sc2[ob] = ns2; p.tm2[ob] = mx2; }
+            latent_store<4, CODEC, DITHER, BF>(p.rq, w, s, z, lat);
+        }
+    }
+}
+
+template <int CODEC, int DITHER>
+static int launch_adam(const AdamParams& p, bool bf, cudaStream_t st) {
+    const int64_t cap = (int64_t)sm_count() * 8;
+    const int grid = (int)(p.n_tiles < cap ? p.n_tiles : cap);
+    if (bf) k_adam_a16w4<CODEC, DITHER, true><<<grid, 256, 0, st>>>(p);
+    else k_adam_a16w4<CODEC, DITHER, false><<<grid, 256, 0, st>>>(p);
+    return check_launch("k_adam_a16w4");
+}
+
+// ---- many small dense bf16 tensors ---------------------------------------------------------------
+__global__ void __launch_bounds__(256) k_adam_dense_multi(const lq_dense_slot* __restrict__ table, const lq_adam_hyper h) {
+    const lq_dense_slot t = table[blockIdx.y];
+    __nv_bfloat16* pw = reinterpret_cast<__nv_bfloat16*>(t.param);
+    const __nv_bfloat16* pg = reinterpret_cast<const __nv_bfloat16*>(t.grad);
+    __nv_bfloat16* p1 = reinterpret_cast<__nv_bfloat16*>(t.state1);
+    __nv_bfloat16* p2 = reinterpret_cast<__nv_bfloat16*>(t.state2);
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < t.numel; i += (int64_t)gridDim.x * blockDim.x) {
+        float m = __bfloat162float(p1[i]);
+        const float s2 = __bfloat162float(p2[i]);
+        float d = rb<true>(__fmul_rn(s2, s2));                             // state2 * state2 (utils/quant.py:1092)
+        adam_moments<true>(h, __bfloat162float(pg[i]), m, d);
+        const float w = adam_apply<true>(h, __bfloat162float(pw[i]), m, d);
+        p1[i] = __float2bfloat16_rn(m);
+        p2[i] = __float2bfloat16_rn(d);
+        pw[i] = __float2bfloat16_rn(w);
+    }
+}
+
+}  // namespace lq
+
+using namespace lq;
+
+extern "C" {
+
+int lq_adam_a16w4_step(int8_t* codes, int32_t* words, const void* grad, int grad_dtype, const void* scales,
+                       const void* zeros, int qp_dtype, int64_t numel, int group, uint8_t* state1, float* scale1,
+                       float* tmax1, uint8_t* state2, float* scale2, float* tmax2, int opt_block,
+                       const lq_adam_hyper* hyper, const lq_requant_opts* opts, lq_stream_t stream) {
+    if (numel == 0) return LQ_OK;
+    AdamParams p{};
+    int rc = fill_requant(p.rq, opts, numel, group);
+    if (rc) return rc;
+    if (!hyper || !codes || !words || !grad || !scales || !zeros || !state1 || !scale1 || !tmax1 || !state2 || !scale2 ||
+        !tmax2 || !dtype_ok(grad_dtype) || !dtype_ok(qp_dtype) || !aligned(codes, 4) || !aligned(words, 4) ||
+        !aligned(grad, 16) || !aligned(state1, 8) || !aligned(state2, 8))
+        return LQ_EINVAL;
+    if ((opt_block != 2048 && opt_block != 128) || numel % opt_block != 0) return LQ_EINVAL;
+    // the chain dtype is the gradient's; mixed gradient / qparam dtypes promote differently op by op in torch
+    if (grad_dtype != qp_dtype || opts->math_dtype != grad_dtype) return LQ_EUNSUPPORTED;
+    if ((rc = ensure_device_for(codes)) != LQ_OK) return rc;
+    p.rq.codes_in = codes; p.rq.words_in = words; p.rq.codes_out = codes; p.rq.words_out = words;
+    p.rq.scales = scales; p.rq.zeros = zeros; p.rq.qp_dtype = qp_dtype;
+    p.grad = grad; p.grad_dtype = grad_dtype;
+    p.st1 = state1; p.sc1 = scale1; p.tm1 = tmax1; p.st2 = state2; p.sc2 = scale2; p.tm2 = tmax2;
+    p.opt_shift = opt_block == 2048 ? 11 : 7;
+    p.n_tiles = (p.rq.n_words + 255) / 256;
+    p.h = *hyper;
+    const bool bf = grad_dtype == LQ_BF16;
+    cudaStream_t st = LQ_ST(stream);
+    if (opts->codec == LQ_CODEC_THREEFOLD && opts->dither == LQ_DITHER_HASH) return launch_adam<LQ_CODEC_THREEFOLD, LQ_DITHER_HASH>(p, bf, st);
+    if (opts->codec == LQ_CODEC_THREEFOLD && opts->dither == LQ_DITHER_PHILOX) return launch_adam<LQ_CODEC_THREEFOLD, LQ_DITHER_PHILOX>(p, bf, st);
+    if (opts->codec == LQ_CODEC_UNIFORM16 && opts->dither == LQ_DITHER_PHILOX) return launch_adam<LQ_CODEC_UNIFORM16, LQ_DITHER_PHILOX>(p, bf, st);
+    return LQ_EUNSUPPORTED;
+}
+
+int lq_adam_dense_multi(const lq_dense_slot* table, int n_tensors, int64_t max_numel, const lq_adam_hyper* hyper,
+                        lq_stream_t stream) {
+    if (n_tensors == 0 || max_numel == 0) return LQ_OK;
+    if (!table || !hyper || n_tensors < 0 || n_tensors > 65535 || max_numel < 0) return LQ_EINVAL;
+    int rc = ensure_device_for(table);
+    if (rc != LQ_OK) return rc;
+    int64_t bx = (max_numel + 255) / 256;
+    if (bx > 64) bx = 64;
+    dim3 grid((unsigned)bx, (unsigned)n_tensors);
+    k_adam_dense_multi<<<grid, 256, 0, LQ_ST(stream)>>>(table, *hyper);
+    return check_launch("k_adam_dense_multi");
+}
+
+}  // extern "C"

@@ -87,7 +87,7 @@ def quantize_decoder(model: nn.Module, lbit: int = 4, gbit: int = 16) -> list:
     return swapped
 
 
-def build_optimizer(model: nn.Module, lr: float = 1e-3, obit: int = 8, mu_f: int = 20):
+def build_optimizer(model: nn.Module, lr: float = 1e-3, obit: int = 8, mu_f: int = 20, direct_grad: bool = True):
     """Parameter groups of main0.py:445-472: [quantized weights], [biases + other decoder-layer weights]."""
     for p in model.parameters():
         p.requires_grad_(False)
@@ -99,7 +99,7 @@ def build_optimizer(model: nn.Module, lr: float = 1e-3, obit: int = 8, mu_f: int
                 groups[1]["params"].append(child.bias)
             if isinstance(child, QLinearA16W4):
                 child.weight.requires_grad = True
-                child.add_hook()
+                child.add_hook(direct=direct_grad)     # False: the reference's backward-hook route
                 groups[0]["params"].append(child.weight)
             elif isinstance(getattr(child, "weight", None), nn.Parameter) and not isinstance(child, nn.Embedding):
                 child.weight.requires_grad_(True)

@@ -218,6 +218,62 @@ def opt8_dequant(q, block, scale, tmax):
 
 
 # ---- activation quantizers ---------------------------------------------------------------------
+# ---- fused optimizer step -------------------------------------------------------------------------
+def make_adam_hyper(beta1, beta2, eps, step_size) -> "L.AdamHyper":
+    """Python doubles -> the fp32 scalars torch's bf16/fp32 elementwise ops would compute with."""
+    h = L.AdamHyper()
+    h.beta1, h.beta2 = beta1, beta2
+    h.one_minus_beta1, h.one_minus_beta2 = 1 - beta1, 1 - beta2
+    h.eps, h.neg_step_size = eps, -step_size
+    return h
+
+
+def adam_a16w4_step(codes, words, grad, scales, zeros, state1, scale1, tmax1, state2, scale2, tmax2,
+                    hyper, opts: RequantOpts, group=128):
+    """In place on codes / words / both states and their block parameters."""
+    _chk(codes, "codes", torch.int8); _chk(words, "words", torch.int32); _chk(grad, "grad")
+    _chk(scales, "scales"); _chk(zeros, "zeros", scales.dtype)
+    _chk(state1, "state1", torch.uint8); _chk(state2, "state2", torch.uint8)
+    for t, nm in ((scale1, "scale1"), (tmax1, "tmax1"), (scale2, "scale2"), (tmax2, "tmax2")):
+        _chk(t, nm, torch.float32)
+    n = grad.numel()
+    assert codes.numel() * 2 == n and words.numel() * 8 == n and state1.numel() == n and state2.numel() == n
+    blocks = scale1.numel()
+    assert tmax1.numel() == blocks and scale2.numel() == blocks and tmax2.numel() == blocks and n % blocks == 0
+    L.check("lq_adam_a16w4_step", L.lib.lq_adam_a16w4_step(
+        _ptr(codes), _ptr(words), _ptr(grad), _dt(grad), _ptr(scales), _ptr(zeros), _dt(scales), n, group,
+        _ptr(state1), _ptr(scale1), _ptr(tmax1), _ptr(state2), _ptr(scale2), _ptr(tmax2), n // blocks,
+        C.byref(hyper), C.byref(opts), _stream()))
+
+
+class DenseAdamTable:
+    """Device-resident table of small dense bf16 parameters for `adam_dense_multi` (rebuilt only when an address
+    changes: parameter data, arena gradient views and in-place states keep theirs from step to step)."""
+
+    def __init__(self):
+        self.key, self.dev, self.n, self.max_numel, self.keep = None, None, 0, 0, None
+
+    def update(self, params, grads, states1, states2):
+        key = tuple((p.data_ptr(), g.data_ptr(), a.data_ptr(), b.data_ptr(), p.numel())
+                    for p, g, a, b in zip(params, grads, states1, states2))
+        if key != self.key:
+            arr = (L.DenseSlot * len(key))()
+            for i, (pp, gp, ap, bp, n) in enumerate(key):
+                arr[i].param, arr[i].grad, arr[i].state1, arr[i].state2, arr[i].numel = pp, gp, ap, bp, n
+            host = torch.frombuffer(bytearray(bytes(arr)), dtype=torch.uint8)
+            self.dev = host.to(params[0].device)
+            self.key, self.n = key, len(key)
+            self.max_numel = max(k[4] for k in key)
+        self.keep = (list(params), list(grads), list(states1), list(states2))
+
+
+def adam_dense_multi(table: DenseAdamTable, hyper):
+    if table.n == 0:
+        return
+    L.check("lq_adam_dense_multi", L.lib.lq_adam_dense_multi(_ptr(table.dev), table.n, table.max_numel,
+                                                             C.byref(hyper), _stream()))
+
+
 def act_quant_per_token(x):
     _chk(x, "x", torch.bfloat16)
     M, K = x.shape
@@ -239,8 +295,13 @@ def act_quant_per_tensor(x):
 _workspaces: dict = {}
 
 
+_ws_need: dict = {}
+
+
 def _workspace(kind, M, N, K, device):
-    need = int(L.lib.lq_gemm_workspace_bytes(kind, M, N, K))
+    need = _ws_need.get((kind, M, N, K))
+    if need is None:
+        need = _ws_need[(kind, M, N, K)] = int(L.lib.lq_gemm_workspace_bytes(kind, M, N, K))
     if need == 0:
         return None, 0
     key = (device.index, torch.cuda.current_stream().cuda_stream)

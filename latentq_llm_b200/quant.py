@@ -160,6 +160,33 @@ class QLinearFunctionW4(torch.autograd.Function):
         return grad_input, None, None, grad_bias
 
 
+class QLinearFunctionW4Direct(torch.autograd.Function):
+    """Hook-free variant of QLinearFunctionW4 for this package's own trainer: same forward and grad-input, but the
+    weight gradient dY^T·x is accumulated straight into `qtensor.grad` (a view of the data-parallel gradient arena)
+    with one fused GEMM (beta = 1) instead of travelling through `dict_temp` and a module backward hook
+    (utils/quant.py:141-142, 398-411).  No [N, K] temporary, no extra add pass, no hook overhead."""
+
+    @staticmethod
+    def forward(ctx, input, weight_d, scales, zeros, bias, qtensor, N, K):
+        ctx.save_for_backward(input, weight_d, scales, zeros)
+        ctx.qtensor, ctx.N, ctx.K = qtensor, N, K
+        return ops.gemm_a16w4_fwd(input, weight_d, scales, zeros, None if bias is None else bias.data, N, K, GROUPSIZE)
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        input, weight_d, scales, zeros = ctx.saved_tensors
+        grad_output = grad_output.contiguous()
+        grad_input = None
+        if ctx.needs_input_grad[0]:
+            grad_input = ops.gemm_a16w4_dgrad(grad_output, weight_d, scales, zeros, ctx.N, ctx.K, GROUPSIZE)
+        q = ctx.qtensor
+        if q.grad is None:
+            q.grad = grad_output.t().mm(input)
+        else:
+            q.grad.addmm_(grad_output.t(), input)
+        return grad_input, None, None, None, None, None, None, None
+
+
 class QLinearFunctionW4_eval(torch.autograd.Function):
     """utils/quant.py:149-169."""
 
@@ -368,14 +395,32 @@ class QLinearA16W4(nn.Module):
         self.wshape = [output_features, input_features]
         self.hook_handle = None
 
-    def add_hook(self):
-        self.hook_handle = self.register_full_backward_hook(backward_hook_fn)
+    def add_hook(self, direct=False):
+        """`direct=False`: the reference's full backward hook (utils/quant.py:435-436).  `direct=True` (an extension
+        used by this package's trainer): no hook, the weight gradient is accumulated into `weight.grad` by the
+        autograd function itself."""
+        if direct:
+            self.hook_handle = "direct"
+            self._flat_qparams = None
+        else:
+            self.hook_handle = self.register_full_backward_hook(backward_hook_fn)
 
     def before_save(self):
         self.qweight.data = self.weight.data.cpu()
 
     def forward(self, x):
         out_shape = x.shape[:-1] + (self.output_features,)
+        if self.hook_handle == "direct":
+            fq = self._flat_qparams
+            if fq is None or fq[2] is not self.weight.qparam:
+                sc, zr, _ = self.weight.qparam
+                fq = self._flat_qparams = (sc.contiguous().reshape(-1), zr.contiguous().reshape(-1), self.weight.qparam)
+            x2 = x.reshape(-1, x.shape[-1])
+            if not x2.is_contiguous():
+                x2 = x2.contiguous()
+            out = QLinearFunctionW4Direct.apply(x2, self.weight.data, fq[0], fq[1], self.bias, self.weight,
+                                                self.output_features, self.input_features)
+            return out.reshape(out_shape)
         fn = QLinearFunctionW4_eval if self.hook_handle is None else QLinearFunctionW4
         out = fn.apply(x.reshape(-1, x.shape[-1]), self.weight.data, self.weight.qparam, self.bias)
         return out.reshape(out_shape)
@@ -793,14 +838,22 @@ class GradientQTensor(object):
 class MyAdam(torch.optim.Adam):
     """utils/quant.py:927-1148.  Same constructor and state layout (`state1/state2` uint8, `qmap*` = scale,
     `absmax*` = t_max per block of 2048 / 128 elements, second state holds sqrt(v)+eps).  The per-parameter
-    device synchronisation and allocator flush of the reference (:985, :1137) are not reproduced."""
+    device synchronisation and allocator flush of the reference (:985, :1137) are not reproduced.
 
-    def __init__(self, params, lr=1e-3, betas=(0.9, 0.999), obit=8, mu_updata_f=20, cpu=False):
+    `fused=True` (default, an extension): a quantized A16W4 weight with 8-bit states takes ONE kernel per step
+    (`ops.adam_a16w4_step`: same arithmetic, every intermediate rounded where the tensor ops below round it, so
+    codes / residual / states are bit-identical to the op-by-op route), and all small dense bf16 parameters of a
+    group take one launch together.  Steps that also refresh the residual-curve level (:1107-1111), parameters
+    with weight decay, CPU-resident states and every other layout use `update_step`, the op-by-op route."""
+
+    def __init__(self, params, lr=1e-3, betas=(0.9, 0.999), obit=8, mu_updata_f=20, cpu=False, fused=True):
         super().__init__(params, lr=lr, betas=betas)
         self.initialized = False
         self.obit = obit
         self.mu_updata_f = mu_updata_f
         self.statedevice = 'cpu' if cpu else 'cuda'
+        self.fused = bool(fused) and not cpu
+        self._dense_tables = {}
 
     def add_param_group(self, param_group):
         assert isinstance(param_group, dict), "param group must be a dict"
@@ -827,6 +880,7 @@ class MyAdam(torch.optim.Adam):
         if closure is not None:
             with torch.enable_grad():
                 loss = closure()
+        dense = {}
         for gindex, group in enumerate(self.param_groups):
             for pindex, p in enumerate(group["params"]):
                 if p.grad is None:
@@ -834,8 +888,70 @@ class MyAdam(torch.optim.Adam):
                 state = self.state[p]
                 if len(state) == 0:
                     self.init_state(group, p, gindex, pindex)
-                self.update_step(group, p, gindex, pindex)
+                if self.fused and self._fused_quant_ok(group, p, state):
+                    self._fused_quant_step(group, p, state)
+                elif self.fused and self._fused_dense_ok(group, p, state):
+                    dense.setdefault((gindex, state["step"]), []).append(p)
+                else:
+                    self.update_step(group, p, gindex, pindex)
+        for (gindex, _), plist in dense.items():
+            self._fused_dense_step(gindex, self.param_groups[gindex], plist)
         return loss
+
+    # ---- fused routes -----------------------------------------------------------------------------
+    def _step_size(self, group, step):
+        beta1, beta2 = group["betas"]
+        return group["lr"] * math.sqrt(1 - beta2 ** step) / (1 - beta1 ** step)
+
+    def _fused_quant_ok(self, group, p, state):
+        if not (isinstance(p, QuantTensor) and p.wbit == 4 and isinstance(p.residual, ResidualTensor)):
+            return False
+        g = p.grad
+        if not (torch.is_tensor(g) and g.is_cuda and g.is_contiguous() and g.dtype in (torch.bfloat16, torch.float32)):
+            return False
+        s1 = state["state1"]
+        if s1.dtype != torch.uint8 or not s1.is_cuda or group["weight_decay"] != 0 or p.qparam[0].dtype != g.dtype:
+            return False
+        nxt = state["step"] + 1
+        return not (nxt > 250 and nxt % self.mu_updata_f == self.mu_updata_f - 1)
+
+    def _fused_quant_step(self, group, p, state):
+        state["step"] += 1
+        beta1, beta2 = group["betas"]
+        hyper = ops.make_adam_hyper(beta1, beta2, group["eps"], self._step_size(group, state["step"]))
+        res, g = p.residual, p.grad
+        flat = getattr(p, "_flat_qparams", None)
+        if flat is None or flat[2] is not p.qparam[0]:
+            flat = p._flat_qparams = (p.qparam[0].contiguous().reshape(-1), p.qparam[1].contiguous().reshape(-1), p.qparam[0])
+        o = ops.make_opts(codec=ops.CODEC_THREEFOLD, dither=ops.DITHER_HASH, math_dtype=g.dtype, res_round_bf16=True,
+                          has_residual=not res.init, mu_enc=res.mu, mu_dec=res.lock_mu)
+        ops.adam_a16w4_step(p.data, res.residual_int.view(-1), g, flat[0], flat[1],
+                            state["state1"], state["qmap1"], state["absmax1"],
+                            state["state2"], state["qmap2"], state["absmax2"], hyper, o, GROUPSIZE)
+        res._after_set_value(flat[0].view(-1, 1))
+        p.grad = None
+
+    @staticmethod
+    def _fused_dense_ok(group, p, state):
+        if isinstance(p, (QuantTensor, FPTensor)) or not torch.is_tensor(p) or group["weight_decay"] != 0:
+            return False
+        g, s1, s2 = p.grad, state["state1"], state["state2"]
+        return (p.is_cuda and p.dtype == torch.bfloat16 and p.data.is_contiguous() and torch.is_tensor(g)
+                and g.dtype == torch.bfloat16 and g.is_cuda and g.is_contiguous() and g.shape == p.shape
+                and s1.dtype == torch.bfloat16 and s1.is_cuda and s2.dtype == torch.bfloat16 and s2.is_cuda
+                and s1.is_contiguous() and s2.is_contiguous())
+
+    def _fused_dense_step(self, gindex, group, plist):
+        step = self.state[plist[0]]["step"] + 1
+        beta1, beta2 = group["betas"]
+        hyper = ops.make_adam_hyper(beta1, beta2, group["eps"], self._step_size(group, step))
+        table = self._dense_tables.setdefault(gindex, ops.DenseAdamTable())
+        table.update([p.data for p in plist], [p.grad for p in plist],
+                     [self.state[p]["state1"] for p in plist], [self.state[p]["state2"] for p in plist])
+        ops.adam_dense_multi(table, hyper)
+        for p in plist:
+            self.state[p]["step"] = step
+            p.grad = None
 
     def get_config(self, gindex, pindex, group):
         return {"betas": group["betas"], "eps": group["eps"], "weight_decay": group["weight_decay"], "lr": group["lr"],

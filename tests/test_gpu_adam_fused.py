@@ -1,0 +1,119 @@
+"""Fused optimizer step (`lq_adam_a16w4_step`, `lq_adam_dense_multi`) against the op-by-op MyAdam.update_step route,
+which `test_gpu_module.py::test_myadam_matches_reference_steps` pins to the reference's own optimizer output.
+Bit-exact: packed codes, residual words, 8-bit states and their block parameters, dense bf16 parameters and states."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _quant_param(Q, N, K, seed):
+    from latentq_llm_b200 import ops
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    w = (torch.randn(N, K, device="cuda", generator=g) * 0.02).to(torch.bfloat16)
+    s, z = ops.find_qparams(w, 128, 15, False)
+    layer = Q.QLinearA16W4(K, N, bias=False, lbit=4, gbit=16)
+    layer.zeros.data = z.view(-1, 1).to(torch.bfloat16)
+    layer.scales.data = s.view(-1, 1).to(torch.bfloat16)
+    codes, _ = ops.a16w4_requant(w, layer.scales.data.view(-1).contiguous(), layer.zeros.data.view(-1).contiguous(),
+                                 ops.make_opts(codec=ops.CODEC_NONE, math_dtype=torch.bfloat16))
+    layer.weight.set_value(codes, [layer.scales, layer.zeros, layer.wshape])
+    layer.to("cuda")
+    return layer
+
+
+def _same_state(sa, sb):
+    for k in ("state1", "state2"):
+        assert torch.equal(sa[k], sb[k]), k
+    for k in ("qmap1", "absmax1", "qmap2", "absmax2"):
+        assert torch.equal(sa[k].reshape(-1), sb[k].reshape(-1)), k
+    assert sa["step"] == sb["step"]
+
+
+@pytest.mark.parametrize("N,K", [(512, 1024), (520, 128), (2048, 2048)])   # 2048-element blocks, 128-element blocks, larger
+def test_fused_quantized_step_is_bit_identical(N, K):
+    from latentq_llm_b200 import quant as Q
+    la, lb = _quant_param(Q, N, K, seed=5), _quant_param(Q, N, K, seed=5)
+    pa, pb = la.weight, lb.weight
+    assert torch.equal(pa.data, pb.data)
+    oa = Q.MyAdam([{"params": [pa], "weight_decay": 0.0}], lr=1e-3, betas=(0.9, 0.95), obit=8, fused=False)
+    ob = Q.MyAdam([{"params": [pb], "weight_decay": 0.0}], lr=1e-3, betas=(0.9, 0.95), obit=8, fused=True)
+    g = torch.Generator(device="cuda").manual_seed(11)
+    for t in range(5):
+        scale = 10.0 ** (-(t % 3) - 1)                         # gradients of different magnitudes
+        grad = (torch.randn(N, K, device="cuda", generator=g) * scale).to(torch.bfloat16)
+        pa.grad, pb.grad = grad.clone(), grad.clone()
+        oa.step(); ob.step()
+        assert torch.equal(pa.data.view(torch.uint8), pb.data.view(torch.uint8)), f"codes differ at step {t}"
+        assert torch.equal(pa.residual.residual_int, pb.residual.residual_int), f"residual words differ at step {t}"
+        _same_state(oa.state[pa], ob.state[pb])
+        assert pa.grad is None and pb.grad is None
+        assert pb.residual.lock_mu == pa.residual.lock_mu and not pb.residual.init
+    # the fused route ran (uint8 states were updated in place, no new tensors)
+    assert ob.state[pb]["state1"].dtype == torch.uint8 and int(ob.state[pb]["state1"].max()) > 0
+
+
+def test_fused_step_moves_codes_and_falls_back_on_curve_update_steps():
+    from latentq_llm_b200 import quant as Q
+    N, K = 512, 512
+    la, lb = _quant_param(Q, N, K, seed=2), _quant_param(Q, N, K, seed=2)
+    pa, pb = la.weight, lb.weight
+    oa = Q.MyAdam([{"params": [pa], "weight_decay": 0.0}], lr=1e-3, betas=(0.9, 0.95), obit=8, mu_updata_f=4, fused=False)
+    ob = Q.MyAdam([{"params": [pb], "weight_decay": 0.0}], lr=1e-3, betas=(0.9, 0.95), obit=8, mu_updata_f=4, fused=True)
+    g = torch.Generator(device="cuda").manual_seed(4)
+    start = pb.data.clone()
+    for t in range(3):
+        grad = (torch.randn(N, K, device="cuda", generator=g) * 1e-2).to(torch.bfloat16)
+        pa.grad, pb.grad = grad.clone(), grad.clone()
+        oa.step(); ob.step()
+    assert not torch.equal(start, pb.data)
+    # jump both optimizers past the step where the residual curve level is refreshed (step > 250, step % f == f-1)
+    oa.state[pa]["step"] = ob.state[pb]["step"] = 253
+    for t in range(3):                                          # steps 254, 255 (refresh: 255 % 4 == 3), 256
+        grad = (torch.randn(N, K, device="cuda", generator=g) * 1e-2).to(torch.bfloat16)
+        pa.grad, pb.grad = grad.clone(), grad.clone()
+        oa.step(); ob.step()
+        assert torch.equal(pa.data.view(torch.uint8), pb.data.view(torch.uint8))
+        assert torch.equal(pa.residual.residual_int, pb.residual.residual_int)
+        assert pa.residual.mu == pb.residual.mu and pa.residual.lock_mu == pb.residual.lock_mu
+    _same_state(oa.state[pa], ob.state[pb])
+
+
+def test_fused_dense_multi_is_bit_identical():
+    from latentq_llm_b200 import quant as Q
+    shapes = [(2048,), (8192,), (7,), (33, 5), (1,), (255, 255)]
+    g = torch.Generator(device="cuda").manual_seed(9)
+    A = [torch.nn.Parameter((torch.randn(*s, device="cuda", generator=g) * 0.5).to(torch.bfloat16)) for s in shapes]
+    B = [torch.nn.Parameter(a.detach().clone()) for a in A]
+    oa = Q.MyAdam([{"params": A, "weight_decay": 0.0}], lr=1e-3, betas=(0.9, 0.95), obit=8, fused=False)
+    ob = Q.MyAdam([{"params": B, "weight_decay": 0.0}], lr=1e-3, betas=(0.9, 0.95), obit=8, fused=True)
+    for t in range(6):
+        for a, b in zip(A, B):
+            gr = (torch.randn(*a.shape, device="cuda", generator=g) * 10.0 ** (-(t % 4))).to(torch.bfloat16)
+            a.grad, b.grad = gr.clone(), gr.clone()
+        oa.step(); ob.step()
+        for i, (a, b) in enumerate(zip(A, B)):
+            assert torch.equal(a.data, b.data), (t, i)
+            assert torch.equal(oa.state[a]["state1"], ob.state[b]["state1"]), (t, i)
+            assert torch.equal(oa.state[a]["state2"], ob.state[b]["state2"]), (t, i)
+            assert b.grad is None
+    assert ob._dense_tables[0].n == len(shapes)
+
+
+def test_fused_entry_point_rejects_bad_arguments():
+    from latentq_llm_b200 import _lib as L, ops
+    n = 4096
+    codes = torch.zeros(n // 2, dtype=torch.int8, device="cuda"); words = torch.zeros(n // 8, dtype=torch.int32, device="cuda")
+    grad = torch.zeros(n, dtype=torch.bfloat16, device="cuda")
+    s = torch.ones(n // 128, dtype=torch.bfloat16, device="cuda"); z = torch.zeros_like(s)
+    st = torch.zeros(n, dtype=torch.uint8, device="cuda")
+    blk = torch.zeros(n // 2048, dtype=torch.float32, device="cuda")
+    h = ops.make_adam_hyper(0.9, 0.95, 1e-8, 1e-3)
+    o = ops.make_opts(codec=ops.CODEC_NONE)                     # the fused step needs a residual codec
+    with pytest.raises(L.LatentQError) as e:
+        ops.adam_a16w4_step(codes, words, grad, s, z, st, blk, blk.clone(), st.clone(), blk.clone(), blk.clone(), h, o)
+    assert e.value.status == L.LQ_EUNSUPPORTED
+    o = ops.make_opts(math_dtype=torch.float32)                 # chain dtype must be the gradient's
+    with pytest.raises(L.LatentQError) as e:
+        ops.adam_a16w4_step(codes, words, grad, s, z, st, blk, blk.clone(), st.clone(), blk.clone(), blk.clone(), h, o)
+    assert e.value.status == L.LQ_EUNSUPPORTED

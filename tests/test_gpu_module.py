@@ -69,6 +69,32 @@ def test_a16w4_module_forward_backward_and_hook(Q):
     assert float((layer.weight.grad.float() - 2 * gw_ref).abs().max() / gw_ref.abs().max()) < 4e-2
 
 
+def test_a16w4_direct_grad_matches_hook_route(Q):
+    """The hook-free route accumulates the same dY^T·x into weight.grad (here: a preallocated arena-style view) and
+    returns the same grad-input as the reference's dict_temp + backward-hook route."""
+    N, K, T = 256, 384, 96
+    hook_layer, _ = _make_a16w4(Q, N, K, seed=3)
+    direct_layer, _ = _make_a16w4(Q, N, K, seed=3)
+    assert torch.equal(hook_layer.weight.data, direct_layer.weight.data)
+    hook_layer.add_hook()
+    direct_layer.add_hook(direct=True)
+    direct_layer.weight.grad = torch.zeros(N, K, dtype=torch.bfloat16, device="cuda")
+    arena_view = direct_layer.weight.grad
+    xs = [torch.randn(T, K, device="cuda").to(torch.bfloat16) for _ in range(2)]
+    dys = [torch.randn(T, N, device="cuda").to(torch.bfloat16) for _ in range(2)]
+    for x, dy in zip(xs, dys):
+        xa, xb = x.clone().requires_grad_(True), x.clone().requires_grad_(True)
+        ya, yb = hook_layer(xa), direct_layer(xb)
+        assert torch.equal(ya, yb)
+        ya.backward(dy); yb.backward(dy)
+        assert torch.equal(xa.grad, xb.grad)
+    assert direct_layer.weight.grad is arena_view                  # accumulated in place
+    ga, gb = hook_layer.weight.grad.float(), direct_layer.weight.grad.float()
+    # the hook route rounds each micro-batch product to bf16 before adding; the fused route rounds once
+    assert float((ga - gb).abs().max() / ga.abs().max()) < 1e-2
+    assert direct_layer.bias.grad is None and len(Q.dict_temp) == 0
+
+
 def test_myadam_matches_reference_steps(Q, golden):
     """Three optimizer steps on one A16W4 parameter (fp32 gradients, full-precision latent copy) against
     vectors produced by the reference's own MyAdam.update_step on CPU.  The reference's CPU kernels and

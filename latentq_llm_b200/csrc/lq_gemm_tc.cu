@@ -35,7 +35,6 @@ constexpr int ROW_BYTES = 128;        // one swizzle row
 constexpr int A_TILE_BYTES = TILE_R * ROW_BYTES;
 constexpr int RAW_BYTES = 4096;       // packed int4 bytes per stage (128 rows x 64 k, or 64 rows x 128 k)
 constexpr int NUM_DQ_WARPS = 16;          // 512 dequant threads, 8 packed bytes (16 weights) each per stage
-constexpr int DQ_PREFETCH = 4;            // stages of scale/zero-point prefetch held in registers
 constexpr int MAX_STAGES = 8;
 constexpr long long WAIT_BUDGET_CYCLES = 2000000000LL;   // ~1 s
 
@@ -138,6 +137,19 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
           "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
         : "r"(taddr) : "memory");
 }
+// 32 lanes x 8 consecutive 32-bit columns <- 8 registers per thread (each thread writes its own lane).
+__device__ __forceinline__ void tmem_st8(uint32_t taddr, const uint4& a, const uint4& b) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};"
+                 ::"r"(taddr), "r"(a.x), "r"(a.y), "r"(a.z), "r"(a.w), "r"(b.x), "r"(b.y), "r"(b.z), "r"(b.w) : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+// MMA whose A operand (128 rows x 16 bf16) sits in tensor memory: row r in lane r, two consecutive k per column.
+__device__ __forceinline__ void umma_ta(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 // Shared-memory matrix descriptor (sm_100 format): start address, leading / stride byte offsets (all >>4),
@@ -180,11 +192,16 @@ struct GemmParams {
 
 // RT = weight-row tiles (of 128 rows) a CTA computes against one token tile.  RT = 2 halves the token-tile
 // bytes fetched from L2 per flop (the dominant operand traffic) at the cost of a shallower pipeline.
-template <int KIND, int TN, int RT>
+// TA = the dequantised weight tile is written to tensor memory (tcgen05.st) and read by the MMA from there instead
+// of from shared memory: the 128 x 64 bf16 tile of a stage takes 32 TMEM columns, and per MMA the shared-memory
+// pipe no longer carries its 4 KB write and 4 KB read (the kernel is shared-memory-bandwidth bound otherwise).
+constexpr int TA_COLS_PER_STAGE = 32;
+template <int KIND, int TN, int RT, bool TA = false>
 struct Cfg {
     static constexpr bool I8 = KIND == KIND_I8;
     static constexpr bool W4 = !I8;
-    static constexpr int A_BYTES = RT * A_TILE_BYTES;
+    static_assert(!TA || (W4 && RT == 1), "tensor-memory A operand: A16W4 kinds, one row tile per CTA");
+    static constexpr int A_BYTES = TA ? 0 : RT * A_TILE_BYTES;
     static constexpr int B_TILE_BYTES = TN * ROW_BYTES;
     static constexpr int RAW_TOTAL = W4 ? RT * RAW_BYTES : 0;
     static constexpr int STAGE_BYTES = A_BYTES + B_TILE_BYTES + RAW_TOTAL;
@@ -192,13 +209,17 @@ struct Cfg {
     static constexpr int STAGES = STAGES_FIT > MAX_STAGES ? MAX_STAGES : STAGES_FIT;
     static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
     static constexpr int ACC_COLS = RT * TN;                               // TMEM columns of one accumulator set
-    static constexpr int ACC_BUFS = (2 * ACC_COLS <= 512) ? 2 : 1;         // double-buffered when TMEM allows
-    static constexpr int TMEM_COLS = (ACC_BUFS * ACC_COLS) < 32 ? 32 : (ACC_BUFS * ACC_COLS);
+    static constexpr int TA_COLS = TA ? STAGES * TA_COLS_PER_STAGE : 0;    // one A slot per pipeline stage
+    static constexpr int ACC_BUFS = (2 * ACC_COLS + TA_COLS <= 512) ? 2 : 1;   // double-buffered when TMEM allows
+    static constexpr int TA_COL0 = ACC_BUFS * ACC_COLS;
+    static constexpr int TMEM_NEED = ACC_BUFS * ACC_COLS + TA_COLS;
+    static constexpr int TMEM_COLS = TMEM_NEED <= 32 ? 32 : TMEM_NEED <= 64 ? 64 : TMEM_NEED <= 128 ? 128 : TMEM_NEED <= 256 ? 256 : 512;
     static constexpr int NUM_WARPS = 6 + (W4 ? NUM_DQ_WARPS : 0);
     static constexpr int THREADS = NUM_WARPS * 32;
     static constexpr uint32_t TX_BYTES = (uint32_t)(B_TILE_BYTES + (W4 ? RAW_TOTAL : A_BYTES));
     static constexpr int UMMA_PER_STAGE = 4;   // 128 bytes of contraction per stage / 32 bytes per MMA
-    static_assert(ACC_COLS <= 512 && STAGES >= 2, "tile configuration does not fit");
+    static_assert(TMEM_NEED <= 512 && STAGES >= 2, "tile configuration does not fit");
+    static_assert(!W4 || STAGES >= 4, "the four dequant teams need at least four pipeline stages");
 };
 
 struct SmemCtl {
@@ -240,10 +261,10 @@ __device__ __forceinline__ uint4 dequant8(uint32_t w, __nv_bfloat162 z128, __nv_
 // ---------------------------------------------------------------------------------------------
 // The kernel
 // ---------------------------------------------------------------------------------------------
-template <int KIND, int TN, int RT>
-__global__ void __launch_bounds__(Cfg<KIND, TN, RT>::THREADS, 1)
+template <int KIND, int TN, int RT, bool TA>
+__global__ void __launch_bounds__(Cfg<KIND, TN, RT, TA>::THREADS, 1)
 k_gemm(const __grid_constant__ CUtensorMap map_tok, const __grid_constant__ CUtensorMap map_w, const GemmParams p) {
-    using C = Cfg<KIND, TN, RT>;
+    using C = Cfg<KIND, TN, RT, TA>;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     SmemCtl* ctl = reinterpret_cast<SmemCtl*>(smem + C::STAGES * C::STAGE_BYTES);
@@ -259,7 +280,7 @@ k_gemm(const __grid_constant__ CUtensorMap map_tok, const __grid_constant__ CUte
     if (threadIdx.x == 0) {
         for (int s = 0; s < C::STAGES; ++s) {
             mbar_init(smem_u32(&ctl->full[s]), 1);
-            mbar_init(smem_u32(&ctl->a_ready[s]), NUM_DQ_WARPS);
+            mbar_init(smem_u32(&ctl->a_ready[s]), 4);   // the 4 warps of the team that converts the stage
             mbar_init(smem_u32(&ctl->empty[s]), 1);
         }
         for (int a = 0; a < 2; ++a) {
@@ -315,7 +336,7 @@ k_gemm(const __grid_constant__ CUtensorMap map_tok, const __grid_constant__ CUte
     } else if (warp == 1) {
         // ===================== MMA issuer =====================
         if (lane == 0) {
-            constexpr uint32_t IDESC = make_idesc(C::I8, KIND == KIND_DGRAD, TN);
+            constexpr uint32_t IDESC = make_idesc(C::I8, KIND == KIND_DGRAD && !TA, TN);
             int stage = 0; uint32_t phase = 0;
             int acc = 0; uint32_t acc_phase = 0;
             bool ok = true;
@@ -336,6 +357,12 @@ k_gemm(const __grid_constant__ CUtensorMap map_tok, const __grid_constant__ CUte
                     // contraction 1024 B apart (stride); one MMA consumes 16 contraction rows = 2048 B.
                     const uint64_t b_desc = make_smem_desc(b_tile(stage), 16, 1024);
                     const uint32_t a_step = (KIND == KIND_DGRAD) ? (2048u >> 4) : (32u >> 4);
+                    if (TA) {
+                        const uint32_t a_tmem = tmem_base + (uint32_t)(C::TA_COL0 + stage * TA_COLS_PER_STAGE);
+#pragma unroll
+                        for (int kk = 0; kk < C::UMMA_PER_STAGE; ++kk)
+                            umma_ta(d_tmem, a_tmem + (uint32_t)(kk * 8), b_desc + (uint64_t)(kk * 2), IDESC, (kb > kb0 || kk > 0) ? 1u : 0u);
+                    } else {
 #pragma unroll
                     for (int r = 0; r < RT; ++r) {
                         const uint64_t a_desc = (KIND == KIND_DGRAD) ? make_smem_desc(a_tile(stage, r), 8192, 1024)
@@ -345,6 +372,7 @@ k_gemm(const __grid_constant__ CUtensorMap map_tok, const __grid_constant__ CUte
                             umma<C::I8>(d_tmem + (uint32_t)(r * TN), a_desc + (uint64_t)(kk * a_step), b_desc + (uint64_t)(kk * 2),
                                         IDESC, (kb > kb0 || kk > 0) ? 1u : 0u);
                         }
+                    }
                     }
                     umma_commit(smem_u32(&ctl->empty[stage]));
                     if (++stage == C::STAGES) { stage = 0; phase ^= 1u; }
@@ -381,6 +409,19 @@ k_gemm(const __grid_constant__ CUtensorMap map_tok, const __grid_constant__ CUte
                     uint32_t v[16];
                     tmem_ld16(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * C::ACC_COLS + rr * TN + c0), v);
                     tmem_ld_wait();
+                    if (C::W4 && p.splits == 1 && r_ok && t_tile * TN + c0 + 16 <= p.M) {
+                        // full 16-token slab of the bf16 result: one base pointer, warp-uniform row stride
+                        __nv_bfloat16* o = p.out + (size_t)(t_tile * TN + c0) * p.R + r;
+                        const size_t stride = (size_t)p.R;
+                        if (p.bias) {
+#pragma unroll
+                            for (int j = 0; j < 16; ++j) o[j * stride] = __float2bfloat16_rn(__fadd_rn(bf16r(__uint_as_float(v[j])), bias));
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 16; ++j) o[j * stride] = __float2bfloat16_rn(__uint_as_float(v[j]));
+                        }
+                        continue;
+                    }
 #pragma unroll
                     for (int j = 0; j < 16; ++j) {
                         const int t = t_tile * TN + c0 + j;
@@ -413,67 +454,157 @@ k_gemm(const __grid_constant__ CUtensorMap map_tok, const __grid_constant__ CUte
     } else {
         // ===================== dequant (A16W4) =====================
         if (C::W4) {
-            const int t = threadIdx.x - 6 * 32;          // 0..511, one 8-byte slice (16 weights) of each raw tile
-            int stage = 0; uint32_t phase = 0;
-            bool ok = true;
+            // The 16 warps form 4 teams of 4 warps; team g converts pipeline stages g, g+4, g+8, ... on its own, which
+            // keeps four stages of conversion in flight (one stage is a dependent chain: shared-memory loads, ALU work,
+            // the store of the tile and its completion fence).
+            //
+            // Tensor-memory A operand (TA): a warp may only write the TMEM lane quarter (warp id % 4); every team has
+            // one warp per quarter.
+            //   forward   : lane = weight row, the stage's 64 k -> 32 columns of that lane
+            //   grad-input: lane = k inside the 128-tile, the stage's 64 weight rows n -> 32 columns (two n per column);
+            //               lane j fetches scale / zero point of rows n_j and n_j+32, shared by shuffle
+            // Shared-memory A operand: thread tt of the team owns 32 raw bytes = 64 weights of one weight row and
+            // writes them as eight 16-byte chunks of the 128-byte-swizzled tile.
+            //   forward   : raw [128 rows][32 B]; row = tt                 -> row tt of the K-major tile
+            //   grad-input: raw [ 64 rows][64 B]; row = tt/2, half = tt%2  -> row tt/2 of MN-atom `half`
+            const int quarter = warp & 3, team = (warp - 6) >> 2;
+            const int tt = ((warp - 6) & 3) * 32 + lane;
             const int groups_per_row = p.wcols / p.group;
-            const int n_rows = (KIND == KIND_FWD) ? p.R : p.C;
-            // geometry of this thread's slice inside a raw tile
-            //   forward   : raw [128 rows][32 B]; row = t/4, 16 k at (t%4)*16   -> row `row` of the K-major tile
-            //   grad-input: raw [ 64 rows][64 B]; row = t/8, 16 k at (t%8)*16   -> row `row` of MN-atom (t%8)/4
-            const int row = (KIND == KIND_FWD) ? (t >> 2) : (t >> 3);
-            const int sub = (KIND == KIND_FWD) ? (t & 3) : (t & 7);
-            const int dst_off = (KIND == KIND_FWD) ? row * ROW_BYTES : ((sub >> 2) * 8192 + row * ROW_BYTES);
-            const int chunk0 = (sub & 3) * 2;
-            const int swz = row & 7;
+            const uint32_t ta_addr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)C::TA_COL0;
+            struct Pos { int item, kb, kb1, r_tile; };
+            auto open_item = [&](Pos& q) {
+                const int split = q.item / (p.t_tiles * p.r_tiles);
+                q.r_tile = q.item % p.r_tiles;
+                q.kb = split * p.kb_per_split;
+                q.kb1 = min(p.kb_total, q.kb + p.kb_per_split);
+            };
+            auto advance = [&](Pos& q, int n) {
+                q.kb += n;
+                while (q.item < n_items && q.kb >= q.kb1) {
+                    const int over = q.kb - q.kb1;
+                    q.item += gridDim.x;
+                    if (q.item >= n_items) break;
+                    open_item(q);
+                    q.kb += over;
+                }
+            };
+            // (scale | zero << 16) as raw bf16 bits for this thread's two 32-element slots of row tile r at position q
+            auto load_qp2 = [&](const Pos& q, int r, uint32_t& a, uint32_t& b) {
+                a = b = 0u;
+                if (q.item >= n_items) return;
+                int wrow, k0, k1;
+                if (TA && KIND == KIND_DGRAD) {            // rows n_lane and n_lane+32, one k group per warp
+                    wrow = q.kb * 64 + lane; k0 = k1 = q.r_tile * TILE_R + quarter * 32;
+                } else if (KIND == KIND_FWD) {
+                    wrow = (q.r_tile * RT + r) * TILE_R + (TA ? quarter * 32 + lane : tt); k0 = q.kb * 64; k1 = k0 + 32;
+                } else {
+                    wrow = q.kb * 64 + (tt >> 1); k0 = (q.r_tile * RT + r) * TILE_R + (tt & 1) * 64; k1 = k0 + 32;
+                }
+                const int n_rows = (KIND == KIND_FWD) ? p.R : p.C;
+                if (wrow >= n_rows || k0 >= p.wcols) return;
+                const size_t g0 = (size_t)wrow * groups_per_row + (size_t)(k0 / p.group);
+                const size_t g1 = (TA && KIND == KIND_DGRAD) ? g0 + (size_t)32 * groups_per_row
+                                                             : (size_t)wrow * groups_per_row + (size_t)(k1 / p.group);
+                const unsigned short* sp = reinterpret_cast<const unsigned short*>(p.scales);
+                const unsigned short* zp = reinterpret_cast<const unsigned short*>(p.zeros);
+                a = (uint32_t)__ldg(sp + g0) | ((uint32_t)__ldg(zp + g0) << 16);
+                b = (uint32_t)__ldg(sp + g1) | ((uint32_t)__ldg(zp + g1) << 16);
+            };
+            constexpr int PF = 2;                                          // own stages of qparam prefetch
+            Pos cur{(int)blockIdx.x, 0, 0, 0};
+            if (cur.item < n_items) { open_item(cur); advance(cur, team); }
+            Pos pre = cur;
+            uint32_t qa[PF][RT], qb[PF][RT];
+#pragma unroll
+            for (int u = 0; u < PF; ++u) {
+#pragma unroll
+                for (int r = 0; r < RT; ++r) load_qp2(pre, r, qa[u][r], qb[u][r]);
+                advance(pre, 4);
+            }
+            uint32_t cnt = (uint32_t)team;
+            bool ok = true;
             long long w_dq = 0;
             const long long t_role = prof ? clock64() : 0;
-            for (int item = blockIdx.x; ok && item < n_items; item += gridDim.x) {
-                const int r_tile = item % p.r_tiles, split = item / (p.t_tiles * p.r_tiles);
-                const int kb0 = split * p.kb_per_split, kb1 = min(p.kb_total, kb0 + p.kb_per_split);
-                // scale / zero-point of (weight row, group) for k-block kb, as raw bf16 bits (scale | zero << 16)
-                auto load_qp = [&](int kb, int r) -> uint32_t {
-                    int wrow, k_abs;
-                    if (KIND == KIND_FWD) { wrow = (r_tile * RT + r) * TILE_R + row; k_abs = kb * 64 + sub * 16; }
-                    else { wrow = kb * 64 + row; k_abs = (r_tile * RT + r) * TILE_R + sub * 16; }
-                    if (kb >= kb1 || wrow >= n_rows || k_abs >= p.wcols) return 0u;
-                    const size_t gi = (size_t)wrow * groups_per_row + (size_t)(k_abs / p.group);
-                    const uint32_t sc = __ldg(reinterpret_cast<const unsigned short*>(p.scales) + gi);
-                    const uint32_t zp = __ldg(reinterpret_cast<const unsigned short*>(p.zeros) + gi);
-                    return sc | (zp << 16);
-                };
-                uint32_t qp[DQ_PREFETCH][RT];
+            const __nv_bfloat162 c128 = __float2bfloat162_rn(128.0f);
+            while (ok && cur.item < n_items) {
 #pragma unroll
-                for (int u = 0; u < DQ_PREFETCH; ++u)
+                for (int u = 0; u < PF; ++u) {
+                    if (cur.item >= n_items) break;
+                    uint32_t ca[RT], cb[RT];
 #pragma unroll
-                    for (int r = 0; r < RT; ++r) qp[u][r] = load_qp(kb0 + u, r);
-                for (int kbb = kb0; ok && kbb < kb1; kbb += DQ_PREFETCH) {
+                    for (int r = 0; r < RT; ++r) { ca[r] = qa[u][r]; cb[r] = qb[u][r]; load_qp2(pre, r, qa[u][r], qb[u][r]); }
+                    advance(pre, 4);
+                    const int stage = (int)(cnt % (uint32_t)C::STAGES);
+                    const uint32_t phase = (cnt / (uint32_t)C::STAGES) & 1u;
+                    // This team did not take part in the stage's previous use (another team converted it), so it first
+                    // waits, like the producer, until that use has been consumed; only then is the parity of the `full`
+                    // wait unambiguous.  (Needs STAGES >= number of teams: then the stage's use before the previous one
+                    // is known to be over, because the producer had to see it retired before it could fill this team's
+                    // own previous stage.)
+                    ok = mbar_wait_t(smem_u32(&ctl->empty[stage]), phase ^ 1u, abort_flag, prof, w_dq) &&
+                         mbar_wait_t(smem_u32(&ctl->full[stage]), phase, abort_flag, prof, w_dq);
+                    ok = __all_sync(0xffffffffu, ok) != 0;                 // the TMEM store below is warp-collective
+                    if (!ok) break;
+                    if (TA && KIND == KIND_DGRAD) {
+                        const uint32_t dst = ta_addr + (uint32_t)(stage * TA_COLS_PER_STAGE);
+                        const int kk = quarter * 32 + lane;
+                        const uint8_t* rp = raw_tile(stage, 0) + (kk >> 1);
+                        const uint32_t sh = (kk & 1) ? 0u : 4u;            // even k sits in the high nibble
 #pragma unroll
-                    for (int u = 0; u < DQ_PREFETCH; ++u) {
-                        const int kb = kbb + u;
-                        if (kb >= kb1) break;
-                        uint32_t cur[RT];
+                        for (int c8 = 0; c8 < 4; ++c8) {
+                            uint32_t col[8];
 #pragma unroll
-                        for (int r = 0; r < RT; ++r) { cur[r] = qp[u][r]; qp[u][r] = load_qp(kb + DQ_PREFETCH, r); }
-                        if (!(ok = mbar_wait_t(smem_u32(&ctl->full[stage]), phase, abort_flag, prof, w_dq))) break;
+                            for (int jj = 0; jj < 8; ++jj) {
+                                const int n = (c8 * 8 + jj) * 2;           // weight rows n, n+1 of the stage
+                                const uint32_t b0 = rp[n * 64], b1 = rp[(n + 1) * 64];
+                                const uint32_t q2 = ((b0 >> sh) & 15u) | (((b1 >> sh) & 15u) << 16) | 0x43004300u;
+                                const uint32_t src = (n < 32) ? ca[0] : cb[0];
+                                const uint32_t qp0 = __shfl_sync(0xffffffffu, src, n & 31), qp1 = __shfl_sync(0xffffffffu, src, (n + 1) & 31);
+                                const __nv_bfloat162 s2 = u32_as_bf2(__byte_perm(qp0, qp1, 0x5410));
+                                const __nv_bfloat162 z128 = __hadd2_rn(u32_as_bf2(__byte_perm(qp0, qp1, 0x7632)), c128);
+                                col[jj] = bf2_as_u32(__hmul2_rn(__hsub2_rn(u32_as_bf2(q2), z128), s2));
+                            }
+                            tmem_st8(dst + (uint32_t)(c8 * 8), make_uint4(col[0], col[1], col[2], col[3]), make_uint4(col[4], col[5], col[6], col[7]));
+                        }
+                    } else {
 #pragma unroll
                         for (int r = 0; r < RT; ++r) {
-                            const float sf = __uint_as_float(cur[r] << 16), zf = __uint_as_float(cur[r] & 0xffff0000u);
-                            const __nv_bfloat162 s2 = __float2bfloat162_rn(sf);
-                            const __nv_bfloat162 z128 = __float2bfloat162_rn(zf + 128.0f);
-                            const uint2 rawv = *reinterpret_cast<const uint2*>(raw_tile(stage, r) + t * 8);
-                            uint8_t* dst = smem + stage * C::STAGE_BYTES + r * A_TILE_BYTES + dst_off;
-                            *reinterpret_cast<uint4*>(dst + (((chunk0 + 0) ^ swz) << 4)) = dequant8(rawv.x, z128, s2);
-                            *reinterpret_cast<uint4*>(dst + (((chunk0 + 1) ^ swz) << 4)) = dequant8(rawv.y, z128, s2);
+                            const __nv_bfloat162 s2a = u32_as_bf2(__byte_perm(ca[r], ca[r], 0x1010)), s2b = u32_as_bf2(__byte_perm(cb[r], cb[r], 0x1010));
+                            const __nv_bfloat162 za = __hadd2_rn(u32_as_bf2(__byte_perm(ca[r], ca[r], 0x3232)), c128);
+                            const __nv_bfloat162 zb = __hadd2_rn(u32_as_bf2(__byte_perm(cb[r], cb[r], 0x3232)), c128);
+                            const int raw_off = TA ? (quarter * 32 + lane) * 32 : tt * 32;   // dgrad: (tt/2)*64 + (tt%2)*32 == tt*32
+                            const uint4* rp = reinterpret_cast<const uint4*>(raw_tile(stage, r) + raw_off);
+                            const uint4 r0 = rp[0], r1 = rp[1];
+                            if (TA) {
+                                const uint32_t dst = ta_addr + (uint32_t)(stage * TA_COLS_PER_STAGE);
+                                tmem_st8(dst + 0, dequant8(r0.x, za, s2a), dequant8(r0.y, za, s2a));
+                                tmem_st8(dst + 8, dequant8(r0.z, za, s2a), dequant8(r0.w, za, s2a));
+                                tmem_st8(dst + 16, dequant8(r1.x, zb, s2b), dequant8(r1.y, zb, s2b));
+                                tmem_st8(dst + 24, dequant8(r1.z, zb, s2b), dequant8(r1.w, zb, s2b));
+                            } else {
+                                const int row = (KIND == KIND_FWD) ? tt : (tt >> 1);
+                                const int atom = (KIND == KIND_FWD) ? 0 : (tt & 1);
+                                uint8_t* dst = smem + stage * C::STAGE_BYTES + r * A_TILE_BYTES + atom * 8192 + row * ROW_BYTES;
+                                const int swz = row & 7;
+                                *reinterpret_cast<uint4*>(dst + ((0 ^ swz) << 4)) = dequant8(r0.x, za, s2a);
+                                *reinterpret_cast<uint4*>(dst + ((1 ^ swz) << 4)) = dequant8(r0.y, za, s2a);
+                                *reinterpret_cast<uint4*>(dst + ((2 ^ swz) << 4)) = dequant8(r0.z, za, s2a);
+                                *reinterpret_cast<uint4*>(dst + ((3 ^ swz) << 4)) = dequant8(r0.w, za, s2a);
+                                *reinterpret_cast<uint4*>(dst + ((4 ^ swz) << 4)) = dequant8(r1.x, zb, s2b);
+                                *reinterpret_cast<uint4*>(dst + ((5 ^ swz) << 4)) = dequant8(r1.y, zb, s2b);
+                                *reinterpret_cast<uint4*>(dst + ((6 ^ swz) << 4)) = dequant8(r1.z, zb, s2b);
+                                *reinterpret_cast<uint4*>(dst + ((7 ^ swz) << 4)) = dequant8(r1.w, zb, s2b);
+                            }
                         }
-                        fence_proxy_async();
-                        __syncwarp();
-                        if (lane == 0) mbar_arrive(smem_u32(&ctl->a_ready[stage]));
-                        if (++stage == C::STAGES) { stage = 0; phase ^= 1u; }
                     }
+                    if (TA) { tmem_st_wait(); tc_fence_before(); } else { fence_proxy_async(); }
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(smem_u32(&ctl->a_ready[stage]));
+                    cnt += 4u;
+                    advance(cur, 4);
                 }
             }
-            if (prof && t == 0) {
+            if (prof && warp == 6 && lane == 0) {
                 atomicAdd(&g_gemm_prof[5], (unsigned long long)w_dq); atomicAdd(&g_gemm_prof[6], (unsigned long long)(clock64() - t_role));
             }
         }
@@ -524,6 +655,18 @@ __global__ void __launch_bounds__(256) k_splitk_reduce(const GemmParams p) {
 // ---------------------------------------------------------------------------------------------
 // Host side: plan, tensor maps, launch
 // ---------------------------------------------------------------------------------------------
+// Where the dequantised weight tile is staged for the tensor core.  Forward: tensor memory (each lane is a weight
+// row, so a thread converts whole words and the MMA reads no A bytes from shared memory).  Grad-input: shared
+// memory, described MN-major (a TMEM lane would be one k, forcing a nibble-wise gather that needs about twice the
+// instructions; measured slower).  LQ_GEMM_A_OPERAND=smem|tmem forces one placement for both (A/B runs, tests);
+// read at every launch.
+static bool a_operand_in_tmem(int kind) {
+    const char* e = getenv("LQ_GEMM_A_OPERAND");
+    if (e && e[0] == 's') return false;
+    if (e && e[0] == 't') return true;
+    return kind == KIND_FWD;
+}
+
 struct Plan { int tn, rt, r_tiles, t_tiles, splits, kb_total, kb_per_split; bool skinny; };
 
 // group: quantization group size, or 0 when unknown (the skinny path needs 64, 128 or 256)
@@ -541,11 +684,7 @@ static Plan make_plan(int kind, int64_t M, int64_t N, int64_t K, int group = 128
     pl.tn = M <= 16 ? 16 : (M <= 64 ? 64 : (M <= 128 ? 128 : 256));
     pl.t_tiles = (int)((M + pl.tn - 1) / pl.tn);
     const int r_tiles1 = (int)((R + TILE_R - 1) / TILE_R);
-    // Two weight-row tiles per CTA for grad-input at large token counts: measured faster there (its dequant
-    // stage is the slower one, and sharing the token tile relieves shared-memory bandwidth); forward is faster
-    // with one tile per CTA and a double-buffered accumulator.
-    pl.rt = (kind == KIND_DGRAD && pl.tn == 256 && r_tiles1 >= 2 && (int64_t)((r_tiles1 + 1) / 2) * pl.t_tiles >= sm_count()) ? 2 : 1;
-    if (const char* e = getenv("LQ_GEMM_RT")) { int v = atoi(e); if ((v == 1 || v == 2) && pl.tn == 256) pl.rt = v; }
+    pl.rt = 1;   // the kernel template supports two weight-row tiles per CTA (RT = 2); no current plan uses it
     pl.r_tiles = (r_tiles1 + pl.rt - 1) / pl.rt;
     const int bk = (kind == KIND_I8) ? 128 : 64;
     pl.kb_total = (int)((Cc + bk - 1) / bk);
@@ -593,20 +732,20 @@ static int make_map(CUtensorMap* m, const void* base, CUtensorMapDataType dt, in
     return LQ_OK;
 }
 
-template <int KIND, int TN, int RT>
+template <int KIND, int TN, int RT, bool TA = false>
 static int launch_tn(const CUtensorMap& mt, const CUtensorMap& mw, const GemmParams& p, cudaStream_t st) {
-    using C = Cfg<KIND, TN, RT>;
+    using C = Cfg<KIND, TN, RT, TA>;
     static bool attr_done[64] = {};
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev >= 0 && dev < 64 && !attr_done[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(k_gemm<KIND, TN, RT>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
+        cudaError_t e = cudaFuncSetAttribute(k_gemm<KIND, TN, RT, TA>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
         if (e != cudaSuccess) { set_cuda_error(e, "cudaFuncSetAttribute"); return LQ_ECUDA; }
         attr_done[dev] = true;
     }
     const int items = p.r_tiles * p.t_tiles * p.splits;
     const int grid = items < sm_count() ? items : sm_count();
-    k_gemm<KIND, TN, RT><<<grid, C::THREADS, C::SMEM_BYTES, st>>>(mt, mw, p);
+    k_gemm<KIND, TN, RT, TA><<<grid, C::THREADS, C::SMEM_BYTES, st>>>(mt, mw, p);
     int rc = check_launch("k_gemm");
     if (rc) return rc;
     if (p.splits > 1) {
@@ -619,12 +758,22 @@ static int launch_tn(const CUtensorMap& mt, const CUtensorMap& mw, const GemmPar
     return rc;
 }
 template <int KIND>
+static int launch_kind_ta(int tn, const CUtensorMap& mt, const CUtensorMap& mw, const GemmParams& p, cudaStream_t st) {
+    switch (tn) {
+        case 16: return launch_tn<KIND, 16, 1, true>(mt, mw, p, st);
+        case 64: return launch_tn<KIND, 64, 1, true>(mt, mw, p, st);
+        case 128: return launch_tn<KIND, 128, 1, true>(mt, mw, p, st);
+        case 256: return launch_tn<KIND, 256, 1, true>(mt, mw, p, st);
+    }
+    return LQ_EUNSUPPORTED;
+}
+template <int KIND>
 static int launch_kind(int tn, int rt, const CUtensorMap& mt, const CUtensorMap& mw, const GemmParams& p, cudaStream_t st) {
     switch (tn) {
         case 16: return launch_tn<KIND, 16, 1>(mt, mw, p, st);
         case 64: return launch_tn<KIND, 64, 1>(mt, mw, p, st);
         case 128: return launch_tn<KIND, 128, 1>(mt, mw, p, st);
-        case 256: return rt == 2 ? launch_tn<KIND, 256, 2>(mt, mw, p, st) : launch_tn<KIND, 256, 1>(mt, mw, p, st);
+        case 256: return launch_tn<KIND, 256, 1>(mt, mw, p, st);
     }
     return LQ_EUNSUPPORTED;
 }
@@ -673,8 +822,12 @@ static int run_gemm(int kind, const void* tok, const void* w, GemmParams p, int6
     }
     if (rc) return rc;
     switch (kind) {
-        case KIND_FWD: return launch_kind<KIND_FWD>(pl.tn, pl.rt, mt, mw, p, st);
-        case KIND_DGRAD: return launch_kind<KIND_DGRAD>(pl.tn, pl.rt, mt, mw, p, st);
+        case KIND_FWD:
+            return (pl.rt == 1 && a_operand_in_tmem(kind)) ? launch_kind_ta<KIND_FWD>(pl.tn, mt, mw, p, st)
+                                                       : launch_kind<KIND_FWD>(pl.tn, pl.rt, mt, mw, p, st);
+        case KIND_DGRAD:
+            return (pl.rt == 1 && a_operand_in_tmem(kind)) ? launch_kind_ta<KIND_DGRAD>(pl.tn, mt, mw, p, st)
+                                                       : launch_kind<KIND_DGRAD>(pl.tn, pl.rt, mt, mw, p, st);
         case KIND_I8: return launch_kind<KIND_I8>(pl.tn, pl.rt, mt, mw, p, st);
     }
     return LQ_EINVAL;

@@ -369,6 +369,24 @@ ORC_API void orc_opt8_dequant(const uint8_t* q, int64_t n, int64_t block, const 
     for (int64_t i = 0; i < n; ++i) x[i] = tmax[i / block] - (float)q[i] * scale[i / block];
 }
 
+/* ---------- C.7b: the same Adam chain as torch's CUDA elementwise kernels evaluate it (utils/quant.py:1098-1105
+ * on a GPU): each op computes in fp32 and stores in the tensor dtype; `a + alpha*b` (add_), `a + alpha*(b*c)`
+ * (addcmul_) and `a + alpha*(b/c)` (addcdiv_) are single expressions that nvcc contracts to an FMA.  m: exp_avg;
+ * d: on entry v (already squared), on exit sqrt(v)+eps.                                                           */
+ORC_API void orc_adam_chain_cuda(float* p, const float* g, float* m, float* d, int64_t n, float beta1, float beta2,
+                                 float omb1, float omb2, float eps, float neg_step, int math_bf16) {
+    int bf = math_bf16;
+    for (int64_t i = 0; i < n; ++i) {
+        float ea = rnd(m[i] * beta1, bf);
+        ea = rnd(fmaf(omb1, g[i], ea), bf);
+        float v = rnd(d[i] * beta2, bf);
+        v = rnd(fmaf(omb2, g[i] * g[i], v), bf);
+        float den = rnd(rnd(sqrtf(v), bf) + eps, bf);
+        p[i] = rnd(fmaf(neg_step, ea / den, p[i]), bf);
+        m[i] = ea; d[i] = den;
+    }
+}
+
 /* ---------- a23: per-token symmetric activation quant (quant_linear.py:520-528) */
 ORC_API void orc_act_quant_per_token(const float* x, int64_t rows, int64_t cols, int math_bf16,
                                      int8_t* q, float* scale) {

@@ -117,3 +117,41 @@ def test_fused_entry_point_rejects_bad_arguments():
     with pytest.raises(L.LatentQError) as e:
         ops.adam_a16w4_step(codes, words, grad, s, z, st, blk, blk.clone(), st.clone(), blk.clone(), blk.clone(), h, o)
     assert e.value.status == L.LQ_EUNSUPPORTED
+
+
+@pytest.mark.parametrize("n_rows,K", [(32, 2048), (40, 128)])     # 2048-element and 128-element state blocks
+def test_fused_quantized_step_matches_oracle(n_rows, K):
+    """The CUDA kernel against the CPU restatement of the GPU evaluation order, two consecutive steps (the second
+    one decodes a live residual and non-trivial 8-bit states)."""
+    import numpy as np
+    import oracle as orc
+    from latentq_llm_b200 import ops
+    n = n_rows * K
+    block = 2048 if n % 2048 == 0 else 128
+    g = torch.Generator(device="cuda").manual_seed(21)
+    w = (torch.randn(n, device="cuda", generator=g) * 0.02).to(torch.bfloat16)
+    s, z = ops.find_qparams(w, 128, 15, False)
+    s, z = s.to(torch.bfloat16).contiguous(), z.to(torch.bfloat16).contiguous()
+    codes, _ = ops.a16w4_requant(w, s, z, ops.make_opts(codec=ops.CODEC_NONE, math_dtype=torch.bfloat16))
+    words = torch.zeros(n // 8, dtype=torch.int32, device="cuda")
+    st1 = torch.zeros(n, dtype=torch.uint8, device="cuda"); st2 = torch.zeros_like(st1)
+    sc1 = torch.full((n // block,), 1e-10, dtype=torch.float32, device="cuda"); sc2 = sc1.clone()
+    tm1 = torch.zeros(n // block, dtype=torch.float32, device="cuda"); tm2 = tm1.clone()
+    host = dict(codes=codes.cpu().numpy(), words=words.cpu().numpy(), st1=st1.cpu().numpy(), sc1=sc1.cpu().numpy(),
+                tm1=tm1.cpu().numpy(), st2=st2.cpu().numpy(), sc2=sc2.cpu().numpy(), tm2=tm2.cpu().numpy())
+    sf, zf = s.float().cpu().numpy(), z.float().cpu().numpy()
+    for t in (1, 2):
+        grad = (torch.randn(n, device="cuda", generator=g) * 1e-2).to(torch.bfloat16)
+        step_size = 1e-3 * (1 - 0.95 ** t) ** 0.5 / (1 - 0.9 ** t)
+        ops.adam_a16w4_step(codes, words, grad, s, z, st1, sc1, tm1, st2, sc2, tm2,
+                            ops.make_adam_hyper(0.9, 0.95, 1e-8, step_size),
+                            ops.make_opts(codec=ops.CODEC_THREEFOLD, dither=ops.DITHER_HASH, math_dtype=torch.bfloat16,
+                                          res_round_bf16=True, has_residual=(t > 1)))
+        out = orc.adam_a16w4_step(host["codes"], host["words"], grad.float().cpu().numpy(), sf, zf,
+                                  host["st1"], host["sc1"], host["tm1"], host["st2"], host["sc2"], host["tm2"],
+                                  beta1=0.9, beta2=0.95, eps=1e-8, step_size=step_size, math_bf16=True,
+                                  has_residual=(t > 1))
+        host = dict(zip(("codes", "words", "st1", "sc1", "tm1", "st2", "sc2", "tm2"), out))
+        for name, dev in (("codes", codes), ("words", words), ("st1", st1), ("sc1", sc1), ("tm1", tm1),
+                          ("st2", st2), ("sc2", sc2), ("tm2", tm2)):
+            assert np.array_equal(dev.cpu().numpy().ravel(), np.asarray(host[name]).ravel()), (t, name)

@@ -27,6 +27,13 @@ def _no_device_timeout():
     assert _lib.lib.lq_gemm_device_status(1) == 0, "a bounded device-side wait expired"
 
 
+@pytest.fixture(params=["tmem", "smem"])
+def a_operand(request, monkeypatch):
+    """Where the dequantised weight tile lives for the MMA: tensor memory (default) or shared memory."""
+    monkeypatch.setenv("LQ_GEMM_A_OPERAND", request.param)
+    return request.param
+
+
 def make_w4_layer(ops, N, K, seed, group=128):
     g = torch.Generator(device="cuda").manual_seed(seed)
     w = (torch.randn(N, K, device="cuda", generator=g) * 0.02).to(torch.bfloat16)
@@ -42,7 +49,7 @@ def rel_err(got, ref):
 
 
 @pytest.mark.parametrize("M,N,K", [(1, 128, 128), (16, 256, 512), (33, 192, 384), (128, 128, 256), (200, 320, 1024)])
-def test_a16w4_fwd_small_vs_oracle(ops, M, N, K):
+def test_a16w4_fwd_small_vs_oracle(ops, a_operand, M, N, K):
     codes, sb, zb = make_w4_layer(ops, N, K, seed=M + N)
     g = torch.Generator(device="cuda").manual_seed(5)
     x = torch.randn(M, K, device="cuda", generator=g).to(torch.bfloat16)
@@ -55,7 +62,7 @@ def test_a16w4_fwd_small_vs_oracle(ops, M, N, K):
 
 
 @pytest.mark.parametrize("M,N,K", [(1, 128, 128), (16, 256, 512), (33, 192, 384), (128, 128, 256), (200, 320, 1024)])
-def test_a16w4_dgrad_small_vs_oracle(ops, M, N, K):
+def test_a16w4_dgrad_small_vs_oracle(ops, a_operand, M, N, K):
     codes, sb, zb = make_w4_layer(ops, N, K, seed=M + K)
     g = torch.Generator(device="cuda").manual_seed(6)
     dy = torch.randn(M, N, device="cuda", generator=g).to(torch.bfloat16)
@@ -68,7 +75,7 @@ def test_a16w4_dgrad_small_vs_oracle(ops, M, N, K):
 
 @pytest.mark.parametrize("K,N", [(4096, 4096), (4096, 11008), (11008, 4096), (4096, 12288)])
 @pytest.mark.parametrize("M", [1, 16, 128, 512, 4096])
-def test_a16w4_llama_shapes(ops, M, K, N):
+def test_a16w4_llama_shapes(ops, a_operand, M, K, N):
     """Benchmark shapes: compare with dequantize (library kernel, itself oracle-checked) + fp32-accumulate matmul."""
     codes, sb, zb = make_w4_layer(ops, N, K, seed=1)
     W = ops.a16w4_dequant(codes, sb, zb, (N, K), torch.bfloat16)
@@ -86,6 +93,25 @@ def test_a16w4_llama_shapes(ops, M, K, N):
     # linearity in the activations: f(2x) == 2 f(x) exactly (power-of-two scaling commutes with rounding)
     y2 = ops.gemm_a16w4_fwd(x * 2, codes, sb, zb, None, N, K)
     assert torch.equal(y2, y * 2)
+
+
+@pytest.mark.parametrize("M,N,K,group", [(300, 384, 1024, 128), (4096, 4096, 4096, 128), (77, 256, 512, 64), (512, 512, 512, 32),
+                                         (1000, 2048, 2048, 256)])
+def test_a16w4_tmem_and_smem_operand_paths_agree_bitwise(ops, monkeypatch, M, N, K, group):
+    """Both placements feed the tensor core the same bf16 weights in the same order: outputs must be identical."""
+    codes, sb, zb = make_w4_layer(ops, N, K, seed=7, group=group)
+    g = torch.Generator(device="cuda").manual_seed(M)
+    x = torch.randn(M, K, device="cuda", generator=g).to(torch.bfloat16)
+    dy = torch.randn(M, N, device="cuda", generator=g).to(torch.bfloat16)
+    out = {}
+    for where in ("tmem", "smem"):
+        monkeypatch.setenv("LQ_GEMM_A_OPERAND", where)
+        out[where] = (ops.gemm_a16w4_fwd(x, codes, sb, zb, None, N, K, group), ops.gemm_a16w4_dgrad(dy, codes, sb, zb, N, K, group))
+    assert torch.equal(out["tmem"][0], out["smem"][0])
+    assert torch.equal(out["tmem"][1], out["smem"][1])
+    W = ops.a16w4_dequant(codes, sb, zb, (N, K), torch.bfloat16, group)
+    e_max, e_fro = rel_err(out["tmem"][0], x.float() @ W.float().t())
+    assert e_max < RTOL and e_fro < RTOL
 
 
 def _a8_inputs(M, N, K, seed):

@@ -675,6 +675,7 @@ static Plan make_plan(int kind, int64_t M, int64_t N, int64_t K, int group = 128
     if (kind == KIND_FWD && M <= 16 && (K % 256) == 0 && (group == 64 || group == 128 || group == 256) && !getenv("LQ_GEMM_NO_SKINNY")) {
         // decode-sized forward: bandwidth-bound register-dequant kernel (lq_gemv.cu)
         pl.skinny = true;
+        if (skinny_rows_supported(K, group) && !getenv("LQ_SKINNY_SPLIT")) { pl.splits = 1; pl.kb_per_split = (int)(K / 64); pl.kb_total = (int)(K / 64); return pl; }
         pl.kb_per_split = skinny_chunks_per_split(N, K, &pl.splits);
         pl.kb_total = (int)(K / 64);
         return pl;
@@ -798,6 +799,7 @@ static int run_gemm(int kind, const void* tok, const void* w, GemmParams p, int6
         sp.x = (const __nv_bfloat16*)tok; sp.qweight = (const uint8_t*)w; sp.scales = p.scales; sp.zeros = p.zeros;
         sp.bias = p.bias; sp.out = p.out; sp.partial = (float*)p.partial;
         sp.M = (int)M; sp.N = (int)N; sp.K = (int)K; sp.group = p.group; sp.splits = pl.splits; sp.chunks_per_split = pl.kb_per_split;
+        if (skinny_rows_supported(K, p.group) && !getenv("LQ_SKINNY_SPLIT")) return launch_skinny_rows(sp, st);
         int rc = launch_skinny_fwd(sp, st);
         if (rc || pl.splits <= 1) return rc;
         const int64_t total = (int64_t)p.M * p.R;

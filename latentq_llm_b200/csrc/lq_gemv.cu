@@ -179,6 +179,165 @@ __global__ void __launch_bounds__(SK_THREADS) k_skinny_fwd(const SkinnyParams p)
     }
 }
 
+// ---------------------------------------------------------------------------------------------
+// Row-block variant (group size 128 or 256): one CTA owns 16 weight rows over the whole K; its 8 warps split K
+// (whole quantization groups each) and their partial sums meet in shared memory in a fixed order.  No partial sums
+// in global memory, no second kernel: one launch per layer, which is what a decode step is made of.  A thread
+// reads 16 bytes (32 weights) of each of its two rows per 128-k chunk, so a row is fetched as 64 contiguous bytes
+// per warp instruction.  Tokens are read straight from global memory (a few KB, L1/L2 resident) and reordered in
+// registers to the k-order of the nibble extraction.  The loop body is straight-line code per chunk: the kernel is
+// bound by instruction issue as much as by HBM, every instruction per byte counts.
+// ---------------------------------------------------------------------------------------------
+constexpr int RB_WARPS = 8;
+constexpr int RB_CHUNK = 128;         // k per chunk
+
+// GC = chunks per quantization group (1: group 128, 2: group 256).  MT = 1 (up to 8 tokens) keeps 4 weight chunks
+// (2 rows x 16 bytes each) in flight per thread and prefetches the token fragment one chunk ahead; MT = 2 has twice
+// the token registers and runs with 2 chunks and no token prefetch instead of spilling (measured faster each way).
+template <int MT, int GC>
+__global__ void __launch_bounds__(RB_WARPS * 32, 2) k_skinny_rows(const SkinnyParams p) {
+    constexpr int RB_PF = MT == 1 ? 4 : 2;
+    constexpr bool XPF = MT == 1;
+    __shared__ float red[RB_WARPS][MT][128];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+    const int row0 = blockIdx.x * 16;
+    const int ra = min(row0 + g, p.N - 1), rb = min(row0 + g + 8, p.N - 1);        // clamped loads, guarded stores
+    const int gpr = p.K / (RB_CHUNK * GC);                                          // groups per weight row
+    const int gper = (gpr + RB_WARPS - 1) / RB_WARPS;
+    const int g_begin = min(gpr, warp * gper), n_groups = min(gpr, g_begin + gper) - g_begin;
+    const int n_chunks = n_groups * GC;
+    const uint4* wa = reinterpret_cast<const uint4*>(p.qweight + (size_t)ra * (p.K / 2) + (size_t)g_begin * GC * (RB_CHUNK / 2)) + t;
+    const uint4* wb = reinterpret_cast<const uint4*>(p.qweight + (size_t)rb * (p.K / 2) + (size_t)g_begin * GC * (RB_CHUNK / 2)) + t;
+    const unsigned short* sca = reinterpret_cast<const unsigned short*>(p.scales) + (size_t)ra * gpr + g_begin;
+    const unsigned short* scb = reinterpret_cast<const unsigned short*>(p.scales) + (size_t)rb * gpr + g_begin;
+    const unsigned short* zpa = reinterpret_cast<const unsigned short*>(p.zeros) + (size_t)ra * gpr + g_begin;
+    const unsigned short* zpb = reinterpret_cast<const unsigned short*>(p.zeros) + (size_t)rb * gpr + g_begin;
+    // this thread's 32 k of token m*8+g inside chunk 0 of the slice (4 x 16 bytes), null when the token does not exist
+    const uint4* xp[MT];
+#pragma unroll
+    for (int m = 0; m < MT; ++m)
+        xp[m] = (m * 8 + g < p.M) ? reinterpret_cast<const uint4*>(p.x + (size_t)(m * 8 + g) * p.K + (size_t)g_begin * GC * RB_CHUNK + t * 32)
+                                  : nullptr;
+
+    uint4 qa[RB_PF], qb[RB_PF];
+#pragma unroll
+    for (int u = 0; u < RB_PF; ++u) {
+        qa[u] = qb[u] = make_uint4(0, 0, 0, 0);
+        if (u < n_chunks) { qa[u] = __ldg(wa + u * 4); qb[u] = __ldg(wb + u * 4); }       // a chunk is 64 bytes = 4 uint4 per row
+    }
+    // (scale | zero << 16) of the current and the next group
+    uint32_t sz_a = 0, sz_b = 0, nx_a = 0, nx_b = 0;
+    if (n_groups > 0) {
+        sz_a = (uint32_t)__ldg(sca) | ((uint32_t)__ldg(zpa) << 16);
+        sz_b = (uint32_t)__ldg(scb) | ((uint32_t)__ldg(zpb) << 16);
+    }
+    if (n_groups > 1) {
+        nx_a = (uint32_t)__ldg(sca + 1) | ((uint32_t)__ldg(zpa + 1) << 16);
+        nx_b = (uint32_t)__ldg(scb + 1) | ((uint32_t)__ldg(zpb + 1) << 16);
+    }
+    uint4 xn[MT][4];
+#pragma unroll
+    for (int m = 0; m < MT; ++m)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) xn[m][j] = (XPF && xp[m] && n_chunks > 0) ? __ldg(xp[m] + j) : make_uint4(0, 0, 0, 0);
+
+    const uint32_t ones[4] = {0x3F803F80u, 0x3F803F80u, 0x3F803F80u, 0x3F803F80u};   // bf16 1.0
+    float tot[MT][4], acc[MT][2][4], sx[MT][4];     // two accumulator chains per token group, sx from an all-ones A
+#pragma unroll
+    for (int m = 0; m < MT; ++m)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) { tot[m][i] = acc[m][0][i] = acc[m][1][i] = sx[m][i] = 0.0f; }
+
+    int grp = 0;
+    for (int cb = 0; cb < n_chunks; cb += RB_PF) {
+#pragma unroll
+        for (int u = 0; u < RB_PF; ++u) {          // ring slot = unroll index: no runtime register indexing
+            const int c = cb + u;
+            if (c < n_chunks) {
+                const uint4 ca = qa[u], cq = qb[u];
+                if (c + RB_PF < n_chunks) { qa[u] = __ldg(wa + (c + RB_PF) * 4); qb[u] = __ldg(wb + (c + RB_PF) * 4); }
+                uint4 xc[MT][4];
+#pragma unroll
+                for (int m = 0; m < MT; ++m)
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        if (XPF) {
+                            xc[m][j] = xn[m][j];
+                            if (xp[m] && c + 1 < n_chunks) xn[m][j] = __ldg(xp[m] + (c + 1) * (RB_CHUNK * 2 / 16) + j);
+                        } else {
+                            xc[m][j] = xp[m] ? __ldg(xp[m] + c * (RB_CHUNK * 2 / 16) + j) : make_uint4(0, 0, 0, 0);
+                        }
+                    }
+                const uint32_t wsa[4] = {ca.x, ca.y, ca.z, ca.w}, wsb[4] = {cq.x, cq.y, cq.z, cq.w};
+#pragma unroll
+                for (int w = 0; w < 4; ++w) {      // one packed word = 8 k of each row = two MMA k-steps
+                    uint32_t pa[4], pb[4];
+                    extract_word(wsa[w], pa); extract_word(wsb[w], pb);
+#pragma unroll
+                    for (int m = 0; m < MT; ++m) {
+                        const uint4 v = xc[m][w];  // (k0,k1)(k2,k3)(k4,k5)(k6,k7) -> (k0,k4)(k1,k5)(k2,k6)(k3,k7)
+                        const uint32_t x0 = __byte_perm(v.x, v.z, 0x5410), x1 = __byte_perm(v.x, v.z, 0x7632);
+                        const uint32_t x2 = __byte_perm(v.y, v.w, 0x5410), x3 = __byte_perm(v.y, v.w, 0x7632);
+                        const uint32_t a0[4] = {pa[0], pb[0], pa[1], pb[1]}, a1[4] = {pa[2], pb[2], pa[3], pb[3]};
+                        mma_16816(acc[m][0], a0, x0, x1);
+                        mma_16816(acc[m][1], a1, x2, x3);
+                        mma_16816(sx[m], ones, x0, x1);
+                        mma_16816(sx[m], ones, x2, x3);
+                    }
+                }
+                if ((u + 1) % GC == 0) {
+                    // fold the group: s * (sum x (128 + q) - (128 + z) * sum x), then rotate the group parameters
+                    const float s_a = __uint_as_float(sz_a << 16), z_a = __uint_as_float(sz_a & 0xffff0000u) + 128.0f;
+                    const float s_b = __uint_as_float(sz_b << 16), z_b = __uint_as_float(sz_b & 0xffff0000u) + 128.0f;
+#pragma unroll
+                    for (int m = 0; m < MT; ++m) {
+                        const float sx0 = sx[m][0], sx1 = sx[m][1];   // tokens 2t, 2t+1 (identical in every row of the ones tile)
+                        tot[m][0] = fmaf(s_a, (acc[m][0][0] + acc[m][1][0]) - z_a * sx0, tot[m][0]);
+                        tot[m][1] = fmaf(s_a, (acc[m][0][1] + acc[m][1][1]) - z_a * sx1, tot[m][1]);
+                        tot[m][2] = fmaf(s_b, (acc[m][0][2] + acc[m][1][2]) - z_b * sx0, tot[m][2]);
+                        tot[m][3] = fmaf(s_b, (acc[m][0][3] + acc[m][1][3]) - z_b * sx1, tot[m][3]);
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) { acc[m][0][i] = acc[m][1][i] = sx[m][i] = 0.0f; }
+                    }
+                    ++grp;
+                    sz_a = nx_a; sz_b = nx_b;
+                    if (grp + 1 < n_groups) {
+                        nx_a = (uint32_t)__ldg(sca + grp + 1) | ((uint32_t)__ldg(zpa + grp + 1) << 16);
+                        nx_b = (uint32_t)__ldg(scb + grp + 1) | ((uint32_t)__ldg(zpb + grp + 1) << 16);
+                    }
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int m = 0; m < MT; ++m)
+        *reinterpret_cast<float4*>(&red[warp][m][lane * 4]) = make_float4(tot[m][0], tot[m][1], tot[m][2], tot[m][3]);
+    __syncthreads();
+    // D fragment: d0,d1 = (row g, tokens 2t, 2t+1); d2,d3 = (row g+8, same tokens)
+    for (int j = threadIdx.x; j < MT * 128; j += RB_WARPS * 32) {
+        const int m = j >> 7, idx = j & 127, ln = idx >> 2, i = idx & 3;
+        const int row = row0 + (ln >> 2) + ((i >= 2) ? 8 : 0);
+        const int tok = m * 8 + 2 * (ln & 3) + (i & 1);
+        if (row >= p.N || tok >= p.M) continue;
+        float a = 0.0f;
+#pragma unroll
+        for (int w = 0; w < RB_WARPS; ++w) a = __fadd_rn(a, red[w][m][idx]);
+        const float f = bf16r(a);
+        p.out[(size_t)tok * p.N + row] = __float2bfloat16_rn(p.bias ? __fadd_rn(f, __bfloat162float(p.bias[row])) : f);
+    }
+}
+
+bool skinny_rows_supported(int64_t K, int group) { return (group == 128 || group == 256) && K % group == 0; }
+
+int launch_skinny_rows(const SkinnyParams& p, cudaStream_t st) {
+    if (!skinny_rows_supported(p.K, p.group)) return LQ_EUNSUPPORTED;
+    const unsigned grid = (unsigned)((p.N + 15) / 16);
+    const bool g128 = p.group == 128;
+    if (p.M <= 8) { if (g128) k_skinny_rows<1, 1><<<grid, RB_WARPS * 32, 0, st>>>(p); else k_skinny_rows<1, 2><<<grid, RB_WARPS * 32, 0, st>>>(p); }
+    else { if (g128) k_skinny_rows<2, 1><<<grid, RB_WARPS * 32, 0, st>>>(p); else k_skinny_rows<2, 2><<<grid, RB_WARPS * 32, 0, st>>>(p); }
+    return check_launch("k_skinny_rows");
+}
+
 int skinny_chunks_per_split(int64_t N, int64_t K, int* splits_out) {
     const int n_blocks = (int)((N + SK_ROWS - 1) / SK_ROWS);
     const int chunks_total = (int)(K / SK_CHUNK);

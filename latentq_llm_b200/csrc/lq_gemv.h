@@ -20,5 +20,8 @@ struct SkinnyParams {
 // split-K plan of the skinny kernel: returns 64-k chunks per split and writes the number of splits
 int skinny_chunks_per_split(int64_t N, int64_t K, int* splits_out);
 int launch_skinny_fwd(const SkinnyParams& p, cudaStream_t st);
+// row-block variant: one launch, no workspace (splits / chunks_per_split / partial are ignored)
+bool skinny_rows_supported(int64_t K, int group);
+int launch_skinny_rows(const SkinnyParams& p, cudaStream_t st);
 
 }  // namespace lq

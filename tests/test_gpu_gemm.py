@@ -114,6 +114,29 @@ def test_a16w4_tmem_and_smem_operand_paths_agree_bitwise(ops, monkeypatch, M, N,
     assert e_max < RTOL and e_fro < RTOL
 
 
+@pytest.mark.parametrize("group", [64, 128, 256])
+@pytest.mark.parametrize("M,N,K", [(1, 320, 1024), (5, 4096, 2816), (8, 192, 768), (9, 1088, 2048), (16, 4096, 4096)])
+def test_a16w4_decode_sized_forward_all_routes(ops, monkeypatch, M, N, K, group):
+    """M <= 16: the row-block kernel (group 128 / 256), the split-K kernel (group 64, or forced) and the tensor-core
+    kernel (forced) against dequantize + fp32 matmul, with bias; ragged row blocks and uneven K slices included."""
+    if K % group:
+        pytest.skip("K must hold whole groups")
+    codes, sb, zb = make_w4_layer(ops, N, K, seed=3, group=group)
+    g = torch.Generator(device="cuda").manual_seed(M + N)
+    x = torch.randn(M, K, device="cuda", generator=g).to(torch.bfloat16)
+    bias = (torch.randn(N, device="cuda", generator=g) * 0.1).to(torch.bfloat16)
+    W = ops.a16w4_dequant(codes, sb, zb, (N, K), torch.bfloat16, group)
+    ref = x.float() @ W.float().t() + bias.float()
+    for env in ({}, {"LQ_SKINNY_SPLIT": "1"}, {"LQ_GEMM_NO_SKINNY": "1"}):
+        for k in ("LQ_SKINNY_SPLIT", "LQ_GEMM_NO_SKINNY"):
+            monkeypatch.delenv(k, raising=False)
+        for k, v in env.items():
+            monkeypatch.setenv(k, v)
+        y = ops.gemm_a16w4_fwd(x, codes, sb, zb, bias, N, K, group)
+        e_max, e_fro = rel_err(y, ref)
+        assert e_max < RTOL and e_fro < RTOL, (env, e_max, e_fro)
+
+
 def _a8_inputs(M, N, K, seed):
     rng = np.random.default_rng(seed)
     x = rng.standard_normal((M, K)).astype(np.float32)

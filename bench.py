@@ -177,7 +177,21 @@ def _requant_part(torch, ops, pk, out, tm, g, numel):
         cnt = ctypes.c_ulonglong(0)
         _lib.lib.lq_fold_fallback_words(1, ctypes.byref(cnt))
         out["requant_" + name]["generic_fallback_words"] = cnt.value
-    del codes, words, delta, s, z
+    del delta
+    # fused optimizer step (8-bit state decode + Adam + state re-encode + requantize in one pass): codes and residual
+    # read and written (2 x 1 B), bf16 gradient read (2 B), two uint8 states read and written (4 B) = 8 B per weight
+    n2 = numel // 4
+    grad = (torch.randn(n2, device="cuda", generator=g, dtype=torch.bfloat16) * 1e-3)
+    st1 = torch.zeros(n2, dtype=torch.uint8, device="cuda"); st2 = torch.zeros_like(st1)
+    blk = [torch.full((n2 // 2048,), 1e-10, dtype=torch.float32, device="cuda") if i % 2 == 0 else
+           torch.zeros(n2 // 2048, dtype=torch.float32, device="cuda") for i in range(4)]
+    hyper = ops.make_adam_hyper(0.9, 0.95, 1e-8, 1e-3)
+    o = ops.make_opts(codec=ops.CODEC_THREEFOLD, dither=ops.DITHER_HASH)
+    ms = tm(lambda: ops.adam_a16w4_step(codes[:n2 // 2], words[:n2 // 8], grad, s[:n2 // GROUP], z[:n2 // GROUP],
+                                        st1, blk[0], blk[1], st2, blk[2], blk[3], hyper, o))
+    gbs = (8.0 + 4.0 / GROUP + 16.0 / 2048) * n2 / ms / 1e6
+    out["adam_a16w4_fused"] = {"GB/s": round(gbs, 1), "frac_hbm": round(gbs / pk["hbm_gbs"], 3), "ms": round(ms, 3), "numel": n2}
+    del codes, words, s, z, grad, st1, st2
 
 
 def _a8w8_part(torch, ops, out, tm, g):

@@ -422,6 +422,23 @@ k_gemm(const __grid_constant__ CUtensorMap map_tok, const __grid_constant__ CUte
                         }
                         continue;
                     }
+                    if (C::I8 && p.splits == 1 && !p.acc_out && t_tile * TN + c0 + 16 <= p.M) {   // warp-uniform condition
+                        // full 16-token slab of the int8 GEMM: acc * row_scale[t] * col_scale[r] * alpha + bias
+                        const int t0 = t_tile * TN + c0;
+                        __nv_bfloat16* o = p.out + (size_t)t0 * p.R + (r_ok ? r : 0);
+                        const size_t stride = (size_t)p.R;
+                        // lane j holds the scale of token t0 + j; broadcast by shuffle (all lanes take part) instead of
+                        // 16 loads per lane
+                        const float rs_lane = (p.row_scale && lane < 16) ? __ldg(p.row_scale + t0 + lane) : 1.0f;
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) {
+                            float f = (float)(int32_t)v[j];
+                            if (p.row_scale) f = __fmul_rn(f, __shfl_sync(0xffffffffu, rs_lane, j));
+                            f = __fmul_rn(__fmul_rn(f, cs), p.alpha);
+                            if (r_ok) o[j * stride] = __float2bfloat16_rn(__fadd_rn(f, bias));
+                        }
+                        continue;
+                    }
 #pragma unroll
                     for (int j = 0; j < 16; ++j) {
                         const int t = t_tile * TN + c0 + j;

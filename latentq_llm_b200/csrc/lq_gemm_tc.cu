@@ -208,6 +208,7 @@ struct Cfg {
     static constexpr int STAGES_FIT = (226 * 1024 - 1024) / STAGE_BYTES;
     static constexpr int STAGES = STAGES_FIT > MAX_STAGES ? MAX_STAGES : STAGES_FIT;
     static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+    static_assert(SMEM_BYTES <= 227 * 1024, "shared memory budget");
     static constexpr int ACC_COLS = RT * TN;                               // TMEM columns of one accumulator set
     static constexpr int TA_COLS = TA ? STAGES * TA_COLS_PER_STAGE : 0;    // one A slot per pipeline stage
     static constexpr int ACC_BUFS = (2 * ACC_COLS + TA_COLS <= 512) ? 2 : 1;   // double-buffered when TMEM allows
@@ -404,43 +405,66 @@ k_gemm(const __grid_constant__ CUtensorMap map_tok, const __grid_constant__ CUte
                 const bool r_ok = r < p.R;
                 const float cs = (C::I8 && p.col_scale && r_ok) ? __ldg(p.col_scale + r) : 1.0f;
                 const float bias = (p.bias && r_ok) ? __bfloat162float(p.bias[r]) : 0.0f;
+                // tokens per TMEM read-out: the int8 kernel has registers to spare (6 warps) and halves the number of
+                // load-wait round trips; the A16W4 kernels run at the register cap of a 22-warp CTA
+                constexpr int SLAB = (C::I8 && TN >= 32) ? 32 : 16;
 #pragma unroll 1
-                for (int c0 = 0; c0 < TN; c0 += 16) {
-                    uint32_t v[16];
-                    tmem_ld16(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * C::ACC_COLS + rr * TN + c0), v);
+                for (int c0 = 0; c0 < TN; c0 += SLAB) {
+                    uint32_t v[SLAB];
+#pragma unroll
+                    for (int h = 0; h < SLAB / 16; ++h)
+                        tmem_ld16(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * C::ACC_COLS + rr * TN + c0 + 16 * h),
+                                  *reinterpret_cast<uint32_t(*)[16]>(&v[16 * h]));
                     tmem_ld_wait();
-                    if (C::W4 && p.splits == 1 && r_ok && t_tile * TN + c0 + 16 <= p.M) {
-                        // full 16-token slab of the bf16 result: one base pointer, warp-uniform row stride
-                        __nv_bfloat16* o = p.out + (size_t)(t_tile * TN + c0) * p.R + r;
-                        const size_t stride = (size_t)p.R;
-                        if (p.bias) {
-#pragma unroll
-                            for (int j = 0; j < 16; ++j) o[j * stride] = __float2bfloat16_rn(__fadd_rn(bf16r(__uint_as_float(v[j])), bias));
-                        } else {
-#pragma unroll
-                            for (int j = 0; j < 16; ++j) o[j * stride] = __float2bfloat16_rn(__uint_as_float(v[j]));
-                        }
-                        continue;
-                    }
-                    if (C::I8 && p.splits == 1 && !p.acc_out && t_tile * TN + c0 + 16 <= p.M) {   // warp-uniform condition
-                        // full 16-token slab of the int8 GEMM: acc * row_scale[t] * col_scale[r] * alpha + bias
+                    if (p.splits == 1 && !(C::I8 && p.acc_out) && t_tile * TN + c0 + SLAB <= p.M &&
+                        (!C::I8 || (reinterpret_cast<uintptr_t>(p.row_scale) & 15) == 0)) {       // warp-uniform condition
+                        // Full slab of SLAB tokens.  Two results per conversion instruction (the single-value conversion
+                        // issues on the slow pipe); pk[i] = bf16 results of tokens (2i, 2i+1) for this lane's row.
                         const int t0 = t_tile * TN + c0;
-                        __nv_bfloat16* o = p.out + (size_t)t0 * p.R + (r_ok ? r : 0);
-                        const size_t stride = (size_t)p.R;
-                        // lane j holds the scale of token t0 + j; broadcast by shuffle (all lanes take part) instead of
-                        // 16 loads per lane
-                        const float rs_lane = (p.row_scale && lane < 16) ? __ldg(p.row_scale + t0 + lane) : 1.0f;
+                        uint32_t pk[SLAB / 2];
+                        if (C::W4) {
 #pragma unroll
-                        for (int j = 0; j < 16; ++j) {
-                            float f = (float)(int32_t)v[j];
-                            if (p.row_scale) f = __fmul_rn(f, __shfl_sync(0xffffffffu, rs_lane, j));
-                            f = __fmul_rn(__fmul_rn(f, cs), p.alpha);
-                            if (r_ok) o[j * stride] = __float2bfloat16_rn(__fadd_rn(f, bias));
+                            for (int i = 0; i < SLAB / 2; ++i) {
+                                pk[i] = bf2_as_u32(__floats2bfloat162_rn(__uint_as_float(v[2 * i]), __uint_as_float(v[2 * i + 1])));
+                                if (p.bias)         // mm output is rounded to bf16 first, the bias is added after
+                                    pk[i] = bf2_as_u32(__floats2bfloat162_rn(__fadd_rn(__uint_as_float(pk[i] << 16), bias),
+                                                                             __fadd_rn(__uint_as_float(pk[i] & 0xffff0000u), bias)));
+                            }
+                        } else {
+                            // acc * row_scale[t] * col_scale[r] * alpha + bias; the 16 token scales are the same addresses
+                            // for every lane: four broadcast 16-byte loads
+                            float rs[SLAB];
+                            if (p.row_scale) {
+                                const float4* rp = reinterpret_cast<const float4*>(p.row_scale + t0);
+#pragma unroll
+                                for (int q = 0; q < SLAB / 4; ++q) { const float4 t4 = __ldg(rp + q); rs[4 * q] = t4.x; rs[4 * q + 1] = t4.y; rs[4 * q + 2] = t4.z; rs[4 * q + 3] = t4.w; }
+                            } else {
+#pragma unroll
+                                for (int j = 0; j < SLAB; ++j) rs[j] = 1.0f;
+                            }
+#pragma unroll
+                            for (int i = 0; i < SLAB / 2; ++i) {
+                                float f0 = (float)(int32_t)v[2 * i], f1 = (float)(int32_t)v[2 * i + 1];
+                                if (p.row_scale) { f0 = __fmul_rn(f0, rs[2 * i]); f1 = __fmul_rn(f1, rs[2 * i + 1]); }
+                                f0 = __fadd_rn(__fmul_rn(__fmul_rn(f0, cs), p.alpha), bias);
+                                f1 = __fadd_rn(__fmul_rn(__fmul_rn(f1, cs), p.alpha), bias);
+                                pk[i] = bf2_as_u32(__floats2bfloat162_rn(f0, f1));
+                            }
+                        }
+                        // (a transpose through shared memory into 16-byte stores was tried: slower than these 2-byte stores)
+                        if (r_ok) {
+                            unsigned short* o16 = reinterpret_cast<unsigned short*>(p.out + (size_t)t0 * p.R + r);
+                            const size_t stride = (size_t)p.R;
+#pragma unroll
+                            for (int i = 0; i < SLAB / 2; ++i) {
+                                o16[(2 * i) * stride] = (unsigned short)(pk[i] & 0xffffu);
+                                o16[(2 * i + 1) * stride] = (unsigned short)(pk[i] >> 16);
+                            }
                         }
                         continue;
                     }
 #pragma unroll
-                    for (int j = 0; j < 16; ++j) {
+                    for (int j = 0; j < SLAB; ++j) {
                         const int t = t_tile * TN + c0 + j;
                         if (!r_ok || t >= p.M) continue;
                         const size_t o = (size_t)t * p.R + r;

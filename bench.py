@@ -34,6 +34,13 @@ UNIT = "TFLOP/s"
 WORKLOAD = "A16W4 dequant-GEMM fwd+grad-input, Llama-2-7B linear shapes (K,N) in {(4096,4096),(4096,11008),(11008,4096),(4096,12288)}, M=4096, group 128"
 
 
+# dram__bytes_read.sum + dram__bytes_write.sum per k_gemm launch from the ncu capture summarised in
+# profiles/ncu_k_gemm_a16w4_k4096_n11008_m4096.md (a tensor-bound kernel: the figure shows there are no re-reads)
+NCU_TRAFFIC_BYTES_PER_LAUNCH = 128.4e6
+NCU_TRAFFIC_NOTE = ("ncu capture of the (K,N)=(4096,11008), M=4096 launches: forward 113.9 MB, grad-input 142.9 MB, mean 128.4 MB "
+                    "per launch against 146.8 MB algorithmic bytes of that shape")
+
+
 def step_flops(m=M_TOKENS):
     return sum(2 * 2.0 * m * n * k for (k, n) in LLAMA_SHAPES)   # fwd + dgrad
 
@@ -397,7 +404,8 @@ def run_ours(args):
                 "config": {"workload": WORKLOAD, "parallelism": "replicas only" if world > 1 else "single GPU",
                            "l2": "per-step working set ~1.1 GB of distinct buffers, larger than the 126 MB L2"},
                 "roofline": {"bound": "tensor", "achieved": round(per_gpu, 2), "peak": pk["bf16_sustained"], "unit": "TFLOP/s",
-                             "frac": round(per_gpu / pk["bf16_sustained"], 4), "traffic": None,
+                             "frac": round(per_gpu / pk["bf16_sustained"], 4), "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH,
+                             "traffic_note": NCU_TRAFFIC_NOTE,
                              "peak_source": pk["src"] + " (sustained bf16 cuBLAS figure: kernels timed inside a long step; burst "
                              + str(pk["bf16"]) + ")", "kernel": "k_gemm<A16W4 fwd/dgrad, 256 tokens>",
                              "algorithmic": "2*M*N*K flops per launch"},

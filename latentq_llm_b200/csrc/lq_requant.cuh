@@ -165,6 +165,19 @@ __device__ __forceinline__ void latent_load(const RequantParams& p, const int64_
         }
 }
 
+// What the chain computes from Z = w/scale + zero alone (A16W4, 3-fold codec, hash dither, bf16 chain):
+// round-half-even, residual, its 4-bit code and carry, clamp.  Returns code << 4 | residual nibble.  Same operations,
+// in the same order, as latent_store below performs for that configuration (it is what the fast path tabulates).
+__device__ __forceinline__ uint32_t encode_from_z_w4_hash_bf16(float Z, const Curve& enc, float v0) {
+    float qf = rne(Z);
+    const float r = rb<true>(__fsub_rn(Z, qf));
+    float carry = 0.0f;
+    const uint32_t nib = res3_encode_fast(r, hash_dither_fast(r, v0), enc, carry) & 15u;
+    qf = rb<true>(__fadd_rn(qf, carry));
+    qf = fminf(fmaxf(qf, 0.0f), 15.0f);
+    return ((f2bits(qf) & 15u) << 4) | nib;
+}
+
 // Quantize 8 latent weights to codes + residual nibbles and store both.
 template <int WBITS, int CODEC, int DITHER, bool BF>
 __device__ __forceinline__ void latent_store(const RequantParams& p, const int64_t w, const float s, const float z,

@@ -233,19 +233,14 @@ __global__ void __launch_bounds__(256) k_requant(const RequantParams p) {
 //  * words whose Z leaves (-64, 64) (weights far outside the quantization range) or is not finite take the
 //    generic path.
 // =================================================================================================
-constexpr int ENC3_TABLE_ENTRIES = 49152;               // bf16 patterns 0x0000..0xBFFF
-__device__ uint8_t g_enc3_table[4][ENC3_TABLE_ENTRIES]; // one per curve level; entry = nibble | carry << 4, 0xFF = unused
-
-__global__ void __launch_bounds__(256) k_build_enc3_table(int slot, Curve c, float v0) {
-    for (int h = blockIdx.x * blockDim.x + threadIdx.x; h < ENC3_TABLE_ENTRIES; h += gridDim.x * blockDim.x) {
-        const float x = __uint_as_float((uint32_t)h << 16);
-        uint8_t e = 0xFF;
-        if (fabsf(x) <= 0.5f) {                         // also rejects NaN patterns
-            float carry;
-            const uint32_t nib = res3_encode(x, hash_dither(x, v0), c, carry) & 15u;
-            e = (uint8_t)(nib | (carry != 0.0f ? 16u : 0u));
-        }
-        g_enc3_table[slot][h] = e;
+constexpr int ENCZ_TABLE_ENTRIES = 65536;               // every bf16 pattern of Z = w/scale + zero
+__device__ uint8_t g_encz_table[4][ENCZ_TABLE_ENTRIES]; // one per curve level; entry = final code << 4 | residual nibble
+__global__ void __launch_bounds__(256) k_build_encz_table(int slot, Curve c, float v0) {
+    for (int h = blockIdx.x * blockDim.x + threadIdx.x; h < ENCZ_TABLE_ENTRIES; h += gridDim.x * blockDim.x) {
+        const float Z = __uint_as_float((uint32_t)h << 16);
+        uint8_t e = 0;                                  // |Z| >= 64, inf, NaN: never looked up (the word takes the generic chain)
+        if (fabsf(Z) < 64.0f) e = (uint8_t)encode_from_z_w4_hash_bf16(Z, c, v0);
+        g_encz_table[slot][h] = e;
     }
 }
 
@@ -253,19 +248,19 @@ __device__ unsigned long long g_fold_fallback_words;    // words the fast path h
 
 constexpr int FAST_THREADS = 512;
 constexpr int FAST_RES_REPL = 8;                          // copies of the decode table (bank-conflict relief)
-constexpr int FAST_SMEM_BYTES = ENC3_TABLE_ENTRIES + 256 * FAST_RES_REPL * 4;
+constexpr int FAST_SMEM_BYTES = ENCZ_TABLE_ENTRIES + 256 * FAST_RES_REPL * 4;
 
 __device__ __forceinline__ uint32_t h2u(__nv_bfloat162 v) { return *reinterpret_cast<uint32_t*>(&v); }
 __device__ __forceinline__ __nv_bfloat162 u2h(uint32_t v) { return *reinterpret_cast<__nv_bfloat162*>(&v); }
 
 __global__ void __launch_bounds__(FAST_THREADS, 2) k_fold_fast(const RequantParams p, const int enc_slot) {
     extern __shared__ __align__(16) uint8_t fsm[];
-    uint8_t* enc = fsm;                                                       // [49152]
-    uint32_t* tres = reinterpret_cast<uint32_t*>(fsm + ENC3_TABLE_ENTRIES);   // [256][FAST_RES_REPL]
+    uint8_t* encz = fsm;                                                      // [65536]: Z bits -> code << 4 | nibble
+    uint32_t* tres = reinterpret_cast<uint32_t*>(fsm + ENCZ_TABLE_ENTRIES);   // [256][FAST_RES_REPL]
     {   // stage the tables
-        const uint4* src = reinterpret_cast<const uint4*>(g_enc3_table[enc_slot]);
-        uint4* dst = reinterpret_cast<uint4*>(enc);
-        for (int i = threadIdx.x; i < ENC3_TABLE_ENTRIES / 16; i += FAST_THREADS) dst[i] = __ldg(src + i);
+        const uint4* src = reinterpret_cast<const uint4*>(g_encz_table[enc_slot]);
+        uint4* dst = reinterpret_cast<uint4*>(encz);
+        for (int i = threadIdx.x; i < ENCZ_TABLE_ENTRIES / 16; i += FAST_THREADS) dst[i] = __ldg(src + i);
         for (int b = threadIdx.x; b < 256; b += FAST_THREADS) {
             // residual byte b holds two nibbles: high = even element, low = odd element; decode as the reference does
             const uint32_t lo = f32_to_bf16_bits(bf16r(res3_decode((uint32_t)b >> 4, p.dec)));
@@ -277,7 +272,7 @@ __global__ void __launch_bounds__(FAST_THREADS, 2) k_fold_fast(const RequantPara
     const uint32_t tres_lane = (threadIdx.x & (FAST_RES_REPL - 1));
     const unsigned short* scales = reinterpret_cast<const unsigned short*>(p.scales);
     const unsigned short* zeros = reinterpret_cast<const unsigned short*>(p.zeros);
-    const __nv_bfloat162 c128 = u2h(0x43004300u), c192 = u2h(0x43404340u), c0 = u2h(0u), c15 = u2h(0x41704170u);
+    const __nv_bfloat162 c128 = u2h(0x43004300u);
     const bool use_res = p.has_residual != 0;
 
     // inputs of one word; the next word's loads are issued before the current word is processed
@@ -346,39 +341,37 @@ __global__ void __launch_bounds__(FAST_THREADS, 2) k_fold_fast(const RequantPara
             atomicAdd(&g_fold_fallback_words, 1ull);
             continue;
         }
-        uint32_t tc[4], tn[4];
+        // everything after Z (rounding, residual, its code and carry, clamp) is one table byte per element:
+        // code << 4 | nibble.  ev / od gather the bytes of the even / odd elements, pair j in byte j.
+        uint32_t ev[4], od[4];
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-            const __nv_bfloat162 q = __hsub2_rn(__hadd2_rn(Z[j], c192), c192);           // round-half-even
-            const uint32_t rb2 = h2u(__hsub2_rn(Z[j], q));                            // residual pair, exact
-            const uint32_t e2 = (uint32_t)enc[rb2 & 0xffffu] | ((uint32_t)enc[rb2 >> 16] << 16);
-            const uint32_t carry = ((e2 >> 4) & 0x00010001u) * 0x3F80u;            // bf16 1.0 where the residual overflowed
-            __nv_bfloat162 qc = __hmin2(__hmax2(__hadd2_rn(q, u2h(carry)), c0), c15);
-            const uint32_t ci = h2u(__hadd2_rn(qc, c128)) & 0x000F000Fu;              // (code_even, code_odd) as integers
-            tc[j] = ci * 16u + (ci >> 16);                                         // low byte = even << 4 | odd
-            const uint32_t ni = e2 & 0x000F000Fu;
-            tn[j] = ni * 16u + (ni >> 16);
+            const uint32_t zb2 = h2u(Z[j]);
+            ev[j] = encz[zb2 & 0xffffu];
+            od[j] = encz[zb2 >> 16];
         }
-        // gather the low bytes: code byte j = pair j; residual element k sits at bits 28 - 4k, i.e. pair j in byte 3 - j
-        const uint32_t code_word = __byte_perm(__byte_perm(tc[0], tc[1], 0x4040), __byte_perm(tc[2], tc[3], 0x4040), 0x5410);
-        const uint32_t res_word = __byte_perm(__byte_perm(tn[3], tn[2], 0x4040), __byte_perm(tn[1], tn[0], 0x4040), 0x5410);
+        const uint32_t e_even = __byte_perm(__byte_perm(ev[0], ev[1], 0x4040), __byte_perm(ev[2], ev[3], 0x4040), 0x5410);
+        const uint32_t e_odd = __byte_perm(__byte_perm(od[0], od[1], 0x4040), __byte_perm(od[2], od[3], 0x4040), 0x5410);
+        // code byte j = code_even << 4 | code_odd; residual element k sits at bits 28 - 4k, i.e. pair j in byte 3 - j
+        const uint32_t code_word = (e_even & 0xF0F0F0F0u) | ((e_odd >> 4) & 0x0F0F0F0Fu);
+        const uint32_t res_word = __byte_perm(((e_even << 4) & 0xF0F0F0F0u) | (e_odd & 0x0F0F0F0Fu), 0u, 0x0123);
         reinterpret_cast<uint32_t*>(p.codes_out)[w] = code_word;
         p.words_out[w] = (int32_t)res_word;
     }
 }
 
-static std::mutex g_enc3_mutex;
+static std::mutex g_encz_mutex;
 // Builds (once per device, curve level and v0) the encode table the fast path reads.
-static int ensure_enc3_table(int mu, float v0, cudaStream_t st) {
+static int ensure_encz_table(int mu, float v0, cudaStream_t st) {
     static bool built[64][4] = {};
     static float built_v0[64][4] = {};
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return LQ_EUNSUPPORTED;
     const int slot = (mu < 0 || mu > 3) ? 0 : mu;
-    std::lock_guard<std::mutex> lock(g_enc3_mutex);
+    std::lock_guard<std::mutex> lock(g_encz_mutex);
     if (built[dev][slot] && built_v0[dev][slot] == v0) return LQ_OK;
-    k_build_enc3_table<<<96, 256, 0, st>>>(slot, curve_for_level(slot), v0);
-    int rc = check_launch("k_build_enc3_table");
+    k_build_encz_table<<<128, 256, 0, st>>>(slot, curve_for_level(slot), v0);
+    int rc = check_launch("k_build_encz_table");
     if (rc) return rc;
     // first use only: make the table visible to every stream before anyone else may read it
     cudaError_t e = cudaStreamSynchronize(st);
@@ -394,7 +387,7 @@ static bool fast_fold_eligible(const RequantParams& p, const lq_requant_opts* o)
            (p.w_in ? p.w_dtype == LQ_BF16 : (!p.delta || p.delta_dtype == LQ_BF16));
 }
 static int launch_fold_fast(const RequantParams& p, const lq_requant_opts* o, cudaStream_t st) {
-    int rc = ensure_enc3_table(o->mu_enc, o->v0, st);
+    int rc = ensure_encz_table(o->mu_enc, o->v0, st);
     if (rc) return rc;
     static bool attr_done[64] = {};
     static int per_sm[64] = {};

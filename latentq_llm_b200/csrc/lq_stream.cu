@@ -253,6 +253,9 @@ constexpr int FAST_SMEM_BYTES = ENCZ_TABLE_ENTRIES + 256 * FAST_RES_REPL * 4;
 __device__ __forceinline__ uint32_t h2u(__nv_bfloat162 v) { return *reinterpret_cast<uint32_t*>(&v); }
 __device__ __forceinline__ __nv_bfloat162 u2h(uint32_t v) { return *reinterpret_cast<__nv_bfloat162*>(&v); }
 
+// FROM_W: requantize a dense bf16 latent; otherwise codes (+ residual when USE_RES) (+ bf16 update when HAS_DELTA).
+// Compile-time variants: the runtime tests of these three cost ~1/4 of the loop's instructions.
+template <bool FROM_W, bool USE_RES, bool HAS_DELTA>
 __global__ void __launch_bounds__(FAST_THREADS, 2) k_fold_fast(const RequantParams p, const int enc_slot) {
     extern __shared__ __align__(16) uint8_t fsm[];
     uint8_t* encz = fsm;                                                      // [65536]: Z bits -> code << 4 | nibble
@@ -273,7 +276,7 @@ __global__ void __launch_bounds__(FAST_THREADS, 2) k_fold_fast(const RequantPara
     const unsigned short* scales = reinterpret_cast<const unsigned short*>(p.scales);
     const unsigned short* zeros = reinterpret_cast<const unsigned short*>(p.zeros);
     const __nv_bfloat162 c128 = u2h(0x43004300u);
-    const bool use_res = p.has_residual != 0;
+    constexpr bool use_res = USE_RES;
 
     // inputs of one word; the next word's loads are issued before the current word is processed
     struct In { uint32_t pk, rw, sb, zb; uint4 dv; };
@@ -282,12 +285,12 @@ __global__ void __launch_bounds__(FAST_THREADS, 2) k_fold_fast(const RequantPara
         in.pk = 0; in.rw = 0; in.dv = make_uint4(0, 0, 0, 0);
         const int64_t g = (w * 8) >> p.group_shift;
         in.sb = __ldg(scales + g); in.zb = __ldg(zeros + g);
-        if (p.w_in) {
+        if (FROM_W) {
             in.dv = __ldg(reinterpret_cast<const uint4*>(p.w_in) + w);
         } else {
             in.pk = __ldg(reinterpret_cast<const uint32_t*>(p.codes_in) + w);
             if (use_res) in.rw = (uint32_t)__ldg(p.words_in + w);
-            if (p.delta) in.dv = __ldg(reinterpret_cast<const uint4*>(p.delta) + w);
+            if (HAS_DELTA) in.dv = __ldg(reinterpret_cast<const uint4*>(p.delta) + w);
         }
         return in;
     };
@@ -300,7 +303,7 @@ __global__ void __launch_bounds__(FAST_THREADS, 2) k_fold_fast(const RequantPara
         if (w + stride < p.n_words) nxt = load_in(w + stride);
         const uint32_t sb = cur.sb, zb = cur.zb;
         __nv_bfloat162 lat[4];
-        if (p.w_in) {
+        if (FROM_W) {
             lat[0] = u2h(cur.dv.x); lat[1] = u2h(cur.dv.y); lat[2] = u2h(cur.dv.z); lat[3] = u2h(cur.dv.w);
         } else {
             const uint32_t pk = cur.pk, rw = cur.rw;
@@ -319,7 +322,7 @@ __global__ void __launch_bounds__(FAST_THREADS, 2) k_fold_fast(const RequantPara
                     const uint32_t b = (rw >> (24 - 8 * j)) & 0xffu;
                     v = __hadd2_rn(__hmul2_rn(u2h(tres[b * FAST_RES_REPL + tres_lane]), s2), v);
                 }
-                if (p.delta) v = __hadd2_rn(v, u2h(d[j]));
+                if (HAS_DELTA) v = __hadd2_rn(v, u2h(d[j]));
                 lat[j] = v;
             }
         }
@@ -386,23 +389,34 @@ static bool fast_fold_eligible(const RequantParams& p, const lq_requant_opts* o)
            p.group_shift >= 3 && o->mu_enc >= 0 && o->mu_enc <= 3 && o->mu_dec >= 0 && o->mu_dec <= 3 &&
            (p.w_in ? p.w_dtype == LQ_BF16 : (!p.delta || p.delta_dtype == LQ_BF16));
 }
-static int launch_fold_fast(const RequantParams& p, const lq_requant_opts* o, cudaStream_t st) {
-    int rc = ensure_encz_table(o->mu_enc, o->v0, st);
-    if (rc) return rc;
+template <bool FROM_W, bool USE_RES, bool HAS_DELTA>
+static int launch_fold_fast_v(const RequantParams& p, int slot, cudaStream_t st) {
     static bool attr_done[64] = {};
     static int per_sm[64] = {};
     int dev = 0;
     cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 64) return LQ_EUNSUPPORTED;
     if (!attr_done[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(k_fold_fast, cudaFuncAttributeMaxDynamicSharedMemorySize, FAST_SMEM_BYTES);
+        cudaError_t e = cudaFuncSetAttribute(k_fold_fast<FROM_W, USE_RES, HAS_DELTA>, cudaFuncAttributeMaxDynamicSharedMemorySize, FAST_SMEM_BYTES);
         if (e != cudaSuccess) { set_cuda_error(e, "cudaFuncSetAttribute(k_fold_fast)"); return LQ_ECUDA; }
         int n = 0;
-        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, k_fold_fast, FAST_THREADS, FAST_SMEM_BYTES) != cudaSuccess || n < 1) n = 1;
+        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, k_fold_fast<FROM_W, USE_RES, HAS_DELTA>, FAST_THREADS, FAST_SMEM_BYTES) != cudaSuccess || n < 1) n = 1;
         per_sm[dev] = n; attr_done[dev] = true;
     }
-    int grid = grid_for(p.n_words, FAST_THREADS, per_sm[dev]);
-    k_fold_fast<<<grid, FAST_THREADS, FAST_SMEM_BYTES, st>>>(p, o->mu_enc);
+    const int grid = grid_for(p.n_words, FAST_THREADS, per_sm[dev]);
+    k_fold_fast<FROM_W, USE_RES, HAS_DELTA><<<grid, FAST_THREADS, FAST_SMEM_BYTES, st>>>(p, slot);
     return check_launch("k_fold_fast");
+}
+static int launch_fold_fast(const RequantParams& p, const lq_requant_opts* o, cudaStream_t st) {
+    int rc = ensure_encz_table(o->mu_enc, o->v0, st);
+    if (rc) return rc;
+    const int slot = o->mu_enc;
+    if (p.w_in) return launch_fold_fast_v<true, false, false>(p, slot, st);
+    const bool res = p.has_residual != 0, dl = p.delta != nullptr;
+    if (res && dl) return launch_fold_fast_v<false, true, true>(p, slot, st);
+    if (res) return launch_fold_fast_v<false, true, false>(p, slot, st);
+    if (dl) return launch_fold_fast_v<false, false, true>(p, slot, st);
+    return launch_fold_fast_v<false, false, false>(p, slot, st);
 }
 
 template <int WBITS, int CODEC, int DITHER, bool BF>

@@ -244,26 +244,67 @@ __global__ void __launch_bounds__(256) k_build_encz_table(int slot, Curve c, flo
     }
 }
 
+// Philox (or any external) dither: for a given Z the outcome is a step function of the 16-bit dither value h
+// (u = h/65536 - 0.5): entry = threshold T | outcome for h < T << 16 | outcome for h >= T << 24 (outcome = code << 4 | nibble).
+// Indexed by sign and magnitude of Z for |Z| < 32 (0x4200 bf16 patterns per sign).
+constexpr int ENCP_HALF = 0x4200, ENCP_ENTRIES = 2 * ENCP_HALF;
+__device__ uint32_t g_encp_table[4][ENCP_ENTRIES];
+__device__ unsigned int g_encp_not_a_step[4];           // patterns whose outcome is not a single step in h (expected: 0)
+__global__ void __launch_bounds__(256) k_build_encp_table(int slot, Curve c) {
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < ENCP_ENTRIES; i += gridDim.x * blockDim.x) {
+        const uint32_t bits = (i < ENCP_HALF) ? (uint32_t)i : (0x8000u | (uint32_t)(i - ENCP_HALF));
+        const float Z = __uint_as_float(bits << 16);
+        auto f = [&](uint32_t h) -> uint32_t {
+            const float v = __fmaf_rn(__uint_as_float(0x4B000000u | h), 1.0f / 65536.0f, -128.5f);   // h/65536 - 0.5, exact
+            return encode_from_z_w4_dither_bf16(Z, v, c);
+        };
+        const uint32_t lo = f(0u), hi = f(65535u);
+        uint32_t T = 0u, out_lo = lo, out_hi = lo;
+        bool step_ok = true;
+        if (hi != lo) {
+            uint32_t a = 0u, b = 65535u;                 // f(a) == lo, f(b) == hi; smallest h with f(h) == hi
+            while (b - a > 1u) { const uint32_t m = (a + b) >> 1; const uint32_t fm = f(m); if (fm == lo) a = m; else { b = m; if (fm != hi) step_ok = false; } }
+            T = b; out_hi = hi;
+            // spot checks away from the threshold (a second step would show as a third value)
+            for (uint32_t h = 0u; h < 65536u; h += 4099u) { const uint32_t e = f(h); if (e != ((h >= T) ? hi : lo)) step_ok = false; }
+        } else {
+            for (uint32_t h = 0u; h < 65536u; h += 4099u) if (f(h) != lo) step_ok = false;
+        }
+        if (!step_ok) atomicAdd(&g_encp_not_a_step[slot], 1u);
+        g_encp_table[slot][i] = T | (out_lo << 16) | (out_hi << 24);
+    }
+}
+
 __device__ unsigned long long g_fold_fallback_words;    // words the fast path handed to the generic code (diagnostic)
 
 constexpr int FAST_THREADS = 512;
+constexpr int FAST_PF = 2;                                // words in flight per thread
 constexpr int FAST_RES_REPL = 8;                          // copies of the decode table (bank-conflict relief)
-constexpr int FAST_SMEM_BYTES = ENCZ_TABLE_ENTRIES + 256 * FAST_RES_REPL * 4;
+template <int DITHER> struct FastCfg {
+    static constexpr bool PX = DITHER == LQ_DITHER_PHILOX;
+    static constexpr int THREADS = PX ? 1024 : FAST_THREADS;          // the Philox table fills most of the SM's shared memory: one CTA
+    static constexpr int MIN_CTAS = PX ? 1 : 2;
+    static constexpr int TABLE_BYTES = PX ? ENCP_ENTRIES * 4 : ENCZ_TABLE_ENTRIES;
+    static constexpr int SMEM_BYTES = TABLE_BYTES + 256 * FAST_RES_REPL * 4;
+};
 
 __device__ __forceinline__ uint32_t h2u(__nv_bfloat162 v) { return *reinterpret_cast<uint32_t*>(&v); }
 __device__ __forceinline__ __nv_bfloat162 u2h(uint32_t v) { return *reinterpret_cast<__nv_bfloat162*>(&v); }
 
 // FROM_W: requantize a dense bf16 latent; otherwise codes (+ residual when USE_RES) (+ bf16 update when HAS_DELTA).
 // Compile-time variants: the runtime tests of these three cost ~1/4 of the loop's instructions.
-template <bool FROM_W, bool USE_RES, bool HAS_DELTA>
-__global__ void __launch_bounds__(FAST_THREADS, 2) k_fold_fast(const RequantParams p, const int enc_slot) {
+template <int DITHER, bool FROM_W, bool USE_RES, bool HAS_DELTA>
+__global__ void __launch_bounds__(FastCfg<DITHER>::THREADS, FastCfg<DITHER>::MIN_CTAS) k_fold_fast(const RequantParams p, const int enc_slot) {
+    using FC = FastCfg<DITHER>;
+    constexpr int FAST_THREADS = FC::THREADS;                                 // (shadows the hash-dither constant)
     extern __shared__ __align__(16) uint8_t fsm[];
-    uint8_t* encz = fsm;                                                      // [65536]: Z bits -> code << 4 | nibble
-    uint32_t* tres = reinterpret_cast<uint32_t*>(fsm + ENCZ_TABLE_ENTRIES);   // [256][FAST_RES_REPL]
+    uint8_t* encz = fsm;                                                      // hash: [65536] Z bits -> code << 4 | nibble
+    const uint32_t* encp = reinterpret_cast<const uint32_t*>(fsm);            // Philox: [ENCP_ENTRIES] threshold | outcomes
+    uint32_t* tres = reinterpret_cast<uint32_t*>(fsm + FC::TABLE_BYTES);      // [256][FAST_RES_REPL]
     {   // stage the tables
-        const uint4* src = reinterpret_cast<const uint4*>(g_encz_table[enc_slot]);
-        uint4* dst = reinterpret_cast<uint4*>(encz);
-        for (int i = threadIdx.x; i < ENCZ_TABLE_ENTRIES / 16; i += FAST_THREADS) dst[i] = __ldg(src + i);
+        const uint4* src = FC::PX ? reinterpret_cast<const uint4*>(g_encp_table[enc_slot]) : reinterpret_cast<const uint4*>(g_encz_table[enc_slot]);
+        uint4* dst = reinterpret_cast<uint4*>(fsm);
+        for (int i = threadIdx.x; i < FC::TABLE_BYTES / 16; i += FAST_THREADS) dst[i] = __ldg(src + i);
         for (int b = threadIdx.x; b < 256; b += FAST_THREADS) {
             // residual byte b holds two nibbles: high = even element, low = odd element; decode as the reference does
             const uint32_t lo = f32_to_bf16_bits(bf16r(res3_decode((uint32_t)b >> 4, p.dec)));
@@ -296,11 +337,12 @@ __global__ void __launch_bounds__(FAST_THREADS, 2) k_fold_fast(const RequantPara
     };
     const int64_t stride = (int64_t)gridDim.x * FAST_THREADS;
     int64_t w = (int64_t)blockIdx.x * FAST_THREADS + threadIdx.x;
-    In nxt;
-    if (w < p.n_words) nxt = load_in(w);
-    for (; w < p.n_words; w += stride) {
-        const In cur = nxt;
-        if (w + stride < p.n_words) nxt = load_in(w + stride);
+    // the loads of the next FAST_PF words of this thread are in flight while one is processed (ring slot = unroll index)
+    In ring[FAST_PF];
+#pragma unroll
+    for (int u = 0; u < FAST_PF; ++u)
+        if (w + u * stride < p.n_words) ring[u] = load_in(w + u * stride);
+    auto process = [&](const In& cur, const int64_t w) {
         const uint32_t sb = cur.sb, zb = cur.zb;
         __nv_bfloat162 lat[4];
         if (FROM_W) {
@@ -338,20 +380,38 @@ __global__ void __launch_bounds__(FAST_THREADS, 2) k_fold_fast(const RequantPara
         }
         // |Z| >= 64, inf or NaN anywhere in the word -> generic path (max of the magnitudes, NaN-propagating)
         const uint32_t zmax = h2u(__hmax2_nan(__hmax2_nan(__habs2(Z[0]), __habs2(Z[1])), __hmax2_nan(__habs2(Z[2]), __habs2(Z[3]))));
-        const bool bad = (((zmax & 0x7fff7fffu) + 0x3d803d80u) & 0x80008000u) != 0u || !fastdiv_ok_scale(sf);
+        // hash table: |Z| < 64 (0x4280); Philox table: |Z| < 32 (0x4200)
+        const bool bad = (((zmax & 0x7fff7fffu) + (FC::PX ? 0x3e003e00u : 0x3d803d80u)) & 0x80008000u) != 0u || !fastdiv_ok_scale(sf);
         if (__builtin_expect(bad, 0)) {
-            requant_word<4, LQ_CODEC_THREEFOLD, LQ_DITHER_HASH, true>(p, w);
+            requant_word<4, LQ_CODEC_THREEFOLD, DITHER, true>(p, w);
             atomicAdd(&g_fold_fallback_words, 1ull);
-            continue;
+            return;
         }
         // everything after Z (rounding, residual, its code and carry, clamp) is one table byte per element:
         // code << 4 | nibble.  ev / od gather the bytes of the even / odd elements, pair j in byte j.
         uint32_t ev[4], od[4];
+        if (FC::PX) {
+            // 16 dither bits per element from one Philox4x32-10 block per word: element 2j = low half of c[j], 2j+1 = high half
+            uint32_t c[4] = {(uint32_t)w, (uint32_t)((uint64_t)w >> 32), (uint32_t)p.stream_id, (uint32_t)(p.stream_id >> 32)};
+            philox4x32_10(c, (uint32_t)p.seed, (uint32_t)(p.seed >> 32));
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            const uint32_t zb2 = h2u(Z[j]);
-            ev[j] = encz[zb2 & 0xffffu];
-            od[j] = encz[zb2 >> 16];
+            for (int j = 0; j < 4; ++j) {
+                const uint32_t zb2 = h2u(Z[j]);
+                const uint32_t mag = zb2 & 0x7fff7fffu;
+                const uint32_t ie = (mag & 0xffffu) + ((zb2 >> 15) & 1u) * (uint32_t)ENCP_HALF;
+                const uint32_t io = (mag >> 16) + (zb2 >> 31) * (uint32_t)ENCP_HALF;
+                const uint32_t ee = encp[ie], eo = encp[io];
+                const uint32_t he = c[j] & 0xffffu, ho = c[j] >> 16;
+                ev[j] = __byte_perm(ee, 0u, (he >= (ee & 0xffffu)) ? 0x4443u : 0x4442u);
+                od[j] = __byte_perm(eo, 0u, (ho >= (eo & 0xffffu)) ? 0x4443u : 0x4442u);
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const uint32_t zb2 = h2u(Z[j]);
+                ev[j] = encz[zb2 & 0xffffu];
+                od[j] = encz[zb2 >> 16];
+            }
         }
         const uint32_t e_even = __byte_perm(__byte_perm(ev[0], ev[1], 0x4040), __byte_perm(ev[2], ev[3], 0x4040), 0x5410);
         const uint32_t e_odd = __byte_perm(__byte_perm(od[0], od[1], 0x4040), __byte_perm(od[2], od[3], 0x4040), 0x5410);
@@ -360,6 +420,16 @@ __global__ void __launch_bounds__(FAST_THREADS, 2) k_fold_fast(const RequantPara
         const uint32_t res_word = __byte_perm(((e_even << 4) & 0xF0F0F0F0u) | (e_odd & 0x0F0F0F0Fu), 0u, 0x0123);
         reinterpret_cast<uint32_t*>(p.codes_out)[w] = code_word;
         p.words_out[w] = (int32_t)res_word;
+    };
+    for (; w < p.n_words; w += FAST_PF * stride) {
+#pragma unroll
+        for (int u = 0; u < FAST_PF; ++u) {
+            const int64_t wu = w + u * stride;
+            if (wu >= p.n_words) break;
+            const In cur = ring[u];
+            if (wu + FAST_PF * stride < p.n_words) ring[u] = load_in(wu + FAST_PF * stride);
+            process(cur, wu);
+        }
     }
 }
 
@@ -383,40 +453,74 @@ static int ensure_encz_table(int mu, float v0, cudaStream_t st) {
     return LQ_OK;
 }
 
+// Builds (once per device and curve level) the threshold table of the Philox fast path; LQ_EUNSUPPORTED if some Z
+// pattern's outcome is not a single step in the dither value (the caller then takes the generic kernel).
+static int ensure_encp_table(int mu, cudaStream_t st) {
+    static int state[64][4] = {};       // 0 = not built, 1 = usable, 2 = built but not usable
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return LQ_EUNSUPPORTED;
+    const int slot = (mu < 0 || mu > 3) ? 0 : mu;
+    std::lock_guard<std::mutex> lock(g_encz_mutex);
+    if (state[dev][slot] == 0) {
+        unsigned int zero = 0, bad = 0;
+        cudaError_t e = cudaMemcpyToSymbolAsync(g_encp_not_a_step, &zero, sizeof(zero), slot * sizeof(unsigned int), cudaMemcpyHostToDevice, st);
+        if (e != cudaSuccess) { set_cuda_error(e, "cudaMemcpyToSymbolAsync"); return LQ_ECUDA; }
+        k_build_encp_table<<<132, 256, 0, st>>>(slot, curve_for_level(slot));
+        int rc = check_launch("k_build_encp_table");
+        if (rc) return rc;
+        e = cudaMemcpyFromSymbolAsync(&bad, g_encp_not_a_step, sizeof(bad), slot * sizeof(unsigned int), cudaMemcpyDeviceToHost, st);
+        if (e == cudaSuccess) e = cudaStreamSynchronize(st);      // first use only; also makes the table visible to every stream
+        if (e != cudaSuccess) { set_cuda_error(e, "ensure_encp_table"); return LQ_ECUDA; }
+        state[dev][slot] = bad == 0 ? 1 : 2;
+    }
+    return state[dev][slot] == 1 ? LQ_OK : LQ_EUNSUPPORTED;
+}
+
 static bool fast_fold_eligible(const RequantParams& p, const lq_requant_opts* o) {
     if (getenv("LQ_REQUANT_GENERIC")) return false;
-    return o->codec == LQ_CODEC_THREEFOLD && o->dither == LQ_DITHER_HASH && o->math_dtype == LQ_BF16 && p.qp_dtype == LQ_BF16 &&
+    return o->codec == LQ_CODEC_THREEFOLD && (o->dither == LQ_DITHER_HASH || o->dither == LQ_DITHER_PHILOX) &&
+           o->math_dtype == LQ_BF16 && p.qp_dtype == LQ_BF16 &&
            p.group_shift >= 3 && o->mu_enc >= 0 && o->mu_enc <= 3 && o->mu_dec >= 0 && o->mu_dec <= 3 &&
            (p.w_in ? p.w_dtype == LQ_BF16 : (!p.delta || p.delta_dtype == LQ_BF16));
 }
-template <bool FROM_W, bool USE_RES, bool HAS_DELTA>
+template <int DITHER, bool FROM_W, bool USE_RES, bool HAS_DELTA>
 static int launch_fold_fast_v(const RequantParams& p, int slot, cudaStream_t st) {
+    using FC = FastCfg<DITHER>;
     static bool attr_done[64] = {};
     static int per_sm[64] = {};
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev < 0 || dev >= 64) return LQ_EUNSUPPORTED;
     if (!attr_done[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(k_fold_fast<FROM_W, USE_RES, HAS_DELTA>, cudaFuncAttributeMaxDynamicSharedMemorySize, FAST_SMEM_BYTES);
+        cudaError_t e = cudaFuncSetAttribute(k_fold_fast<DITHER, FROM_W, USE_RES, HAS_DELTA>, cudaFuncAttributeMaxDynamicSharedMemorySize, FC::SMEM_BYTES);
         if (e != cudaSuccess) { set_cuda_error(e, "cudaFuncSetAttribute(k_fold_fast)"); return LQ_ECUDA; }
         int n = 0;
-        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, k_fold_fast<FROM_W, USE_RES, HAS_DELTA>, FAST_THREADS, FAST_SMEM_BYTES) != cudaSuccess || n < 1) n = 1;
+        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, k_fold_fast<DITHER, FROM_W, USE_RES, HAS_DELTA>, FC::THREADS, FC::SMEM_BYTES) != cudaSuccess || n < 1) n = 1;
         per_sm[dev] = n; attr_done[dev] = true;
     }
-    const int grid = grid_for(p.n_words, FAST_THREADS, per_sm[dev]);
-    k_fold_fast<FROM_W, USE_RES, HAS_DELTA><<<grid, FAST_THREADS, FAST_SMEM_BYTES, st>>>(p, slot);
+    const int grid = grid_for(p.n_words, FC::THREADS, per_sm[dev]);
+    k_fold_fast<DITHER, FROM_W, USE_RES, HAS_DELTA><<<grid, FC::THREADS, FC::SMEM_BYTES, st>>>(p, slot);
     return check_launch("k_fold_fast");
 }
+template <int DITHER>
+static int launch_fold_fast_d(const RequantParams& p, int slot, cudaStream_t st) {
+    if (p.w_in) return launch_fold_fast_v<DITHER, true, false, false>(p, slot, st);
+    const bool res = p.has_residual != 0, dl = p.delta != nullptr;
+    if (res && dl) return launch_fold_fast_v<DITHER, false, true, true>(p, slot, st);
+    if (res) return launch_fold_fast_v<DITHER, false, true, false>(p, slot, st);
+    if (dl) return launch_fold_fast_v<DITHER, false, false, true>(p, slot, st);
+    return launch_fold_fast_v<DITHER, false, false, false>(p, slot, st);
+}
+// LQ_EUNSUPPORTED: the caller takes the generic kernel
 static int launch_fold_fast(const RequantParams& p, const lq_requant_opts* o, cudaStream_t st) {
+    if (o->dither == LQ_DITHER_PHILOX) {
+        int rc = ensure_encp_table(o->mu_enc, st);
+        if (rc) return rc;
+        return launch_fold_fast_d<LQ_DITHER_PHILOX>(p, o->mu_enc, st);
+    }
     int rc = ensure_encz_table(o->mu_enc, o->v0, st);
     if (rc) return rc;
-    const int slot = o->mu_enc;
-    if (p.w_in) return launch_fold_fast_v<true, false, false>(p, slot, st);
-    const bool res = p.has_residual != 0, dl = p.delta != nullptr;
-    if (res && dl) return launch_fold_fast_v<false, true, true>(p, slot, st);
-    if (res) return launch_fold_fast_v<false, true, false>(p, slot, st);
-    if (dl) return launch_fold_fast_v<false, false, true>(p, slot, st);
-    return launch_fold_fast_v<false, false, false>(p, slot, st);
+    return launch_fold_fast_d<LQ_DITHER_HASH>(p, o->mu_enc, st);
 }
 
 template <int WBITS, int CODEC, int DITHER, bool BF>
@@ -438,7 +542,10 @@ static int launch_requant_bf(const RequantParams& p, bool bf, cudaStream_t st) {
 template <int WBITS>
 static int launch_requant(const RequantParams& p, const lq_requant_opts* o, cudaStream_t st) {
     { int rc_dev = ensure_device_for(p.codes_out); if (rc_dev) return rc_dev; }
-    if (WBITS == 4 && fast_fold_eligible(p, o)) return launch_fold_fast(p, o, st);
+    if (WBITS == 4 && fast_fold_eligible(p, o)) {
+        const int rc = launch_fold_fast(p, o, st);
+        if (rc != LQ_EUNSUPPORTED) return rc;
+    }
     const bool bf = o->math_dtype == LQ_BF16;
     switch (o->codec) {
         case LQ_CODEC_NONE: return launch_requant_bf<WBITS, LQ_CODEC_NONE, LQ_DITHER_HASH>(p, bf, st);

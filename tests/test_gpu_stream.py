@@ -270,10 +270,12 @@ def test_empty_and_bad_inputs(ops):
         ops.find_qparams(torch.zeros(100, device="cuda"), 128)
 
 
-def test_fast_fold_path_equals_generic_kernel(ops, monkeypatch):
-    """The packed-bf16 / table-driven fast path of the production configuration against the generic kernel on 4M
-    weights, including weights far outside the quantization range (which the fast path hands to the generic code)
-    and every pair of curve levels."""
+@pytest.mark.parametrize("dither", ["hash", "philox"])
+def test_fast_fold_path_equals_generic_kernel(ops, monkeypatch, dither):
+    """The packed-bf16 / table-driven fast paths (hash dither: the reference's production configuration; Philox
+    dither: threshold table) against the generic kernel on 4M weights, including weights far outside the quantization
+    range (which the fast path hands to the generic code) and every pair of curve levels."""
+    DITH = ops.DITHER_HASH if dither == "hash" else ops.DITHER_PHILOX
     N, K = 2048, 2048
     g = torch.Generator(device="cuda").manual_seed(5)
     w = (torch.randn(N, K, device="cuda", generator=g) * 0.02).to(torch.bfloat16)
@@ -281,7 +283,7 @@ def test_fast_fold_path_equals_generic_kernel(ops, monkeypatch):
     sb, zb = s.to(torch.bfloat16), z.to(torch.bfloat16)
     codes0, _ = ops.a16w4_requant(w, sb, zb, ops.make_opts(codec=ops.CODEC_NONE, math_dtype=torch.bfloat16))
     delta = (torch.randn(N * K, device="cuda", generator=g) * 2e-3).to(torch.bfloat16)
-    delta[::4099] = 3.0          # |Z| far beyond 64
+    delta[::4099] = 3.0          # |Z| far beyond 64 (hash table) / 32 (Philox table)
     delta[1::7919] = -0.7
     delta[2::10007] = float("inf")
     results = {}
@@ -293,11 +295,12 @@ def test_fast_fold_path_equals_generic_kernel(ops, monkeypatch):
         c, wd = codes0.clone(), torch.zeros(N * K // 8, dtype=torch.int32, device="cuda")
         outs = []
         for step, (mu_enc, mu_dec) in enumerate([(0, 0), (1, 0), (2, 1), (3, 2), (0, 3)]):
-            o = ops.make_opts(codec=ops.CODEC_THREEFOLD, dither=ops.DITHER_HASH, has_residual=step > 0, mu_enc=mu_enc, mu_dec=mu_dec)
+            o = ops.make_opts(codec=ops.CODEC_THREEFOLD, dither=DITH, has_residual=step > 0, mu_enc=mu_enc, mu_dec=mu_dec,
+                              seed=77, step=step, param_id=9)
             ops.a16w4_fold_delta(c, wd, delta if step != 3 else None, sb, zb, o)
             outs.append((c.clone(), wd.clone()))
         # requantize-from-latent entry as well
-        o = ops.make_opts(codec=ops.CODEC_THREEFOLD, dither=ops.DITHER_HASH, mu_enc=1)
+        o = ops.make_opts(codec=ops.CODEC_THREEFOLD, dither=DITH, mu_enc=1, seed=77, step=9, param_id=9)
         outs.append(ops.a16w4_requant((w.float() + delta.view(N, K).float() * 0.1).to(torch.bfloat16), sb, zb, o))
         results[mode] = outs
     for (cf, wf), (cg, wg) in zip(results["fast"], results["generic"]):
@@ -308,7 +311,7 @@ def test_fast_fold_path_equals_generic_kernel(ops, monkeypatch):
     cnt = ctypes.c_ulonglong(0)
     monkeypatch.delenv("LQ_REQUANT_GENERIC", raising=False)
     _lib.lib.lq_fold_fallback_words(1, ctypes.byref(cnt))
-    o = ops.make_opts(codec=ops.CODEC_THREEFOLD, dither=ops.DITHER_HASH, has_residual=False)
+    o = ops.make_opts(codec=ops.CODEC_THREEFOLD, dither=DITH, has_residual=False, seed=1)
     c, wd = codes0.clone(), torch.zeros(N * K // 8, dtype=torch.int32, device="cuda")
     ops.a16w4_fold_delta(c, wd, delta, sb, zb, o)
     _lib.lib.lq_fold_fallback_words(1, ctypes.byref(cnt))

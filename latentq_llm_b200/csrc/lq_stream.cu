@@ -278,7 +278,6 @@ __global__ void __launch_bounds__(256) k_build_encp_table(int slot, Curve c) {
 __device__ unsigned long long g_fold_fallback_words;    // words the fast path handed to the generic code (diagnostic)
 
 constexpr int FAST_THREADS = 512;
-constexpr int FAST_PF = 2;                                // words in flight per thread
 constexpr int FAST_RES_REPL = 8;                          // copies of the decode table (bank-conflict relief)
 template <int DITHER> struct FastCfg {
     static constexpr bool PX = DITHER == LQ_DITHER_PHILOX;
@@ -319,117 +318,128 @@ __global__ void __launch_bounds__(FastCfg<DITHER>::THREADS, FastCfg<DITHER>::MIN
     const __nv_bfloat162 c128 = u2h(0x43004300u);
     constexpr bool use_res = USE_RES;
 
-    // inputs of one word; the next word's loads are issued before the current word is processed
-    struct In { uint32_t pk, rw, sb, zb; uint4 dv; };
-    auto load_in = [&](int64_t w) -> In {
+    // A thread handles two adjacent residual words (16 weights of one quantization group) per step: one 8-byte load
+    // each for codes and residual words, scale-derived values computed once, 32-bit indices.  The loads of the next
+    // step are in flight while the current one is processed.
+    struct In { uint2 pk, rw; uint32_t sb, zb; uint4 dv[2]; };
+    const uint32_t n_pairs = (uint32_t)(p.n_words >> 1);
+    const int gsh = p.group_shift - 4;                       // word-pair index -> group index
+    auto load_in = [&](uint32_t wp) -> In {
         In in;
-        in.pk = 0; in.rw = 0; in.dv = make_uint4(0, 0, 0, 0);
-        const int64_t g = (w * 8) >> p.group_shift;
+        in.pk = in.rw = make_uint2(0u, 0u); in.dv[0] = in.dv[1] = make_uint4(0, 0, 0, 0);
+        const uint32_t g = wp >> gsh;
         in.sb = __ldg(scales + g); in.zb = __ldg(zeros + g);
         if (FROM_W) {
-            in.dv = __ldg(reinterpret_cast<const uint4*>(p.w_in) + w);
+            in.dv[0] = __ldg(reinterpret_cast<const uint4*>(p.w_in) + 2 * (size_t)wp);
+            in.dv[1] = __ldg(reinterpret_cast<const uint4*>(p.w_in) + 2 * (size_t)wp + 1);
         } else {
-            in.pk = __ldg(reinterpret_cast<const uint32_t*>(p.codes_in) + w);
-            if (use_res) in.rw = (uint32_t)__ldg(p.words_in + w);
-            if (HAS_DELTA) in.dv = __ldg(reinterpret_cast<const uint4*>(p.delta) + w);
+            in.pk = __ldg(reinterpret_cast<const uint2*>(p.codes_in) + wp);
+            if (use_res) in.rw = __ldg(reinterpret_cast<const uint2*>(p.words_in) + wp);
+            if (HAS_DELTA) {
+                in.dv[0] = __ldg(reinterpret_cast<const uint4*>(p.delta) + 2 * (size_t)wp);
+                in.dv[1] = __ldg(reinterpret_cast<const uint4*>(p.delta) + 2 * (size_t)wp + 1);
+            }
         }
         return in;
     };
-    const int64_t stride = (int64_t)gridDim.x * FAST_THREADS;
-    int64_t w = (int64_t)blockIdx.x * FAST_THREADS + threadIdx.x;
-    // the loads of the next FAST_PF words of this thread are in flight while one is processed (ring slot = unroll index)
-    In ring[FAST_PF];
-#pragma unroll
-    for (int u = 0; u < FAST_PF; ++u)
-        if (w + u * stride < p.n_words) ring[u] = load_in(w + u * stride);
-    auto process = [&](const In& cur, const int64_t w) {
+    auto process = [&](const In& cur, const uint32_t wp) {
         const uint32_t sb = cur.sb, zb = cur.zb;
-        __nv_bfloat162 lat[4];
-        if (FROM_W) {
-            lat[0] = u2h(cur.dv.x); lat[1] = u2h(cur.dv.y); lat[2] = u2h(cur.dv.z); lat[3] = u2h(cur.dv.w);
-        } else {
-            const uint32_t pk = cur.pk, rw = cur.rw;
-            const uint32_t d[4] = {cur.dv.x, cur.dv.y, cur.dv.z, cur.dv.w};
-            const __nv_bfloat162 s2 = u2h(sb * 0x00010001u), z2 = u2h(zb * 0x00010001u);
-            const uint32_t lo_n = pk & 0x0F0F0F0Fu, hi_n = (pk >> 4) & 0x0F0F0F0Fu;   // odd / even elements, one per byte
-            // codes in element order, one per byte: (c0,c1,c2,c3) and (c4,c5,c6,c7)
-            const uint32_t c03 = __byte_perm(hi_n, lo_n, 0x5140), c47 = __byte_perm(hi_n, lo_n, 0x7362);
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                // bytes [c_even, 0x43, c_odd, 0x43]  =  bf16 pair (128 + c_even, 128 + c_odd)
-                const uint32_t pair = __byte_perm((j < 2) ? c03 : c47, 0x43434343u, (j & 1) ? 0x4342 : 0x4140);
-                __nv_bfloat162 v = __hsub2_rn(__hsub2_rn(u2h(pair), c128), z2);
-                v = __hmul2_rn(v, s2);
-                if (use_res) {
-                    const uint32_t b = (rw >> (24 - 8 * j)) & 0xffu;
-                    v = __hadd2_rn(__hmul2_rn(u2h(tres[b * FAST_RES_REPL + tres_lane]), s2), v);
-                }
-                if (HAS_DELTA) v = __hadd2_rn(v, u2h(d[j]));
-                lat[j] = v;
-            }
-        }
+        const __nv_bfloat162 s2 = u2h(sb * 0x00010001u), z2 = u2h(zb * 0x00010001u);
+        const __nv_bfloat162 z128 = __hadd2_rn(z2, c128);          // exact: zero points are integers in [0, 127]
         const float sf = __uint_as_float(sb << 16);
         const float rs = __frcp_rn(sf);
-        const __nv_bfloat162 z2 = u2h(zb * 0x00010001u);
-        __nv_bfloat162 Z[4];
+        __nv_bfloat162 Z[2][4];
+        uint32_t zmax = 0u;
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            const uint32_t lb = h2u(lat[j]);
-            const float q0 = __fmul_rn(__uint_as_float(lb << 16), rs), q1 = __fmul_rn(__uint_as_float(lb & 0xffff0000u), rs);
-            Z[j] = __hadd2_rn(__floats2bfloat162_rn(q0, q1), z2);
+        for (int h = 0; h < 2; ++h) {
+            __nv_bfloat162 lat[4];
+            const uint4 dv = cur.dv[h];
+            if (FROM_W) {
+                lat[0] = u2h(dv.x); lat[1] = u2h(dv.y); lat[2] = u2h(dv.z); lat[3] = u2h(dv.w);
+            } else {
+                const uint32_t pk = h ? cur.pk.y : cur.pk.x, rw = h ? cur.rw.y : cur.rw.x;
+                const uint32_t d[4] = {dv.x, dv.y, dv.z, dv.w};
+                const uint32_t lo_n = pk & 0x0F0F0F0Fu, hi_n = (pk >> 4) & 0x0F0F0F0Fu;   // odd / even elements, one per byte
+                // codes in element order, one per byte: (c0,c1,c2,c3) and (c4,c5,c6,c7)
+                const uint32_t c03 = __byte_perm(hi_n, lo_n, 0x5140), c47 = __byte_perm(hi_n, lo_n, 0x7362);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    // bytes [c_even, 0x43, c_odd, 0x43]  =  bf16 pair (128 + c_even, 128 + c_odd)
+                    const uint32_t pair = __byte_perm((j < 2) ? c03 : c47, 0x43434343u, (j & 1) ? 0x4342 : 0x4140);
+                    __nv_bfloat162 v = __hmul2_rn(__hsub2_rn(u2h(pair), z128), s2);
+                    if (use_res) {
+                        const uint32_t b = (rw >> (24 - 8 * j)) & 0xffu;
+                        v = __hadd2_rn(__hmul2_rn(u2h(tres[b * FAST_RES_REPL + tres_lane]), s2), v);
+                    }
+                    if (HAS_DELTA) v = __hadd2_rn(v, u2h(d[j]));
+                    lat[j] = v;
+                }
+            }
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const uint32_t lb = h2u(lat[j]);
+                const float q0 = __fmul_rn(__uint_as_float(lb << 16), rs), q1 = __fmul_rn(__uint_as_float(lb & 0xffff0000u), rs);
+                Z[h][j] = __hadd2_rn(__floats2bfloat162_rn(q0, q1), z2);
+            }
+            // max of the magnitudes of the word, NaN-propagating
+            const uint32_t zm = h2u(__hmax2_nan(__hmax2_nan(__habs2(Z[h][0]), __habs2(Z[h][1])), __hmax2_nan(__habs2(Z[h][2]), __habs2(Z[h][3]))));
+            zmax = h ? h2u(__hmax2_nan(u2h(zmax), u2h(zm))) : zm;
         }
-        // |Z| >= 64, inf or NaN anywhere in the word -> generic path (max of the magnitudes, NaN-propagating)
-        const uint32_t zmax = h2u(__hmax2_nan(__hmax2_nan(__habs2(Z[0]), __habs2(Z[1])), __hmax2_nan(__habs2(Z[2]), __habs2(Z[3]))));
-        // hash table: |Z| < 64 (0x4280); Philox table: |Z| < 32 (0x4200)
+        // |Z| beyond the table (hash: 64 = 0x4280, Philox: 32 = 0x4200), inf or NaN anywhere in the two words -> generic chain
         const bool bad = (((zmax & 0x7fff7fffu) + (FC::PX ? 0x3e003e00u : 0x3d803d80u)) & 0x80008000u) != 0u || !fastdiv_ok_scale(sf);
         if (__builtin_expect(bad, 0)) {
-            requant_word<4, LQ_CODEC_THREEFOLD, DITHER, true>(p, w);
-            atomicAdd(&g_fold_fallback_words, 1ull);
+            requant_word<4, LQ_CODEC_THREEFOLD, DITHER, true>(p, 2 * (int64_t)wp);
+            requant_word<4, LQ_CODEC_THREEFOLD, DITHER, true>(p, 2 * (int64_t)wp + 1);
+            atomicAdd(&g_fold_fallback_words, 2ull);
             return;
         }
-        // everything after Z (rounding, residual, its code and carry, clamp) is one table byte per element:
-        // code << 4 | nibble.  ev / od gather the bytes of the even / odd elements, pair j in byte j.
-        uint32_t ev[4], od[4];
-        if (FC::PX) {
-            // 16 dither bits per element from one Philox4x32-10 block per word: element 2j = low half of c[j], 2j+1 = high half
-            uint32_t c[4] = {(uint32_t)w, (uint32_t)((uint64_t)w >> 32), (uint32_t)p.stream_id, (uint32_t)(p.stream_id >> 32)};
-            philox4x32_10(c, (uint32_t)p.seed, (uint32_t)(p.seed >> 32));
+        uint32_t code_word[2], res_word[2];
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                const uint32_t zb2 = h2u(Z[j]);
-                const uint32_t mag = zb2 & 0x7fff7fffu;
-                const uint32_t ie = (mag & 0xffffu) + ((zb2 >> 15) & 1u) * (uint32_t)ENCP_HALF;
-                const uint32_t io = (mag >> 16) + (zb2 >> 31) * (uint32_t)ENCP_HALF;
-                const uint32_t ee = encp[ie], eo = encp[io];
-                const uint32_t he = c[j] & 0xffffu, ho = c[j] >> 16;
-                ev[j] = __byte_perm(ee, 0u, (he >= (ee & 0xffffu)) ? 0x4443u : 0x4442u);
-                od[j] = __byte_perm(eo, 0u, (ho >= (eo & 0xffffu)) ? 0x4443u : 0x4442u);
-            }
-        } else {
+        for (int h = 0; h < 2; ++h) {
+            // everything after Z (rounding, residual, its code and carry, clamp) is one table byte per element:
+            // code << 4 | nibble.  ev / od gather the bytes of the even / odd elements, pair j in byte j.
+            uint32_t ev[4], od[4];
+            if (FC::PX) {
+                // 16 dither bits per element from one Philox4x32-10 block per word: element 2j = low half of c[j], 2j+1 = high half
+                const uint64_t w64 = 2 * (uint64_t)wp + (uint64_t)h;
+                uint32_t c[4] = {(uint32_t)w64, (uint32_t)(w64 >> 32), (uint32_t)p.stream_id, (uint32_t)(p.stream_id >> 32)};
+                philox4x32_10(c, (uint32_t)p.seed, (uint32_t)(p.seed >> 32));
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                const uint32_t zb2 = h2u(Z[j]);
-                ev[j] = encz[zb2 & 0xffffu];
-                od[j] = encz[zb2 >> 16];
+                for (int j = 0; j < 4; ++j) {
+                    const uint32_t zb2 = h2u(Z[h][j]);
+                    const uint32_t mag = zb2 & 0x7fff7fffu;
+                    const uint32_t ie = (mag & 0xffffu) + ((zb2 >> 15) & 1u) * (uint32_t)ENCP_HALF;
+                    const uint32_t io = (mag >> 16) + (zb2 >> 31) * (uint32_t)ENCP_HALF;
+                    const uint32_t ee = encp[ie], eo = encp[io];
+                    const uint32_t he = c[j] & 0xffffu, ho = c[j] >> 16;
+                    ev[j] = __byte_perm(ee, 0u, (he >= (ee & 0xffffu)) ? 0x4443u : 0x4442u);
+                    od[j] = __byte_perm(eo, 0u, (ho >= (eo & 0xffffu)) ? 0x4443u : 0x4442u);
+                }
+            } else {
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const uint32_t zb2 = h2u(Z[h][j]);
+                    ev[j] = encz[zb2 & 0xffffu];
+                    od[j] = encz[zb2 >> 16];
+                }
             }
+            const uint32_t e_even = __byte_perm(__byte_perm(ev[0], ev[1], 0x4040), __byte_perm(ev[2], ev[3], 0x4040), 0x5410);
+            const uint32_t e_odd = __byte_perm(__byte_perm(od[0], od[1], 0x4040), __byte_perm(od[2], od[3], 0x4040), 0x5410);
+            // code byte j = code_even << 4 | code_odd; residual element k sits at bits 28 - 4k, i.e. pair j in byte 3 - j
+            code_word[h] = (e_even & 0xF0F0F0F0u) | ((e_odd >> 4) & 0x0F0F0F0Fu);
+            res_word[h] = __byte_perm(((e_even << 4) & 0xF0F0F0F0u) | (e_odd & 0x0F0F0F0Fu), 0u, 0x0123);
         }
-        const uint32_t e_even = __byte_perm(__byte_perm(ev[0], ev[1], 0x4040), __byte_perm(ev[2], ev[3], 0x4040), 0x5410);
-        const uint32_t e_odd = __byte_perm(__byte_perm(od[0], od[1], 0x4040), __byte_perm(od[2], od[3], 0x4040), 0x5410);
-        // code byte j = code_even << 4 | code_odd; residual element k sits at bits 28 - 4k, i.e. pair j in byte 3 - j
-        const uint32_t code_word = (e_even & 0xF0F0F0F0u) | ((e_odd >> 4) & 0x0F0F0F0Fu);
-        const uint32_t res_word = __byte_perm(((e_even << 4) & 0xF0F0F0F0u) | (e_odd & 0x0F0F0F0Fu), 0u, 0x0123);
-        reinterpret_cast<uint32_t*>(p.codes_out)[w] = code_word;
-        p.words_out[w] = (int32_t)res_word;
+        reinterpret_cast<uint2*>(p.codes_out)[wp] = make_uint2(code_word[0], code_word[1]);
+        reinterpret_cast<uint2*>(p.words_out)[wp] = make_uint2(res_word[0], res_word[1]);
     };
-    for (; w < p.n_words; w += FAST_PF * stride) {
-#pragma unroll
-        for (int u = 0; u < FAST_PF; ++u) {
-            const int64_t wu = w + u * stride;
-            if (wu >= p.n_words) break;
-            const In cur = ring[u];
-            if (wu + FAST_PF * stride < p.n_words) ring[u] = load_in(wu + FAST_PF * stride);
-            process(cur, wu);
-        }
+    const uint32_t stride = gridDim.x * FAST_THREADS;
+    uint32_t wp = blockIdx.x * FAST_THREADS + threadIdx.x;
+    In nxt;
+    if (wp < n_pairs) nxt = load_in(wp);
+    for (; wp < n_pairs; wp += stride) {
+        const In cur = nxt;
+        if (wp + stride < n_pairs) nxt = load_in(wp + stride);      // n_pairs < 2^30: no wrap
+        process(cur, wp);
     }
 }
 
@@ -480,7 +490,10 @@ static bool fast_fold_eligible(const RequantParams& p, const lq_requant_opts* o)
     if (getenv("LQ_REQUANT_GENERIC")) return false;
     return o->codec == LQ_CODEC_THREEFOLD && (o->dither == LQ_DITHER_HASH || o->dither == LQ_DITHER_PHILOX) &&
            o->math_dtype == LQ_BF16 && p.qp_dtype == LQ_BF16 &&
-           p.group_shift >= 3 && o->mu_enc >= 0 && o->mu_enc <= 3 && o->mu_dec >= 0 && o->mu_dec <= 3 &&
+           p.group_shift >= 4 && (p.n_words & 1) == 0 && p.n_words < ((int64_t)1 << 31) &&
+           o->mu_enc >= 0 && o->mu_enc <= 3 && o->mu_dec >= 0 && o->mu_dec <= 3 &&
+           aligned(p.codes_out, 8) && aligned(p.words_out, 8) && (p.w_in || aligned(p.codes_in, 8)) &&
+           (p.w_in || !p.has_residual || aligned(p.words_in, 8)) &&
            (p.w_in ? p.w_dtype == LQ_BF16 : (!p.delta || p.delta_dtype == LQ_BF16));
 }
 template <int DITHER, bool FROM_W, bool USE_RES, bool HAS_DELTA>
@@ -498,7 +511,7 @@ static int launch_fold_fast_v(const RequantParams& p, int slot, cudaStream_t st)
         if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, k_fold_fast<DITHER, FROM_W, USE_RES, HAS_DELTA>, FC::THREADS, FC::SMEM_BYTES) != cudaSuccess || n < 1) n = 1;
         per_sm[dev] = n; attr_done[dev] = true;
     }
-    const int grid = grid_for(p.n_words, FC::THREADS, per_sm[dev]);
+    const int grid = grid_for(p.n_words / 2, FC::THREADS, per_sm[dev]);
     k_fold_fast<DITHER, FROM_W, USE_RES, HAS_DELTA><<<grid, FC::THREADS, FC::SMEM_BYTES, st>>>(p, slot);
     return check_launch("k_fold_fast");
 }

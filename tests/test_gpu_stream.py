@@ -316,4 +316,4 @@ def test_fast_fold_path_equals_generic_kernel(ops, monkeypatch, dither):
     ops.a16w4_fold_delta(c, wd, delta, sb, zb, o)
     _lib.lib.lq_fold_fallback_words(1, ctypes.byref(cnt))
     poisoned = N * K // 4099 + N * K // 7919 + N * K // 10007 + 3
-    assert 0 < cnt.value <= poisoned, (cnt.value, poisoned)
+    assert 0 < cnt.value <= 2 * poisoned, (cnt.value, poisoned)     # a poisoned word takes its neighbour along

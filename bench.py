@@ -239,7 +239,7 @@ def _decode_part(torch, ops, pk, out, tm):
                                   "timing": "CUDA graph replay of the 4 layers"}
 
 
-def finetune_measurement(torch, arch="opt-1.3b", steps=2, warmup=1, micro_batch=4, seq=512, grad_accum=8):
+def finetune_measurement(torch, arch="opt-1.3b", steps=2, warmup=1, micro_batch=4, seq=512, grad_accum=8, cuda_graph=True):
     """Latent fine-tune step (BASELINE config 4): A16W4 int4 group-128 latent weights, seq 512, micro-batch 4,
     grad-accum 8 per rank, uniform random token ids, data-parallel over the ranks of this launch with one bf16
     gradient all-reduce per optimizer step.  tokens/s = world * micro_batch * seq * grad_accum / step time.
@@ -251,7 +251,7 @@ def finetune_measurement(torch, arch="opt-1.3b", steps=2, warmup=1, micro_batch=
     model = ft.build_model(arch, "cuda", seed=1234)
     ft.quantize_decoder(model, lbit=4, gbit=16)
     opt, groups = ft.build_optimizer(model, lr=1e-4)
-    tuner = ft.LatentFineTuner(model, opt, groups, grad_accum=grad_accum)
+    tuner = ft.LatentFineTuner(model, opt, groups, grad_accum=grad_accum, cuda_graph=cuda_graph)
     vocab = ft.ARCHS[arch]["vocab_size"]
     host = [torch.randint(0, vocab, (micro_batch, seq), generator=torch.Generator().manual_seed(100 + rank * 1000 + i)).pin_memory()
             for i in range(grad_accum)]
@@ -281,7 +281,8 @@ def finetune_measurement(torch, arch="opt-1.3b", steps=2, warmup=1, micro_batch=
     res = {"arch": arch, "tokens_per_s": round(tokens / ms * 1e3, 1), "ms_per_step": round(ms, 1), "world": world,
            "micro_batch": micro_batch, "seq": seq, "grad_accum": grad_accum, "loss_first": round(losses[0], 4),
            "loss_last": round(losses[-1], 4), "replica_codes_identical": same,
-           "grad_arena_bytes": tuner.arena.flat.numel() * 2, "h2d_bytes_per_step": grad_accum * micro_batch * seq * 8}
+           "grad_arena_bytes": tuner.arena.flat.numel() * 2, "h2d_bytes_per_step": grad_accum * micro_batch * seq * 8,
+           "micro_batch_fwd_bwd": "one captured CUDA graph, replayed" if cuda_graph else "eager"}
     del tuner, opt, model
     torch.cuda.empty_cache()
     return res

@@ -112,8 +112,13 @@ class LatentFineTuner:
     """One optimizer step = `grad_accum` micro-batches of forward/backward on this rank, one bucketed all-reduce of
     the gradient arena, one MyAdam step (dequantize + Adam + stochastic requantize per quantized weight)."""
 
-    def __init__(self, model, optimizer, groups, grad_accum: int = 8, group=None, gate_timeout_s: float = 600.0):
+    def __init__(self, model, optimizer, groups, grad_accum: int = 8, group=None, gate_timeout_s: float = 600.0,
+                 cuda_graph: bool = False):
+        """`cuda_graph=True`: forward + backward of one micro-batch are captured once (first `step`, fixed [B, S]) and
+        replayed; the ~430 kernel-launching Python calls per micro-batch (144 quantized linears, three GEMMs each)
+        otherwise leave the GPU waiting for the host."""
         self.model, self.opt, self.grad_accum, self.group = model, optimizer, grad_accum, group
+        self.cuda_graph, self._graph, self._static_ids, self._static_loss, self._graph_scale = cuda_graph, None, None, None, None
         self.params = groups[0]["params"] + groups[1]["params"]
         self.arena = GradArena(self.params, dtype=torch.bfloat16, device=next(model.parameters()).device)
         self.step_no = 0
@@ -128,7 +133,14 @@ class LatentFineTuner:
         self.model.train()
         self.arena.attach()
         total = torch.zeros((), device=self.arena.flat.device, dtype=torch.float32)
+        if self.cuda_graph:
+            self._ensure_graph(micro_batches[0], len(micro_batches))
         for ids in micro_batches:
+            if self.cuda_graph:
+                self._static_ids.copy_(ids, non_blocking=True)
+                self._graph.replay()
+                total += self._static_loss.detach().float()
+                continue
             out = self.model(input_ids=ids, labels=ids, use_cache=False)
             (out.loss / len(micro_batches)).backward()
             total += out.loss.detach().float()
@@ -140,6 +152,35 @@ class LatentFineTuner:
             p.grad = None
         self.step_no += 1
         return total / max(1, len(micro_batches))
+
+
+    # (method of LatentFineTuner, defined below the class body for readability)
+
+
+def _ensure_graph(self, ids, n_micro):
+    """Capture forward + backward of one micro-batch (gradients accumulate in place in the arena views)."""
+    if self._graph is not None:
+        if tuple(ids.shape) != tuple(self._static_ids.shape) or n_micro != self._graph_scale:
+            raise ValueError("the captured step has a fixed micro-batch shape and accumulation count")
+        return
+    self._static_ids = ids.clone()
+    self._graph_scale = n_micro
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):                         # warm-up on a side stream: lazy initialisations, autograd buffers
+        for _ in range(2):
+            out = self.model(input_ids=self._static_ids, labels=self._static_ids, use_cache=False)
+            (out.loss / n_micro).backward()
+    torch.cuda.current_stream().wait_stream(side)
+    self._graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(self._graph):
+        out = self.model(input_ids=self._static_ids, labels=self._static_ids, use_cache=False)
+        self._static_loss = out.loss
+        (out.loss / n_micro).backward()
+    self.arena.attach()                                   # drop what warm-up and capture accumulated
+
+
+LatentFineTuner._ensure_graph = _ensure_graph
 
 
 def synthetic_batches(n: int, batch: int, seq: int, vocab: int, device, seed: int):

@@ -1047,10 +1047,20 @@ class MyAdam(torch.optim.Adam):
             state["state2"] = exp_avg_sq
 
         if isinstance(p, QuantTensor):
+            new_codes = None
             if p.wbit == 8:
-                p.data = Qfunc_8bit_res(pdata, p.residual, qscales=p.qparam)
+                new_codes = Qfunc_8bit_res(pdata, p.residual, qscales=p.qparam)
             elif p.wbit == 4:
-                p.data = Qfunc_4bit_g_res(pdata, p.residual, qparam=p.qparam)
+                new_codes = Qfunc_4bit_g_res(pdata, p.residual, qparam=p.qparam)
+            if new_codes is not None:
+                old = p.data
+                # same values as the reference's `p.data = ...`; written into the existing storage when possible so that
+                # captured CUDA graphs of the forward/backward keep reading the live codes
+                if (torch.is_tensor(old) and old.is_cuda and old.dtype == new_codes.dtype and old.numel() == new_codes.numel()
+                        and old.device == new_codes.device and old.is_contiguous()):
+                    old.view(-1).copy_(new_codes.reshape(-1))
+                else:
+                    p.data = new_codes
         if isinstance(p.grad, GradientQTensor):
             p.grad.zero()
         else:

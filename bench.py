@@ -239,7 +239,8 @@ def _decode_part(torch, ops, pk, out, tm):
                                   "timing": "CUDA graph replay of the 4 layers"}
 
 
-def finetune_measurement(torch, arch="opt-1.3b", steps=2, warmup=1, micro_batch=4, seq=512, grad_accum=8, cuda_graph=True):
+def finetune_measurement(torch, arch="opt-1.3b", steps=2, warmup=1, micro_batch=4, seq=512, grad_accum=8, cuda_graph=True,
+                         decode_batches=()):
     """Latent fine-tune step (BASELINE config 4): A16W4 int4 group-128 latent weights, seq 512, micro-batch 4,
     grad-accum 8 per rank, uniform random token ids, data-parallel over the ranks of this launch with one bf16
     gradient all-reduce per optimizer step.  tokens/s = world * micro_batch * seq * grad_accum / step time.
@@ -283,6 +284,27 @@ def finetune_measurement(torch, arch="opt-1.3b", steps=2, warmup=1, micro_batch=
            "loss_last": round(losses[-1], 4), "replica_codes_identical": same,
            "grad_arena_bytes": tuner.arena.flat.numel() * 2, "h2d_bytes_per_step": grad_accum * micro_batch * seq * 8,
            "micro_batch_fwd_bwd": "one captured CUDA graph, replayed" if cuda_graph else "eager"}
+    if decode_batches:
+        # greedy decode through the same quantized model (eval path of the module API, HF generate with a KV cache):
+        # 512-token random prompts; tokens/s over the decode steps only (prefill timed separately and subtracted)
+        model.eval()
+        dec = {}
+        from torch.nn.attention import SDPBackend, sdpa_kernel
+        # (the cuDNN attention backend rebuilds its plan for every new KV length: ~5 ms of host time per layer and token)
+        with torch.no_grad(), sdpa_kernel([SDPBackend.FLASH_ATTENTION, SDPBackend.EFFICIENT_ATTENTION, SDPBackend.MATH]):
+            for b in decode_batches:
+                prompt = torch.randint(0, vocab, (b, 512), device="cuda")
+                kw = dict(do_sample=False, use_cache=True, pad_token_id=0)
+                model.generate(prompt, max_new_tokens=2, min_new_tokens=2, **kw)           # warm-up
+                torch.cuda.synchronize(); t0 = time.perf_counter()
+                model.generate(prompt, max_new_tokens=1, min_new_tokens=1, **kw)
+                torch.cuda.synchronize(); t1 = time.perf_counter()
+                model.generate(prompt, max_new_tokens=33, min_new_tokens=33, **kw)
+                torch.cuda.synchronize(); t2 = time.perf_counter()
+                dec[f"batch{b}"] = {"prefill_ms": round((t1 - t0) * 1e3, 1),
+                                    "decode_tokens_per_s": round(b * 32 / max(1e-9, (t2 - t1) - (t1 - t0)), 1)}
+        res["greedy_decode"] = dec
+        res["greedy_decode_note"] = "HF generate loop, eager: one Python-driven launch sequence per token (host-bound at small batch)"
     del tuner, opt, model
     torch.cuda.empty_cache()
     return res
@@ -427,9 +449,16 @@ def run_ours(args):
             ft_res = finetune_measurement(torch)
         except Exception as e:                      # the headline line must still be printed
             ft_res = {"error": repr(e)[:300]}
+        torch.cuda.empty_cache()
+        try:                                        # Llama-2-7B architecture, seq 1024, micro-batch 4, one micro-batch per step
+            ft7 = finetune_measurement(torch, arch="llama-2-7b", steps=2, warmup=1, micro_batch=4, seq=1024, grad_accum=1,
+                                       decode_batches=(1, 16, 64) if rank == 0 else ())
+        except Exception as e:
+            ft7 = {"error": repr(e)[:300]}
     if rank == 0:
         if ft_res is not None:
             line.setdefault("extra", {})["finetune_opt1.3b"] = ft_res
+            line["extra"]["finetune_llama2_7b"] = ft7
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()

@@ -43,12 +43,14 @@ def build_model(arch: str, device="cuda", seed: int = 1234, layers: int | None =
     if layers is not None:
         cfg["num_hidden_layers"] = layers
     torch.manual_seed(seed)
-    if kind == "opt":
-        from transformers import OPTConfig, OPTForCausalLM
-        model = OPTForCausalLM(OPTConfig(**cfg))
-    else:
-        from transformers import LlamaConfig, LlamaForCausalLM
-        model = LlamaForCausalLM(LlamaConfig(**cfg))
+    # parameters are created and initialised on the target device (a 7B model takes minutes to initialise on the host)
+    with torch.device(device):
+        if kind == "opt":
+            from transformers import OPTConfig, OPTForCausalLM
+            model = OPTForCausalLM(OPTConfig(**cfg, torch_dtype=torch.bfloat16))
+        else:
+            from transformers import LlamaConfig, LlamaForCausalLM
+            model = LlamaForCausalLM(LlamaConfig(**cfg, torch_dtype=torch.bfloat16))
     return model.to(torch.bfloat16).to(device)
 
 

@@ -157,6 +157,8 @@ def extra_measurements(torch, ops, pk, only=None, numel=1 << 30):
     g = torch.Generator(device="cuda").manual_seed(7)
     if only in (None, "requant"):
         _requant_part(torch, ops, pk, out, tm, g, numel)
+    if only in (None, "stream"):
+        _stream_part(torch, ops, pk, out, tm, g)
     if only in (None, "a8w8"):
         _a8w8_part(torch, ops, out, tm, g)
     if only in (None, "decode"):
@@ -199,6 +201,32 @@ def _requant_part(torch, ops, pk, out, tm, g, numel):
     gbs = (8.0 + 4.0 / GROUP + 16.0 / 2048) * n2 / ms / 1e6
     out["adam_a16w4_fused"] = {"GB/s": round(gbs, 1), "frac_hbm": round(gbs / pk["hbm_gbs"], 3), "ms": round(ms, 3), "numel": n2}
     del codes, words, s, z, grad, st1, st2
+
+
+def _stream_part(torch, ops, pk, out, tm, g, numel=1 << 28):
+    """The other HBM-streaming entry points of the path, GB/s over their algorithmic bytes (inputs + outputs)."""
+    def rec(name, nbytes, fn):
+        ms = tm(fn)
+        out["stream_" + name] = {"GB/s": round(nbytes / ms / 1e6, 1), "frac_hbm": round(nbytes / ms / 1e6 / pk["hbm_gbs"], 3), "ms": round(ms, 3)}
+    n = numel
+    w = (torch.randn(n, device="cuda", generator=g, dtype=torch.float32) * 0.02).to(torch.bfloat16)
+    s, z = ops.find_qparams(w, GROUP, 15, False)
+    sb, zb = s.to(torch.bfloat16), z.to(torch.bfloat16)
+    rec("find_qparams_bf16", 2.0 * n + 8.0 * n / GROUP, lambda: ops.find_qparams(w, GROUP, 15, False))
+    codes, _ = ops.a16w4_requant(w, sb, zb, ops.make_opts(codec=ops.CODEC_NONE, math_dtype=torch.bfloat16))
+    rec("a16w4_dequant_bf16", 0.5 * n + 2.0 * n + 4.0 * n / GROUP, lambda: ops.a16w4_dequant(codes, sb, zb, (n // 4096, 4096), torch.bfloat16))
+    u8 = torch.randint(0, 16, (n,), device="cuda", generator=g, dtype=torch.uint8)
+    rec("pack_nibbles", 1.5 * n, lambda: ops.pack_nibbles(u8))
+    rec("unpack_nibbles", 1.5 * n, lambda: ops.unpack_nibbles(codes))
+    del u8, codes
+    x = torch.randn(n, device="cuda", generator=g, dtype=torch.float32)
+    rec("opt8_quant", 5.0 * n + 8.0 * n / 2048, lambda: ops.opt8_quant(x, 2048))
+    q, sc, tmx = ops.opt8_quant(x, 2048)
+    rec("opt8_dequant", 5.0 * n + 8.0 * n / 2048, lambda: ops.opt8_dequant(q, 2048, sc, tmx))
+    del x, q
+    xa = w.view(-1, 4096)
+    rec("act_quant_per_token", 3.0 * n + 4.0 * n / 4096, lambda: ops.act_quant_per_token(xa))
+    del w, xa
 
 
 def _a8w8_part(torch, ops, out, tm, g):
@@ -471,7 +499,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-extra", action="store_true", help="skip the secondary measurements and the CPU baseline")
-    ap.add_argument("--only", default="", choices=["", "requant", "a8w8", "decode"],
+    ap.add_argument("--only", default="", choices=["", "requant", "stream", "a8w8", "decode"],
                     help="run one family of the secondary measurements only (profiling a single kernel)")
     ap.add_argument("--numel", type=int, default=1 << 30, help="weights in the requantize measurement")
     ap.add_argument("--shapes", default="", help="comma-separated indices into the shape list (profiling a smaller case)")

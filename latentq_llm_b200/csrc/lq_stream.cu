@@ -210,6 +210,51 @@ __global__ void __launch_bounds__(256) k_find_qparams(const void* x, int dtype, 
     }
 }
 
+// bf16 input, group of 32 / 64 / 128 / 256: LPG = group / 8 lanes share a group and reduce with log2(LPG) shuffle
+// steps; min and -max travel packed in one register (bf16 min/max are exact), and every lane has four 16-byte loads
+// in flight.  A warp covers 4 x 256 elements per step.
+template <int LPG>
+__global__ void __launch_bounds__(256) k_find_qparams_bf16(const uint4* __restrict__ x, int64_t n_vec, float maxq, int sym,
+                                                           float* __restrict__ scales, float* __restrict__ zeros) {
+    const int lane = threadIdx.x & 31;
+    const int64_t warp = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int64_t n_warps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+    const __nv_bfloat162 zero2 = __float2bfloat162_rn(0.0f);
+    for (int64_t v0 = warp * 128; v0 < n_vec; v0 += n_warps * 128) {       // 128 vectors of 8 elements per warp step
+        uint4 v[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int64_t i = v0 + j * 32 + lane;
+            v[j] = (i < n_vec) ? __ldg(x + i) : make_uint4(0, 0, 0, 0);
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&v[j].x), b = *reinterpret_cast<const __nv_bfloat162*>(&v[j].y);
+            const __nv_bfloat162 c = *reinterpret_cast<const __nv_bfloat162*>(&v[j].z), d = *reinterpret_cast<const __nv_bfloat162*>(&v[j].w);
+            const __nv_bfloat162 mn2 = __hmin2(__hmin2(__hmin2(a, b), __hmin2(c, d)), zero2);      // xmin = min(min, 0)
+            const __nv_bfloat162 mx2 = __hmax2(__hmax2(__hmax2(a, b), __hmax2(c, d)), zero2);      // xmax = max(max, 0)
+            // (min, -max) packed: one shuffle and one packed min per step
+            __nv_bfloat162 pk = __halves2bfloat162(__hmin(__low2bfloat16(mn2), __high2bfloat16(mn2)),
+                                                   __hneg(__hmax(__low2bfloat16(mx2), __high2bfloat16(mx2))));
+#pragma unroll
+            for (int o = LPG / 2; o > 0; o >>= 1) {
+                const uint32_t other = __shfl_xor_sync(0xffffffffu, *reinterpret_cast<uint32_t*>(&pk), o);
+                pk = __hmin2(pk, *reinterpret_cast<const __nv_bfloat162*>(&other));
+            }
+            const int64_t i = v0 + j * 32 + lane;
+            if ((lane & (LPG - 1)) == 0 && i < n_vec) {
+                float mn = __bfloat162float(__low2bfloat16(pk)), mx = -__bfloat162float(__high2bfloat16(pk));
+                if (sym) { mx = fmaxf(fabsf(mn), mx); if (mn < 0.0f) mn = -mx; }
+                if (mn == 0.0f && mx == 0.0f) { mn = -1.0f; mx = 1.0f; }
+                const float sc = __fdiv_rn(__fsub_rn(mx, mn), maxq);
+                const int64_t g = i / LPG;
+                scales[g] = sc;
+                zeros[g] = sym ? __fmul_rn(maxq + 1.0f, 0.5f) : rintf(__fdiv_rn(-mn, sc));
+            }
+        }
+    }
+}
+
 // =================================================================================================
 // Latent-weight requantize (device functions in lq_requant.cuh)
 // =================================================================================================
@@ -865,6 +910,18 @@ int lq_find_qparams(const void* x, int dtype, int64_t numel, int group, int maxq
         return LQ_EINVAL;
     { int rc_dev = ensure_device_for(x); if (rc_dev) return rc_dev; }
     int64_t n_groups = numel / group;
+    if (dtype == LQ_BF16 && (group == 32 || group == 64 || group == 128 || group == 256)) {
+        const int64_t n_vec = numel / 8;
+        const int grid = grid_for((n_vec + 3) / 4, 256, 8);
+        const uint4* xv = reinterpret_cast<const uint4*>(x);
+        switch (group) {
+            case 32: k_find_qparams_bf16<4><<<grid, 256, 0, LQ_ST(stream)>>>(xv, n_vec, (float)maxq, sym, scales, zeros); break;
+            case 64: k_find_qparams_bf16<8><<<grid, 256, 0, LQ_ST(stream)>>>(xv, n_vec, (float)maxq, sym, scales, zeros); break;
+            case 128: k_find_qparams_bf16<16><<<grid, 256, 0, LQ_ST(stream)>>>(xv, n_vec, (float)maxq, sym, scales, zeros); break;
+            default: k_find_qparams_bf16<32><<<grid, 256, 0, LQ_ST(stream)>>>(xv, n_vec, (float)maxq, sym, scales, zeros); break;
+        }
+        return check_launch("lq_find_qparams");
+    }
     k_find_qparams<<<grid_for(n_groups * 32, 256, 8), 256, 0, LQ_ST(stream)>>>(x, dtype, n_groups, group, (float)maxq,
                                                                                sym, scales, zeros);
     return check_launch("lq_find_qparams");

@@ -37,6 +37,23 @@ def test_find_qparams_golden(ops, golden):
     assert np.array_equal(s.cpu().numpy(), so) and np.array_equal(z.cpu().numpy(), zo)
 
 
+@pytest.mark.parametrize("group", [32, 64, 128, 256])
+@pytest.mark.parametrize("sym", [False, True])
+def test_find_qparams_bf16_packed_kernel_vs_oracle(ops, group, sym):
+    """The packed bf16 min/max kernel (groups of 32..256): ragged tail, an all-zero group, all-positive and all-negative
+    groups (min and max are clamped to include 0), the golden weights rounded to bf16."""
+    g = torch.Generator(device="cuda").manual_seed(group)
+    n_groups = 4 * 1024 // group * 7 + 3                         # not a multiple of the 1024-element warp step
+    w = (torch.randn(n_groups, group, device="cuda", generator=g) * 0.02).to(torch.bfloat16)
+    w[1] = 0
+    w[2] = w[2].abs() + 0.01
+    w[3] = -w[3].abs() - 0.01
+    w[5, 0] = 3.0
+    s, z = ops.find_qparams(w.reshape(-1), group, 15, sym)
+    so, zo = orc.find_qparams(w.float().cpu().numpy(), group, 15, sym)
+    assert np.array_equal(s.cpu().numpy(), so) and np.array_equal(z.cpu().numpy(), zo)
+
+
 def test_dequant_golden(ops, golden):
     s, z = golden["qp_scale_sym0"], golden["qp_zero_sym0"]
     codes = dev(golden["rq_none_codes_f32"])

@@ -179,6 +179,38 @@ __global__ void __launch_bounds__(256) k_a16w4_dequant(const uint32_t* __restric
     }
 }
 
+// bf16 qparams, bf16 output, power-of-two group >= 16: two packed words (16 weights) per thread, packed bf16x2 arithmetic
+// (the integers 128 + q are formed by OR-ing the nibble into bf16 128.0; (128+q) - (128+z) and the product with the
+// scale are single bf16 roundings, i.e. exactly bf16((q - z) * s) as the op-by-op chain computes it).
+__global__ void __launch_bounds__(256) k_a16w4_dequant_bf16(const uint2* __restrict__ packed, const unsigned short* __restrict__ scales,
+                                                            const unsigned short* __restrict__ zeros, uint4* __restrict__ out,
+                                                            uint32_t n_pairs, int pair_shift) {
+    const uint32_t c128 = 0x43004300u;
+    for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < n_pairs; i += gridDim.x * blockDim.x) {
+        const uint32_t g = i >> pair_shift;
+        const uint32_t sb = __ldg(scales + g), zb = __ldg(zeros + g);
+        const uint2 pk = __ldg(packed + i);
+        const uint32_t s2u = sb * 0x00010001u, z2u = zb * 0x00010001u;
+        const __nv_bfloat162 s2 = *reinterpret_cast<const __nv_bfloat162*>(&s2u);
+        const __nv_bfloat162 z128 = __hadd2_rn(*reinterpret_cast<const __nv_bfloat162*>(&z2u), *reinterpret_cast<const __nv_bfloat162*>(&c128));
+        uint32_t o[8];
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const uint32_t w = h ? pk.y : pk.x;
+            const uint32_t lo_n = w & 0x0F0F0F0Fu, hi_n = (w >> 4) & 0x0F0F0F0Fu;       // odd / even elements, one per byte
+            const uint32_t c03 = __byte_perm(hi_n, lo_n, 0x5140), c47 = __byte_perm(hi_n, lo_n, 0x7362);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const uint32_t pair = __byte_perm((j < 2) ? c03 : c47, 0x43434343u, (j & 1) ? 0x4342 : 0x4140);
+                const __nv_bfloat162 v = __hmul2_rn(__hsub2_rn(*reinterpret_cast<const __nv_bfloat162*>(&pair), z128), s2);
+                o[4 * h + j] = *reinterpret_cast<const uint32_t*>(&v);
+            }
+        }
+        out[2 * (size_t)i] = make_uint4(o[0], o[1], o[2], o[3]);
+        out[2 * (size_t)i + 1] = make_uint4(o[4], o[5], o[6], o[7]);
+    }
+}
+
 // =================================================================================================
 // Group min/max -> (scale, zero)   (Quantizer.find_params)
 // =================================================================================================
@@ -682,17 +714,33 @@ __global__ void __launch_bounds__(256) k_opt8_dequant(const uint8_t* __restrict_
 // =================================================================================================
 // Activation quantizers
 // =================================================================================================
+// One CTA per token.  VPT = 16-byte vectors per thread kept in registers between the absmax pass and the quantize pass
+// (VPT * 2048 >= K); larger rows re-read from L2.
+template <int VPT>
 __global__ void __launch_bounds__(256) k_act_quant_per_token(const __nv_bfloat16* __restrict__ x, int64_t K,
                                                              int8_t* __restrict__ x8, float* __restrict__ a_scale) {
     __shared__ float s_mx[8];
     const int64_t base = (int64_t)blockIdx.x * K;
-    float am = 0.0f;
-    for (int64_t e = threadIdx.x * 8; e < K; e += blockDim.x * 8) {
-        float v[8];
-        load8(x, LQ_BF16, base + e, v);
+    const uint4* xv = reinterpret_cast<const uint4*>(x + base);
+    const int n_vec = (int)(K / 8);
+    uint4 keep[VPT > 0 ? VPT : 1];
+    __nv_bfloat162 am2 = __float2bfloat162_rn(0.0f);
+    if (VPT > 0) {
 #pragma unroll
-        for (int k = 0; k < 8; ++k) am = fmaxf(am, fabsf(v[k]));
+        for (int u = 0; u < VPT; ++u) {
+            const int i = threadIdx.x + u * 256;
+            keep[u] = (i < n_vec) ? __ldg(xv + i) : make_uint4(0, 0, 0, 0);
+            const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&keep[u]);
+            am2 = __hmax2(am2, __hmax2(__hmax2(__habs2(h[0]), __habs2(h[1])), __hmax2(__habs2(h[2]), __habs2(h[3]))));
+        }
+    } else {
+        for (int i = threadIdx.x; i < n_vec; i += 256) {
+            const uint4 v = __ldg(xv + i);
+            const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+            am2 = __hmax2(am2, __hmax2(__hmax2(__habs2(h[0]), __habs2(h[1])), __hmax2(__habs2(h[2]), __habs2(h[3]))));
+        }
     }
+    float am = fmaxf(__bfloat162float(__low2bfloat16(am2)), __bfloat162float(__high2bfloat16(am2)));
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, o));
     if ((threadIdx.x & 31) == 0) s_mx[threadIdx.x >> 5] = am;
@@ -703,19 +751,41 @@ __global__ void __launch_bounds__(256) k_act_quant_per_token(const __nv_bfloat16
     if (threadIdx.x == 0) a_scale[blockIdx.x] = s;
     const float rs = __frcp_rn(s);
     const bool ok = fastdiv_ok_scale(s);
-    for (int64_t e = threadIdx.x * 8; e < K; e += blockDim.x * 8) {
-        float v[8];
-        load8(x, LQ_BF16, base + e, v);
+    // 8 values -> 8 int8: x/s rounded to bf16 (x, s bf16: bf16(x * RN(1/s)) == bf16(x / s)), round-half-even, clamp
+    auto quant8 = [&](const uint4& v) -> uint2 {
+        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
         uint32_t b[8];
 #pragma unroll
-        for (int k = 0; k < 8; ++k) {
-            float t = rintf(bf16r(div_rn(v[k], s, rs, ok)));
-            b[k] = (uint32_t)(int)fminf(fmaxf(t, -128.0f), 127.0f) & 0xffu;
+        for (int j = 0; j < 4; ++j) {
+            const float a0 = __uint_as_float(w[j] << 16), a1 = __uint_as_float(w[j] & 0xffff0000u);
+            float t0, t1;
+            if (ok) {
+                const __nv_bfloat162 q = __floats2bfloat162_rn(__fmul_rn(a0, rs), __fmul_rn(a1, rs));
+                const uint32_t qu = *reinterpret_cast<const uint32_t*>(&q);
+                t0 = __uint_as_float(qu << 16); t1 = __uint_as_float(qu & 0xffff0000u);
+            } else {
+                t0 = bf16r(__fdiv_rn(a0, s)); t1 = bf16r(__fdiv_rn(a1, s));
+            }
+            // |t| <= 127 * (1 + 2^-8): magic-number round-half-even, clamp, low byte of the two's complement
+            t0 = fminf(fmaxf(__fsub_rn(__fadd_rn(t0, 12582912.0f), 12582912.0f), -128.0f), 127.0f);
+            t1 = fminf(fmaxf(__fsub_rn(__fadd_rn(t1, 12582912.0f), 12582912.0f), -128.0f), 127.0f);
+            b[2 * j] = __float_as_uint(__fadd_rn(t0, 12582912.0f)) & 0xffu;
+            b[2 * j + 1] = __float_as_uint(__fadd_rn(t1, 12582912.0f)) & 0xffu;
         }
         uint2 o2;
         o2.x = b[0] | (b[1] << 8) | (b[2] << 16) | (b[3] << 24);
         o2.y = b[4] | (b[5] << 8) | (b[6] << 16) | (b[7] << 24);
-        *reinterpret_cast<uint2*>(x8 + base + e) = o2;
+        return o2;
+    };
+    uint2* ov = reinterpret_cast<uint2*>(x8 + base);
+    if (VPT > 0) {
+#pragma unroll
+        for (int u = 0; u < VPT; ++u) {
+            const int i = threadIdx.x + u * 256;
+            if (i < n_vec) ov[i] = quant8(keep[u]);
+        }
+    } else {
+        for (int i = threadIdx.x; i < n_vec; i += 256) ov[i] = quant8(__ldg(xv + i));
     }
 }
 
@@ -892,6 +962,15 @@ int lq_a16w4_dequant(const int8_t* qweight, const void* scales, const void* zero
         !dtype_ok(qp_dtype) || !dtype_ok(out_dtype) || !aligned(qweight, 4) || !aligned(out, 16))
         return LQ_EINVAL;
     { int rc_dev = ensure_device_for(out); if (rc_dev) return rc_dev; }
+    if (qp_dtype == LQ_BF16 && out_dtype == LQ_BF16 && group >= 16 && (group & (group - 1)) == 0 && (numel % 16) == 0 &&
+        numel < ((int64_t)1 << 34) && aligned(qweight, 8)) {
+        int sh = 0; while ((16 << sh) < group) ++sh;
+        const uint32_t n_pairs = (uint32_t)(numel / 16);
+        k_a16w4_dequant_bf16<<<grid_for(n_pairs, 256, 8), 256, 0, LQ_ST(stream)>>>(
+            reinterpret_cast<const uint2*>(qweight), reinterpret_cast<const unsigned short*>(scales),
+            reinterpret_cast<const unsigned short*>(zeros), reinterpret_cast<uint4*>(out), n_pairs, sh);
+        return check_launch("lq_a16w4_dequant");
+    }
     int grid = grid_for(numel / 8, 256, 8);
     if (qp_dtype == LQ_BF16)
         k_a16w4_dequant<true><<<grid, 256, 0, LQ_ST(stream)>>>(reinterpret_cast<const uint32_t*>(qweight), scales, zeros,
@@ -1038,7 +1117,11 @@ int lq_act_quant_per_token(const void* x, int64_t M, int64_t K, int8_t* x8, floa
     if (M == 0) return LQ_OK;
     if (!x || !x8 || !a_scale || M < 0 || K <= 0 || (K % 8) || !aligned(x, 16) || !aligned(x8, 8)) return LQ_EINVAL;
     { int rc_dev = ensure_device_for(x); if (rc_dev) return rc_dev; }
-    k_act_quant_per_token<<<(unsigned)M, 256, 0, LQ_ST(stream)>>>(reinterpret_cast<const __nv_bfloat16*>(x), K, x8, a_scale);
+    const __nv_bfloat16* xb = reinterpret_cast<const __nv_bfloat16*>(x);
+    if (K <= 2048) k_act_quant_per_token<1><<<(unsigned)M, 256, 0, LQ_ST(stream)>>>(xb, K, x8, a_scale);
+    else if (K <= 4096) k_act_quant_per_token<2><<<(unsigned)M, 256, 0, LQ_ST(stream)>>>(xb, K, x8, a_scale);
+    else if (K <= 8192) k_act_quant_per_token<4><<<(unsigned)M, 256, 0, LQ_ST(stream)>>>(xb, K, x8, a_scale);
+    else k_act_quant_per_token<0><<<(unsigned)M, 256, 0, LQ_ST(stream)>>>(xb, K, x8, a_scale);
     return check_launch("lq_act_quant_per_token");
 }
 int lq_act_quant_per_tensor(const void* x, int64_t n, float* clampv_out, int8_t* x8, lq_stream_t stream) {

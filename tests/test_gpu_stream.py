@@ -265,6 +265,19 @@ def test_requant_roundtrip_property_full_size(ops):
     assert torch.unique(outs[0][1]).numel() > 1000
 
 
+@pytest.mark.parametrize("K", [2048, 4096, 8192, 11008])
+def test_act_quant_per_token_row_sizes(ops, K):
+    """Rows kept in registers (K <= 8192) and the re-reading variant (K > 8192), with outlier channels and a zero row."""
+    rng = np.random.default_rng(K)
+    x = rng.standard_normal((37, K)).astype(np.float32)
+    x[:, ::97] *= 20.0
+    x[5] = 0.0
+    xb = dev(x, torch.bfloat16)
+    x8, s = ops.act_quant_per_token(xb)
+    qo, so = orc.act_quant_per_token(xb.float().cpu().numpy(), math_bf16=True)
+    assert np.array_equal(x8.cpu().numpy(), qo) and np.array_equal(s.cpu().numpy().ravel(), so.ravel())
+
+
 def test_act_quant_vs_oracle(ops, golden):
     rng = np.random.default_rng(8)
     x = rng.standard_normal((24, 512)).astype(np.float32)

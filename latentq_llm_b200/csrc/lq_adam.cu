@@ -8,6 +8,8 @@
 // multiply-add into an FMA in torch's own build; the same contraction is spelled out here with __fmaf_rn
 // (checked on the GPU against torch's add_/addcmul_/addcdiv_ on 2^24-element bf16 tensors: the separately
 // rounded forms of add_(alpha) and addcdiv_ differ from torch in a few elements per million, the fused ones never).
+#include <cstdlib>
+
 #include "lq_requant.cuh"
 
 namespace lq {
@@ -123,6 +125,160 @@ __global__ void __launch_bounds__(256) k_adam_a16w4(const AdamParams p) {
     }
 }
 
+// ---------------------------------------------------------------------------------------------------------------
+// Fast variant of the production configuration (bf16 chain, bf16 qparams and gradient, 3-fold codec, hash dither, group a
+// power of two >= 8): packed bf16x2 reconstruction of the latent weights with the residual decode from a 256-entry table,
+// bf16 roundings as packed conversions (two values per instruction), and everything after Z = w/scale + zero from the
+// 64 KB table of the requantize fast path.  Same results as k_adam_a16w4, bit for bit; a word whose Z leaves the table's
+// range (|Z| >= 64, non-finite) is encoded by the generic chain.
+// ---------------------------------------------------------------------------------------------------------------
+constexpr int ADAM_TRES_REPL = 8;
+constexpr int ADAM_FAST_SMEM = ENCZ_TABLE_ENTRIES + 256 * ADAM_TRES_REPL * 4;
+
+__device__ __forceinline__ void rb2(float a, float b, float& ra, float& rbv) {       // bf16 roundings of two values, one conversion
+    const __nv_bfloat162 q = __floats2bfloat162_rn(a, b);
+    const uint32_t u = *reinterpret_cast<const uint32_t*>(&q);
+    ra = __uint_as_float(u << 16); rbv = __uint_as_float(u & 0xffff0000u);
+}
+
+template <bool USE_RES>
+__global__ void __launch_bounds__(256, 3) k_adam_a16w4_fast(const AdamParams p, const int enc_slot) {
+    extern __shared__ __align__(16) uint8_t asm_[];
+    uint8_t* encz = asm_;
+    uint32_t* tres = reinterpret_cast<uint32_t*>(asm_ + ENCZ_TABLE_ENTRIES);
+    __shared__ float s_red[4][8];
+    {
+        const uint4* src = reinterpret_cast<const uint4*>(g_encz_table[enc_slot]);
+        uint4* dst = reinterpret_cast<uint4*>(encz);
+        for (int i = threadIdx.x; i < ENCZ_TABLE_ENTRIES / 16; i += 256) dst[i] = __ldg(src + i);
+        for (int b = threadIdx.x; b < 256; b += 256) {
+            const uint32_t lo = f32_to_bf16_bits(bf16r(res3_decode((uint32_t)b >> 4, p.rq.dec)));
+            const uint32_t hi = f32_to_bf16_bits(bf16r(res3_decode((uint32_t)b & 15u, p.rq.dec)));
+            for (int r = 0; r < ADAM_TRES_REPL; ++r) tres[b * ADAM_TRES_REPL + r] = lo | (hi << 16);
+        }
+    }
+    __syncthreads();
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const uint32_t tres_lane = tid & (ADAM_TRES_REPL - 1);
+    const unsigned short* scales = reinterpret_cast<const unsigned short*>(p.rq.scales);
+    const unsigned short* zeros = reinterpret_cast<const unsigned short*>(p.rq.zeros);
+    const uint32_t n_words = (uint32_t)p.rq.n_words;
+    const int gsh = p.rq.group_shift - 3;                     // word index -> group index
+    const int osh = p.opt_shift - 3;                          // word index -> optimizer-state block
+    const uint32_t c128u = 0x43004300u;
+    for (uint32_t tile = blockIdx.x; tile < (uint32_t)p.n_tiles; tile += gridDim.x) {
+        const uint32_t w = tile * 256u + (uint32_t)tid;
+        const bool active = w < n_words;
+        float lat[8], m[8], d[8];
+        float sf = 1.0f;
+        uint32_t zb = 0u, ob = 0u;
+        float mn1 = INFINITY, mx1 = -INFINITY, mn2 = INFINITY, mx2 = -INFINITY;
+        if (active) {
+            const uint32_t g = w >> gsh;
+            const uint32_t sb = __ldg(scales + g);
+            zb = __ldg(zeros + g);
+            ob = w >> osh;
+            const float s1 = p.sc1[ob], t1 = p.tm1[ob], s2f = p.sc2[ob], t2 = p.tm2[ob];
+            const uint2 q1 = *reinterpret_cast<const uint2*>(p.st1 + (size_t)w * 8);
+            const uint2 q2 = *reinterpret_cast<const uint2*>(p.st2 + (size_t)w * 8);
+            const uint4 gv = __ldg(reinterpret_cast<const uint4*>(p.grad) + w);
+            const uint32_t pk = __ldg(reinterpret_cast<const uint32_t*>(p.rq.codes_in) + w);
+            uint32_t rw = 0u;
+            if (USE_RES) rw = (uint32_t)__ldg(p.rq.words_in + w);
+            sf = __uint_as_float(sb << 16);
+            // latent weights: bf16((q - z) * s) (+ bf16(bf16(res * s) + that)), packed
+            const uint32_t s2u = sb * 0x00010001u, z2u = zb * 0x00010001u;
+            const __nv_bfloat162 s2 = *reinterpret_cast<const __nv_bfloat162*>(&s2u);
+            const __nv_bfloat162 z128 = __hadd2_rn(*reinterpret_cast<const __nv_bfloat162*>(&z2u), *reinterpret_cast<const __nv_bfloat162*>(&c128u));
+            const uint32_t lo_n = pk & 0x0F0F0F0Fu, hi_n = (pk >> 4) & 0x0F0F0F0Fu;
+            const uint32_t c03 = __byte_perm(hi_n, lo_n, 0x5140), c47 = __byte_perm(hi_n, lo_n, 0x7362);
+            const uint32_t gw[4] = {gv.x, gv.y, gv.z, gv.w};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const uint32_t pair = __byte_perm((j < 2) ? c03 : c47, 0x43434343u, (j & 1) ? 0x4342 : 0x4140);
+                __nv_bfloat162 v = __hmul2_rn(__hsub2_rn(*reinterpret_cast<const __nv_bfloat162*>(&pair), z128), s2);
+                if (USE_RES) {
+                    const uint32_t b = (rw >> (24 - 8 * j)) & 0xffu;
+                    const uint32_t tr = tres[b * ADAM_TRES_REPL + tres_lane];
+                    v = __hadd2_rn(__hmul2_rn(*reinterpret_cast<const __nv_bfloat162*>(&tr), s2), v);
+                }
+                const uint32_t vu = *reinterpret_cast<const uint32_t*>(&v);
+                lat[2 * j] = __uint_as_float(vu << 16); lat[2 * j + 1] = __uint_as_float(vu & 0xffff0000u);
+                // the two elements of the pair through the optimizer chain (every intermediate rounded to bf16)
+                const int k0 = 2 * j, k1 = 2 * j + 1;
+                const float g0 = __uint_as_float(gw[j] << 16), g1 = __uint_as_float(gw[j] & 0xffff0000u);
+                const float c10 = u2f(((k0 < 4 ? q1.x : q1.y) >> (8 * (k0 & 3))) & 0xffu), c11 = u2f(((k1 < 4 ? q1.x : q1.y) >> (8 * (k1 & 3))) & 0xffu);
+                const float c20 = u2f(((k0 < 4 ? q2.x : q2.y) >> (8 * (k0 & 3))) & 0xffu), c21 = u2f(((k1 < 4 ? q2.x : q2.y) >> (8 * (k1 & 3))) & 0xffu);
+                float m0, m1, v0, v1, t0, t1v;
+                rb2(__fsub_rn(t1, __fmul_rn(c10, s1)), __fsub_rn(t1, __fmul_rn(c11, s1)), m0, m1);       // DeQfunc_8bit_opt(...).to(bf16)
+                const float r20 = __fsub_rn(t2, __fmul_rn(c20, s2f)), r21 = __fsub_rn(t2, __fmul_rn(c21, s2f));
+                rb2(__fmul_rn(r20, r20), __fmul_rn(r21, r21), v0, v1);                                   // (s2 * s2).to(bf16)
+                rb2(__fmul_rn(m0, p.h.beta1), __fmul_rn(m1, p.h.beta1), m0, m1);
+                rb2(__fmaf_rn(p.h.one_minus_beta1, g0, m0), __fmaf_rn(p.h.one_minus_beta1, g1, m1), m0, m1);
+                rb2(__fmul_rn(v0, p.h.beta2), __fmul_rn(v1, p.h.beta2), v0, v1);
+                rb2(__fmaf_rn(p.h.one_minus_beta2, __fmul_rn(g0, g0), v0), __fmaf_rn(p.h.one_minus_beta2, __fmul_rn(g1, g1), v1), v0, v1);
+                rb2(__fsqrt_rn(v0), __fsqrt_rn(v1), t0, t1v);
+                rb2(__fadd_rn(t0, p.h.eps), __fadd_rn(t1v, p.h.eps), v0, v1);                            // sqrt(v) + eps
+                rb2(__fmaf_rn(p.h.neg_step_size, __fdiv_rn(m0, v0), lat[k0]), __fmaf_rn(p.h.neg_step_size, __fdiv_rn(m1, v1), lat[k1]), lat[k0], lat[k1]);
+                m[k0] = m0; m[k1] = m1; d[k0] = v0; d[k1] = v1;
+                mn1 = fminf(mn1, fminf(m0, m1)); mx1 = fmaxf(mx1, fmaxf(m0, m1));
+                mn2 = fminf(mn2, fminf(v0, v1)); mx2 = fmaxf(mx2, fmaxf(v0, v1));
+            }
+        }
+#pragma unroll
+        for (int o = 8; o > 0; o >>= 1) {
+            mn1 = fminf(mn1, __shfl_xor_sync(0xffffffffu, mn1, o)); mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, o));
+            mn2 = fminf(mn2, __shfl_xor_sync(0xffffffffu, mn2, o)); mx2 = fmaxf(mx2, __shfl_xor_sync(0xffffffffu, mx2, o));
+        }
+        if (p.opt_shift == 11) {
+            mn1 = fminf(mn1, __shfl_xor_sync(0xffffffffu, mn1, 16)); mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 16));
+            mn2 = fminf(mn2, __shfl_xor_sync(0xffffffffu, mn2, 16)); mx2 = fmaxf(mx2, __shfl_xor_sync(0xffffffffu, mx2, 16));
+            __syncthreads();
+            if (lane == 0) { s_red[0][warp] = mn1; s_red[1][warp] = mx1; s_red[2][warp] = mn2; s_red[3][warp] = mx2; }
+            __syncthreads();
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                mn1 = fminf(mn1, s_red[0][i]); mx1 = fmaxf(mx1, s_red[1][i]);
+                mn2 = fminf(mn2, s_red[2][i]); mx2 = fmaxf(mx2, s_red[3][i]);
+            }
+        }
+        if (active) {
+            const float ns1 = __fadd_rn(__fdiv_rn(__fsub_rn(mx1, mn1), 255.0f), 1e-10f);
+            const float ns2 = __fadd_rn(__fdiv_rn(__fsub_rn(mx2, mn2), 255.0f), 1e-10f);
+            *reinterpret_cast<uint2*>(p.st1 + (size_t)w * 8) = opt8_encode8(m, mx1, ns1);
+            *reinterpret_cast<uint2*>(p.st2 + (size_t)w * 8) = opt8_encode8(d, mx2, ns2);
+            const bool leader = p.opt_shift == 11 ? (tid == 0) : ((tid & 15) == 0);
+            if (leader) { p.sc1[ob] = ns1; p.tm1[ob] = mx1; p.sc2[ob] = ns2; p.tm2[ob] = mx2; }
+            // requantize: Z = bf16(bf16(lat / s) + z), then one table byte per element
+            const float rs = __frcp_rn(sf);
+            const uint32_t z2u = zb * 0x00010001u;
+            const __nv_bfloat162 z2 = *reinterpret_cast<const __nv_bfloat162*>(&z2u);
+            uint32_t zbits[4], zmax = 0u;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const __nv_bfloat162 Zp = __hadd2_rn(__floats2bfloat162_rn(__fmul_rn(lat[2 * j], rs), __fmul_rn(lat[2 * j + 1], rs)), z2);
+                zbits[j] = *reinterpret_cast<const uint32_t*>(&Zp);
+                __nv_bfloat162 az = __habs2(Zp);
+                if (j) az = __hmax2_nan(*reinterpret_cast<const __nv_bfloat162*>(&zmax), az);        // NaN-propagating max of the magnitudes
+                zmax = *reinterpret_cast<const uint32_t*>(&az);
+            }
+            const bool bad = (((zmax & 0x7fff7fffu) + 0x3d803d80u) & 0x80008000u) != 0u || !fastdiv_ok_scale(sf);
+            if (__builtin_expect(bad, 0)) {
+                const float z = __uint_as_float(zb << 16);
+                latent_store<4, LQ_CODEC_THREEFOLD, LQ_DITHER_HASH, true>(p.rq, (int64_t)w, sf, z, lat);
+            } else {
+                uint32_t ev[4], od[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) { ev[j] = encz[zbits[j] & 0xffffu]; od[j] = encz[zbits[j] >> 16]; }
+                const uint32_t e_even = __byte_perm(__byte_perm(ev[0], ev[1], 0x4040), __byte_perm(ev[2], ev[3], 0x4040), 0x5410);
+                const uint32_t e_odd = __byte_perm(__byte_perm(od[0], od[1], 0x4040), __byte_perm(od[2], od[3], 0x4040), 0x5410);
+                reinterpret_cast<uint32_t*>(p.rq.codes_out)[w] = (e_even & 0xF0F0F0F0u) | ((e_odd >> 4) & 0x0F0F0F0Fu);
+                p.rq.words_out[w] = (int32_t)__byte_perm(((e_even << 4) & 0xF0F0F0F0u) | (e_odd & 0x0F0F0F0Fu), 0u, 0x0123);
+            }
+        }
+    }
+}
+
 template <int CODEC, int DITHER>
 static int launch_adam(const AdamParams& p, bool bf, cudaStream_t st) {
     const int64_t cap = (int64_t)sm_count() * 8;
@@ -182,7 +338,29 @@ int lq_adam_a16w4_step(int8_t* codes, int32_t* words, const void* grad, int grad
     p.h = *hyper;
     const bool bf = grad_dtype == LQ_BF16;
     cudaStream_t st = LQ_ST(stream);
-    if (opts->codec == LQ_CODEC_THREEFOLD && opts->dither == LQ_DITHER_HASH) return launch_adam<LQ_CODEC_THREEFOLD, LQ_DITHER_HASH>(p, bf, st);
+    if (opts->codec == LQ_CODEC_THREEFOLD && opts->dither == LQ_DITHER_HASH) {
+        if (bf && p.rq.group_shift >= 3 && p.rq.n_words < ((int64_t)1 << 31) && opts->mu_enc >= 0 && opts->mu_enc <= 3 &&
+            opts->mu_dec >= 0 && opts->mu_dec <= 3 && !getenv("LQ_REQUANT_GENERIC")) {
+            rc = ensure_encz_table(opts->mu_enc, opts->v0, st);
+            if (rc) return rc;
+            static bool attr_done[64][2] = {};
+            int dev = 0;
+            cudaGetDevice(&dev);
+            const int ur = p.rq.has_residual ? 1 : 0;
+            if (dev >= 0 && dev < 64 && !attr_done[dev][ur]) {
+                cudaError_t e = ur ? cudaFuncSetAttribute(k_adam_a16w4_fast<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, ADAM_FAST_SMEM)
+                                   : cudaFuncSetAttribute(k_adam_a16w4_fast<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, ADAM_FAST_SMEM);
+                if (e != cudaSuccess) { set_cuda_error(e, "cudaFuncSetAttribute(k_adam_a16w4_fast)"); return LQ_ECUDA; }
+                attr_done[dev][ur] = true;
+            }
+            const int64_t cap = (int64_t)sm_count() * 3;
+            const int grid = (int)(p.n_tiles < cap ? p.n_tiles : cap);
+            if (ur) k_adam_a16w4_fast<true><<<grid, 256, ADAM_FAST_SMEM, st>>>(p, opts->mu_enc);
+            else k_adam_a16w4_fast<false><<<grid, 256, ADAM_FAST_SMEM, st>>>(p, opts->mu_enc);
+            return check_launch("k_adam_a16w4_fast");
+        }
+        return launch_adam<LQ_CODEC_THREEFOLD, LQ_DITHER_HASH>(p, bf, st);
+    }
     if (opts->codec == LQ_CODEC_THREEFOLD && opts->dither == LQ_DITHER_PHILOX) return launch_adam<LQ_CODEC_THREEFOLD, LQ_DITHER_PHILOX>(p, bf, st);
     if (opts->codec == LQ_CODEC_UNIFORM16 && opts->dither == LQ_DITHER_PHILOX) return launch_adam<LQ_CODEC_UNIFORM16, LQ_DITHER_PHILOX>(p, bf, st);
     return LQ_EUNSUPPORTED;

@@ -2,6 +2,8 @@
 // optimizer step: dtype-generic 8-element loads/stores, conversion-free rounding helpers, and the two halves
 // of the per-word chain (reconstruct the latent weights / quantize them back to codes + residual nibbles).
 #pragma once
+#include <mutex>
+
 #include "lq_common.cuh"
 
 namespace lq {
@@ -274,6 +276,40 @@ static inline int fill_requant(RequantParams& p, const lq_requant_opts* o, int64
     return LQ_OK;
 }
 static inline bool dtype_ok(int d) { return d == LQ_F32 || d == LQ_BF16; }
+
+
+// ---- table of the bf16 fast paths: everything after Z as one byte (each translation unit that launches a kernel
+// reading it holds its own copy; built once per device, curve level and hash offset) ---------------------------
+constexpr int ENCZ_TABLE_ENTRIES = 65536;               // every bf16 pattern of Z = w/scale + zero
+static __device__ uint8_t g_encz_table[4][ENCZ_TABLE_ENTRIES]; // one per curve level; entry = final code << 4 | residual nibble
+static __global__ void __launch_bounds__(256) k_build_encz_table(int slot, Curve c, float v0) {
+    for (int h = blockIdx.x * blockDim.x + threadIdx.x; h < ENCZ_TABLE_ENTRIES; h += gridDim.x * blockDim.x) {
+        const float Z = __uint_as_float((uint32_t)h << 16);
+        uint8_t e = 0;                                  // |Z| >= 64, inf, NaN: never looked up (the word takes the generic chain)
+        if (fabsf(Z) < 64.0f) e = (uint8_t)encode_from_z_w4_hash_bf16(Z, c, v0);
+        g_encz_table[slot][h] = e;
+    }
+}
+
+static std::mutex g_encz_mutex;
+// Builds (once per device, curve level and v0) the encode table the fast path reads.
+static inline int ensure_encz_table(int mu, float v0, cudaStream_t st) {
+    static bool built[64][4] = {};
+    static float built_v0[64][4] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return LQ_EUNSUPPORTED;
+    const int slot = (mu < 0 || mu > 3) ? 0 : mu;
+    std::lock_guard<std::mutex> lock(g_encz_mutex);
+    if (built[dev][slot] && built_v0[dev][slot] == v0) return LQ_OK;
+    k_build_encz_table<<<128, 256, 0, st>>>(slot, curve_for_level(slot), v0);
+    int rc = check_launch("k_build_encz_table");
+    if (rc) return rc;
+    // first use only: make the table visible to every stream before anyone else may read it
+    cudaError_t e = cudaStreamSynchronize(st);
+    if (e != cudaSuccess) { set_cuda_error(e, "cudaStreamSynchronize"); return LQ_ECUDA; }
+    built[dev][slot] = true; built_v0[dev][slot] = v0;
+    return LQ_OK;
+}
 
 
 }  // namespace lq

@@ -310,17 +310,6 @@ __global__ void __launch_bounds__(256) k_requant(const RequantParams p) {
 //  * words whose Z leaves (-64, 64) (weights far outside the quantization range) or is not finite take the
 //    generic path.
 // =================================================================================================
-constexpr int ENCZ_TABLE_ENTRIES = 65536;               // every bf16 pattern of Z = w/scale + zero
-__device__ uint8_t g_encz_table[4][ENCZ_TABLE_ENTRIES]; // one per curve level; entry = final code << 4 | residual nibble
-__global__ void __launch_bounds__(256) k_build_encz_table(int slot, Curve c, float v0) {
-    for (int h = blockIdx.x * blockDim.x + threadIdx.x; h < ENCZ_TABLE_ENTRIES; h += gridDim.x * blockDim.x) {
-        const float Z = __uint_as_float((uint32_t)h << 16);
-        uint8_t e = 0;                                  // |Z| >= 64, inf, NaN: never looked up (the word takes the generic chain)
-        if (fabsf(Z) < 64.0f) e = (uint8_t)encode_from_z_w4_hash_bf16(Z, c, v0);
-        g_encz_table[slot][h] = e;
-    }
-}
-
 // Philox (or any external) dither: for a given Z the outcome is a step function of the 16-bit dither value h
 // (u = h/65536 - 0.5): entry = threshold T | outcome for h < T << 16 | outcome for h >= T << 24 (outcome = code << 4 | nibble).
 // Indexed by sign and magnitude of Z for |Z| < 32 (0x4200 bf16 patterns per sign).
@@ -518,26 +507,6 @@ __global__ void __launch_bounds__(FastCfg<DITHER>::THREADS, FastCfg<DITHER>::MIN
         if (wp + stride < n_pairs) nxt = load_in(wp + stride);      // n_pairs < 2^30: no wrap
         process(cur, wp);
     }
-}
-
-static std::mutex g_encz_mutex;
-// Builds (once per device, curve level and v0) the encode table the fast path reads.
-static int ensure_encz_table(int mu, float v0, cudaStream_t st) {
-    static bool built[64][4] = {};
-    static float built_v0[64][4] = {};
-    int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return LQ_EUNSUPPORTED;
-    const int slot = (mu < 0 || mu > 3) ? 0 : mu;
-    std::lock_guard<std::mutex> lock(g_encz_mutex);
-    if (built[dev][slot] && built_v0[dev][slot] == v0) return LQ_OK;
-    k_build_encz_table<<<128, 256, 0, st>>>(slot, curve_for_level(slot), v0);
-    int rc = check_launch("k_build_encz_table");
-    if (rc) return rc;
-    // first use only: make the table visible to every stream before anyone else may read it
-    cudaError_t e = cudaStreamSynchronize(st);
-    if (e != cudaSuccess) { set_cuda_error(e, "cudaStreamSynchronize"); return LQ_ECUDA; }
-    built[dev][slot] = true; built_v0[dev][slot] = v0;
-    return LQ_OK;
 }
 
 // Builds (once per device and curve level) the threshold table of the Philox fast path; LQ_EUNSUPPORTED if some Z

@@ -119,13 +119,18 @@ def test_fused_entry_point_rejects_bad_arguments():
     assert e.value.status == L.LQ_EUNSUPPORTED
 
 
+@pytest.mark.parametrize("generic", [False, True])                # table-driven fast kernel / generic kernel
 @pytest.mark.parametrize("n_rows,K", [(32, 2048), (40, 128)])     # 2048-element and 128-element state blocks
-def test_fused_quantized_step_matches_oracle(n_rows, K):
+def test_fused_quantized_step_matches_oracle(n_rows, K, generic, monkeypatch):
     """The CUDA kernel against the CPU restatement of the GPU evaluation order, two consecutive steps (the second
     one decodes a live residual and non-trivial 8-bit states)."""
     import numpy as np
     import oracle as orc
     from latentq_llm_b200 import ops
+    if generic:
+        monkeypatch.setenv("LQ_REQUANT_GENERIC", "1")
+    else:
+        monkeypatch.delenv("LQ_REQUANT_GENERIC", raising=False)
     n = n_rows * K
     block = 2048 if n % 2048 == 0 else 128
     g = torch.Generator(device="cuda").manual_seed(21)

@@ -273,3 +273,67 @@ class QuantLinearA8W8(nn.Module):
         b = (self.bias.to(torch.bfloat16) / sc) if self.bias is not None else 0 * sc
         out = ops.gemm_a8w8(Am, Bm, None, None, clampv / 127., b.contiguous()) * sc.view(1, -1)
         return out.reshape(out_shape).to(x.dtype)
+
+
+# ---------------------------------------------------------------------------------------------------
+# Model surgery and the reference's aliases (PTQ/quant/quant_linear.py:398, 479, 722-770)
+# ---------------------------------------------------------------------------------------------------
+QuantLinear0 = QuantLinearGPTQ
+QuantLinear1 = QuantLinearA8W8
+QuantLinear2 = QuantLinearA16W4
+
+config = {'method': 'gptq'}      # 'gptq' -> QuantLinearGPTQ, anything else -> QuantLinearA16W4 (group-wise layers)
+
+
+def make_quant_linear(module, quantizers, bits, groupsize, name=''):
+    """PTQ/quant/quant_linear.py:729-766: replace every sub-module whose qualified name is a key of `quantizers` by an
+    (empty) packed layer of the same shape — A8W8 when `groupsize == -1`, otherwise the layout `config['method']`
+    selects — carrying over the calibration statistics the PTQ pass attached to the float layer."""
+    if isinstance(module, (QuantLinearA8W8, QuantLinearGPTQ, QuantLinearA16W4)):
+        return
+    for attr, child in list(module.named_children()):
+        qualified = f"{name}.{attr}" if name else attr
+        if qualified not in quantizers:
+            continue
+        has_bias = getattr(child, "bias", None) is not None
+        if groupsize == -1:
+            new = QuantLinearA8W8(bits, groupsize, child.in_features, child.out_features, has_bias)
+            if hasattr(child, 'inp_absmax'):
+                new.inp_absmax.data = child.inp_absmax
+            if hasattr(child, 'inp_bias'):
+                new.input_bias = None
+                new.register_buffer('input_bias', child.inp_bias)
+                new.tmp_bias = torch.nn.functional.linear(child.inp_bias.float(), child.weight.float()).to(torch.float16)
+        else:
+            cls = QuantLinearGPTQ if config['method'] == 'gptq' else QuantLinearA16W4
+            new = cls(bits, groupsize, child.in_features, child.out_features, has_bias)
+        new.name = qualified
+        if hasattr(new, 'out_scale'):
+            if hasattr(child, 'qk_absmax'):
+                new.out_scale.data = child.qk_absmax.max()
+            if hasattr(child, 'v_absmax'):
+                new.out_scale.data = child.v_absmax
+        setattr(module, attr, new)
+    for attr, child in module.named_children():
+        make_quant_linear(child, quantizers, bits, groupsize, f"{name}.{attr}" if name else attr)
+
+
+def autotune_warmup_linear(model, transpose=False):
+    """PTQ/quant/quant_linear.py:772-800 pre-tunes the Triton kernels.  Nothing is tuned here (plans are computed from
+    the shape); one call per distinct (K, N) performs the library's one-time per-kernel set-up outside any timed region."""
+    seen = set()
+    with torch.no_grad():
+        for m in model.modules():
+            if not isinstance(m, QuantLinearGPTQ) or (m.infeatures, m.outfeatures) in seen:
+                continue
+            seen.add((m.infeatures, m.outfeatures))
+            dev = m.qweight.device
+            if dev.type != "cuda":
+                continue
+            for rows in (1, 64, 2048):
+                a = torch.randn(rows, m.infeatures, dtype=torch.float16, device=dev)
+                matmul248(a, m.qweight, m.scales, m.qzeros, m.g_idx, m.bits, m.maxq)
+                if transpose:
+                    a = torch.randn(rows, m.outfeatures, dtype=torch.float16, device=dev)
+                    transpose_matmul248(a, m.qweight, m.scales, m.qzeros, m.g_idx, m.bits, m.maxq)
+    return len(seen)

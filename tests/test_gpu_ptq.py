@@ -76,3 +76,40 @@ def test_per_token_fake_quant(golden):
     q, s = orc.act_quant_per_token(t.float().cpu().numpy(), math_bf16=True)
     want = orc.bf16_round(q.astype(np.float32) * s[:, None])
     assert np.array_equal(out.float().cpu().numpy(), want)
+
+
+def test_make_quant_linear_surgery_and_warmup():
+    """Model surgery of the PTQ side: named linears are replaced by packed layers of the configured layout, calibration
+    statistics travel, untouched layers stay, and a packed GPTQ model runs after the one-time warm-up."""
+    import torch.nn as nn
+    from latentq_llm_b200 import ptq
+
+    class Block(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.fc1, self.fc2, self.keep = nn.Linear(256, 512), nn.Linear(512, 256, bias=False), nn.Linear(256, 64)
+
+    class Net(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.blocks = nn.ModuleList([Block(), Block()])
+
+    names = {"blocks.0.fc1": None, "blocks.0.fc2": None, "blocks.1.fc1": None}
+    for method, cls in (("gptq", ptq.QuantLinearGPTQ), ("a16w4", ptq.QuantLinearA16W4)):
+        net = Net()
+        ptq.config["method"] = method
+        ptq.make_quant_linear(net, names, 4, 128)
+        assert isinstance(net.blocks[0].fc1, cls) and isinstance(net.blocks[0].fc2, cls) and isinstance(net.blocks[1].fc1, cls)
+        assert isinstance(net.blocks[1].fc2, nn.Linear) and isinstance(net.blocks[0].keep, nn.Linear)
+        assert net.blocks[0].fc1.name == "blocks.0.fc1" and net.blocks[0].fc2.bias is None
+    ptq.config["method"] = "gptq"
+    net = Net()
+    net.blocks[0].fc1.inp_absmax = torch.full((256,), 2.0, dtype=torch.float16)
+    ptq.make_quant_linear(net, {"blocks.0.fc1": None}, 8, -1)
+    assert isinstance(net.blocks[0].fc1, ptq.QuantLinearA8W8) and float(net.blocks[0].fc1.inp_absmax.max()) == 2.0
+    assert ptq.QuantLinear0 is ptq.QuantLinearGPTQ and ptq.QuantLinear1 is ptq.QuantLinearA8W8 and ptq.QuantLinear2 is ptq.QuantLinearA16W4
+    # a packed GPTQ layer inside a model: warm-up visits each distinct (K, N) once
+    net = Net().cuda()
+    ptq.make_quant_linear(net, {"blocks.0.fc1": None, "blocks.1.fc1": None}, 4, 128)
+    net = net.cuda()
+    assert ptq.autotune_warmup_linear(net, transpose=True) == 1

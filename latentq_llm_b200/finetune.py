@@ -188,3 +188,76 @@ LatentFineTuner._ensure_graph = _ensure_graph
 def synthetic_batches(n: int, batch: int, seq: int, vocab: int, device, seed: int):
     g = torch.Generator(device=device).manual_seed(seed)
     return [torch.randint(0, vocab, (batch, seq), device=device, generator=g) for _ in range(n)]
+
+
+# ---------------------------------------------------------------------------------------------------
+# Checkpoint I/O in the reference's key layout (main0.py:299-343 reads `<decoder>.<i>.<sub>.{qweight,zeros,scales,bias}`)
+# ---------------------------------------------------------------------------------------------------
+def decoder_prefix(model: nn.Module) -> str:
+    return "model.decoder.layers." if hasattr(model.model, "decoder") else "model.layers."
+
+
+@torch.no_grad()
+def save_quantized_decoder(model: nn.Module, path: str, with_residual: bool = True) -> int:
+    """Write every QLinearA16W4 of the decoder as the reference's A16W4 checkpoint keys: `qweight` int8 nibble pairs
+    (flat, the layout the GEMMs read), `zeros` / `scales` [G, 1], `bias`.  With `with_residual` the 4-bit residual words
+    and the curve level travel too (`residual_int`, `residual_mu`: an extension, needed to resume training exactly).
+    Returns the number of layers written."""
+    from safetensors.torch import save_file
+    prefix, out, n = decoder_prefix(model), {}, 0
+    for li, layer in enumerate(decoder_layers(model)):
+        for subname, sub in layer.named_modules():
+            if not isinstance(sub, QLinearA16W4):
+                continue
+            key = f"{prefix}{li}.{subname}"
+            out[key + ".qweight"] = sub.weight.data.reshape(-1).contiguous().cpu()
+            out[key + ".zeros"] = sub.zeros.data.contiguous().cpu()
+            out[key + ".scales"] = sub.scales.data.contiguous().cpu()
+            if sub.bias is not None:
+                out[key + ".bias"] = sub.bias.data.contiguous().cpu()
+            res = getattr(sub.weight, "residual", None)
+            if with_residual and res is not None and hasattr(res, "residual_int") and not res.init:
+                out[key + ".residual_int"] = res.residual_int.reshape(-1).contiguous().cpu()
+                out[key + ".residual_mu"] = torch.tensor([res.mu, res.lock_mu], dtype=torch.int32)
+            n += 1
+    save_file(out, path)
+    return n
+
+
+@torch.no_grad()
+def load_quantized_decoder(model: nn.Module, ckt, lbit: int = 4, gbit: int = 16) -> list:
+    """The A16W4 branch of main0.py:299-343: swap every nn.Linear of the decoder layers for a QLinearA16W4 filled from the
+    checkpoint (`ckt`: a path to a .safetensors file or a dict of tensors with the keys above)."""
+    if isinstance(ckt, str):
+        from safetensors.torch import load_file
+        ckt = load_file(ckt)
+    prefix, swapped = decoder_prefix(model), []
+    for li, layer in enumerate(decoder_layers(model)):
+        for subname, sub in list(layer.named_modules()):
+            for name, child in list(sub.named_children()):
+                if not isinstance(child, (nn.Linear, QLinearA16W4)):
+                    continue
+                qual = f"{subname + '.' if subname else ''}{name}"
+                key = f"{prefix}{li}.{qual}"
+                dev = child.weight.data.device if isinstance(child, nn.Linear) else child.scales.device
+                n_out, n_in = (child.weight.shape if isinstance(child, nn.Linear) else child.wshape)
+                new = QLinearA16W4(int(n_in), int(n_out), bias=child.bias is not None, lbit=lbit, gbit=gbit)
+                new.lname = key
+                new.zeros.data = ckt[key + ".zeros"].to(torch.bfloat16).to(dev)
+                new.scales.data = ckt[key + ".scales"].to(torch.bfloat16).to(dev)
+                new.weight.set_value(ckt[key + ".qweight"].to(dev), [new.scales, new.zeros, new.wshape])
+                if lbit == 4:
+                    new.weight.residual.name = key + ".residual"
+                    if key + ".residual_int" in ckt:
+                        res = new.weight.residual
+                        res.residual_int.copy_(ckt[key + ".residual_int"].to(dev).view_as(res.residual_int))
+                        mu, lock_mu = (int(v) for v in ckt[key + ".residual_mu"].tolist())
+                        res.mu = lock_mu                           # _after_set_value copies mu into lock_mu
+                        res._after_set_value(new.scales.data.view(-1, 1))
+                        res.mu = mu
+                if child.bias is not None:
+                    new.bias.data = ckt[key + ".bias"].to(torch.bfloat16).to(dev)
+                new.to(dev)
+                setattr(sub, name, new)
+                swapped.append(new)
+    return swapped

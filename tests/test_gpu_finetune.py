@@ -60,3 +60,36 @@ def test_cuda_graph_step_with_dropout_trains():
     batches = ft.synthetic_batches(2, 4, 64, 1024, "cuda", seed=3)
     losses = [float(tuner.step(batches)) for _ in range(6)]
     assert all(l == l for l in losses) and losses[-1] < losses[0] - 0.05, losses
+
+
+def test_checkpoint_roundtrip_in_reference_key_layout(tmp_path):
+    """Train two steps, save the decoder in the reference's A16W4 key layout (+ residual words), load it into a freshly
+    built model: codes, qparams, residuals and the eval forward are identical; keys are the ones main0.py reads."""
+    from safetensors.torch import load_file
+    from latentq_llm_b200 import finetune as ft
+    model = ft.build_model("opt-tiny", "cuda", seed=7)
+    swapped = ft.quantize_decoder(model, lbit=4, gbit=16)
+    opt, groups = ft.build_optimizer(model, lr=2e-3)
+    tuner = ft.LatentFineTuner(model, opt, groups, grad_accum=2)
+    batches = ft.synthetic_batches(2, 4, 64, 1024, "cuda", seed=3)
+    for _ in range(2):
+        tuner.step(batches)
+    path = str(tmp_path / "decoder.safetensors")
+    assert ft.save_quantized_decoder(model, path) == len(swapped)
+    keys = set(load_file(path).keys())
+    assert {"model.decoder.layers.0.self_attn.q_proj.qweight", "model.decoder.layers.0.self_attn.q_proj.zeros",
+            "model.decoder.layers.0.self_attn.q_proj.scales", "model.decoder.layers.0.self_attn.q_proj.bias",
+            "model.decoder.layers.1.fc2.qweight"} <= keys
+    fresh = ft.build_model("opt-tiny", "cuda", seed=7)
+    # non-quantized parameters (biases were trained, layer norms too) travel by the ordinary state dict
+    loaded = ft.load_quantized_decoder(fresh, path)
+    assert len(loaded) == len(swapped)
+    for a, b in zip(swapped, loaded):
+        assert torch.equal(a.weight.data.view(-1), b.weight.data.view(-1))
+        assert torch.equal(a.scales.data, b.scales.data) and torch.equal(a.zeros.data, b.zeros.data)
+        assert torch.equal(a.weight.residual.residual_int, b.weight.residual.residual_int)
+        assert a.weight.residual.lock_mu == b.weight.residual.lock_mu and not b.weight.residual.init
+        assert torch.equal(a.bias.data, b.bias.data)
+    x = torch.randn(3, 16, 256, device="cuda").to(torch.bfloat16)
+    with torch.no_grad():
+        assert torch.equal(swapped[0](x), loaded[0](x))

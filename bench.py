@@ -186,7 +186,18 @@ def _requant_part(torch, ops, pk, out, tm, g, numel):
         cnt = ctypes.c_ulonglong(0)
         _lib.lib.lq_fold_fallback_words(1, ctypes.byref(cnt))
         out["requant_" + name]["generic_fallback_words"] = cnt.value
-    del delta
+    # same for int8 codes with one scale per weight row of 4096 (A8W8): codes 1 B + residual 0.5 B read and written, delta 2 B
+    n8 = numel // 2
+    codes8 = torch.randint(-100, 100, (n8 // 4096, 4096), device="cuda", generator=g, dtype=torch.int8)
+    qs8 = torch.full((n8 // 4096,), 0.0006, device="cuda", dtype=torch.bfloat16)
+    o = ops.make_opts(codec=ops.CODEC_THREEFOLD, dither=ops.DITHER_HASH)
+    ms = tm(lambda: ops.a8w8_fold_delta(codes8, words[:n8 // 8], delta[:n8], qs8, o))
+    gbs = (5.0 + 2.0 / 4096) * n8 / ms / 1e6
+    cnt = ctypes.c_ulonglong(0)
+    _lib.lib.lq_fold_fallback_words(1, ctypes.byref(cnt))
+    out["requant_a8w8_threefold_hash"] = {"GB/s": round(gbs, 1), "frac_hbm": round(gbs / pk["hbm_gbs"], 3), "ms": round(ms, 3),
+                                          "numel": n8, "generic_fallback_words": cnt.value}
+    del delta, codes8, qs8
     # fused optimizer step (8-bit state decode + Adam + state re-encode + requantize in one pass): codes and residual
     # read and written (2 x 1 B), bf16 gradient read (2 B), two uint8 states read and written (4 B) = 8 B per weight
     n2 = numel // 4

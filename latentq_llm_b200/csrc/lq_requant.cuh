@@ -179,6 +179,16 @@ __device__ __forceinline__ uint32_t encode_from_z_w4_hash_bf16(float Z, const Cu
     qf = fminf(fmaxf(qf, 0.0f), 15.0f);
     return ((f2bits(qf) & 15u) << 4) | nib;
 }
+// int8 codes (A8W8: no zero point, clamp [-128, 127]); returns (code & 0xff) | nibble << 8
+__device__ __forceinline__ uint32_t encode_from_z_w8_hash_bf16(float Z, const Curve& enc, float v0) {
+    float qf = rne(Z);
+    const float r = rb<true>(__fsub_rn(Z, qf));
+    float carry = 0.0f;
+    const uint32_t nib = res3_encode_fast(r, hash_dither_fast(r, v0), enc, carry) & 15u;
+    qf = rb<true>(__fadd_rn(qf, carry));
+    qf = fminf(fmaxf(qf, -128.0f), 127.0f);
+    return (f2bits(qf) & 0xffu) | (nib << 8);
+}
 // Same with an external dither value v in [-0.5, 0.5) (explicit buffer or Philox) instead of the hash of the residual.
 __device__ __forceinline__ uint32_t encode_from_z_w4_dither_bf16(float Z, float v, const Curve& enc) {
     float qf = rne(Z);

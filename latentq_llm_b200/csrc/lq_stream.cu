@@ -532,6 +532,177 @@ static int ensure_encp_table(int mu, cudaStream_t st) {
     return state[dev][slot] == 1 ? LQ_OK : LQ_EUNSUPPORTED;
 }
 
+// =================================================================================================
+// A8W8 fast path (int8 codes, one bf16 scale per weight row, bf16 chain, 3-fold codec, hash dither): same structure as
+// k_fold_fast; the table entry per bf16 pattern of Z = w/scale is 16 bits (int8 code | nibble << 8), 128 KB: one CTA
+// of 1024 threads per SM.
+// =================================================================================================
+__device__ uint16_t g_enc8_table[4][65536];
+__global__ void __launch_bounds__(256) k_build_enc8_table(int slot, Curve c, float v0) {
+    for (int h = blockIdx.x * blockDim.x + threadIdx.x; h < 65536; h += gridDim.x * blockDim.x) {
+        const float Z = __uint_as_float((uint32_t)h << 16);
+        g_enc8_table[slot][h] = (fabsf(Z) < 256.0f) ? (uint16_t)encode_from_z_w8_hash_bf16(Z, c, v0) : (uint16_t)0;
+    }
+}
+static int ensure_enc8_table(int mu, float v0, cudaStream_t st) {
+    static bool built[64][4] = {};
+    static float built_v0[64][4] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return LQ_EUNSUPPORTED;
+    const int slot = (mu < 0 || mu > 3) ? 0 : mu;
+    std::lock_guard<std::mutex> lock(g_encz_mutex);
+    if (built[dev][slot] && built_v0[dev][slot] == v0) return LQ_OK;
+    k_build_enc8_table<<<128, 256, 0, st>>>(slot, curve_for_level(slot), v0);
+    int rc = check_launch("k_build_enc8_table");
+    if (rc) return rc;
+    cudaError_t e = cudaStreamSynchronize(st);       // first use only: visible to every stream before anyone reads it
+    if (e != cudaSuccess) { set_cuda_error(e, "cudaStreamSynchronize"); return LQ_ECUDA; }
+    built[dev][slot] = true; built_v0[dev][slot] = v0;
+    return LQ_OK;
+}
+
+constexpr int FAST8_THREADS = 1024;
+constexpr int FAST8_SMEM = 65536 * 2 + 256 * FAST_RES_REPL * 4;
+
+template <bool FROM_W, bool USE_RES, bool HAS_DELTA>
+__global__ void __launch_bounds__(FAST8_THREADS, 1) k_fold_fast8(const RequantParams p, const int enc_slot, const uint64_t row_magic) {
+    extern __shared__ __align__(16) uint8_t fsm8[];
+    const uint16_t* enc8 = reinterpret_cast<const uint16_t*>(fsm8);
+    uint32_t* tres = reinterpret_cast<uint32_t*>(fsm8 + 65536 * 2);
+    {
+        const uint4* src = reinterpret_cast<const uint4*>(g_enc8_table[enc_slot]);
+        uint4* dst = reinterpret_cast<uint4*>(fsm8);
+        for (int i = threadIdx.x; i < 65536 * 2 / 16; i += FAST8_THREADS) dst[i] = __ldg(src + i);
+        for (int b = threadIdx.x; b < 256; b += FAST8_THREADS) {
+            const uint32_t lo = f32_to_bf16_bits(bf16r(res3_decode((uint32_t)b >> 4, p.dec)));
+            const uint32_t hi = f32_to_bf16_bits(bf16r(res3_decode((uint32_t)b & 15u, p.dec)));
+            for (int r = 0; r < FAST_RES_REPL; ++r) tres[b * FAST_RES_REPL + r] = lo | (hi << 16);
+        }
+    }
+    __syncthreads();
+    const uint32_t tres_lane = threadIdx.x & (FAST_RES_REPL - 1);
+    const unsigned short* scales = reinterpret_cast<const unsigned short*>(p.scales);
+    const uint32_t n_words = (uint32_t)p.n_words;
+    struct In { uint2 pk; uint32_t rw, sb; uint4 dv; };
+    auto load_in = [&](uint32_t w) -> In {
+        In in;
+        in.pk = make_uint2(0u, 0u); in.rw = 0u; in.dv = make_uint4(0, 0, 0, 0);
+        const uint32_t row = (uint32_t)__umul64hi((uint64_t)w, row_magic);       // w / (words per row): magic = ceil(2^64 / wpr), exact while w * wpr < 2^64
+        in.sb = __ldg(scales + row);
+        if (FROM_W) {
+            in.dv = __ldg(reinterpret_cast<const uint4*>(p.w_in) + w);
+        } else {
+            in.pk = __ldg(reinterpret_cast<const uint2*>(p.codes_in) + w);
+            if (USE_RES) in.rw = (uint32_t)__ldg(p.words_in + w);
+            if (HAS_DELTA) in.dv = __ldg(reinterpret_cast<const uint4*>(p.delta) + w);
+        }
+        return in;
+    };
+    auto process = [&](const In& cur, const uint32_t w) {
+        const uint32_t sb = cur.sb;
+        const uint32_t s2u = sb * 0x00010001u;
+        const __nv_bfloat162 s2 = u2h(s2u);
+        const float sf = __uint_as_float(sb << 16);
+        const float rs = __frcp_rn(sf);
+        __nv_bfloat162 lat[4];
+        const uint32_t d[4] = {cur.dv.x, cur.dv.y, cur.dv.z, cur.dv.w};
+        if (FROM_W) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) lat[j] = u2h(d[j]);
+        } else {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                // two int8 codes -> exact fp32 through the 2^23 magic (byte ^ 0x80 = code + 128), then one packed conversion
+                const uint32_t word = (j < 2) ? cur.pk.x : cur.pk.y;
+                const uint32_t b0 = ((word >> (16 * (j & 1))) & 0xffu) ^ 0x80u, b1 = ((word >> (16 * (j & 1) + 8)) & 0xffu) ^ 0x80u;
+                const float c0 = __fsub_rn(__uint_as_float(0x4B000000u | b0), 8388736.0f), c1 = __fsub_rn(__uint_as_float(0x4B000000u | b1), 8388736.0f);
+                __nv_bfloat162 v = __hmul2_rn(__floats2bfloat162_rn(c0, c1), s2);
+                if (USE_RES) {
+                    const uint32_t b = (cur.rw >> (24 - 8 * j)) & 0xffu;
+                    v = __hadd2_rn(__hmul2_rn(u2h(tres[b * FAST_RES_REPL + tres_lane]), s2), v);
+                }
+                if (HAS_DELTA) v = __hadd2_rn(v, u2h(d[j]));
+                lat[j] = v;
+            }
+        }
+        uint32_t zb[4], zmax = 0u;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const uint32_t lb = h2u(lat[j]);
+            const __nv_bfloat162 Z = __floats2bfloat162_rn(__fmul_rn(__uint_as_float(lb << 16), rs), __fmul_rn(__uint_as_float(lb & 0xffff0000u), rs));
+            zb[j] = h2u(Z);
+            __nv_bfloat162 az = __habs2(Z);
+            if (j) az = __hmax2_nan(u2h(zmax), az);
+            zmax = h2u(az);
+        }
+        // |Z| >= 256 (0x4380), inf or NaN anywhere in the word -> generic chain
+        const bool bad = (((zmax & 0x7fff7fffu) + 0x3c803c80u) & 0x80008000u) != 0u || !fastdiv_ok_scale(sf);
+        if (__builtin_expect(bad, 0)) {
+            requant_word<8, LQ_CODEC_THREEFOLD, LQ_DITHER_HASH, true>(p, (int64_t)w);
+            atomicAdd(&g_fold_fallback_words, 1ull);
+            return;
+        }
+        uint32_t ev[4], od[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) { ev[j] = enc8[zb[j] & 0xffffu]; od[j] = enc8[zb[j] >> 16]; }
+        // entries: code in byte 0, nibble in byte 1.  Code bytes in element order; residual element k at bits 28 - 4k.
+        uint2 codes;
+        codes.x = __byte_perm(__byte_perm(ev[0], od[0], 0x4040), __byte_perm(ev[1], od[1], 0x4040), 0x5410);
+        codes.y = __byte_perm(__byte_perm(ev[2], od[2], 0x4040), __byte_perm(ev[3], od[3], 0x4040), 0x5410);
+        uint32_t res_word = 0u;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) res_word |= ((((ev[j] >> 8) & 15u) << 4) | ((od[j] >> 8) & 15u)) << (24 - 8 * j);
+        reinterpret_cast<uint2*>(p.codes_out)[w] = codes;
+        p.words_out[w] = (int32_t)res_word;
+    };
+    const uint32_t stride = gridDim.x * FAST8_THREADS;
+    uint32_t w = blockIdx.x * FAST8_THREADS + threadIdx.x;
+    In nxt;
+    if (w < n_words) nxt = load_in(w);
+    for (; w < n_words; w += stride) {
+        const In cur = nxt;
+        if (w + stride < n_words) nxt = load_in(w + stride);
+        process(cur, w);
+    }
+}
+
+static bool fast_fold8_eligible(const RequantParams& p, const lq_requant_opts* o) {
+    if (getenv("LQ_REQUANT_GENERIC")) return false;
+    const int64_t wpr = p.group / 8;                        // words per weight row (group = columns)
+    return o->codec == LQ_CODEC_THREEFOLD && o->dither == LQ_DITHER_HASH && o->math_dtype == LQ_BF16 && p.qp_dtype == LQ_BF16 &&
+           o->mu_enc >= 0 && o->mu_enc <= 3 && o->mu_dec >= 0 && o->mu_dec <= 3 && p.n_words < ((int64_t)1 << 30) &&
+           wpr > 1 && wpr < (1 << 24) &&
+           (p.w_in ? p.w_dtype == LQ_BF16 : (!p.delta || p.delta_dtype == LQ_BF16));
+}
+template <bool FROM_W, bool USE_RES, bool HAS_DELTA>
+static int launch_fold_fast8_v(const RequantParams& p, int slot, cudaStream_t st) {
+    static bool attr_done[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 64) return LQ_EUNSUPPORTED;
+    if (!attr_done[dev]) {
+        cudaError_t e = cudaFuncSetAttribute(k_fold_fast8<FROM_W, USE_RES, HAS_DELTA>, cudaFuncAttributeMaxDynamicSharedMemorySize, FAST8_SMEM);
+        if (e != cudaSuccess) { set_cuda_error(e, "cudaFuncSetAttribute(k_fold_fast8)"); return LQ_ECUDA; }
+        attr_done[dev] = true;
+    }
+    const uint64_t wpr = (uint64_t)(p.group / 8);
+    const uint64_t magic = ~(uint64_t)0 / wpr + 1;                          // ceil(2^64 / wpr) for wpr > 1
+    const int grid = grid_for(p.n_words, FAST8_THREADS, 1);
+    k_fold_fast8<FROM_W, USE_RES, HAS_DELTA><<<grid, FAST8_THREADS, FAST8_SMEM, st>>>(p, slot, magic);
+    return check_launch("k_fold_fast8");
+}
+static int launch_fold_fast8(const RequantParams& p, const lq_requant_opts* o, cudaStream_t st) {
+    int rc = ensure_enc8_table(o->mu_enc, o->v0, st);
+    if (rc) return rc;
+    const int slot = o->mu_enc;
+    if (p.w_in) return launch_fold_fast8_v<true, false, false>(p, slot, st);
+    const bool res = p.has_residual != 0, dl = p.delta != nullptr;
+    if (res && dl) return launch_fold_fast8_v<false, true, true>(p, slot, st);
+    if (res) return launch_fold_fast8_v<false, true, false>(p, slot, st);
+    if (dl) return launch_fold_fast8_v<false, false, true>(p, slot, st);
+    return launch_fold_fast8_v<false, false, false>(p, slot, st);
+}
+
 static bool fast_fold_eligible(const RequantParams& p, const lq_requant_opts* o) {
     if (getenv("LQ_REQUANT_GENERIC")) return false;
     return o->codec == LQ_CODEC_THREEFOLD && (o->dither == LQ_DITHER_HASH || o->dither == LQ_DITHER_PHILOX) &&
@@ -603,6 +774,10 @@ static int launch_requant(const RequantParams& p, const lq_requant_opts* o, cuda
     { int rc_dev = ensure_device_for(p.codes_out); if (rc_dev) return rc_dev; }
     if (WBITS == 4 && fast_fold_eligible(p, o)) {
         const int rc = launch_fold_fast(p, o, st);
+        if (rc != LQ_EUNSUPPORTED) return rc;
+    }
+    if (WBITS == 8 && fast_fold8_eligible(p, o)) {
+        const int rc = launch_fold_fast8(p, o, st);
         if (rc != LQ_EUNSUPPORTED) return rc;
     }
     const bool bf = o->math_dtype == LQ_BF16;

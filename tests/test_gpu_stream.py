@@ -347,3 +347,45 @@ def test_fast_fold_path_equals_generic_kernel(ops, monkeypatch, dither):
     _lib.lib.lq_fold_fallback_words(1, ctypes.byref(cnt))
     poisoned = N * K // 4099 + N * K // 7919 + N * K // 10007 + 3
     assert 0 < cnt.value <= 2 * poisoned, (cnt.value, poisoned)     # a poisoned word takes its neighbour along
+
+
+@pytest.mark.parametrize("N,K", [(1024, 4096), (517, 1736)])      # 512 and 217 (not a power of two) words per row
+def test_fast_fold_path_int8_equals_generic_kernel(ops, monkeypatch, N, K):
+    """A8W8 latent requantize: the table-driven bf16 fast path against the generic kernel, every variant (from dense
+    weights, with / without residual, with / without update), weights beyond the int8 range and non-finite updates."""
+    import ctypes
+    from latentq_llm_b200 import _lib
+    g = torch.Generator(device="cuda").manual_seed(6)
+    w = (torch.randn(N, K, device="cuda", generator=g) * 0.02).to(torch.bfloat16)
+    w[:, 5] *= 8.0
+    qs = (w.float().abs().amax(dim=1) / 127.0).to(torch.bfloat16)
+    delta = (torch.randn(N * K, device="cuda", generator=g) * 1e-4).to(torch.bfloat16)
+    delta[::4099] = 3.0           # |Z| beyond 256: handed to the generic chain
+    delta[1::7919] = float("-inf")
+    delta[2::10007] = 0.05        # clamps at +127 inside the table
+    results = {}
+    cnt = ctypes.c_ulonglong(0)
+    for mode in ("fast", "generic"):
+        if mode == "generic":
+            monkeypatch.setenv("LQ_REQUANT_GENERIC", "1")
+        else:
+            monkeypatch.delenv("LQ_REQUANT_GENERIC", raising=False)
+        _lib.lib.lq_fold_fallback_words(1, ctypes.byref(cnt))
+        outs = []
+        o = ops.make_opts(codec=ops.CODEC_THREEFOLD, dither=ops.DITHER_HASH, math_dtype=torch.bfloat16, mu_enc=1)
+        c, wd = ops.a8w8_requant(w, qs, o)
+        outs.append((c.clone(), wd.clone()))
+        for step, (mu_enc, mu_dec) in enumerate([(0, 1), (1, 0), (2, 1), (3, 2), (0, 3)]):
+            o = ops.make_opts(codec=ops.CODEC_THREEFOLD, dither=ops.DITHER_HASH, math_dtype=torch.bfloat16,
+                              has_residual=step != 1, mu_enc=mu_enc, mu_dec=mu_dec)
+            ops.a8w8_fold_delta(c, wd, delta if step != 3 else None, qs, o)
+            outs.append((c.clone(), wd.clone()))
+        _lib.lib.lq_fold_fallback_words(1, ctypes.byref(cnt))
+        if mode == "fast":
+            poisoned = N * K // 4099 + N * K // 7919 + 2
+            assert 0 < cnt.value <= 6 * poisoned, (cnt.value, poisoned)    # the fast kernel ran; only poisoned words left it
+        results[mode] = outs
+    for i, ((cf, wf), (cg, wg)) in enumerate(zip(results["fast"], results["generic"])):
+        assert torch.equal(cf, cg), i
+        assert torch.equal(wf, wg), i
+    assert results["fast"][-1][0].unique().numel() > 100

@@ -73,6 +73,63 @@ def allreduce_mean(arena: GradArena, group=None, bucket_bytes: int = 64 << 20) -
     return len(works)
 
 
+class ChunkReducer:
+    """Mean all-reduce of the arena, range by range, each range launched as soon as its gradients are final.
+
+    `ranges` are (start, end) element ranges of `arena.flat`.  On a GPU every range is reduced on a side stream that
+    waits either for the compute stream as it stands at the launch call, or for an event the backward pass records when
+    the range is complete — so the transfer overlaps the rest of the backward pass — and `wait(k)` makes the compute
+    stream wait for range k only, so the optimizer steps parameters whose gradients have arrived while later ranges
+    are still in flight.  With NCCL the division by the world size happens inside the collective; gloo (CPU tests) sums
+    and divides afterwards."""
+
+    def __init__(self, arena: GradArena, ranges: Sequence, group=None):
+        self.arena, self.group = arena, group
+        self.ranges = [(int(a), int(b)) for a, b in ranges]
+        self.world = dist.get_world_size(group)
+        self.cuda = arena.flat.is_cuda
+        self.in_collective_mean = self.cuda and dist.get_backend(group) == "nccl"
+        self.comm = torch.cuda.Stream(device=arena.flat.device) if self.cuda else None
+        self.works = [None] * len(self.ranges)
+        self.launched = 0
+
+    def begin(self) -> None:
+        self.works = [None] * len(self.ranges)
+        self.launched = 0
+
+    def launch(self, k: int, after_event=None) -> None:
+        a, b = self.ranges[k]
+        if b <= a or self.works[k] is not None:
+            return
+        view = self.arena.flat[a:b]
+        op = dist.ReduceOp.AVG if self.in_collective_mean else dist.ReduceOp.SUM
+        if self.cuda:
+            if after_event is not None:
+                self.comm.wait_event(after_event)
+            else:
+                self.comm.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(self.comm):
+                self.works[k] = dist.all_reduce(view, op=op, group=self.group, async_op=True)
+        else:
+            self.works[k] = dist.all_reduce(view, op=op, group=self.group, async_op=True)
+        self.launched += 1
+
+    def wait(self, k: int) -> None:
+        """Order everything launched on the compute stream from here on after range k's reduction (host-blocking on CPU)."""
+        w = self.works[k]
+        if w is None or w is True:
+            return
+        w.wait()
+        if not self.in_collective_mean:
+            a, b = self.ranges[k]
+            self.arena.flat[a:b].div_(self.world)
+        self.works[k] = True
+
+    def wait_all(self) -> None:
+        for k in range(len(self.ranges)):
+            self.wait(k)
+
+
 def shard_micro_batches(n_micro_batches: int, rank: int, world: int) -> List[int]:
     """DistributedSampler-style assignment (main0.py:387-392): rank r takes micro-batches r, r+W, r+2W, …"""
     return list(range(rank, n_micro_batches, world))

@@ -18,7 +18,7 @@ import torch
 import torch.nn as nn
 
 from . import ops
-from .dp import GradArena, StepGate, allreduce_mean, shard_micro_batches
+from .dp import ChunkReducer, GradArena, StepGate, allreduce_mean, shard_micro_batches
 from .quant import GROUPSIZE, MyAdam, QLinearA16W4
 
 ARCHS = {
@@ -115,10 +115,15 @@ class LatentFineTuner:
     the gradient arena, one MyAdam step (dequantize + Adam + stochastic requantize per quantized weight)."""
 
     def __init__(self, model, optimizer, groups, grad_accum: int = 8, group=None, gate_timeout_s: float = 600.0,
-                 cuda_graph: bool = False):
+                 cuda_graph: bool = False, overlap_chunks: int = 8):
         """`cuda_graph=True`: forward + backward of one micro-batch are captured once (first `step`, fixed [B, S]) and
         replayed; the ~430 kernel-launching Python calls per micro-batch (144 quantized linears, three GEMMs each)
-        otherwise leave the GPU waiting for the host."""
+        otherwise leave the GPU waiting for the host.
+
+        `overlap_chunks` (world size > 1): the decoder layers are cut into that many runs; during the backward pass of
+        the step's last micro-batch the gradients of a run are all-reduced as soon as the pass has left the run (its
+        layers come last in the forward order, first in the backward order), and the optimizer then steps run by run
+        as the reductions land.  0 = one bucketed all-reduce after the backward pass."""
         self.model, self.opt, self.grad_accum, self.group = model, optimizer, grad_accum, group
         self.cuda_graph, self._graph, self._static_ids, self._static_loss, self._graph_scale = cuda_graph, None, None, None, None
         self.params = groups[0]["params"] + groups[1]["params"]
@@ -126,6 +131,9 @@ class LatentFineTuner:
         self.step_no = 0
         dist_on = torch.distributed.is_available() and torch.distributed.is_initialized()
         self.gate = StepGate(timeout_s=gate_timeout_s) if dist_on and torch.distributed.get_world_size() > 1 else None
+        self._reducer, self._events, self._capturing, self._reduce_in_backward = None, {}, False, False
+        if self.gate is not None and overlap_chunks > 0:
+            self._plan_overlap(groups, overlap_chunks)
         # the hidden states entering the first decoder layer must require grad, otherwise autograd skips the custom
         # backward of the quantized linears (embeddings are frozen, as in the reference's parameter groups)
         model.get_input_embeddings().register_forward_hook(lambda m, i, o: o.requires_grad_(True))
@@ -137,24 +145,84 @@ class LatentFineTuner:
         total = torch.zeros((), device=self.arena.flat.device, dtype=torch.float32)
         if self.cuda_graph:
             self._ensure_graph(micro_batches[0], len(micro_batches))
-        for ids in micro_batches:
+        red, last = self._reducer, len(micro_batches) - 1
+        for i, ids in enumerate(micro_batches):
+            if red is not None and i == last:
+                self.gate.arrive_and_wait(self.step_no)  # host-side liveness check before the step's first collective
+                red.begin()
+                self._reduce_in_backward = not self.cuda_graph
             if self.cuda_graph:
                 self._static_ids.copy_(ids, non_blocking=True)
                 self._graph.replay()
                 total += self._static_loss.detach().float()
+                if red is not None and i == last:        # the replayed backward pass records one event per run of layers
+                    for k in sorted(self._events, reverse=True):
+                        red.launch(k, after_event=self._events[k])
                 continue
             out = self.model(input_ids=ids, labels=ids, use_cache=False)
-            (out.loss / len(micro_batches)).backward()
+            (out.loss / len(micro_batches)).backward()   # (last micro-batch: the layer hooks launch the reductions)
             total += out.loss.detach().float()
-        if self.gate is not None:
-            self.gate.arrive_and_wait(self.step_no)      # host-side liveness check before the collective
-        allreduce_mean(self.arena, self.group)
-        self.opt.step()
+        self._reduce_in_backward = False
+        if red is not None:
+            for k in range(len(red.ranges)):             # whatever is left: the first run of layers, the dense parameters
+                red.launch(k)
+            self.opt.before_param = self._wait_for_param
+            self.opt.step()
+            red.wait_all()
+        else:
+            if self.gate is not None:
+                self.gate.arrive_and_wait(self.step_no)  # host-side liveness check before the collective
+            allreduce_mean(self.arena, self.group)
+            self.opt.step()
         for p in self.params:                           # MyAdam drops quantized grads (p.grad = None); clear the rest too
             p.grad = None
         self.step_no += 1
         return total / max(1, len(micro_batches))
 
+
+    def _plan_overlap(self, groups, n_chunks: int) -> None:
+        """Cut the quantized-weight part of the arena into runs of consecutive decoder layers; the dense parameters
+        (biases, norms: a few MB) form one more range, reduced after the backward pass."""
+        layers = list(decoder_layers(self.model))
+        layer_of = {}
+        for li, layer in enumerate(layers):
+            for child in layer.modules():
+                if isinstance(child, QLinearA16W4):
+                    layer_of[id(child.weight)] = li
+        qp = groups[0]["params"]
+        order = [layer_of.get(id(p), -1) for p in qp]
+        if not qp or min(order) < 0 or any(b < a for a, b in zip(order, order[1:])):
+            return                                        # parameters not in layer order: keep the single all-reduce
+        q_end = self.arena.offsets[len(qp)] if len(self.params) > len(qp) else self.arena.numel
+        n_chunks = max(1, min(n_chunks, len(layers)))
+        first_layer = [round(k * len(layers) / n_chunks) for k in range(n_chunks)]
+        starts = []
+        for fl in first_layer:                            # arena offset of the first quantized weight of layer >= fl
+            idx = next((i for i, l in enumerate(order) if l >= fl), None)
+            starts.append(q_end if idx is None else self.arena.offsets[idx])
+        ranges = [(starts[k], starts[k + 1] if k + 1 < n_chunks else q_end) for k in range(n_chunks)]
+        ranges.append((q_end, self.arena.numel))
+        self._reducer = ChunkReducer(self.arena, ranges, self.group)
+        self._range_of = {}
+        for i, p in enumerate(self.params):
+            off = self.arena.offsets[i]
+            self._range_of[id(p)] = next(k for k, (a, b) in enumerate(ranges) if a <= off < b or (a == b == off))
+        for k in range(1, n_chunks):                      # run k is final once the backward pass enters the layer below it
+            if ranges[k][1] > ranges[k][0]:
+                layers[first_layer[k] - 1].register_full_backward_pre_hook(lambda m, go, k=k: self._run_done(k))
+                self._events[k] = None
+
+    def _run_done(self, k: int) -> None:
+        if self._capturing:
+            if self._events.get(k) is None:
+                # external: the captured record becomes an event node that streams outside the graph can wait for
+                self._events[k] = torch.cuda.Event(external=True)
+            self._events[k].record()
+        elif self._reduce_in_backward:
+            self._reducer.launch(k)
+
+    def _wait_for_param(self, p) -> None:
+        self._reducer.wait(self._range_of[id(p)])
 
     # (method of LatentFineTuner, defined below the class body for readability)
 
@@ -175,10 +243,14 @@ def _ensure_graph(self, ids, n_micro):
             (out.loss / n_micro).backward()
     torch.cuda.current_stream().wait_stream(side)
     self._graph = torch.cuda.CUDAGraph()
-    with torch.cuda.graph(self._graph):
-        out = self.model(input_ids=self._static_ids, labels=self._static_ids, use_cache=False)
-        self._static_loss = out.loss
-        (out.loss / n_micro).backward()
+    self._capturing = True
+    try:
+        with torch.cuda.graph(self._graph):
+            out = self.model(input_ids=self._static_ids, labels=self._static_ids, use_cache=False)
+            self._static_loss = out.loss
+            (out.loss / n_micro).backward()
+    finally:
+        self._capturing = False
     self.arena.attach()                                   # drop what warm-up and capture accumulated
 
 

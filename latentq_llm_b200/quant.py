@@ -853,6 +853,7 @@ class MyAdam(torch.optim.Adam):
         self.mu_updata_f = mu_updata_f
         self.statedevice = 'cpu' if cpu else 'cuda'
         self.fused = bool(fused) and not cpu
+        self.before_param = None                 # optional callable(p), run before a parameter with a gradient is stepped
         self._dense_tables = {}
 
     def add_param_group(self, param_group):
@@ -885,6 +886,8 @@ class MyAdam(torch.optim.Adam):
             for pindex, p in enumerate(group["params"]):
                 if p.grad is None:
                     continue
+                if self.before_param is not None:           # data-parallel step: wait for this gradient's all-reduce only
+                    self.before_param(p)
                 state = self.state[p]
                 if len(state) == 0:
                     self.init_state(group, p, gindex, pindex)

@@ -69,6 +69,50 @@ def test_bucketed_allreduce_mean_world2():
         assert ok and ident and not differ
 
 
+def _worker_chunk_reducer(rank, world, port, q):
+    from latentq_llm_b200.dp import ChunkReducer, GradArena, allreduce_mean
+    _init(rank, world, port)
+    params = [_P([96, 128]), _P([128, 64]), _P([64, 64]), _P([40])]
+    outs = []
+    for chunked in (True, False):
+        arena = GradArena(params, dtype=torch.bfloat16, device="cpu")
+        arena.attach()
+        g = torch.Generator().manual_seed(200 + rank)
+        for p in params:
+            p.grad.add_(torch.randn(*p.shape, generator=g).to(torch.bfloat16))
+        if chunked:
+            o = arena.offsets
+            red = ChunkReducer(arena, [(o[0], o[1]), (o[1], o[3]), (o[3], o[3]), (o[3], arena.numel)])
+            red.begin()
+            for k in (1, 3):                         # ranges become final out of order, like layers in a backward pass
+                red.launch(k)
+            for k in range(4):                       # the rest; ranges already launched and the empty one are skipped
+                red.launch(k)
+            assert red.launched == 3
+            red.wait(3); red.wait(0)                 # the optimizer waits range by range
+            red.wait_all()
+        else:
+            allreduce_mean(arena, bucket_bytes=4096)
+        outs.append(arena.flat.clone())
+    q.put((rank, bool(torch.equal(outs[0], outs[1])), float(outs[0].float().abs().sum())))
+    dist.destroy_process_group()
+
+
+def test_chunk_reducer_equals_bucketed_allreduce_world2():
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker_chunk_reducer, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res = sorted(q.get(timeout=120) for _ in range(2))
+    for p in procs:
+        p.join(60)
+        assert p.exitcode == 0
+    assert all(same and total > 0 for _, same, total in res)
+    assert res[0][2] == res[1][2]
+
+
 def _worker_dead_peer(rank, world, port, q):
     from latentq_llm_b200.dp import GradArena, PeerLostError, StepGate, allreduce_mean
     _init(rank, world, port)

@@ -311,10 +311,12 @@ __global__ void __launch_bounds__(256) k_requant(const RequantParams p) {
 //    generic path.
 // =================================================================================================
 // Philox (or any external) dither: for a given Z the outcome is a step function of the 16-bit dither value h
-// (u = h/65536 - 0.5): entry = threshold T | outcome for h < T << 16 | outcome for h >= T << 24 (outcome = code << 4 | nibble).
-// Indexed by sign and magnitude of Z for |Z| < 32 (0x4200 bf16 patterns per sign).
-constexpr int ENCP_HALF = 0x4200, ENCP_ENTRIES = 2 * ENCP_HALF;
-__device__ uint32_t g_encp_table[4][ENCP_ENTRIES];
+// (u = h/65536 - 0.5): entry = outcome for h < T | outcome for h >= T << 8 | threshold T << 16 (outcome = code << 4 | nibble),
+// so that "h >= T" is the single unsigned comparison (h << 16 | 0xffff) >= entry.
+// Indexed by the bf16 pattern of Z itself for |Z| < 32: 0x0000..0x41ff and 0x8000..0xc1ff; the entries between the two
+// runs are never read (such a Z takes the generic path) and never written.
+constexpr int ENCP_HALF = 0x4200, ENCP_ENTRIES = 2 * ENCP_HALF, ENCP_SPAN = 0x8000 + ENCP_HALF;
+__device__ uint32_t g_encp_table[4][ENCP_SPAN];
 __device__ unsigned int g_encp_not_a_step[4];           // patterns whose outcome is not a single step in h (expected: 0)
 __global__ void __launch_bounds__(256) k_build_encp_table(int slot, Curve c) {
     for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < ENCP_ENTRIES; i += gridDim.x * blockDim.x) {
@@ -337,7 +339,7 @@ __global__ void __launch_bounds__(256) k_build_encp_table(int slot, Curve c) {
             for (uint32_t h = 0u; h < 65536u; h += 4099u) if (f(h) != lo) step_ok = false;
         }
         if (!step_ok) atomicAdd(&g_encp_not_a_step[slot], 1u);
-        g_encp_table[slot][i] = T | (out_lo << 16) | (out_hi << 24);
+        g_encp_table[slot][bits] = out_lo | (out_hi << 8) | (T << 16);
     }
 }
 
@@ -349,7 +351,7 @@ template <int DITHER> struct FastCfg {
     static constexpr bool PX = DITHER == LQ_DITHER_PHILOX;
     static constexpr int THREADS = PX ? 1024 : FAST_THREADS;          // the Philox table fills most of the SM's shared memory: one CTA
     static constexpr int MIN_CTAS = PX ? 1 : 2;
-    static constexpr int TABLE_BYTES = PX ? ENCP_ENTRIES * 4 : ENCZ_TABLE_ENTRIES;
+    static constexpr int TABLE_BYTES = PX ? ENCP_SPAN * 4 : ENCZ_TABLE_ENTRIES;
     static constexpr int SMEM_BYTES = TABLE_BYTES + 256 * FAST_RES_REPL * 4;
 };
 
@@ -364,12 +366,19 @@ __global__ void __launch_bounds__(FastCfg<DITHER>::THREADS, FastCfg<DITHER>::MIN
     constexpr int FAST_THREADS = FC::THREADS;                                 // (shadows the hash-dither constant)
     extern __shared__ __align__(16) uint8_t fsm[];
     uint8_t* encz = fsm;                                                      // hash: [65536] Z bits -> code << 4 | nibble
-    const uint32_t* encp = reinterpret_cast<const uint32_t*>(fsm);            // Philox: [ENCP_ENTRIES] threshold | outcomes
+    const uint32_t* encp = reinterpret_cast<const uint32_t*>(fsm);            // Philox: [ENCP_SPAN] outcomes | threshold
     uint32_t* tres = reinterpret_cast<uint32_t*>(fsm + FC::TABLE_BYTES);      // [256][FAST_RES_REPL]
     {   // stage the tables
         const uint4* src = FC::PX ? reinterpret_cast<const uint4*>(g_encp_table[enc_slot]) : reinterpret_cast<const uint4*>(g_encz_table[enc_slot]);
         uint4* dst = reinterpret_cast<uint4*>(fsm);
-        for (int i = threadIdx.x; i < FC::TABLE_BYTES / 16; i += FAST_THREADS) dst[i] = __ldg(src + i);
+        if (FC::PX) {       // the two populated runs of the table
+            for (int i = threadIdx.x; i < ENCP_HALF / 4; i += FAST_THREADS) {
+                dst[i] = __ldg(src + i);
+                dst[0x8000 / 4 + i] = __ldg(src + 0x8000 / 4 + i);
+            }
+        } else {
+            for (int i = threadIdx.x; i < FC::TABLE_BYTES / 16; i += FAST_THREADS) dst[i] = __ldg(src + i);
+        }
         for (int b = threadIdx.x; b < 256; b += FAST_THREADS) {
             // residual byte b holds two nibbles: high = even element, low = odd element; decode as the reference does
             const uint32_t lo = f32_to_bf16_bits(bf16r(res3_decode((uint32_t)b >> 4, p.dec)));
@@ -464,33 +473,38 @@ __global__ void __launch_bounds__(FastCfg<DITHER>::THREADS, FastCfg<DITHER>::MIN
         for (int h = 0; h < 2; ++h) {
             // everything after Z (rounding, residual, its code and carry, clamp) is one table byte per element:
             // code << 4 | nibble.  ev / od gather the bytes of the even / odd elements, pair j in byte j.
-            uint32_t ev[4], od[4];
+            uint32_t e_even, e_odd;
             if (FC::PX) {
                 // 16 dither bits per element from one Philox4x32-10 block per word: element 2j = low half of c[j], 2j+1 = high half
                 const uint64_t w64 = 2 * (uint64_t)wp + (uint64_t)h;
                 uint32_t c[4] = {(uint32_t)w64, (uint32_t)(w64 >> 32), (uint32_t)p.stream_id, (uint32_t)(p.stream_id >> 32)};
                 philox4x32_10(c, (uint32_t)p.seed, (uint32_t)(p.seed >> 32));
+                uint32_t ee[4], eo[4], se[4], so[4];
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
                     const uint32_t zb2 = h2u(Z[h][j]);
-                    const uint32_t mag = zb2 & 0x7fff7fffu;
-                    const uint32_t ie = (mag & 0xffffu) + ((zb2 >> 15) & 1u) * (uint32_t)ENCP_HALF;
-                    const uint32_t io = (mag >> 16) + (zb2 >> 31) * (uint32_t)ENCP_HALF;
-                    const uint32_t ee = encp[ie], eo = encp[io];
-                    const uint32_t he = c[j] & 0xffffu, ho = c[j] >> 16;
-                    ev[j] = __byte_perm(ee, 0u, (he >= (ee & 0xffffu)) ? 0x4443u : 0x4442u);
-                    od[j] = __byte_perm(eo, 0u, (ho >= (eo & 0xffffu)) ? 0x4443u : 0x4442u);
+                    ee[j] = encp[zb2 & 0xffffu]; eo[j] = encp[zb2 >> 16];
+                    // dither bits in the high half, ones below: >= entry exactly when dither >= threshold.
+                    // The outcome is byte 0 or byte 1 of the entry: se / so are that byte's index.
+                    se[j] = (__byte_perm(c[j], 0xffffffffu, 0x1044) >= ee[j]) ? 1u : 0u;
+                    so[j] = ((c[j] | 0xffffu) >= eo[j]) ? 1u : 0u;
                 }
+                // gather the chosen bytes two entries at a time: selector nibbles (byte of the first entry, 4 + byte of the second)
+                e_even = __byte_perm(__byte_perm(ee[0], ee[1], 0x40u + se[0] + (se[1] << 4)),
+                                     __byte_perm(ee[2], ee[3], 0x40u + se[2] + (se[3] << 4)), 0x5410);
+                e_odd = __byte_perm(__byte_perm(eo[0], eo[1], 0x40u + so[0] + (so[1] << 4)),
+                                    __byte_perm(eo[2], eo[3], 0x40u + so[2] + (so[3] << 4)), 0x5410);
             } else {
+                uint32_t ev[4], od[4];
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
                     const uint32_t zb2 = h2u(Z[h][j]);
                     ev[j] = encz[zb2 & 0xffffu];
                     od[j] = encz[zb2 >> 16];
                 }
+                e_even = __byte_perm(__byte_perm(ev[0], ev[1], 0x4040), __byte_perm(ev[2], ev[3], 0x4040), 0x5410);
+                e_odd = __byte_perm(__byte_perm(od[0], od[1], 0x4040), __byte_perm(od[2], od[3], 0x4040), 0x5410);
             }
-            const uint32_t e_even = __byte_perm(__byte_perm(ev[0], ev[1], 0x4040), __byte_perm(ev[2], ev[3], 0x4040), 0x5410);
-            const uint32_t e_odd = __byte_perm(__byte_perm(od[0], od[1], 0x4040), __byte_perm(od[2], od[3], 0x4040), 0x5410);
             // code byte j = code_even << 4 | code_odd; residual element k sits at bits 28 - 4k, i.e. pair j in byte 3 - j
             code_word[h] = (e_even & 0xF0F0F0F0u) | ((e_odd >> 4) & 0x0F0F0F0Fu);
             res_word[h] = __byte_perm(((e_even << 4) & 0xF0F0F0F0u) | (e_odd & 0x0F0F0F0Fu), 0u, 0x0123);

@@ -244,6 +244,9 @@ def _ensure_graph(self, ids, n_micro):
     torch.cuda.current_stream().wait_stream(side)
     self._graph = torch.cuda.CUDAGraph()
     self._capturing = True
+    quiet = getattr(torch.autograd.graph, "set_warn_on_accumulate_grad_stream_mismatch", None)
+    if quiet is not None:
+        quiet(False)            # warm-up (side stream) and capture (capture stream) differ on purpose
     try:
         with torch.cuda.graph(self._graph):
             out = self.model(input_ids=self._static_ids, labels=self._static_ids, use_cache=False)

@@ -157,6 +157,9 @@ def extra_measurements(torch, ops, pk, only=None, numel=1 << 30):
     g = torch.Generator(device="cuda").manual_seed(7)
     if only in (None, "requant"):
         _requant_part(torch, ops, pk, out, tm, g, numel)
+    if only in (None, "sweep"):
+        _sweep_part(torch, ops, pk, out, tm, g)
+        torch.cuda.empty_cache()
     if only in (None, "stream"):
         _stream_part(torch, ops, pk, out, tm, g)
     if only in (None, "a8w8"):
@@ -212,6 +215,31 @@ def _requant_part(torch, ops, pk, out, tm, g, numel):
     gbs = (8.0 + 4.0 / GROUP + 16.0 / 2048) * n2 / ms / 1e6
     out["adam_a16w4_fused"] = {"GB/s": round(gbs, 1), "frac_hbm": round(gbs / pk["hbm_gbs"], 3), "ms": round(ms, 3), "numel": n2}
     del codes, words, s, z, grad, st1, st2
+
+
+def _sweep_part(torch, ops, pk, out, tm, g):
+    """fold_delta GB/s over the weight counts of the requantize sweep (1e8 .. 7e9 weights, the last one beyond 2^32)."""
+    sizes = [int(x) // 2048 * 2048 for x in (1e8, 3e8, 1e9, 3e9, 7e9)]
+    nmax = sizes[-1]
+    codes = torch.randint(-128, 128, (nmax // 2,), device="cuda", generator=g, dtype=torch.int8)
+    words = torch.zeros(nmax // 8, dtype=torch.int32, device="cuda")
+    delta = torch.empty(nmax, device="cuda", dtype=torch.bfloat16)
+    for a in range(0, nmax, 1 << 30):
+        b = min(nmax, a + (1 << 30))
+        delta[a:b] = torch.randn(b - a, device="cuda", generator=g, dtype=torch.bfloat16) * 1e-4
+    s = torch.full((nmax // GROUP,), 0.008, device="cuda", dtype=torch.bfloat16)
+    z = torch.full((nmax // GROUP,), 8.0, device="cuda", dtype=torch.bfloat16)
+    rows = []
+    for n in sizes:
+        row = {"numel": n}
+        for name, dith in (("hash", ops.DITHER_HASH), ("philox", ops.DITHER_PHILOX)):
+            o = ops.make_opts(codec=ops.CODEC_THREEFOLD, dither=dith, seed=1, step=1, param_id=0)
+            ms = tm(lambda: ops.a16w4_fold_delta(codes[:n // 2], words[:n // 8], delta[:n], s[:n // GROUP], z[:n // GROUP], o))
+            gbs = (4.0 + 4.0 / GROUP) * n / ms / 1e6
+            row[name] = {"GB/s": round(gbs, 1), "frac_hbm": round(gbs / pk["hbm_gbs"], 3), "ms": round(ms, 3)}
+        rows.append(row)
+    out["requant_sweep_threefold"] = rows
+    del codes, words, delta, s, z
 
 
 def _stream_part(torch, ops, pk, out, tm, g, numel=1 << 28):
@@ -542,7 +570,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-extra", action="store_true", help="skip the secondary measurements and the CPU baseline")
-    ap.add_argument("--only", default="", choices=["", "requant", "stream", "a8w8", "decode"],
+    ap.add_argument("--only", default="", choices=["", "requant", "sweep", "stream", "a8w8", "decode"],
                     help="run one family of the secondary measurements only (profiling a single kernel)")
     ap.add_argument("--numel", type=int, default=1 << 30, help="weights in the requantize measurement")
     ap.add_argument("--shapes", default="", help="comma-separated indices into the shape list (profiling a smaller case)")

@@ -389,3 +389,49 @@ def test_fast_fold_path_int8_equals_generic_kernel(ops, monkeypatch, N, K):
         assert torch.equal(cf, cg), i
         assert torch.equal(wf, wg), i
     assert results["fast"][-1][0].unique().numel() > 100
+
+
+def test_requant_beyond_2p32_elements(ops):
+    """2^32 + 2^22 weights in one call (64-bit element indices, Philox counters beyond 2^29 words): slices at the start,
+    across the 2^32-element boundary and at the very end equal the same slices requantized on their own (hash dither is
+    position-independent), and the last words of the Philox run equal the oracle fed with the Philox stream at that
+    word offset."""
+    n = (1 << 32) + (1 << 22)
+    g = torch.Generator(device="cuda").manual_seed(3)
+    codes = torch.randint(-128, 128, (n // 2,), device="cuda", generator=g, dtype=torch.int8)
+    words = torch.randint(-2 ** 31, 2 ** 31 - 1, (n // 8,), device="cuda", generator=g, dtype=torch.int32)
+    delta = torch.empty(n, device="cuda", dtype=torch.bfloat16)
+    for a in range(0, n, 1 << 30):                                  # filled in pieces: no fp32 temporary of the full size
+        b = min(n, a + (1 << 30))
+        delta[a:b] = (torch.randn(b - a, device="cuda", generator=g, dtype=torch.float32) * 1e-3).to(torch.bfloat16)
+    s = (0.004 + 0.004 * torch.rand(n // 128, device="cuda", generator=g)).to(torch.bfloat16)
+    z = torch.randint(0, 16, (n // 128,), device="cuda", generator=g).to(torch.bfloat16)
+    T = 1 << 20
+    spans = [(0, T), ((1 << 32) - T // 2, (1 << 32) + T // 2), (n - T, n)]
+
+    def cut(a, b):
+        return (codes[a // 2:b // 2].clone(), words[a // 8:b // 8].clone(), delta[a:b].clone(),
+                s[a // 128:b // 128].clone(), z[a // 128:b // 128].clone())
+
+    # hash dither (the table-driven fast path)
+    o = ops.make_opts(codec=ops.CODEC_THREEFOLD, dither=ops.DITHER_HASH, math_dtype=torch.bfloat16, has_residual=True,
+                      mu_enc=1, mu_dec=2)
+    parts = [cut(a, b) for a, b in spans]
+    ops.a16w4_fold_delta(codes, words, delta, s, z, o)
+    for (a, b), (c, w, d, ss, zz) in zip(spans, parts):
+        ops.a16w4_fold_delta(c, w, d, ss, zz, o)
+        assert torch.equal(c, codes[a // 2:b // 2]) and torch.equal(w, words[a // 8:b // 8]), (a, b)
+    # Philox dither: counters are 64-bit word indices
+    nw = 4096
+    a = n - 8 * nw
+    c0, w0, d0, s0, z0 = cut(a, n)
+    seed, stream = 0x1234567, (9 << 32) | 4
+    o = ops.make_opts(codec=ops.CODEC_THREEFOLD, dither=ops.DITHER_PHILOX, math_dtype=torch.bfloat16, has_residual=True,
+                      mu_enc=2, mu_dec=1, seed=seed, step=9, param_id=4)
+    assert o.stream_id == stream
+    ops.a16w4_fold_delta(codes, words, delta, s, z, o)
+    dith = orc.philox_dither(seed, stream, nw, first_word=n // 8 - nw)
+    co, wo, _ = orc.a16w4_requant(s0.float().cpu().numpy(), z0.float().cpu().numpy(), codes=c0.cpu().numpy(),
+                                  words=w0.cpu().numpy(), delta=d0.float().cpu().numpy(), codec=orc.CODEC_THREEFOLD,
+                                  math_bf16=True, res_round_bf16=True, has_residual=True, mu_enc=2, mu_dec=1, dither=dith)
+    assert np.array_equal(codes[a // 2:].cpu().numpy(), co) and np.array_equal(words[a // 8:].cpu().numpy(), wo)

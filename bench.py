@@ -286,7 +286,7 @@ def _decode_part(torch, ops, pk, out, tm):
     # One pass over the four layers is captured in a CUDA graph and replayed, as a decode loop would do: at these
     # sizes a launch from Python costs more than the kernel runs.
     layers = build_layers(torch, ops)
-    for m in (1, 16, 128, 512):
+    for m in (1, 8, 16, 64, 128, 512):
         xs = [L["x"][:m].contiguous() for L in layers]
         ys = [torch.empty(m, L["N"], device="cuda", dtype=torch.bfloat16) for L in layers]
 

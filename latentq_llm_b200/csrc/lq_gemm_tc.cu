@@ -888,8 +888,11 @@ extern "C" {
 size_t lq_gemm_workspace_bytes(int kind, int64_t M, int64_t N, int64_t K) {
     if (kind < 0 || kind > 2 || M <= 0 || N <= 0 || K <= 0) return 0;
     // the forward plan depends on the group size (decode-sized kernel or tensor-core kernel): cover both
-    const Plan pl = make_plan(kind, M, N, K, 128), pl2 = make_plan(kind, M, N, K, 0);
-    const int splits = pl.splits > pl2.splits ? pl.splits : pl2.splits;
+    int splits = 1;
+    for (int group : {64, 128, 0}) {
+        const Plan pl = make_plan(kind, M, N, K, group);
+        if (pl.splits > splits) splits = pl.splits;
+    }
     if (splits <= 1) return 0;
     const int64_t R = (kind == KIND_DGRAD) ? K : N;
     return (size_t)splits * (size_t)M * (size_t)R * 4;

@@ -115,10 +115,13 @@ def test_a16w4_tmem_and_smem_operand_paths_agree_bitwise(ops, monkeypatch, M, N,
 
 
 @pytest.mark.parametrize("group", [64, 128, 256])
-@pytest.mark.parametrize("M,N,K", [(1, 320, 1024), (5, 4096, 2816), (8, 192, 768), (9, 1088, 2048), (16, 4096, 4096)])
+@pytest.mark.parametrize("M,N,K", [(1, 320, 1024), (5, 4096, 2816), (8, 192, 768), (9, 1088, 2048), (16, 4096, 4096),
+                                   (3, 960, 4096), (2, 576, 11008), (8, 4992, 11008), (12, 8960, 2048)])
 def test_a16w4_decode_sized_forward_all_routes(ops, monkeypatch, M, N, K, group):
-    """M <= 16: the row-block kernel (group 128 / 256), the split-K kernel (group 64, or forced) and the tensor-core
-    kernel (forced) against dequantize + fp32 matmul, with bias; ragged row blocks and uneven K slices included."""
+    """M <= 16: the streaming row-block kernel (group 128 / 256, at least two groups per warp, tokens staged in shared
+    memory; default for M <= 2, forced for the rest), the one-block-per-CTA row kernel (default for M > 2 and other K),
+    the split-K kernel (group 64, or forced) and the tensor-core kernel (forced) against dequantize + fp32 matmul,
+    with bias; ragged row blocks, uneven K slices and more row blocks than persistent CTAs included."""
     if K % group:
         pytest.skip("K must hold whole groups")
     codes, sb, zb = make_w4_layer(ops, N, K, seed=3, group=group)
@@ -127,11 +130,12 @@ def test_a16w4_decode_sized_forward_all_routes(ops, monkeypatch, M, N, K, group)
     bias = (torch.randn(N, device="cuda", generator=g) * 0.1).to(torch.bfloat16)
     W = ops.a16w4_dequant(codes, sb, zb, (N, K), torch.bfloat16, group)
     ref = x.float() @ W.float().t() + bias.float()
-    for env in ({}, {"LQ_SKINNY_SPLIT": "1"}, {"LQ_GEMM_NO_SKINNY": "1"}):
-        for k in ("LQ_SKINNY_SPLIT", "LQ_GEMM_NO_SKINNY"):
+    for env in ({}, {"LQ_SKINNY_NO_STREAM": "1"}, {"LQ_SKINNY_STREAM_ALL": "1"}, {"LQ_SKINNY_SPLIT": "1"}, {"LQ_GEMM_NO_SKINNY": "1"}):
+        for k in ("LQ_SKINNY_SPLIT", "LQ_GEMM_NO_SKINNY", "LQ_SKINNY_NO_STREAM", "LQ_SKINNY_STREAM_ALL"):
             monkeypatch.delenv(k, raising=False)
         for k, v in env.items():
             monkeypatch.setenv(k, v)
+        ops._ws_need.clear()            # the plan (and its scratch size) depends on these switches
         y = ops.gemm_a16w4_fwd(x, codes, sb, zb, bias, N, K, group)
         e_max, e_fro = rel_err(y, ref)
         assert e_max < RTOL and e_fro < RTOL, (env, e_max, e_fro)

@@ -336,3 +336,73 @@ def load_quantized_decoder(model: nn.Module, ckt, lbit: int = 4, gbit: int = 16)
                 setattr(sub, name, new)
                 swapped.append(new)
     return swapped
+
+
+# ---------------------------------------------------------------------------------------------------
+# Exact resume: everything the next optimizer step reads (the reference saves the model only, main0.py:585-588)
+# ---------------------------------------------------------------------------------------------------
+_STATE_KEYS = ("state1", "state2", "qmap1", "absmax1", "qmap2", "absmax2")
+
+
+@torch.no_grad()
+def save_training_state(model: nn.Module, optimizer: MyAdam, groups, path: str, step_no: int = 0) -> int:
+    """One .safetensors file with, per trained parameter in optimizer order (`<group>.<index>`): packed codes, residual
+    words and curve levels of a quantized weight, or the dense tensor; both optimizer states with their block parameters
+    and the step count.  Quantization parameters (`scales`, `zeros`) are frozen and travel with the model checkpoint
+    (`save_quantized_decoder`).  Returns the number of tensors written."""
+    from safetensors.torch import save_file
+    from .quant import QuantTensor
+    out = {"meta.step_no": torch.tensor([int(step_no)], dtype=torch.int64)}
+    for gi, group in enumerate(groups):
+        for pi, p in enumerate(group["params"]):
+            key = f"{gi}.{pi}"
+            if isinstance(p, QuantTensor):
+                out[key + ".codes"] = p.data.reshape(-1).contiguous().cpu()
+                res = getattr(p, "residual", None)
+                if res is not None and hasattr(res, "residual_int"):
+                    out[key + ".residual_int"] = res.residual_int.reshape(-1).contiguous().cpu()
+                    out[key + ".residual_meta"] = torch.tensor([res.mu, res.lock_mu, int(res.init)], dtype=torch.int32)
+            else:
+                out[key + ".dense"] = p.data.contiguous().cpu()
+            st = optimizer.state.get(p, {})
+            if len(st):
+                out[key + ".opt_step"] = torch.tensor([int(st["step"])], dtype=torch.int64)
+                for k in _STATE_KEYS:
+                    if k in st:
+                        out[f"{key}.opt_{k}"] = st[k].contiguous().cpu()
+    save_file(out, path)
+    return len(out)
+
+
+@torch.no_grad()
+def load_training_state(model: nn.Module, optimizer: MyAdam, groups, ckt) -> int:
+    """Restore `save_training_state` into a model / optimizer of the same structure, IN PLACE (parameter objects, gradient
+    arena views and a captured CUDA graph stay valid).  Returns the saved step number."""
+    if isinstance(ckt, str):
+        from safetensors.torch import load_file
+        ckt = load_file(ckt)
+    from .quant import QuantTensor
+    for gi, group in enumerate(groups):
+        for pi, p in enumerate(group["params"]):
+            key = f"{gi}.{pi}"
+            if isinstance(p, QuantTensor):
+                p.data.view(-1).copy_(ckt[key + ".codes"].to(p.data.device).view(p.data.dtype))
+                res = getattr(p, "residual", None)
+                if res is not None and key + ".residual_int" in ckt:
+                    res.residual_int.view(-1).copy_(ckt[key + ".residual_int"].to(res.residual_int.device))
+                    mu, lock_mu, init = (int(v) for v in ckt[key + ".residual_meta"].tolist())
+                    if not init:
+                        res.mu = lock_mu
+                        res._after_set_value(p.qparam[0].reshape(-1, 1))      # weight_scale, lock_mu, init = False
+                    res.mu, res.init = mu, bool(init)
+            else:
+                p.data.copy_(ckt[key + ".dense"].to(p.data.device))
+            if key + ".opt_step" in ckt:
+                st = optimizer.state[p]
+                if len(st) == 0:
+                    optimizer.init_state(group, p, gi, pi)
+                st["step"] = int(ckt[key + ".opt_step"][0])
+                for k in _STATE_KEYS:
+                    if f"{key}.opt_{k}" in ckt:
+                        st[k].copy_(ckt[f"{key}.opt_{k}"].to(st[k].device).view_as(st[k]))
+    return int(ckt["meta.step_no"][0])

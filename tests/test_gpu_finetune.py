@@ -93,3 +93,41 @@ def test_checkpoint_roundtrip_in_reference_key_layout(tmp_path):
     x = torch.randn(3, 16, 256, device="cuda").to(torch.bfloat16)
     with torch.no_grad():
         assert torch.equal(swapped[0](x), loaded[0](x))
+
+
+def test_training_state_checkpoint_resumes_bit_exactly(tmp_path):
+    """Four steps in one go against two steps, save, a fresh model + optimizer, load, two more steps: same losses, codes,
+    residual words, dense parameters and optimizer states (eager and captured routes)."""
+    from latentq_llm_b200 import finetune as ft
+
+    def fresh(use_graph):
+        model = ft.build_model("llama-tiny", "cuda", seed=11)
+        swapped = ft.quantize_decoder(model, lbit=4, gbit=16)
+        opt, groups = ft.build_optimizer(model, lr=2e-3)
+        return model, swapped, opt, groups, ft.LatentFineTuner(model, opt, groups, grad_accum=2, cuda_graph=use_graph)
+
+    def snapshot(swapped, opt, groups):
+        out = [m.weight.data.clone() for m in swapped] + [m.weight.residual.residual_int.clone() for m in swapped]
+        out += [p.data.clone() for p in groups[1]["params"]]
+        for g in groups:
+            for p in g["params"]:
+                out += [opt.state[p][k].clone() for k in ("state1", "state2") if k in opt.state[p]]
+        return out
+
+    for use_graph in (False, True):
+        batches = ft.synthetic_batches(2, 2, 64, 1024, "cuda", seed=5)
+        model, swapped, opt, groups, tuner = fresh(use_graph)
+        ref_losses = [float(tuner.step(batches)) for _ in range(4)]
+        ref = snapshot(swapped, opt, groups)
+
+        model, swapped, opt, groups, tuner = fresh(use_graph)
+        first = [float(tuner.step(batches)) for _ in range(2)]
+        path = str(tmp_path / f"state_{int(use_graph)}.safetensors")
+        assert ft.save_training_state(model, opt, groups, path, step_no=tuner.step_no) > 10
+        model, swapped, opt, groups, tuner = fresh(use_graph)          # same initial weights; state comes from the file
+        tuner.step_no = ft.load_training_state(model, opt, groups, path)
+        assert tuner.step_no == 2
+        second = [float(tuner.step(batches)) for _ in range(2)]
+        assert first + second == ref_losses
+        got = snapshot(swapped, opt, groups)
+        assert len(got) == len(ref) and all(torch.equal(a, b) for a, b in zip(got, ref))

@@ -27,6 +27,25 @@ __device__ __forceinline__ void mma_16816(float (&d)[4], const uint32_t (&a)[4],
         : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
         : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
+// Programmatic dependent launch: a decode step is a chain of these launches.  A kernel lets its successor start
+// (launch_dependents) once its own weight loads are issued, and reads the tokens — the only operand the predecessor
+// may have produced — after pdl_wait(), which returns when the predecessor grid has completed and its writes are
+// visible.  The successor's launch latency and first weight-load latency then overlap this kernel's tail.  Both
+// are no-ops for a launch without the attribute; only kernels that call launch_dependents can be overtaken, and they
+// write nothing but their output.
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+template <typename... KArgs, typename... Args>
+static void launch_pdl(void (*kern)(KArgs...), unsigned grid, unsigned block, size_t smem, cudaStream_t st, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid); cfg.blockDim = dim3(block); cfg.dynamicSmemBytes = smem; cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = getenv("LQ_SKINNY_NO_PDL") ? 0 : 1;
+    cfg.attrs = attr; cfg.numAttrs = 1;
+    cudaLaunchKernelEx(&cfg, kern, KArgs(args)...);
+}
+
 // d = a * b (no accumulator input: starts a new group sum without clearing registers first)
 __device__ __forceinline__ void mma_16816_start(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
     asm volatile(
@@ -242,11 +261,13 @@ __global__ void __launch_bounds__(RB_WARPS * 32, 2) k_skinny_rows(const SkinnyPa
         nx_a = (uint32_t)__ldg(sca + 1) | ((uint32_t)__ldg(zpa + 1) << 16);
         nx_b = (uint32_t)__ldg(scb + 1) | ((uint32_t)__ldg(zpb + 1) << 16);
     }
+    pdl_launch_dependents();        // weight and group-parameter loads are issued: the next launch may start
+    pdl_wait();                     // the tokens may be the previous launch's output
     uint4 xn[MT][4];
 #pragma unroll
     for (int m = 0; m < MT; ++m)
 #pragma unroll
-        for (int j = 0; j < 4; ++j) xn[m][j] = (XPF && xp[m] && n_chunks > 0) ? __ldg(xp[m] + j) : make_uint4(0, 0, 0, 0);
+        for (int j = 0; j < 4; ++j) xn[m][j] = (XPF && xp[m] && n_chunks > 0) ? xp[m][j] : make_uint4(0, 0, 0, 0);
 
     const uint32_t ones[4] = {0x3F803F80u, 0x3F803F80u, 0x3F803F80u, 0x3F803F80u};   // bf16 1.0
     float tot[MT][4], acc[MT][2][4], sx[MT][4];     // two accumulator chains per token group, sx from an all-ones A
@@ -270,9 +291,9 @@ __global__ void __launch_bounds__(RB_WARPS * 32, 2) k_skinny_rows(const SkinnyPa
                     for (int j = 0; j < 4; ++j) {
                         if (XPF) {
                             xc[m][j] = xn[m][j];
-                            if (xp[m] && c + 1 < n_chunks) xn[m][j] = __ldg(xp[m] + (c + 1) * (RB_CHUNK * 2 / 16) + j);
+                            if (xp[m] && c + 1 < n_chunks) xn[m][j] = xp[m][(c + 1) * (RB_CHUNK * 2 / 16) + j];
                         } else {
-                            xc[m][j] = xp[m] ? __ldg(xp[m] + c * (RB_CHUNK * 2 / 16) + j) : make_uint4(0, 0, 0, 0);
+                            xc[m][j] = xp[m] ? xp[m][c * (RB_CHUNK * 2 / 16) + j] : make_uint4(0, 0, 0, 0);
                         }
                     }
                 const uint32_t wsa[4] = {ca.x, ca.y, ca.z, ca.w}, wsb[4] = {cq.x, cq.y, cq.z, cq.w};
@@ -384,9 +405,11 @@ __global__ void __launch_bounds__(RB_WARPS * 32, 2) k_skinny_stream(const Skinny
 #pragma unroll
     for (int m = 0; m < MT; ++m) xrow[m] = min(m * 8 + g, p.M - 1);
 
+    pdl_launch_dependents();        // weight and group-parameter loads are issued: the next launch may start
     // ---- once per CTA, while the first weight loads are in flight: token fragments and per-group token sums
     for (int i = tid; i < gpr * 8 * MT; i += RB_WARPS * 32) sxs[i] = 0.0f;
     __syncthreads();
+    pdl_wait();                     // the tokens may be the previous launch's output
     {
         const int kw_per_tok = p.K / 8, items = p.M * kw_per_tok;
         for (int base = 0; base < items; base += 2 * RB_WARPS * 32) {
@@ -398,7 +421,7 @@ __global__ void __launch_bounds__(RB_WARPS * 32, 2) k_skinny_stream(const Skinny
                 const int idx = base + h * RB_WARPS * 32 + tid;
                 on[h] = idx < items;
                 tok[h] = on[h] ? idx / kw_per_tok : 0; kw[h] = on[h] ? idx - tok[h] * kw_per_tok : 0;
-                v[h] = on[h] ? __ldg(reinterpret_cast<const uint4*>(p.x + (size_t)tok[h] * p.K) + kw[h]) : make_uint4(0, 0, 0, 0);
+                v[h] = on[h] ? reinterpret_cast<const uint4*>(p.x + (size_t)tok[h] * p.K)[kw[h]] : make_uint4(0, 0, 0, 0);
             }
 #pragma unroll
             for (int h = 0; h < 2; ++h) {
@@ -521,7 +544,7 @@ static int launch_skinny_stream_v(const SkinnyParams& p, int x_stride, size_t sm
         if (e != cudaSuccess) { set_cuda_error(e, "cudaFuncSetAttribute(k_skinny_stream)"); return LQ_ECUDA; }
         attr_done[dev] = true;
     }
-    k_skinny_stream<MT, GC><<<grid, RB_WARPS * 32, smem, st>>>(p, x_stride);
+    launch_pdl(k_skinny_stream<MT, GC>, grid, RB_WARPS * 32, smem, st, p, x_stride);
     return check_launch("k_skinny_stream");
 }
 
@@ -551,8 +574,8 @@ int launch_skinny_rows(const SkinnyParams& p, cudaStream_t st) {
         return launch_skinny_stream(p, st);
     const unsigned grid = (unsigned)((p.N + 15) / 16);
     const bool g128 = p.group == 128;
-    if (p.M <= 8) { if (g128) k_skinny_rows<1, 1><<<grid, RB_WARPS * 32, 0, st>>>(p); else k_skinny_rows<1, 2><<<grid, RB_WARPS * 32, 0, st>>>(p); }
-    else { if (g128) k_skinny_rows<2, 1><<<grid, RB_WARPS * 32, 0, st>>>(p); else k_skinny_rows<2, 2><<<grid, RB_WARPS * 32, 0, st>>>(p); }
+    if (p.M <= 8) { if (g128) launch_pdl(k_skinny_rows<1, 1>, grid, RB_WARPS * 32, 0, st, p); else launch_pdl(k_skinny_rows<1, 2>, grid, RB_WARPS * 32, 0, st, p); }
+    else { if (g128) launch_pdl(k_skinny_rows<2, 1>, grid, RB_WARPS * 32, 0, st, p); else launch_pdl(k_skinny_rows<2, 2>, grid, RB_WARPS * 32, 0, st, p); }
     return check_launch("k_skinny_rows");
 }
 

@@ -249,4 +249,6 @@ def main(ref):
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) < 2:
+        sys.exit("usage: python tests/golden/gen_golden.py /path/to/latentQ_LLM")
+    main(sys.argv[1])

@@ -10,6 +10,7 @@
 #include <string>
 
 #include "lq_common.cuh"
+#include <cuda_fp16.h>
 #include "lq_requant.cuh"
 
 namespace lq {
@@ -626,11 +627,12 @@ __global__ void __launch_bounds__(FAST8_THREADS, 1) k_fold_fast8(const RequantPa
         } else {
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
-                // two int8 codes -> exact fp32 through the 2^23 magic (byte ^ 0x80 = code + 128), then one packed conversion
-                const uint32_t word = (j < 2) ? cur.pk.x : cur.pk.y;
-                const uint32_t b0 = ((word >> (16 * (j & 1))) & 0xffu) ^ 0x80u, b1 = ((word >> (16 * (j & 1) + 8)) & 0xffu) ^ 0x80u;
-                const float c0 = __fsub_rn(__uint_as_float(0x4B000000u | b0), 8388736.0f), c1 = __fsub_rn(__uint_as_float(0x4B000000u | b1), 8388736.0f);
-                __nv_bfloat162 v = __hmul2_rn(__floats2bfloat162_rn(c0, c1), s2);
+                // two int8 codes -> exact bf16 pair: byte ^ 0x80 = code + 128 goes into the mantissa of fp16 1024.0
+                // (1024 + code + 128, exact), minus 1152 in fp16 (exact), widened and packed to bf16 (integers up to 256 are exact)
+                const uint32_t wx = ((j < 2) ? cur.pk.x : cur.pk.y) ^ 0x80808080u;
+                const uint32_t h2 = __byte_perm(wx, 0x64646464u, (j & 1) ? 0x4342 : 0x4140);
+                const float2 cf = __half22float2(__hsub2(*reinterpret_cast<const __half2*>(&h2), __floats2half2_rn(1152.0f, 1152.0f)));
+                __nv_bfloat162 v = __hmul2_rn(__floats2bfloat162_rn(cf.x, cf.y), s2);
                 if (USE_RES) {
                     const uint32_t b = (cur.rw >> (24 - 8 * j)) & 0xffu;
                     v = __hadd2_rn(__hmul2_rn(u2h(tres[b * FAST_RES_REPL + tres_lane]), s2), v);

@@ -141,6 +141,34 @@ def test_a16w4_decode_sized_forward_all_routes(ops, monkeypatch, M, N, K, group)
         assert e_max < RTOL and e_fro < RTOL, (env, e_max, e_fro)
 
 
+@pytest.mark.parametrize("M", [1, 2, 8, 16])
+def test_a16w4_decode_chain_of_dependent_launches(ops, monkeypatch, M):
+    """Decode kernels are launched with programmatic stream serialization: a launch may start (and fetch its weights)
+    while its predecessor is still running, but must read its tokens only once the predecessor has finished.  A chain in
+    which every launch consumes the previous launch's output, without any synchronisation in between, must give exactly
+    the result of the same chain with the early start switched off."""
+    K = N = 2048
+    layers = [make_w4_layer(ops, N, K, seed=20 + i) for i in range(3)]
+    g = torch.Generator(device="cuda").manual_seed(M)
+    x0 = torch.randn(M, K, device="cuda", generator=g).to(torch.bfloat16)
+    outs = {}
+    for mode in ("pdl", "plain"):
+        if mode == "plain":
+            monkeypatch.setenv("LQ_SKINNY_NO_PDL", "1")
+        else:
+            monkeypatch.delenv("LQ_SKINNY_NO_PDL", raising=False)
+        bufs = [torch.empty(M, N, device="cuda", dtype=torch.bfloat16) for _ in range(2)]
+        x = x0
+        for it in range(30):                                    # 30 dependent launches, ping-pong buffers
+            codes, sb, zb = layers[it % 3]
+            y = ops.gemm_a16w4_fwd(x, codes, sb, zb, None, N, K, out=bufs[it % 2])
+            x = y
+        torch.cuda.synchronize()
+        outs[mode] = x.clone()
+    assert torch.isfinite(outs["pdl"].float()).all()
+    assert torch.equal(outs["pdl"], outs["plain"])
+
+
 def _a8_inputs(M, N, K, seed):
     rng = np.random.default_rng(seed)
     x = rng.standard_normal((M, K)).astype(np.float32)

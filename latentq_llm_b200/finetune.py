@@ -111,8 +111,9 @@ def build_optimizer(model: nn.Module, lr: float = 1e-3, obit: int = 8, mu_f: int
 
 
 class LatentFineTuner:
-    """One optimizer step = `grad_accum` micro-batches of forward/backward on this rank, one bucketed all-reduce of
-    the gradient arena, one MyAdam step (dequantize + Adam + stochastic requantize per quantized weight)."""
+    """One optimizer step = `grad_accum` micro-batches of forward/backward on this rank, one mean all-reduce of the
+    gradient arena (by runs of layers, overlapped with the last backward pass and the optimizer step), one MyAdam step
+    (dequantize + Adam + stochastic requantize per quantized weight)."""
 
     def __init__(self, model, optimizer, groups, grad_accum: int = 8, group=None, gate_timeout_s: float = 600.0,
                  cuda_graph: bool = False, overlap_chunks: int = 8):

@@ -308,7 +308,7 @@ def _decode_part(torch, ops, pk, out, tm):
 
 def finetune_measurement(torch, arch="opt-1.3b", steps=2, warmup=1, micro_batch=4, seq=512, grad_accum=8, cuda_graph=True,
                          decode_batches=()):
-    """Latent fine-tune step (BASELINE config 4): A16W4 int4 group-128 latent weights, seq 512, micro-batch 4,
+    """Latent fine-tune step (the fine-tune configuration of the benchmark set): A16W4 int4 group-128 latent weights, seq 512, micro-batch 4,
     grad-accum 8 per rank, uniform random token ids, data-parallel over the ranks of this launch: the bf16
     gradient arena is all-reduced once per optimizer step, under the last backward pass and the optimizer step.  tokens/s = world * micro_batch * seq * grad_accum / step time.
     Token ids come from pinned host memory every step and the loss is read back (end-to-end through the module API)."""

@@ -8,13 +8,23 @@
  *
  * Pinning status:
  *   - functions restating pure-torch reference code (utils/quant.py,
- *     PTQ/quant/quantizer.py, PTQ/quant/quant_linear.py) are pinned by golden
- *     vectors produced by executing the reference's own functions on CPU
+ *     PTQ/quant/quantizer.py, PTQ/quant/quant_linear.py), including three
+ *     MyAdam.update_step steps and the per-tensor activation quantizer of
+ *     QLinearFunctionA8W8_dynamic.forward, are pinned by golden vectors
+ *     produced by executing the reference's own functions on CPU
  *     (tests/golden/gen_golden.py);
  *   - the 3-fold / uniform residual codecs of utils/cuda_src/
- *     multi_random_quant_kernel.cu and the external torch_int int8 GEMM have
- *     no golden vectors anywhere in the reference and were not executed:
- *     PARITY UNPINNED for those (restated from source text / call sites).
+ *     multi_random_quant_kernel.cu are pinned by vectors produced from the
+ *     reference's own kernel text compiled for the CPU (oracle/build_ref.py:
+ *     the kernels are never launched on a GPU), over the codecs' whole bf16
+ *     input domain and an fp32 grid, with and without FMA contraction (both
+ *     builds give the same bytes);
+ *   - the external torch_int int8 GEMM has no source in the reference: its
+ *     int32 accumulators are mathematically determined, its bf16 epilogue is
+ *     PARITY UNPINNED (inferred from the call sites);
+ *   - how torch's CUDA elementwise kernels round the Adam ops
+ *     (orc_adam_chain_cuda) is not reference code at all: it is checked on a
+ *     GPU against torch's own ops.
  *
  * Every floating-point expression below is a separately rounded IEEE fp32
  * operation (compile with -ffp-contract=off) except where fmaf() is written
@@ -421,21 +431,21 @@ ORC_API void orc_gemm_i8_acc(const int8_t* x, const int8_t* w, int64_t M, int64_
         }
 }
 
-/* ---------- C.7: MyAdam.update_step on one A16W4 parameter, fp32 or bf16 chain
- * (utils/quant.py:1062-1148).  States are the uint8 block codec above with
- * block = 2048 (or 128).  step is the value AFTER the increment at :1095.     */
-ORC_API void orc_adam_dense(float* p, const float* g, float* m, float* s2, int64_t n,
-                            float beta1, float beta2, float eps, float step_size, float wd, int math_bf16) {
-    /* m: exp_avg; s2: stored sqrt(v)+eps (second state is squared on load, :1089) */
-    int bf = math_bf16;
+/* ---------- C.7: the Adam chain of MyAdam.update_step as torch's CPU elementwise kernels evaluate it in fp32
+ * (utils/quant.py:1098-1112 with CPU tensors, the configuration the golden optimizer steps were produced in):
+ *   exp_avg.mul_(b1).add_(g, alpha=1-b1)            -> fma(alpha, g, fl(m*b1))
+ *   exp_avg_sq.mul_(b2).addcmul_(g, g, value=1-b2)  -> fma(fl(value*g), g, fl(v*b2))
+ *   sqrt_().add_(eps)                               -> fl(fl(sqrt(v)) + eps)
+ *   pdata.addcdiv_(exp_avg, denom, value=-step)     -> fl(p + fl(fl(value*m)/den))      (no contraction)
+ * m: exp_avg; d: on entry v (already squared), on exit sqrt(v)+eps.  Pinned by the golden optimizer steps.  */
+ORC_API void orc_adam_chain_cpu(float* p, const float* g, float* m, float* d, int64_t n, float beta1, float beta2,
+                                float omb1, float omb2, float eps, float neg_step) {
     for (int64_t i = 0; i < n; ++i) {
-        float grad = g[i];
-        if (wd != 0.0f) grad = rnd(grad + rnd(wd * p[i], bf), bf);
-        float ea = rnd(rnd(m[i] * beta1, bf) + rnd((1.0f - beta1) * grad, bf), bf);
-        float v = rnd(s2[i] * s2[i], bf);
-        float eq = rnd(rnd(v * beta2, bf) + rnd(rnd((1.0f - beta2) * grad, bf) * grad, bf), bf);
-        float den = rnd(rnd(sqrtf(eq), bf) + eps, bf);
-        p[i] = rnd(p[i] + rnd(rnd(-step_size * ea, bf) / den, bf), bf);
-        m[i] = ea; s2[i] = den;
+        float ea = fmaf(omb1, g[i], m[i] * beta1);
+        float v = fmaf(omb2 * g[i], g[i], d[i] * beta2);
+        float den = sqrtf(v) + eps;
+        float t = neg_step * ea;
+        p[i] = p[i] + t / den;
+        m[i] = ea; d[i] = den;
     }
 }

@@ -244,6 +244,99 @@ def main(ref):
     out["a8w8_qweight"], out["a8w8_qzeros"] = a8.qweight.numpy(), a8.qzeros.numpy().astype(np.int32)
     out["a8w8_scales"] = f32(a8.scales.reshape(-1))
 
+    # --- a14: the activation quantizer inside QLinearFunctionA8W8_dynamic.forward (utils/quant.py:258-272) -----
+    # The class body is executed as written; the external int8 GEMM is replaced by a recorder that keeps its
+    # arguments (the quantized activations, the bias/qscales operand and alpha = clampv/127).
+    seen = {}
+
+    def linear_a8_w8_bbf16_obf16(x8, w8, bias_over_scale, alpha):
+        seen["x8"], seen["alpha"], seen["bias_arg"] = x8.clone(), alpha.clone(), bias_over_scale.clone()
+        return torch.zeros(x8.shape[0], w8.shape[0], dtype=bias_over_scale.dtype)
+
+    dyn = slice_module(qpath, {"QLinearFunctionA8W8_dynamic"},
+                       {"linear_a8_w8_bbf16_obf16": linear_a8_w8_bbf16_obf16, "dict_temp": []})
+
+    class Ctx:
+        def save_for_backward(self, *a):
+            pass
+    for tag, dt in (("f32", torch.float32), ("bf16", torch.bfloat16)):
+        Xa = torch.randn(24, 256, generator=g)
+        Xa[:, 11] *= 20.0
+        Xa = Xa.to(dt)
+        w8 = torch.randint(-128, 128, (16, 256), generator=g, dtype=torch.int8)
+        qsc = (torch.rand(16, generator=g) * 1e-2 + 1e-3).to(dt)
+        bia = (torch.randn(16, generator=g) * 0.1).to(dt)
+        dyn["QLinearFunctionA8W8_dynamic"].forward(Ctx(), Xa, w8, (None, qsc), bia)
+        out[f"pt_x_{tag}"] = f32(Xa)
+        out[f"pt_x8_{tag}"] = seen["x8"].numpy()
+        out[f"pt_clampv_{tag}"] = f32(Xa.max().reshape(1))
+        out[f"pt_alpha_{tag}"] = f32(seen["alpha"].reshape(1))
+
+    # --- a9-a11: the CUDA residual codecs, from the reference's own kernel text compiled for the CPU ------------
+    # (oracle/build_ref.py: no GPU launch).  Built with and without FMA contraction; the fixtures are the FMA
+    # build (nvcc's default), `rc_variants_agree` records whether the other build produced the same bytes.
+    import ctypes as C
+    sys.path.insert(0, os.path.dirname(os.path.dirname(OUT)))
+    import oracle as orc
+    from oracle import build_ref
+    build_ref.build(ref)
+    libs = {v: C.CDLL(build_ref.lib_path(v)) for v in ("fma", "nofma")}
+
+    def p_(a):
+        return a.ctypes.data_as(C.c_void_p)
+
+    def bf(a16):
+        return (a16.astype(np.uint32) << 16).view(np.float32)
+    pats, _ = orc.bf16_codec_domain()
+    all_nibbles = np.array([0x01234567, 0x89abcdef - (1 << 32)], dtype=np.int64).astype(np.int32)
+    agree = True
+    for mu in range(4):
+        k1, b1, k2, b2, k3 = orc.curve_args(mu)
+        args = (k1, C.c_float(b1), k2, C.c_float(b2), k3)
+        xg = orc.f32_codec_grid(mu)
+        res = {}
+        for v, L in libs.items():
+            r = {}
+            x = pats.copy(); y = np.empty(x.size // 8, np.int32); c8 = np.empty(8, np.float32)
+            L.ref_quant_bf16(p_(x), p_(y), *args, y.size, p_(c8))
+            r["q_bf16_words"], r["q_bf16_flags"], r["q_consts"] = y, np.packbits(bf(x) != 0), c8
+            x = xg.copy(); y = np.empty(x.size // 8, np.int32)
+            L.ref_quant_f32(p_(x), p_(y), *args, y.size, None)
+            r["q_f32_words"], r["q_f32_flags"] = y, np.packbits(x != 0)
+            assert set(np.unique(x)) <= {0.0, 1.0}
+            o16 = np.empty(16, np.uint16); c7 = np.empty(7, np.float32)
+            L.ref_dequant_bf16(p_(all_nibbles), p_(o16), *args, 2, p_(c7))
+            o32 = np.empty(16, np.float32)
+            L.ref_dequant_f32(p_(all_nibbles), p_(o32), *args, 2, None)
+            r["dq_bf16"], r["dq_f32"], r["dq_consts"] = bf(o16), o32, c7
+            res[v] = r
+        for k, a in res["fma"].items():
+            out[f"rc_{k}_mu{mu}"] = a
+            agree &= np.array_equal(a, res["nofma"][k])
+    xg = orc.f32_codec_grid(0, seed=77)
+    res = {}
+    for v, L in libs.items():
+        r = {}
+        x = pats.copy(); y = np.empty(x.size // 8, np.int32)
+        L.ref_uniform_quant_bf16(p_(x), p_(y), y.size)
+        r["uq_bf16_words"], r["uq_bf16_flags"] = y, np.packbits(bf(x) != 0)
+        x = xg.copy(); y = np.empty(x.size // 8, np.int32)
+        L.ref_uniform_quant_f32(p_(x), p_(y), y.size)
+        r["uq_f32_words"], r["uq_f32_flags"] = y, np.packbits(x != 0)
+        x = xg.copy(); y = np.empty(x.size // 8, np.int32)
+        L.ref_uniform_quant_s_f32(p_(x), p_(y), y.size)
+        r["uqs_f32_words"], r["uqs_f32_flags"] = y, np.packbits(x != 0)
+        o16 = np.empty(16, np.uint16); o32 = np.empty(16, np.float32)
+        L.ref_uniform_dequant_bf16(p_(all_nibbles), p_(o16), 2)
+        L.ref_uniform_dequant_f32(p_(all_nibbles), p_(o32), 2)
+        r["udq_bf16"], r["udq_f32"] = bf(o16), o32
+        res[v] = r
+    for k, a in res["fma"].items():
+        out[f"rc_{k}"] = a
+        agree &= np.array_equal(a, res["nofma"][k])
+    out["rc_variants_agree"] = np.array([agree])
+    out["rc_all_nibbles"] = all_nibbles
+
     np.savez_compressed(os.path.join(OUT, "reference_vectors.npz"), **out)
     print("wrote", len(out), "arrays,", os.path.getsize(os.path.join(OUT, "reference_vectors.npz")), "bytes")
 

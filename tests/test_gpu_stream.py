@@ -162,6 +162,53 @@ def test_uniform_ext_codecs_vs_oracle(ops, dtype):
     assert np.array_equal(out.float().cpu().numpy(), orc.resu_dequant(wo))
 
 
+@pytest.mark.parametrize("mu", [0, 1, 2, 3])
+def test_threefold_codec_golden_reference_kernels(ops, golden, mu):
+    """lq_res3_quant / lq_res3_dequant against what the reference's own kernel text computes (fixtures made by
+    oracle/build_ref.py): every bf16 input of the codec's domain, and an fp32 grid with the segment boundaries."""
+    k = orc.curve_args(mu)
+    pats, _ = orc.bf16_codec_domain()
+    for tag, x in (("bf16", torch.from_numpy(pats.view(np.int16)).cuda().view(torch.bfloat16)),
+                   ("f32", dev(orc.f32_codec_grid(mu)))):
+        words = torch.empty(x.numel() // 8, dtype=torch.int32, device="cuda")
+        ops.res3_quant(x, words, *k)
+        assert np.array_equal(words.cpu().numpy(), golden[f"rc_q_{tag}_words_mu{mu}"])
+        assert np.array_equal(np.packbits(x.float().cpu().numpy() != 0), golden[f"rc_q_{tag}_flags_mu{mu}"])
+    nib = dev(golden["rc_all_nibbles"])
+    for tag, dt in (("bf16", torch.bfloat16), ("f32", torch.float32)):
+        out = torch.empty(16, dtype=dt, device="cuda")
+        ops.res3_dequant(nib, out, *k)
+        assert np.array_equal(out.float().cpu().numpy(), golden[f"rc_dq_{tag}_mu{mu}"])
+
+
+def test_uniform_ext_codecs_golden_reference_kernels(ops, golden):
+    pats, _ = orc.bf16_codec_domain()
+    x = torch.from_numpy(pats.view(np.int16)).cuda().view(torch.bfloat16)
+    words = torch.empty(x.numel() // 8, dtype=torch.int32, device="cuda")
+    ops.resu_quant(x, words)
+    assert np.array_equal(words.cpu().numpy(), golden["rc_uq_bf16_words"])
+    assert np.array_equal(np.packbits(x.float().cpu().numpy() != 0), golden["rc_uq_bf16_flags"])
+    for fn, tag in ((ops.resu_quant, "uq"), (ops.resu_quant_s, "uqs")):
+        x = dev(orc.f32_codec_grid(0, seed=77))
+        words = torch.empty(x.numel() // 8, dtype=torch.int32, device="cuda")
+        fn(x, words)
+        assert np.array_equal(words.cpu().numpy(), golden[f"rc_{tag}_f32_words"])
+        assert np.array_equal(np.packbits(x.cpu().numpy() != 0), golden[f"rc_{tag}_f32_flags"])
+    nib = dev(golden["rc_all_nibbles"])
+    for tag, dt in (("bf16", torch.bfloat16), ("f32", torch.float32)):
+        out = torch.empty(16, dtype=dt, device="cuda")
+        ops.resu_dequant(nib, out)
+        assert np.array_equal(out.float().cpu().numpy(), golden[f"rc_udq_{tag}"])
+
+
+def test_act_quant_per_tensor_golden(ops, golden):
+    """The quantizer inside QLinearFunctionA8W8_dynamic.forward as the reference executed it on bf16 activations."""
+    xb = dev(golden["pt_x_bf16"], torch.bfloat16)
+    x8, clampv = ops.act_quant_per_tensor(xb)
+    assert float(clampv) == float(golden["pt_clampv_bf16"][0])
+    assert np.array_equal(x8.cpu().numpy(), golden["pt_x8_bf16"])
+
+
 def test_philox_stream_matches_oracle(ops):
     d = ops.philox_dither(0x1234567887654321, (7 << 32) | 3, 4096, "cuda", first_word=(1 << 33) + 5)
     assert np.array_equal(d.cpu().numpy(), orc.philox_dither(0x1234567887654321, (7 << 32) | 3, 4096, first_word=(1 << 33) + 5))

@@ -226,6 +226,10 @@ LQ_API size_t lq_gemm_a16w4_fwd_static_max_bytes(void);
 LQ_API int lq_gemm_a16w4_fwd_static(const void* x, const int8_t* qweight, const void* scales, const void* zeros,
                                     const void* bias, void* y, int64_t M, int64_t N, int64_t K, int group,
                                     lq_stream_t stream);
+/* Diagnostic for the entry point above (no counterpart in the reference): copies n_floats fp32 partial sums,
+ * starting at element first_float, out of the built-in array of the CURRENT device into host memory.
+ * Synchronises with the device; allocates nothing. */
+LQ_API int lq_gemm_a16w4_fwd_static_peek(float* host_out, size_t first_float, size_t n_floats);
 
 /* Every device-side wait in the GEMM kernels is bounded; when one expires the kernel gives up cleanly and
  * raises a device flag.  This call synchronises with the device, returns LQ_ETIMEOUT if the flag is set
@@ -238,6 +242,15 @@ LQ_API int lq_gemm_device_status(int reset);
  * accumulator, [4] MMA role total, [5] dequant waiting for TMA data, [6] dequant role total,
  * [7] epilogue waiting for an accumulator, [8] epilogue role total, [9] number of CTAs. */
 LQ_API int lq_gemm_profile(int enable, unsigned long long* out16);
+
+/* Issue-rate microbenchmark of the tensor cores (no counterpart in the reference): `ctas` CTAs each issue n_mma
+ * tcgen05.mma instructions of shape 128 x n x (32 bytes of k) — kind LQ_GEMM_A8W8: int8 operands, 32 k; otherwise
+ * bf16, 16 k — on operands resident in shared memory (a_in_tmem != 0: bf16 A operand in tensor memory), rotating over
+ * n_acc independent accumulators (n_acc * n <= 256).  The measured int8 / bf16 ceilings that the GEMM rooflines are
+ * quoted against come from this call.  With max_cycles_out == NULL the launch is asynchronous (time it with events);
+ * otherwise the call synchronises and returns the longest per-CTA cycle count of the run. */
+LQ_API int lq_mma_issue_rate(int kind, int a_in_tmem, int n, int n_acc, int n_mma, int ctas,
+                             unsigned long long* max_cycles_out, lq_stream_t stream);
 
 #ifdef __cplusplus
 }

@@ -92,7 +92,9 @@ SIGNATURES = {
     "lq_gemm_profile": [_i, _p],
     "lq_gemm_a16w4_fwd_static_max_bytes": [],
     "lq_gemm_a16w4_fwd_static": [_p, _p, _p, _p, _p, _p, _i64, _i64, _i64, _i, _p],
+    "lq_gemm_a16w4_fwd_static_peek": [_p, _sz, _sz],
     "lq_gemm_a8w8": [_p, _p, _p, _p, _f, _p, _p, _p, _i64, _i64, _i64, _p, _sz, _p],
+    "lq_mma_issue_rate": [_i, _i, _i, _i, _i, _i, _p, _p],
 }
 _RESTYPE = {"lq_status_string": C.c_char_p, "lq_last_cuda_error": C.c_char_p, "lq_gemm_workspace_bytes": C.c_size_t,
             "lq_gemm_a16w4_fwd_static_max_bytes": C.c_size_t}

@@ -34,8 +34,8 @@ UNIT = "TFLOP/s"
 WORKLOAD = "A16W4 dequant-GEMM fwd+grad-input, Llama-2-7B linear shapes (K,N) in {(4096,4096),(4096,11008),(11008,4096),(4096,12288)}, M=4096, group 128"
 
 
-# dram__bytes_read.sum + dram__bytes_write.sum per k_gemm launch from the ncu capture summarised in
-# profiles/ncu_k_gemm_a16w4_k4096_n11008_m4096.md (a tensor-bound kernel: the figure shows there are no re-reads)
+# dram__bytes_read.sum + dram__bytes_write.sum per k_gemm launch from an ncu capture of the (K,N)=(4096,11008),
+# M=4096 launches (a tensor-bound kernel: the figure shows there are no re-reads)
 NCU_TRAFFIC_BYTES_PER_LAUNCH = 128.4e6
 NCU_TRAFFIC_NOTE = ("ncu capture of the (K,N)=(4096,11008), M=4096 launches: forward 113.9 MB, grad-input 142.9 MB, mean 128.4 MB "
                     "per launch against 146.8 MB algorithmic bytes of that shape")
@@ -345,7 +345,9 @@ def finetune_measurement(torch, arch="opt-1.3b", steps=2, warmup=1, micro_batch=
     same = True
     if world > 1:
         from latentq_llm_b200.dp import replicas_identical
-        same = replicas_identical([p.data for p in groups[0]["params"][:8]])
+        qp = groups[0]["params"]                       # every quantized weight: packed codes and residual words
+        same = replicas_identical([p.data for p in qp] + [p.residual.residual_int for p in qp
+                                                           if hasattr(getattr(p, "residual", None), "residual_int")])
     res = {"arch": arch, "tokens_per_s": round(tokens / ms * 1e3, 1), "ms_per_step": round(ms, 1), "world": world,
            "micro_batch": micro_batch, "seq": seq, "grad_accum": grad_accum, "loss_first": round(losses[0], 4),
            "loss_last": round(losses[-1], 4), "replica_codes_identical": same,

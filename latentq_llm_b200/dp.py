@@ -56,20 +56,28 @@ class GradArena:
             yield self.flat[start:min(self.numel, start + per)]
 
 
+def _mean_in_collective(flat: torch.Tensor, group) -> bool:
+    """NCCL averages inside the collective (`ReduceOp.AVG`); gloo sums, and the caller divides afterwards."""
+    return flat.is_cuda and dist.get_backend(group) == "nccl"
+
+
 def allreduce_mean(arena: GradArena, group=None, bucket_bytes: int = 64 << 20) -> int:
-    """Bucketed sum all-reduce of the arena followed by division by the world size.  Returns the bucket count.
-    NVSwitch gives every peer full bandwidth, so buckets are sized for launch latency / overlap (tens of MB)."""
+    """Bucketed mean all-reduce of the arena, with the same reduction as `ChunkReducer` (NCCL: `AVG`; gloo: sum, then
+    division by the world size), so that the two routes give the same bits at every world size.  Returns the bucket
+    count.  NVSwitch gives every peer full bandwidth, so buckets are sized for launch latency / overlap (tens of MB)."""
     if not (dist.is_available() and dist.is_initialized()):
         return 0
     world = dist.get_world_size(group)
     if world == 1:
         return 0
+    in_coll = _mean_in_collective(arena.flat, group)
     works = []
     for b in arena.buckets(bucket_bytes):
-        works.append(dist.all_reduce(b, op=dist.ReduceOp.SUM, group=group, async_op=True))
+        works.append(dist.all_reduce(b, op=dist.ReduceOp.AVG if in_coll else dist.ReduceOp.SUM, group=group, async_op=True))
     for w in works:
         w.wait()
-    arena.flat.div_(world)
+    if not in_coll:
+        arena.flat.div_(world)
     return len(works)
 
 
@@ -88,7 +96,7 @@ class ChunkReducer:
         self.ranges = [(int(a), int(b)) for a, b in ranges]
         self.world = dist.get_world_size(group)
         self.cuda = arena.flat.is_cuda
-        self.in_collective_mean = self.cuda and dist.get_backend(group) == "nccl"
+        self.in_collective_mean = _mean_in_collective(arena.flat, group)
         self.comm = torch.cuda.Stream(device=arena.flat.device) if self.cuda else None
         self.works = [None] * len(self.ranges)
         self.launched = 0
@@ -135,13 +143,28 @@ def shard_micro_batches(n_micro_batches: int, rank: int, world: int) -> List[int
     return list(range(rank, n_micro_batches, world))
 
 
+def tensor_hash64(t: torch.Tensor) -> torch.Tensor:
+    """Position-sensitive 64-bit hash of a tensor's bytes (int64 scalar on the tensor's device): every 8-byte word is
+    multiplied by an odd weight derived from its index and the products are summed modulo 2^64, so swapping two
+    different words, or changing one, changes the hash."""
+    b = t.detach().contiguous().reshape(-1).view(torch.uint8)
+    pad = (-b.numel()) % 8
+    if pad:
+        b = torch.cat([b, torch.zeros(pad, dtype=torch.uint8, device=b.device)])
+    w = b.view(torch.int64)
+    idx = torch.arange(w.numel(), dtype=torch.int64, device=w.device)
+    weight = (idx * -0x61C8864680B583EB + 0x2545F4914F6CDD1D) | 1         # int64 arithmetic wraps
+    mixed = (w ^ (w >> 29)) * weight
+    return mixed.sum() + w.numel()
+
+
 def replicas_identical(tensors: Sequence[torch.Tensor], group=None) -> bool:
-    """True when the given tensors hold the same bytes on every rank (checksum max == min)."""
+    """True when every given tensor holds the same bytes on every rank: one `tensor_hash64` per tensor, compared
+    across ranks (max == min)."""
     if not (dist.is_available() and dist.is_initialized()) or dist.get_world_size(group) == 1:
         return True
-    sums = torch.stack([t.reshape(-1).to(torch.float64).sum() if t.is_floating_point()
-                        else t.reshape(-1).to(torch.int64).sum().to(torch.float64) for t in tensors])
-    hi, lo = sums.clone(), sums.clone()
+    hashes = torch.stack([tensor_hash64(t) for t in tensors])
+    hi, lo = hashes.clone(), hashes.clone()
     dist.all_reduce(hi, op=dist.ReduceOp.MAX, group=group)
     dist.all_reduce(lo, op=dist.ReduceOp.MIN, group=group)
     return bool(torch.equal(hi, lo))
@@ -154,24 +177,34 @@ class PeerLostError(RuntimeError):
 class StepGate:
     """Host-side liveness check at the step boundary, before any collective is launched.
 
-    Every rank publishes `gate/<step>/<rank>` in the process group's key-value store and waits (bounded) for the
+    Every rank publishes `gate/<run>/<step>/<rank>` in the process group's key-value store and waits (bounded) for the
     same key of every peer.  A rank that died between steps is therefore noticed on the host, with no kernel or
     collective in flight, instead of turning the next all-reduce into a hang.
     """
 
-    def __init__(self, store=None, rank=None, world=None, timeout_s: float = 30.0):
+    def __init__(self, store=None, rank=None, world=None, timeout_s: float = 30.0, nonce: str = "0"):
+        """`nonce` names the run: a restarted job that resumes at an earlier step number must not be let through by
+        keys its previous incarnation left in a long-lived store."""
         self.store = store if store is not None else dist.distributed_c10d._get_default_store()
         self.rank = dist.get_rank() if rank is None else rank
         self.world = dist.get_world_size() if world is None else world
         self.timeout_s = timeout_s
+        self.nonce = str(nonce)
 
     def arrive_and_wait(self, step: int) -> None:
         import datetime
-        self.store.set(f"gate/{step}/{self.rank}", "1")
-        keys = [f"gate/{step}/{r}" for r in range(self.world) if r != self.rank]
+        self.store.set(f"gate/{self.nonce}/{step}/{self.rank}", "1")
+        keys = [f"gate/{self.nonce}/{step}/{r}" for r in range(self.world) if r != self.rank]
         if not keys:
             return
         try:
             self.store.wait(keys, datetime.timedelta(seconds=self.timeout_s))
         except Exception as e:  # the store raises on timeout
             raise PeerLostError(f"rank {self.rank}: a peer did not reach step {step} within {self.timeout_s}s") from e
+        # every peer has passed step-1 (it published `step`), so nobody can still be waiting for this rank's key of
+        # step-2: drop it, the store does not grow with the run
+        if step >= 2:
+            try:
+                self.store.delete_key(f"gate/{self.nonce}/{step - 2}/{self.rank}")
+            except Exception:
+                pass                                     # a store without delete support only keeps the key

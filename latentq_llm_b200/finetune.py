@@ -116,7 +116,7 @@ class LatentFineTuner:
     (dequantize + Adam + stochastic requantize per quantized weight)."""
 
     def __init__(self, model, optimizer, groups, grad_accum: int = 8, group=None, gate_timeout_s: float = 600.0,
-                 cuda_graph: bool = False, overlap_chunks: int = 8):
+                 cuda_graph: bool = False, overlap_chunks: int = 8, run_id: str = "0"):
         """`cuda_graph=True`: forward + backward of one micro-batch are captured once (first `step`, fixed [B, S]) and
         replayed; the ~430 kernel-launching Python calls per micro-batch (144 quantized linears, three GEMMs each)
         otherwise leave the GPU waiting for the host.
@@ -124,14 +124,16 @@ class LatentFineTuner:
         `overlap_chunks` (world size > 1): the decoder layers are cut into that many runs; during the backward pass of
         the step's last micro-batch the gradients of a run are all-reduced as soon as the pass has left the run (its
         layers come last in the forward order, first in the backward order), and the optimizer then steps run by run
-        as the reductions land.  0 = one bucketed all-reduce after the backward pass."""
+        as the reductions land.  0 = one bucketed all-reduce after the backward pass.
+
+        `run_id` names this launch of the job in the step gate's keys (give a restarted job a new one)."""
         self.model, self.opt, self.grad_accum, self.group = model, optimizer, grad_accum, group
         self.cuda_graph, self._graph, self._static_ids, self._static_loss, self._graph_scale = cuda_graph, None, None, None, None
         self.params = groups[0]["params"] + groups[1]["params"]
         self.arena = GradArena(self.params, dtype=torch.bfloat16, device=next(model.parameters()).device)
         self.step_no = 0
         dist_on = torch.distributed.is_available() and torch.distributed.is_initialized()
-        self.gate = StepGate(timeout_s=gate_timeout_s) if dist_on and torch.distributed.get_world_size() > 1 else None
+        self.gate = StepGate(timeout_s=gate_timeout_s, nonce=run_id) if dist_on and torch.distributed.get_world_size() > 1 else None
         self._reducer, self._events, self._capturing, self._reduce_in_backward = None, {}, False, False
         if self.gate is not None and overlap_chunks > 0:
             self._plan_overlap(groups, overlap_chunks)
@@ -168,6 +170,7 @@ class LatentFineTuner:
             for k in range(len(red.ranges)):             # whatever is left: the first run of layers, the dense parameters
                 red.launch(k)
             self.opt.before_param = self._wait_for_param
+            self.opt.last_to_first = True                # the order the reductions were queued in: last run first
             self.opt.step()
             red.wait_all()
         else:
@@ -225,40 +228,34 @@ class LatentFineTuner:
     def _wait_for_param(self, p) -> None:
         self._reducer.wait(self._range_of[id(p)])
 
-    # (method of LatentFineTuner, defined below the class body for readability)
-
-
-def _ensure_graph(self, ids, n_micro):
-    """Capture forward + backward of one micro-batch (gradients accumulate in place in the arena views)."""
-    if self._graph is not None:
-        if tuple(ids.shape) != tuple(self._static_ids.shape) or n_micro != self._graph_scale:
-            raise ValueError("the captured step has a fixed micro-batch shape and accumulation count")
-        return
-    self._static_ids = ids.clone()
-    self._graph_scale = n_micro
-    side = torch.cuda.Stream()
-    side.wait_stream(torch.cuda.current_stream())
-    with torch.cuda.stream(side):                         # warm-up on a side stream: lazy initialisations, autograd buffers
-        for _ in range(2):
-            out = self.model(input_ids=self._static_ids, labels=self._static_ids, use_cache=False)
-            (out.loss / n_micro).backward()
-    torch.cuda.current_stream().wait_stream(side)
-    self._graph = torch.cuda.CUDAGraph()
-    self._capturing = True
-    quiet = getattr(torch.autograd.graph, "set_warn_on_accumulate_grad_stream_mismatch", None)
-    if quiet is not None:
-        quiet(False)            # warm-up (side stream) and capture (capture stream) differ on purpose
-    try:
-        with torch.cuda.graph(self._graph):
-            out = self.model(input_ids=self._static_ids, labels=self._static_ids, use_cache=False)
-            self._static_loss = out.loss
-            (out.loss / n_micro).backward()
-    finally:
-        self._capturing = False
-    self.arena.attach()                                   # drop what warm-up and capture accumulated
-
-
-LatentFineTuner._ensure_graph = _ensure_graph
+    def _ensure_graph(self, ids, n_micro):
+        """Capture forward + backward of one micro-batch (gradients accumulate in place in the arena views)."""
+        if self._graph is not None:
+            if tuple(ids.shape) != tuple(self._static_ids.shape) or n_micro != self._graph_scale:
+                raise ValueError("the captured step has a fixed micro-batch shape and accumulation count")
+            return
+        self._static_ids = ids.clone()
+        self._graph_scale = n_micro
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):                         # warm-up on a side stream: lazy initialisations, autograd buffers
+            for _ in range(2):
+                out = self.model(input_ids=self._static_ids, labels=self._static_ids, use_cache=False)
+                (out.loss / n_micro).backward()
+        torch.cuda.current_stream().wait_stream(side)
+        self._graph = torch.cuda.CUDAGraph()
+        self._capturing = True
+        quiet = getattr(torch.autograd.graph, "set_warn_on_accumulate_grad_stream_mismatch", None)
+        if quiet is not None:
+            quiet(False)            # warm-up (side stream) and capture (capture stream) differ on purpose
+        try:
+            with torch.cuda.graph(self._graph):
+                out = self.model(input_ids=self._static_ids, labels=self._static_ids, use_cache=False)
+                self._static_loss = out.loss
+                (out.loss / n_micro).backward()
+        finally:
+            self._capturing = False
+        self.arena.attach()                                   # drop what warm-up and capture accumulated
 
 
 def synthetic_batches(n: int, batch: int, seq: int, vocab: int, device, seed: int):

@@ -854,6 +854,7 @@ class MyAdam(torch.optim.Adam):
         self.statedevice = 'cpu' if cpu else 'cuda'
         self.fused = bool(fused) and not cpu
         self.before_param = None                 # optional callable(p), run before a parameter with a gradient is stepped
+        self.last_to_first = False               # walk each group's parameters from the last to the first (see step)
         self._dense_tables = {}
 
     def add_param_group(self, param_group):
@@ -883,7 +884,12 @@ class MyAdam(torch.optim.Adam):
                 loss = closure()
         dense = {}
         for gindex, group in enumerate(self.param_groups):
-            for pindex, p in enumerate(group["params"]):
+            # Parameters are independent of one another (dither streams are keyed by parameter, not by visiting order),
+            # so the walk may run backwards: a data-parallel step then meets the gradients in the order their
+            # all-reduces were queued during the backward pass (last layers first) instead of waiting for the whole
+            # queue before the first parameter.
+            walk = list(enumerate(group["params"]))
+            for pindex, p in (reversed(walk) if self.last_to_first else walk):
                 if p.grad is None:
                     continue
                 if self.before_param is not None:           # data-parallel step: wait for this gradient's all-reduce only

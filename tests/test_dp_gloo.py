@@ -50,6 +50,11 @@ def _worker_allreduce(rank, world, port, q):
     ok = all(torch.allclose(p.grad.float(), w.float(), rtol=2e-2, atol=1e-3) for p, w in zip(params, want))
     ident = replicas_identical([p.grad for p in params])
     differ = replicas_identical([torch.full((4,), float(rank))])
+    # same multiset of bytes, same sum, different order on rank 1: a checksum of sums would pass, the hash must not
+    swapped = torch.arange(64, dtype=torch.int8)
+    if rank == 1:
+        swapped[[5, 40]] = swapped[[40, 5]]
+    differ = differ or replicas_identical([swapped])
     q.put((rank, ok, ident, differ))
     dist.destroy_process_group()
 

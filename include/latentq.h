@@ -163,6 +163,35 @@ LQ_API int lq_adam_a16w4_step(int8_t* codes, int32_t* words, const void* grad, i
                               uint8_t* state2, float* scale2, float* tmax2, int opt_block,
                               const lq_adam_hyper* hyper, const lq_requant_opts* opts, lq_stream_t stream);
 
+/* The statistic of the residual-curve refresh (utils/quant.py:1107-1111) for the step about to be taken: stat_out
+ * (fp32 [numel / 128]) receives, per run of 128 elements, the fp32 sum of abs(exp_avg) / denom after the moment
+ * update (each quotient rounded to the gradient's dtype like the tensor op).  Reads the gradient and both 8-bit
+ * states, changes nothing; the reference's per-group mean is stat_out / 128 for group size 128.  Call it before the
+ * step of a refresh iteration: the level it selects is the one that step encodes with. */
+LQ_API int lq_adam_moment_stat(const void* grad, int grad_dtype, int64_t numel,
+                               const uint8_t* state1, const float* scale1, const float* tmax1,
+                               const uint8_t* state2, const float* scale2, const float* tmax2, int opt_block,
+                               const lq_adam_hyper* hyper, float* stat_out, lq_stream_t stream);
+/* One quantized A8W8 weight (the `wbit == 8` branches of MyAdam.update_step, utils/quant.py:1070-1071, 1139-1141):
+ * latent = residual.add(codes * qscales[row]); Adam; states re-encoded; codes, residual = Qfunc_8bit_res(latent).
+ * codes int8 [rows, cols], one scale per row, cols a multiple of 8. */
+LQ_API int lq_adam_a8w8_step(int8_t* codes, int32_t* words, const void* grad, int grad_dtype,
+                             const void* qscales, int qp_dtype, int64_t rows, int64_t cols,
+                             uint8_t* state1, float* scale1, float* tmax1,
+                             uint8_t* state2, float* scale2, float* tmax2, int opt_block,
+                             const lq_adam_hyper* hyper, const lq_requant_opts* opts, lq_stream_t stream);
+
+/* GradientQTensor (utils/quant.py:846-921): the optional 8-bit stochastic gradient accumulator.
+ * first != 0 is set_value(): scale[row] = clamp(4 * absmax(row), 1e-5) / 127 (stored in `dtype`), then
+ * qdata = clamp(round(fdata / scale + noise), -128, 127); first == 0 is add_(): fdata <- qdata * scale + fdata
+ * first, scale unchanged.  noise comes from opts->dither (LQ_DITHER_EXPLICIT: opts->dither_buf, one fp32 value per
+ * element; LQ_DITHER_PHILOX: opts->seed / opts->stream_id); no other field of opts is read.  cols a multiple of 8. */
+LQ_API int lq_gradq_accumulate(const void* fdata, int dtype, int64_t rows, int64_t cols, int8_t* qdata, void* scale,
+                               int first, const lq_requant_opts* opts, lq_stream_t stream);
+/* get_value(): out = qdata.to(dtype) * scale[row]. */
+LQ_API int lq_gradq_dequant(const int8_t* qdata, const void* scale, int dtype, int64_t rows, int64_t cols, void* out,
+                            lq_stream_t stream);
+
 /* Many small dense bf16 parameters with bf16 optimizer states (numel < 65536, utils/quant.py:1020-1027) in one
  * launch.  `table` is a DEVICE array of n_tensors records {param, grad, state1, state2, numel}; state2 holds
  * sqrt(v)+eps as in the reference (:1133-1135).  All four arrays of a record are bf16 and 16-byte aligned. */
@@ -242,6 +271,34 @@ LQ_API int lq_gemm_device_status(int reset);
  * accumulator, [4] MMA role total, [5] dequant waiting for TMA data, [6] dequant role total,
  * [7] epilogue waiting for an accumulator, [8] epilogue role total, [9] number of CTAs. */
 LQ_API int lq_gemm_profile(int enable, unsigned long long* out16);
+
+/* ------------------------------------------------------------------------
+ * Decode-side operations around the GEMMs of a Llama-architecture layer (bf16 everywhere).  hf_rounding != 0
+ * rounds every intermediate to bf16 like the eager modules' tensor ops; 0 keeps fp32 up to the final cast like the
+ * reference's Triton kernels.
+ * ------------------------------------------------------------------------ */
+/* Residual add + RMSNorm (PTQ/quant/triton_norm.py:7-39; LlamaRMSNorm): if delta != NULL, h[M,K] += delta first
+ * (in place); y = h * rsqrt(mean(h^2) + eps) * gamma[K]. */
+LQ_API int lq_add_rmsnorm(void* h, const void* delta, const void* gamma, float eps, void* y, int64_t M, int64_t K,
+                          int hf_rounding, lq_stream_t stream);
+/* Rotate-half RoPE on the q and k heads of a fused projection output (PTQ/quant/fused_attn.py:8-58, 124-129):
+ * qkv[M, (Hq + 2*Hkv) * hd] = q | k | v per token; q is rotated in place, rotated k and v are written into the caches
+ * [batch, Hkv, max_len, hd] at positions[m] (int64, one per token; batch index = m / tokens_per_seq).
+ * inv_freq: hd/2 fp32 frequencies (theta^(-2i/hd)). */
+LQ_API int lq_rope_kv_store(void* qkv, const int64_t* positions, const float* inv_freq, void* k_cache, void* v_cache,
+                            int64_t M, int tokens_per_seq, int Hq, int Hkv, int hd, int64_t max_len, int hf_rounding,
+                            lq_stream_t stream);
+/* Single-query attention over the cache (the reference calls F.scaled_dot_product_attention,
+ * PTQ/quant/fused_attn.py:148-149): out[b, h*hd..] = softmax(q[b,h]·K[b,hk,0..positions[b]] * scale) · V.
+ * q: row b at q + b*q_row_stride elements, heads contiguous.  hd = 64 or 128.  The workspace holds the partial results
+ * of the key-range splits and one ticket counter per (batch, head); the counters must be ZERO before the first call
+ * and are left zero by every call. */
+LQ_API size_t lq_decode_attention_workspace_bytes(int64_t B, int Hq, int hd, int64_t max_len);
+LQ_API int lq_decode_attention(const void* q, int64_t q_row_stride, const void* k_cache, const void* v_cache,
+                               const int64_t* positions, void* out, int64_t B, int Hq, int Hkv, int hd, int64_t max_len,
+                               float scale, void* workspace, size_t workspace_bytes, lq_stream_t stream);
+/* act[M, I] = silu(gate_up[M, 0:I]) * gate_up[M, I:2I] (epilogue of PTQ/quant/fused_mlp.py:84-168; LlamaMLP). */
+LQ_API int lq_silu_mul(const void* gate_up, void* act, int64_t M, int64_t I, int hf_rounding, lq_stream_t stream);
 
 /* Issue-rate microbenchmark of the tensor cores (no counterpart in the reference): `ctas` CTAs each issue n_mma
  * tcgen05.mma instructions of shape 128 x n x (32 bytes of k) — kind LQ_GEMM_A8W8: int8 operands, 32 k; otherwise

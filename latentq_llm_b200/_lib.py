@@ -83,6 +83,10 @@ SIGNATURES = {
     "lq_opt8_dequant": [_p, _i64, _i, _p, _p, _p, _p],
     "lq_adam_a16w4_step": [_p, _p, _p, _i, _p, _p, _i, _i64, _i, _p, _p, _p, _p, _p, _p, _i, _HYPER, _OPTS, _p],
     "lq_adam_dense_multi": [_p, _i, _i64, _HYPER, _p],
+    "lq_adam_moment_stat": [_p, _i, _i64, _p, _p, _p, _p, _p, _p, _i, _HYPER, _p, _p],
+    "lq_adam_a8w8_step": [_p, _p, _p, _i, _p, _i, _i64, _i64, _p, _p, _p, _p, _p, _p, _i, _HYPER, _OPTS, _p],
+    "lq_gradq_accumulate": [_p, _i, _i64, _i64, _p, _p, _i, _OPTS, _p],
+    "lq_gradq_dequant": [_p, _p, _i, _i64, _i64, _p, _p],
     "lq_act_quant_per_token": [_p, _i64, _i64, _p, _p, _p],
     "lq_act_quant_per_tensor": [_p, _i64, _p, _p, _p],
     "lq_gemm_workspace_bytes": [_i, _i64, _i64, _i64],
@@ -95,9 +99,14 @@ SIGNATURES = {
     "lq_gemm_a16w4_fwd_static_peek": [_p, _sz, _sz],
     "lq_gemm_a8w8": [_p, _p, _p, _p, _f, _p, _p, _p, _i64, _i64, _i64, _p, _sz, _p],
     "lq_mma_issue_rate": [_i, _i, _i, _i, _i, _i, _p, _p],
+    "lq_add_rmsnorm": [_p, _p, _p, _f, _p, _i64, _i64, _i, _p],
+    "lq_rope_kv_store": [_p, _p, _p, _p, _p, _i64, _i, _i, _i, _i, _i64, _i, _p],
+    "lq_decode_attention_workspace_bytes": [_i64, _i, _i, _i64],
+    "lq_decode_attention": [_p, _i64, _p, _p, _p, _p, _i64, _i, _i, _i, _i64, _f, _p, _sz, _p],
+    "lq_silu_mul": [_p, _p, _i64, _i64, _i, _p],
 }
 _RESTYPE = {"lq_status_string": C.c_char_p, "lq_last_cuda_error": C.c_char_p, "lq_gemm_workspace_bytes": C.c_size_t,
-            "lq_gemm_a16w4_fwd_static_max_bytes": C.c_size_t}
+            "lq_gemm_a16w4_fwd_static_max_bytes": C.c_size_t, "lq_decode_attention_workspace_bytes": C.c_size_t}
 
 for _name, _args in SIGNATURES.items():
     _fn = getattr(lib, _name)          # AttributeError here = header and library disagree

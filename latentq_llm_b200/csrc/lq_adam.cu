@@ -59,8 +59,8 @@ __device__ __forceinline__ uint2 opt8_encode8(const float (&x)[8], float mx, flo
 
 // One thread per word of 8 elements; a CTA covers 256 words = one 2048-element optimizer-state block, or sixteen
 // 128-element blocks (16 lanes each).
-template <int CODEC, int DITHER, bool BF>
-__global__ void __launch_bounds__(256) k_adam_a16w4(const AdamParams p) {
+template <int WBITS, int CODEC, int DITHER, bool BF>
+__global__ void __launch_bounds__(256) k_adam_quant(const AdamParams p) {
     __shared__ float s_red[4][8];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     for (int64_t tile = blockIdx.x; tile < p.n_tiles; tile += gridDim.x) {
@@ -74,14 +74,14 @@ __global__ void __launch_bounds__(256) k_adam_a16w4(const AdamParams p) {
         if (active) {
             const int64_t g = p.rq.group_shift >= 0 ? (e0 >> p.rq.group_shift) : (e0 / p.rq.group);
             s = load1(p.rq.scales, p.rq.qp_dtype, g);
-            z = load1(p.rq.zeros, p.rq.qp_dtype, g);
+            z = (WBITS == 4) ? load1(p.rq.zeros, p.rq.qp_dtype, g) : 0.0f;
             ob = e0 >> p.opt_shift;
             const float s1 = p.sc1[ob], t1 = p.tm1[ob], s2 = p.sc2[ob], t2 = p.tm2[ob];   // rewritten below: plain loads
             const uint2 q1 = *reinterpret_cast<const uint2*>(p.st1 + e0);
             const uint2 q2 = *reinterpret_cast<const uint2*>(p.st2 + e0);
             float gr[8];
             load8(p.grad, p.grad_dtype, e0, gr);
-            latent_load<4, CODEC, BF>(p.rq, w, s, z, lat);
+            latent_load<WBITS, CODEC, BF>(p.rq, w, s, z, lat);
 #pragma unroll
             for (int k = 0; k < 8; ++k) {
                 const float c1 = u2f(((k < 4 ? q1.x : q1.y) >> (8 * (k & 3))) & 0xffu);
@@ -120,7 +120,7 @@ __global__ void __launch_bounds__(256) k_adam_a16w4(const AdamParams p) {
             *reinterpret_cast<uint2*>(p.st2 + e0) = opt8_encode8(d, mx2, ns2);
             const bool leader = p.opt_shift == 11 ? (tid == 0) : ((tid & 15) == 0);
             if (leader) { p.sc1[ob] = ns1; p.tm1[ob] = mx1; p.sc2[ob] = ns2; p.tm2[ob] = mx2; }
-            latent_store<4, CODEC, DITHER, BF>(p.rq, w, s, z, lat);
+            latent_store<WBITS, CODEC, DITHER, BF>(p.rq, w, s, z, lat);
         }
     }
 }
@@ -279,13 +279,46 @@ __global__ void __launch_bounds__(256, 3) k_adam_a16w4_fast(const AdamParams p, 
     }
 }
 
-template <int CODEC, int DITHER>
+template <int WBITS, int CODEC, int DITHER>
 static int launch_adam(const AdamParams& p, bool bf, cudaStream_t st) {
     const int64_t cap = (int64_t)sm_count() * 8;
     const int grid = (int)(p.n_tiles < cap ? p.n_tiles : cap);
-    if (bf) k_adam_a16w4<CODEC, DITHER, true><<<grid, 256, 0, st>>>(p);
-    else k_adam_a16w4<CODEC, DITHER, false><<<grid, 256, 0, st>>>(p);
-    return check_launch("k_adam_a16w4");
+    if (bf) k_adam_quant<WBITS, CODEC, DITHER, true><<<grid, 256, 0, st>>>(p);
+    else k_adam_quant<WBITS, CODEC, DITHER, false><<<grid, 256, 0, st>>>(p);
+    return check_launch("k_adam_quant");
+}
+
+// ---- the statistic behind the residual-curve refresh (utils/quant.py:1107-1111) ---------------------------------
+// abs(exp_avg) / denom of the step ABOUT to be taken (the reference evaluates it after the moment update and before
+// the requantize, whose curve level it may change), summed in fp32 over runs of 128 elements: 16 adjacent threads, fixed
+// order.  Reads the gradient and both 8-bit states, writes only the sums.
+template <bool BF>
+__global__ void __launch_bounds__(256) k_adam_moment_stat(const AdamParams p, float* __restrict__ stat_out) {
+    for (int64_t w = (int64_t)blockIdx.x * 256 + threadIdx.x; w < p.n_tiles * 256; w += (int64_t)gridDim.x * 256) {
+        const bool active = w < p.rq.n_words;
+        float t = 0.0f;
+        if (active) {
+            const int64_t e0 = w * 8, ob = e0 >> p.opt_shift;
+            const float s1 = p.sc1[ob], t1 = p.tm1[ob], s2 = p.sc2[ob], t2 = p.tm2[ob];
+            const uint2 q1 = *reinterpret_cast<const uint2*>(p.st1 + e0);
+            const uint2 q2 = *reinterpret_cast<const uint2*>(p.st2 + e0);
+            float gr[8];
+            load8(p.grad, p.grad_dtype, e0, gr);
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+                const float c1 = u2f(((k < 4 ? q1.x : q1.y) >> (8 * (k & 3))) & 0xffu);
+                const float c2 = u2f(((k < 4 ? q2.x : q2.y) >> (8 * (k & 3))) & 0xffu);
+                float m = rb<BF>(__fsub_rn(t1, __fmul_rn(c1, s1)));
+                const float r2 = __fsub_rn(t2, __fmul_rn(c2, s2));
+                float d = rb<BF>(__fmul_rn(r2, r2));
+                adam_moments<BF>(p.h, gr[k], m, d);
+                t = __fadd_rn(t, rb<BF>(__fdiv_rn(fabsf(m), d)));
+            }
+        }
+#pragma unroll
+        for (int o = 8; o > 0; o >>= 1) t = __fadd_rn(t, __shfl_xor_sync(0xffffffffu, t, o));
+        if (active && (threadIdx.x & 15) == 0) stat_out[w >> 4] = t;
+    }
 }
 
 // ---- many small dense bf16 tensors ---------------------------------------------------------------
@@ -304,6 +337,84 @@ __global__ void __launch_bounds__(256) k_adam_dense_multi(const lq_dense_slot* _
         p1[i] = __float2bfloat16_rn(m);
         p2[i] = __float2bfloat16_rn(d);
         pw[i] = __float2bfloat16_rn(w);
+    }
+}
+
+// ---- 8-bit stochastic gradient accumulator: GradientQTensor (utils/quant.py:846-921) ----------------------------
+// One CTA per weight row.  FIRST (set_value): scale = clamp(4 * absmax(row), 1e-5) / 127 in the gradient's dtype, then
+// q = clamp(round_half_even(f / scale + noise), -128, 127).  Otherwise (add_): f <- q * scale + f first, scale kept.
+// noise: explicit fp32 buffer, or the library's Philox stream (one block per 8 elements), rounded to the chain dtype
+// like the reference's noise tensor.
+template <bool BF, bool FIRST, int DITHER>
+__global__ void __launch_bounds__(256) k_gradq(const void* __restrict__ f, int dtype, int cols, int8_t* __restrict__ q,
+                                               void* __restrict__ scale, const float* __restrict__ noise, uint64_t seed,
+                                               uint64_t stream_id) {
+    __shared__ float red[8];
+    const int64_t row = blockIdx.x;
+    const int words = cols >> 3;
+    float s;
+    if (FIRST) {
+        float am = 0.0f;
+        for (int w = threadIdx.x; w < words; w += 256) {
+            float v[8];
+            load8(f, dtype, row * cols + (int64_t)w * 8, v);
+#pragma unroll
+            for (int k = 0; k < 8; ++k) am = fmaxf(am, fabsf(v[k]));
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, o));
+        if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = am;
+        __syncthreads();
+#pragma unroll
+        for (int i = 0; i < 8; ++i) am = fmaxf(am, red[i]);
+        const float vmax = rb<BF>(__fmul_rn(am, 4.0f));
+        s = rb<BF>(__fdiv_rn(fmaxf(vmax, rb<BF>(1e-5f)), 127.0f));
+        if (threadIdx.x == 0) {
+            if (dtype == LQ_BF16) reinterpret_cast<__nv_bfloat16*>(scale)[row] = __float2bfloat16_rn(s);
+            else reinterpret_cast<float*>(scale)[row] = s;
+        }
+    } else {
+        s = load1(scale, dtype, row);
+    }
+    for (int w = threadIdx.x; w < words; w += 256) {
+        const int64_t e0 = row * cols + (int64_t)w * 8;
+        float v[8], u[8];
+        load8(f, dtype, e0, v);
+        if (DITHER == LQ_DITHER_EXPLICIT) load8(noise, LQ_F32, e0, u);
+        else philox_dither8(seed, stream_id, (uint64_t)(e0 >> 3), u);
+        uint2 old = make_uint2(0u, 0u);
+        if (!FIRST) old = *reinterpret_cast<const uint2*>(q + e0);
+        uint32_t b[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            float x = v[k];
+            if (!FIRST) {
+                const uint32_t byte = ((k < 4 ? old.x : old.y) >> (8 * (k & 3))) & 0xffu;
+                const float c = __fsub_rn(u2f(byte ^ 0x80u), 128.0f);                 // signed byte
+                x = rb<BF>(__fadd_rn(rb<BF>(__fmul_rn(c, s)), x));                    // dequant() + fdata
+            }
+            float t = rb<BF>(__fadd_rn(rb<BF>(__fdiv_rn(x, s)), rb<BF>(u[k])));
+            t = fminf(fmaxf(rne(t), -128.0f), 127.0f);
+            b[k] = f2bits(t) & 0xffu;
+        }
+        *reinterpret_cast<uint2*>(q + e0) = make_uint2(b[0] | (b[1] << 8) | (b[2] << 16) | (b[3] << 24),
+                                                      b[4] | (b[5] << 8) | (b[6] << 16) | (b[7] << 24));
+    }
+}
+// get_value(): qdata.to(dtype) * scale
+__global__ void __launch_bounds__(256) k_gradq_dequant(const int8_t* __restrict__ q, const void* __restrict__ scale, int dtype,
+                                                       int cols, int64_t n_words, void* __restrict__ out) {
+    for (int64_t w = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; w < n_words; w += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t e0 = w * 8;
+        const float s = load1(scale, dtype, e0 / cols);
+        const uint2 pk = *reinterpret_cast<const uint2*>(q + e0);
+        float v[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            const uint32_t byte = ((k < 4 ? pk.x : pk.y) >> (8 * (k & 3))) & 0xffu;
+            v[k] = __fmul_rn(__fsub_rn(u2f(byte ^ 0x80u), 128.0f), s);                // store8 rounds to the dtype
+        }
+        store8(out, dtype, e0, v);
     }
 }
 
@@ -359,11 +470,98 @@ int lq_adam_a16w4_step(int8_t* codes, int32_t* words, const void* grad, int grad
             else k_adam_a16w4_fast<false><<<grid, 256, ADAM_FAST_SMEM, st>>>(p, opts->mu_enc);
             return check_launch("k_adam_a16w4_fast");
         }
-        return launch_adam<LQ_CODEC_THREEFOLD, LQ_DITHER_HASH>(p, bf, st);
+        return launch_adam<4, LQ_CODEC_THREEFOLD, LQ_DITHER_HASH>(p, bf, st);
     }
-    if (opts->codec == LQ_CODEC_THREEFOLD && opts->dither == LQ_DITHER_PHILOX) return launch_adam<LQ_CODEC_THREEFOLD, LQ_DITHER_PHILOX>(p, bf, st);
-    if (opts->codec == LQ_CODEC_UNIFORM16 && opts->dither == LQ_DITHER_PHILOX) return launch_adam<LQ_CODEC_UNIFORM16, LQ_DITHER_PHILOX>(p, bf, st);
+    if (opts->codec == LQ_CODEC_THREEFOLD && opts->dither == LQ_DITHER_PHILOX) return launch_adam<4, LQ_CODEC_THREEFOLD, LQ_DITHER_PHILOX>(p, bf, st);
+    if (opts->codec == LQ_CODEC_UNIFORM16 && opts->dither == LQ_DITHER_PHILOX) return launch_adam<4, LQ_CODEC_UNIFORM16, LQ_DITHER_PHILOX>(p, bf, st);
     return LQ_EUNSUPPORTED;
+}
+
+int lq_adam_a8w8_step(int8_t* codes, int32_t* words, const void* grad, int grad_dtype, const void* qscales, int qp_dtype,
+                      int64_t rows, int64_t cols, uint8_t* state1, float* scale1, float* tmax1, uint8_t* state2, float* scale2,
+                      float* tmax2, int opt_block, const lq_adam_hyper* hyper, const lq_requant_opts* opts, lq_stream_t stream) {
+    if (rows == 0 || cols == 0) return LQ_OK;
+    if (rows < 0 || cols < 0) return LQ_EINVAL;
+    AdamParams p{};
+    const int64_t numel = rows * cols;
+    int rc = fill_requant(p.rq, opts, numel, cols);          // one scale per weight row: the "group" is the row
+    if (rc) return rc;
+    if (!hyper || !codes || !words || !grad || !qscales || !state1 || !scale1 || !tmax1 || !state2 || !scale2 || !tmax2 ||
+        !dtype_ok(grad_dtype) || !dtype_ok(qp_dtype) || !aligned(codes, 8) || !aligned(words, 4) || !aligned(grad, 16) ||
+        !aligned(state1, 8) || !aligned(state2, 8))
+        return LQ_EINVAL;
+    if ((opt_block != 2048 && opt_block != 128) || numel % opt_block != 0) return LQ_EINVAL;
+    if (grad_dtype != qp_dtype || opts->math_dtype != grad_dtype) return LQ_EUNSUPPORTED;
+    if ((rc = ensure_device_for(codes)) != LQ_OK) return rc;
+    p.rq.codes_in = codes; p.rq.words_in = words; p.rq.codes_out = codes; p.rq.words_out = words;
+    p.rq.scales = qscales; p.rq.zeros = nullptr; p.rq.qp_dtype = qp_dtype;
+    p.grad = grad; p.grad_dtype = grad_dtype;
+    p.st1 = state1; p.sc1 = scale1; p.tm1 = tmax1; p.st2 = state2; p.sc2 = scale2; p.tm2 = tmax2;
+    p.opt_shift = opt_block == 2048 ? 11 : 7;
+    p.n_tiles = (p.rq.n_words + 255) / 256;
+    p.h = *hyper;
+    const bool bf = grad_dtype == LQ_BF16;
+    cudaStream_t st = LQ_ST(stream);
+    if (opts->codec == LQ_CODEC_THREEFOLD && opts->dither == LQ_DITHER_HASH) return launch_adam<8, LQ_CODEC_THREEFOLD, LQ_DITHER_HASH>(p, bf, st);
+    if (opts->codec == LQ_CODEC_THREEFOLD && opts->dither == LQ_DITHER_PHILOX) return launch_adam<8, LQ_CODEC_THREEFOLD, LQ_DITHER_PHILOX>(p, bf, st);
+    return LQ_EUNSUPPORTED;
+}
+
+int lq_adam_moment_stat(const void* grad, int grad_dtype, int64_t numel, const uint8_t* state1, const float* scale1,
+                        const float* tmax1, const uint8_t* state2, const float* scale2, const float* tmax2, int opt_block,
+                        const lq_adam_hyper* hyper, float* stat_out, lq_stream_t stream) {
+    if (numel == 0) return LQ_OK;
+    if (!grad || !state1 || !scale1 || !tmax1 || !state2 || !scale2 || !tmax2 || !hyper || !stat_out || !dtype_ok(grad_dtype) ||
+        numel < 0 || (numel % 128) != 0 || !aligned(grad, 16) || !aligned(state1, 8) || !aligned(state2, 8))
+        return LQ_EINVAL;
+    if ((opt_block != 2048 && opt_block != 128) || numel % opt_block != 0) return LQ_EINVAL;
+    int rc = ensure_device_for(grad);
+    if (rc != LQ_OK) return rc;
+    AdamParams p{};
+    p.rq.n_words = numel / 8;
+    p.grad = grad; p.grad_dtype = grad_dtype;
+    p.st1 = const_cast<uint8_t*>(state1); p.sc1 = const_cast<float*>(scale1); p.tm1 = const_cast<float*>(tmax1);
+    p.st2 = const_cast<uint8_t*>(state2); p.sc2 = const_cast<float*>(scale2); p.tm2 = const_cast<float*>(tmax2);
+    p.opt_shift = opt_block == 2048 ? 11 : 7;
+    p.n_tiles = (p.rq.n_words + 255) / 256;
+    p.h = *hyper;
+    const int grid = grid_for(p.rq.n_words, 256, 8);
+    if (grad_dtype == LQ_BF16) k_adam_moment_stat<true><<<grid, 256, 0, LQ_ST(stream)>>>(p, stat_out);
+    else k_adam_moment_stat<false><<<grid, 256, 0, LQ_ST(stream)>>>(p, stat_out);
+    return check_launch("k_adam_moment_stat");
+}
+
+int lq_gradq_accumulate(const void* fdata, int dtype, int64_t rows, int64_t cols, int8_t* qdata, void* scale, int first,
+                        const lq_requant_opts* opts, lq_stream_t stream) {
+    if (rows == 0 || cols == 0) return LQ_OK;
+    if (!fdata || !qdata || !scale || !opts || !dtype_ok(dtype) || rows < 0 || cols < 0 || (cols % 8) != 0 || cols >= (1ll << 31) ||
+        rows >= (1ll << 31) || !aligned(fdata, 16) || !aligned(qdata, 8))
+        return LQ_EINVAL;
+    if (opts->dither == LQ_DITHER_EXPLICIT && (!opts->dither_buf || !aligned(opts->dither_buf, 16))) return LQ_EINVAL;
+    if (opts->dither != LQ_DITHER_EXPLICIT && opts->dither != LQ_DITHER_PHILOX) return LQ_EUNSUPPORTED;
+    int rc = ensure_device_for(fdata);
+    if (rc != LQ_OK) return rc;
+    const bool bf = dtype == LQ_BF16, ex = opts->dither == LQ_DITHER_EXPLICIT;
+    cudaStream_t st = LQ_ST(stream);
+#define LQ_GRADQ(BFv, FIRSTv, DITHv) k_gradq<BFv, FIRSTv, DITHv><<<(unsigned)rows, 256, 0, st>>>(fdata, dtype, (int)cols, qdata, scale, opts->dither_buf, opts->seed, opts->stream_id)
+    if (bf) { if (first) { if (ex) LQ_GRADQ(true, true, LQ_DITHER_EXPLICIT); else LQ_GRADQ(true, true, LQ_DITHER_PHILOX); }
+              else { if (ex) LQ_GRADQ(true, false, LQ_DITHER_EXPLICIT); else LQ_GRADQ(true, false, LQ_DITHER_PHILOX); } }
+    else { if (first) { if (ex) LQ_GRADQ(false, true, LQ_DITHER_EXPLICIT); else LQ_GRADQ(false, true, LQ_DITHER_PHILOX); }
+           else { if (ex) LQ_GRADQ(false, false, LQ_DITHER_EXPLICIT); else LQ_GRADQ(false, false, LQ_DITHER_PHILOX); } }
+#undef LQ_GRADQ
+    return check_launch("k_gradq");
+}
+
+int lq_gradq_dequant(const int8_t* qdata, const void* scale, int dtype, int64_t rows, int64_t cols, void* out, lq_stream_t stream) {
+    if (rows == 0 || cols == 0) return LQ_OK;
+    if (!qdata || !scale || !out || !dtype_ok(dtype) || rows < 0 || cols < 0 || (cols % 8) != 0 || cols >= (1ll << 31) ||
+        !aligned(qdata, 8) || !aligned(out, 16))
+        return LQ_EINVAL;
+    int rc = ensure_device_for(qdata);
+    if (rc != LQ_OK) return rc;
+    const int64_t n_words = rows * cols / 8;
+    k_gradq_dequant<<<grid_for(n_words, 256, 8), 256, 0, LQ_ST(stream)>>>(qdata, scale, dtype, (int)cols, n_words, out);
+    return check_launch("k_gradq_dequant");
 }
 
 int lq_adam_dense_multi(const lq_dense_slot* table, int n_tensors, int64_t max_numel, const lq_adam_hyper* hyper,

@@ -1,0 +1,339 @@
+// Decode-side operations around the quantized GEMMs of a Llama-architecture layer (bf16, sm_100a): what the
+// reference fuses around its int4 matmul in PTQ/quant —
+//   * RMSNorm                      (PTQ/quant/triton_norm.py:7-39), here with the residual add that precedes it,
+//   * rotate-half RoPE on q and k  (PTQ/quant/fused_attn.py:8-58), here writing k and v straight into the KV cache,
+//   * silu(gate) * up              (epilogue of PTQ/quant/fused_mlp.py:84-168),
+//   * single-query attention over the KV cache (the reference calls F.scaled_dot_product_attention,
+//     PTQ/quant/fused_attn.py:148-149).
+// A decode step then is nine launches per layer instead of the ~45 elementwise kernels of the eager modules.
+// All kernels are HBM/L2 streaming kernels over a few hundred KB: one pass, 16-byte accesses, no scratch
+// besides the attention's split partials.
+//
+// Rounding: `hf_rounding != 0` reproduces the bf16 tensor-op chain of the eager HF modules (every op result
+// rounded to bf16); 0 keeps fp32 up to the single final cast like the reference's Triton kernels do.
+#include "lq_common.cuh"
+
+namespace lq {
+
+__device__ __forceinline__ float bf_lo(uint32_t w) { return __uint_as_float(w << 16); }
+__device__ __forceinline__ float bf_hi(uint32_t w) { return __uint_as_float(w & 0xffff0000u); }
+__device__ __forceinline__ uint32_t pack_bf2(float a, float b) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// ---------------------------------------------------------------------------------------------
+// h += delta (optional); y = RMSNorm(h) * gamma.  One CTA per token row.
+// ---------------------------------------------------------------------------------------------
+constexpr int NORM_THREADS = 256;
+__global__ void __launch_bounds__(NORM_THREADS) k_add_rmsnorm(__nv_bfloat16* __restrict__ h, const __nv_bfloat16* __restrict__ delta,
+                                                               const __nv_bfloat16* __restrict__ gamma, float eps,
+                                                               __nv_bfloat16* __restrict__ y, int K, int hf_rounding) {
+    __shared__ float red[NORM_THREADS / 32];
+    const size_t row = (size_t)blockIdx.x * K;
+    uint4* hv = reinterpret_cast<uint4*>(h + row);
+    const uint4* dv = delta ? reinterpret_cast<const uint4*>(delta + row) : nullptr;
+    float ss = 0.0f;
+    for (int i = threadIdx.x; i < K / 8; i += NORM_THREADS) {
+        uint4 a = hv[i];
+        uint32_t w[4] = {a.x, a.y, a.z, a.w};
+        if (dv) {                                      // residual + hidden_states: one bf16 rounding of the fp32 sum
+            const uint4 d = __ldg(dv + i);
+            const uint32_t e[4] = {d.x, d.y, d.z, d.w};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) w[j] = pack_bf2(__fadd_rn(bf_lo(w[j]), bf_lo(e[j])), __fadd_rn(bf_hi(w[j]), bf_hi(e[j])));
+            hv[i] = make_uint4(w[0], w[1], w[2], w[3]);
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) { const float lo = bf_lo(w[j]), hi = bf_hi(w[j]); ss = fmaf(lo, lo, ss); ss = fmaf(hi, hi, ss); }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    float tot = 0.0f;
+#pragma unroll
+    for (int wv = 0; wv < NORM_THREADS / 32; ++wv) tot += red[wv];          // same order in every thread
+    const float rstd = hf_rounding ? rsqrtf(tot / (float)K + eps) : 1.0f / sqrtf(tot / (float)K + eps);
+    const uint4* gv = reinterpret_cast<const uint4*>(gamma);
+    uint4* yv = reinterpret_cast<uint4*>(y + row);
+    for (int i = threadIdx.x; i < K / 8; i += NORM_THREADS) {
+        const uint4 a = hv[i], g = __ldg(gv + i);          // this thread wrote hv[i] itself
+        const uint32_t w[4] = {a.x, a.y, a.z, a.w}, gw[4] = {g.x, g.y, g.z, g.w};
+        uint32_t o[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            float lo = __fmul_rn(bf_lo(w[j]), rstd), hi = __fmul_rn(bf_hi(w[j]), rstd);
+            if (hf_rounding) { lo = bf16r(lo); hi = bf16r(hi); }
+            o[j] = pack_bf2(__fmul_rn(lo, bf_lo(gw[j])), __fmul_rn(hi, bf_hi(gw[j])));
+        }
+        yv[i] = make_uint4(o[0], o[1], o[2], o[3]);
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// RoPE (rotate-half) on the q and k heads of a fused qkv row, k and v stored into the cache at the token's position.
+// grid (token, head of q|k|v), hd/2 threads.  Cache layout [batch, kv head, max_len, hd].
+// ---------------------------------------------------------------------------------------------
+__global__ void k_rope_kv_store(__nv_bfloat16* __restrict__ qkv, const long long* __restrict__ positions,
+                                const float* __restrict__ inv_freq, __nv_bfloat16* __restrict__ k_cache,
+                                __nv_bfloat16* __restrict__ v_cache, int tokens_per_seq, int Hq, int Hkv, int hd, int max_len,
+                                int hf_rounding) {
+    const int m = blockIdx.x, head = blockIdx.y, i = threadIdx.x, half = hd >> 1;
+    const long long pos = positions[m];
+    __nv_bfloat16* src = qkv + (size_t)m * (size_t)(Hq + 2 * Hkv) * hd + (size_t)head * hd;
+    const int b = m / tokens_per_seq;
+    if (head >= Hq + Hkv) {                                   // v: plain copy into the cache
+        if (pos < 0 || pos >= max_len) return;
+        __nv_bfloat16* dst = v_cache + (((size_t)b * Hkv + (head - Hq - Hkv)) * max_len + (size_t)pos) * hd;
+        reinterpret_cast<uint32_t*>(dst)[i] = reinterpret_cast<const uint32_t*>(src)[i];
+        return;
+    }
+    const float x = __bfloat162float(src[i]), yv = __bfloat162float(src[i + half]);
+    float s, c;
+    sincosf((float)pos * inv_freq[i], &s, &c);
+    float ox, oy;
+    if (hf_rounding) {        // cos / sin cast to bf16, then q*cos + rotate_half(q)*sin as bf16 tensor ops
+        c = bf16r(c); s = bf16r(s);
+        ox = __fadd_rn(bf16r(__fmul_rn(x, c)), bf16r(__fmul_rn(-yv, s)));
+        oy = __fadd_rn(bf16r(__fmul_rn(yv, c)), bf16r(__fmul_rn(x, s)));
+    } else {
+        ox = __fsub_rn(__fmul_rn(x, c), __fmul_rn(yv, s));
+        oy = __fadd_rn(__fmul_rn(x, s), __fmul_rn(yv, c));
+    }
+    const __nv_bfloat16 bx = __float2bfloat16_rn(ox), by = __float2bfloat16_rn(oy);
+    if (head < Hq) { src[i] = bx; src[i + half] = by; return; }                 // q: in place
+    if (pos < 0 || pos >= max_len) return;
+    __nv_bfloat16* dst = k_cache + (((size_t)b * Hkv + (head - Hq)) * max_len + (size_t)pos) * hd;
+    dst[i] = bx; dst[i + half] = by;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Single-query attention over the cache: out[b, h, :] = softmax(q . K[0..pos] * scale) . V[0..pos].
+// grid (batch * q heads, splits); 128 threads = 16 key slots of 8 lanes, a lane holds hd/8 dims (hd = 64 or 128).
+// Each split covers a contiguous range of keys and leaves (max, sum, weighted V) in the workspace; the split
+// that finishes last for its (batch, head) combines them (a ticket counter; nobody waits for anybody).
+// ---------------------------------------------------------------------------------------------
+constexpr int ATT_THREADS = 128, ATT_SLOTS = ATT_THREADS / 8;
+template <int HD>
+__global__ void __launch_bounds__(ATT_THREADS) k_decode_attn(const __nv_bfloat16* __restrict__ q, int q_row_stride,
+                                                              const __nv_bfloat16* __restrict__ k_cache,
+                                                              const __nv_bfloat16* __restrict__ v_cache,
+                                                              const long long* __restrict__ positions, __nv_bfloat16* __restrict__ out,
+                                                              int Hq, int Hkv, int max_len, float scale, float* __restrict__ part,
+                                                              unsigned int* __restrict__ tickets) {
+    constexpr int D = HD / 8;                                 // dims per lane
+    __shared__ float sm_m[ATT_SLOTS], sm_l[ATT_SLOTS], sm_acc[ATT_SLOTS][HD];
+    __shared__ bool is_last;
+    const int bh = blockIdx.x, b = bh / Hq, h = bh - b * Hq, hk = h / (Hq / Hkv);
+    const int splits = gridDim.y, split = blockIdx.y;
+    const int slot = threadIdx.x >> 3, sub = threadIdx.x & 7;
+    long long n_keys = positions[b] + 1;
+    if (n_keys > max_len) n_keys = max_len;
+    if (n_keys < 0) n_keys = 0;
+    const int per = (int)((n_keys + splits - 1) / splits);
+    const int j0 = split * per, j1 = (int)min((long long)(j0 + per), n_keys);
+
+    float qf[D];
+    {
+        const __nv_bfloat16* qp = q + (size_t)b * q_row_stride + (size_t)h * HD + sub * D;
+#pragma unroll
+        for (int d = 0; d < D; d += 2) {
+            const uint32_t w = *reinterpret_cast<const uint32_t*>(qp + d);
+            qf[d] = bf_lo(w) * scale; qf[d + 1] = bf_hi(w) * scale;
+        }
+    }
+    const __nv_bfloat16* kb = k_cache + ((size_t)b * Hkv + hk) * (size_t)max_len * HD + sub * D;
+    const __nv_bfloat16* vb = v_cache + ((size_t)b * Hkv + hk) * (size_t)max_len * HD + sub * D;
+    float mx = -INFINITY, l = 0.0f, acc[D];
+#pragma unroll
+    for (int d = 0; d < D; ++d) acc[d] = 0.0f;
+    for (int j = j0 + slot; j < j1; j += ATT_SLOTS) {
+        float kf[D];
+#pragma unroll
+        for (int d = 0; d < D; d += 8) {
+            const uint4 w = __ldg(reinterpret_cast<const uint4*>(kb + (size_t)j * HD + d));
+            kf[d] = bf_lo(w.x); kf[d + 1] = bf_hi(w.x); kf[d + 2] = bf_lo(w.y); kf[d + 3] = bf_hi(w.y);
+            kf[d + 4] = bf_lo(w.z); kf[d + 5] = bf_hi(w.z); kf[d + 6] = bf_lo(w.w); kf[d + 7] = bf_hi(w.w);
+        }
+        float s = 0.0f;
+#pragma unroll
+        for (int d = 0; d < D; ++d) s = fmaf(qf[d], kf[d], s);
+        s += __shfl_xor_sync(0xffffffffu, s, 1); s += __shfl_xor_sync(0xffffffffu, s, 2); s += __shfl_xor_sync(0xffffffffu, s, 4);
+        const float mn = fmaxf(mx, s), corr = __expf(mx - mn), p = __expf(s - mn);
+        l = l * corr + p;
+#pragma unroll
+        for (int d = 0; d < D; d += 8) {
+            const uint4 w = __ldg(reinterpret_cast<const uint4*>(vb + (size_t)j * HD + d));
+            const float vf[8] = {bf_lo(w.x), bf_hi(w.x), bf_lo(w.y), bf_hi(w.y), bf_lo(w.z), bf_hi(w.z), bf_lo(w.w), bf_hi(w.w)};
+#pragma unroll
+            for (int e = 0; e < 8; ++e) acc[d + e] = fmaf(p, vf[e], acc[d + e] * corr);
+        }
+        mx = mn;
+    }
+    // combine the 16 key slots of the CTA
+    if (sub == 0) { sm_m[slot] = mx; sm_l[slot] = l; }
+#pragma unroll
+    for (int d = 0; d < D; ++d) sm_acc[slot][sub * D + d] = acc[d];
+    __syncthreads();
+    float* my = part + ((size_t)bh * splits + split) * (HD + 2);
+    if (threadIdx.x < HD) {
+        float M = -INFINITY;
+#pragma unroll
+        for (int s2 = 0; s2 < ATT_SLOTS; ++s2) M = fmaxf(M, sm_m[s2]);
+        float L = 0.0f, a = 0.0f;
+#pragma unroll
+        for (int s2 = 0; s2 < ATT_SLOTS; ++s2) {
+            const float w = (sm_m[s2] == -INFINITY) ? 0.0f : __expf(sm_m[s2] - M);
+            L = fmaf(sm_l[s2], w, L); a = fmaf(sm_acc[s2][threadIdx.x], w, a);
+        }
+        if (splits == 1) {
+            out[(size_t)b * Hq * HD + (size_t)h * HD + threadIdx.x] = __float2bfloat16_rn(L > 0.0f ? a / L : 0.0f);
+        } else {
+            my[threadIdx.x] = a;
+            if (threadIdx.x == 0) { my[HD] = M; my[HD + 1] = L; }
+        }
+    }
+    if (splits == 1) return;
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const unsigned int t = atomicAdd(tickets + bh, 1u);
+        is_last = (t == (unsigned int)splits - 1u);
+        if (is_last) tickets[bh] = 0u;                          // leave the counter as it was found
+    }
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+    if (threadIdx.x < HD) {
+        const float* base = part + (size_t)bh * splits * (HD + 2);
+        float M = -INFINITY;
+        for (int s2 = 0; s2 < splits; ++s2) M = fmaxf(M, __ldcg(base + (size_t)s2 * (HD + 2) + HD));
+        float L = 0.0f, a = 0.0f;
+        for (int s2 = 0; s2 < splits; ++s2) {
+            const float ms = __ldcg(base + (size_t)s2 * (HD + 2) + HD);
+            const float w = (ms == -INFINITY) ? 0.0f : __expf(ms - M);
+            L = fmaf(__ldcg(base + (size_t)s2 * (HD + 2) + HD + 1), w, L);
+            a = fmaf(__ldcg(base + (size_t)s2 * (HD + 2) + threadIdx.x), w, a);
+        }
+        out[(size_t)b * Hq * HD + (size_t)h * HD + threadIdx.x] = __float2bfloat16_rn(L > 0.0f ? a / L : 0.0f);
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// act[m, i] = silu(gu[m, i]) * gu[m, I + i]
+// ---------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) k_silu_mul(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ act,
+                                                  int64_t M, int I, int hf_rounding) {
+    const int64_t vec_per_row = I / 8, total = M * vec_per_row;
+    for (int64_t v = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; v < total; v += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t m = v / vec_per_row, c = v - m * vec_per_row;
+        const uint4 g = __ldg(reinterpret_cast<const uint4*>(gu + m * 2 * (int64_t)I) + c);
+        const uint4 u = __ldg(reinterpret_cast<const uint4*>(gu + m * 2 * (int64_t)I + I) + c);
+        const uint32_t gw[4] = {g.x, g.y, g.z, g.w}, uw[4] = {u.x, u.y, u.z, u.w};
+        uint32_t o[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const float g0 = bf_lo(gw[j]), g1 = bf_hi(gw[j]);
+            float s0 = g0 / (1.0f + expf(-g0)), s1 = g1 / (1.0f + expf(-g1));
+            if (hf_rounding) { s0 = bf16r(s0); s1 = bf16r(s1); }
+            o[j] = pack_bf2(__fmul_rn(s0, bf_lo(uw[j])), __fmul_rn(s1, bf_hi(uw[j])));
+        }
+        reinterpret_cast<uint4*>(act + m * (int64_t)I)[c] = make_uint4(o[0], o[1], o[2], o[3]);
+    }
+}
+
+static inline bool al16p(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+}  // namespace lq
+
+using namespace lq;
+
+extern "C" {
+
+int lq_add_rmsnorm(void* h, const void* delta, const void* gamma, float eps, void* y, int64_t M, int64_t K, int hf_rounding,
+                   lq_stream_t stream) {
+    if (!h || !gamma || !y || !al16p(h) || !al16p(gamma) || !al16p(y) || (delta && !al16p(delta))) return LQ_EINVAL;
+    if (M < 0 || K <= 0 || (K % 8) != 0 || M >= (1ll << 31) || K >= (1ll << 24)) return LQ_EUNSUPPORTED;
+    if (M == 0) return LQ_OK;
+    { int rc = ensure_device_for(h); if (rc) return rc; }
+    k_add_rmsnorm<<<(unsigned)M, NORM_THREADS, 0, (cudaStream_t)stream>>>((__nv_bfloat16*)h, (const __nv_bfloat16*)delta,
+                                                                           (const __nv_bfloat16*)gamma, eps, (__nv_bfloat16*)y, (int)K,
+                                                                           hf_rounding);
+    return check_launch("k_add_rmsnorm");
+}
+
+int lq_rope_kv_store(void* qkv, const int64_t* positions, const float* inv_freq, void* k_cache, void* v_cache, int64_t M,
+                     int tokens_per_seq, int Hq, int Hkv, int hd, int64_t max_len, int hf_rounding, lq_stream_t stream) {
+    if (!qkv || !positions || !inv_freq || !k_cache || !v_cache) return LQ_EINVAL;
+    if (M < 0 || tokens_per_seq < 1 || Hq < 1 || Hkv < 1 || (Hq % Hkv) != 0 || hd < 8 || hd > 512 || (hd % 4) != 0 || max_len < 1 ||
+        max_len >= (1ll << 31) || M >= (1ll << 31) || Hq + 2 * Hkv > 65535)
+        return LQ_EUNSUPPORTED;
+    if (M == 0) return LQ_OK;
+    { int rc = ensure_device_for(qkv); if (rc) return rc; }
+    dim3 grid((unsigned)M, (unsigned)(Hq + 2 * Hkv));
+    k_rope_kv_store<<<grid, hd / 2, 0, (cudaStream_t)stream>>>((__nv_bfloat16*)qkv, (const long long*)positions, inv_freq,
+                                                               (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, tokens_per_seq, Hq,
+                                                               Hkv, hd, (int)max_len, hf_rounding);
+    return check_launch("k_rope_kv_store");
+}
+
+static int attn_splits(int64_t B, int Hq, int64_t max_len) {
+    const int64_t ctas = B * Hq;
+    int64_t s = (2 * (int64_t)sm_count() + ctas - 1) / ctas;      // about two CTAs per SM in flight
+    const int64_t cap = (max_len + 127) / 128;                      // at least 128 keys per split
+    if (s > cap) s = cap;
+    if (s > 32) s = 32;
+    if (s < 1) s = 1;
+    return (int)s;
+}
+
+size_t lq_decode_attention_workspace_bytes(int64_t B, int Hq, int hd, int64_t max_len) {
+    if (B <= 0 || Hq <= 0 || hd <= 0 || max_len <= 0) return 0;
+    const int s = attn_splits(B, Hq, max_len);
+    return (size_t)B * Hq * ((size_t)s * (hd + 2) * sizeof(float) + sizeof(unsigned int));
+}
+
+int lq_decode_attention(const void* q, int64_t q_row_stride, const void* k_cache, const void* v_cache, const int64_t* positions,
+                        void* out, int64_t B, int Hq, int Hkv, int hd, int64_t max_len, float scale, void* workspace,
+                        size_t workspace_bytes, lq_stream_t stream) {
+    if (!q || !k_cache || !v_cache || !positions || !out || !al16p(q) || !al16p(k_cache) || !al16p(v_cache)) return LQ_EINVAL;
+    if (B < 0 || Hq < 1 || Hkv < 1 || (Hq % Hkv) != 0 || (hd != 64 && hd != 128) || max_len < 1 || max_len >= (1ll << 31) ||
+        B * Hq >= (1ll << 31) || (q_row_stride % 8) != 0)
+        return LQ_EUNSUPPORTED;
+    if (B == 0) return LQ_OK;
+    { int rc = ensure_device_for(q); if (rc) return rc; }
+    const int splits = attn_splits(B, Hq, max_len);
+    float* part = nullptr; unsigned int* tickets = nullptr;
+    if (splits > 1) {
+        if (!workspace || workspace_bytes < lq_decode_attention_workspace_bytes(B, Hq, hd, max_len) || !al16p(workspace)) return LQ_EWORKSPACE;
+        part = (float*)workspace;
+        tickets = (unsigned int*)(part + (size_t)B * Hq * splits * (hd + 2));
+    }
+    dim3 grid((unsigned)(B * Hq), (unsigned)splits);
+    cudaStream_t st = (cudaStream_t)stream;
+    if (hd == 128)
+        k_decode_attn<128><<<grid, ATT_THREADS, 0, st>>>((const __nv_bfloat16*)q, (int)q_row_stride, (const __nv_bfloat16*)k_cache,
+                                                         (const __nv_bfloat16*)v_cache, (const long long*)positions, (__nv_bfloat16*)out,
+                                                         Hq, Hkv, (int)max_len, scale, part, tickets);
+    else
+        k_decode_attn<64><<<grid, ATT_THREADS, 0, st>>>((const __nv_bfloat16*)q, (int)q_row_stride, (const __nv_bfloat16*)k_cache,
+                                                        (const __nv_bfloat16*)v_cache, (const long long*)positions, (__nv_bfloat16*)out,
+                                                        Hq, Hkv, (int)max_len, scale, part, tickets);
+    return check_launch("k_decode_attn");
+}
+
+int lq_silu_mul(const void* gate_up, void* act, int64_t M, int64_t I, int hf_rounding, lq_stream_t stream) {
+    if (!gate_up || !act || !al16p(gate_up) || !al16p(act)) return LQ_EINVAL;
+    if (M < 0 || I <= 0 || (I % 8) != 0 || I >= (1ll << 30)) return LQ_EUNSUPPORTED;
+    if (M == 0) return LQ_OK;
+    { int rc = ensure_device_for(gate_up); if (rc) return rc; }
+    const int64_t total = M * (I / 8);
+    int64_t g = (total + 255) / 256;
+    const int64_t cap = (int64_t)sm_count() * 8;
+    if (g > cap) g = cap;
+    k_silu_mul<<<(unsigned)g, 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)gate_up, (__nv_bfloat16*)act, M, (int)I, hf_rounding);
+    return check_launch("k_silu_mul");
+}
+
+}  // extern "C"

@@ -63,8 +63,51 @@ struct GemmParams {
     float alpha;
     __nv_bfloat16* out;            // [M, R]
     int32_t* acc_out;              // int8: raw accumulators [M, R] or null
-    void* partial;                 // split-K partial sums [splits][M][R] (fp32 / int32)
+    void* partial;                 // split-K partial sums [splits][M][R] (fp32 / int32); balanced mode: slots + flags
+    int sk_grid;                   // balanced mode (SK): number of CTAs the k-block units are dealt to
 };
+
+// One CTA's share of the work as a sequence of segments (a tile and a range of its k-blocks).
+//   tile-cyclic (SK = false): items blockIdx.x, blockIdx.x + gridDim.x, ...; an item is one (row tile, token tile,
+//     split) and its whole k range.
+//   balanced (SK = true): the (tile, k-block) units of the whole problem, tile-major, are dealt to the CTAs as equal
+//     contiguous ranges, so a CTA's range may start and end in the middle of a tile ("stream-K").  The segment that
+//     holds a tile's first k-block owns the tile's output; segments that start later in the tile hand their partial
+//     sums to the owner through global memory.
+struct Seg { int r_tile, t_tile, split, kb0, kb1; };
+template <bool SK>
+struct SegWalk {
+    int pos, end;
+    __device__ __forceinline__ explicit SegWalk(const GemmParams& p) {
+        if (SK) {
+            const long long units = (long long)p.r_tiles * p.t_tiles * p.kb_total;
+            pos = (int)(units * blockIdx.x / gridDim.x);
+            end = (int)(units * (blockIdx.x + 1) / gridDim.x);
+        } else {
+            pos = (int)blockIdx.x;
+            end = p.r_tiles * p.t_tiles * p.splits;
+        }
+    }
+    __device__ __forceinline__ bool next(const GemmParams& p, Seg& s) {
+        if (pos >= end) return false;
+        if (SK) {
+            const int tile = pos / p.kb_total;
+            s.kb0 = pos - tile * p.kb_total;
+            s.kb1 = min(p.kb_total, s.kb0 + (end - pos));
+            s.r_tile = tile % p.r_tiles; s.t_tile = tile / p.r_tiles; s.split = 0;
+            pos += s.kb1 - s.kb0;
+        } else {
+            s.r_tile = pos % p.r_tiles; s.t_tile = (pos / p.r_tiles) % p.t_tiles; s.split = pos / (p.t_tiles * p.r_tiles);
+            s.kb0 = s.split * p.kb_per_split; s.kb1 = min(p.kb_total, s.kb0 + p.kb_per_split);
+            pos += (int)gridDim.x;
+        }
+        return true;
+    }
+};
+// Balanced mode: first unit of CTA c's range.
+__device__ __forceinline__ int sk_first_unit(const GemmParams& p, int c) {
+    return (int)((long long)p.r_tiles * p.t_tiles * p.kb_total * c / gridDim.x);
+}
 
 // RT = weight-row tiles (of 128 rows) a CTA computes against one token tile.  RT = 2 halves the token-tile
 // bytes fetched from L2 per flop (the dominant operand traffic) at the cost of a shallower pipeline.
@@ -138,9 +181,10 @@ __device__ __forceinline__ uint4 dequant8(uint32_t w, __nv_bfloat162 z128, __nv_
 // ---------------------------------------------------------------------------------------------
 // The kernel
 // ---------------------------------------------------------------------------------------------
-template <int KIND, int TN, int RT, bool TA>
+template <int KIND, int TN, int RT, bool TA, bool SK>
 __global__ void __launch_bounds__(Cfg<KIND, TN, RT, TA>::THREADS, 1)
 k_gemm(const __grid_constant__ CUtensorMap map_tok, const __grid_constant__ CUtensorMap map_w, const GemmParams p) {
+    static_assert(!SK || (KIND != KIND_I8 && RT == 1), "balanced mode: A16W4 kinds, one row tile per CTA");
     using C = Cfg<KIND, TN, RT, TA>;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -179,7 +223,6 @@ k_gemm(const __grid_constant__ CUtensorMap map_tok, const __grid_constant__ CUte
     const uint32_t tmem_base = ctl->tmem_base;
     const bool prof = g_gemm_prof_on != 0;
 
-    const int n_items = p.r_tiles * p.t_tiles * p.splits;     // r_tiles counts groups of RT row tiles
 
     if (warp == 0) {
         // ===================== TMA producer =====================
@@ -187,10 +230,11 @@ k_gemm(const __grid_constant__ CUtensorMap map_tok, const __grid_constant__ CUte
             int stage = 0; uint32_t phase = 0;
             bool ok = true;
             long long w_empty = 0;
-            for (int item = blockIdx.x; ok && item < n_items; item += gridDim.x) {
-                const int r_tile = item % p.r_tiles, t_tile = (item / p.r_tiles) % p.t_tiles, split = item / (p.t_tiles * p.r_tiles);
-                const int kb0 = split * p.kb_per_split, kb1 = min(p.kb_total, kb0 + p.kb_per_split);
-                for (int kb = kb0; kb < kb1; ++kb) {
+            SegWalk<SK> walk(p);
+            Seg sg;
+            while (ok && walk.next(p, sg)) {
+                const int r_tile = sg.r_tile, t_tile = sg.t_tile;
+                for (int kb = sg.kb0; kb < sg.kb1; ++kb) {
                     if (!(ok = mbar_wait_t(smem_u32(&ctl->empty[stage]), phase ^ 1u, abort_flag, prof, w_empty))) break;
                     const uint32_t bar = smem_u32(&ctl->full[stage]);
                     mbar_expect_tx(bar, C::TX_BYTES);
@@ -219,9 +263,10 @@ k_gemm(const __grid_constant__ CUtensorMap map_tok, const __grid_constant__ CUte
             bool ok = true;
             long long w_full = 0, w_aready = 0, w_acc = 0;
             const long long t_role = prof ? clock64() : 0;
-            for (int item = blockIdx.x; ok && item < n_items; item += gridDim.x) {
-                const int split = item / (p.t_tiles * p.r_tiles);
-                const int kb0 = split * p.kb_per_split, kb1 = min(p.kb_total, kb0 + p.kb_per_split);
+            SegWalk<SK> walk(p);
+            Seg sg;
+            while (ok && walk.next(p, sg)) {
+                const int kb0 = sg.kb0, kb1 = sg.kb1;
                 if (!(ok = mbar_wait_t(smem_u32(&ctl->acc_empty[acc]), acc_phase ^ 1u, abort_flag, prof, w_acc))) break;
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + (uint32_t)(acc * C::ACC_COLS);
@@ -274,10 +319,38 @@ k_gemm(const __grid_constant__ CUtensorMap map_tok, const __grid_constant__ CUte
         bool ok = true;
         long long w_accf = 0;
         const long long t_role = prof ? clock64() : 0;
-        for (int item = blockIdx.x; ok && item < n_items; item += gridDim.x) {
-            const int r_tile = item % p.r_tiles, t_tile = (item / p.r_tiles) % p.t_tiles, split = item / (p.t_tiles * p.r_tiles);
+        SegWalk<SK> walk(p);
+        Seg sg;
+        // balanced mode: partial sums travel as [CTA][token column][weight row] fp32 slots, one flag per (CTA, lane quarter)
+        float* const sk_slots = reinterpret_cast<float*>(p.partial);
+        volatile unsigned int* const sk_flags = SK ? reinterpret_cast<volatile unsigned int*>(sk_slots + (size_t)gridDim.x * (TN * TILE_R)) : nullptr;
+        while (ok && walk.next(p, sg)) {
+            const int r_tile = sg.r_tile, t_tile = sg.t_tile, split = sg.split;
             if (!(ok = mbar_wait_t(smem_u32(&ctl->acc_full[acc]), acc_phase, abort_flag, prof, w_accf))) break;
             tc_fence_after();
+            const bool sk_contrib = SK && sg.kb0 != 0;                       // starts inside a tile: hands its sums to the owner
+            const bool sk_owner = SK && sg.kb0 == 0 && sg.kb1 < p.kb_total;   // holds the tile's first k-block, not its last
+            int sk_last = (int)blockIdx.x;                                   // owner: CTAs blockIdx.x+1 .. sk_last contribute
+            if (sk_owner) {
+                const int tile_end = (sg.t_tile * p.r_tiles + sg.r_tile + 1) * p.kb_total;
+                while (sk_last + 1 < (int)gridDim.x && sk_first_unit(p, sk_last + 1) < tile_end) ++sk_last;
+                // every lane waits (bounded) for this lane quarter's flag of each contributor: its own acquire
+                for (int c = (int)blockIdx.x + 1; c <= sk_last && ok; ++c) {
+                    const long long t0 = clock64();
+                    unsigned int seen = 0;
+                    for (uint32_t it = 0;; ++it) {
+                        asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(sk_flags + c * 4 + quad) : "memory");
+                        if (seen != 0u) break;
+                        if ((it & 15u) == 15u) {
+                            if (*abort_flag) break;
+                            if (clock64() - t0 > WAIT_BUDGET_CYCLES) { *abort_flag = 1; break; }
+                            __nanosleep(64);
+                        }
+                    }
+                    ok = __all_sync(0xffffffffu, seen != 0u) != 0;
+                }
+                if (!ok) break;
+            }
 #pragma unroll 1
             for (int rr = 0; rr < RT; ++rr) {
                 const int r = (r_tile * RT + rr) * TILE_R + quad * 32 + lane;
@@ -295,6 +368,22 @@ k_gemm(const __grid_constant__ CUtensorMap map_tok, const __grid_constant__ CUte
                         tmem_ld16(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * C::ACC_COLS + rr * TN + c0 + 16 * h),
                                   *reinterpret_cast<uint32_t(*)[16]>(&v[16 * h]));
                     tmem_ld_wait();
+                    if (SK) {
+                        const int row = quad * 32 + lane;
+                        if (sk_contrib) {              // lanes are consecutive weight rows: 128-byte coalesced stores
+                            float* dst = sk_slots + (size_t)blockIdx.x * (TN * TILE_R) + (size_t)c0 * TILE_R + row;
+#pragma unroll
+                            for (int j = 0; j < SLAB; ++j) dst[j * TILE_R] = __uint_as_float(v[j]);
+                            continue;
+                        }
+                        if (sk_owner) {                // k order: own sums first, then the contributors in CTA order
+                            for (int c = (int)blockIdx.x + 1; c <= sk_last; ++c) {
+                                const float* src = sk_slots + (size_t)c * (TN * TILE_R) + (size_t)c0 * TILE_R + row;
+#pragma unroll
+                                for (int j = 0; j < SLAB; ++j) v[j] = __float_as_uint(__fadd_rn(__uint_as_float(v[j]), __ldcg(src + j * TILE_R)));
+                            }
+                        }
+                    }
                     if (p.splits == 1 && !(C::I8 && p.acc_out) && t_tile * TN + c0 + SLAB <= p.M &&
                         (!C::I8 || (reinterpret_cast<uintptr_t>(p.row_scale) & 15) == 0)) {       // warp-uniform condition
                         // Full slab of SLAB tokens.  Two results per conversion instruction (the single-value conversion
@@ -364,8 +453,15 @@ k_gemm(const __grid_constant__ CUtensorMap map_tok, const __grid_constant__ CUte
                 }
             }
             tc_fence_before();
+            if (sk_contrib) __threadfence();               // this lane's slot stores, before the warp's flag
             __syncwarp();
-            if (lane == 0) mbar_arrive(smem_u32(&ctl->acc_empty[acc]));
+            if (lane == 0) {
+                mbar_arrive(smem_u32(&ctl->acc_empty[acc]));
+                if (sk_contrib) {
+                    const unsigned int one = 1u;
+                    asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(sk_flags + blockIdx.x * 4 + quad), "r"(one) : "memory");
+                }
+            }
             if (++acc == C::ACC_BUFS) { acc = 0; acc_phase ^= 1u; }
         }
         if (prof && warp == 2 && lane == 0) {
@@ -391,27 +487,21 @@ k_gemm(const __grid_constant__ CUtensorMap map_tok, const __grid_constant__ CUte
             const int tt = ((warp - 6) & 3) * 32 + lane;
             const int groups_per_row = p.wcols / p.group;
             const uint32_t ta_addr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)C::TA_COL0;
-            struct Pos { int item, kb, kb1, r_tile; };
-            auto open_item = [&](Pos& q) {
-                const int split = q.item / (p.t_tiles * p.r_tiles);
-                q.r_tile = q.item % p.r_tiles;
-                q.kb = split * p.kb_per_split;
-                q.kb1 = min(p.kb_total, q.kb + p.kb_per_split);
-            };
+            // position in this CTA's sequence of k-blocks: the walker stands behind the segment that holds k-block `kb`
+            struct Pos { SegWalk<SK> walk; int kb, kb1, r_tile; bool valid; };
             auto advance = [&](Pos& q, int n) {
                 q.kb += n;
-                while (q.item < n_items && q.kb >= q.kb1) {
+                while (q.valid && q.kb >= q.kb1) {
                     const int over = q.kb - q.kb1;
-                    q.item += gridDim.x;
-                    if (q.item >= n_items) break;
-                    open_item(q);
-                    q.kb += over;
+                    Seg sg;
+                    if (!q.walk.next(p, sg)) { q.valid = false; break; }
+                    q.kb = sg.kb0 + over; q.kb1 = sg.kb1; q.r_tile = sg.r_tile;
                 }
             };
             // (scale | zero << 16) as raw bf16 bits for this thread's two 32-element slots of row tile r at position q
             auto load_qp2 = [&](const Pos& q, int r, uint32_t& a, uint32_t& b) {
                 a = b = 0u;
-                if (q.item >= n_items) return;
+                if (!q.valid) return;
                 int wrow, k0, k1;
                 if (TA && KIND == KIND_DGRAD) {            // rows n_lane and n_lane+32, one k group per warp
                     wrow = q.kb * 64 + lane; k0 = k1 = q.r_tile * TILE_R + quarter * 32;
@@ -431,8 +521,9 @@ k_gemm(const __grid_constant__ CUtensorMap map_tok, const __grid_constant__ CUte
                 b = (uint32_t)__ldg(sp + g1) | ((uint32_t)__ldg(zp + g1) << 16);
             };
             constexpr int PF = 2;                                          // own stages of qparam prefetch
-            Pos cur{(int)blockIdx.x, 0, 0, 0};
-            if (cur.item < n_items) { open_item(cur); advance(cur, team); }
+            Pos cur{SegWalk<SK>(p), 0, 0, 0, true};
+            advance(cur, 0);                                               // opens the first segment (kb == kb1 == 0)
+            advance(cur, team);
             Pos pre = cur;
             uint32_t qa[PF][RT], qb[PF][RT];
 #pragma unroll
@@ -446,10 +537,10 @@ k_gemm(const __grid_constant__ CUtensorMap map_tok, const __grid_constant__ CUte
             long long w_dq = 0;
             const long long t_role = prof ? clock64() : 0;
             const __nv_bfloat162 c128 = __float2bfloat162_rn(128.0f);
-            while (ok && cur.item < n_items) {
+            while (ok && cur.valid) {
 #pragma unroll
                 for (int u = 0; u < PF; ++u) {
-                    if (cur.item >= n_items) break;
+                    if (!cur.valid) break;
                     uint32_t ca[RT], cb[RT];
 #pragma unroll
                     for (int r = 0; r < RT; ++r) { ca[r] = qa[u][r]; cb[r] = qb[u][r]; load_qp2(pre, r, qa[u][r], qb[u][r]); }
@@ -587,7 +678,11 @@ static bool a_operand_in_tmem(int kind) {
     return kind == KIND_FWD;
 }
 
-struct Plan { int tn, rt, r_tiles, t_tiles, splits, kb_total, kb_per_split; bool skinny; };
+struct Plan { int tn, rt, r_tiles, t_tiles, splits, kb_total, kb_per_split; bool skinny; bool sk; int sk_grid; };
+
+// Balanced ("stream-K") forward: bytes of the per-CTA partial-sum slots and of the flags behind them.
+static size_t sk_slot_bytes(const Plan& pl) { return (size_t)pl.sk_grid * (size_t)pl.tn * TILE_R * 4; }
+static size_t sk_flag_bytes(const Plan& pl) { return (size_t)pl.sk_grid * 4 * sizeof(unsigned int); }
 
 // group: quantization group size, or 0 when unknown (the skinny path needs 64, 128 or 256)
 static Plan make_plan(int kind, int64_t M, int64_t N, int64_t K, int group = 128) {
@@ -611,6 +706,21 @@ static Plan make_plan(int kind, int64_t M, int64_t N, int64_t K, int group = 128
     pl.kb_total = (int)((Cc + bk - 1) / bk);
     const int tiles = pl.r_tiles * pl.t_tiles;
     const int sms = sm_count();
+    // Balanced ("stream-K") forward, opt-in with LQ_GEMM_BALANCE=1: whole tiles leave SMs idle or a last wave nearly
+    // empty when there are few tiles per SM, so the (tile, k-block) units are dealt out evenly instead and partial
+    // sums are handed over through global memory.  Measured on the four Llama-2-7B shapes it does not pay yet: the
+    // owner's epilogue pulls up to five contributors' partial sums with latency-bound loads (176 us against 124 us
+    // for the four layers at 128 tokens; equal at 512), so the tile-cyclic plan stays the default.
+    if (kind == KIND_FWD && pl.tn >= 64 && tiles <= 2 * sms && getenv("LQ_GEMM_BALANCE")) {
+        const long long units = (long long)tiles * pl.kb_total;
+        long long grid = units / 4;                                  // at least 4 k-blocks per CTA
+        if (grid > sms) grid = sms;
+        if (grid < 1) grid = 1;
+        if (grid > tiles || tiles % grid != 0) {                     // (whole tiles per CTA need no hand-over at all)
+            pl.sk = true; pl.sk_grid = (int)grid; pl.splits = 1; pl.kb_per_split = pl.kb_total;
+            return pl;
+        }
+    }
     int splits = 1;
     if (tiles * 2 <= sms) {
         splits = sms / tiles;
@@ -653,20 +763,28 @@ static int make_map(CUtensorMap* m, const void* base, CUtensorMapDataType dt, in
     return LQ_OK;
 }
 
-template <int KIND, int TN, int RT, bool TA = false>
+template <int KIND, int TN, int RT, bool TA = false, bool SK = false>
 static int launch_tn(const CUtensorMap& mt, const CUtensorMap& mw, const GemmParams& p, cudaStream_t st) {
     using C = Cfg<KIND, TN, RT, TA>;
     static bool attr_done[64] = {};
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev >= 0 && dev < 64 && !attr_done[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(k_gemm<KIND, TN, RT, TA>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
+        cudaError_t e = cudaFuncSetAttribute(k_gemm<KIND, TN, RT, TA, SK>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
         if (e != cudaSuccess) { set_cuda_error(e, "cudaFuncSetAttribute"); return LQ_ECUDA; }
         attr_done[dev] = true;
     }
+    if (SK) {
+        // hand-over flags start at zero in every launch (a memset node when the launch is being captured)
+        unsigned char* flags = reinterpret_cast<unsigned char*>(p.partial) + (size_t)p.sk_grid * (size_t)TN * TILE_R * 4;
+        cudaError_t e = cudaMemsetAsync(flags, 0, (size_t)p.sk_grid * 4 * sizeof(unsigned int), st);
+        if (e != cudaSuccess) { set_cuda_error(e, "cudaMemsetAsync(hand-over flags)"); return LQ_ECUDA; }
+        k_gemm<KIND, TN, RT, TA, SK><<<p.sk_grid, C::THREADS, C::SMEM_BYTES, st>>>(mt, mw, p);
+        return check_launch("k_gemm (balanced)");
+    }
     const int items = p.r_tiles * p.t_tiles * p.splits;
     const int grid = items < sm_count() ? items : sm_count();
-    k_gemm<KIND, TN, RT, TA><<<grid, C::THREADS, C::SMEM_BYTES, st>>>(mt, mw, p);
+    k_gemm<KIND, TN, RT, TA, SK><<<grid, C::THREADS, C::SMEM_BYTES, st>>>(mt, mw, p);
     int rc = check_launch("k_gemm");
     if (rc) return rc;
     if (p.splits > 1) {
@@ -677,6 +795,16 @@ static int launch_tn(const CUtensorMap& mt, const CUtensorMap& mw, const GemmPar
         rc = check_launch("k_splitk_reduce");
     }
     return rc;
+}
+// balanced forward (token tiles of 64 / 128 / 256), either placement of the weight tile
+template <bool TA>
+static int launch_fwd_sk(int tn, const CUtensorMap& mt, const CUtensorMap& mw, const GemmParams& p, cudaStream_t st) {
+    switch (tn) {
+        case 64: return launch_tn<KIND_FWD, 64, 1, TA, true>(mt, mw, p, st);
+        case 128: return launch_tn<KIND_FWD, 128, 1, TA, true>(mt, mw, p, st);
+        case 256: return launch_tn<KIND_FWD, 256, 1, TA, true>(mt, mw, p, st);
+    }
+    return LQ_EUNSUPPORTED;
 }
 template <int KIND>
 static int launch_kind_ta(int tn, const CUtensorMap& mt, const CUtensorMap& mw, const GemmParams& p, cudaStream_t st) {
@@ -714,6 +842,10 @@ static int run_gemm(int kind, const void* tok, const void* w, GemmParams p, int6
         if (!workspace || workspace_bytes < need || !al16(workspace)) return LQ_EWORKSPACE;
         p.partial = workspace;
     }
+    if (pl.sk) {
+        if (!workspace || workspace_bytes < sk_slot_bytes(pl) + sk_flag_bytes(pl) || !al16(workspace)) return LQ_EWORKSPACE;
+        p.partial = workspace; p.sk_grid = pl.sk_grid;
+    }
     if (pl.skinny) {
         SkinnyParams sp{};
         sp.x = (const __nv_bfloat16*)tok; sp.qweight = (const uint8_t*)w; sp.scales = p.scales; sp.zeros = p.zeros;
@@ -745,6 +877,7 @@ static int run_gemm(int kind, const void* tok, const void* w, GemmParams p, int6
     if (rc) return rc;
     switch (kind) {
         case KIND_FWD:
+            if (pl.sk) return a_operand_in_tmem(kind) ? launch_fwd_sk<true>(pl.tn, mt, mw, p, st) : launch_fwd_sk<false>(pl.tn, mt, mw, p, st);
             return (pl.rt == 1 && a_operand_in_tmem(kind)) ? launch_kind_ta<KIND_FWD>(pl.tn, mt, mw, p, st)
                                                        : launch_kind<KIND_FWD>(pl.tn, pl.rt, mt, mw, p, st);
         case KIND_DGRAD:
@@ -764,14 +897,15 @@ extern "C" {
 size_t lq_gemm_workspace_bytes(int kind, int64_t M, int64_t N, int64_t K) {
     if (kind < 0 || kind > 2 || M <= 0 || N <= 0 || K <= 0) return 0;
     // the forward plan depends on the group size (decode-sized kernel or tensor-core kernel): cover both
-    int splits = 1;
+    const int64_t R = (kind == KIND_DGRAD) ? K : N;
+    size_t need = 0;
     for (int group : {64, 128, 0}) {
         const Plan pl = make_plan(kind, M, N, K, group);
-        if (pl.splits > splits) splits = pl.splits;
+        size_t b = pl.splits > 1 ? (size_t)pl.splits * (size_t)M * (size_t)R * 4 : 0;
+        if (pl.sk) b = sk_slot_bytes(pl) + sk_flag_bytes(pl);
+        if (b > need) need = b;
     }
-    if (splits <= 1) return 0;
-    const int64_t R = (kind == KIND_DGRAD) ? K : N;
-    return (size_t)splits * (size_t)M * (size_t)R * 4;
+    return need;
 }
 
 static bool shape_ok_w4(int64_t M, int64_t N, int64_t K, int group) {
@@ -872,7 +1006,7 @@ int lq_gemm_a16w4_fwd_static(const void* x, const int8_t* qweight, const void* s
     // Partial sums needed by this shape's split-K plan; shapes that need more than the array holds are refused
     // (host arithmetic only, before anything touches the device).
     const Plan pl = make_plan(KIND_FWD, M, N, K, group);
-    const size_t need = pl.splits > 1 ? (size_t)pl.splits * (size_t)M * (size_t)N * 4 : 0;
+    const size_t need = pl.sk ? sk_slot_bytes(pl) + sk_flag_bytes(pl) : (pl.splits > 1 ? (size_t)pl.splits * (size_t)M * (size_t)N * 4 : 0);
     if (need > (size_t)LQ_STATIC_SCRATCH_BYTES) {
         lq::set_cuda_error(cudaErrorInvalidValue, "lq_gemm_a16w4_fwd_static: shape needs more scratch than the built-in 8 MiB; "
                                                   "use lq_gemm_a16w4_fwd with a workspace");

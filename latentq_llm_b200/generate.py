@@ -76,3 +76,122 @@ class GraphedGreedyDecoder:
                     self._step()
                 toks.append(self.tok.clone())
         return torch.cat(toks, dim=1)
+
+
+class FusedLlamaGreedyDecoder:
+    """Greedy decode of a Llama-architecture model (RMSNorm / RoPE / SwiGLU, no biases) whose decoder linears are
+    `QLinearA16W4`, with the decode step written as a chain of this library's kernels instead of the eager modules:
+
+        per layer   residual add + RMSNorm -> fused q|k|v projection (one launch, N = (Hq + 2 Hkv) hd) -> RoPE on q, k
+                    with k, v written into the KV cache -> single-query attention over the cache -> o projection ->
+                    residual add + RMSNorm -> fused gate|up projection (N = 2 I) -> silu(gate) * up -> down projection
+        then        residual add + final RMSNorm -> lm_head -> argmax -> embedding of the new token
+
+    nine launches per layer (the reference's fusion list: PTQ/quant/fused_attn.py:164-204 fused QKV, :8-58 RoPE,
+    PTQ/quant/fused_mlp.py:84-168 gate/up with the silu epilogue, PTQ/quant/triton_norm.py:7-39 RMSNorm), captured
+    once as a CUDA graph and replayed per token.  The prompt is prefilled through the model's own modules into the
+    same static KV cache.  `hf_rounding=True` rounds intermediates like the eager modules' bf16 tensor ops."""
+
+    def __init__(self, model, batch: int, max_len: int, hf_rounding: bool = True):
+        from transformers import StaticCache
+        from .quant import QLinearA16W4
+        cfg = model.config
+        self.model, self.batch, self.max_len, self.hf = model, batch, max_len, hf_rounding
+        self.device = dev = next(model.parameters()).device
+        self.Hq, self.Hkv = cfg.num_attention_heads, getattr(cfg, "num_key_value_heads", None) or cfg.num_attention_heads
+        self.hd = getattr(cfg, "head_dim", None) or cfg.hidden_size // cfg.num_attention_heads
+        self.D, self.I, self.eps = cfg.hidden_size, cfg.intermediate_size, cfg.rms_norm_eps
+        self.inv_freq = model.model.rotary_emb.inv_freq.detach().to(dev, torch.float32).contiguous()
+        self.cache = StaticCache(config=cfg, max_cache_len=max_len)
+
+        def flat(lin):
+            if not isinstance(lin, QLinearA16W4) or lin.bias is not None:
+                raise TypeError("FusedLlamaGreedyDecoder needs bias-free QLinearA16W4 projections")
+            sc, zr, _ = lin.weight.qparam
+            return lin.weight.data.reshape(-1), sc.reshape(-1), zr.reshape(-1)
+
+        def fuse(*lins):
+            parts = [flat(l) for l in lins]
+            return tuple(torch.cat([p[i] for p in parts]).contiguous() for i in range(3))
+
+        self.layers = []
+        for layer in model.model.layers:
+            a, m = layer.self_attn, layer.mlp
+            self.layers.append(dict(ln1=layer.input_layernorm.weight.detach(), ln2=layer.post_attention_layernorm.weight.detach(),
+                                    qkv=fuse(a.q_proj, a.k_proj, a.v_proj), o=flat(a.o_proj),
+                                    gu=fuse(m.gate_proj, m.up_proj), down=flat(m.down_proj)))
+        bf = dict(dtype=torch.bfloat16, device=dev)
+        self.h = torch.zeros((batch, self.D), **bf)
+        self.xn = torch.zeros((batch, self.D), **bf)
+        self.qkv = torch.zeros((batch, (self.Hq + 2 * self.Hkv) * self.hd), **bf)
+        self.att = torch.zeros((batch, self.Hq * self.hd), **bf)
+        self.tmp = torch.zeros((batch, self.D), **bf)
+        self.gu = torch.zeros((batch, 2 * self.I), **bf)
+        self.act = torch.zeros((batch, self.I), **bf)
+        self.tok = torch.zeros((batch,), dtype=torch.long, device=dev)
+        self.pos = torch.zeros((batch,), dtype=torch.long, device=dev)
+        self.logits = None
+        self.graph = None
+
+    def _step(self):
+        from . import ops
+        D, I, Hq, Hkv, hd = self.D, self.I, self.Hq, self.Hkv, self.hd
+        torch.index_select(self.model.model.embed_tokens.weight, 0, self.tok, out=self.h)
+        delta = None
+        for li, L in enumerate(self.layers):
+            kc, vc = self.cache.layers[li].keys, self.cache.layers[li].values
+            ops.add_rmsnorm(self.h, delta, L["ln1"], self.eps, out=self.xn, hf_rounding=self.hf)
+            ops.gemm_a16w4_fwd(self.xn, *L["qkv"], None, (Hq + 2 * Hkv) * hd, D, out=self.qkv)
+            ops.rope_kv_store(self.qkv, self.pos, self.inv_freq, kc, vc, Hq, Hkv, hd, hf_rounding=self.hf)
+            ops.decode_attention(self.qkv, self.pos, kc, vc, Hq, Hkv, hd, out=self.att)
+            ops.gemm_a16w4_fwd(self.att, *L["o"], None, D, Hq * hd, out=self.tmp)
+            ops.add_rmsnorm(self.h, self.tmp, L["ln2"], self.eps, out=self.xn, hf_rounding=self.hf)
+            ops.gemm_a16w4_fwd(self.xn, *L["gu"], None, 2 * I, D, out=self.gu)
+            ops.silu_mul(self.gu, out=self.act, hf_rounding=self.hf)
+            ops.gemm_a16w4_fwd(self.act, *L["down"], None, D, I, out=self.tmp)
+            delta = self.tmp
+        ops.add_rmsnorm(self.h, delta, self.model.model.norm.weight.detach(), self.eps, out=self.xn, hf_rounding=self.hf)
+        self.logits = torch.nn.functional.linear(self.xn, self.model.lm_head.weight)
+        self.tok.copy_(self.logits.argmax(-1))
+        self.pos.add_(1)
+
+    @torch.no_grad()
+    def _prefill(self, prompt):
+        p = prompt.shape[1]
+        self.cache.reset()
+        with sdpa_kernel(_SDPA):
+            out = self.model(input_ids=prompt, past_key_values=self.cache,
+                             cache_position=torch.arange(p, device=self.device), use_cache=True)
+        return out.logits[:, -1].argmax(-1)
+
+    @torch.no_grad()
+    def _capture(self, first, p):
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):                       # warm-up: lazy initialisations must not be captured
+            self.tok.copy_(first); self.pos.fill_(p)
+            self._step(); self._step()
+        torch.cuda.current_stream().wait_stream(side)
+        self.graph = torch.cuda.CUDAGraph()
+        self.tok.copy_(first); self.pos.fill_(p)
+        with torch.cuda.graph(self.graph):
+            self._step()
+
+    @torch.no_grad()
+    def generate(self, prompt: torch.Tensor, max_new_tokens: int, use_graph: bool = True) -> torch.Tensor:
+        b, p = prompt.shape
+        if b != self.batch or p + max_new_tokens > self.max_len:
+            raise ValueError("prompt does not fit the decoder's batch size / cache length")
+        self.model.eval()
+        if use_graph and self.graph is None:
+            self._capture(self._prefill(prompt), p)         # throw-away prefill: capture needs an initialised cache
+        first = self._prefill(prompt)
+        self.tok.copy_(first); self.pos.fill_(p)
+        toks = [first.clone()]
+        for _ in range(max_new_tokens - 1):
+            if use_graph:
+                self.graph.replay()
+            else:
+                self._step()
+            toks.append(self.tok.clone())
+        return torch.stack(toks, dim=1)

@@ -246,6 +246,31 @@ def adam_a16w4_step(codes, words, grad, scales, zeros, state1, scale1, tmax1, st
         C.byref(hyper), C.byref(opts), _stream()))
 
 
+def adam_a8w8_step(codes, words, grad, qscales, state1, scale1, tmax1, state2, scale2, tmax2, hyper, opts: RequantOpts):
+    """MyAdam.update_step for one A8W8 weight (int8 codes [rows, cols], one scale per row), in place."""
+    _chk(codes, "codes", torch.int8); _chk(words, "words", torch.int32); _chk(grad, "grad"); _chk(qscales, "qscales", grad.dtype)
+    _chk(state1, "state1", torch.uint8); _chk(state2, "state2", torch.uint8)
+    rows, cols = grad.shape
+    n = rows * cols
+    assert codes.numel() == n and words.numel() * 8 == n and qscales.numel() == rows and state1.numel() == n and state2.numel() == n
+    blocks = scale1.numel()
+    L.check("lq_adam_a8w8_step", L.lib.lq_adam_a8w8_step(
+        _ptr(codes), _ptr(words), _ptr(grad), _dt(grad), _ptr(qscales), _dt(qscales), rows, cols,
+        _ptr(state1), _ptr(scale1), _ptr(tmax1), _ptr(state2), _ptr(scale2), _ptr(tmax2), n // blocks,
+        C.byref(hyper), C.byref(opts), _stream()))
+
+
+def adam_moment_stat(grad, state1, scale1, tmax1, state2, scale2, tmax2, hyper):
+    """Sums of |exp_avg| / denom per 128 elements for the step about to be taken (utils/quant.py:1107-1111)."""
+    _chk(grad, "grad"); _chk(state1, "state1", torch.uint8); _chk(state2, "state2", torch.uint8)
+    n = grad.numel()
+    out = torch.empty(n // 128, dtype=torch.float32, device=grad.device)
+    L.check("lq_adam_moment_stat", L.lib.lq_adam_moment_stat(
+        _ptr(grad), _dt(grad), n, _ptr(state1), _ptr(scale1), _ptr(tmax1), _ptr(state2), _ptr(scale2), _ptr(tmax2),
+        n // scale1.numel(), C.byref(hyper), _ptr(out), _stream()))
+    return out
+
+
 class DenseAdamTable:
     """Device-resident table of small dense bf16 parameters for `adam_dense_multi` (rebuilt only when an address
     changes: parameter data, arena gradient views and in-place states keep theirs from step to step)."""
@@ -354,3 +379,73 @@ def gemm_a8w8(x8, w8, row_scale=None, col_scale=None, alpha=1.0, bias=None, want
     L.call("lq_gemm_a8w8", _ptr(x8), _ptr(w8), _ptr(row_scale), _ptr(col_scale), float(alpha), _ptr(bias), _ptr(y), _ptr(acc),
            M, N, K, _ptr(ws), nb, _stream())
     return (y, acc) if want_acc else y
+
+
+# ---- decode-side operations of a Llama-architecture layer ------------------------------------------
+def add_rmsnorm(h, delta, gamma, eps, out=None, hf_rounding=True):
+    """h [M, K] += delta (in place, when given); returns RMSNorm(h) * gamma (PTQ/quant/triton_norm.py:7-39)."""
+    _chk(h, "h", torch.bfloat16); _chk(gamma, "gamma", torch.bfloat16)
+    if delta is not None:
+        _chk(delta, "delta", torch.bfloat16)
+        assert delta.shape == h.shape
+    M, K = h.shape
+    y = out if out is not None else torch.empty_like(h)
+    L.call("lq_add_rmsnorm", _ptr(h), _ptr(delta), _ptr(gamma), float(eps), _ptr(y), M, K, int(hf_rounding), _stream())
+    return y
+
+
+def rope_kv_store(qkv, positions, inv_freq, k_cache, v_cache, Hq, Hkv, hd, tokens_per_seq=1, hf_rounding=True):
+    """RoPE on the q and k heads of qkv [M, (Hq + 2 Hkv) hd] (q in place); rotated k and v go into the caches
+    [batch, Hkv, max_len, hd] at positions[m] (PTQ/quant/fused_attn.py:8-58)."""
+    _chk(qkv, "qkv", torch.bfloat16); _chk(positions, "positions", torch.int64); _chk(inv_freq, "inv_freq", torch.float32)
+    _chk(k_cache, "k_cache", torch.bfloat16); _chk(v_cache, "v_cache", torch.bfloat16)
+    M = qkv.shape[0]
+    assert qkv.shape[1] == (Hq + 2 * Hkv) * hd and positions.numel() == M and inv_freq.numel() == hd // 2
+    assert k_cache.shape == v_cache.shape and k_cache.shape[1] == Hkv and k_cache.shape[3] == hd
+    L.call("lq_rope_kv_store", _ptr(qkv), _ptr(positions), _ptr(inv_freq), _ptr(k_cache), _ptr(v_cache), M, tokens_per_seq,
+           Hq, Hkv, hd, k_cache.shape[2], int(hf_rounding), _stream())
+
+
+_attn_ws: dict = {}
+
+
+def decode_attention(qkv, positions, k_cache, v_cache, Hq, Hkv, hd, scale=None, out=None):
+    """One query token per sequence against the cache: q = first Hq*hd columns of qkv [B, ...]; keys 0..positions[b]."""
+    _chk(qkv, "qkv", torch.bfloat16); _chk(positions, "positions", torch.int64)
+    B, max_len = qkv.shape[0], k_cache.shape[2]
+    y = out if out is not None else torch.empty((B, Hq * hd), dtype=torch.bfloat16, device=qkv.device)
+    need = int(L.lib.lq_decode_attention_workspace_bytes(B, Hq, hd, max_len))
+    key = (qkv.device.index, torch.cuda.current_stream().cuda_stream)
+    ws = _attn_ws.get(key)
+    if ws is None or ws.numel() < need:
+        ws = _attn_ws[key] = torch.zeros(max(need, 1), dtype=torch.uint8, device=qkv.device)   # ticket counters start at zero
+    L.call("lq_decode_attention", _ptr(qkv), qkv.stride(0), _ptr(k_cache), _ptr(v_cache), _ptr(positions), _ptr(y), B, Hq, Hkv,
+           hd, max_len, float(scale if scale is not None else hd ** -0.5), _ptr(ws), ws.numel(), _stream())
+    return y
+
+
+def silu_mul(gate_up, out=None, hf_rounding=True):
+    """silu(gate_up[:, :I]) * gate_up[:, I:] (PTQ/quant/fused_mlp.py:84-168)."""
+    _chk(gate_up, "gate_up", torch.bfloat16)
+    M, I2 = gate_up.shape
+    y = out if out is not None else torch.empty((M, I2 // 2), dtype=torch.bfloat16, device=gate_up.device)
+    L.call("lq_silu_mul", _ptr(gate_up), _ptr(y), M, I2 // 2, int(hf_rounding), _stream())
+    return y
+
+
+# ---- 8-bit gradient accumulator (GradientQTensor, utils/quant.py:846-921) ---------------------------
+def gradq_accumulate(fdata, qdata, scale, first, opts):
+    """set_value (first) / add_ of the 8-bit stochastic gradient accumulator, in place on qdata [rows, cols] int8 and
+    scale [rows] (fdata's dtype)."""
+    _chk(fdata, "fdata"); _chk(qdata, "qdata", torch.int8); _chk(scale, "scale", fdata.dtype)
+    rows, cols = fdata.shape
+    assert qdata.shape == fdata.shape and scale.numel() == rows
+    L.call("lq_gradq_accumulate", _ptr(fdata), _dt(fdata), rows, cols, _ptr(qdata), _ptr(scale), int(first), C.byref(opts), _stream())
+
+
+def gradq_dequant(qdata, scale, out=None):
+    _chk(qdata, "qdata", torch.int8); _chk(scale, "scale")
+    rows, cols = qdata.shape
+    y = out if out is not None else torch.empty((rows, cols), dtype=scale.dtype, device=qdata.device)
+    L.call("lq_gradq_dequant", _ptr(qdata), _ptr(scale), _dt(scale), rows, cols, _ptr(y), _stream())
+    return y

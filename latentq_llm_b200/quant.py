@@ -769,51 +769,58 @@ class ResidualTensor(object):
 
 
 class GradientQTensor(object):
-    """utils/quant.py:846-921: optional 8-bit stochastic gradient accumulator (torch ops, as in the reference)."""
+    """The optional 8-bit stochastic gradient accumulator (utils/quant.py:846-921): one scale per weight row fixed by
+    the first micro-batch (4 x its absmax / 127), every later micro-batch folded in as
+    `round((q * scale + g) / scale + noise)`.  Same interface as the reference's class; the arithmetic runs in one
+    kernel per call (`ops.gradq_accumulate`) with the library's counter-based Philox stream as the noise, keyed by
+    (`seed`, call counter), so replicas that feed the same gradients hold the same accumulator."""
 
-    def __init__(self, shape, bit=8):
+    def __init__(self, shape, bit=8, seed=0):
         self.acc_ite = 0
         self.bit = bit
-        self.qdata = 0
+        self.qdata = None
         self.scale = None
         self.qzero = None
         self.shape = shape
         self.fixscale = False
+        self.seed = seed
+        self.calls = 0
 
-    def find_param(self, data):
-        self.vmax = data.abs().amax(dim=1, keepdim=True) * 4
-        self.scale = torch.clamp(self.vmax, min=1e-5) / (2 ** (self.bit - 1) - 1)
-        self.scale = self.scale.to(data.dtype)
+    def _opts(self):
+        self.calls += 1
+        return ops.make_opts(dither=ops.DITHER_PHILOX, seed=self.seed, step=self.calls, param_id=0x67726164)
 
-    def quant(self, fdata):
-        noise = fdata.new(fdata.shape).uniform_(-0.5, 0.5)
-        qdata = torch.round(fdata / self.scale + noise)
-        self.qdata = torch.clamp(qdata, -2 ** (self.bit - 1), 2 ** (self.bit - 1) - 1).to(torch.int8)
-
-    def dequant(self):
-        return self.qdata.to(self.fdtype) * self.scale
+    def _kernel(self, fdata, first):
+        f2 = fdata.reshape(fdata.shape[0], -1)
+        if not f2.is_contiguous():
+            f2 = f2.contiguous()
+        if first or self.qdata is None or self.qdata.shape != f2.shape or self.scale.dtype != f2.dtype:
+            self.qdata = torch.empty(f2.shape, dtype=torch.int8, device=f2.device)
+            self.scale = torch.empty(f2.shape[0], dtype=f2.dtype, device=f2.device)
+        ops.gradq_accumulate(f2, self.qdata, self.scale, first, self._opts())
 
     def set_value(self, fdata):
         if self.bit > 8:
             self.qdata = fdata
             return
-        if not (self.fixscale and self.scale is None):
-            self.find_param(fdata)
-        self.quant(fdata)
+        self._kernel(fdata, True)
         self.fdtype = fdata.dtype
         self.acc_ite = 1
 
     def zero(self):
         self.acc_ite = 0
-        self.qdata = None
+        if self.bit > 8:
+            self.qdata = None
 
     def add_(self, fdata):
         if self.bit > 8:
             self.qdata += fdata
         else:
-            odata = self.dequant()
             self.acc_ite += 1
-            self.quant(odata + fdata)
+            self._kernel(fdata, False)
+
+    def dequant(self):
+        return ops.gradq_dequant(self.qdata, self.scale).view(*self.shape)
 
     def get_value(self):
         return self.qdata if self.bit > 8 else self.dequant()
@@ -822,8 +829,9 @@ class GradientQTensor(object):
         return f"GradientQTensor bitwidth {self.bit} !"
 
     def to(self, device):
-        self.qdata = self.qdata.to(device)
-        if self.bit <= 8:
+        if self.qdata is not None:
+            self.qdata = self.qdata.to(device)
+        if self.bit <= 8 and self.scale is not None:
             self.scale = self.scale.to(device)
         return self
 
@@ -855,6 +863,7 @@ class MyAdam(torch.optim.Adam):
         self.fused = bool(fused) and not cpu
         self.before_param = None                 # optional callable(p), run before a parameter with a gradient is stepped
         self.last_to_first = False               # walk each group's parameters from the last to the first (see step)
+        self.op_by_op_steps = 0                  # parameter steps that took `update_step` instead of a fused kernel
         self._dense_tables = {}
 
     def add_param_group(self, param_group):
@@ -902,6 +911,7 @@ class MyAdam(torch.optim.Adam):
                 elif self.fused and self._fused_dense_ok(group, p, state):
                     dense.setdefault((gindex, state["step"]), []).append(p)
                 else:
+                    self.op_by_op_steps += 1
                     self.update_step(group, p, gindex, pindex)
         for (gindex, _), plist in dense.items():
             self._fused_dense_step(gindex, self.param_groups[gindex], plist)
@@ -913,32 +923,59 @@ class MyAdam(torch.optim.Adam):
         return group["lr"] * math.sqrt(1 - beta2 ** step) / (1 - beta1 ** step)
 
     def _fused_quant_ok(self, group, p, state):
-        if not (isinstance(p, QuantTensor) and p.wbit == 4 and isinstance(p.residual, ResidualTensor)):
+        if not (isinstance(p, QuantTensor) and p.wbit in (4, 8) and isinstance(p.residual, ResidualTensor)):
             return False
         g = p.grad
+        if isinstance(g, GradientQTensor):
+            return g.bit <= 8 and g.qdata is not None and g.qdata.is_cuda
         if not (torch.is_tensor(g) and g.is_cuda and g.is_contiguous() and g.dtype in (torch.bfloat16, torch.float32)):
             return False
         s1 = state["state1"]
-        if s1.dtype != torch.uint8 or not s1.is_cuda or group["weight_decay"] != 0 or p.qparam[0].dtype != g.dtype:
-            return False
-        nxt = state["step"] + 1
-        return not (nxt > 250 and nxt % self.mu_updata_f == self.mu_updata_f - 1)
+        qs = p.qparam[0] if p.wbit == 4 else p.qparam
+        return bool(s1.dtype == torch.uint8 and s1.is_cuda and group["weight_decay"] == 0 and qs.dtype == g.dtype
+                    and (p.wbit == 4 or p.shape[1] % 8 == 0))
 
     def _fused_quant_step(self, group, p, state):
         state["step"] += 1
+        step = state["step"]
         beta1, beta2 = group["betas"]
-        hyper = ops.make_adam_hyper(beta1, beta2, group["eps"], self._step_size(group, state["step"]))
+        step_size = self._step_size(group, step)
+        hyper = ops.make_adam_hyper(beta1, beta2, group["eps"], step_size)
         res, g = p.residual, p.grad
-        flat = getattr(p, "_flat_qparams", None)
-        if flat is None or flat[2] is not p.qparam[0]:
-            flat = p._flat_qparams = (p.qparam[0].contiguous().reshape(-1), p.qparam[1].contiguous().reshape(-1), p.qparam[0])
+        if isinstance(g, GradientQTensor):
+            g = g.get_value()                    # utils/quant.py:1064-1065
+            if g.dtype != (p.qparam[0] if p.wbit == 4 else p.qparam).dtype:
+                state["step"] -= 1
+                return self.update_step(group, p, None, None)
+        st = (state["state1"], state["qmap1"], state["absmax1"], state["state2"], state["qmap2"], state["absmax2"])
+        # The step that also refreshes the residual-curve level (utils/quant.py:1107-1111): one extra read-only pass leaves
+        # the sums of |exp_avg| / denom per 128 elements; the rest is a handful of operations on one value per group / row.
+        # It runs BEFORE the step, like the reference's update_mu, so this step already encodes with the new level.
+        if step > 250 and step % self.mu_updata_f == self.mu_updata_f - 1:
+            if p.numel() % 128 != 0 or res.qshape[1] % 128 != 0:
+                raise RuntimeError("residual-curve refresh needs statistics rows that are multiples of 128 elements")
+            stat = ops.adam_moment_stat(g, *st, hyper)
+            per = res.qshape[1]                                    # elements per statistics row: 128 (A16W4) or the row length
+            sums = stat.view(-1, 1) if per == 128 else stat.view(res.qshape[0], per // 128).sum(dim=1, keepdim=True)
+            optmizer_std = (sums / per).to(g.dtype) * step_size    # torch.mean(...) in the chain dtype, then * step_size
+            res.update_mu(optmizer_std)
         o = ops.make_opts(codec=ops.CODEC_THREEFOLD, dither=ops.DITHER_HASH, math_dtype=g.dtype, res_round_bf16=True,
                           has_residual=not res.init, mu_enc=res.mu, mu_dec=res.lock_mu)
-        ops.adam_a16w4_step(p.data, res.residual_int.view(-1), g, flat[0], flat[1],
-                            state["state1"], state["qmap1"], state["absmax1"],
-                            state["state2"], state["qmap2"], state["absmax2"], hyper, o, GROUPSIZE)
-        res._after_set_value(flat[0].view(-1, 1))
-        p.grad = None
+        if p.wbit == 4:
+            flat = getattr(p, "_flat_qparams", None)
+            if flat is None or flat[2] is not p.qparam[0]:
+                flat = p._flat_qparams = (p.qparam[0].contiguous().reshape(-1), p.qparam[1].contiguous().reshape(-1), p.qparam[0])
+            ops.adam_a16w4_step(p.data, res.residual_int.view(-1), g, flat[0], flat[1], *st, hyper, o, GROUPSIZE)
+            scale_col = flat[0].view(-1, 1)
+        else:
+            qs = p.qparam.contiguous().reshape(-1)
+            ops.adam_a8w8_step(p.data.view(p.shape[0], -1), res.residual_int.view(-1), g.view(p.shape[0], -1), qs, *st, hyper, o)
+            scale_col = qs.view(-1, 1)
+        res._after_set_value(scale_col)
+        if isinstance(p.grad, GradientQTensor):
+            p.grad.zero()
+        else:
+            p.grad = None
 
     @staticmethod
     def _fused_dense_ok(group, p, state):

@@ -449,3 +449,28 @@ ORC_API void orc_adam_chain_cpu(float* p, const float* g, float* m, float* d, in
         m[i] = ea; d[i] = den;
     }
 }
+
+/* ---------- GradientQTensor (utils/quant.py:846-921): 8-bit stochastic gradient accumulator.  first: set_value
+ * (find_param, then quant); otherwise add_ (dequant + fdata, then quant with the kept scale).  Every tensor op rounds
+ * in the tensor dtype (math_bf16); noise is the uniform_(-0.5, 0.5) draw in that dtype. */
+ORC_API void orc_gradq_accumulate(const float* f, int64_t rows, int64_t cols, int8_t* q, float* scale, int first,
+                                  const float* noise, int math_bf16) {
+    int bf = math_bf16;
+    for (int64_t r = 0; r < rows; ++r) {
+        if (first) {
+            float am = 0.0f;
+            for (int64_t c = 0; c < cols; ++c) am = fmaxf(am, fabsf(f[r * cols + c]));
+            float vmax = rnd(am * 4.0f, bf);
+            scale[r] = rnd(fmaxf(vmax, rnd(1e-5f, bf)) / 127.0f, bf);
+        }
+        float s = scale[r];
+        for (int64_t c = 0; c < cols; ++c) {
+            int64_t i = r * cols + c;
+            float x = f[i];
+            if (!first) x = rnd(rnd((float)q[i] * s, bf) + x, bf);
+            float t = rnd(rnd(x / s, bf) + rnd(noise[i], bf), bf);
+            t = fminf(fmaxf(rintf(t), -128.0f), 127.0f);
+            q[i] = (int8_t)t;
+        }
+    }
+}

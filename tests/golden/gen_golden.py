@@ -272,6 +272,27 @@ def main(ref):
         out[f"pt_clampv_{tag}"] = f32(Xa.max().reshape(1))
         out[f"pt_alpha_{tag}"] = f32(seen["alpha"].reshape(1))
 
+    # --- GradientQTensor (utils/quant.py:846-921): set_value then two add_ calls, fp32 and bf16, seeded noise ----------
+    gq = slice_module(qpath, {"GradientQTensor"})
+    for tag, dt in (("f32", torch.float32), ("bf16", torch.bfloat16)):
+        acc = gq["GradientQTensor"]([24, 256], bit=8)
+        for it in range(3):
+            fd = (torch.randn(24, 256, generator=g) * (1e-3 if it else 2e-3)).to(dt)
+            if it == 0:
+                fd[3] = 0.0                                   # an all-zero row: the 1e-5 floor of the scale
+            seed = 900 + it
+            torch.manual_seed(seed)
+            if it == 0:
+                acc.set_value(fd.clone())
+            else:
+                acc.add_(fd.clone())
+            torch.manual_seed(seed)
+            out[f"gq_noise{it}_{tag}"] = f32(torch.empty(24, 256, dtype=dt).uniform_(-0.5, 0.5))
+            out[f"gq_f{it}_{tag}"] = f32(fd)
+            out[f"gq_q{it}_{tag}"] = acc.qdata.numpy().copy()
+        out[f"gq_scale_{tag}"] = f32(acc.scale.reshape(-1))
+        out[f"gq_value_{tag}"] = f32(acc.get_value())
+
     # --- a9-a11: the CUDA residual codecs, from the reference's own kernel text compiled for the CPU ------------
     # (oracle/build_ref.py: no GPU launch).  Built with and without FMA contraction; the fixtures are the FMA
     # build (nvcc's default), `rc_variants_agree` records whether the other build produced the same bytes.

@@ -53,7 +53,11 @@ def test_fused_quantized_step_is_bit_identical(N, K):
     assert ob.state[pb]["state1"].dtype == torch.uint8 and int(ob.state[pb]["state1"].max()) > 0
 
 
-def test_fused_step_moves_codes_and_falls_back_on_curve_update_steps():
+@pytest.mark.parametrize("gscale", [1e-2, 3e-4, 1e-5])       # different |m| / denom levels -> different curve levels
+def test_fused_step_through_a_curve_refresh_step(gscale):
+    """Steps on which the residual-curve level is refreshed (utils/quant.py:1107-1111) stay on the fused route: a
+    read-only statistics kernel runs first, the level it selects is the one the step encodes with — as in the op-by-op
+    route, whose codes, residual words, states and levels must come out identical."""
     from latentq_llm_b200 import quant as Q
     N, K = 512, 512
     la, lb = _quant_param(Q, N, K, seed=2), _quant_param(Q, N, K, seed=2)
@@ -69,14 +73,102 @@ def test_fused_step_moves_codes_and_falls_back_on_curve_update_steps():
     assert not torch.equal(start, pb.data)
     # jump both optimizers past the step where the residual curve level is refreshed (step > 250, step % f == f-1)
     oa.state[pa]["step"] = ob.state[pb]["step"] = 253
-    for t in range(3):                                          # steps 254, 255 (refresh: 255 % 4 == 3), 256
-        grad = (torch.randn(N, K, device="cuda", generator=g) * 1e-2).to(torch.bfloat16)
+    for t in range(7):                                          # steps 254 .. 260; refreshes at 255 and 259
+        grad = (torch.randn(N, K, device="cuda", generator=g) * gscale).to(torch.bfloat16)
         pa.grad, pb.grad = grad.clone(), grad.clone()
         oa.step(); ob.step()
-        assert torch.equal(pa.data.view(torch.uint8), pb.data.view(torch.uint8))
-        assert torch.equal(pa.residual.residual_int, pb.residual.residual_int)
-        assert pa.residual.mu == pb.residual.mu and pa.residual.lock_mu == pb.residual.lock_mu
+        assert pa.residual.mu == pb.residual.mu and pa.residual.lock_mu == pb.residual.lock_mu, t
+        assert torch.equal(pa.data.view(torch.uint8), pb.data.view(torch.uint8)), t
+        assert torch.equal(pa.residual.residual_int, pb.residual.residual_int), t
     _same_state(oa.state[pa], ob.state[pb])
+    assert ob.op_by_op_steps == 0 and oa.op_by_op_steps == 10
+
+
+def _a8w8_param(Q, N, K, seed):
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    layer = Q.QLinearA8W8(K, N, bias=False, lbit=4, gbit=16)
+    w = torch.randn(N, K, device="cuda", generator=g) * 0.02
+    qs = (w.abs().amax(dim=1, keepdim=True) / 127).to(torch.bfloat16)
+    layer.qscales.data = qs
+    w8 = torch.clamp(torch.round(w / qs.float()), -128, 127).to(torch.int8)
+    layer.weight.set_value(w8, layer.qscales)
+    layer.to("cuda")
+    return layer
+
+
+@pytest.mark.parametrize("N,K", [(192, 512), (64, 128), (256, 2048)])
+def test_fused_a8w8_step_is_bit_identical(N, K):
+    """`lq_adam_a8w8_step` (int8 latent weights, one scale per row) against the op-by-op route, including two steps
+    that refresh the curve level (statistics per weight row)."""
+    from latentq_llm_b200 import quant as Q
+    la, lb = _a8w8_param(Q, N, K, seed=7), _a8w8_param(Q, N, K, seed=7)
+    pa, pb = la.weight, lb.weight
+    oa = Q.MyAdam([{"params": [pa], "weight_decay": 0.0}], lr=1e-3, betas=(0.9, 0.95), obit=8, mu_updata_f=4, fused=False)
+    ob = Q.MyAdam([{"params": [pb], "weight_decay": 0.0}], lr=1e-3, betas=(0.9, 0.95), obit=8, mu_updata_f=4, fused=True)
+    g = torch.Generator(device="cuda").manual_seed(13)
+    for t in range(9):
+        if t == 4:
+            oa.state[pa]["step"] = ob.state[pb]["step"] = 253
+        grad = (torch.randn(N, K, device="cuda", generator=g) * 10.0 ** (-(t % 3) - 2)).to(torch.bfloat16)
+        pa.grad, pb.grad = grad.clone(), grad.clone()
+        oa.step(); ob.step()
+        assert torch.equal(pa.data, pb.data), f"codes differ at step {t}"
+        assert torch.equal(pa.residual.residual_int, pb.residual.residual_int), f"residual words differ at step {t}"
+        assert pa.residual.mu == pb.residual.mu and pa.residual.lock_mu == pb.residual.lock_mu
+        _same_state(oa.state[pa], ob.state[pb])
+    assert ob.op_by_op_steps == 0
+
+
+def test_gradient_accumulator_kernel_vs_reference_vectors(golden):
+    """GradientQTensor (utils/quant.py:846-921): set_value and two add_ calls with the noise the reference drew,
+    against what the reference's class produced (fp32 and bf16), then the Philox-noise route against the oracle."""
+    import numpy as np
+    import oracle as orc
+    from latentq_llm_b200 import ops
+    for tag, dt in (("f32", torch.float32), ("bf16", torch.bfloat16)):
+        q = torch.empty((24, 256), dtype=torch.int8, device="cuda")
+        sc = torch.empty(24, dtype=dt, device="cuda")
+        for it in range(3):
+            f = torch.from_numpy(golden[f"gq_f{it}_{tag}"]).cuda().to(dt)
+            noise = torch.from_numpy(golden[f"gq_noise{it}_{tag}"]).cuda()
+            ops.gradq_accumulate(f, q, sc, it == 0, ops.make_opts(dither=ops.DITHER_EXPLICIT, dither_buf=noise))
+            assert np.array_equal(q.cpu().numpy(), golden[f"gq_q{it}_{tag}"]), (tag, it)
+        assert np.array_equal(sc.float().cpu().numpy(), golden[f"gq_scale_{tag}"])
+        assert np.array_equal(ops.gradq_dequant(q, sc).float().cpu().numpy(), golden[f"gq_value_{tag}"])
+    # Philox noise: the library's stream, one block per 8 elements
+    rng = np.random.default_rng(3)
+    f = orc.bf16_round((rng.standard_normal((40, 1024)) * 1e-3).astype(np.float32))
+    q = torch.empty((40, 1024), dtype=torch.int8, device="cuda")
+    sc = torch.empty(40, dtype=torch.bfloat16, device="cuda")
+    ops.gradq_accumulate(torch.from_numpy(f).cuda().to(torch.bfloat16), q, sc, True,
+                         ops.make_opts(dither=ops.DITHER_PHILOX, seed=99, step=1, param_id=5))
+    want_q, want_s = orc.gradq_accumulate(f, orc.philox_dither(99, (1 << 32) | 5, 40 * 1024 // 8).reshape(40, 1024), math_bf16=True)
+    assert np.array_equal(q.cpu().numpy(), want_q) and np.array_equal(sc.float().cpu().numpy(), want_s)
+
+
+def test_gradient_accumulator_class_in_the_hook_route():
+    """QLinearA16W4 with gbit=8: the backward hook folds every micro-batch into the 8-bit accumulator, the optimizer
+    reads it back (utils/quant.py:398-411, 1064-1065) and stays on the fused route."""
+    from latentq_llm_b200 import quant as Q
+    N, K, M = 256, 512, 32
+    layer = _quant_param(Q, N, K, seed=3)
+    layer.weight.grad = Q.GradientQTensor([N, K], bit=8, seed=1)
+    layer.add_hook()
+    opt = Q.MyAdam([{"params": [layer.weight], "weight_decay": 0.0}], lr=1e-3, betas=(0.9, 0.95), obit=8)
+    g = torch.Generator(device="cuda").manual_seed(8)
+    before = layer.weight.data.clone()
+    dense = torch.zeros(N, K, device="cuda")
+    for mb in range(3):
+        x = torch.randn(M, K, device="cuda", generator=g).to(torch.bfloat16).requires_grad_(True)
+        y = layer(x)
+        y.backward(torch.ones_like(y) * 1e-2)
+        dense += (torch.ones(M, N, device="cuda") * 1e-2).t() @ x.detach().float()
+    acc = layer.weight.grad
+    assert isinstance(acc, Q.GradientQTensor) and acc.acc_ite == 3 and acc.qdata.dtype == torch.int8
+    got = acc.get_value().float()
+    assert float((got - dense).abs().max()) <= 3.0 * float(acc.scale.float().max())     # within a few quantization steps
+    opt.step()
+    assert opt.op_by_op_steps == 0 and acc.acc_ite == 0 and not torch.equal(before, layer.weight.data)
 
 
 def test_fused_dense_multi_is_bit_identical():

@@ -95,6 +95,26 @@ def test_a16w4_llama_shapes(ops, a_operand, M, K, N):
     assert torch.equal(y2, y * 2)
 
 
+@pytest.mark.parametrize("M,N,K", [(24, 512, 1024), (64, 320, 2048), (128, 11008, 4096), (200, 4096, 4096), (512, 4096, 11008)])
+def test_a16w4_fwd_balanced_plan_vs_oracle(ops, a_operand, monkeypatch, M, N, K):
+    """The forward kernel with its (tile, k-block) units dealt out evenly over the SMs: CTAs that start inside a tile
+    hand their partial sums to the tile's owner through the workspace.  Same tolerance as the tile-cyclic plan, and the
+    same bits on every run (the hand-over order is fixed)."""
+    monkeypatch.setenv("LQ_GEMM_BALANCE", "1")
+    ops._ws_need.clear()
+    codes, sb, zb = make_w4_layer(ops, N, K, seed=M + N)
+    g = torch.Generator(device="cuda").manual_seed(9)
+    x = torch.randn(M, K, device="cuda", generator=g).to(torch.bfloat16)
+    bias = (torch.randn(N, device="cuda", generator=g) * 0.1).to(torch.bfloat16)
+    y = ops.gemm_a16w4_fwd(x, codes, sb, zb, bias, N, K)
+    W = ops.a16w4_dequant(codes, sb, zb, (N, K), torch.bfloat16)
+    ref = (x.float() @ W.float().t()).to(torch.bfloat16).float() + bias.float()
+    e_max, e_fro = rel_err(y, ref)
+    assert e_max < RTOL and e_fro < RTOL, (e_max, e_fro)
+    assert torch.equal(y, ops.gemm_a16w4_fwd(x, codes, sb, zb, bias, N, K))
+    ops._ws_need.clear()
+
+
 @pytest.mark.parametrize("M,N,K,group", [(300, 384, 1024, 128), (4096, 4096, 4096, 128), (77, 256, 512, 64), (512, 512, 512, 32),
                                          (1000, 2048, 2048, 256)])
 def test_a16w4_tmem_and_smem_operand_paths_agree_bitwise(ops, monkeypatch, M, N, K, group):

@@ -190,3 +190,15 @@ def test_adam_steps_golden(golden):
         assert np.array_equal(st2, g[f"adam_state2_{step}"].ravel())
         for a, k in ((sc1, "qmap1"), (tm1, "absmax1"), (sc2, "qmap2"), (tm2, "absmax2")):
             assert np.array_equal(a, g[f"adam_{k}_{step}"])
+
+
+# ---- GradientQTensor (utils/quant.py:846-921) as the reference's class executed it on the CPU ----
+def test_gradient_accumulator_golden(golden):
+    for tag, bf in (("f32", False), ("bf16", True)):
+        q, sc = orc.gradq_accumulate(golden[f"gq_f0_{tag}"], golden[f"gq_noise0_{tag}"], math_bf16=bf)
+        assert np.array_equal(q, golden[f"gq_q0_{tag}"]) and np.array_equal(sc, golden[f"gq_scale_{tag}"])
+        for it in (1, 2):
+            q, sc = orc.gradq_accumulate(golden[f"gq_f{it}_{tag}"], golden[f"gq_noise{it}_{tag}"], qdata=q, scale=sc, math_bf16=bf)
+            assert np.array_equal(q, golden[f"gq_q{it}_{tag}"])
+        val = q.astype(np.float32) * sc[:, None]
+        assert np.array_equal(orc.bf16_round(val) if bf else val, golden[f"gq_value_{tag}"])

@@ -4,8 +4,8 @@ Some users of this library cannot allocate device memory where they call it: the
 framework that owns the whole device heap, or in a serving loop where an allocation's device-wide
 synchronisation is not acceptable.  For them the split-K partial sums live in an array built into
 the library.  This test drives the entry point through the C ABI exactly as such a caller would
-(no workspace argument) on shapes whose plan really splits K — the tensor-core route (M > 16) and
-the decode route of group size 64 — twice in a row per route, the second call smaller than the
+(no workspace argument) on shapes whose plan really hands partial sums through the array — the
+tensor-core route (M > 16) and the decode route of group size 64 — twice in a row per route, the second call smaller than the
 first so that the first call's partial sums lie underneath it.  Each result is compared with the
 CPU oracle and with `lq_gemm_a16w4_fwd`; the array itself is read back to show that the launch
 wrote its partial sums there.
@@ -50,9 +50,15 @@ def _call_static(lib, x, codes, s, z, bias, M, N, K, group):
     return got
 
 
-# (group, first M, second M): the tensor-core kernel with 4 K-splits, and the decode kernel of group size 64
-@pytest.mark.parametrize("group,Ms", [(128, (64, 24)), (64, (16, 5))])
-def test_static_scratch_forward_twice_against_oracle(group, Ms):
+# (group, (first M, second M), balanced plan?, where the partial sums of output row 0, columns 0..63 land in the array):
+#  - group 128, M > 16: the tensor-core kernel with four K-splits, partial sums laid out [split][token][column]
+#  - the same in the kernel's balanced mode: each 128-column tile is shared by four CTAs, the second of which (CTA 1)
+#    writes its sums for k = 256..511 into slot 1, laid out [token][weight row] (64 x 128 floats)
+#  - group 64, M <= 16: the decode kernel with four K-splits, partial sums laid out [split][token][column]
+@pytest.mark.parametrize("group,Ms,balanced,peek_at", [(128, (64, 24), False, 0), (128, (64, 24), True, 64 * 128), (64, (16, 5), False, 0)])
+def test_static_scratch_forward_twice_against_oracle(group, Ms, balanced, peek_at, monkeypatch):
+    if balanced:
+        monkeypatch.setenv("LQ_GEMM_BALANCE", "1")
     from latentq_llm_b200 import _lib, ops
     lib = _lib.lib
     N, K = 512, 1024
@@ -70,12 +76,13 @@ def test_static_scratch_forward_twice_against_oracle(group, Ms):
         ref = orc.gemm_a16w4(x_h, codes_h, s_h, z_h, N, K, group=group, bias=bias_h)
         err = np.abs(got.float().cpu().numpy().astype(np.float64) - ref).max() / np.abs(ref).max()
         assert err <= RTOL, (group, call, err)
+        ops._ws_need.clear()                               # (the workspace size is cached per shape; the plan just changed)
         want = ops.gemm_a16w4_fwd(x, codes, s, z, bias, N, K, group=group)
         assert torch.equal(got, want), "static-scratch and workspace variants run the same kernels on the same plan"
-        # the launch wrote fp32 partial sums into the built-in array: split 0 of output (0, 0..63) differs from what
-        # the previous call left there, is finite, and is only PART of the result (K really was split)
+        # the launch wrote fp32 partial sums into the built-in array: one K-slice of output (0, 0..63) differs from
+        # what the previous call left there, is finite, and is only PART of the result (K really was split)
         part = np.empty(64, np.float32)
-        assert lib.lq_gemm_a16w4_fwd_static_peek(part.ctypes.data_as(C.c_void_p), 0, 64) == 0
+        assert lib.lq_gemm_a16w4_fwd_static_peek(part.ctypes.data_as(C.c_void_p), peek_at, 64) == 0
         assert np.isfinite(part).all() and not np.array_equal(part, poison)
         full = ref[0, :64] - bias_h[:64]
         assert np.abs(part - full).max() > 0.05 * np.abs(full).max()

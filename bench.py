@@ -54,6 +54,22 @@ def peaks():
     return {"hbm_gbs": 6650.0, "bf16": 1590.0, "bf16_sustained": 1400.0, "src": "fallback"}
 
 
+def roofline_entry(per_gpu_tflops, pk, clocks):
+    """Tensor roofline of the headline kernel.  The denominator is the burst cuBLAS figure when the SM clock sampled
+    during the timed region stayed near its maximum (the conditions the burst figure was taken under), else the
+    sustained one; both fractions are given."""
+    sm, mx = (clocks or {}).get("sm_mhz"), (clocks or {}).get("sm_max_mhz")
+    burst = bool(sm and mx and sm >= 0.9 * mx)
+    peak = pk["bf16"] if burst else pk["bf16_sustained"]
+    return {"bound": "tensor", "achieved": round(per_gpu_tflops, 2), "peak": peak, "unit": "TFLOP/s",
+            "frac": round(per_gpu_tflops / peak, 4), "frac_of_burst": round(per_gpu_tflops / pk["bf16"], 4),
+            "frac_of_sustained": round(per_gpu_tflops / pk["bf16_sustained"], 4),
+            "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH, "traffic_note": NCU_TRAFFIC_NOTE,
+            "peak_source": pk["src"] + (" (burst bf16 cuBLAS figure: SM clock during the timed region near its maximum)" if burst else
+                                        " (sustained bf16 cuBLAS figure: SM clock during the timed region well below its maximum)"),
+            "kernel": "k_gemm<A16W4 fwd/dgrad, 256 tokens>", "algorithmic": "2*M*N*K flops per launch"}
+
+
 class ClockSampler:
     """nvidia-smi clock / throttle-reason samples taken while the timed region runs."""
     Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
@@ -143,11 +159,29 @@ def extra_measurements(torch, ops, pk, only=None, numel=1 << 30):
     `only` restricts to one family ("requant", "a8w8", "decode") for profiling runs."""
     out = {}
 
-    def tm(fn, reps=5, warm=2):
+    def tm(fn, reps=5, warm=2, graph=False):
+        """Mean device time of one call in ms.  graph=True: `reps` calls are captured into one CUDA graph and the graph
+        is replayed (best of 3), so that host time between short launches (Python, output allocation) is not in the
+        figure; falls back to eager timing if the call cannot be captured."""
         for _ in range(warm):
             fn()
         torch.cuda.synchronize()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        if graph:
+            try:
+                gr = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(gr):
+                    for _ in range(reps):
+                        fn()
+                gr.replay(); torch.cuda.synchronize()
+                best = float("inf")
+                for _ in range(3):
+                    e0.record(); gr.replay(); e1.record(); torch.cuda.synchronize()
+                    best = min(best, e0.elapsed_time(e1) / reps)
+                del gr
+                return best
+            except Exception:
+                torch.cuda.synchronize()
         e0.record()
         for _ in range(reps):
             fn()
@@ -245,7 +279,7 @@ def _sweep_part(torch, ops, pk, out, tm, g):
 def _stream_part(torch, ops, pk, out, tm, g, numel=1 << 28):
     """The other HBM-streaming entry points of the path, GB/s over their algorithmic bytes (inputs + outputs)."""
     def rec(name, nbytes, fn):
-        ms = tm(fn)
+        ms = tm(fn, reps=20, warm=2, graph=True)          # 20 calls per graph replay: device time only
         out["stream_" + name] = {"GB/s": round(nbytes / ms / 1e6, 1), "frac_hbm": round(nbytes / ms / 1e6 / pk["hbm_gbs"], 3), "ms": round(ms, 3)}
     n = numel
     w = (torch.randn(n, device="cuda", generator=g, dtype=torch.float32) * 0.02).to(torch.bfloat16)
@@ -268,17 +302,50 @@ def _stream_part(torch, ops, pk, out, tm, g, numel=1 << 28):
     del w, xa
 
 
+def mma_peaks(torch):
+    """Measured tensor-core ceilings from the library's tcgen05.mma issue-rate microbenchmark (one CTA per SM, operands
+    resident in shared memory / tensor memory, ~50 ms per run): int8 TOP/s and bf16 TFLOP/s."""
+    import ctypes
+    from latentq_llm_b200 import _lib
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    res = {}
+    for name, kind, ta, kk in (("int8_tops_measured", _lib.GEMM_A8W8, 0, 32), ("bf16_tflops_mma_smem_a", 0, 0, 16),
+                               ("bf16_tflops_mma_tmem_a", 0, 1, 16)):
+        n_mma = 1 << 19
+        _lib.lib.lq_mma_issue_rate(kind, ta, 256, 1, 4096, sms, None, None)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        rc = _lib.lib.lq_mma_issue_rate(kind, ta, 256, 1, n_mma, sms, None, None)
+        e1.record(); torch.cuda.synchronize()
+        assert rc == 0
+        res[name] = round(2.0 * 128 * 256 * kk * n_mma * sms / (e0.elapsed_time(e1) * 1e-3) / 1e12, 1)
+    res["note"] = "128x256 MMAs, one accumulator, all SMs, about 50 ms per figure"
+    return res
+
+
 def _a8w8_part(torch, ops, out, tm, g):
-    # int8 GEMM, OPT-1.3B shapes, M = 32x512 tokens
-    tot_ops, tot_ms = 0.0, 0.0
-    for (k, n) in [(2048, 2048), (2048, 8192), (8192, 2048)]:
-        m = 16384
-        x8 = torch.randint(-128, 128, (m, k), device="cuda", generator=g, dtype=torch.int8)
-        w8 = torch.randint(-128, 128, (n, k), device="cuda", generator=g, dtype=torch.int8)
-        rs = torch.rand(m, device="cuda", generator=g); cs = torch.rand(n, device="cuda", generator=g)
-        ms = tm(lambda: ops.gemm_a8w8(x8, w8, rs, cs, 1.0, None))
-        tot_ops += 2.0 * m * n * k; tot_ms += ms
-    out["a8w8_opt_m16384"] = {"TOP/s": round(tot_ops / tot_ms / 1e9, 1), "ms": round(tot_ms, 3)}
+    # int8 GEMM on the OPT-1.3B shapes at M = 4x512 and 32x512 tokens, the whole A8W8 forward: per-token activation
+    # quantizer, then the GEMM with per-token and per-channel scales and bias in its epilogue (bf16 out).  Activations
+    # ~N(0,1) with 1 % of the channels scaled x20.  The denominator is the measured int8 issue rate.
+    pkm = mma_peaks(torch)
+    out["tensor_peaks_mma_probe"] = pkm
+    for m in (2048, 16384):
+        tot_ops, tot_ms, tot_q = 0.0, 0.0, 0.0
+        for (k, n) in [(2048, 2048), (2048, 8192), (8192, 2048)]:
+            x = torch.randn(m, k, device="cuda", generator=g)
+            x[:, torch.randperm(k, device="cuda", generator=g)[:max(1, k // 100)]] *= 20.0
+            x = x.to(torch.bfloat16)
+            w8 = torch.randint(-128, 128, (n, k), device="cuda", generator=g, dtype=torch.int8)
+            cs = torch.rand(n, device="cuda", generator=g)
+            bias = torch.randn(n, device="cuda", generator=g).to(torch.bfloat16)
+            x8, rs = ops.act_quant_per_token(x)
+            ms = tm(lambda: ops.gemm_a8w8(x8, w8, rs, cs, 1.0, bias), reps=10, warm=3, graph=True)
+            tot_q += tm(lambda: ops.act_quant_per_token(x), reps=10, warm=3, graph=True)
+            tot_ops += 2.0 * m * n * k; tot_ms += ms
+        tops = tot_ops / tot_ms / 1e9
+        out[f"a8w8_opt_m{m}"] = {"TOP/s": round(tops, 1), "ms": round(tot_ms, 3), "frac_int8_measured": round(tops / pkm["int8_tops_measured"], 3),
+                                 "act_quant_ms": round(tot_q, 3), "TOP/s_with_act_quant": round(tot_ops / (tot_ms + tot_q) / 1e9, 1)}
 
 
 def _decode_part(torch, ops, pk, out, tm):
@@ -286,7 +353,7 @@ def _decode_part(torch, ops, pk, out, tm):
     # One pass over the four layers is captured in a CUDA graph and replayed, as a decode loop would do: at these
     # sizes a launch from Python costs more than the kernel runs.
     layers = build_layers(torch, ops)
-    for m in (1, 8, 16, 64, 128, 512):
+    for m in (1, 8, 16, 64, 128, 512, 4096):
         xs = [L["x"][:m].contiguous() for L in layers]
         ys = [torch.empty(m, L["N"], device="cuda", dtype=torch.bfloat16) for L in layers]
 
@@ -301,12 +368,29 @@ def _decode_part(torch, ops, pk, out, tm):
         ms_tot = tm(graph.replay, reps=20, warm=3)
         bytes_tot = sum(L["N"] * L["K"] / 2 + 4.0 * L["N"] * L["K"] / GROUP + 2.0 * m * (L["K"] + L["N"]) for L in layers)
         fl = sum(2.0 * m * L["N"] * L["K"] for L in layers)
+        roof_ms = max(fl / (pk["bf16"] * 1e9), bytes_tot / (pk["hbm_gbs"] * 1e6))
         out[f"a16w4_fwd_m{m}"] = {"TFLOP/s": round(fl / ms_tot / 1e9, 2), "GB/s": round(bytes_tot / ms_tot / 1e6, 1),
                                   "frac_hbm": round(bytes_tot / ms_tot / 1e6 / pk["hbm_gbs"], 3), "ms": round(ms_tot, 4),
+                                  "frac_roofline": round(roof_ms / ms_tot, 3),
                                   "timing": "CUDA graph replay of the 4 layers"}
+        if m >= 16:                                       # grad-input dx = dy·deq(W) over the same layers
+            dys = [L["dy"][:m].contiguous() for L in layers]
+            dxs = [torch.empty(m, L["K"], device="cuda", dtype=torch.bfloat16) for L in layers]
+
+            def one_pass_dgrad():
+                for L, dy, dx in zip(layers, dys, dxs):
+                    ops.gemm_a16w4_dgrad(dy, L["codes"], L["s"], L["z"], L["N"], L["K"], out=dx)
+
+            one_pass_dgrad(); torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                one_pass_dgrad()
+            ms_d = tm(graph.replay, reps=20, warm=3)
+            out[f"a16w4_dgrad_m{m}"] = {"TFLOP/s": round(fl / ms_d / 1e9, 2), "ms": round(ms_d, 4),
+                                        "frac_roofline": round(roof_ms / ms_d, 3), "timing": "CUDA graph replay of the 4 layers"}
 
 
-def finetune_measurement(torch, arch="opt-1.3b", steps=2, warmup=1, micro_batch=4, seq=512, grad_accum=8, cuda_graph=True,
+def finetune_measurement(torch, arch="opt-1.3b", steps=10, warmup=2, micro_batch=4, seq=512, grad_accum=8, cuda_graph=True,
                          decode_batches=()):
     """Latent fine-tune step (the fine-tune configuration of the benchmark set): A16W4 int4 group-128 latent weights, seq 512, micro-batch 4,
     grad-accum 8 per rank, uniform random token ids, data-parallel over the ranks of this launch: the bf16
@@ -348,7 +432,24 @@ def finetune_measurement(torch, arch="opt-1.3b", steps=2, warmup=1, micro_batch=
         qp = groups[0]["params"]                       # every quantized weight: packed codes and residual words
         same = replicas_identical([p.data for p in qp] + [p.residual.residual_int for p in qp
                                                            if hasattr(getattr(p, "residual", None), "residual_int")])
+    # data-parallel efficiency measured in this run: the same step with the gradient exchange switched off (every rank
+    # steps on its own gradients; done last, the replicas diverge from here on) against the step with it
+    dp_eff, ms_local = None, None
+    if world > 1:
+        tuner.exchange = False
+        one_step()
+        dist.barrier(); torch.cuda.synchronize()
+        e0.record()
+        for _ in range(max(2, steps // 2)):
+            one_step()
+        e1.record(); torch.cuda.synchronize()
+        t = torch.tensor([e0.elapsed_time(e1) / max(2, steps // 2)], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_local = float(t)
+        dp_eff = round(ms_local / ms, 4)
     res = {"arch": arch, "tokens_per_s": round(tokens / ms * 1e3, 1), "ms_per_step": round(ms, 1), "world": world,
+           "steps_timed": steps, "warmup_steps": warmup, "dp_efficiency": dp_eff,
+           "ms_per_step_without_exchange": None if ms_local is None else round(ms_local, 1),
            "micro_batch": micro_batch, "seq": seq, "grad_accum": grad_accum, "loss_first": round(losses[0], 4),
            "loss_last": round(losses[-1], 4), "replica_codes_identical": same,
            "grad_arena_bytes": tuner.arena.flat.numel() * 2, "h2d_bytes_per_step": grad_accum * micro_batch * seq * 8,
@@ -383,41 +484,75 @@ def finetune_measurement(torch, arch="opt-1.3b", steps=2, warmup=1, micro_batch=
                 torch.cuda.synchronize(); t2 = time.perf_counter()
                 dec[f"batch{b}"]["graphed_tokens_per_s"] = round(b * 64 / max(1e-9, (t2 - t1) - (t1 - t0)), 1)
                 del gd
+                # the decode step as a chain of the library's own kernels (fused q|k|v and gate|up projections, RMSNorm,
+                # RoPE + KV-cache write, single-query attention, silu*up), one CUDA graph; timed over graph replays only
+                if ft.ARCHS[arch]["kind"] == "llama":
+                    from latentq_llm_b200.generate import FusedLlamaGreedyDecoder
+                    fd = FusedLlamaGreedyDecoder(model, batch=b, max_len=512 + 72)
+                    fd.generate(prompt, 4)
+                    torch.cuda.synchronize()
+                    fd.generate(prompt, 2)
+                    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    ev0.record()
+                    for _ in range(64):
+                        fd.graph.replay()
+                    ev1.record(); torch.cuda.synchronize()
+                    ms_tok = ev0.elapsed_time(ev1) / 64
+                    dec[f"batch{b}"]["fused_tokens_per_s"] = round(b / ms_tok * 1e3, 1)
+                    dec[f"batch{b}"]["fused_ms_per_step"] = round(ms_tok, 3)
+                    del fd
+                torch.cuda.empty_cache()
         res["greedy_decode"] = dec
         res["greedy_decode_note"] = ("512-token random prompts; hf_generate = the reference's route (eager loop, host-bound); "
-                                     "graphed = decode step captured as one CUDA graph on a static KV cache")
+                                     "graphed = decode step of the eager modules captured as one CUDA graph on a static KV cache; "
+                                     "fused = decode step as nine library kernels per layer, one CUDA graph")
     del tuner, opt, model
     torch.cuda.empty_cache()
     return res
 
 
-def cpu_baseline(sample_m=256, reps=2):
+_CPU_DATA: dict = {}
+
+
+def cpu_baseline(sample_m=512, reps=1):
     """The reference's CPU path for this workload (DeQfunc_4bit_g then input.mm(W.t()) / grad.mm(W), fp32,
-    utils/quant.py:116-121,136-140) restated with the oracle, on a bounded sample: the (4096,4096) shape at M=sample_m."""
+    utils/quant.py:116-121,136-140) restated with the oracle, on a bounded sample: all four shapes at M=sample_m
+    (the benchmark's M is 4096; the CPU path's rate does not depend on M beyond the weight dequantize)."""
     import numpy as np
     import torch
     import oracle as orc
-    k, n = LLAMA_SHAPES[0]
-    rng = np.random.default_rng(0)
     threads = os.cpu_count() or 1
     torch.set_num_threads(threads)
-    codes = rng.integers(-128, 128, n * k // 2, dtype=np.int8)
-    s = np.full(n * k // GROUP, 0.008, np.float32)
-    z = np.full(n * k // GROUP, 8.0, np.float32)
-    x = torch.from_numpy(rng.standard_normal((sample_m, k)).astype(np.float32))
-    dy = torch.from_numpy(rng.standard_normal((sample_m, n)).astype(np.float32))
-    best = float("inf")
-    for _ in range(reps + 1):
+    data = _CPU_DATA.get(sample_m)
+    if data is None:                                        # synthetic inputs, made once per process
+        rng = np.random.default_rng(0)
+        data = _CPU_DATA[sample_m] = []
+        for (k, n) in LLAMA_SHAPES:
+            data.append((k, n, rng.integers(-128, 128, n * k // 2, dtype=np.int8), np.full(n * k // GROUP, 0.008, np.float32),
+                         np.full(n * k // GROUP, 8.0, np.float32),
+                         torch.from_numpy(rng.standard_normal((sample_m, k)).astype(np.float32)),
+                         torch.from_numpy(rng.standard_normal((sample_m, n)).astype(np.float32))))
+    def deq(codes, s, z, n, k):
+        """python_decompress + DeQfunc_4bit_g (utils/quant.py:12-19, 66-72) as the reference runs them on CPU tensors."""
+        c = torch.from_numpy(codes)
+        q = torch.stack([(c >> 4) % 16, c % 16], dim=1).reshape(-1, GROUP).to(torch.float32)
+        return ((q - torch.from_numpy(z).view(-1, 1)) * torch.from_numpy(s).view(-1, 1)).view(n, k)
+
+    k0, n0, c0, s0, z0 = data[0][:5]                       # the torch restatement against the oracle's, once
+    assert np.array_equal(deq(c0[:4096], s0[:64], z0[:64], 2, 4096).numpy().ravel(), orc.a16w4_dequant(c0[:4096], s0[:64], z0[:64], GROUP))
+    best, chk = float("inf"), 0.0
+    for _ in range(reps):
         t0 = time.perf_counter()
-        w = torch.from_numpy(orc.a16w4_dequant(codes, s, z, GROUP)).view(n, k)
-        y = x.mm(w.t())
-        w = torch.from_numpy(orc.a16w4_dequant(codes, s, z, GROUP)).view(n, k)     # backward dequantizes again (:136)
-        dx = dy.mm(w)
+        for (k, n, codes, s, z, x, dy) in data:
+            y = x.mm(deq(codes, s, z, n, k).t())
+            dx = dy.mm(deq(codes, s, z, n, k))             # backward dequantizes again (:136)
+            chk += float(y[0, 0] + dx[0, 0])
         best = min(best, time.perf_counter() - t0)
-    fl = 2 * 2.0 * sample_m * n * k
+    fl = step_flops(sample_m)
     return {"value": round(fl / best / 1e12, 4), "unit": UNIT, "cores": threads, "kind": "port",
-            "sample": f"(K,N)=({k},{n}), M={sample_m}, fwd+grad-input incl. weight dequantize, best of {reps + 1}",
-            "seconds": round(best, 3)}, float(y.sum() + dx.sum())
+            "sample": f"all four (K,N) shapes at M={sample_m} (the benchmark's M is {M_TOKENS}), fwd+grad-input incl. weight "
+                      f"dequantize, best of {reps}",
+            "seconds": round(best, 3)}, chk
 
 
 def run_reference(args):
@@ -429,12 +564,12 @@ def run_reference(args):
     t_all = time.perf_counter()
     vals = []
     for _ in range(args.warmup):
-        cpu_baseline(reps=0)
-    for _ in range(args.steps):
-        b, _ = cpu_baseline(reps=0)
+        cpu_baseline(reps=1)
+    for _ in range(args.steps):                             # every step is one bounded sample of the workload
+        b, _ = cpu_baseline(reps=1)
         vals.append(b)
     secs = sum(v["seconds"] for v in vals)
-    fl = 2 * 2.0 * 256 * LLAMA_SHAPES[0][0] * LLAMA_SHAPES[0][1] * len(vals)
+    fl = step_flops(512) * len(vals)
     value = fl / secs / 1e12
     cb = dict(vals[-1]); cb["value"] = round(value, 4)
     line = {"impl": "reference", "metric": METRIC, "value": round(value, 4), "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
@@ -526,12 +661,7 @@ def run_ours(args):
                 "dtype": "bf16", "data": "synthetic",
                 "config": {"workload": WORKLOAD, "parallelism": "replicas only" if world > 1 else "single GPU",
                            "l2": "per-step working set ~1.1 GB of distinct buffers, larger than the 126 MB L2"},
-                "roofline": {"bound": "tensor", "achieved": round(per_gpu, 2), "peak": pk["bf16_sustained"], "unit": "TFLOP/s",
-                             "frac": round(per_gpu / pk["bf16_sustained"], 4), "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH,
-                             "traffic_note": NCU_TRAFFIC_NOTE,
-                             "peak_source": pk["src"] + " (sustained bf16 cuBLAS figure: kernels timed inside a long step; burst "
-                             + str(pk["bf16"]) + ")", "kernel": "k_gemm<A16W4 fwd/dgrad, 256 tokens>",
-                             "algorithmic": "2*M*N*K flops per launch"},
+                "roofline": roofline_entry(per_gpu, pk, clocks),
                 "e2e": {"value": round(e2e_value, 2), "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                         "ms_per_step": round(ms_e2e / e2e_steps, 3),
                         "pipeline": "pinned host buffers; upload, GEMM and download on three streams"},
@@ -552,7 +682,7 @@ def run_ours(args):
             ft_res = {"error": repr(e)[:300]}
         torch.cuda.empty_cache()
         try:                                        # Llama-2-7B architecture, seq 1024, micro-batch 4, one micro-batch per step
-            ft7 = finetune_measurement(torch, arch="llama-2-7b", steps=2, warmup=1, micro_batch=4, seq=1024, grad_accum=1,
+            ft7 = finetune_measurement(torch, arch="llama-2-7b", steps=10, warmup=2, micro_batch=4, seq=1024, grad_accum=1,
                                        decode_batches=(1, 16, 64) if rank == 0 else ())
         except Exception as e:
             ft7 = {"error": repr(e)[:300]}

@@ -145,6 +145,7 @@ __global__ void __launch_bounds__(ATT_THREADS) k_decode_attn(const __nv_bfloat16
     }
     const __nv_bfloat16* kb = k_cache + ((size_t)b * Hkv + hk) * (size_t)max_len * HD + sub * D;
     const __nv_bfloat16* vb = v_cache + ((size_t)b * Hkv + hk) * (size_t)max_len * HD + sub * D;
+    const unsigned int slot_mask = 0xffu << (8 * (slot & 3));
     float mx = -INFINITY, l = 0.0f, acc[D];
 #pragma unroll
     for (int d = 0; d < D; ++d) acc[d] = 0.0f;
@@ -159,7 +160,8 @@ __global__ void __launch_bounds__(ATT_THREADS) k_decode_attn(const __nv_bfloat16
         float s = 0.0f;
 #pragma unroll
         for (int d = 0; d < D; ++d) s = fmaf(qf[d], kf[d], s);
-        s += __shfl_xor_sync(0xffffffffu, s, 1); s += __shfl_xor_sync(0xffffffffu, s, 2); s += __shfl_xor_sync(0xffffffffu, s, 4);
+        // the four key slots of a warp run different numbers of iterations: only this slot's 8 lanes take part
+        s += __shfl_xor_sync(slot_mask, s, 1); s += __shfl_xor_sync(slot_mask, s, 2); s += __shfl_xor_sync(slot_mask, s, 4);
         const float mn = fmaxf(mx, s), corr = __expf(mx - mn), p = __expf(s - mn);
         l = l * corr + p;
 #pragma unroll

@@ -132,6 +132,7 @@ class LatentFineTuner:
         self.params = groups[0]["params"] + groups[1]["params"]
         self.arena = GradArena(self.params, dtype=torch.bfloat16, device=next(model.parameters()).device)
         self.step_no = 0
+        self.exchange = True                    # False: skip the gradient exchange (timing the step without it)
         dist_on = torch.distributed.is_available() and torch.distributed.is_initialized()
         self.gate = StepGate(timeout_s=gate_timeout_s, nonce=run_id) if dist_on and torch.distributed.get_world_size() > 1 else None
         self._reducer, self._events, self._capturing, self._reduce_in_backward = None, {}, False, False
@@ -148,7 +149,7 @@ class LatentFineTuner:
         total = torch.zeros((), device=self.arena.flat.device, dtype=torch.float32)
         if self.cuda_graph:
             self._ensure_graph(micro_batches[0], len(micro_batches))
-        red, last = self._reducer, len(micro_batches) - 1
+        red, last = (self._reducer if self.exchange else None), len(micro_batches) - 1
         for i, ids in enumerate(micro_batches):
             if red is not None and i == last:
                 self.gate.arrive_and_wait(self.step_no)  # host-side liveness check before the step's first collective
@@ -174,9 +175,9 @@ class LatentFineTuner:
             self.opt.step()
             red.wait_all()
         else:
-            if self.gate is not None:
+            if self.gate is not None and self.exchange:
                 self.gate.arrive_and_wait(self.step_no)  # host-side liveness check before the collective
-            allreduce_mean(self.arena, self.group)
+                allreduce_mean(self.arena, self.group)
             self.opt.step()
         for p in self.params:                           # MyAdam drops quantized grads (p.grad = None); clear the rest too
             p.grad = None

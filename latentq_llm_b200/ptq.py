@@ -5,9 +5,10 @@ of the packed-weight layouts on either side of the hot path): `QuantLinearGPTQ`,
 Same constructor arguments, buffer names / shapes / dtypes (= the `.safetensors` keys) and `pack` / `unpack` /
 `forward` semantics as the reference; packing and the GEMMs run on the GPU through liblatentq.  The Triton
 kernels of the reference (`matmul_248_kernel`, `transpose_matmul_248_kernel`) are replaced by the tcgen05 dequant
-GEMM after an in-memory layout conversion (GPTQ int32 [K/8, N] -> nibble pairs); only the trivial `g_idx`
-(k // groupsize) of the reference's own exporter is supported.  Tensor-core arithmetic is bf16 here (fp16 in
-the reference's Triton kernels), so outputs agree to ~1e-2 relative, not bit for bit.
+GEMM after an in-memory layout conversion (GPTQ int32 [K/8, N] -> nibble pairs) that is done once per set of
+buffers and cached; a general `g_idx` (act-order checkpoints) is served by sorting the input features by group at
+conversion time and gathering the activation columns per call.  Tensor-core arithmetic is bf16 here (fp16 in the
+reference's Triton kernels), so outputs agree to ~1e-2 relative, not bit for bit.
 
 Citations are `path:line` inside FWkey/latentQ_LLM.
 """
@@ -50,27 +51,67 @@ def _gptq_as_nibblepair(qweight, scales, qzeros, maxq, N, K, groupsize):
     return codes, s, z
 
 
+# Converted weights per set of GPTQ buffers: the layout conversion (a full pass over the weights) and the inspection of
+# g_idx (a host synchronisation) happen once, not per call.  Keyed by the buffers' storage and in-place version counters,
+# so `pack`, `load_state_dict` or any in-place edit makes a new entry; bounded.
+_GPTQ_CACHE: dict = {}
+_GPTQ_CACHE_MAX = 1024
+
+
+def _gptq_prepared(qweight, scales, qzeros, g_idx, maxq):
+    """(codes, scales, zeros, perm, inv_perm, N, K, groupsize) for the GEMM.  `perm` is None for the exporter's
+    g_idx = k // groupsize.  A general g_idx (act-order checkpoints: input feature k uses the scale / zero row
+    g_idx[k], PTQ/quant/quant_linear.py:113-122) is handled by sorting the input features by group once: the weight rows
+    are stored in that order, and a call gathers the activation columns with `perm` (or scatters the grad-input back)."""
+    key = tuple((t.data_ptr(), t._version, tuple(t.shape)) for t in (qweight, scales, qzeros, g_idx))
+    hit = _GPTQ_CACHE.get(key)
+    if hit is not None:
+        return hit
+    K, N = qweight.shape[0] * 8, qweight.shape[1]
+    groupsize = K // scales.shape[0]
+    perm = inv_perm = None
+    qw = qweight
+    if not _trivial_g_idx(g_idx, K, groupsize):
+        gi = g_idx.to(torch.int64)
+        counts = torch.bincount(gi, minlength=scales.shape[0])
+        if counts.numel() != scales.shape[0] or not bool((counts == groupsize).all()):
+            raise NotImplementedError("g_idx must assign exactly `groupsize` input features to every group")
+        perm = torch.argsort(gi, stable=True)
+        inv_perm = torch.empty_like(perm)
+        inv_perm[perm] = torch.arange(K, device=perm.device)
+        # reorder the weight rows (input features) by group: unpack [K/8, N] words to one code per k, gather, repack
+        shifts = torch.arange(0, 32, 4, device=qweight.device, dtype=torch.int32)
+        codes_kn = ((qweight.unsqueeze(1) >> shifts.view(1, 8, 1)) & 15).reshape(K, N)
+        codes_kn = codes_kn.index_select(0, perm).view(K // 8, 8, N)
+        qw = torch.zeros((K // 8, N), dtype=torch.int64, device=qweight.device)
+        for j in range(8):
+            qw |= codes_kn[:, j, :].to(torch.int64) << (4 * j)
+        qw = torch.where(qw >= 2 ** 31, qw - 2 ** 32, qw).to(torch.int32)
+    codes, s, z = _gptq_as_nibblepair(qw, scales, qzeros, maxq, N, K, groupsize)
+    if len(_GPTQ_CACHE) >= _GPTQ_CACHE_MAX:
+        _GPTQ_CACHE.clear()
+    out = _GPTQ_CACHE[key] = (codes, s, z, perm, inv_perm, N, K, groupsize)
+    return out
+
+
 def matmul248(input, qweight, scales, qzeros, g_idx, bits, maxq):
     """PTQ/quant/quant_linear.py:263-269: input[M,K] · deq(qweight)[K,N] -> fp16 [M,N]."""
     assert bits == 4
-    K, N = qweight.shape[0] * 8, qweight.shape[1]
-    groupsize = K // scales.shape[0]
-    if not _trivial_g_idx(g_idx, K, groupsize):
-        raise NotImplementedError("only g_idx = k // groupsize (what the reference's exporter writes) is supported")
-    codes, s, z = _gptq_as_nibblepair(qweight, scales, qzeros, maxq, N, K, groupsize)
-    y = ops.gemm_a16w4_fwd(input.to(torch.bfloat16).contiguous(), codes, s, z, None, N, K, groupsize)
+    codes, s, z, perm, _, N, K, groupsize = _gptq_prepared(qweight, scales, qzeros, g_idx, maxq)
+    x = input.to(torch.bfloat16)
+    x = x.index_select(1, perm) if perm is not None else x.contiguous()
+    y = ops.gemm_a16w4_fwd(x, codes, s, z, None, N, K, groupsize)
     return y.to(torch.float16)
 
 
 def transpose_matmul248(input, qweight, scales, qzeros, g_idx, bits, maxq):
     """PTQ/quant/quant_linear.py:272-279: grad-input, input[M,N] · deq(qweight)^T -> fp16 [M,K]."""
     assert bits == 4
-    K, N = qweight.shape[0] * 8, qweight.shape[1]
-    groupsize = K // scales.shape[0]
-    if not _trivial_g_idx(g_idx, K, groupsize):
-        raise NotImplementedError("only g_idx = k // groupsize is supported")
-    codes, s, z = _gptq_as_nibblepair(qweight, scales, qzeros, maxq, N, K, groupsize)
-    return ops.gemm_a16w4_dgrad(input.to(torch.bfloat16).contiguous(), codes, s, z, N, K, groupsize).to(torch.float16)
+    codes, s, z, _, inv_perm, N, K, groupsize = _gptq_prepared(qweight, scales, qzeros, g_idx, maxq)
+    dx = ops.gemm_a16w4_dgrad(input.to(torch.bfloat16).contiguous(), codes, s, z, N, K, groupsize)
+    if inv_perm is not None:
+        dx = dx.index_select(1, inv_perm)
+    return dx.to(torch.float16)
 
 
 class QuantLinearFunction(torch.autograd.Function):

@@ -37,8 +37,47 @@ def test_gptq_pack_unpack_and_gemm(golden):
     y.backward(dy)
     ref = dy.float() @ W
     assert float((x.grad.float() - ref).abs().max() / ref.abs().max()) < 1e-2
+    # the layout conversion is cached per set of buffers: the second call converts nothing
+    n_cached = len(ptq._GPTQ_CACHE)
+    m(x.detach())
+    assert len(ptq._GPTQ_CACHE) == n_cached
+    bad = m.g_idx.clone(); bad[:5] = 1                       # 123 / 133 members: not a grouping the layout can hold
     with pytest.raises(NotImplementedError):
-        ptq.matmul248(x.detach(), m.qweight, m.scales, m.qzeros, m.g_idx.flip(0), 4, 15)
+        ptq.matmul248(x.detach(), m.qweight, m.scales, m.qzeros, bad, 4, 15)
+
+
+def test_gptq_gemm_with_act_order_g_idx(golden):
+    """A general g_idx (input feature k takes the scale / zero row g_idx[k], PTQ/quant/quant_linear.py:113-122), as
+    act-order GPTQ checkpoints carry it: forward and grad-input against the module's own `unpack`."""
+    from latentq_llm_b200 import ptq
+    K, N, gs = 512, 256, 128
+    g = torch.Generator().manual_seed(5)
+    lin = torch.nn.Linear(K, N, bias=False)
+    lin.weight.data = torch.randn(N, K, generator=g) * 0.02
+    order = torch.randperm(K, generator=g)
+    g_idx = torch.empty(K, dtype=torch.int32)
+    g_idx[order] = (torch.arange(K) // gs).to(torch.int32)   # feature order[i] belongs to group i // gs
+    # per-group min/max parameters over the features of each group
+    W = lin.weight.data
+    scale, zero = torch.empty(N, K // gs), torch.empty(N, K // gs)
+    for gi in range(K // gs):
+        blk = W[:, g_idx == gi]
+        lo, hi = blk.amin(1).clamp(max=0), blk.amax(1).clamp(min=0)
+        scale[:, gi] = (hi - lo) / 15
+        zero[:, gi] = torch.round(-lo / scale[:, gi])
+    m = ptq.QuantLinearGPTQ(4, gs, K, N, False).cuda()
+    m.pack(lin, scale, zero, g_idx.cuda())
+    Wd = m.unpack(m.qweight, m.scales, m.qzeros)             # honours g_idx
+    assert float((Wd.cpu() - W).abs().max()) < float(scale.max())
+    for M in (4, 48):                                        # decode route and tensor-core route
+        x = torch.randn(M, K, device="cuda").half().requires_grad_(True)
+        y = m(x)
+        ref = x.detach().float() @ Wd.t()
+        assert float((y.float() - ref).abs().max() / ref.abs().max()) < 1e-2
+        dy = torch.randn(M, N, device="cuda").half()
+        y.backward(dy)
+        ref = dy.float() @ Wd
+        assert float((x.grad.float() - ref).abs().max() / ref.abs().max()) < 1e-2
 
 
 def test_a16w4_and_a8w8_packers(golden):

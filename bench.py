@@ -200,7 +200,35 @@ def extra_measurements(torch, ops, pk, only=None, numel=1 << 30):
         _a8w8_part(torch, ops, out, tm, g)
     if only in (None, "decode"):
         _decode_part(torch, ops, pk, out, tm)
+    if only == "decode_step":
+        _decode_step_part(torch, out, layers=numel if numel <= 64 else 4)
     return out
+
+
+def _decode_step_part(torch, out, layers=4, batch=1, prompt_len=512):
+    """One decode step of the Llama-2-7B architecture (first `layers` layers) through the fused kernel chain, run eagerly
+    between cudaProfilerStart / cudaProfilerStop (for `ncu --profile-from-start off`), and timed as a graph replay."""
+    from latentq_llm_b200 import finetune as ft
+    from latentq_llm_b200.generate import FusedLlamaGreedyDecoder
+    model = ft.build_model("llama-2-7b", "cuda", seed=1, layers=layers)
+    ft.quantize_decoder(model, lbit=0, gbit=16)
+    model.eval()
+    prompt = torch.randint(0, 32000, (batch, prompt_len), device="cuda")
+    dec = FusedLlamaGreedyDecoder(model, batch=batch, max_len=prompt_len + 72)
+    dec.generate(prompt, 4)                      # capture + warm-up
+    dec.generate(prompt, 2, use_graph=False)
+    torch.cuda.synchronize()
+    with torch.no_grad():
+        torch.cuda.profiler.start()
+        dec._step()
+        torch.cuda.synchronize()
+        torch.cuda.profiler.stop()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(32):
+        dec.graph.replay()
+    e1.record(); torch.cuda.synchronize()
+    out["decode_step"] = {"layers": layers, "batch": batch, "ms_per_step_graph": round(e0.elapsed_time(e1) / 32, 4)}
 
 
 def _requant_part(torch, ops, pk, out, tm, g, numel):
@@ -702,9 +730,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-extra", action="store_true", help="skip the secondary measurements and the CPU baseline")
-    ap.add_argument("--only", default="", choices=["", "requant", "sweep", "stream", "a8w8", "decode"],
+    ap.add_argument("--only", default="", choices=["", "requant", "sweep", "stream", "a8w8", "decode", "decode_step"],
                     help="run one family of the secondary measurements only (profiling a single kernel)")
-    ap.add_argument("--numel", type=int, default=1 << 30, help="weights in the requantize measurement")
+    ap.add_argument("--numel", type=int, default=1 << 30, help="weights in the requantize measurement (decode_step: layers)")
     ap.add_argument("--shapes", default="", help="comma-separated indices into the shape list (profiling a smaller case)")
     args = ap.parse_args()
     if args.shapes:

@@ -239,6 +239,13 @@ LQ_API int lq_gemm_a8w8(const int8_t* x8, const int8_t* w8, const float* row_sca
                         int64_t M, int64_t N, int64_t K, void* workspace, size_t workspace_bytes,
                         lq_stream_t stream);
 
+/* QLinearFunctionW4.backward grad_weight (utils/quant.py:141-142) and its accumulation over micro-batches by the
+ * backward hook (:408-411): dw[N,K] (+)= dy[M,N]^T · x[M,K], all bf16 row-major, fp32 accumulation in tensor memory.
+ * accumulate != 0: dw = bf16(fp32(dw) + product), one rounding, what a GEMM with beta = 1 computes; 0: dw = bf16(product).
+ * Both operands are read by TMA as 64 x 64 boxes and fed to tcgen05.mma MN-major (no transpose pass).  N, K multiples of 8. */
+LQ_API int lq_gemm_wgrad(const void* dy, const void* x, void* dw, int64_t M, int64_t N, int64_t K, int accumulate,
+                         lq_stream_t stream);
+
 /* Forward GEMM for callers that cannot allocate device memory (no counterpart in the reference).
  * Same arithmetic and arguments as lq_gemm_a16w4_fwd minus the workspace: split-K partial sums go into an
  * 8 MiB array built into the library (lq_gemm_a16w4_fwd_static_max_bytes), which every GPU that loads the
@@ -272,6 +279,13 @@ LQ_API int lq_gemm_device_status(int reset);
  * [7] epilogue waiting for an accumulator, [8] epilogue role total, [9] number of CTAs. */
 LQ_API int lq_gemm_profile(int enable, unsigned long long* out16);
 
+/* Decode chain switch (no counterpart in the reference).  While enabled, the decode-sized forward (M <= 16) and the
+ * decode-side kernels below are launched with programmatic stream serialization: a kernel may start, and the forward
+ * may fetch its WEIGHTS, while the previous kernel in the stream is still running; activations written by that kernel
+ * are read only after it has completed.  Enable it only around chains whose weights are not written by the previous
+ * kernel in the stream (a decode step).  Default: off.  Process-wide; returns the previous setting. */
+LQ_API int lq_decode_chain(int enable);
+
 /* ------------------------------------------------------------------------
  * Decode-side operations around the GEMMs of a Llama-architecture layer (bf16 everywhere).  hf_rounding != 0
  * rounds every intermediate to bf16 like the eager modules' tensor ops; 0 keeps fp32 up to the final cast like the
@@ -291,12 +305,19 @@ LQ_API int lq_rope_kv_store(void* qkv, const int64_t* positions, const float* in
 /* Single-query attention over the cache (the reference calls F.scaled_dot_product_attention,
  * PTQ/quant/fused_attn.py:148-149): out[b, h*hd..] = softmax(q[b,h]·K[b,hk,0..positions[b]] * scale) · V.
  * q: row b at q + b*q_row_stride elements, heads contiguous.  hd = 64 or 128.  The workspace holds the partial results
- * of the key-range splits and one ticket counter per (batch, head); the counters must be ZERO before the first call
- * and are left zero by every call. */
+ * of the key-range splits and, behind them, one ticket counter per (batch, head); the counters must be ZERO before the
+ * first call and are left zero by every call.  Their offset depends on B, Hq, hd and max_len: clear a workspace before
+ * using it with another shape. */
 LQ_API size_t lq_decode_attention_workspace_bytes(int64_t B, int Hq, int hd, int64_t max_len);
 LQ_API int lq_decode_attention(const void* q, int64_t q_row_stride, const void* k_cache, const void* v_cache,
                                const int64_t* positions, void* out, int64_t B, int Hq, int Hkv, int hd, int64_t max_len,
                                float scale, void* workspace, size_t workspace_bytes, lq_stream_t stream);
+/* Fused gate | up projection of a decode step (PTQ/quant/fused_mlp.py:84-168: C = silu(A·B1) * (A·B2) in one kernel):
+ * qweight holds 2*I weight rows, gate rows first; act[M, I] = silu(x·Wgate^T) * (x·Wup^T), both products rounded to
+ * bf16 first like the separate projections.  Decode-sized only (M <= 16, K a multiple of 256, group 128 or 256);
+ * other shapes return LQ_EUNSUPPORTED: use lq_gemm_a16w4_fwd into [M, 2I] and lq_silu_mul. */
+LQ_API int lq_gemm_a16w4_fwd_silu(const void* x, const int8_t* qweight, const void* scales, const void* zeros, void* act,
+                                  int64_t M, int64_t I, int64_t K, int group, int hf_rounding, lq_stream_t stream);
 /* act[M, I] = silu(gate_up[M, 0:I]) * gate_up[M, I:2I] (epilogue of PTQ/quant/fused_mlp.py:84-168; LlamaMLP). */
 LQ_API int lq_silu_mul(const void* gate_up, void* act, int64_t M, int64_t I, int hf_rounding, lq_stream_t stream);
 

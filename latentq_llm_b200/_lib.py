@@ -58,6 +58,7 @@ _HYPER = C.POINTER(AdamHyper)
 # name -> argtypes; every function returns int except the ones listed in _RESTYPE.
 SIGNATURES = {
     "lq_version": [],
+    "lq_decode_chain": [_i],
     "lq_status_string": [_i],
     "lq_last_cuda_error": [],
     "lq_res3_quant": [_p, _i, _p, _i64, _i, _f, _i, _f, _i, _f, _p],
@@ -99,11 +100,13 @@ SIGNATURES = {
     "lq_gemm_a16w4_fwd_static_peek": [_p, _sz, _sz],
     "lq_gemm_a8w8": [_p, _p, _p, _p, _f, _p, _p, _p, _i64, _i64, _i64, _p, _sz, _p],
     "lq_mma_issue_rate": [_i, _i, _i, _i, _i, _i, _p, _p],
+    "lq_gemm_wgrad": [_p, _p, _p, _i64, _i64, _i64, _i, _p],
     "lq_add_rmsnorm": [_p, _p, _p, _f, _p, _i64, _i64, _i, _p],
     "lq_rope_kv_store": [_p, _p, _p, _p, _p, _i64, _i, _i, _i, _i, _i64, _i, _p],
     "lq_decode_attention_workspace_bytes": [_i64, _i, _i, _i64],
     "lq_decode_attention": [_p, _i64, _p, _p, _p, _p, _i64, _i, _i, _i, _i64, _f, _p, _sz, _p],
     "lq_silu_mul": [_p, _p, _i64, _i64, _i, _p],
+    "lq_gemm_a16w4_fwd_silu": [_p, _p, _p, _p, _p, _i64, _i64, _i64, _i, _i, _p],
 }
 _RESTYPE = {"lq_status_string": C.c_char_p, "lq_last_cuda_error": C.c_char_p, "lq_gemm_workspace_bytes": C.c_size_t,
             "lq_gemm_a16w4_fwd_static_max_bytes": C.c_size_t, "lq_decode_attention_workspace_bytes": C.c_size_t}

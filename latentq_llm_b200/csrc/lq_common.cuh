@@ -21,6 +21,28 @@ int sm_count();                       // cached per current device
 // target device 0, and tensor-map encoding fails outright).  No-op when a context is already current.
 int ensure_device_for(const void* device_ptr);
 
+// ---- programmatic dependent launch (decode chain) -------------------------------------------------
+// A decode step is a chain of short launches in which every kernel consumes its predecessor's output.  Inside such a
+// chain (lq_decode_chain(1)) kernels are launched with programmatic stream serialization: a kernel signals
+// launch_dependents early, so that its successor's launch latency (and, for the GEMMs, the first round of weight loads)
+// overlaps its own run, and every kernel reads what a predecessor may have written only after pdl_wait(), which returns
+// once the predecessor grid has completed and its writes are visible.  Outside a chain the attribute is off and both
+// instructions are no-ops: a caller whose previous kernel wrote the WEIGHTS (an optimizer step followed by a forward)
+// must not have those read early.
+bool decode_chain_enabled();
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+template <typename... KArgs, typename... Args>
+static inline void launch_pdl(void (*kern)(KArgs...), dim3 grid, unsigned block, size_t smem, cudaStream_t st, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid; cfg.blockDim = dim3(block); cfg.dynamicSmemBytes = smem; cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = decode_chain_enabled() ? 1 : 0;
+    cfg.attrs = attr; cfg.numAttrs = 1;
+    cudaLaunchKernelEx(&cfg, kern, KArgs(args)...);
+}
+
 // ---- numeric helpers ------------------------------------------------------------
 __device__ __forceinline__ float bf16r(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
 template <bool BF> __device__ __forceinline__ float rnd(float x) { return BF ? bf16r(x) : x; }

@@ -30,6 +30,8 @@ __global__ void __launch_bounds__(NORM_THREADS) k_add_rmsnorm(__nv_bfloat16* __r
                                                                const __nv_bfloat16* __restrict__ gamma, float eps,
                                                                __nv_bfloat16* __restrict__ y, int K, int hf_rounding) {
     __shared__ float red[NORM_THREADS / 32];
+    pdl_launch_dependents();                          // (decode chain) the successor may be launched; it waits for this grid
+    pdl_wait();                                       // h / delta may be the predecessor's output
     const size_t row = (size_t)blockIdx.x * K;
     uint4* hv = reinterpret_cast<uint4*>(h + row);
     const uint4* dv = delta ? reinterpret_cast<const uint4*>(delta + row) : nullptr;
@@ -71,6 +73,72 @@ __global__ void __launch_bounds__(NORM_THREADS) k_add_rmsnorm(__nv_bfloat16* __r
     }
 }
 
+// Register-resident variant for K <= 2048 * VPT: every thread requests all its vectors of h, delta and gamma before
+// anything is reduced (one round of memory latency instead of three), and the row is never re-read.
+template <int VPT>
+__global__ void __launch_bounds__(NORM_THREADS) k_add_rmsnorm_r(__nv_bfloat16* __restrict__ h, const __nv_bfloat16* __restrict__ delta,
+                                                                 const __nv_bfloat16* __restrict__ gamma, float eps,
+                                                                 __nv_bfloat16* __restrict__ y, int K, int hf_rounding) {
+    __shared__ float red[NORM_THREADS / 32];
+    const uint4* gv = reinterpret_cast<const uint4*>(gamma);
+    const int nvec = K / 8;
+    uint4 g[VPT], a[VPT], d[VPT];
+#pragma unroll
+    for (int u = 0; u < VPT; ++u) {                   // gamma is a parameter: fetched before the dependency wait
+        const int i = threadIdx.x + u * NORM_THREADS;
+        g[u] = i < nvec ? __ldg(gv + i) : make_uint4(0, 0, 0, 0);
+    }
+    pdl_launch_dependents();
+    pdl_wait();                                       // h / delta may be the predecessor's output
+    const size_t row = (size_t)blockIdx.x * K;
+    uint4* hv = reinterpret_cast<uint4*>(h + row);
+    const uint4* dv = delta ? reinterpret_cast<const uint4*>(delta + row) : nullptr;
+#pragma unroll
+    for (int u = 0; u < VPT; ++u) {
+        const int i = threadIdx.x + u * NORM_THREADS;
+        a[u] = i < nvec ? hv[i] : make_uint4(0, 0, 0, 0);
+        d[u] = (dv && i < nvec) ? __ldg(dv + i) : make_uint4(0, 0, 0, 0);
+    }
+    float ss = 0.0f;
+#pragma unroll
+    for (int u = 0; u < VPT; ++u) {
+        uint32_t* w = reinterpret_cast<uint32_t*>(&a[u]);
+        const uint32_t* e = reinterpret_cast<const uint32_t*>(&d[u]);
+        if (dv) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) w[j] = pack_bf2(__fadd_rn(bf_lo(w[j]), bf_lo(e[j])), __fadd_rn(bf_hi(w[j]), bf_hi(e[j])));
+            const int i = threadIdx.x + u * NORM_THREADS;
+            if (i < nvec) hv[i] = a[u];
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) { const float lo = bf_lo(w[j]), hi = bf_hi(w[j]); ss = fmaf(lo, lo, ss); ss = fmaf(hi, hi, ss); }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    float tot = 0.0f;
+#pragma unroll
+    for (int wv = 0; wv < NORM_THREADS / 32; ++wv) tot += red[wv];
+    const float rstd = hf_rounding ? rsqrtf(tot / (float)K + eps) : 1.0f / sqrtf(tot / (float)K + eps);
+    uint4* yv = reinterpret_cast<uint4*>(y + row);
+#pragma unroll
+    for (int u = 0; u < VPT; ++u) {
+        const int i = threadIdx.x + u * NORM_THREADS;
+        if (i >= nvec) continue;
+        const uint32_t* w = reinterpret_cast<const uint32_t*>(&a[u]);
+        const uint32_t* gw = reinterpret_cast<const uint32_t*>(&g[u]);
+        uint32_t o[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            float lo = __fmul_rn(bf_lo(w[j]), rstd), hi = __fmul_rn(bf_hi(w[j]), rstd);
+            if (hf_rounding) { lo = bf16r(lo); hi = bf16r(hi); }
+            o[j] = pack_bf2(__fmul_rn(lo, bf_lo(gw[j])), __fmul_rn(hi, bf_hi(gw[j])));
+        }
+        yv[i] = make_uint4(o[0], o[1], o[2], o[3]);
+    }
+}
+
 // ---------------------------------------------------------------------------------------------
 // RoPE (rotate-half) on the q and k heads of a fused qkv row, k and v stored into the cache at the token's position.
 // grid (token, head of q|k|v), hd/2 threads.  Cache layout [batch, kv head, max_len, hd].
@@ -80,6 +148,8 @@ __global__ void k_rope_kv_store(__nv_bfloat16* __restrict__ qkv, const long long
                                 __nv_bfloat16* __restrict__ v_cache, int tokens_per_seq, int Hq, int Hkv, int hd, int max_len,
                                 int hf_rounding) {
     const int m = blockIdx.x, head = blockIdx.y, i = threadIdx.x, half = hd >> 1;
+    pdl_launch_dependents();
+    pdl_wait();                                       // qkv is the predecessor's output
     const long long pos = positions[m];
     __nv_bfloat16* src = qkv + (size_t)m * (size_t)(Hq + 2 * Hkv) * hd + (size_t)head * hd;
     const int b = m / tokens_per_seq;
@@ -128,6 +198,8 @@ __global__ void __launch_bounds__(ATT_THREADS) k_decode_attn(const __nv_bfloat16
     const int bh = blockIdx.x, b = bh / Hq, h = bh - b * Hq, hk = h / (Hq / Hkv);
     const int splits = gridDim.y, split = blockIdx.y;
     const int slot = threadIdx.x >> 3, sub = threadIdx.x & 7;
+    pdl_launch_dependents();
+    pdl_wait();                                       // q and the newest cache row are the predecessor's output
     long long n_keys = positions[b] + 1;
     if (n_keys > max_len) n_keys = max_len;
     if (n_keys < 0) n_keys = 0;
@@ -149,27 +221,59 @@ __global__ void __launch_bounds__(ATT_THREADS) k_decode_attn(const __nv_bfloat16
     float mx = -INFINITY, l = 0.0f, acc[D];
 #pragma unroll
     for (int d = 0; d < D; ++d) acc[d] = 0.0f;
-    for (int j = j0 + slot; j < j1; j += ATT_SLOTS) {
-        float kf[D];
+    // KPI keys per slot in flight: the K and V rows of all of them are requested before any arithmetic (the kernel is a
+    // chain of memory latencies otherwise; a split covers about 64 keys, i.e. one such round per slot).  A key beyond the
+    // range reads key j1-1 again and gets weight zero.
+    constexpr int KPI = 4;
+    for (int j = j0 + slot; j < j1; j += KPI * ATT_SLOTS) {
+        uint4 kq[KPI][D / 8], vq[KPI][D / 8];
+        bool on[KPI];
 #pragma unroll
-        for (int d = 0; d < D; d += 8) {
-            const uint4 w = __ldg(reinterpret_cast<const uint4*>(kb + (size_t)j * HD + d));
-            kf[d] = bf_lo(w.x); kf[d + 1] = bf_hi(w.x); kf[d + 2] = bf_lo(w.y); kf[d + 3] = bf_hi(w.y);
-            kf[d + 4] = bf_lo(w.z); kf[d + 5] = bf_hi(w.z); kf[d + 6] = bf_lo(w.w); kf[d + 7] = bf_hi(w.w);
+        for (int u = 0; u < KPI; ++u) {
+            const int ju = j + u * ATT_SLOTS;
+            on[u] = ju < j1;
+            const size_t row = (size_t)(on[u] ? ju : j1 - 1) * HD;
+#pragma unroll
+            for (int d = 0; d < D / 8; ++d) {
+                kq[u][d] = __ldg(reinterpret_cast<const uint4*>(kb + row) + d);
+                vq[u][d] = __ldg(reinterpret_cast<const uint4*>(vb + row) + d);
+            }
         }
-        float s = 0.0f;
+        float sc[KPI];
 #pragma unroll
-        for (int d = 0; d < D; ++d) s = fmaf(qf[d], kf[d], s);
-        // the four key slots of a warp run different numbers of iterations: only this slot's 8 lanes take part
-        s += __shfl_xor_sync(slot_mask, s, 1); s += __shfl_xor_sync(slot_mask, s, 2); s += __shfl_xor_sync(slot_mask, s, 4);
-        const float mn = fmaxf(mx, s), corr = __expf(mx - mn), p = __expf(s - mn);
-        l = l * corr + p;
+        for (int u = 0; u < KPI; ++u) {
+            float a = 0.0f;
 #pragma unroll
-        for (int d = 0; d < D; d += 8) {
-            const uint4 w = __ldg(reinterpret_cast<const uint4*>(vb + (size_t)j * HD + d));
-            const float vf[8] = {bf_lo(w.x), bf_hi(w.x), bf_lo(w.y), bf_hi(w.y), bf_lo(w.z), bf_hi(w.z), bf_lo(w.w), bf_hi(w.w)};
+            for (int d = 0; d < D / 8; ++d) {
+                const uint32_t w[4] = {kq[u][d].x, kq[u][d].y, kq[u][d].z, kq[u][d].w};
 #pragma unroll
-            for (int e = 0; e < 8; ++e) acc[d + e] = fmaf(p, vf[e], acc[d + e] * corr);
+                for (int e = 0; e < 4; ++e) { a = fmaf(qf[d * 8 + 2 * e], bf_lo(w[e]), a); a = fmaf(qf[d * 8 + 2 * e + 1], bf_hi(w[e]), a); }
+            }
+            // the four key slots of a warp run different numbers of iterations: only this slot's 8 lanes take part
+            a += __shfl_xor_sync(slot_mask, a, 1); a += __shfl_xor_sync(slot_mask, a, 2); a += __shfl_xor_sync(slot_mask, a, 4);
+            sc[u] = on[u] ? a : -INFINITY;
+        }
+        float mn = mx;
+#pragma unroll
+        for (int u = 0; u < KPI; ++u) mn = fmaxf(mn, sc[u]);
+        const float corr = __expf(mx - mn);
+        float pw[KPI];
+        l *= corr;
+#pragma unroll
+        for (int u = 0; u < KPI; ++u) { pw[u] = on[u] ? __expf(sc[u] - mn) : 0.0f; l += pw[u]; }
+#pragma unroll
+        for (int d = 0; d < D; ++d) acc[d] *= corr;
+#pragma unroll
+        for (int u = 0; u < KPI; ++u) {
+#pragma unroll
+            for (int d = 0; d < D / 8; ++d) {
+                const uint32_t w[4] = {vq[u][d].x, vq[u][d].y, vq[u][d].z, vq[u][d].w};
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    acc[d * 8 + 2 * e] = fmaf(pw[u], bf_lo(w[e]), acc[d * 8 + 2 * e]);
+                    acc[d * 8 + 2 * e + 1] = fmaf(pw[u], bf_hi(w[e]), acc[d * 8 + 2 * e + 1]);
+                }
+            }
         }
         mx = mn;
     }
@@ -228,6 +332,8 @@ __global__ void __launch_bounds__(ATT_THREADS) k_decode_attn(const __nv_bfloat16
 __global__ void __launch_bounds__(256) k_silu_mul(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ act,
                                                   int64_t M, int I, int hf_rounding) {
     const int64_t vec_per_row = I / 8, total = M * vec_per_row;
+    pdl_launch_dependents();
+    pdl_wait();                                       // gate | up is the predecessor's output
     for (int64_t v = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; v < total; v += (int64_t)gridDim.x * blockDim.x) {
         const int64_t m = v / vec_per_row, c = v - m * vec_per_row;
         const uint4 g = __ldg(reinterpret_cast<const uint4*>(gu + m * 2 * (int64_t)I) + c);
@@ -259,9 +365,15 @@ int lq_add_rmsnorm(void* h, const void* delta, const void* gamma, float eps, voi
     if (M < 0 || K <= 0 || (K % 8) != 0 || M >= (1ll << 31) || K >= (1ll << 24)) return LQ_EUNSUPPORTED;
     if (M == 0) return LQ_OK;
     { int rc = ensure_device_for(h); if (rc) return rc; }
-    k_add_rmsnorm<<<(unsigned)M, NORM_THREADS, 0, (cudaStream_t)stream>>>((__nv_bfloat16*)h, (const __nv_bfloat16*)delta,
-                                                                           (const __nv_bfloat16*)gamma, eps, (__nv_bfloat16*)y, (int)K,
-                                                                           hf_rounding);
+    const int vpt = (int)((K / 8 + NORM_THREADS - 1) / NORM_THREADS);
+#define LQ_NORM_ARGS dim3((unsigned)M), NORM_THREADS, 0, (cudaStream_t)stream, (__nv_bfloat16*)h, (const __nv_bfloat16*)delta, \
+                     (const __nv_bfloat16*)gamma, eps, (__nv_bfloat16*)y, (int)K, hf_rounding
+    if (vpt <= 1) launch_pdl(k_add_rmsnorm_r<1>, LQ_NORM_ARGS);
+    else if (vpt <= 2) launch_pdl(k_add_rmsnorm_r<2>, LQ_NORM_ARGS);
+    else if (vpt <= 4) launch_pdl(k_add_rmsnorm_r<4>, LQ_NORM_ARGS);
+    else if (vpt <= 6) launch_pdl(k_add_rmsnorm_r<6>, LQ_NORM_ARGS);
+    else launch_pdl(k_add_rmsnorm, LQ_NORM_ARGS);
+#undef LQ_NORM_ARGS
     return check_launch("k_add_rmsnorm");
 }
 
@@ -274,16 +386,15 @@ int lq_rope_kv_store(void* qkv, const int64_t* positions, const float* inv_freq,
     if (M == 0) return LQ_OK;
     { int rc = ensure_device_for(qkv); if (rc) return rc; }
     dim3 grid((unsigned)M, (unsigned)(Hq + 2 * Hkv));
-    k_rope_kv_store<<<grid, hd / 2, 0, (cudaStream_t)stream>>>((__nv_bfloat16*)qkv, (const long long*)positions, inv_freq,
-                                                               (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, tokens_per_seq, Hq,
-                                                               Hkv, hd, (int)max_len, hf_rounding);
+    launch_pdl(k_rope_kv_store, grid, (unsigned)(hd / 2), 0, (cudaStream_t)stream, (__nv_bfloat16*)qkv, (const long long*)positions, inv_freq,
+               (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, tokens_per_seq, Hq, Hkv, hd, (int)max_len, hf_rounding);
     return check_launch("k_rope_kv_store");
 }
 
 static int attn_splits(int64_t B, int Hq, int64_t max_len) {
     const int64_t ctas = B * Hq;
-    int64_t s = (2 * (int64_t)sm_count() + ctas - 1) / ctas;      // about two CTAs per SM in flight
-    const int64_t cap = (max_len + 127) / 128;                      // at least 128 keys per split
+    int64_t s = (4 * (int64_t)sm_count() + ctas - 1) / ctas;      // about four CTAs per SM in flight
+    const int64_t cap = (max_len + 63) / 64;                        // at least 64 keys (two rounds of the 16 slots x 2) per split
     if (s > cap) s = cap;
     if (s > 32) s = 32;
     if (s < 1) s = 1;
@@ -315,13 +426,11 @@ int lq_decode_attention(const void* q, int64_t q_row_stride, const void* k_cache
     dim3 grid((unsigned)(B * Hq), (unsigned)splits);
     cudaStream_t st = (cudaStream_t)stream;
     if (hd == 128)
-        k_decode_attn<128><<<grid, ATT_THREADS, 0, st>>>((const __nv_bfloat16*)q, (int)q_row_stride, (const __nv_bfloat16*)k_cache,
-                                                         (const __nv_bfloat16*)v_cache, (const long long*)positions, (__nv_bfloat16*)out,
-                                                         Hq, Hkv, (int)max_len, scale, part, tickets);
+        launch_pdl(k_decode_attn<128>, grid, (unsigned)ATT_THREADS, 0, st, (const __nv_bfloat16*)q, (int)q_row_stride, (const __nv_bfloat16*)k_cache,
+                   (const __nv_bfloat16*)v_cache, (const long long*)positions, (__nv_bfloat16*)out, Hq, Hkv, (int)max_len, scale, part, tickets);
     else
-        k_decode_attn<64><<<grid, ATT_THREADS, 0, st>>>((const __nv_bfloat16*)q, (int)q_row_stride, (const __nv_bfloat16*)k_cache,
-                                                        (const __nv_bfloat16*)v_cache, (const long long*)positions, (__nv_bfloat16*)out,
-                                                        Hq, Hkv, (int)max_len, scale, part, tickets);
+        launch_pdl(k_decode_attn<64>, grid, (unsigned)ATT_THREADS, 0, st, (const __nv_bfloat16*)q, (int)q_row_stride, (const __nv_bfloat16*)k_cache,
+                   (const __nv_bfloat16*)v_cache, (const long long*)positions, (__nv_bfloat16*)out, Hq, Hkv, (int)max_len, scale, part, tickets);
     return check_launch("k_decode_attn");
 }
 
@@ -334,7 +443,7 @@ int lq_silu_mul(const void* gate_up, void* act, int64_t M, int64_t I, int hf_rou
     int64_t g = (total + 255) / 256;
     const int64_t cap = (int64_t)sm_count() * 8;
     if (g > cap) g = cap;
-    k_silu_mul<<<(unsigned)g, 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)gate_up, (__nv_bfloat16*)act, M, (int)I, hf_rounding);
+    launch_pdl(k_silu_mul, dim3((unsigned)g), 256u, 0, (cudaStream_t)stream, (const __nv_bfloat16*)gate_up, (__nv_bfloat16*)act, M, (int)I, hf_rounding);
     return check_launch("k_silu_mul");
 }
 

@@ -29,7 +29,7 @@
 
 namespace lq {
 
-enum { KIND_FWD = LQ_GEMM_A16W4_FWD, KIND_DGRAD = LQ_GEMM_A16W4_DGRAD, KIND_I8 = LQ_GEMM_A8W8 };
+enum { KIND_FWD = LQ_GEMM_A16W4_FWD, KIND_DGRAD = LQ_GEMM_A16W4_DGRAD, KIND_I8 = LQ_GEMM_A8W8, KIND_WGRAD = 3 };
 
 constexpr int ROW_BYTES = 128;        // one swizzle row
 constexpr int A_TILE_BYTES = TILE_R * ROW_BYTES;
@@ -65,6 +65,7 @@ struct GemmParams {
     int32_t* acc_out;              // int8: raw accumulators [M, R] or null
     void* partial;                 // split-K partial sums [splits][M][R] (fp32 / int32); balanced mode: slots + flags
     int sk_grid;                   // balanced mode (SK): number of CTAs the k-block units are dealt to
+    int accumulate;                // weight gradient: out += product (rounded once from the fp32 sum) instead of out = product
 };
 
 // One CTA's share of the work as a sequence of segments (a tile and a range of its k-blocks).
@@ -118,7 +119,8 @@ constexpr int TA_COLS_PER_STAGE = 32;
 template <int KIND, int TN, int RT, bool TA = false>
 struct Cfg {
     static constexpr bool I8 = KIND == KIND_I8;
-    static constexpr bool W4 = !I8;
+    static constexpr bool WG = KIND == KIND_WGRAD;      // dense bf16 weight gradient: both operands by TMA, MN-major
+    static constexpr bool W4 = !I8 && !WG;
     static_assert(!TA || (W4 && RT == 1), "tensor-memory A operand: A16W4 kinds, one row tile per CTA");
     static constexpr int A_BYTES = TA ? 0 : RT * A_TILE_BYTES;
     static constexpr int B_TILE_BYTES = TN * ROW_BYTES;
@@ -243,12 +245,21 @@ k_gemm(const __grid_constant__ CUtensorMap map_tok, const __grid_constant__ CUte
                         const int row0 = (r_tile * RT + r) * TILE_R;
                         if (KIND == KIND_I8)            // int8 weights straight into the MMA tile
                             tma_load_2d(a_tile(stage, r), &map_w, kb * 128, row0, bar);
-                        else if (KIND == KIND_FWD)      // raw: 128 weight rows x 32 bytes (64 k)
+                        else if (KIND == KIND_WGRAD) {  // dY[64 tokens, 128 n] as two MN-major atoms of 64 n (128 B rows)
+                            tma_load_2d(a_tile(stage, r), &map_w, row0, kb * 64, bar);
+                            tma_load_2d(a_tile(stage, r) + 8192u, &map_w, row0 + 64, kb * 64, bar);
+                        } else if (KIND == KIND_FWD)    // raw: 128 weight rows x 32 bytes (64 k)
                             tma_load_2d(smem_u32(raw_tile(stage, r)), &map_w, kb * 32, row0, bar);
                         else                            // raw: 64 weight rows (n) x 64 bytes (128 k)
                             tma_load_2d(smem_u32(raw_tile(stage, r)), &map_w, row0 / 2, kb * 64, bar);
                     }
-                    tma_load_2d(b_tile(stage), &map_tok, kb * (C::I8 ? 128 : 64), t_tile * TN, bar);
+                    if (KIND == KIND_WGRAD) {           // X[64 tokens, TN k] as TN/64 MN-major atoms
+#pragma unroll
+                        for (int h = 0; h < TN / 64; ++h)
+                            tma_load_2d(b_tile(stage) + (uint32_t)(h * 8192), &map_tok, t_tile * TN + h * 64, kb * 64, bar);
+                    } else {
+                        tma_load_2d(b_tile(stage), &map_tok, kb * (C::I8 ? 128 : 64), t_tile * TN, bar);
+                    }
                     if (++stage == C::STAGES) { stage = 0; phase ^= 1u; }
                 }
             }
@@ -257,7 +268,7 @@ k_gemm(const __grid_constant__ CUtensorMap map_tok, const __grid_constant__ CUte
     } else if (warp == 1) {
         // ===================== MMA issuer =====================
         if (lane == 0) {
-            constexpr uint32_t IDESC = make_idesc(C::I8, KIND == KIND_DGRAD && !TA, TN);
+            constexpr uint32_t IDESC = make_idesc(C::I8, (KIND == KIND_DGRAD && !TA) || C::WG, TN, C::WG);
             int stage = 0; uint32_t phase = 0;
             int acc = 0; uint32_t acc_phase = 0;
             bool ok = true;
@@ -280,21 +291,22 @@ k_gemm(const __grid_constant__ CUtensorMap map_tok, const __grid_constant__ CUte
                     // K-major tiles: 8-row groups are 1024 B apart; one MMA consumes 32 B of every row.
                     // MN-major A (grad-input): 64-element atoms are 8192 B apart (leading), 8-row groups of the
                     // contraction 1024 B apart (stride); one MMA consumes 16 contraction rows = 2048 B.
-                    const uint64_t b_desc = make_smem_desc(b_tile(stage), 16, 1024);
-                    const uint32_t a_step = (KIND == KIND_DGRAD) ? (2048u >> 4) : (32u >> 4);
+                    const uint64_t b_desc = C::WG ? make_smem_desc(b_tile(stage), 8192, 1024) : make_smem_desc(b_tile(stage), 16, 1024);
+                    const uint32_t a_step = (KIND == KIND_DGRAD || C::WG) ? (2048u >> 4) : (32u >> 4);
+                    const uint32_t b_step = C::WG ? (2048u >> 4) : (32u >> 4);
                     if (TA) {
                         const uint32_t a_tmem = tmem_base + (uint32_t)(C::TA_COL0 + stage * TA_COLS_PER_STAGE);
 #pragma unroll
                         for (int kk = 0; kk < C::UMMA_PER_STAGE; ++kk)
-                            umma_ta(d_tmem, a_tmem + (uint32_t)(kk * 8), b_desc + (uint64_t)(kk * 2), IDESC, (kb > kb0 || kk > 0) ? 1u : 0u);
+                            umma_ta(d_tmem, a_tmem + (uint32_t)(kk * 8), b_desc + (uint64_t)(kk * b_step), IDESC, (kb > kb0 || kk > 0) ? 1u : 0u);
                     } else {
 #pragma unroll
                     for (int r = 0; r < RT; ++r) {
-                        const uint64_t a_desc = (KIND == KIND_DGRAD) ? make_smem_desc(a_tile(stage, r), 8192, 1024)
-                                                                     : make_smem_desc(a_tile(stage, r), 16, 1024);
+                        const uint64_t a_desc = (KIND == KIND_DGRAD || C::WG) ? make_smem_desc(a_tile(stage, r), 8192, 1024)
+                                                                              : make_smem_desc(a_tile(stage, r), 16, 1024);
 #pragma unroll
                         for (int kk = 0; kk < C::UMMA_PER_STAGE; ++kk) {
-                            umma<C::I8>(d_tmem + (uint32_t)(r * TN), a_desc + (uint64_t)(kk * a_step), b_desc + (uint64_t)(kk * 2),
+                            umma<C::I8>(d_tmem + (uint32_t)(r * TN), a_desc + (uint64_t)(kk * a_step), b_desc + (uint64_t)(kk * b_step),
                                         IDESC, (kb > kb0 || kk > 0) ? 1u : 0u);
                         }
                     }
@@ -383,6 +395,34 @@ k_gemm(const __grid_constant__ CUtensorMap map_tok, const __grid_constant__ CUte
                                 for (int j = 0; j < SLAB; ++j) v[j] = __float_as_uint(__fadd_rn(__uint_as_float(v[j]), __ldcg(src + j * TILE_R)));
                             }
                         }
+                    }
+                    if (C::WG) {
+                        // weight gradient: lane = output row n, the slab's 16 columns are consecutive in memory.
+                        // dW = bf16(fp32(dW) + acc) when accumulating (what a GEMM with beta = 1 computes), else bf16(acc).
+                        const int t0 = t_tile * TN + c0;
+                        if (r_ok && t0 < p.M) {
+                            __nv_bfloat16* dst = p.out + (size_t)r * p.M + t0;
+                            if (t0 + SLAB <= p.M && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+                                uint4 o[2] = {make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0)};
+                                if (p.accumulate) { o[0] = *reinterpret_cast<const uint4*>(dst); o[1] = *reinterpret_cast<const uint4*>(dst + 8); }
+                                uint32_t* ow = reinterpret_cast<uint32_t*>(o);
+#pragma unroll
+                                for (int i = 0; i < 8; ++i) {
+                                    const float a0 = __fadd_rn(__uint_as_float(ow[i] << 16), __uint_as_float(v[2 * i]));
+                                    const float a1 = __fadd_rn(__uint_as_float(ow[i] & 0xffff0000u), __uint_as_float(v[2 * i + 1]));
+                                    ow[i] = bf2_as_u32(__floats2bfloat162_rn(a0, a1));
+                                }
+                                *reinterpret_cast<uint4*>(dst) = o[0]; *reinterpret_cast<uint4*>(dst + 8) = o[1];
+                            } else {
+#pragma unroll
+                                for (int j = 0; j < SLAB; ++j) {
+                                    if (t0 + j >= p.M) break;
+                                    const float old = p.accumulate ? __bfloat162float(dst[j]) : 0.0f;
+                                    dst[j] = __float2bfloat16_rn(__fadd_rn(old, __uint_as_float(v[j])));
+                                }
+                            }
+                        }
+                        continue;
                     }
                     if (p.splits == 1 && !(C::I8 && p.acc_out) && t_tile * TN + c0 + SLAB <= p.M &&
                         (!C::I8 || (reinterpret_cast<uintptr_t>(p.row_scale) & 15) == 0)) {       // warp-uniform condition
@@ -942,6 +982,52 @@ int lq_gemm_a8w8(const int8_t* x8, const int8_t* w8, const float* row_scale, con
     p.row_scale = row_scale; p.col_scale = col_scale; p.alpha = alpha; p.bias = (const __nv_bfloat16*)bias;
     p.out = (__nv_bfloat16*)y; p.acc_out = acc_out;
     return run_gemm(KIND_I8, x8, w8, p, M, N, K, workspace, workspace_bytes, (cudaStream_t)stream);
+}
+
+int lq_gemm_a16w4_fwd_silu(const void* x, const int8_t* qweight, const void* scales, const void* zeros, void* act, int64_t M,
+                           int64_t I, int64_t K, int group, int hf_rounding, lq_stream_t stream) {
+    if (!x || !qweight || !scales || !zeros || !act || !al16(x) || !al16(qweight) || !al16(act)) return LQ_EINVAL;
+    if (!shape_ok_w4(M, 2 * I, K, group) || (I % 8) != 0) return LQ_EUNSUPPORTED;
+    // the fused epilogue exists in the decode-sized row-block kernels only (a thread there holds gate[f] and up[f])
+    if (M > 16 || (K % 256) != 0 || !skinny_rows_supported(K, group)) return LQ_EUNSUPPORTED;
+    if (M == 0) return LQ_OK;
+    { int rc_dev = ensure_device_for(x); if (rc_dev) return rc_dev; }
+    SkinnyParams sp{};
+    sp.x = (const __nv_bfloat16*)x; sp.qweight = (const uint8_t*)qweight; sp.scales = (const __nv_bfloat16*)scales;
+    sp.zeros = (const __nv_bfloat16*)zeros; sp.out = (__nv_bfloat16*)act;
+    sp.M = (int)M; sp.N = (int)I; sp.K = (int)K; sp.group = group; sp.splits = 1; sp.chunks_per_split = (int)(K / 64);
+    sp.pair_stride = (int)I; sp.hf_rounding = hf_rounding;
+    return launch_skinny_rows(sp, (cudaStream_t)stream);
+}
+
+int lq_gemm_wgrad(const void* dy, const void* x, void* dw, int64_t M, int64_t N, int64_t K, int accumulate, lq_stream_t stream) {
+    if (!dy || !x || !dw || !al16(dy) || !al16(x) || !al16(dw)) return LQ_EINVAL;
+    if (M < 0 || N <= 0 || K <= 0 || M >= (1 << 30) || N >= (1 << 30) || K >= (1 << 30) || (N % 8) != 0 || (K % 8) != 0) return LQ_EUNSUPPORTED;
+    if (M == 0) {
+        if (accumulate) return LQ_OK;
+        cudaError_t e = cudaMemsetAsync(dw, 0, (size_t)N * (size_t)K * 2, (cudaStream_t)stream);
+        if (e != cudaSuccess) { set_cuda_error(e, "cudaMemsetAsync"); return LQ_ECUDA; }
+        return LQ_OK;
+    }
+    { int rc_dev = ensure_device_for(dy); if (rc_dev) return rc_dev; }
+    const int tn = K > 128 ? 256 : (K > 64 ? 128 : 64);
+    GemmParams p{};
+    p.M = (int)K; p.R = (int)N; p.C = (int)M; p.wcols = (int)K; p.group = 0;
+    p.r_tiles = (int)((N + TILE_R - 1) / TILE_R); p.t_tiles = (int)((K + tn - 1) / tn); p.splits = 1;
+    p.kb_total = (int)((M + 63) / 64); p.kb_per_split = p.kb_total;
+    p.out = (__nv_bfloat16*)dw; p.alpha = 1.0f; p.accumulate = accumulate ? 1 : 0;
+    CUtensorMap mt, mw;
+    // both operands are read as [64 tokens] x [64 features] boxes (128-byte rows, 128B swizzle): MN-major MMA atoms
+    int rc = make_map(&mt, x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)M, (uint64_t)K, 64, 64, true);
+    if (rc) return rc;
+    rc = make_map(&mw, dy, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)M, (uint64_t)N, 64, 64, true);
+    if (rc) return rc;
+    cudaStream_t st = (cudaStream_t)stream;
+    switch (tn) {
+        case 64: return launch_tn<KIND_WGRAD, 64, 1>(mt, mw, p, st);
+        case 128: return launch_tn<KIND_WGRAD, 128, 1>(mt, mw, p, st);
+        default: return launch_tn<KIND_WGRAD, 256, 1>(mt, mw, p, st);
+    }
 }
 
 int lq_gemm_profile(int enable, unsigned long long* out16) {

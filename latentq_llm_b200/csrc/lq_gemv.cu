@@ -27,23 +27,11 @@ __device__ __forceinline__ void mma_16816(float (&d)[4], const uint32_t (&a)[4],
         : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
         : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
-// Programmatic dependent launch: a decode step is a chain of these launches.  A kernel lets its successor start
-// (launch_dependents) once its own weight loads are issued, and reads the tokens — the only operand the predecessor
-// may have produced — after pdl_wait(), which returns when the predecessor grid has completed and its writes are
-// visible.  The successor's launch latency and first weight-load latency then overlap this kernel's tail.  Both
-// are no-ops for a launch without the attribute; only kernels that call launch_dependents can be overtaken, and they
-// write nothing but their output.
-__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
-__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
-template <typename... KArgs, typename... Args>
-static void launch_pdl(void (*kern)(KArgs...), unsigned grid, unsigned block, size_t smem, cudaStream_t st, Args... args) {
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(grid); cfg.blockDim = dim3(block); cfg.dynamicSmemBytes = smem; cfg.stream = st;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = getenv("LQ_SKINNY_NO_PDL") ? 0 : 1;
-    cfg.attrs = attr; cfg.numAttrs = 1;
-    cudaLaunchKernelEx(&cfg, kern, KArgs(args)...);
+// silu(gate) * up on bf16 projection outputs, as the standalone kernel computes it
+__device__ __forceinline__ float silu_mul_bf16(float gate, float up, int hf_rounding) {
+    float s = gate / (1.0f + expf(-gate));
+    if (hf_rounding) s = bf16r(s);
+    return __fmul_rn(s, up);
 }
 
 // d = a * b (no accumulator input: starts a new group sum without clearing registers first)
@@ -226,8 +214,10 @@ __global__ void __launch_bounds__(RB_WARPS * 32, 2) k_skinny_rows(const SkinnyPa
     constexpr bool XPF = MT == 1;
     __shared__ float red[RB_WARPS][MT][128];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
-    const int row0 = blockIdx.x * 16;
-    const int ra = min(row0 + g, p.N - 1), rb = min(row0 + g + 8, p.N - 1);        // clamped loads, guarded stores
+    const bool pair = p.pair_stride > 0;
+    const int row0 = blockIdx.x * (pair ? 8 : 16);
+    const int ra = min(row0 + g, p.N - 1);                                          // clamped loads, guarded stores
+    const int rb = pair ? p.pair_stride + ra : min(row0 + g + 8, p.N - 1);
     const int gpr = p.K / (RB_CHUNK * GC);                                          // groups per weight row
     const int gper = (gpr + RB_WARPS - 1) / RB_WARPS;
     const int g_begin = min(gpr, warp * gper), n_groups = min(gpr, g_begin + gper) - g_begin;
@@ -344,8 +334,17 @@ __global__ void __launch_bounds__(RB_WARPS * 32, 2) k_skinny_rows(const SkinnyPa
     // D fragment: d0,d1 = (row g, tokens 2t, 2t+1); d2,d3 = (row g+8, same tokens)
     for (int j = threadIdx.x; j < MT * 128; j += RB_WARPS * 32) {
         const int m = j >> 7, idx = j & 127, ln = idx >> 2, i = idx & 3;
-        const int row = row0 + (ln >> 2) + ((i >= 2) ? 8 : 0);
         const int tok = m * 8 + 2 * (ln & 3) + (i & 1);
+        if (pair) {                                            // d0,d1 = gate[f], d2,d3 = up[f] of the same tokens
+            const int f = row0 + (ln >> 2);
+            if (i >= 2 || f >= p.N || tok >= p.M) continue;
+            float ag = 0.0f, au = 0.0f;
+#pragma unroll
+            for (int w = 0; w < RB_WARPS; ++w) { ag = __fadd_rn(ag, red[w][m][idx]); au = __fadd_rn(au, red[w][m][idx + 2]); }
+            p.out[(size_t)tok * p.N + f] = __float2bfloat16_rn(silu_mul_bf16(bf16r(ag), bf16r(au), p.hf_rounding));
+            continue;
+        }
+        const int row = row0 + (ln >> 2) + ((i >= 2) ? 8 : 0);
         if (row >= p.N || tok >= p.M) continue;
         float a = 0.0f;
 #pragma unroll
@@ -381,11 +380,15 @@ __global__ void __launch_bounds__(RB_WARPS * 32, 2) k_skinny_stream(const Skinny
     const int gper = (gpr + RB_WARPS - 1) / RB_WARPS;
     const int g_begin = min(gpr, warp * gper), n_groups = min(gpr, g_begin + gper) - g_begin;
     const int n_chunks = n_groups * GC;
-    const int n_blocks = (p.N + 15) / 16;
+    const bool pair = p.pair_stride > 0;
+    const int rows_per_blk = pair ? 8 : 16;
+    const int n_blocks = (p.N + rows_per_blk - 1) / rows_per_blk;
     int blk = blockIdx.x;                                  // grid <= n_blocks
     const unsigned short* sc_all = reinterpret_cast<const unsigned short*>(p.scales);
     const unsigned short* zp_all = reinterpret_cast<const unsigned short*>(p.zeros);
-    auto row_of = [&](int b, int half) { return min(b * 16 + g + half * 8, p.N - 1); };          // clamped loads, guarded stores
+    auto row_of = [&](int b, int half) {                                                           // clamped loads, guarded stores
+        return pair ? half * p.pair_stride + min(b * 8 + g, p.N - 1) : min(b * 16 + g + half * 8, p.N - 1);
+    };
     auto wptr = [&](int row) { return reinterpret_cast<const uint4*>(p.qweight + (size_t)row * (p.K / 2) + (size_t)g_begin * GC * (RB_CHUNK / 2)) + t; };
     auto load_sz = [&](int row, int grp) {
         const size_t i = (size_t)row * gpr + g_begin + grp;
@@ -510,8 +513,17 @@ __global__ void __launch_bounds__(RB_WARPS * 32, 2) k_skinny_stream(const Skinny
         // D fragment: d0,d1 = (row g, tokens 2t, 2t+1); d2,d3 = (row g+8, same tokens)
         for (int j = tid; j < MT * 128; j += RB_WARPS * 32) {
             const int m = j >> 7, idx = j & 127, ln = idx >> 2, i = idx & 3;
-            const int row = blk * 16 + (ln >> 2) + ((i >= 2) ? 8 : 0);
             const int tok = m * 8 + 2 * (ln & 3) + (i & 1);
+            if (pair) {                                        // d0,d1 = gate[f], d2,d3 = up[f] of the same tokens
+                const int f = blk * 8 + (ln >> 2);
+                if (i >= 2 || f >= p.N || tok >= p.M) continue;
+                float ag = 0.0f, au = 0.0f;
+#pragma unroll
+                for (int w = 0; w < RB_WARPS; ++w) { ag = __fadd_rn(ag, red[buf][w][m][idx]); au = __fadd_rn(au, red[buf][w][m][idx + 2]); }
+                p.out[(size_t)tok * p.N + f] = __float2bfloat16_rn(silu_mul_bf16(bf16r(ag), bf16r(au), p.hf_rounding));
+                continue;
+            }
+            const int row = blk * 16 + (ln >> 2) + ((i >= 2) ? 8 : 0);
             if (row >= p.N || tok >= p.M) continue;
             float a = 0.0f;
 #pragma unroll
@@ -544,7 +556,7 @@ static int launch_skinny_stream_v(const SkinnyParams& p, int x_stride, size_t sm
         if (e != cudaSuccess) { set_cuda_error(e, "cudaFuncSetAttribute(k_skinny_stream)"); return LQ_ECUDA; }
         attr_done[dev] = true;
     }
-    launch_pdl(k_skinny_stream<MT, GC>, grid, RB_WARPS * 32, smem, st, p, x_stride);
+    launch_pdl(k_skinny_stream<MT, GC>, dim3(grid), RB_WARPS * 32, smem, st, p, x_stride);
     return check_launch("k_skinny_stream");
 }
 
@@ -558,7 +570,8 @@ static int launch_skinny_stream(const SkinnyParams& p, cudaStream_t st) {
     const int mt = p.M <= 8 ? 1 : 2, gc = p.group / RB_CHUNK;
     const int x_stride = skinny_x_stride(p.K);
     const size_t smem = skinny_stream_smem(p.M, p.K, p.group);
-    const int n_blocks = (p.N + 15) / 16;
+    const int rpb = p.pair_stride > 0 ? 8 : 16;
+    const int n_blocks = (p.N + rpb - 1) / rpb;
     const unsigned grid = (unsigned)std::min(n_blocks, 2 * sm_count());
     if (mt == 1) return gc == 1 ? launch_skinny_stream_v<1, 1>(p, x_stride, smem, grid, st) : launch_skinny_stream_v<1, 2>(p, x_stride, smem, grid, st);
     return gc == 1 ? launch_skinny_stream_v<2, 1>(p, x_stride, smem, grid, st) : launch_skinny_stream_v<2, 2>(p, x_stride, smem, grid, st);
@@ -572,10 +585,11 @@ int launch_skinny_rows(const SkinnyParams& p, cudaStream_t st) {
     if ((p.M <= 2 || getenv("LQ_SKINNY_STREAM_ALL")) && skinny_stream_supported(p.K, p.group) &&
         skinny_stream_smem(p.M, p.K, p.group) <= 96 * 1024)
         return launch_skinny_stream(p, st);
-    const unsigned grid = (unsigned)((p.N + 15) / 16);
+    const int rpb = p.pair_stride > 0 ? 8 : 16;
+    const unsigned grid = (unsigned)((p.N + rpb - 1) / rpb);
     const bool g128 = p.group == 128;
-    if (p.M <= 8) { if (g128) launch_pdl(k_skinny_rows<1, 1>, grid, RB_WARPS * 32, 0, st, p); else launch_pdl(k_skinny_rows<1, 2>, grid, RB_WARPS * 32, 0, st, p); }
-    else { if (g128) launch_pdl(k_skinny_rows<2, 1>, grid, RB_WARPS * 32, 0, st, p); else launch_pdl(k_skinny_rows<2, 2>, grid, RB_WARPS * 32, 0, st, p); }
+    if (p.M <= 8) { if (g128) launch_pdl(k_skinny_rows<1, 1>, dim3(grid), RB_WARPS * 32, 0, st, p); else launch_pdl(k_skinny_rows<1, 2>, dim3(grid), RB_WARPS * 32, 0, st, p); }
+    else { if (g128) launch_pdl(k_skinny_rows<2, 1>, dim3(grid), RB_WARPS * 32, 0, st, p); else launch_pdl(k_skinny_rows<2, 2>, dim3(grid), RB_WARPS * 32, 0, st, p); }
     return check_launch("k_skinny_rows");
 }
 

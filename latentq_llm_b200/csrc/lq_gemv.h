@@ -15,6 +15,11 @@ struct SkinnyParams {
     __nv_bfloat16* out;            // [M, N]
     float* partial;                // [splits][M][N] when splits > 1
     int M, N, K, group, splits, chunks_per_split;
+    // Paired rows (fused gate | up projection, row-block kernels only): pair_stride > 0 makes fragment rows 0..7 of a
+    // block the weight rows f..f+7 and fragment rows 8..15 the rows pair_stride + f.., so that one thread holds
+    // gate[f] and up[f] of a token; the output is act[M, N] = silu(gate) * up with N = pair_stride features.
+    int pair_stride;
+    int hf_rounding;               // pair epilogue: round silu(gate) to bf16 before the product (eager-module chain)
 };
 
 // split-K plan of the skinny kernel: returns 64-k chunks per split and writes the number of splits

@@ -24,6 +24,8 @@ int check_launch(const char* where) {
     if (e != cudaSuccess) { set_cuda_error(e, where); return LQ_ECUDA; }
     return LQ_OK;
 }
+static int g_decode_chain = 0;
+bool decode_chain_enabled() { return g_decode_chain != 0 && !getenv("LQ_SKINNY_NO_PDL"); }
 int sm_count() {
     static int cached[64];
     int dev = 0;
@@ -1030,6 +1032,12 @@ __global__ void __launch_bounds__(256) k_philox_dither(uint64_t seed, uint64_t s
 using namespace lq;
 
 extern "C" {
+
+int lq_decode_chain(int enable) {
+    const int old = lq::g_decode_chain;
+    lq::g_decode_chain = enable ? 1 : 0;
+    return old;
+}
 
 int lq_version(void) { return 100; }
 const char* lq_status_string(int s) {

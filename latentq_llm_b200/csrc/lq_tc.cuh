@@ -127,9 +127,9 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr, uint32_t lbo_
     return d;
 }
 // Instruction descriptor: D format (bits 4-5), A/B formats (7-9 / 10-12), A/B major (15 / 16), N>>3 (17-22), M>>4 (24-28).
-__host__ __device__ constexpr uint32_t make_idesc(bool i8, bool a_mn_major, int n) {
-    return (i8 ? 2u : 1u) << 4 | 1u << 7 | 1u << 10 | (a_mn_major ? 1u : 0u) << 15 | (uint32_t)(n >> 3) << 17 |
-           (uint32_t)(TILE_R >> 4) << 24;
+__host__ __device__ constexpr uint32_t make_idesc(bool i8, bool a_mn_major, int n, bool b_mn_major = false) {
+    return (i8 ? 2u : 1u) << 4 | 1u << 7 | 1u << 10 | (a_mn_major ? 1u : 0u) << 15 | (b_mn_major ? 1u : 0u) << 16 |
+           (uint32_t)(n >> 3) << 17 | (uint32_t)(TILE_R >> 4) << 24;
 }
 
 }  // namespace lq

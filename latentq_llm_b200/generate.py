@@ -31,7 +31,9 @@ class GraphedGreedyDecoder:
         self.graph = None
 
     def _step(self):
-        out = self.model(input_ids=self.tok, past_key_values=self.cache, cache_position=self.pos, use_cache=True)
+        from . import ops
+        with ops.decode_chain():          # the decode-sized GEMMs may fetch their (constant) weights while their predecessor runs
+            out = self.model(input_ids=self.tok, past_key_values=self.cache, cache_position=self.pos, use_cache=True)
         self.tok.copy_(out.logits[:, -1:].argmax(-1))
         self.pos.add_(1)
 
@@ -87,7 +89,8 @@ class FusedLlamaGreedyDecoder:
                     residual add + RMSNorm -> fused gate|up projection (N = 2 I) -> silu(gate) * up -> down projection
         then        residual add + final RMSNorm -> lm_head -> argmax -> embedding of the new token
 
-    nine launches per layer (the reference's fusion list: PTQ/quant/fused_attn.py:164-204 fused QKV, :8-58 RoPE,
+    eight launches per layer at decode-sized batches, where silu(gate) * up is the epilogue of the gate|up launch, nine
+    otherwise (the reference's fusion list: PTQ/quant/fused_attn.py:164-204 fused QKV, :8-58 RoPE,
     PTQ/quant/fused_mlp.py:84-168 gate/up with the silu epilogue, PTQ/quant/triton_norm.py:7-39 RMSNorm), captured
     once as a CUDA graph and replayed per token.  The prompt is prefilled through the model's own modules into the
     same static KV cache.  `hf_rounding=True` rounds intermediates like the eager modules' bf16 tensor ops."""
@@ -135,6 +138,10 @@ class FusedLlamaGreedyDecoder:
 
     def _step(self):
         from . import ops
+        with ops.decode_chain():          # launches may start while their predecessor runs (weights are constant here)
+            self._step_kernels(ops)
+
+    def _step_kernels(self, ops):
         D, I, Hq, Hkv, hd = self.D, self.I, self.Hq, self.Hkv, self.hd
         torch.index_select(self.model.model.embed_tokens.weight, 0, self.tok, out=self.h)
         delta = None
@@ -146,8 +153,7 @@ class FusedLlamaGreedyDecoder:
             ops.decode_attention(self.qkv, self.pos, kc, vc, Hq, Hkv, hd, out=self.att)
             ops.gemm_a16w4_fwd(self.att, *L["o"], None, D, Hq * hd, out=self.tmp)
             ops.add_rmsnorm(self.h, self.tmp, L["ln2"], self.eps, out=self.xn, hf_rounding=self.hf)
-            ops.gemm_a16w4_fwd(self.xn, *L["gu"], None, 2 * I, D, out=self.gu)
-            ops.silu_mul(self.gu, out=self.act, hf_rounding=self.hf)
+            ops.gemm_a16w4_fwd_silu(self.xn, *L["gu"], I, D, out=self.act, gate_up=self.gu, hf_rounding=self.hf)
             ops.gemm_a16w4_fwd(self.act, *L["down"], None, D, I, out=self.tmp)
             delta = self.tmp
         ops.add_rmsnorm(self.h, delta, self.model.model.norm.weight.detach(), self.eps, out=self.xn, hf_rounding=self.hf)

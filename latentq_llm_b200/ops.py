@@ -363,6 +363,23 @@ def gemm_a16w4_dgrad(dy, qweight, scales, zeros, N, K, group=128, out=None):
     return dx
 
 
+def gemm_wgrad(dy, x, dw=None, accumulate=False):
+    """dw[N, K] (+)= dy[M, N]^T · x[M, K] (utils/quant.py:141-142): the weight gradient of a quantized linear, written
+    (or accumulated, one rounding of the fp32 sum) straight into `dw`, e.g. a view of the gradient arena."""
+    _chk(dy, "dy", torch.bfloat16); _chk(x, "x", torch.bfloat16)
+    M, N = dy.shape
+    K = x.shape[1]
+    assert x.shape[0] == M
+    if dw is None:
+        assert not accumulate
+        dw = torch.empty((N, K), dtype=torch.bfloat16, device=dy.device)
+    else:
+        _chk(dw, "dw", torch.bfloat16)
+        assert tuple(dw.shape) == (N, K)
+    L.call("lq_gemm_wgrad", _ptr(dy), _ptr(x), _ptr(dw), M, N, K, int(accumulate), _stream())
+    return dw
+
+
 def gemm_a8w8(x8, w8, row_scale=None, col_scale=None, alpha=1.0, bias=None, want_acc=False):
     _chk(x8, "x8", torch.int8); _chk(w8, "w8", torch.int8)
     M, K = x8.shape
@@ -379,6 +396,21 @@ def gemm_a8w8(x8, w8, row_scale=None, col_scale=None, alpha=1.0, bias=None, want
     L.call("lq_gemm_a8w8", _ptr(x8), _ptr(w8), _ptr(row_scale), _ptr(col_scale), float(alpha), _ptr(bias), _ptr(y), _ptr(acc),
            M, N, K, _ptr(ws), nb, _stream())
     return (y, acc) if want_acc else y
+
+
+class decode_chain:
+    """Context manager: launches inside it form a decode chain (every kernel consumes its predecessor's output, the
+    weights are constant), so the decode kernels may be started while their predecessor is still running; they read what
+    the predecessor wrote only after it has completed.  Outside such a block a forward right after an optimizer step is
+    safe: nothing is read early."""
+
+    def __enter__(self):
+        self.old = L.lib.lq_decode_chain(1)
+        return self
+
+    def __exit__(self, *exc):
+        L.lib.lq_decode_chain(self.old)
+        return False
 
 
 # ---- decode-side operations of a Llama-architecture layer ------------------------------------------
@@ -415,10 +447,12 @@ def decode_attention(qkv, positions, k_cache, v_cache, Hq, Hkv, hd, scale=None, 
     B, max_len = qkv.shape[0], k_cache.shape[2]
     y = out if out is not None else torch.empty((B, Hq * hd), dtype=torch.bfloat16, device=qkv.device)
     need = int(L.lib.lq_decode_attention_workspace_bytes(B, Hq, hd, max_len))
-    key = (qkv.device.index, torch.cuda.current_stream().cuda_stream)
+    # one workspace per shape and stream: the ticket counters sit behind the partial results, at an offset that depends on
+    # the shape, and must be zero when a call starts (every call leaves them zero)
+    key = (qkv.device.index, torch.cuda.current_stream().cuda_stream, B, Hq, hd, max_len)
     ws = _attn_ws.get(key)
-    if ws is None or ws.numel() < need:
-        ws = _attn_ws[key] = torch.zeros(max(need, 1), dtype=torch.uint8, device=qkv.device)   # ticket counters start at zero
+    if ws is None:
+        ws = _attn_ws[key] = torch.zeros(max(need, 1), dtype=torch.uint8, device=qkv.device)
     L.call("lq_decode_attention", _ptr(qkv), qkv.stride(0), _ptr(k_cache), _ptr(v_cache), _ptr(positions), _ptr(y), B, Hq, Hkv,
            hd, max_len, float(scale if scale is not None else hd ** -0.5), _ptr(ws), ws.numel(), _stream())
     return y
@@ -449,3 +483,21 @@ def gradq_dequant(qdata, scale, out=None):
     y = out if out is not None else torch.empty((rows, cols), dtype=scale.dtype, device=qdata.device)
     L.call("lq_gradq_dequant", _ptr(qdata), _ptr(scale), _dt(scale), rows, cols, _ptr(y), _stream())
     return y
+
+
+def gemm_a16w4_fwd_silu(x, qweight, scales, zeros, I, K, group=128, out=None, gate_up=None, hf_rounding=True):
+    """act[M, I] = silu(x·Wgate^T) * (x·Wup^T) for a fused gate | up weight of 2*I rows (PTQ/quant/fused_mlp.py:84-168).
+    Decode-sized token counts take ONE launch (the epilogue of the decode GEMM); larger ones run the GEMM into `gate_up`
+    [M, 2I] (allocated if not given) and `silu_mul`."""
+    _chk(x, "x", torch.bfloat16); _chk(qweight, "qweight", torch.int8)
+    M = x.shape[0]
+    y = out if out is not None else torch.empty((M, I), dtype=torch.bfloat16, device=x.device)
+    if M <= 16 and K % 256 == 0 and group in (128, 256) and I % 8 == 0:
+        rc = L.lib.lq_gemm_a16w4_fwd_silu(_ptr(x), _ptr(qweight), _ptr(scales), _ptr(zeros), _ptr(y), M, I, K, group,
+                                          int(hf_rounding), _stream())
+        if rc != L.LQ_EUNSUPPORTED:
+            L.check("lq_gemm_a16w4_fwd_silu", rc)
+            return y
+    gu = gate_up if gate_up is not None else torch.empty((M, 2 * I), dtype=torch.bfloat16, device=x.device)
+    gemm_a16w4_fwd(x, qweight, scales, zeros, None, 2 * I, K, group, out=gu)
+    return silu_mul(gu, out=y, hf_rounding=hf_rounding)

@@ -12,6 +12,7 @@ Citations are `path:line` inside FWkey/latentQ_LLM.
 from __future__ import annotations
 
 import math
+import os
 from typing import Optional, Union
 
 import torch
@@ -160,11 +161,20 @@ class QLinearFunctionW4(torch.autograd.Function):
         return grad_input, None, None, grad_bias
 
 
+# The hook-free route's weight gradient dY^T·X is a plain dense bf16 GEMM with beta = 1.  Default: the library GEMM
+# (`addmm_`).  LQ_WGRAD_TCGEN05=1 (read at import) selects this package's tcgen05 kernel `ops.gemm_wgrad` instead: same
+# single rounding of the fp32 sum, measured at 0.65-0.85 of the library's rate on the fine-tune shapes (one-CTA 128 x 256
+# tiles keep the shared-memory port busy with 12 KB of operand reads per MMA on top of the TMA writes; the library pairs
+# CTAs on 256 x 256 tiles).
+_WGRAD_TCGEN05 = bool(os.environ.get("LQ_WGRAD_TCGEN05"))
+
+
 class QLinearFunctionW4Direct(torch.autograd.Function):
     """Hook-free variant of QLinearFunctionW4 for this package's own trainer: same forward and grad-input, but the
     weight gradient dY^T·x is accumulated straight into `qtensor.grad` (a view of the data-parallel gradient arena)
-    with one fused GEMM (beta = 1) instead of travelling through `dict_temp` and a module backward hook
-    (utils/quant.py:141-142, 398-411).  No [N, K] temporary, no extra add pass, no hook overhead."""
+    by one GEMM with beta = 1 (the library's, or `ops.gemm_wgrad`: tcgen05, both operands MN-major straight from their
+    row-major tensors; both round the fp32 sum once into the arena) instead of travelling through `dict_temp` and a module
+    backward hook (utils/quant.py:141-142, 398-411).  No [N, K] temporary, no extra add pass, no hook overhead."""
 
     @staticmethod
     def forward(ctx, input, weight_d, scales, zeros, bias, qtensor, N, K):
@@ -180,10 +190,16 @@ class QLinearFunctionW4Direct(torch.autograd.Function):
         if ctx.needs_input_grad[0]:
             grad_input = ops.gemm_a16w4_dgrad(grad_output, weight_d, scales, zeros, ctx.N, ctx.K, GROUPSIZE)
         q = ctx.qtensor
-        if q.grad is None:
-            q.grad = grad_output.t().mm(input)
+        x2 = input if input.is_contiguous() else input.contiguous()
+        if not _WGRAD_TCGEN05 or ctx.N % 8 or ctx.K % 8:
+            if q.grad is None:
+                q.grad = grad_output.t().mm(x2)
+            else:
+                q.grad.addmm_(grad_output.t(), x2)
+        elif q.grad is None:
+            q.grad = ops.gemm_wgrad(grad_output, x2)
         else:
-            q.grad.addmm_(grad_output.t(), input)
+            ops.gemm_wgrad(grad_output, x2, q.grad, accumulate=True)
         return grad_input, None, None, None, None, None, None, None
 
 

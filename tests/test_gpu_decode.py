@@ -92,3 +92,26 @@ def test_silu_mul(ops, hf):
     gu = orc.bf16_round((rng.standard_normal((7, 2 * 11008)) * 2).astype(np.float32))
     got = ops.silu_mul(_bf(gu), hf_rounding=hf).float().cpu().numpy()
     _close(got, orc.silu_mul(gu, hf_rounding=hf))
+
+
+@pytest.mark.parametrize("hf", [True, False])
+@pytest.mark.parametrize("M,I,K", [(1, 1024, 4096), (2, 544, 4096), (8, 1024, 1024), (16, 288, 2048), (48, 512, 1024)])
+def test_fused_gate_up_silu(ops, M, I, K, hf):
+    """silu(x·Wgate^T) * (x·Wup^T) from the fused 2I-row weight: one launch at decode sizes (streaming kernel for one
+    or two tokens, row-block kernel up to 16), GEMM + silu*up beyond; against the oracle's dequantize-matmul-silu chain
+    within two bf16 ulps of the largest magnitude."""
+    rng = np.random.default_rng(M + I)
+    w = orc.bf16_round((rng.standard_normal((2 * I, K)) * 0.02).astype(np.float32))
+    s, z = orc.find_qparams(w, 128, 15, False)
+    s, z = orc.bf16_round(s), orc.bf16_round(z)
+    codes, _, _ = orc.a16w4_requant(s, z, w=w, codec=orc.CODEC_NONE, math_bf16=True)
+    x = orc.bf16_round(rng.standard_normal((M, K)).astype(np.float32))
+    got = ops.gemm_a16w4_fwd_silu(_bf(x), torch.from_numpy(codes).cuda(), _bf(s), _bf(z), I, K, hf_rounding=hf).float().cpu().numpy()
+    gu = orc.gemm_a16w4(x, codes, s, z, 2 * I, K)
+    want = orc.silu_mul(gu, hf_rounding=hf)
+    # (both projections are rounded to bf16 before silu and the product: an ulp in either moves the product by up to two)
+    assert np.abs(got - want).max() <= 2.0 ** -6 * np.abs(want).max()
+    # and exactly what the two separate launches give (same GEMM kernels, same rounding points)
+    sep = ops.silu_mul(ops.gemm_a16w4_fwd(_bf(x), torch.from_numpy(codes).cuda(), _bf(s), _bf(z), None, 2 * I, K), hf_rounding=hf)
+    if M <= 16:
+        assert np.array_equal(got, sep.float().cpu().numpy())

@@ -179,14 +179,34 @@ def test_a16w4_decode_chain_of_dependent_launches(ops, monkeypatch, M):
             monkeypatch.delenv("LQ_SKINNY_NO_PDL", raising=False)
         bufs = [torch.empty(M, N, device="cuda", dtype=torch.bfloat16) for _ in range(2)]
         x = x0
-        for it in range(30):                                    # 30 dependent launches, ping-pong buffers
-            codes, sb, zb = layers[it % 3]
-            y = ops.gemm_a16w4_fwd(x, codes, sb, zb, None, N, K, out=bufs[it % 2])
-            x = y
+        with ops.decode_chain():                                # the early start is only ever on inside a decode chain
+            for it in range(30):                                # 30 dependent launches, ping-pong buffers
+                codes, sb, zb = layers[it % 3]
+                y = ops.gemm_a16w4_fwd(x, codes, sb, zb, None, N, K, out=bufs[it % 2])
+                x = y
         torch.cuda.synchronize()
         outs[mode] = x.clone()
     assert torch.isfinite(outs["pdl"].float()).all()
     assert torch.equal(outs["pdl"], outs["plain"])
+
+
+def test_decode_forward_right_after_a_requantize_reads_the_new_weights(ops):
+    """Outside a decode chain nothing is fetched early: a decode-sized forward launched directly behind the kernel that
+    rewrote its weights (an optimizer step) sees the new codes, with no synchronisation in between."""
+    N = K = 2048
+    codes, sb, zb = make_w4_layer(ops, N, K, seed=77)
+    words = torch.zeros(N * K // 8, dtype=torch.int32, device="cuda")
+    g = torch.Generator(device="cuda").manual_seed(3)
+    x = torch.randn(1, K, device="cuda", generator=g).to(torch.bfloat16)
+    delta = (torch.randn(N * K, device="cuda", generator=g) * 0.02).to(torch.bfloat16)
+    o = ops.make_opts(codec=ops.CODEC_THREEFOLD, dither=ops.DITHER_HASH, has_residual=False)
+    torch.cuda.synchronize()
+    for _ in range(5):
+        ops.a16w4_fold_delta(codes, words, delta, sb, zb, o)          # rewrites the codes ...
+        y = ops.gemm_a16w4_fwd(x, codes, sb, zb, None, N, K)          # ... read by the very next launch
+        torch.cuda.synchronize()
+        assert torch.equal(y, ops.gemm_a16w4_fwd(x, codes, sb, zb, None, N, K))
+        o = ops.make_opts(codec=ops.CODEC_THREEFOLD, dither=ops.DITHER_HASH, has_residual=True)
 
 
 def _a8_inputs(M, N, K, seed):
@@ -236,3 +256,47 @@ def test_a8w8_opt_shapes(ops, M, K, N):
     colsum = w8.to(torch.int64).sum(0)
     want = (x8.to(torch.int64) * colsum[None, :]).sum(1)
     assert torch.equal(acc.to(torch.int64).sum(1), want)
+
+
+@pytest.mark.parametrize("K,N", [(2048, 2048), (2048, 8192), (8192, 2048)])
+def test_a8w8_full_forward_opt_shapes_m2048(ops, K, N):
+    """The whole A8W8 forward at benchmark size (M = 4x512 tokens, OPT-1.3B shapes): activations ~N(0,1) with 1 % of the
+    channels scaled x20, per-token activation quantizer on the GPU, int8 GEMM with per-token and per-channel scales and
+    bias in its epilogue.  Quantized activations and scales against the oracle bit for bit; the bf16 output against the
+    oracle's epilogue applied to exact integer accumulators (computed on the device in fp64), bit for bit."""
+    M = 2048
+    x, w8, w_scale, bias = _a8_inputs(M, N, K, seed=K + N)
+    xb = torch.from_numpy(x).cuda().to(torch.bfloat16)
+    x8, a_scale = ops.act_quant_per_token(xb)
+    q_o, s_o = orc.act_quant_per_token(xb.float().cpu().numpy(), math_bf16=True)
+    assert np.array_equal(x8.cpu().numpy(), q_o) and np.array_equal(a_scale.cpu().numpy(), s_o)
+    w8d = torch.from_numpy(w8).cuda()
+    y = ops.gemm_a8w8(x8, w8d, a_scale, torch.from_numpy(w_scale).cuda(), 1.0, torch.from_numpy(bias).cuda().to(torch.bfloat16))
+    acc = (x8.double() @ w8d.double().t()).to(torch.int64).cpu().numpy().astype(np.int32)      # exact: |acc| < 2^31
+    y_o = orc.gemm_i8_epilogue_fused(acc, s_o, w_scale, bias)
+    assert np.array_equal(y.float().cpu().numpy(), y_o)
+    ref = xb.float().cpu().numpy() @ (w8.astype(np.float32) * w_scale[:, None]).T + bias
+    _, e_fro = rel_err(y.float().cpu(), torch.from_numpy(ref))
+    assert e_fro < 6e-2, e_fro              # the int8 quantization error of the product itself
+
+
+@pytest.mark.parametrize("M,N,K", [(2048, 2048, 2048), (300, 320, 192), (64, 128, 64), (4096, 1024, 8192), (1000, 136, 264)])
+def test_wgrad_gemm_vs_fp32_matmul(ops, M, N, K):
+    """dw (+)= dy^T x on tcgen05 with both operands MN-major: against an fp32 matmul, written and accumulated (one
+    rounding of fp32(dw) + product, like a GEMM with beta = 1), on full tiles and ragged edges."""
+    g = torch.Generator(device="cuda").manual_seed(M + N + K)
+    dy = torch.randn(M, N, device="cuda", generator=g).to(torch.bfloat16)
+    x = torch.randn(M, K, device="cuda", generator=g).to(torch.bfloat16)
+    prod = dy.float().t() @ x.float()
+    dw = ops.gemm_wgrad(dy, x)
+    e_max, e_fro = rel_err(dw, prod)
+    assert e_max < RTOL and e_fro < RTOL, (e_max, e_fro)
+    old = (torch.randn(N, K, device="cuda", generator=g) * prod.abs().mean()).to(torch.bfloat16)
+    acc = old.clone()
+    ops.gemm_wgrad(dy, x, acc, accumulate=True)
+    want = (old.float() + prod).to(torch.bfloat16)
+    e_max, e_fro = rel_err(acc, want.float())
+    assert e_max < RTOL and e_fro < RTOL, (e_max, e_fro)
+    assert float((acc == want).float().mean()) > 0.9                 # same single rounding: only the fp32 sum order differs
+    # linearity: doubling dy doubles the product exactly
+    assert torch.equal(ops.gemm_wgrad(dy * 2, x), dw * 2)

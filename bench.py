@@ -200,9 +200,16 @@ def extra_measurements(torch, ops, pk, only=None, numel=1 << 30):
         _a8w8_part(torch, ops, out, tm, g)
     if only in (None, "decode"):
         _decode_part(torch, ops, pk, out, tm)
+    if only == "mma_probe":
+        out["mma_issue_rate"] = mma_probe_sweep(torch)
+    if only in (None, "wgrad"):
+        _wgrad_part(torch, ops, pk, out, tm, g)
     if only == "decode_step":
-        _decode_step_part(torch, out, layers=numel if numel <= 64 else 4)
+        _decode_step_part(torch, out, layers=DECODE_STEP_ARGS["layers"], batch=DECODE_STEP_ARGS["batch"])
     return out
+
+
+DECODE_STEP_ARGS = {"layers": 4, "batch": 1}
 
 
 def _decode_step_part(torch, out, layers=4, batch=1, prompt_len=512):
@@ -352,6 +359,28 @@ def mma_peaks(torch):
     return res
 
 
+def mma_probe_sweep(torch):
+    """Cycles per tcgen05.mma and T(FL)OP/s over token-tile widths and numbers of independent accumulators."""
+    import ctypes
+    from latentq_llm_b200 import _lib
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    rows = []
+    for name, kind, ta, kk in (("bf16_smem_a", 0, 0, 16), ("bf16_tmem_a", 0, 1, 16), ("int8_smem_a", _lib.GEMM_A8W8, 0, 32)):
+        for n in (32, 64, 128, 256):
+            for n_acc in (1, 2, 4, 8):
+                if n_acc * n > 256:
+                    continue
+                cyc = ctypes.c_ulonglong(0)
+                assert _lib.lib.lq_mma_issue_rate(kind, ta, n, n_acc, 8192, sms, ctypes.byref(cyc), None) == 0
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                _lib.lib.lq_mma_issue_rate(kind, ta, n, n_acc, 8192, sms, None, None)
+                e1.record(); torch.cuda.synchronize()
+                rows.append({"kind": name, "N": n, "accumulators": n_acc, "cycles_per_mma": round(cyc.value / 8192, 1),
+                             "T(FL)OP/s": round(2.0 * 128 * n * kk * 8192 * sms / (e0.elapsed_time(e1) * 1e-3) / 1e12, 1)})
+    return rows
+
+
 def _a8w8_part(torch, ops, out, tm, g):
     # int8 GEMM on the OPT-1.3B shapes at M = 4x512 and 32x512 tokens, the whole A8W8 forward: per-token activation
     # quantizer, then the GEMM with per-token and per-channel scales and bias in its epilogue (bf16 out).  Activations
@@ -359,7 +388,7 @@ def _a8w8_part(torch, ops, out, tm, g):
     pkm = mma_peaks(torch)
     out["tensor_peaks_mma_probe"] = pkm
     for m in (2048, 16384):
-        tot_ops, tot_ms, tot_q = 0.0, 0.0, 0.0
+        tot_ops, tot_ms, tot_q, per_shape = 0.0, 0.0, 0.0, {}
         for (k, n) in [(2048, 2048), (2048, 8192), (8192, 2048)]:
             x = torch.randn(m, k, device="cuda", generator=g)
             x[:, torch.randperm(k, device="cuda", generator=g)[:max(1, k // 100)]] *= 20.0
@@ -371,9 +400,31 @@ def _a8w8_part(torch, ops, out, tm, g):
             ms = tm(lambda: ops.gemm_a8w8(x8, w8, rs, cs, 1.0, bias), reps=10, warm=3, graph=True)
             tot_q += tm(lambda: ops.act_quant_per_token(x), reps=10, warm=3, graph=True)
             tot_ops += 2.0 * m * n * k; tot_ms += ms
+            per_shape[f"{k}x{n}"] = round(2.0 * m * n * k / ms / 1e9, 1)
         tops = tot_ops / tot_ms / 1e9
         out[f"a8w8_opt_m{m}"] = {"TOP/s": round(tops, 1), "ms": round(tot_ms, 3), "frac_int8_measured": round(tops / pkm["int8_tops_measured"], 3),
-                                 "act_quant_ms": round(tot_q, 3), "TOP/s_with_act_quant": round(tot_ops / (tot_ms + tot_q) / 1e9, 1)}
+                                 "act_quant_ms": round(tot_q, 3), "TOP/s_with_act_quant": round(tot_ops / (tot_ms + tot_q) / 1e9, 1),
+                                 "TOP/s_per_shape_KxN": per_shape}
+
+
+def _wgrad_part(torch, ops, pk, out, tm, g):
+    """Weight gradient dW += dY^T·X of the fine-tune step (OPT-1.3B at 2048 tokens, Llama-2-7B at 4096): this package's
+    tcgen05 kernel against the library GEMM with beta = 1 that the trainer uses by default."""
+    rows = {}
+    for (m, n, k) in [(2048, 2048, 2048), (2048, 8192, 2048), (2048, 2048, 8192), (4096, 4096, 4096), (4096, 11008, 4096), (4096, 4096, 11008)]:
+        dy = torch.randn(m, n, device="cuda", generator=g).to(torch.bfloat16)
+        x = torch.randn(m, k, device="cuda", generator=g).to(torch.bfloat16)
+        dw = torch.zeros(n, k, device="cuda", dtype=torch.bfloat16)
+        t_own = tm(lambda: ops.gemm_wgrad(dy, x, dw, accumulate=True), reps=10, warm=2)
+        t_lib = tm(lambda: dw.addmm_(dy.t(), x), reps=10, warm=2)
+        fl = 2.0 * m * n * k
+        rows[f"M{m}_N{n}_K{k}"] = {"tcgen05_TFLOP/s": round(fl / t_own / 1e9, 1), "library_TFLOP/s": round(fl / t_lib / 1e9, 1),
+                                   "frac_burst": round(fl / t_own / 1e9 / pk["bf16"], 3)}
+        del dy, x, dw
+    out["wgrad"] = rows
+
+
+DECODE_M_LIST = (1, 8, 16, 64, 128, 512, 4096)
 
 
 def _decode_part(torch, ops, pk, out, tm):
@@ -381,7 +432,7 @@ def _decode_part(torch, ops, pk, out, tm):
     # One pass over the four layers is captured in a CUDA graph and replayed, as a decode loop would do: at these
     # sizes a launch from Python costs more than the kernel runs.
     layers = build_layers(torch, ops)
-    for m in (1, 8, 16, 64, 128, 512, 4096):
+    for m in DECODE_M_LIST:
         xs = [L["x"][:m].contiguous() for L in layers]
         ys = [torch.empty(m, L["N"], device="cuda", dtype=torch.bfloat16) for L in layers]
 
@@ -730,15 +781,22 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-extra", action="store_true", help="skip the secondary measurements and the CPU baseline")
-    ap.add_argument("--only", default="", choices=["", "requant", "sweep", "stream", "a8w8", "decode", "decode_step"],
+    ap.add_argument("--only", default="", choices=["", "requant", "sweep", "stream", "a8w8", "decode", "decode_step", "wgrad", "mma_probe"],
                     help="run one family of the secondary measurements only (profiling a single kernel)")
-    ap.add_argument("--numel", type=int, default=1 << 30, help="weights in the requantize measurement (decode_step: layers)")
+    ap.add_argument("--numel", type=int, default=1 << 30, help="weights in the requantize measurement")
+    ap.add_argument("--layers", type=int, default=4, help="--only decode_step: decoder layers of the 7B architecture to build")
+    ap.add_argument("--batch", type=int, default=1, help="--only decode_step: sequences decoded together")
+    ap.add_argument("--m", default="", help="--only decode: comma-separated token counts instead of the whole sweep")
     ap.add_argument("--shapes", default="", help="comma-separated indices into the shape list (profiling a smaller case)")
     args = ap.parse_args()
     if args.shapes:
         global LLAMA_SHAPES, WORKLOAD
         LLAMA_SHAPES = [LLAMA_SHAPES[int(i)] for i in args.shapes.split(",")]
         WORKLOAD += f" [subset {LLAMA_SHAPES}]"
+    DECODE_STEP_ARGS.update(layers=args.layers, batch=args.batch)
+    if args.m:
+        global DECODE_M_LIST
+        DECODE_M_LIST = tuple(int(v) for v in args.m.split(","))
     if args.only:
         import torch
         from latentq_llm_b200 import ops

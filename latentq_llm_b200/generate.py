@@ -143,7 +143,7 @@ class FusedLlamaGreedyDecoder:
 
     def _step_kernels(self, ops):
         D, I, Hq, Hkv, hd = self.D, self.I, self.Hq, self.Hkv, self.hd
-        torch.index_select(self.model.model.embed_tokens.weight, 0, self.tok, out=self.h)
+        self.h.copy_(torch.nn.functional.embedding(self.tok, self.model.model.embed_tokens.weight))
         delta = None
         for li, L in enumerate(self.layers):
             kc, vc = self.cache.layers[li].keys, self.cache.layers[li].values

@@ -69,9 +69,12 @@ def test_a16w4_module_forward_backward_and_hook(Q):
     assert float((layer.weight.grad.float() - 2 * gw_ref).abs().max() / gw_ref.abs().max()) < 4e-2
 
 
-def test_a16w4_direct_grad_matches_hook_route(Q):
+@pytest.mark.parametrize("wgrad", ["library", "tcgen05"])
+def test_a16w4_direct_grad_matches_hook_route(Q, monkeypatch, wgrad):
     """The hook-free route accumulates the same dY^T·x into weight.grad (here: a preallocated arena-style view) and
-    returns the same grad-input as the reference's dict_temp + backward-hook route."""
+    returns the same grad-input as the reference's dict_temp + backward-hook route, with the library GEMM and with
+    this package's tcgen05 weight-gradient kernel."""
+    monkeypatch.setattr(Q, "_WGRAD_TCGEN05", wgrad == "tcgen05")
     N, K, T = 256, 384, 96
     hook_layer, _ = _make_a16w4(Q, N, K, seed=3)
     direct_layer, _ = _make_a16w4(Q, N, K, seed=3)

@@ -35,7 +35,10 @@ constexpr int ROW_BYTES = 128;        // one swizzle row
 constexpr int A_TILE_BYTES = TILE_R * ROW_BYTES;
 constexpr int RAW_BYTES = 4096;       // packed int4 bytes per stage (128 rows x 64 k, or 64 rows x 128 k)
 constexpr int NUM_DQ_WARPS = 16;          // 512 dequant threads, 8 packed bytes (16 weights) each per stage
-constexpr int MAX_STAGES = 8;
+#ifndef LQ_MAX_STAGES
+#define LQ_MAX_STAGES 8
+#endif
+constexpr int MAX_STAGES = LQ_MAX_STAGES;
 
 __device__ int g_gemm_status;   // 0 = fine, 1 = a bounded wait expired in some CTA
 // Optional phase profile (lq_gemm_profile): cycles summed over CTAs.
@@ -126,9 +129,9 @@ struct Cfg {
     static constexpr int B_TILE_BYTES = TN * ROW_BYTES;
     static constexpr int RAW_TOTAL = W4 ? RT * RAW_BYTES : 0;
     static constexpr int STAGE_BYTES = A_BYTES + B_TILE_BYTES + RAW_TOTAL;
-    static constexpr int STAGES_FIT = (226 * 1024 - 1024) / STAGE_BYTES;
+    static constexpr int STAGES_FIT = (227 * 1024 - 1024 - 512) / STAGE_BYTES;
     static constexpr int STAGES = STAGES_FIT > MAX_STAGES ? MAX_STAGES : STAGES_FIT;
-    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 512 /*barriers*/;
     static_assert(SMEM_BYTES <= 227 * 1024, "shared memory budget");
     static constexpr int ACC_COLS = RT * TN;                               // TMEM columns of one accumulator set
     static constexpr int TA_COLS = TA ? STAGES * TA_COLS_PER_STAGE : 0;    // one A slot per pipeline stage
@@ -153,6 +156,7 @@ struct SmemCtl {
     uint32_t tmem_base;
     int abort_flag;
 };
+static_assert(sizeof(SmemCtl) <= 512, "barrier block of the shared-memory budget");
 
 // ---------------------------------------------------------------------------------------------
 // int4 -> bf16 dequant of 8 codes held in one little-endian 32-bit word of the nibble-pair layout
@@ -228,7 +232,9 @@ k_gemm(const __grid_constant__ CUtensorMap map_tok, const __grid_constant__ CUte
 
     if (warp == 0) {
         // ===================== TMA producer =====================
-        if (lane == 0) {
+        // warp-uniform loop, one elected lane issues the copies (same reason as for the MMA issuer below)
+        {
+            const bool leader = elect_one_sync();
             int stage = 0; uint32_t phase = 0;
             bool ok = true;
             long long w_empty = 0;
@@ -239,36 +245,45 @@ k_gemm(const __grid_constant__ CUtensorMap map_tok, const __grid_constant__ CUte
                 for (int kb = sg.kb0; kb < sg.kb1; ++kb) {
                     if (!(ok = mbar_wait_t(smem_u32(&ctl->empty[stage]), phase ^ 1u, abort_flag, prof, w_empty))) break;
                     const uint32_t bar = smem_u32(&ctl->full[stage]);
-                    mbar_expect_tx(bar, C::TX_BYTES);
+                    if (leader) {
+                        mbar_expect_tx(bar, C::TX_BYTES);
 #pragma unroll
-                    for (int r = 0; r < RT; ++r) {
-                        const int row0 = (r_tile * RT + r) * TILE_R;
-                        if (KIND == KIND_I8)            // int8 weights straight into the MMA tile
-                            tma_load_2d(a_tile(stage, r), &map_w, kb * 128, row0, bar);
-                        else if (KIND == KIND_WGRAD) {  // dY[64 tokens, 128 n] as two MN-major atoms of 64 n (128 B rows)
-                            tma_load_2d(a_tile(stage, r), &map_w, row0, kb * 64, bar);
-                            tma_load_2d(a_tile(stage, r) + 8192u, &map_w, row0 + 64, kb * 64, bar);
-                        } else if (KIND == KIND_FWD)    // raw: 128 weight rows x 32 bytes (64 k)
-                            tma_load_2d(smem_u32(raw_tile(stage, r)), &map_w, kb * 32, row0, bar);
-                        else                            // raw: 64 weight rows (n) x 64 bytes (128 k)
-                            tma_load_2d(smem_u32(raw_tile(stage, r)), &map_w, row0 / 2, kb * 64, bar);
-                    }
-                    if (KIND == KIND_WGRAD) {           // X[64 tokens, TN k] as TN/64 MN-major atoms
+                        for (int r = 0; r < RT; ++r) {
+                            const int row0 = (r_tile * RT + r) * TILE_R;
+                            if (KIND == KIND_I8)            // int8 weights straight into the MMA tile
+                                tma_load_2d(a_tile(stage, r), &map_w, kb * 128, row0, bar);
+                            else if (KIND == KIND_WGRAD) {  // dY[64 tokens, 128 n] as two MN-major atoms of 64 n (128 B rows)
+                                tma_load_2d(a_tile(stage, r), &map_w, row0, kb * 64, bar);
+                                tma_load_2d(a_tile(stage, r) + 8192u, &map_w, row0 + 64, kb * 64, bar);
+                            } else if (KIND == KIND_FWD)    // raw: 128 weight rows x 32 bytes (64 k)
+                                tma_load_2d(smem_u32(raw_tile(stage, r)), &map_w, kb * 32, row0, bar);
+                            else                            // raw: 64 weight rows (n) x 64 bytes (128 k)
+                                tma_load_2d(smem_u32(raw_tile(stage, r)), &map_w, row0 / 2, kb * 64, bar);
+                        }
+                        if (KIND == KIND_WGRAD) {           // X[64 tokens, TN k] as TN/64 MN-major atoms
 #pragma unroll
-                        for (int h = 0; h < TN / 64; ++h)
-                            tma_load_2d(b_tile(stage) + (uint32_t)(h * 8192), &map_tok, t_tile * TN + h * 64, kb * 64, bar);
-                    } else {
-                        tma_load_2d(b_tile(stage), &map_tok, kb * (C::I8 ? 128 : 64), t_tile * TN, bar);
+                            for (int h = 0; h < TN / 64; ++h)
+                                tma_load_2d(b_tile(stage) + (uint32_t)(h * 8192), &map_tok, t_tile * TN + h * 64, kb * 64, bar);
+                        } else {
+                            tma_load_2d(b_tile(stage), &map_tok, kb * (C::I8 ? 128 : 64), t_tile * TN, bar);
+                        }
                     }
                     if (++stage == C::STAGES) { stage = 0; phase ^= 1u; }
                 }
             }
-            if (prof) atomicAdd(&g_gemm_prof[0], (unsigned long long)w_empty);
+            if (prof && lane == 0) atomicAdd(&g_gemm_prof[0], (unsigned long long)w_empty);
         }
     } else if (warp == 1) {
         // ===================== MMA issuer =====================
-        if (lane == 0) {
+        // The whole warp walks the loop and one elected lane issues the MMAs and commits.  With the loop inside an
+        // `if (lane == 0)` the operands of every tcgen05.mma are per-thread values and the issuing thread's own
+        // instruction latencies bound the kernel at token tiles of 128 and below (a stage of four MMAs took ~480
+        // cycles to issue against 256 cycles of tensor work); kept warp-uniform they cost ~290.
+        // No warp-level synchronisation sits inside the loop: if a bounded wait gives up in some lanes only, those lanes
+        // leave for the teardown and the others follow at their next wait (the abort flag is raised).
+        {
             constexpr uint32_t IDESC = make_idesc(C::I8, (KIND == KIND_DGRAD && !TA) || C::WG, TN, C::WG);
+            const bool leader = elect_one_sync();
             int stage = 0; uint32_t phase = 0;
             int acc = 0; uint32_t acc_phase = 0;
             bool ok = true;
@@ -283,8 +298,7 @@ k_gemm(const __grid_constant__ CUtensorMap map_tok, const __grid_constant__ CUte
                 const uint32_t d_tmem = tmem_base + (uint32_t)(acc * C::ACC_COLS);
                 for (int kb = kb0; kb < kb1; ++kb) {
                     // A16W4: the team that converted the stage waited for its TMA data before it started, so its
-                    // `a_ready` arrival also covers the token tile: one barrier round trip per stage instead of two (the
-                    // round trips of this single thread are on the critical path: +12 % measured)
+                    // `a_ready` arrival also covers the token tile: one barrier round trip per stage instead of two
                     if (C::W4) { if (!(ok = mbar_wait_t(smem_u32(&ctl->a_ready[stage]), phase, abort_flag, prof, w_aready))) break; }
                     else { if (!(ok = mbar_wait_t(smem_u32(&ctl->full[stage]), phase, abort_flag, prof, w_full))) break; }
                     tc_fence_after();
@@ -294,31 +308,33 @@ k_gemm(const __grid_constant__ CUtensorMap map_tok, const __grid_constant__ CUte
                     const uint64_t b_desc = C::WG ? make_smem_desc(b_tile(stage), 8192, 1024) : make_smem_desc(b_tile(stage), 16, 1024);
                     const uint32_t a_step = (KIND == KIND_DGRAD || C::WG) ? (2048u >> 4) : (32u >> 4);
                     const uint32_t b_step = C::WG ? (2048u >> 4) : (32u >> 4);
-                    if (TA) {
-                        const uint32_t a_tmem = tmem_base + (uint32_t)(C::TA_COL0 + stage * TA_COLS_PER_STAGE);
+                    const uint32_t first = kb > kb0 ? 1u : 0u;
+                    if (leader) {
+                        if (TA) {
+                            const uint32_t a_tmem = tmem_base + (uint32_t)(C::TA_COL0 + stage * TA_COLS_PER_STAGE);
 #pragma unroll
-                        for (int kk = 0; kk < C::UMMA_PER_STAGE; ++kk)
-                            umma_ta(d_tmem, a_tmem + (uint32_t)(kk * 8), b_desc + (uint64_t)(kk * b_step), IDESC, (kb > kb0 || kk > 0) ? 1u : 0u);
-                    } else {
+                            for (int kk = 0; kk < C::UMMA_PER_STAGE; ++kk)
+                                umma_ta(d_tmem, a_tmem + (uint32_t)(kk * 8), b_desc + (uint64_t)(kk * b_step), IDESC, kk > 0 ? 1u : first);
+                        } else {
 #pragma unroll
-                    for (int r = 0; r < RT; ++r) {
-                        const uint64_t a_desc = (KIND == KIND_DGRAD || C::WG) ? make_smem_desc(a_tile(stage, r), 8192, 1024)
-                                                                              : make_smem_desc(a_tile(stage, r), 16, 1024);
+                            for (int r = 0; r < RT; ++r) {
+                                const uint64_t a_desc = (KIND == KIND_DGRAD || C::WG) ? make_smem_desc(a_tile(stage, r), 8192, 1024)
+                                                                                      : make_smem_desc(a_tile(stage, r), 16, 1024);
 #pragma unroll
-                        for (int kk = 0; kk < C::UMMA_PER_STAGE; ++kk) {
-                            umma<C::I8>(d_tmem + (uint32_t)(r * TN), a_desc + (uint64_t)(kk * a_step), b_desc + (uint64_t)(kk * b_step),
-                                        IDESC, (kb > kb0 || kk > 0) ? 1u : 0u);
+                                for (int kk = 0; kk < C::UMMA_PER_STAGE; ++kk)
+                                    umma<C::I8>(d_tmem + (uint32_t)(r * TN), a_desc + (uint64_t)(kk * a_step), b_desc + (uint64_t)(kk * b_step),
+                                                IDESC, kk > 0 ? 1u : first);
+                            }
                         }
+                        umma_commit(smem_u32(&ctl->empty[stage]));
                     }
-                    }
-                    umma_commit(smem_u32(&ctl->empty[stage]));
                     if (++stage == C::STAGES) { stage = 0; phase ^= 1u; }
                 }
                 if (!ok) break;
-                umma_commit(smem_u32(&ctl->acc_full[acc]));
+                if (leader) umma_commit(smem_u32(&ctl->acc_full[acc]));
                 if (++acc == C::ACC_BUFS) { acc = 0; acc_phase ^= 1u; }
             }
-            if (prof) {
+            if (prof && lane == 0) {
                 atomicAdd(&g_gemm_prof[1], (unsigned long long)w_full); atomicAdd(&g_gemm_prof[2], (unsigned long long)w_aready);
                 atomicAdd(&g_gemm_prof[3], (unsigned long long)w_acc); atomicAdd(&g_gemm_prof[4], (unsigned long long)(clock64() - t_role));
                 atomicAdd(&g_gemm_prof[9], 1ull);
@@ -526,6 +542,10 @@ k_gemm(const __grid_constant__ CUtensorMap map_tok, const __grid_constant__ CUte
             const int quarter = warp & 3, team = (warp - 6) >> 2;
             const int tt = ((warp - 6) & 3) * 32 + lane;
             const int groups_per_row = p.wcols / p.group;
+            // k / group without a division in the per-stage path: groups are multiples of 32 and so is every k asked for
+            const int g32 = p.group >> 5;
+            const int g_shift = (g32 & (g32 - 1)) == 0 ? 31 - __clz(g32) : -1;
+            auto group_of = [&](int k) { const int k32 = k >> 5; return g_shift >= 0 ? (k32 >> g_shift) : (k32 / g32); };
             const uint32_t ta_addr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)C::TA_COL0;
             // position in this CTA's sequence of k-blocks: the walker stands behind the segment that holds k-block `kb`
             struct Pos { SegWalk<SK> walk; int kb, kb1, r_tile; bool valid; };
@@ -552,13 +572,14 @@ k_gemm(const __grid_constant__ CUtensorMap map_tok, const __grid_constant__ CUte
                 }
                 const int n_rows = (KIND == KIND_FWD) ? p.R : p.C;
                 if (wrow >= n_rows || k0 >= p.wcols) return;
-                const size_t g0 = (size_t)wrow * groups_per_row + (size_t)(k0 / p.group);
-                const size_t g1 = (TA && KIND == KIND_DGRAD) ? g0 + (size_t)32 * groups_per_row
-                                                             : (size_t)wrow * groups_per_row + (size_t)(k1 / p.group);
+                const int gk0 = group_of(k0);
+                const size_t g0 = (size_t)wrow * groups_per_row + (size_t)gk0;
+                const size_t g1 = (TA && KIND == KIND_DGRAD) ? g0 + (size_t)32 * groups_per_row : g0 + (size_t)(group_of(k1) - gk0);
                 const unsigned short* sp = reinterpret_cast<const unsigned short*>(p.scales);
                 const unsigned short* zp = reinterpret_cast<const unsigned short*>(p.zeros);
                 a = (uint32_t)__ldg(sp + g0) | ((uint32_t)__ldg(zp + g0) << 16);
-                b = (uint32_t)__ldg(sp + g1) | ((uint32_t)__ldg(zp + g1) << 16);
+                b = a;
+                if (g1 != g0) b = (uint32_t)__ldg(sp + g1) | ((uint32_t)__ldg(zp + g1) << 16);   // groups of 64 and up: one pair per thread
             };
             constexpr int PF = 2;                                          // own stages of qparam prefetch
             Pos cur{SegWalk<SK>(p), 0, 0, 0, true};
@@ -592,7 +613,9 @@ k_gemm(const __grid_constant__ CUtensorMap map_tok, const __grid_constant__ CUte
                     // wait unambiguous.  (Needs STAGES >= number of teams: then the stage's use before the previous one
                     // is known to be over, because the producer had to see it retired before it could fill this team's
                     // own previous stage.)
-                    ok = mbar_wait_t(smem_u32(&ctl->empty[stage]), phase ^ 1u, abort_flag, prof, w_dq) &&
+                    // With a stage count that is a multiple of the four teams a team meets the same stages every round
+                    // and needs no such wait: `full` completing already implies that the producer saw the stage retired.
+                    ok = (C::STAGES % 4 == 0 || mbar_wait_t(smem_u32(&ctl->empty[stage]), phase ^ 1u, abort_flag, prof, w_dq)) &&
                          mbar_wait_t(smem_u32(&ctl->full[stage]), phase, abort_flag, prof, w_dq);
                     ok = __all_sync(0xffffffffu, ok) != 0;                 // the TMEM store below is warp-collective
                     if (!ok) break;

@@ -45,6 +45,8 @@ __device__ int g_gemm_status;   // 0 = fine, 1 = a bounded wait expired in some 
 //  [0] producer waiting for a free stage   [1] MMA waiting for TMA data   [2] MMA waiting for the dequantised tile
 //  [3] MMA waiting for a free accumulator  [4] MMA role total             [5] dequant waiting for TMA data
 //  [6] dequant role total                  [7] epilogue waiting for an accumulator  [8] epilogue role total  [9] CTAs
+//  balanced mode, lane quarter 0: [10] publishing partial sums (incl. ticket)  [11] adding a tile's parts up
+//  (with its epilogue)  [12] tiles added up  [14] hand-over copies
 __device__ unsigned long long g_gemm_prof[16];
 __device__ int g_gemm_prof_on;
 
@@ -67,51 +69,81 @@ struct GemmParams {
     __nv_bfloat16* out;            // [M, R]
     int32_t* acc_out;              // int8: raw accumulators [M, R] or null
     void* partial;                 // split-K partial sums [splits][M][R] (fp32 / int32); balanced mode: slots + flags
-    int sk_grid;                   // balanced mode (SK): number of CTAs the k-block units are dealt to
+    // balanced mode (SK), see SegWalk
+    int sk_full;                   // tiles computed whole (a multiple of the grid size), the first ones
+    int sk_rem;                    // shared tiles behind them, one owner CTA each (CTA j owns shared tile j)
+    int sk_h;                      // k-blocks of a shared tile its owner computes (the head); the rest is its tail
+    int sk_helpers;                // CTAs sk_rem .. sk_rem + sk_helpers - 1 share out the tails
+    int sk_q, sk_r;                // tail units / helpers and tail units % helpers (helper h starts at unit h * q + h * r / helpers)
+    int sk_pmax;                   // partial-sum slots per shared tile
     int accumulate;                // weight gradient: out += product (rounded once from the fp32 sum) instead of out = product
 };
 
 // One CTA's share of the work as a sequence of segments (a tile and a range of its k-blocks).
 //   tile-cyclic (SK = false): items blockIdx.x, blockIdx.x + gridDim.x, ...; an item is one (row tile, token tile,
 //     split) and its whole k range.
-//   balanced (SK = true): the (tile, k-block) units of the whole problem, tile-major, are dealt to the CTAs as equal
-//     contiguous ranges, so a CTA's range may start and end in the middle of a tile ("stream-K").  The segment that
-//     holds a tile's first k-block owns the tile's output; segments that start later in the tile hand their partial
-//     sums to the owner through global memory.
+//   balanced (SK = true): the first `sk_full` tiles are computed whole, tile-cyclic.  Each of the `sk_rem` tiles behind
+//     them (fewer than the grid has CTAs) is shared: its owner, CTA j for shared tile j, computes the head
+//     [0, sk_h) of its k range as its last piece of work, and the tails [sk_h, kb_total) of all shared tiles, laid end
+//     to end as "tail units", are dealt in equal contiguous ranges to the helper CTAs, which have no tile of their own
+//     left.  The host sizes the head so that the helpers are done a few k-blocks before the owners: an owner normally
+//     finds its tile's other parts already published and adds them up in its epilogue.
 struct Seg { int r_tile, t_tile, split, kb0, kb1; };
+// Balanced mode: first tail unit of helper h, floor(units * h / helpers).
+__device__ __forceinline__ int sk_helper_first(const GemmParams& p, int h) { return h * p.sk_q + (h * p.sk_r) / p.sk_helpers; }
+// Balanced mode: the helper whose range holds tail unit u.
+__device__ __forceinline__ int sk_helper_of(const GemmParams& p, int u) {
+    int h = min(p.sk_helpers - 1, u / p.sk_q);
+    while (sk_helper_first(p, h) > u) --h;
+    return h;
+}
 template <bool SK>
 struct SegWalk {
-    int pos, end;
+    int pos, end;       // tile-cyclic: next item, number of items; balanced: next whole tile, then this helper's tail units
+    bool whole, owner;  // balanced: still in the whole tiles; an owned head is still to come
     __device__ __forceinline__ explicit SegWalk(const GemmParams& p) {
+        pos = (int)blockIdx.x;
         if (SK) {
-            const long long units = (long long)p.r_tiles * p.t_tiles * p.kb_total;
-            pos = (int)(units * blockIdx.x / gridDim.x);
-            end = (int)(units * (blockIdx.x + 1) / gridDim.x);
+            end = p.sk_full; whole = true; owner = (int)blockIdx.x < p.sk_rem;
         } else {
-            pos = (int)blockIdx.x;
-            end = p.r_tiles * p.t_tiles * p.splits;
+            end = p.r_tiles * p.t_tiles * p.splits; whole = false; owner = false;
         }
     }
     __device__ __forceinline__ bool next(const GemmParams& p, Seg& s) {
-        if (pos >= end) return false;
         if (SK) {
-            const int tile = pos / p.kb_total;
-            s.kb0 = pos - tile * p.kb_total;
-            s.kb1 = min(p.kb_total, s.kb0 + (end - pos));
+            int tile;
+            if (whole) {
+                if (pos < end) {
+                    tile = pos; pos += (int)gridDim.x; s.kb0 = 0; s.kb1 = p.kb_total;
+                } else {
+                    whole = false;
+                    const int h = (int)blockIdx.x - p.sk_rem;
+                    if (!owner && h < p.sk_helpers) { pos = sk_helper_first(p, h); end = sk_helper_first(p, h + 1); }
+                    else { pos = end = 0; }
+                }
+            }
+            if (!whole) {
+                const int tail = p.kb_total - p.sk_h;
+                if (owner) {
+                    owner = false; tile = p.sk_full + (int)blockIdx.x; s.kb0 = 0; s.kb1 = p.sk_h;
+                } else if (pos < end) {
+                    const int j = pos / tail;
+                    tile = p.sk_full + j; s.kb0 = p.sk_h + (pos - j * tail); s.kb1 = min(p.kb_total, s.kb0 + (end - pos));
+                    pos += s.kb1 - s.kb0;
+                } else {
+                    return false;
+                }
+            }
             s.r_tile = tile % p.r_tiles; s.t_tile = tile / p.r_tiles; s.split = 0;
-            pos += s.kb1 - s.kb0;
-        } else {
-            s.r_tile = pos % p.r_tiles; s.t_tile = (pos / p.r_tiles) % p.t_tiles; s.split = pos / (p.t_tiles * p.r_tiles);
-            s.kb0 = s.split * p.kb_per_split; s.kb1 = min(p.kb_total, s.kb0 + p.kb_per_split);
-            pos += (int)gridDim.x;
+            return true;
         }
+        if (pos >= end) return false;
+        s.r_tile = pos % p.r_tiles; s.t_tile = (pos / p.r_tiles) % p.t_tiles; s.split = pos / (p.t_tiles * p.r_tiles);
+        s.kb0 = s.split * p.kb_per_split; s.kb1 = min(p.kb_total, s.kb0 + p.kb_per_split);
+        pos += (int)gridDim.x;
         return true;
     }
 };
-// Balanced mode: first unit of CTA c's range.
-__device__ __forceinline__ int sk_first_unit(const GemmParams& p, int c) {
-    return (int)((long long)p.r_tiles * p.t_tiles * p.kb_total * c / gridDim.x);
-}
 
 // RT = weight-row tiles (of 128 rows) a CTA computes against one token tile.  RT = 2 halves the token-tile
 // bytes fetched from L2 per flop (the dominant operand traffic) at the cost of a shallower pipeline.
@@ -119,7 +151,10 @@ __device__ __forceinline__ int sk_first_unit(const GemmParams& p, int c) {
 // of from shared memory: the 128 x 64 bf16 tile of a stage takes 32 TMEM columns, and per MMA the shared-memory
 // pipe no longer carries its 4 KB write and 4 KB read (the kernel is shared-memory-bandwidth bound otherwise).
 constexpr int TA_COLS_PER_STAGE = 32;
-template <int KIND, int TN, int RT, bool TA = false>
+constexpr int FIX_COLS = 16;                                         // balanced mode: token columns per hand-over copy
+constexpr int FIX_COPY_BYTES = FIX_COLS * 32 * 4;                    // one lane quarter of them as fp32: 2 KB
+constexpr int FIX_RING = 8;                                          // staging buffers per lane quarter
+template <int KIND, int TN, int RT, bool TA = false, bool SK = false>
 struct Cfg {
     static constexpr bool I8 = KIND == KIND_I8;
     static constexpr bool WG = KIND == KIND_WGRAD;      // dense bf16 weight gradient: both operands by TMA, MN-major
@@ -129,9 +164,10 @@ struct Cfg {
     static constexpr int B_TILE_BYTES = TN * ROW_BYTES;
     static constexpr int RAW_TOTAL = W4 ? RT * RAW_BYTES : 0;
     static constexpr int STAGE_BYTES = A_BYTES + B_TILE_BYTES + RAW_TOTAL;
-    static constexpr int STAGES_FIT = (227 * 1024 - 1024 - 512) / STAGE_BYTES;
+    static constexpr int FIX_BYTES = SK ? 4 * FIX_RING * FIX_COPY_BYTES : 0;    // balanced mode: the staging rings
+    static constexpr int STAGES_FIT = (227 * 1024 - 1024 - 512 - FIX_BYTES) / STAGE_BYTES;
     static constexpr int STAGES = STAGES_FIT > MAX_STAGES ? MAX_STAGES : STAGES_FIT;
-    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 512 /*barriers*/;
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + FIX_BYTES + 1024 /*alignment slack*/ + 512 /*barriers*/;
     static_assert(SMEM_BYTES <= 227 * 1024, "shared memory budget");
     static constexpr int ACC_COLS = RT * TN;                               // TMEM columns of one accumulator set
     static constexpr int TA_COLS = TA ? STAGES * TA_COLS_PER_STAGE : 0;    // one A slot per pipeline stage
@@ -153,6 +189,7 @@ struct SmemCtl {
     uint64_t empty[MAX_STAGES];    // MMAs that read the stage retired
     uint64_t acc_full[2];
     uint64_t acc_empty[2];
+    uint64_t fix_full[4][FIX_RING];   // balanced mode: hand-over copy landed (per lane quarter, per staging buffer)
     uint32_t tmem_base;
     int abort_flag;
 };
@@ -188,13 +225,13 @@ __device__ __forceinline__ uint4 dequant8(uint32_t w, __nv_bfloat162 z128, __nv_
 // The kernel
 // ---------------------------------------------------------------------------------------------
 template <int KIND, int TN, int RT, bool TA, bool SK>
-__global__ void __launch_bounds__(Cfg<KIND, TN, RT, TA>::THREADS, 1)
+__global__ void __launch_bounds__(Cfg<KIND, TN, RT, TA, SK>::THREADS, 1)
 k_gemm(const __grid_constant__ CUtensorMap map_tok, const __grid_constant__ CUtensorMap map_w, const GemmParams p) {
-    static_assert(!SK || (KIND != KIND_I8 && RT == 1), "balanced mode: A16W4 kinds, one row tile per CTA");
-    using C = Cfg<KIND, TN, RT, TA>;
+    static_assert(!SK || (KIND != KIND_I8 && RT == 1 && TN % FIX_COLS == 0), "balanced mode: A16W4 kinds, one row tile per CTA");
+    using C = Cfg<KIND, TN, RT, TA, SK>;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-    SmemCtl* ctl = reinterpret_cast<SmemCtl*>(smem + C::STAGES * C::STAGE_BYTES);
+    SmemCtl* ctl = reinterpret_cast<SmemCtl*>(smem + C::STAGES * C::STAGE_BYTES + C::FIX_BYTES);
     volatile int* abort_flag = &ctl->abort_flag;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -214,6 +251,8 @@ k_gemm(const __grid_constant__ CUtensorMap map_tok, const __grid_constant__ CUte
             mbar_init(smem_u32(&ctl->acc_full[a]), 1);
             mbar_init(smem_u32(&ctl->acc_empty[a]), 4);
         }
+        for (int q = 0; q < 4; ++q)
+            for (int b = 0; b < FIX_RING; ++b) mbar_init(smem_u32(&ctl->fix_full[q][b]), 1);
         ctl->abort_flag = 0;
         fence_barrier_init();
         fence_proxy_async();
@@ -349,36 +388,85 @@ k_gemm(const __grid_constant__ CUtensorMap map_tok, const __grid_constant__ CUte
         const long long t_role = prof ? clock64() : 0;
         SegWalk<SK> walk(p);
         Seg sg;
-        // balanced mode: partial sums travel as [CTA][token column][weight row] fp32 slots, one flag per (CTA, lane quarter)
+        // Balanced mode.  A segment that covers part of a shared tile's k range publishes its fp32 partial sums in a slot
+        // of the workspace ([shared tile][part][lane quarter][token column][32 rows]) and takes a ticket of the (tile,
+        // lane quarter).  Whoever draws the last ticket adds the tile's parts up in k order (owner's head first, then the
+        // helpers' pieces; always the same order, whoever does it) and runs the ordinary epilogue on the sums.  Nobody
+        // waits for another CTA.  An owner first looks at the ticket counter: when every helper has already published
+        // (the schedule is built for that), it skips its own publication and starts from its accumulator.  The other
+        // parts come in as 2 KB bulk copies (16 token columns of one part) through a ring of staging buffers per lane
+        // quarter, several copies ahead of the additions.
         float* const sk_slots = reinterpret_cast<float*>(p.partial);
-        volatile unsigned int* const sk_flags = SK ? reinterpret_cast<volatile unsigned int*>(sk_slots + (size_t)gridDim.x * (TN * TILE_R)) : nullptr;
+        unsigned int* const sk_tickets = SK ? reinterpret_cast<unsigned int*>(sk_slots + (size_t)p.sk_rem * p.sk_pmax * (TN * TILE_R)) : nullptr;
+        uint8_t* const fix_ring = smem + C::STAGES * C::STAGE_BYTES + quad * FIX_RING * FIX_COPY_BYTES;
+        uint32_t fix_phase = 0;                    // bit b: parity to wait for on staging buffer b of this quarter
         while (ok && walk.next(p, sg)) {
             const int r_tile = sg.r_tile, t_tile = sg.t_tile, split = sg.split;
             if (!(ok = mbar_wait_t(smem_u32(&ctl->acc_full[acc]), acc_phase, abort_flag, prof, w_accf))) break;
             tc_fence_after();
-            const bool sk_contrib = SK && sg.kb0 != 0;                       // starts inside a tile: hands its sums to the owner
-            const bool sk_owner = SK && sg.kb0 == 0 && sg.kb1 < p.kb_total;   // holds the tile's first k-block, not its last
-            int sk_last = (int)blockIdx.x;                                   // owner: CTAs blockIdx.x+1 .. sk_last contribute
-            if (sk_owner) {
-                const int tile_end = (sg.t_tile * p.r_tiles + sg.r_tile + 1) * p.kb_total;
-                while (sk_last + 1 < (int)gridDim.x && sk_first_unit(p, sk_last + 1) < tile_end) ++sk_last;
-                // every lane waits (bounded) for this lane quarter's flag of each contributor: its own acquire
-                for (int c = (int)blockIdx.x + 1; c <= sk_last && ok; ++c) {
-                    const long long t0 = clock64();
-                    unsigned int seen = 0;
-                    for (uint32_t it = 0;; ++it) {
-                        asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(sk_flags + c * 4 + quad) : "memory");
-                        if (seen != 0u) break;
-                        if ((it & 15u) == 15u) {
-                            if (*abort_flag) break;
-                            if (clock64() - t0 > WAIT_BUDGET_CYCLES) { *abort_flag = 1; break; }
-                            __nanosleep(64);
-                        }
-                    }
-                    ok = __all_sync(0xffffffffu, seen != 0u) != 0;
+            bool emit = true, sk_sum = false;
+            int sk_parts = 1, sk_part_lo = 0;      // parts of the tile; first part that comes through the ring (1: own sums from the accumulator)
+            int sk_issued = 0, sk_taken = 0, sk_copies = 0, sk_is = 0, sk_ip = 0;   // copies issued / consumed / in all; slab and part of the next issue
+            const float* sk_part0 = nullptr;       // this quarter's share of the tile's first slot
+            auto sk_issue = [&]() {                // next copy of the sequence (slab-major, parts in k order inside a slab)
+                const float* src = sk_part0 + (size_t)sk_ip * 4 * (TN * 32) + (size_t)sk_is * (FIX_COLS * 32);
+                if (lane == 0) {
+                    const int b = sk_issued & (FIX_RING - 1);
+                    const uint32_t bar = smem_u32(&ctl->fix_full[quad][b]);
+                    mbar_expect_tx(bar, FIX_COPY_BYTES);
+                    bulk_load(smem_u32(fix_ring + b * FIX_COPY_BYTES), src, FIX_COPY_BYTES, bar);
                 }
-                if (!ok) break;
+                ++sk_issued;
+                if (++sk_ip == sk_parts) { sk_ip = sk_part_lo; ++sk_is; }
+            };
+            if (SK && !(sg.kb0 == 0 && sg.kb1 == p.kb_total)) {
+                const long long t_pub = prof ? clock64() : 0;
+                const uint32_t acc_addr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * C::ACC_COLS);
+                const int j = t_tile * p.r_tiles + r_tile - p.sk_full;      // shared tile
+                const int tail = p.kb_total - p.sk_h;
+                const int h_first = sk_helper_of(p, j * tail), h_last = sk_helper_of(p, (j + 1) * tail - 1);
+                sk_parts = 2 + h_last - h_first;
+                const bool is_owner = sg.kb0 == 0;
+                const int my_part = is_owner ? 0 : 1 + ((int)blockIdx.x - p.sk_rem) - h_first;
+                sk_part0 = sk_slots + ((size_t)j * p.sk_pmax * 4 + (size_t)quad) * (size_t)(TN * 32);
+                unsigned int* const ticket_ptr = sk_tickets + j * 4 + quad;
+                unsigned int ticket = 0;
+                if (is_owner) {                    // have all helpers published already?
+                    if (lane == 0) asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(ticket) : "l"(ticket_ptr) : "memory");
+                    ticket = __shfl_sync(0xffffffffu, ticket, 0);
+                }
+                if (is_owner && ticket == (unsigned int)(sk_parts - 1)) {
+                    sk_part_lo = 1;                // own sums stay in the accumulator
+                } else {
+                    // publish: lanes are consecutive rows, every store instruction writes 128 contiguous bytes
+                    float* dst = const_cast<float*>(sk_part0) + (size_t)my_part * 4 * (TN * 32) + lane;
+#pragma unroll 1
+                    for (int c0 = 0; c0 < TN; c0 += 16) {
+                        uint32_t v[16];
+                        tmem_ld16(acc_addr + (uint32_t)c0, v);
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int jj = 0; jj < 16; ++jj) dst[(c0 + jj) * 32] = __uint_as_float(v[jj]);
+                    }
+                    fence_proxy_async_all();       // the slot is read back with bulk copies (async proxy)
+                    __threadfence();
+                    __syncwarp();
+                    if (lane == 0) ticket = atomicAdd(ticket_ptr, 1u);
+                    ticket = __shfl_sync(0xffffffffu, ticket, 0);
+                }
+                emit = sk_sum = ticket == (unsigned int)(sk_parts - 1);
+                if (prof && warp == 2 && lane == 0) atomicAdd(&g_gemm_prof[10], (unsigned long long)(clock64() - t_pub));
+                if (sk_sum) {
+                    __threadfence();
+                    fence_proxy_async_all();
+                    sk_ip = sk_part_lo;
+                    sk_copies = (sk_parts - sk_part_lo) * (TN / FIX_COLS);
+                    for (int i = 0; i < FIX_RING && i < sk_copies; ++i) sk_issue();
+                    if (prof && warp == 2 && lane == 0) { atomicAdd(&g_gemm_prof[12], 1ull); atomicAdd(&g_gemm_prof[14], (unsigned long long)sk_copies); }
+                }
             }
+            const long long t_emit = prof ? clock64() : 0;
+            if (emit) {
 #pragma unroll 1
             for (int rr = 0; rr < RT; ++rr) {
                 const int r = (r_tile * RT + rr) * TILE_R + quad * 32 + lane;
@@ -391,26 +479,36 @@ k_gemm(const __grid_constant__ CUtensorMap map_tok, const __grid_constant__ CUte
 #pragma unroll 1
                 for (int c0 = 0; c0 < TN; c0 += SLAB) {
                     uint32_t v[SLAB];
-#pragma unroll
-                    for (int h = 0; h < SLAB / 16; ++h)
-                        tmem_ld16(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * C::ACC_COLS + rr * TN + c0 + 16 * h),
-                                  *reinterpret_cast<uint32_t(*)[16]>(&v[16 * h]));
-                    tmem_ld_wait();
-                    if (SK) {
-                        const int row = quad * 32 + lane;
-                        if (sk_contrib) {              // lanes are consecutive weight rows: 128-byte coalesced stores
-                            float* dst = sk_slots + (size_t)blockIdx.x * (TN * TILE_R) + (size_t)c0 * TILE_R + row;
-#pragma unroll
-                            for (int j = 0; j < SLAB; ++j) dst[j * TILE_R] = __uint_as_float(v[j]);
-                            continue;
+                    if (SK && sk_sum) {
+                        // the slab's sums: the tile's parts in k order, each a 2 KB copy in the staging ring (the first
+                        // from the accumulator when this is the owner and it did not publish)
+                        if (sk_part_lo) {
+                            tmem_ld16(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * C::ACC_COLS + c0), *reinterpret_cast<uint32_t(*)[16]>(&v[0]));
+                            tmem_ld_wait();
                         }
-                        if (sk_owner) {                // k order: own sums first, then the contributors in CTA order
-                            for (int c = (int)blockIdx.x + 1; c <= sk_last; ++c) {
-                                const float* src = sk_slots + (size_t)c * (TN * TILE_R) + (size_t)c0 * TILE_R + row;
+#pragma unroll 1
+                        for (int part = sk_part_lo; part < sk_parts; ++part) {
+                            const int b = sk_taken & (FIX_RING - 1);
+                            if (ok) ok = mbar_wait(smem_u32(&ctl->fix_full[quad][b]), (fix_phase >> b) & 1u, abort_flag);
+                            fix_phase ^= 1u << b;
+                            const float* src = reinterpret_cast<const float*>(fix_ring + b * FIX_COPY_BYTES) + lane;
+                            if (part == 0) {
 #pragma unroll
-                                for (int j = 0; j < SLAB; ++j) v[j] = __float_as_uint(__fadd_rn(__uint_as_float(v[j]), __ldcg(src + j * TILE_R)));
+                                for (int jj = 0; jj < 16; ++jj) v[jj] = __float_as_uint(src[jj * 32]);
+                            } else {
+#pragma unroll
+                                for (int jj = 0; jj < 16; ++jj) v[jj] = __float_as_uint(__fadd_rn(__uint_as_float(v[jj]), src[jj * 32]));
                             }
+                            ++sk_taken;
+                            __syncwarp();                                     // every lane has read the buffer: refill it
+                            if (ok && sk_issued < sk_copies) sk_issue();
                         }
+                    } else {
+#pragma unroll
+                        for (int h = 0; h < SLAB / 16; ++h)
+                            tmem_ld16(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * C::ACC_COLS + rr * TN + c0 + 16 * h),
+                                      *reinterpret_cast<uint32_t(*)[16]>(&v[16 * h]));
+                        tmem_ld_wait();
                     }
                     if (C::WG) {
                         // weight gradient: lane = output row n, the slab's 16 columns are consecutive in memory.
@@ -508,16 +606,12 @@ k_gemm(const __grid_constant__ CUtensorMap map_tok, const __grid_constant__ CUte
                     }
                 }
             }
+            }   // emit
+            if (SK && sk_sum && prof && warp == 2 && lane == 0) atomicAdd(&g_gemm_prof[11], (unsigned long long)(clock64() - t_emit));
+            if (!ok) break;
             tc_fence_before();
-            if (sk_contrib) __threadfence();               // this lane's slot stores, before the warp's flag
             __syncwarp();
-            if (lane == 0) {
-                mbar_arrive(smem_u32(&ctl->acc_empty[acc]));
-                if (sk_contrib) {
-                    const unsigned int one = 1u;
-                    asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(sk_flags + blockIdx.x * 4 + quad), "r"(one) : "memory");
-                }
-            }
+            if (lane == 0) mbar_arrive(smem_u32(&ctl->acc_empty[acc]));
             if (++acc == C::ACC_BUFS) { acc = 0; acc_phase ^= 1u; }
         }
         if (prof && warp == 2 && lane == 0) {
@@ -741,14 +835,24 @@ static bool a_operand_in_tmem(int kind) {
     return kind == KIND_FWD;
 }
 
-struct Plan { int tn, rt, r_tiles, t_tiles, splits, kb_total, kb_per_split; bool skinny; bool sk; int sk_grid; };
+struct Plan {
+    int tn, rt, r_tiles, t_tiles, splits, kb_total, kb_per_split;
+    bool skinny;
+    bool sk;                                                    // balanced forward (see SegWalk)
+    int sk_grid, sk_full, sk_rem, sk_h, sk_helpers, sk_pmax;
+};
 
-// Balanced ("stream-K") forward: bytes of the per-CTA partial-sum slots and of the flags behind them.
-static size_t sk_slot_bytes(const Plan& pl) { return (size_t)pl.sk_grid * (size_t)pl.tn * TILE_R * 4; }
-static size_t sk_flag_bytes(const Plan& pl) { return (size_t)pl.sk_grid * 4 * sizeof(unsigned int); }
+// Balanced forward: bytes of the partial-sum slots (sk_pmax per shared tile) and of the tickets behind them.
+static size_t sk_slot_bytes(const Plan& pl) { return (size_t)pl.sk_rem * pl.sk_pmax * (size_t)pl.tn * TILE_R * 4; }
+static size_t sk_ticket_bytes(const Plan& pl) { return (size_t)pl.sk_rem * 4 * sizeof(unsigned int); }
+static size_t plan_workspace_bytes(const Plan& pl, int64_t M, int64_t R) {
+    if (pl.sk) return sk_slot_bytes(pl) + sk_ticket_bytes(pl);
+    return pl.splits > 1 ? (size_t)pl.splits * (size_t)M * (size_t)R * 4 : 0;
+}
 
 // group: quantization group size, or 0 when unknown (the skinny path needs 64, 128 or 256)
-static Plan make_plan(int kind, int64_t M, int64_t N, int64_t K, int group = 128) {
+// allow_balanced = false asks for the plan a caller with too little workspace for the balanced one falls back to.
+static Plan make_plan(int kind, int64_t M, int64_t N, int64_t K, int group = 128, bool allow_balanced = true) {
     Plan pl{};
     if (kind == KIND_FWD && M <= 16 && (K % 256) == 0 && (group == 64 || group == 128 || group == 256) && !getenv("LQ_GEMM_NO_SKINNY")) {
         // decode-sized forward: bandwidth-bound register-dequant kernel (lq_gemv.cu)
@@ -769,18 +873,37 @@ static Plan make_plan(int kind, int64_t M, int64_t N, int64_t K, int group = 128
     pl.kb_total = (int)((Cc + bk - 1) / bk);
     const int tiles = pl.r_tiles * pl.t_tiles;
     const int sms = sm_count();
-    // Balanced ("stream-K") forward, opt-in with LQ_GEMM_BALANCE=1: whole tiles leave SMs idle or a last wave nearly
-    // empty when there are few tiles per SM, so the (tile, k-block) units are dealt out evenly instead and partial
-    // sums are handed over through global memory.  Measured on the four Llama-2-7B shapes it does not pay yet: the
-    // owner's epilogue pulls up to five contributors' partial sums with latency-bound loads (176 us against 124 us
-    // for the four layers at 128 tokens; equal at 512), so the tile-cyclic plan stays the default.
-    if (kind == KIND_FWD && pl.tn >= 64 && tiles <= 2 * sms && getenv("LQ_GEMM_BALANCE")) {
-        const long long units = (long long)tiles * pl.kb_total;
-        long long grid = units / 4;                                  // at least 4 k-blocks per CTA
-        if (grid > sms) grid = sms;
-        if (grid < 1) grid = 1;
-        if (grid > tiles || tiles % grid != 0) {                     // (whole tiles per CTA need no hand-over at all)
-            pl.sk = true; pl.sk_grid = (int)grid; pl.splits = 1; pl.kb_per_split = pl.kb_total;
+    // Balanced forward, opt-in with LQ_GEMM_BALANCE=1 (read at every launch).  With few tiles per SM, whole tiles
+    // leave SMs idle or a last wave nearly empty (86 tiles of a 11008-row layer on 148 SMs; 172 tiles at 512 tokens =
+    // one full wave and one of 24 tiles).  The tiles of the last, incomplete wave can be shared instead: an owner
+    // computes the head of the k range, the CTAs without a tile of their own the tails (see SegWalk); the head is
+    // sized so that the helpers finish `margin` k-blocks before the owners.  Measured on the four Llama-2-7B shapes
+    // it does not pay: adding up a tile's parts and the epilogue behind it are ~14 k cycles of single-warp-per-lane-
+    // quarter work at the very end (470 cycles per 16-column slab and part), as much as the ~13 k cycles the shorter
+    // main loop saves (41 us against 25 us for the 11008-row layer at 128 tokens), so whole tiles stay the default.
+    if (kind == KIND_FWD && pl.tn >= 64 && allow_balanced && (pl.tn < 256 || a_operand_in_tmem(kind))) {
+        const char* e = getenv("LQ_GEMM_BALANCE");
+        const bool off = !e || e[0] == '0', force = e && e[0] == '1';
+        const int kb = pl.kb_total;
+        const int full = tiles / sms * sms, rem = tiles - full;
+        const int margin = 4 + pl.tn / 64;
+        int helpers = sms - rem, h = 0;
+        if (helpers > 6 * rem) helpers = 6 * rem;                   // a tile's sums are added up by one CTA: bound its parts
+        bool found = false;
+        for (int it = 0; it < 16 && rem > 0 && helpers > 0 && !off; ++it) {
+            h = (rem * kb + margin * helpers + rem + helpers - 1) / (rem + helpers);
+            if (h < 1) h = 1;
+            const int tail_units = rem * (kb - h);
+            if (h >= kb || tail_units < 2) break;
+            if (tail_units >= 4 * helpers) { found = true; break; }
+            helpers = tail_units / 4;                               // at least four k-blocks per helper
+        }
+        if (found && force) {
+            pl.sk = true; pl.splits = 1; pl.kb_per_split = kb;
+            pl.sk_full = full; pl.sk_rem = rem; pl.sk_h = h; pl.sk_helpers = helpers;
+            pl.sk_grid = full > 0 ? sms : rem + helpers;
+            const int share = rem * (kb - h) / helpers;             // smallest helper range
+            pl.sk_pmax = 1 + (kb - h + share - 1) / share + 1;
             return pl;
         }
     }
@@ -827,8 +950,8 @@ static int make_map(CUtensorMap* m, const void* base, CUtensorMapDataType dt, in
 }
 
 template <int KIND, int TN, int RT, bool TA = false, bool SK = false>
-static int launch_tn(const CUtensorMap& mt, const CUtensorMap& mw, const GemmParams& p, cudaStream_t st) {
-    using C = Cfg<KIND, TN, RT, TA>;
+static int launch_tn(const CUtensorMap& mt, const CUtensorMap& mw, const GemmParams& p, cudaStream_t st, int sk_grid = 0) {
+    using C = Cfg<KIND, TN, RT, TA, SK>;
     static bool attr_done[64] = {};
     int dev = 0;
     cudaGetDevice(&dev);
@@ -838,11 +961,11 @@ static int launch_tn(const CUtensorMap& mt, const CUtensorMap& mw, const GemmPar
         attr_done[dev] = true;
     }
     if (SK) {
-        // hand-over flags start at zero in every launch (a memset node when the launch is being captured)
-        unsigned char* flags = reinterpret_cast<unsigned char*>(p.partial) + (size_t)p.sk_grid * (size_t)TN * TILE_R * 4;
-        cudaError_t e = cudaMemsetAsync(flags, 0, (size_t)p.sk_grid * 4 * sizeof(unsigned int), st);
-        if (e != cudaSuccess) { set_cuda_error(e, "cudaMemsetAsync(hand-over flags)"); return LQ_ECUDA; }
-        k_gemm<KIND, TN, RT, TA, SK><<<p.sk_grid, C::THREADS, C::SMEM_BYTES, st>>>(mt, mw, p);
+        // hand-over tickets start at zero in every launch (a memset node when the launch is being captured)
+        unsigned char* tickets = reinterpret_cast<unsigned char*>(p.partial) + (size_t)p.sk_rem * p.sk_pmax * (size_t)TN * TILE_R * 4;
+        cudaError_t e = cudaMemsetAsync(tickets, 0, (size_t)p.sk_rem * 4 * sizeof(unsigned int), st);
+        if (e != cudaSuccess) { set_cuda_error(e, "cudaMemsetAsync(hand-over tickets)"); return LQ_ECUDA; }
+        k_gemm<KIND, TN, RT, TA, SK><<<sk_grid, C::THREADS, C::SMEM_BYTES, st>>>(mt, mw, p);
         return check_launch("k_gemm (balanced)");
     }
     const int items = p.r_tiles * p.t_tiles * p.splits;
@@ -861,11 +984,13 @@ static int launch_tn(const CUtensorMap& mt, const CUtensorMap& mw, const GemmPar
 }
 // balanced forward (token tiles of 64 / 128 / 256), either placement of the weight tile
 template <bool TA>
-static int launch_fwd_sk(int tn, const CUtensorMap& mt, const CUtensorMap& mw, const GemmParams& p, cudaStream_t st) {
+static int launch_fwd_sk(int tn, const CUtensorMap& mt, const CUtensorMap& mw, const GemmParams& p, cudaStream_t st, int sk_grid) {
     switch (tn) {
-        case 64: return launch_tn<KIND_FWD, 64, 1, TA, true>(mt, mw, p, st);
-        case 128: return launch_tn<KIND_FWD, 128, 1, TA, true>(mt, mw, p, st);
-        case 256: return launch_tn<KIND_FWD, 256, 1, TA, true>(mt, mw, p, st);
+        case 64: return launch_tn<KIND_FWD, 64, 1, TA, true>(mt, mw, p, st, sk_grid);
+        case 128: return launch_tn<KIND_FWD, 128, 1, TA, true>(mt, mw, p, st, sk_grid);
+        case 256:   // (with the weight tile in shared memory the staging buffers leave too few pipeline stages)
+            if constexpr (TA) return launch_tn<KIND_FWD, 256, 1, TA, true>(mt, mw, p, st, sk_grid);
+            break;
     }
     return LQ_EUNSUPPORTED;
 }
@@ -896,8 +1021,10 @@ static int run_gemm(int kind, const void* tok, const void* w, GemmParams p, int6
                     void* workspace, size_t workspace_bytes, cudaStream_t st) {
     if (M == 0) return LQ_OK;
     { int rc_dev = ensure_device_for(tok); if (rc_dev) return rc_dev; }
-    const Plan pl = make_plan(kind, M, N, K, p.group);
+    Plan pl = make_plan(kind, M, N, K, p.group);
     p.M = (int)M; p.R = (int)((kind == KIND_DGRAD) ? K : N); p.C = (int)((kind == KIND_DGRAD) ? N : K);
+    // a caller whose workspace is too small for the balanced plan gets the whole-tile plan (which may need less or none)
+    if (pl.sk && (!workspace || workspace_bytes < plan_workspace_bytes(pl, M, p.R))) pl = make_plan(kind, M, N, K, p.group, false);
     p.wcols = (int)K;
     p.r_tiles = pl.r_tiles; p.t_tiles = pl.t_tiles; p.splits = pl.splits; p.kb_total = pl.kb_total; p.kb_per_split = pl.kb_per_split;
     if (pl.splits > 1) {
@@ -906,8 +1033,11 @@ static int run_gemm(int kind, const void* tok, const void* w, GemmParams p, int6
         p.partial = workspace;
     }
     if (pl.sk) {
-        if (!workspace || workspace_bytes < sk_slot_bytes(pl) + sk_flag_bytes(pl) || !al16(workspace)) return LQ_EWORKSPACE;
-        p.partial = workspace; p.sk_grid = pl.sk_grid;
+        if (!workspace || workspace_bytes < plan_workspace_bytes(pl, M, p.R) || !al16(workspace)) return LQ_EWORKSPACE;
+        p.partial = workspace;
+        p.sk_full = pl.sk_full; p.sk_rem = pl.sk_rem; p.sk_h = pl.sk_h; p.sk_helpers = pl.sk_helpers; p.sk_pmax = pl.sk_pmax;
+        const int tail_units = pl.sk_rem * (pl.kb_total - pl.sk_h);
+        p.sk_q = tail_units / pl.sk_helpers; p.sk_r = tail_units % pl.sk_helpers;
     }
     if (pl.skinny) {
         SkinnyParams sp{};
@@ -940,7 +1070,7 @@ static int run_gemm(int kind, const void* tok, const void* w, GemmParams p, int6
     if (rc) return rc;
     switch (kind) {
         case KIND_FWD:
-            if (pl.sk) return a_operand_in_tmem(kind) ? launch_fwd_sk<true>(pl.tn, mt, mw, p, st) : launch_fwd_sk<false>(pl.tn, mt, mw, p, st);
+            if (pl.sk) return a_operand_in_tmem(kind) ? launch_fwd_sk<true>(pl.tn, mt, mw, p, st, pl.sk_grid) : launch_fwd_sk<false>(pl.tn, mt, mw, p, st, pl.sk_grid);
             return (pl.rt == 1 && a_operand_in_tmem(kind)) ? launch_kind_ta<KIND_FWD>(pl.tn, mt, mw, p, st)
                                                        : launch_kind<KIND_FWD>(pl.tn, pl.rt, mt, mw, p, st);
         case KIND_DGRAD:
@@ -963,10 +1093,10 @@ size_t lq_gemm_workspace_bytes(int kind, int64_t M, int64_t N, int64_t K) {
     const int64_t R = (kind == KIND_DGRAD) ? K : N;
     size_t need = 0;
     for (int group : {64, 128, 0}) {
-        const Plan pl = make_plan(kind, M, N, K, group);
-        size_t b = pl.splits > 1 ? (size_t)pl.splits * (size_t)M * (size_t)R * 4 : 0;
-        if (pl.sk) b = sk_slot_bytes(pl) + sk_flag_bytes(pl);
-        if (b > need) need = b;
+        for (bool balanced : {true, false}) {
+            const size_t b = plan_workspace_bytes(make_plan(kind, M, N, K, group, balanced), M, R);
+            if (b > need) need = b;
+        }
     }
     return need;
 }
@@ -1114,8 +1244,10 @@ int lq_gemm_a16w4_fwd_static(const void* x, const int8_t* qweight, const void* s
     if (!shape_ok_w4(M, N, K, group)) return LQ_EUNSUPPORTED;
     // Partial sums needed by this shape's split-K plan; shapes that need more than the array holds are refused
     // (host arithmetic only, before anything touches the device).
-    const Plan pl = make_plan(KIND_FWD, M, N, K, group);
-    const size_t need = pl.sk ? sk_slot_bytes(pl) + sk_flag_bytes(pl) : (pl.splits > 1 ? (size_t)pl.splits * (size_t)M * (size_t)N * 4 : 0);
+    // (the balanced plan is used when its slots fit the array, else the whole-tile plan, as with any too-small workspace)
+    Plan pl = make_plan(KIND_FWD, M, N, K, group);
+    if (pl.sk && plan_workspace_bytes(pl, M, N) > (size_t)LQ_STATIC_SCRATCH_BYTES) pl = make_plan(KIND_FWD, M, N, K, group, false);
+    const size_t need = plan_workspace_bytes(pl, M, N);
     if (need > (size_t)LQ_STATIC_SCRATCH_BYTES) {
         lq::set_cuda_error(cudaErrorInvalidValue, "lq_gemm_a16w4_fwd_static: shape needs more scratch than the built-in 8 MiB; "
                                                   "use lq_gemm_a16w4_fwd with a workspace");

@@ -97,9 +97,9 @@ def test_a16w4_llama_shapes(ops, a_operand, M, K, N):
 
 @pytest.mark.parametrize("M,N,K", [(24, 512, 1024), (64, 320, 2048), (128, 11008, 4096), (200, 4096, 4096), (512, 4096, 11008)])
 def test_a16w4_fwd_balanced_plan_vs_oracle(ops, a_operand, monkeypatch, M, N, K):
-    """The forward kernel with its (tile, k-block) units dealt out evenly over the SMs: CTAs that start inside a tile
-    hand their partial sums to the tile's owner through the workspace.  Same tolerance as the tile-cyclic plan, and the
-    same bits on every run (the hand-over order is fixed)."""
+    """The forward kernel with its (tile, k-block) units dealt out evenly over the SMs: segments that cover part of a
+    tile's k range publish their partial sums in the workspace and the last one to finish adds them up in k order.
+    Same tolerance as the whole-tile plan, and the same bits on every run (the order of the additions is fixed)."""
     monkeypatch.setenv("LQ_GEMM_BALANCE", "1")
     ops._ws_need.clear()
     codes, sb, zb = make_w4_layer(ops, N, K, seed=M + N)
@@ -118,7 +118,10 @@ def test_a16w4_fwd_balanced_plan_vs_oracle(ops, a_operand, monkeypatch, M, N, K)
 @pytest.mark.parametrize("M,N,K,group", [(300, 384, 1024, 128), (4096, 4096, 4096, 128), (77, 256, 512, 64), (512, 512, 512, 32),
                                          (1000, 2048, 2048, 256)])
 def test_a16w4_tmem_and_smem_operand_paths_agree_bitwise(ops, monkeypatch, M, N, K, group):
-    """Both placements feed the tensor core the same bf16 weights in the same order: outputs must be identical."""
+    """Both placements feed the tensor core the same bf16 weights in the same order: outputs must be identical
+    (whole-tile plan for both: the balanced plan's 256-token tile exists for one placement only)."""
+    monkeypatch.setenv("LQ_GEMM_BALANCE", "0")
+    ops._ws_need.clear()
     codes, sb, zb = make_w4_layer(ops, N, K, seed=7, group=group)
     g = torch.Generator(device="cuda").manual_seed(M)
     x = torch.randn(M, K, device="cuda", generator=g).to(torch.bfloat16)

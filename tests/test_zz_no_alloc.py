@@ -50,15 +50,17 @@ def _call_static(lib, x, codes, s, z, bias, M, N, K, group):
     return got
 
 
-# (group, (first M, second M), balanced plan?, where the partial sums of output row 0, columns 0..63 land in the array):
-#  - group 128, M > 16: the tensor-core kernel with four K-splits, partial sums laid out [split][token][column]
-#  - the same in the kernel's balanced mode: each 128-column tile is shared by four CTAs, the second of which (CTA 1)
-#    writes its sums for k = 256..511 into slot 1, laid out [token][weight row] (64 x 128 floats)
+# (group, (first M, second M), balanced plan?, where partial sums of token 0 (and 1) land in the array):
+#  - group 128, M > 16, whole-tile plan: the tensor-core kernel with four K-splits, partial sums laid out
+#    [split][token][column]: 64 floats from 0 = split 0 of output (0, 0..63)
+#  - the same in the kernel's balanced mode (forced; by itself the planner takes it for larger shapes): the owner of a
+#    128-column tile computes k-blocks 0..8, helper CTAs the rest in pieces of four; the first helper's sums
+#    (k = 576..831) go to part 1 of tile 0, slots laid out [tile][part][lane quarter][token][32 weight rows]:
+#    64 floats from there = outputs (0, 0..31) and (1, 0..31)
 #  - group 64, M <= 16: the decode kernel with four K-splits, partial sums laid out [split][token][column]
-@pytest.mark.parametrize("group,Ms,balanced,peek_at", [(128, (64, 24), False, 0), (128, (64, 24), True, 64 * 128), (64, (16, 5), False, 0)])
+@pytest.mark.parametrize("group,Ms,balanced,peek_at", [(128, (64, 24), False, 0), (128, (64, 24), True, 4 * 64 * 32), (64, (16, 5), False, 0)])
 def test_static_scratch_forward_twice_against_oracle(group, Ms, balanced, peek_at, monkeypatch):
-    if balanced:
-        monkeypatch.setenv("LQ_GEMM_BALANCE", "1")
+    monkeypatch.setenv("LQ_GEMM_BALANCE", "1" if balanced else "0")
     from latentq_llm_b200 import _lib, ops
     lib = _lib.lib
     N, K = 512, 1024
@@ -85,6 +87,8 @@ def test_static_scratch_forward_twice_against_oracle(group, Ms, balanced, peek_a
         assert lib.lq_gemm_a16w4_fwd_static_peek(part.ctypes.data_as(C.c_void_p), peek_at, 64) == 0
         assert np.isfinite(part).all() and not np.array_equal(part, poison)
         full = ref[0, :64] - bias_h[:64]
+        if balanced:
+            full = np.concatenate([ref[0, :32] - bias_h[:32], ref[1, :32] - bias_h[:32]])
         assert np.abs(part - full).max() > 0.05 * np.abs(full).max()
         poison = part.copy()
 

@@ -165,9 +165,9 @@ struct Cfg {
     static constexpr int RAW_TOTAL = W4 ? RT * RAW_BYTES : 0;
     static constexpr int STAGE_BYTES = A_BYTES + B_TILE_BYTES + RAW_TOTAL;
     static constexpr int FIX_BYTES = SK ? 4 * FIX_RING * FIX_COPY_BYTES : 0;    // balanced mode: the staging rings
-    static constexpr int STAGES_FIT = (227 * 1024 - 1024 - 512 - FIX_BYTES) / STAGE_BYTES;
+    static constexpr int STAGES_FIT = (227 * 1024 - 1024 - 1024 - FIX_BYTES) / STAGE_BYTES;
     static constexpr int STAGES = STAGES_FIT > MAX_STAGES ? MAX_STAGES : STAGES_FIT;
-    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + FIX_BYTES + 1024 /*alignment slack*/ + 512 /*barriers*/;
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + FIX_BYTES + 1024 /*alignment slack*/ + 1024 /*barriers*/;
     static_assert(SMEM_BYTES <= 227 * 1024, "shared memory budget");
     static constexpr int ACC_COLS = RT * TN;                               // TMEM columns of one accumulator set
     static constexpr int TA_COLS = TA ? STAGES * TA_COLS_PER_STAGE : 0;    // one A slot per pipeline stage
@@ -175,7 +175,12 @@ struct Cfg {
     static constexpr int TA_COL0 = ACC_BUFS * ACC_COLS;
     static constexpr int TMEM_NEED = ACC_BUFS * ACC_COLS + TA_COLS;
     static constexpr int TMEM_COLS = TMEM_NEED <= 32 ? 32 : TMEM_NEED <= 64 ? 64 : TMEM_NEED <= 128 ? 128 : TMEM_NEED <= 256 ? 256 : 512;
-    static constexpr int NUM_WARPS = 6 + (W4 ? NUM_DQ_WARPS : 0);
+    // Epilogue warps: one per TMEM lane quarter, or two (the second set behind all other warps, each warp of a pair
+    // draining half of the token columns) where the accumulator is wide enough to split.  With a single accumulator
+    // buffer the epilogue is exposed time between two tiles; splitting it halves that.
+    static constexpr int EPI_SPLIT = (!SK && TN >= 64) ? 2 : 1;
+    static constexpr int FIRST_EXTRA_EPI = 6 + (W4 ? NUM_DQ_WARPS : 0);
+    static constexpr int NUM_WARPS = FIRST_EXTRA_EPI + (EPI_SPLIT - 1) * 4;
     static constexpr int THREADS = NUM_WARPS * 32;
     static constexpr uint32_t TX_BYTES = (uint32_t)(B_TILE_BYTES + (W4 ? RAW_TOTAL : A_BYTES));
     static constexpr int UMMA_PER_STAGE = 4;   // 128 bytes of contraction per stage / 32 bytes per MMA
@@ -193,7 +198,7 @@ struct SmemCtl {
     uint32_t tmem_base;
     int abort_flag;
 };
-static_assert(sizeof(SmemCtl) <= 512, "barrier block of the shared-memory budget");
+static_assert(sizeof(SmemCtl) <= 1024, "barrier block of the shared-memory budget");
 
 // ---------------------------------------------------------------------------------------------
 // int4 -> bf16 dequant of 8 codes held in one little-endian 32-bit word of the nibble-pair layout
@@ -249,7 +254,7 @@ k_gemm(const __grid_constant__ CUtensorMap map_tok, const __grid_constant__ CUte
         }
         for (int a = 0; a < 2; ++a) {
             mbar_init(smem_u32(&ctl->acc_full[a]), 1);
-            mbar_init(smem_u32(&ctl->acc_empty[a]), 4);
+            mbar_init(smem_u32(&ctl->acc_empty[a]), 4 * C::EPI_SPLIT);
         }
         for (int q = 0; q < 4; ++q)
             for (int b = 0; b < FIX_RING; ++b) mbar_init(smem_u32(&ctl->fix_full[q][b]), 1);
@@ -379,9 +384,10 @@ k_gemm(const __grid_constant__ CUtensorMap map_tok, const __grid_constant__ CUte
                 atomicAdd(&g_gemm_prof[9], 1ull);
             }
         }
-    } else if (warp < 6) {
+    } else if (warp < 6 || warp >= C::FIRST_EXTRA_EPI) {
         // ===================== epilogue =====================
         const int quad = warp & 3;                 // TMEM lane quadrant this warp may read
+        const int col_lo = (warp < 6 ? 0 : 1) * (TN / C::EPI_SPLIT), col_hi = col_lo + TN / C::EPI_SPLIT;   // its token columns
         int acc = 0; uint32_t acc_phase = 0;
         bool ok = true;
         long long w_accf = 0;
@@ -477,7 +483,7 @@ k_gemm(const __grid_constant__ CUtensorMap map_tok, const __grid_constant__ CUte
                 // load-wait round trips; the A16W4 kernels run at the register cap of a 22-warp CTA
                 constexpr int SLAB = (C::I8 && TN >= 32) ? 32 : 16;
 #pragma unroll 1
-                for (int c0 = 0; c0 < TN; c0 += SLAB) {
+                for (int c0 = col_lo; c0 < col_hi; c0 += SLAB) {
                     uint32_t v[SLAB];
                     if (SK && sk_sum) {
                         // the slab's sums: the tile's parts in k order, each a 2 KB copy in the staging ring (the first
@@ -619,7 +625,7 @@ k_gemm(const __grid_constant__ CUtensorMap map_tok, const __grid_constant__ CUte
         }
     } else {
         // ===================== dequant (A16W4) =====================
-        if (C::W4) {
+        if (C::W4 && warp < 6 + NUM_DQ_WARPS) {
             // The 16 warps form 4 teams of 4 warps; team g converts pipeline stages g, g+4, g+8, ... on its own, which
             // keeps four stages of conversion in flight (one stage is a dependent chain: shared-memory loads, ALU work,
             // the store of the tile and its completion fence).

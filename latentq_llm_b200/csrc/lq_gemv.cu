@@ -241,15 +241,16 @@ __global__ void __launch_bounds__(RB_WARPS * 32, 2) k_skinny_rows(const SkinnyPa
         qa[u] = qb[u] = make_uint4(0, 0, 0, 0);
         if (u < n_chunks) { qa[u] = __ldg(wa + u * 4); qb[u] = __ldg(wb + u * 4); }       // a chunk is 64 bytes = 4 uint4 per row
     }
-    // (scale | zero << 16) of the current and the next group
-    uint32_t sz_a = 0, sz_b = 0, nx_a = 0, nx_b = 0;
-    if (n_groups > 0) {
-        sz_a = (uint32_t)__ldg(sca) | ((uint32_t)__ldg(zpa) << 16);
-        sz_b = (uint32_t)__ldg(scb) | ((uint32_t)__ldg(zpb) << 16);
-    }
-    if (n_groups > 1) {
-        nx_a = (uint32_t)__ldg(sca + 1) | ((uint32_t)__ldg(zpa + 1) << 16);
-        nx_b = (uint32_t)__ldg(scb + 1) | ((uint32_t)__ldg(zpb + 1) << 16);
+    // (scale | zero << 16) of the group that starts with the chunk in ring slot u: fetched as far ahead as the chunk
+    // itself (they come from DRAM too; one group ahead was a stall per group)
+    uint32_t sza[RB_PF], szb[RB_PF], sz_a = 0, sz_b = 0;
+#pragma unroll
+    for (int u = 0; u < RB_PF; ++u) {
+        sza[u] = szb[u] = 0;
+        if (u % GC == 0 && u < n_chunks) {
+            sza[u] = (uint32_t)__ldg(sca + u / GC) | ((uint32_t)__ldg(zpa + u / GC) << 16);
+            szb[u] = (uint32_t)__ldg(scb + u / GC) | ((uint32_t)__ldg(zpb + u / GC) << 16);
+        }
     }
     pdl_launch_dependents();        // weight and group-parameter loads are issued: the next launch may start
     pdl_wait();                     // the tokens may be the previous launch's output
@@ -273,7 +274,15 @@ __global__ void __launch_bounds__(RB_WARPS * 32, 2) k_skinny_rows(const SkinnyPa
             const int c = cb + u;
             if (c < n_chunks) {
                 const uint4 ca = qa[u], cq = qb[u];
-                if (c + RB_PF < n_chunks) { qa[u] = __ldg(wa + (c + RB_PF) * 4); qb[u] = __ldg(wb + (c + RB_PF) * 4); }
+                if (u % GC == 0) { sz_a = sza[u]; sz_b = szb[u]; }
+                if (c + RB_PF < n_chunks) {
+                    qa[u] = __ldg(wa + (c + RB_PF) * 4); qb[u] = __ldg(wb + (c + RB_PF) * 4);
+                    if (u % GC == 0) {
+                        const int gn = (c + RB_PF) / GC;
+                        sza[u] = (uint32_t)__ldg(sca + gn) | ((uint32_t)__ldg(zpa + gn) << 16);
+                        szb[u] = (uint32_t)__ldg(scb + gn) | ((uint32_t)__ldg(zpb + gn) << 16);
+                    }
+                }
                 uint4 xc[MT][4];
 #pragma unroll
                 for (int m = 0; m < MT; ++m)
@@ -318,11 +327,6 @@ __global__ void __launch_bounds__(RB_WARPS * 32, 2) k_skinny_rows(const SkinnyPa
                         for (int i = 0; i < 4; ++i) { acc[m][0][i] = acc[m][1][i] = sx[m][i] = 0.0f; }
                     }
                     ++grp;
-                    sz_a = nx_a; sz_b = nx_b;
-                    if (grp + 1 < n_groups) {
-                        nx_a = (uint32_t)__ldg(sca + grp + 1) | ((uint32_t)__ldg(zpa + grp + 1) << 16);
-                        nx_b = (uint32_t)__ldg(scb + grp + 1) | ((uint32_t)__ldg(zpb + grp + 1) << 16);
-                    }
                 }
             }
         }
@@ -367,9 +371,15 @@ __global__ void __launch_bounds__(RB_WARPS * 32, 2) k_skinny_rows(const SkinnyPa
 // Needs at least two quantization groups per warp (the group parameters are fetched one group ahead, across the
 // row-block boundary); other shapes use k_skinny_rows.
 // ---------------------------------------------------------------------------------------------
+#ifndef LQ_GEMV_PF
+#define LQ_GEMV_PF 4
+#endif
+#ifndef LQ_GEMV_MINB
+#define LQ_GEMV_MINB 2
+#endif
 template <int MT, int GC>
-__global__ void __launch_bounds__(RB_WARPS * 32, 2) k_skinny_stream(const SkinnyParams p, const int x_stride) {
-    constexpr int PF = 4;
+__global__ void __launch_bounds__(RB_WARPS * 32, LQ_GEMV_MINB) k_skinny_stream(const SkinnyParams p, const int x_stride) {
+    constexpr int PF = LQ_GEMV_PF;
     extern __shared__ __align__(16) uint8_t ss_smem[];
     uint4* xs = reinterpret_cast<uint4*>(ss_smem);                                               // [M][x_stride]
     float* sxs = reinterpret_cast<float*>(ss_smem + (size_t)p.M * x_stride * 16);               // [groups][8 * MT]
@@ -402,7 +412,13 @@ __global__ void __launch_bounds__(RB_WARPS * 32, 2) k_skinny_stream(const Skinny
         qa[u] = qb[u] = make_uint4(0, 0, 0, 0);
         if (u < n_chunks) { qa[u] = __ldg(wa + u * 4); qb[u] = __ldg(wb + u * 4); }
     }
-    uint32_t sz_a = load_sz(ra, 0), sz_b = load_sz(rb, 0), nx_a = load_sz(ra, 1), nx_b = load_sz(rb, 1);
+    // group parameters ride in the same ring as the chunks: slot u holds those of the group its chunk starts
+    uint32_t sza[PF], szb[PF], sz_a = 0, sz_b = 0;
+#pragma unroll
+    for (int u = 0; u < PF; ++u) {
+        sza[u] = szb[u] = 0;
+        if (u % GC == 0 && u < n_chunks) { sza[u] = load_sz(ra, u / GC); szb[u] = load_sz(rb, u / GC); }
+    }
     // token rows of this thread's B fragments (a token that does not exist reads the last one: its outputs are dropped)
     int xrow[MT];
 #pragma unroll
@@ -465,8 +481,14 @@ __global__ void __launch_bounds__(RB_WARPS * 32, 2) k_skinny_stream(const Skinny
                 const int c = cb + u;
                 if (c < n_chunks) {
                     const uint4 ca = qa[u], cq = qb[u];
-                    if (c + PF < n_chunks) { qa[u] = __ldg(wa + (c + PF) * 4); qb[u] = __ldg(wb + (c + PF) * 4); }
-                    else if (has_next) { qa[u] = __ldg(na + u * 4); qb[u] = __ldg(nb + u * 4); }   // slot u of the next row block
+                    if (u % GC == 0) { sz_a = sza[u]; sz_b = szb[u]; }
+                    if (c + PF < n_chunks) {
+                        qa[u] = __ldg(wa + (c + PF) * 4); qb[u] = __ldg(wb + (c + PF) * 4);
+                        if (u % GC == 0) { sza[u] = load_sz(ra, (c + PF) / GC); szb[u] = load_sz(rb, (c + PF) / GC); }
+                    } else if (has_next) {                                                          // slot u of the next row block
+                        qa[u] = __ldg(na + u * 4); qb[u] = __ldg(nb + u * 4);
+                        if (u % GC == 0) { sza[u] = load_sz(na_row, u / GC); szb[u] = load_sz(nb_row, u / GC); }
+                    }
                     const uint32_t wsa[4] = {ca.x, ca.y, ca.z, ca.w}, wsb[4] = {cq.x, cq.y, cq.z, cq.w};
                     const int cg = g_begin * GC + c;                                              // chunk index within the row
 #pragma unroll
@@ -499,9 +521,6 @@ __global__ void __launch_bounds__(RB_WARPS * 32, 2) k_skinny_stream(const Skinny
                             tot[m][3] = fmaf(s_b, (acc[m][0][3] + acc[m][1][3]) - z_b * sx.y, tot[m][3]);
                         }
                         ++grp;
-                        sz_a = nx_a; sz_b = nx_b;
-                        if (grp + 1 < n_groups) { nx_a = load_sz(ra, grp + 1); nx_b = load_sz(rb, grp + 1); }
-                        else if (has_next) { nx_a = load_sz(na_row, grp + 1 - n_groups); nx_b = load_sz(nb_row, grp + 1 - n_groups); }
                     }
                 }
             }
@@ -572,7 +591,7 @@ static int launch_skinny_stream(const SkinnyParams& p, cudaStream_t st) {
     const size_t smem = skinny_stream_smem(p.M, p.K, p.group);
     const int rpb = p.pair_stride > 0 ? 8 : 16;
     const int n_blocks = (p.N + rpb - 1) / rpb;
-    const unsigned grid = (unsigned)std::min(n_blocks, 2 * sm_count());
+    const unsigned grid = (unsigned)std::min(n_blocks, LQ_GEMV_MINB * sm_count());
     if (mt == 1) return gc == 1 ? launch_skinny_stream_v<1, 1>(p, x_stride, smem, grid, st) : launch_skinny_stream_v<1, 2>(p, x_stride, smem, grid, st);
     return gc == 1 ? launch_skinny_stream_v<2, 1>(p, x_stride, smem, grid, st) : launch_skinny_stream_v<2, 2>(p, x_stride, smem, grid, st);
 }

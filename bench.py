@@ -36,8 +36,8 @@ WORKLOAD = "A16W4 dequant-GEMM fwd+grad-input, Llama-2-7B linear shapes (K,N) in
 
 # dram__bytes_read.sum + dram__bytes_write.sum per k_gemm launch from an ncu capture of the (K,N)=(4096,11008),
 # M=4096 launches (a tensor-bound kernel: the figure shows there are no re-reads)
-NCU_TRAFFIC_BYTES_PER_LAUNCH = 128.4e6
-NCU_TRAFFIC_NOTE = ("ncu capture of the (K,N)=(4096,11008), M=4096 launches: forward 113.9 MB, grad-input 142.9 MB, mean 128.4 MB "
+NCU_TRAFFIC_BYTES_PER_LAUNCH = 128.9e6
+NCU_TRAFFIC_NOTE = ("ncu capture of the (K,N)=(4096,11008), M=4096 launches: forward 115.2 MB, grad-input 142.6 MB, mean 128.9 MB "
                     "per launch against 146.8 MB algorithmic bytes of that shape")
 
 
@@ -722,7 +722,7 @@ def run_ours(args):
     e2e_step(); torch.cuda.synchronize()
     e2e_steps = max(2, min(args.steps, 10))
     ms_e2e, _ = timed(torch, e2e_step, e2e_steps, barrier)
-    assert torch.equal(host[1]["y"], layers[1]["y"].cpu()) and torch.equal(host[-1]["dx"], layers[-1]["dx"].cpu()), \
+    assert torch.equal(host[len(layers) // 2]["y"], layers[len(layers) // 2]["y"].cpu()) and torch.equal(host[-1]["dx"], layers[-1]["dx"].cpu()), \
         "end-to-end results in host memory differ from the device results"
 
     t = torch.tensor([ms, ms_e2e], device="cuda", dtype=torch.float64)

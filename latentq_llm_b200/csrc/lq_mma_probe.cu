@@ -2,8 +2,8 @@
 // quoted against.  One CTA per SM issues a long run of 128 x N x (32 bytes of k) MMAs on operands that stay
 // resident in shared memory (optionally the A operand in tensor memory), rotating over `n_acc` independent
 // accumulators, and reports the cycles the run took.  kind::i8 gives the int8 peak that the A8W8 GEMM is compared
-// with; running it with one accumulator against several shows how much of an MMA's time is the dependency on
-// the previous MMA into the same accumulator (what bounds GEMMs with narrow token tiles).
+// with; running it with one accumulator against several shows whether an MMA's time depends on the previous MMA
+// into the same accumulator.
 //
 // No counterpart in the reference.  The kernel reads no global memory and writes 8 bytes per CTA.
 #include "lq_common.cuh"
@@ -60,7 +60,11 @@ __global__ void __launch_bounds__(128, 1) k_mma_probe(int n, int n_acc, int n_mm
     __syncthreads();
     tc_fence_after();
 
-    if (warp == 1 && lane == 0) {
+    if (warp == 1) {
+        // The whole warp runs the loop and one elected lane issues: the operands of tcgen05.mma then stay warp-uniform.
+        // (Issued from inside an `if (lane == 0)` the same loop measures the issuing thread, ~115 cycles per MMA, not
+        // the tensor pipe.)
+        const bool leader = elect_one_sync();
         const uint32_t idesc = make_idesc(I8, false, n);
         const uint64_t a_desc = make_smem_desc(smem_u32(smem), 16, 1024);
         const uint64_t b_desc = make_smem_desc(smem_u32(smem + PROBE_A_BYTES), 16, 1024);
@@ -71,16 +75,20 @@ __global__ void __launch_bounds__(128, 1) k_mma_probe(int n, int n_acc, int n_mm
             for (int kk = 0; kk < 4; ++kk) {
                 const uint32_t d = tmem_base + (uint32_t)(acc * n);
                 const uint32_t accumulate = (i + kk >= n_acc) ? 1u : 0u;
-                if (!I8 && a_in_tmem) umma_ta(d, tmem_base + (uint32_t)(PROBE_TA_COL0 + kk * 8), b_desc + (uint64_t)(kk * 2), idesc, accumulate);
-                else umma<I8>(d, a_desc + (uint64_t)(kk * 2), b_desc + (uint64_t)(kk * 2), idesc, accumulate);
+                if (leader) {
+                    if (!I8 && a_in_tmem) umma_ta(d, tmem_base + (uint32_t)(PROBE_TA_COL0 + kk * 8), b_desc + (uint64_t)(kk * 2), idesc, accumulate);
+                    else umma<I8>(d, a_desc + (uint64_t)(kk * 2), b_desc + (uint64_t)(kk * 2), idesc, accumulate);
+                }
                 if (++acc == n_acc) acc = 0;
             }
         }
-        umma_commit(smem_u32(&ctl->done));
+        if (leader) umma_commit(smem_u32(&ctl->done));
         mbar_wait(smem_u32(&ctl->done), 0, abort_flag);
         const long long t1 = clock64();
-        if (blockIdx.x < PROBE_MAX_CTAS) g_probe_cycles[blockIdx.x] = (unsigned long long)(t1 - t0);
-        if (*abort_flag) atomicExch(&g_probe_status, 1);
+        if (leader) {
+            if (blockIdx.x < PROBE_MAX_CTAS) g_probe_cycles[blockIdx.x] = (unsigned long long)(t1 - t0);
+            if (*abort_flag) atomicExch(&g_probe_status, 1);
+        }
     }
     tc_fence_before();
     __syncthreads();

@@ -303,3 +303,21 @@ def test_wgrad_gemm_vs_fp32_matmul(ops, M, N, K):
     assert float((acc == want).float().mean()) > 0.9                 # same single rounding: only the fp32 sum order differs
     # linearity: doubling dy doubles the product exactly
     assert torch.equal(ops.gemm_wgrad(dy * 2, x), dw * 2)
+
+
+def test_mma_issue_rate_probe_runs_and_rejects_bad_arguments():
+    """`lq_mma_issue_rate` (the tensor-core ceiling the GEMM rooflines quote): a short run returns a plausible cycle
+    count per 128 x 256 MMA (the ideal is 128 cycles for either kind), and argument errors come back as LQ_EINVAL
+    without a launch."""
+    import ctypes as C
+    from latentq_llm_b200 import _lib
+    lib = _lib.lib
+    torch.zeros(1, device="cuda")
+    for kind, ta in ((_lib.GEMM_A16W4_FWD, 0), (_lib.GEMM_A16W4_FWD, 1), (_lib.GEMM_A8W8, 0)):
+        cyc = C.c_ulonglong(0)
+        assert lib.lq_mma_issue_rate(kind, ta, 256, 1, 1024, 4, C.byref(cyc), None) == 0
+        assert 100.0 <= cyc.value / 1024 <= 400.0, (kind, ta, cyc.value / 1024)
+    cyc = C.c_ulonglong(0)
+    assert lib.lq_mma_issue_rate(_lib.GEMM_A16W4_FWD, 0, 250, 1, 1024, 4, C.byref(cyc), None) == _lib.LQ_EINVAL     # N not a multiple of 16
+    assert lib.lq_mma_issue_rate(_lib.GEMM_A16W4_FWD, 0, 256, 2, 1024, 4, C.byref(cyc), None) == _lib.LQ_EINVAL     # accumulators beyond 256 columns
+    assert lib.lq_mma_issue_rate(_lib.GEMM_A8W8, 1, 256, 1, 1024, 4, C.byref(cyc), None) == _lib.LQ_EINVAL          # int8 has no tensor-memory A here

@@ -216,7 +216,9 @@ LQ_API int lq_act_quant_per_tensor(const void* x, int64_t n, float* clampv_out, 
  * GEMMs (tcgen05 / TMEM; TMA-staged operands).  Row-major everywhere.
  * ------------------------------------------------------------------------ */
 enum { LQ_GEMM_A16W4_FWD = 0, LQ_GEMM_A16W4_DGRAD = 1, LQ_GEMM_A8W8 = 2 };
-/* Bytes of caller-provided scratch the GEMM of that kind/shape may use (split-K partial sums). */
+/* Bytes of caller-provided scratch the GEMM of that kind/shape may use (split-K partial sums; with LQ_GEMM_BALANCE=1
+ * in the environment the partial sums of the shared-tile forward plan, which falls back to whole tiles when the
+ * workspace given is smaller). */
 LQ_API size_t lq_gemm_workspace_bytes(int kind, int64_t M, int64_t N, int64_t K);
 
 /* QLinearFunctionW4.forward (utils/quant.py:116-121): y[M,N] = x[M,K] · deq(qweight)[N,K]ᵀ (+ bias),

@@ -377,9 +377,15 @@ __global__ void __launch_bounds__(RB_WARPS * 32, 2) k_skinny_rows(const SkinnyPa
 #ifndef LQ_GEMV_MINB
 #define LQ_GEMV_MINB 2
 #endif
-template <int MT, int GC>
+// NC4: every warp's slice is exactly four groups of 128 (K = 4096, the shape of three of a Llama-7B layer's four
+// projections).  The loop is then written out for that case: a chunk's successor in the prefetch ring is always chunk
+// u of the next row block, the four (scale, zero) pairs of a row come as two 8-byte loads per row block, and every
+// shared-memory address is a constant offset from a per-warp base, which removes the index arithmetic that made up
+// about half of the general loop's instructions.
+template <int MT, int GC, bool NC4>
 __global__ void __launch_bounds__(RB_WARPS * 32, LQ_GEMV_MINB) k_skinny_stream(const SkinnyParams p, const int x_stride) {
     constexpr int PF = LQ_GEMV_PF;
+    static_assert(!NC4 || (GC == 1 && PF == 4), "the written-out loop is for group 128 and a ring of four chunks");
     extern __shared__ __align__(16) uint8_t ss_smem[];
     uint4* xs = reinterpret_cast<uint4*>(ss_smem);                                               // [M][x_stride]
     float* sxs = reinterpret_cast<float*>(ss_smem + (size_t)p.M * x_stride * 16);               // [groups][8 * MT]
@@ -417,8 +423,13 @@ __global__ void __launch_bounds__(RB_WARPS * 32, LQ_GEMV_MINB) k_skinny_stream(c
 #pragma unroll
     for (int u = 0; u < PF; ++u) {
         sza[u] = szb[u] = 0;
-        if (u % GC == 0 && u < n_chunks) { sza[u] = load_sz(ra, u / GC); szb[u] = load_sz(rb, u / GC); }
+        if (!NC4 && u % GC == 0 && u < n_chunks) { sza[u] = load_sz(ra, u / GC); szb[u] = load_sz(rb, u / GC); }
     }
+    // NC4: the row's four scales and four zero points of this warp's slice (8 bytes each; 32 groups per row, four per warp)
+    auto load_s4 = [&](int row) { return __ldg(reinterpret_cast<const uint2*>(sc_all + (size_t)row * 32 + warp * 4)); };
+    auto load_z4 = [&](int row) { return __ldg(reinterpret_cast<const uint2*>(zp_all + (size_t)row * 32 + warp * 4)); };
+    uint2 s4a = make_uint2(0, 0), z4a = s4a, s4b = s4a, z4b = s4a;
+    if (NC4) { s4a = load_s4(ra); z4a = load_z4(ra); s4b = load_s4(rb); z4b = load_z4(rb); }
     // token rows of this thread's B fragments (a token that does not exist reads the last one: its outputs are dropped)
     int xrow[MT];
 #pragma unroll
@@ -464,6 +475,11 @@ __global__ void __launch_bounds__(RB_WARPS * 32, LQ_GEMV_MINB) k_skinny_stream(c
     __syncthreads();
 
     int buf = 0;
+    // NC4: per-warp bases of the staged tokens and token sums (everything else is a compile-time offset)
+    const uint4* xbase[MT];
+#pragma unroll
+    for (int m = 0; m < MT; ++m) xbase[m] = xs + (size_t)xrow[m] * x_stride + g_begin * 16 + t;
+    const float* sxbase = sxs + g_begin * (8 * MT) + 2 * t;
     for (; blk < n_blocks; blk += gridDim.x) {
         const int nblk = blk + (int)gridDim.x;
         const bool has_next = nblk < n_blocks;
@@ -474,8 +490,51 @@ __global__ void __launch_bounds__(RB_WARPS * 32, LQ_GEMV_MINB) k_skinny_stream(c
         for (int m = 0; m < MT; ++m)
 #pragma unroll
             for (int i = 0; i < 4; ++i) { tot[m][i] = acc[m][0][i] = acc[m][1][i] = 0.0f; }
+        if constexpr (NC4) {
+            uint2 ns4a = s4a, nz4a = z4a, ns4b = s4b, nz4b = z4b;
+            if (has_next) { ns4a = load_s4(na_row); nz4a = load_z4(na_row); ns4b = load_s4(nb_row); nz4b = load_z4(nb_row); }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const uint4 ca = qa[u], cq = qb[u];
+                if (has_next) { qa[u] = __ldg(na + u * 4); qb[u] = __ldg(nb + u * 4); }
+                const uint32_t wsa[4] = {ca.x, ca.y, ca.z, ca.w}, wsb[4] = {cq.x, cq.y, cq.z, cq.w};
+#pragma unroll
+                for (int w = 0; w < 4; ++w) {
+                    uint32_t pa[4], pb[4];
+                    extract_word(wsa[w], pa); extract_word(wsb[w], pb);
+                    const uint32_t a0[4] = {pa[0], pb[0], pa[1], pb[1]}, a1[4] = {pa[2], pb[2], pa[3], pb[3]};
+#pragma unroll
+                    for (int m = 0; m < MT; ++m) {
+                        const uint4 f = xbase[m][u * 16 + w * 4];
+                        if (w == 0) {
+                            mma_16816_start(acc[m][0], a0, f.x, f.y);
+                            mma_16816_start(acc[m][1], a1, f.z, f.w);
+                        } else {
+                            mma_16816(acc[m][0], a0, f.x, f.y);
+                            mma_16816(acc[m][1], a1, f.z, f.w);
+                        }
+                    }
+                }
+                // group u of the slice: bf16 bits (u & 1 ? high : low) half of word (u >> 1) of the packed loads
+                const uint32_t sw_a = u < 2 ? s4a.x : s4a.y, zw_a = u < 2 ? z4a.x : z4a.y;
+                const uint32_t sw_b = u < 2 ? s4b.x : s4b.y, zw_b = u < 2 ? z4b.x : z4b.y;
+                const float s_a = __uint_as_float((u & 1) ? (sw_a & 0xffff0000u) : (sw_a << 16));
+                const float z_a = __uint_as_float((u & 1) ? (zw_a & 0xffff0000u) : (zw_a << 16)) + 128.0f;
+                const float s_b = __uint_as_float((u & 1) ? (sw_b & 0xffff0000u) : (sw_b << 16));
+                const float z_b = __uint_as_float((u & 1) ? (zw_b & 0xffff0000u) : (zw_b << 16)) + 128.0f;
+#pragma unroll
+                for (int m = 0; m < MT; ++m) {
+                    const float2 sx = *reinterpret_cast<const float2*>(sxbase + u * (8 * MT) + m * 8);
+                    tot[m][0] = fmaf(s_a, (acc[m][0][0] + acc[m][1][0]) - z_a * sx.x, tot[m][0]);
+                    tot[m][1] = fmaf(s_a, (acc[m][0][1] + acc[m][1][1]) - z_a * sx.y, tot[m][1]);
+                    tot[m][2] = fmaf(s_b, (acc[m][0][2] + acc[m][1][2]) - z_b * sx.x, tot[m][2]);
+                    tot[m][3] = fmaf(s_b, (acc[m][0][3] + acc[m][1][3]) - z_b * sx.y, tot[m][3]);
+                }
+            }
+            s4a = ns4a; z4a = nz4a; s4b = ns4b; z4b = nz4b;
+        }
         int grp = 0;
-        for (int cb = 0; cb < n_chunks; cb += PF) {
+        for (int cb = 0; !NC4 && cb < n_chunks; cb += PF) {
 #pragma unroll
             for (int u = 0; u < PF; ++u) {
                 const int c = cb + u;
@@ -564,18 +623,18 @@ static bool skinny_stream_supported(int64_t K, int group) {
     return gpr - (RB_WARPS - 1) * gper >= 2;
 }
 
-template <int MT, int GC>
+template <int MT, int GC, bool NC4 = false>
 static int launch_skinny_stream_v(const SkinnyParams& p, int x_stride, size_t smem, unsigned grid, cudaStream_t st) {
     static bool attr_done[64] = {};
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev < 0 || dev >= 64) return LQ_EUNSUPPORTED;
     if (!attr_done[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(k_skinny_stream<MT, GC>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
+        cudaError_t e = cudaFuncSetAttribute(k_skinny_stream<MT, GC, NC4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
         if (e != cudaSuccess) { set_cuda_error(e, "cudaFuncSetAttribute(k_skinny_stream)"); return LQ_ECUDA; }
         attr_done[dev] = true;
     }
-    launch_pdl(k_skinny_stream<MT, GC>, dim3(grid), RB_WARPS * 32, smem, st, p, x_stride);
+    launch_pdl(k_skinny_stream<MT, GC, NC4>, dim3(grid), RB_WARPS * 32, smem, st, p, x_stride);
     return check_launch("k_skinny_stream");
 }
 
@@ -592,6 +651,10 @@ static int launch_skinny_stream(const SkinnyParams& p, cudaStream_t st) {
     const int rpb = p.pair_stride > 0 ? 8 : 16;
     const int n_blocks = (p.N + rpb - 1) / rpb;
     const unsigned grid = (unsigned)std::min(n_blocks, LQ_GEMV_MINB * sm_count());
+    // K = 4096 with groups of 128: the written-out loop (scales / zeros are read as 8-byte words there)
+    const bool nc4 = gc == 1 && p.K == 4096 && LQ_GEMV_PF == 4 && !getenv("LQ_SKINNY_NO_NC4") &&
+                     (reinterpret_cast<uintptr_t>(p.scales) & 7) == 0 && (reinterpret_cast<uintptr_t>(p.zeros) & 7) == 0;
+    if (nc4) return mt == 1 ? launch_skinny_stream_v<1, 1, true>(p, x_stride, smem, grid, st) : launch_skinny_stream_v<2, 1, true>(p, x_stride, smem, grid, st);
     if (mt == 1) return gc == 1 ? launch_skinny_stream_v<1, 1>(p, x_stride, smem, grid, st) : launch_skinny_stream_v<1, 2>(p, x_stride, smem, grid, st);
     return gc == 1 ? launch_skinny_stream_v<2, 1>(p, x_stride, smem, grid, st) : launch_skinny_stream_v<2, 2>(p, x_stride, smem, grid, st);
 }

@@ -321,3 +321,34 @@ def test_mma_issue_rate_probe_runs_and_rejects_bad_arguments():
     assert lib.lq_mma_issue_rate(_lib.GEMM_A16W4_FWD, 0, 250, 1, 1024, 4, C.byref(cyc), None) == _lib.LQ_EINVAL     # N not a multiple of 16
     assert lib.lq_mma_issue_rate(_lib.GEMM_A16W4_FWD, 0, 256, 2, 1024, 4, C.byref(cyc), None) == _lib.LQ_EINVAL     # accumulators beyond 256 columns
     assert lib.lq_mma_issue_rate(_lib.GEMM_A8W8, 1, 256, 1, 1024, 4, C.byref(cyc), None) == _lib.LQ_EINVAL          # int8 has no tensor-memory A here
+
+
+@pytest.mark.parametrize("M,N", [(1, 4096), (2, 12288), (1, 1088), (12, 4160)])
+def test_a16w4_streaming_kernel_written_out_loop_equals_general_loop(ops, monkeypatch, M, N):
+    """K = 4096 with groups of 128 runs the streaming kernel's written-out loop (four chunks per warp, group parameters
+    as 8-byte loads, constant shared-memory offsets).  Same operations in the same order as the general loop: identical
+    bits, with and without bias, for more and for fewer row blocks than persistent CTAs, one and two token groups; the
+    fused gate|up + silu epilogue included."""
+    K = 4096
+    codes, sb, zb = make_w4_layer(ops, N, K, seed=11)
+    g = torch.Generator(device="cuda").manual_seed(N + M)
+    x = torch.randn(M, K, device="cuda", generator=g).to(torch.bfloat16)
+    bias = (torch.randn(N, device="cuda", generator=g) * 0.1).to(torch.bfloat16)
+    monkeypatch.setenv("LQ_SKINNY_STREAM_ALL", "1")             # (M = 12 takes the streaming kernel only when forced)
+    out = {}
+    for mode in ("written_out", "general"):
+        if mode == "general":
+            monkeypatch.setenv("LQ_SKINNY_NO_NC4", "1")
+        else:
+            monkeypatch.delenv("LQ_SKINNY_NO_NC4", raising=False)
+        ops._ws_need.clear()
+        y = ops.gemm_a16w4_fwd(x, codes, sb, zb, bias, N, K)
+        act = ops.gemm_a16w4_fwd_silu(x, codes, sb, zb, N // 2, K, hf_rounding=1) if N % 16 == 0 else None
+        out[mode] = (y, act)
+    assert torch.equal(out["written_out"][0], out["general"][0])
+    if out["general"][1] is not None:
+        assert torch.equal(out["written_out"][1], out["general"][1])
+    W = ops.a16w4_dequant(codes, sb, zb, (N, K), torch.bfloat16)
+    e_max, e_fro = rel_err(out["written_out"][0], x.float() @ W.float().t() + bias.float())
+    assert e_max < RTOL and e_fro < RTOL
+    ops._ws_need.clear()

@@ -208,22 +208,27 @@ constexpr int RB_CHUNK = 128;         // k per chunk
 // GC = chunks per quantization group (1: group 128, 2: group 256).  MT = 1 (up to 8 tokens) keeps 4 weight chunks
 // (2 rows x 16 bytes each) in flight per thread and prefetches the token fragment one chunk ahead; MT = 2 has twice
 // the token registers and runs with 2 chunks and no token prefetch instead of spilling (measured faster each way).
-template <int MT, int GC>
+// NC4: K = 4096 with groups of 128, i.e. exactly four chunks per warp.  The chunk loop is then written out (constant
+// trip count: every token and weight offset is a compile-time constant) and a row's four (scale, zero) pairs come as
+// two 8-byte loads.
+template <int MT, int GC, bool NC4 = false>
 __global__ void __launch_bounds__(RB_WARPS * 32, 2) k_skinny_rows(const SkinnyParams p) {
     constexpr int RB_PF = MT == 1 ? 4 : 2;
     constexpr bool XPF = MT == 1;
+    static_assert(!NC4 || GC == 1, "the written-out loop is for group 128");
     __shared__ float red[RB_WARPS][MT][128];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
     const bool pair = p.pair_stride > 0;
     const int row0 = blockIdx.x * (pair ? 8 : 16);
     const int ra = min(row0 + g, p.N - 1);                                          // clamped loads, guarded stores
     const int rb = pair ? p.pair_stride + ra : min(row0 + g + 8, p.N - 1);
-    const int gpr = p.K / (RB_CHUNK * GC);                                          // groups per weight row
-    const int gper = (gpr + RB_WARPS - 1) / RB_WARPS;
-    const int g_begin = min(gpr, warp * gper), n_groups = min(gpr, g_begin + gper) - g_begin;
+    const int gpr = NC4 ? 32 : p.K / (RB_CHUNK * GC);                               // groups per weight row
+    const int gper = NC4 ? 4 : (gpr + RB_WARPS - 1) / RB_WARPS;
+    const int g_begin = NC4 ? warp * 4 : min(gpr, warp * gper), n_groups = NC4 ? 4 : min(gpr, g_begin + gper) - g_begin;
     const int n_chunks = n_groups * GC;
-    const uint4* wa = reinterpret_cast<const uint4*>(p.qweight + (size_t)ra * (p.K / 2) + (size_t)g_begin * GC * (RB_CHUNK / 2)) + t;
-    const uint4* wb = reinterpret_cast<const uint4*>(p.qweight + (size_t)rb * (p.K / 2) + (size_t)g_begin * GC * (RB_CHUNK / 2)) + t;
+    const int row_bytes = NC4 ? 2048 : p.K / 2, row_elems = NC4 ? 4096 : p.K;
+    const uint4* wa = reinterpret_cast<const uint4*>(p.qweight + (size_t)ra * row_bytes + (size_t)g_begin * GC * (RB_CHUNK / 2)) + t;
+    const uint4* wb = reinterpret_cast<const uint4*>(p.qweight + (size_t)rb * row_bytes + (size_t)g_begin * GC * (RB_CHUNK / 2)) + t;
     const unsigned short* sca = reinterpret_cast<const unsigned short*>(p.scales) + (size_t)ra * gpr + g_begin;
     const unsigned short* scb = reinterpret_cast<const unsigned short*>(p.scales) + (size_t)rb * gpr + g_begin;
     const unsigned short* zpa = reinterpret_cast<const unsigned short*>(p.zeros) + (size_t)ra * gpr + g_begin;
@@ -232,7 +237,7 @@ __global__ void __launch_bounds__(RB_WARPS * 32, 2) k_skinny_rows(const SkinnyPa
     const uint4* xp[MT];
 #pragma unroll
     for (int m = 0; m < MT; ++m)
-        xp[m] = (m * 8 + g < p.M) ? reinterpret_cast<const uint4*>(p.x + (size_t)(m * 8 + g) * p.K + (size_t)g_begin * GC * RB_CHUNK + t * 32)
+        xp[m] = (m * 8 + g < p.M) ? reinterpret_cast<const uint4*>(p.x + (size_t)(m * 8 + g) * row_elems + (size_t)g_begin * GC * RB_CHUNK + t * 32)
                                   : nullptr;
 
     uint4 qa[RB_PF], qb[RB_PF];
@@ -247,10 +252,15 @@ __global__ void __launch_bounds__(RB_WARPS * 32, 2) k_skinny_rows(const SkinnyPa
 #pragma unroll
     for (int u = 0; u < RB_PF; ++u) {
         sza[u] = szb[u] = 0;
-        if (u % GC == 0 && u < n_chunks) {
+        if (!NC4 && u % GC == 0 && u < n_chunks) {
             sza[u] = (uint32_t)__ldg(sca + u / GC) | ((uint32_t)__ldg(zpa + u / GC) << 16);
             szb[u] = (uint32_t)__ldg(scb + u / GC) | ((uint32_t)__ldg(zpb + u / GC) << 16);
         }
+    }
+    uint2 s4a = make_uint2(0, 0), z4a = s4a, s4b = s4a, z4b = s4a;
+    if (NC4) {
+        s4a = __ldg(reinterpret_cast<const uint2*>(sca)); z4a = __ldg(reinterpret_cast<const uint2*>(zpa));
+        s4b = __ldg(reinterpret_cast<const uint2*>(scb)); z4b = __ldg(reinterpret_cast<const uint2*>(zpb));
     }
     pdl_launch_dependents();        // weight and group-parameter loads are issued: the next launch may start
     pdl_wait();                     // the tokens may be the previous launch's output
@@ -267,68 +277,106 @@ __global__ void __launch_bounds__(RB_WARPS * 32, 2) k_skinny_rows(const SkinnyPa
 #pragma unroll
         for (int i = 0; i < 4; ++i) { tot[m][i] = acc[m][0][i] = acc[m][1][i] = sx[m][i] = 0.0f; }
 
-    int grp = 0;
-    for (int cb = 0; cb < n_chunks; cb += RB_PF) {
+    // Two token groups (9..16 tokens): the zero point is subtracted from the codes before the MMA (exact: small
+    // integers in bf16) instead of being applied to token sums from an all-ones MMA.  That trades 16 of the 32
+    // mma.sync per chunk (the legacy tensor path runs 0.5 per cycle per SM) for 32 half-rate packed subtractions;
+    // with one token group the sums are the cheaper way.
+    constexpr bool ZSUB = MT == 2;
+    __nv_bfloat162 zp2a = __float2bfloat162_rn(0.0f), zp2b = zp2a;
+    auto sz_of_chunk = [&](const int c, const int u) {
+        if (NC4) {          // group c of the slice: bf16 half (c & 1) of word (c >> 1) of the packed loads
+            const uint32_t sw_a = c < 2 ? s4a.x : s4a.y, zw_a = c < 2 ? z4a.x : z4a.y;
+            const uint32_t sw_b = c < 2 ? s4b.x : s4b.y, zw_b = c < 2 ? z4b.x : z4b.y;
+            sz_a = ((c & 1) ? (sw_a >> 16) : (sw_a & 0xffffu)) | ((c & 1) ? (zw_a & 0xffff0000u) : (zw_a << 16));
+            sz_b = ((c & 1) ? (sw_b >> 16) : (sw_b & 0xffffu)) | ((c & 1) ? (zw_b & 0xffff0000u) : (zw_b << 16));
+        } else {
+            sz_a = sza[u]; sz_b = szb[u];
+        }
+        if (ZSUB) {         // (128 + z) in both halves
+            const __nv_bfloat162 c128 = __float2bfloat162_rn(128.0f);
+            zp2a = __hadd2_rn(sk_u2((sz_a & 0xffff0000u) | (sz_a >> 16)), c128);
+            zp2b = __hadd2_rn(sk_u2((sz_b & 0xffff0000u) | (sz_b >> 16)), c128);
+        }
+    };
+    // chunk c of the slice, held in ring slot u (u a compile-time constant at every call)
+    auto do_chunk = [&](const int c, const int u) {
+        const uint4 ca = qa[u], cq = qb[u];
+        if (u % GC == 0) sz_of_chunk(c, u);
+        if (c + RB_PF < n_chunks) {
+            qa[u] = __ldg(wa + (c + RB_PF) * 4); qb[u] = __ldg(wb + (c + RB_PF) * 4);
+            if (!NC4 && u % GC == 0) {
+                const int gn = (c + RB_PF) / GC;
+                sza[u] = (uint32_t)__ldg(sca + gn) | ((uint32_t)__ldg(zpa + gn) << 16);
+                szb[u] = (uint32_t)__ldg(scb + gn) | ((uint32_t)__ldg(zpb + gn) << 16);
+            }
+        }
+        uint4 xc[MT][4];
 #pragma unroll
-        for (int u = 0; u < RB_PF; ++u) {          // ring slot = unroll index: no runtime register indexing
-            const int c = cb + u;
-            if (c < n_chunks) {
-                const uint4 ca = qa[u], cq = qb[u];
-                if (u % GC == 0) { sz_a = sza[u]; sz_b = szb[u]; }
-                if (c + RB_PF < n_chunks) {
-                    qa[u] = __ldg(wa + (c + RB_PF) * 4); qb[u] = __ldg(wb + (c + RB_PF) * 4);
-                    if (u % GC == 0) {
-                        const int gn = (c + RB_PF) / GC;
-                        sza[u] = (uint32_t)__ldg(sca + gn) | ((uint32_t)__ldg(zpa + gn) << 16);
-                        szb[u] = (uint32_t)__ldg(scb + gn) | ((uint32_t)__ldg(zpb + gn) << 16);
-                    }
-                }
-                uint4 xc[MT][4];
+        for (int m = 0; m < MT; ++m)
 #pragma unroll
-                for (int m = 0; m < MT; ++m)
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        if (XPF) {
-                            xc[m][j] = xn[m][j];
-                            if (xp[m] && c + 1 < n_chunks) xn[m][j] = xp[m][(c + 1) * (RB_CHUNK * 2 / 16) + j];
-                        } else {
-                            xc[m][j] = xp[m] ? xp[m][c * (RB_CHUNK * 2 / 16) + j] : make_uint4(0, 0, 0, 0);
-                        }
-                    }
-                const uint32_t wsa[4] = {ca.x, ca.y, ca.z, ca.w}, wsb[4] = {cq.x, cq.y, cq.z, cq.w};
-#pragma unroll
-                for (int w = 0; w < 4; ++w) {      // one packed word = 8 k of each row = two MMA k-steps
-                    uint32_t pa[4], pb[4];
-                    extract_word(wsa[w], pa); extract_word(wsb[w], pb);
-#pragma unroll
-                    for (int m = 0; m < MT; ++m) {
-                        const uint4 v = xc[m][w];  // (k0,k1)(k2,k3)(k4,k5)(k6,k7) -> (k0,k4)(k1,k5)(k2,k6)(k3,k7)
-                        const uint32_t x0 = __byte_perm(v.x, v.z, 0x5410), x1 = __byte_perm(v.x, v.z, 0x7632);
-                        const uint32_t x2 = __byte_perm(v.y, v.w, 0x5410), x3 = __byte_perm(v.y, v.w, 0x7632);
-                        const uint32_t a0[4] = {pa[0], pb[0], pa[1], pb[1]}, a1[4] = {pa[2], pb[2], pa[3], pb[3]};
-                        mma_16816(acc[m][0], a0, x0, x1);
-                        mma_16816(acc[m][1], a1, x2, x3);
-                        mma_16816(sx[m], ones, x0, x1);
-                        mma_16816(sx[m], ones, x2, x3);
-                    }
-                }
-                if ((u + 1) % GC == 0) {
-                    // fold the group: s * (sum x (128 + q) - (128 + z) * sum x), then rotate the group parameters
-                    const float s_a = __uint_as_float(sz_a << 16), z_a = __uint_as_float(sz_a & 0xffff0000u) + 128.0f;
-                    const float s_b = __uint_as_float(sz_b << 16), z_b = __uint_as_float(sz_b & 0xffff0000u) + 128.0f;
-#pragma unroll
-                    for (int m = 0; m < MT; ++m) {
-                        const float sx0 = sx[m][0], sx1 = sx[m][1];   // tokens 2t, 2t+1 (identical in every row of the ones tile)
-                        tot[m][0] = fmaf(s_a, (acc[m][0][0] + acc[m][1][0]) - z_a * sx0, tot[m][0]);
-                        tot[m][1] = fmaf(s_a, (acc[m][0][1] + acc[m][1][1]) - z_a * sx1, tot[m][1]);
-                        tot[m][2] = fmaf(s_b, (acc[m][0][2] + acc[m][1][2]) - z_b * sx0, tot[m][2]);
-                        tot[m][3] = fmaf(s_b, (acc[m][0][3] + acc[m][1][3]) - z_b * sx1, tot[m][3]);
-#pragma unroll
-                        for (int i = 0; i < 4; ++i) { acc[m][0][i] = acc[m][1][i] = sx[m][i] = 0.0f; }
-                    }
-                    ++grp;
+            for (int j = 0; j < 4; ++j) {
+                if (XPF) {
+                    xc[m][j] = xn[m][j];
+                    if (xp[m] && c + 1 < n_chunks) xn[m][j] = xp[m][(c + 1) * (RB_CHUNK * 2 / 16) + j];
+                } else {
+                    xc[m][j] = xp[m] ? xp[m][c * (RB_CHUNK * 2 / 16) + j] : make_uint4(0, 0, 0, 0);
                 }
             }
+        const uint32_t wsa[4] = {ca.x, ca.y, ca.z, ca.w}, wsb[4] = {cq.x, cq.y, cq.z, cq.w};
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {      // one packed word = 8 k of each row = two MMA k-steps
+            uint32_t pa[4], pb[4];
+            extract_word(wsa[w], pa); extract_word(wsb[w], pb);
+            if (ZSUB) {
+#pragma unroll
+                for (int i = 0; i < 4; ++i) { pa[i] = sk_bf2(__hsub2_rn(sk_u2(pa[i]), zp2a)); pb[i] = sk_bf2(__hsub2_rn(sk_u2(pb[i]), zp2b)); }
+            }
+#pragma unroll
+            for (int m = 0; m < MT; ++m) {
+                const uint4 v = xc[m][w];  // (k0,k1)(k2,k3)(k4,k5)(k6,k7) -> (k0,k4)(k1,k5)(k2,k6)(k3,k7)
+                const uint32_t x0 = __byte_perm(v.x, v.z, 0x5410), x1 = __byte_perm(v.x, v.z, 0x7632);
+                const uint32_t x2 = __byte_perm(v.y, v.w, 0x5410), x3 = __byte_perm(v.y, v.w, 0x7632);
+                const uint32_t a0[4] = {pa[0], pb[0], pa[1], pb[1]}, a1[4] = {pa[2], pb[2], pa[3], pb[3]};
+                mma_16816(acc[m][0], a0, x0, x1);
+                mma_16816(acc[m][1], a1, x2, x3);
+                if (!ZSUB) {
+                    mma_16816(sx[m], ones, x0, x1);
+                    mma_16816(sx[m], ones, x2, x3);
+                }
+            }
+        }
+        if ((u + 1) % GC == 0) {
+            // fold the group: s * (sum x (128 + q) - (128 + z) * sum x), or s * sum x (q - z) with the zero point
+            // already subtracted
+            const float s_a = __uint_as_float(sz_a << 16), z_a = __uint_as_float(sz_a & 0xffff0000u) + 128.0f;
+            const float s_b = __uint_as_float(sz_b << 16), z_b = __uint_as_float(sz_b & 0xffff0000u) + 128.0f;
+#pragma unroll
+            for (int m = 0; m < MT; ++m) {
+                if (ZSUB) {
+                    tot[m][0] = fmaf(s_a, acc[m][0][0] + acc[m][1][0], tot[m][0]);
+                    tot[m][1] = fmaf(s_a, acc[m][0][1] + acc[m][1][1], tot[m][1]);
+                    tot[m][2] = fmaf(s_b, acc[m][0][2] + acc[m][1][2], tot[m][2]);
+                    tot[m][3] = fmaf(s_b, acc[m][0][3] + acc[m][1][3], tot[m][3]);
+                } else {
+                    const float sx0 = sx[m][0], sx1 = sx[m][1];   // tokens 2t, 2t+1 (identical in every row of the ones tile)
+                    tot[m][0] = fmaf(s_a, (acc[m][0][0] + acc[m][1][0]) - z_a * sx0, tot[m][0]);
+                    tot[m][1] = fmaf(s_a, (acc[m][0][1] + acc[m][1][1]) - z_a * sx1, tot[m][1]);
+                    tot[m][2] = fmaf(s_b, (acc[m][0][2] + acc[m][1][2]) - z_b * sx0, tot[m][2]);
+                    tot[m][3] = fmaf(s_b, (acc[m][0][3] + acc[m][1][3]) - z_b * sx1, tot[m][3]);
+                }
+#pragma unroll
+                for (int i = 0; i < 4; ++i) { acc[m][0][i] = acc[m][1][i] = sx[m][i] = 0.0f; }
+            }
+        }
+    };
+    if constexpr (NC4) {
+#pragma unroll
+        for (int c = 0; c < 4; ++c) do_chunk(c, c % RB_PF);
+    } else {
+        for (int cb = 0; cb < n_chunks; cb += RB_PF) {
+#pragma unroll
+            for (int u = 0; u < RB_PF; ++u)          // ring slot = unroll index: no runtime register indexing
+                if (cb + u < n_chunks) do_chunk(cb + u, u);
         }
     }
 #pragma unroll
@@ -670,6 +718,14 @@ int launch_skinny_rows(const SkinnyParams& p, cudaStream_t st) {
     const int rpb = p.pair_stride > 0 ? 8 : 16;
     const unsigned grid = (unsigned)((p.N + rpb - 1) / rpb);
     const bool g128 = p.group == 128;
+    // K = 4096 with groups of 128: the written-out loop (scales / zeros are read as 8-byte words there)
+    const bool nc4 = g128 && p.K == 4096 && !getenv("LQ_SKINNY_NO_NC4") &&
+                     (reinterpret_cast<uintptr_t>(p.scales) & 7) == 0 && (reinterpret_cast<uintptr_t>(p.zeros) & 7) == 0;
+    if (nc4) {
+        if (p.M <= 8) launch_pdl(k_skinny_rows<1, 1, true>, dim3(grid), RB_WARPS * 32, 0, st, p);
+        else launch_pdl(k_skinny_rows<2, 1, true>, dim3(grid), RB_WARPS * 32, 0, st, p);
+        return check_launch("k_skinny_rows");
+    }
     if (p.M <= 8) { if (g128) launch_pdl(k_skinny_rows<1, 1>, dim3(grid), RB_WARPS * 32, 0, st, p); else launch_pdl(k_skinny_rows<1, 2>, dim3(grid), RB_WARPS * 32, 0, st, p); }
     else { if (g128) launch_pdl(k_skinny_rows<2, 1>, dim3(grid), RB_WARPS * 32, 0, st, p); else launch_pdl(k_skinny_rows<2, 2>, dim3(grid), RB_WARPS * 32, 0, st, p); }
     return check_launch("k_skinny_rows");

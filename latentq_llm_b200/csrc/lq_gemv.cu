@@ -270,18 +270,16 @@ __global__ void __launch_bounds__(RB_WARPS * 32, 2) k_skinny_rows(const SkinnyPa
 #pragma unroll
         for (int j = 0; j < 4; ++j) xn[m][j] = (XPF && xp[m] && n_chunks > 0) ? xp[m][j] : make_uint4(0, 0, 0, 0);
 
-    const uint32_t ones[4] = {0x3F803F80u, 0x3F803F80u, 0x3F803F80u, 0x3F803F80u};   // bf16 1.0
-    float tot[MT][4], acc[MT][2][4], sx[MT][4];     // two accumulator chains per token group, sx from an all-ones A
+    float tot[MT][4], acc[MT][2][4];     // two accumulator chains per token group
 #pragma unroll
     for (int m = 0; m < MT; ++m)
 #pragma unroll
-        for (int i = 0; i < 4; ++i) { tot[m][i] = acc[m][0][i] = acc[m][1][i] = sx[m][i] = 0.0f; }
+        for (int i = 0; i < 4; ++i) { tot[m][i] = acc[m][0][i] = acc[m][1][i] = 0.0f; }
 
-    // Two token groups (9..16 tokens): the zero point is subtracted from the codes before the MMA (exact: small
-    // integers in bf16) instead of being applied to token sums from an all-ones MMA.  That trades 16 of the 32
-    // mma.sync per chunk (the legacy tensor path runs 0.5 per cycle per SM) for 32 half-rate packed subtractions;
-    // with one token group the sums are the cheaper way.
-    constexpr bool ZSUB = MT == 2;
+    // The zero point is subtracted from the codes before the MMA (exact: small integers in bf16; zero points are
+    // integer-valued) instead of being applied to token sums from an all-ones MMA: that trades half of the mma.sync
+    // of a chunk (the legacy tensor path runs 0.5 per cycle per SM) for 32 half-rate packed subtractions.  Measured
+    // -11 % at 16 tokens, -2 % at 4..8, and the group sum loses no bits to the cancellation of 128 * sum(x).
     __nv_bfloat162 zp2a = __float2bfloat162_rn(0.0f), zp2b = zp2a;
     auto sz_of_chunk = [&](const int c, const int u) {
         if (NC4) {          // group c of the slice: bf16 half (c & 1) of word (c >> 1) of the packed loads
@@ -292,11 +290,9 @@ __global__ void __launch_bounds__(RB_WARPS * 32, 2) k_skinny_rows(const SkinnyPa
         } else {
             sz_a = sza[u]; sz_b = szb[u];
         }
-        if (ZSUB) {         // (128 + z) in both halves
-            const __nv_bfloat162 c128 = __float2bfloat162_rn(128.0f);
-            zp2a = __hadd2_rn(sk_u2((sz_a & 0xffff0000u) | (sz_a >> 16)), c128);
-            zp2b = __hadd2_rn(sk_u2((sz_b & 0xffff0000u) | (sz_b >> 16)), c128);
-        }
+        const __nv_bfloat162 c128 = __float2bfloat162_rn(128.0f);          // (128 + z) in both halves
+        zp2a = __hadd2_rn(sk_u2((sz_a & 0xffff0000u) | (sz_a >> 16)), c128);
+        zp2b = __hadd2_rn(sk_u2((sz_b & 0xffff0000u) | (sz_b >> 16)), c128);
     };
     // chunk c of the slice, held in ring slot u (u a compile-time constant at every call)
     auto do_chunk = [&](const int c, const int u) {
@@ -327,10 +323,8 @@ __global__ void __launch_bounds__(RB_WARPS * 32, 2) k_skinny_rows(const SkinnyPa
         for (int w = 0; w < 4; ++w) {      // one packed word = 8 k of each row = two MMA k-steps
             uint32_t pa[4], pb[4];
             extract_word(wsa[w], pa); extract_word(wsb[w], pb);
-            if (ZSUB) {
 #pragma unroll
-                for (int i = 0; i < 4; ++i) { pa[i] = sk_bf2(__hsub2_rn(sk_u2(pa[i]), zp2a)); pb[i] = sk_bf2(__hsub2_rn(sk_u2(pb[i]), zp2b)); }
-            }
+            for (int i = 0; i < 4; ++i) { pa[i] = sk_bf2(__hsub2_rn(sk_u2(pa[i]), zp2a)); pb[i] = sk_bf2(__hsub2_rn(sk_u2(pb[i]), zp2b)); }
 #pragma unroll
             for (int m = 0; m < MT; ++m) {
                 const uint4 v = xc[m][w];  // (k0,k1)(k2,k3)(k4,k5)(k6,k7) -> (k0,k4)(k1,k5)(k2,k6)(k3,k7)
@@ -339,33 +333,19 @@ __global__ void __launch_bounds__(RB_WARPS * 32, 2) k_skinny_rows(const SkinnyPa
                 const uint32_t a0[4] = {pa[0], pb[0], pa[1], pb[1]}, a1[4] = {pa[2], pb[2], pa[3], pb[3]};
                 mma_16816(acc[m][0], a0, x0, x1);
                 mma_16816(acc[m][1], a1, x2, x3);
-                if (!ZSUB) {
-                    mma_16816(sx[m], ones, x0, x1);
-                    mma_16816(sx[m], ones, x2, x3);
-                }
             }
         }
         if ((u + 1) % GC == 0) {
-            // fold the group: s * (sum x (128 + q) - (128 + z) * sum x), or s * sum x (q - z) with the zero point
-            // already subtracted
-            const float s_a = __uint_as_float(sz_a << 16), z_a = __uint_as_float(sz_a & 0xffff0000u) + 128.0f;
-            const float s_b = __uint_as_float(sz_b << 16), z_b = __uint_as_float(sz_b & 0xffff0000u) + 128.0f;
+            // fold the group: tot += s * sum x (q - z)
+            const float s_a = __uint_as_float(sz_a << 16), s_b = __uint_as_float(sz_b << 16);
 #pragma unroll
             for (int m = 0; m < MT; ++m) {
-                if (ZSUB) {
-                    tot[m][0] = fmaf(s_a, acc[m][0][0] + acc[m][1][0], tot[m][0]);
-                    tot[m][1] = fmaf(s_a, acc[m][0][1] + acc[m][1][1], tot[m][1]);
-                    tot[m][2] = fmaf(s_b, acc[m][0][2] + acc[m][1][2], tot[m][2]);
-                    tot[m][3] = fmaf(s_b, acc[m][0][3] + acc[m][1][3], tot[m][3]);
-                } else {
-                    const float sx0 = sx[m][0], sx1 = sx[m][1];   // tokens 2t, 2t+1 (identical in every row of the ones tile)
-                    tot[m][0] = fmaf(s_a, (acc[m][0][0] + acc[m][1][0]) - z_a * sx0, tot[m][0]);
-                    tot[m][1] = fmaf(s_a, (acc[m][0][1] + acc[m][1][1]) - z_a * sx1, tot[m][1]);
-                    tot[m][2] = fmaf(s_b, (acc[m][0][2] + acc[m][1][2]) - z_b * sx0, tot[m][2]);
-                    tot[m][3] = fmaf(s_b, (acc[m][0][3] + acc[m][1][3]) - z_b * sx1, tot[m][3]);
-                }
+                tot[m][0] = fmaf(s_a, acc[m][0][0] + acc[m][1][0], tot[m][0]);
+                tot[m][1] = fmaf(s_a, acc[m][0][1] + acc[m][1][1], tot[m][1]);
+                tot[m][2] = fmaf(s_b, acc[m][0][2] + acc[m][1][2], tot[m][2]);
+                tot[m][3] = fmaf(s_b, acc[m][0][3] + acc[m][1][3], tot[m][3]);
 #pragma unroll
-                for (int i = 0; i < 4; ++i) { acc[m][0][i] = acc[m][1][i] = sx[m][i] = 0.0f; }
+                for (int i = 0; i < 4; ++i) { acc[m][0][i] = acc[m][1][i] = 0.0f; }
             }
         }
     };

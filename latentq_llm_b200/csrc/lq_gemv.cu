@@ -211,11 +211,15 @@ constexpr int RB_CHUNK = 128;         // k per chunk
 // NC4: K = 4096 with groups of 128, i.e. exactly four chunks per warp.  The chunk loop is then written out (constant
 // trip count: every token and weight offset is a compile-time constant) and a row's four (scale, zero) pairs come as
 // two 8-byte loads.
-template <int MT, int GC, bool NC4 = false>
+// NCH = 11: K = 11008 (86 groups: eleven chunks per warp, nine in the last warp): the same loop written out for up
+// to eleven chunks, each guarded by the warp's own count; group parameters stay 2-byte loads (rows of 86 groups are
+// not 8-byte aligned) but at constant offsets.
+template <int MT, int GC, int NCH = 0>
 __global__ void __launch_bounds__(RB_WARPS * 32, 2) k_skinny_rows(const SkinnyParams p) {
     constexpr int RB_PF = MT == 1 ? 4 : 2;
     constexpr bool XPF = MT == 1;
-    static_assert(!NC4 || GC == 1, "the written-out loop is for group 128");
+    constexpr bool NC4 = NCH == 4;
+    static_assert(NCH == 0 || GC == 1, "the written-out loops are for group 128");
     __shared__ float red[RB_WARPS][MT][128];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
     const bool pair = p.pair_stride > 0;
@@ -352,6 +356,10 @@ __global__ void __launch_bounds__(RB_WARPS * 32, 2) k_skinny_rows(const SkinnyPa
     if constexpr (NC4) {
 #pragma unroll
         for (int c = 0; c < 4; ++c) do_chunk(c, c % RB_PF);
+    } else if constexpr (NCH > 0) {
+#pragma unroll
+        for (int c = 0; c < NCH; ++c)
+            if (c < n_chunks) do_chunk(c, c % RB_PF);
     } else {
         for (int cb = 0; cb < n_chunks; cb += RB_PF) {
 #pragma unroll
@@ -410,10 +418,13 @@ __global__ void __launch_bounds__(RB_WARPS * 32, 2) k_skinny_rows(const SkinnyPa
 // u of the next row block, the four (scale, zero) pairs of a row come as two 8-byte loads per row block, and every
 // shared-memory address is a constant offset from a per-warp base, which removes the index arithmetic that made up
 // about half of the general loop's instructions.
-template <int MT, int GC, bool NC4>
+// NCH = 11: K = 11008 (eleven chunks per warp, nine in the last): written out the same way with every chunk guarded by
+// the warp's own count and 2-byte group-parameter loads at constant offsets.
+template <int MT, int GC, int NCH>
 __global__ void __launch_bounds__(RB_WARPS * 32, LQ_GEMV_MINB) k_skinny_stream(const SkinnyParams p, const int x_stride) {
     constexpr int PF = LQ_GEMV_PF;
-    static_assert(!NC4 || (GC == 1 && PF == 4), "the written-out loop is for group 128 and a ring of four chunks");
+    constexpr bool NC4 = NCH == 4;
+    static_assert(NCH == 0 || (GC == 1 && PF == 4), "the written-out loops are for group 128 and a ring of four chunks");
     extern __shared__ __align__(16) uint8_t ss_smem[];
     uint4* xs = reinterpret_cast<uint4*>(ss_smem);                                               // [M][x_stride]
     float* sxs = reinterpret_cast<float*>(ss_smem + (size_t)p.M * x_stride * 16);               // [groups][8 * MT]
@@ -561,8 +572,60 @@ __global__ void __launch_bounds__(RB_WARPS * 32, LQ_GEMV_MINB) k_skinny_stream(c
             }
             s4a = ns4a; z4a = nz4a; s4b = ns4b; z4b = nz4b;
         }
+        if constexpr (NCH > 4) {
+            // group parameters of this block and the next at constant offsets from one pointer per row and array
+            const unsigned short *csa = sc_all + (size_t)ra * gpr + g_begin, *cza = zp_all + (size_t)ra * gpr + g_begin;
+            const unsigned short *csb = sc_all + (size_t)rb * gpr + g_begin, *czb = zp_all + (size_t)rb * gpr + g_begin;
+            const unsigned short *nsa = sc_all + (size_t)na_row * gpr + g_begin, *nza = zp_all + (size_t)na_row * gpr + g_begin;
+            const unsigned short *nsb = sc_all + (size_t)nb_row * gpr + g_begin, *nzb = zp_all + (size_t)nb_row * gpr + g_begin;
+#pragma unroll
+            for (int c = 0; c < NCH; ++c) {
+                const int u = c & 3;
+                if (c < n_chunks) {
+                    const uint4 ca = qa[u], cq = qb[u];
+                    sz_a = sza[u]; sz_b = szb[u];
+                    if (c + 4 < n_chunks) {
+                        qa[u] = __ldg(wa + (c + 4) * 4); qb[u] = __ldg(wb + (c + 4) * 4);
+                        sza[u] = (uint32_t)__ldg(csa + c + 4) | ((uint32_t)__ldg(cza + c + 4) << 16);
+                        szb[u] = (uint32_t)__ldg(csb + c + 4) | ((uint32_t)__ldg(czb + c + 4) << 16);
+                    } else if (has_next) {                                           // slot u of the next row block
+                        qa[u] = __ldg(na + u * 4); qb[u] = __ldg(nb + u * 4);
+                        sza[u] = (uint32_t)__ldg(nsa + u) | ((uint32_t)__ldg(nza + u) << 16);
+                        szb[u] = (uint32_t)__ldg(nsb + u) | ((uint32_t)__ldg(nzb + u) << 16);
+                    }
+                    const uint32_t wsa[4] = {ca.x, ca.y, ca.z, ca.w}, wsb[4] = {cq.x, cq.y, cq.z, cq.w};
+#pragma unroll
+                    for (int w = 0; w < 4; ++w) {
+                        uint32_t pa[4], pb[4];
+                        extract_word(wsa[w], pa); extract_word(wsb[w], pb);
+                        const uint32_t a0[4] = {pa[0], pb[0], pa[1], pb[1]}, a1[4] = {pa[2], pb[2], pa[3], pb[3]};
+#pragma unroll
+                        for (int m = 0; m < MT; ++m) {
+                            const uint4 f = xbase[m][c * 16 + w * 4];
+                            if (w == 0) {
+                                mma_16816_start(acc[m][0], a0, f.x, f.y);
+                                mma_16816_start(acc[m][1], a1, f.z, f.w);
+                            } else {
+                                mma_16816(acc[m][0], a0, f.x, f.y);
+                                mma_16816(acc[m][1], a1, f.z, f.w);
+                            }
+                        }
+                    }
+                    const float s_a = __uint_as_float(sz_a << 16), z_a = __uint_as_float(sz_a & 0xffff0000u) + 128.0f;
+                    const float s_b = __uint_as_float(sz_b << 16), z_b = __uint_as_float(sz_b & 0xffff0000u) + 128.0f;
+#pragma unroll
+                    for (int m = 0; m < MT; ++m) {
+                        const float2 sx = *reinterpret_cast<const float2*>(sxbase + c * (8 * MT) + m * 8);
+                        tot[m][0] = fmaf(s_a, (acc[m][0][0] + acc[m][1][0]) - z_a * sx.x, tot[m][0]);
+                        tot[m][1] = fmaf(s_a, (acc[m][0][1] + acc[m][1][1]) - z_a * sx.y, tot[m][1]);
+                        tot[m][2] = fmaf(s_b, (acc[m][0][2] + acc[m][1][2]) - z_b * sx.x, tot[m][2]);
+                        tot[m][3] = fmaf(s_b, (acc[m][0][3] + acc[m][1][3]) - z_b * sx.y, tot[m][3]);
+                    }
+                }
+            }
+        }
         int grp = 0;
-        for (int cb = 0; !NC4 && cb < n_chunks; cb += PF) {
+        for (int cb = 0; NCH == 0 && cb < n_chunks; cb += PF) {
 #pragma unroll
             for (int u = 0; u < PF; ++u) {
                 const int c = cb + u;
@@ -651,18 +714,18 @@ static bool skinny_stream_supported(int64_t K, int group) {
     return gpr - (RB_WARPS - 1) * gper >= 2;
 }
 
-template <int MT, int GC, bool NC4 = false>
+template <int MT, int GC, int NCH = 0>
 static int launch_skinny_stream_v(const SkinnyParams& p, int x_stride, size_t smem, unsigned grid, cudaStream_t st) {
     static bool attr_done[64] = {};
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev < 0 || dev >= 64) return LQ_EUNSUPPORTED;
     if (!attr_done[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(k_skinny_stream<MT, GC, NC4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
+        cudaError_t e = cudaFuncSetAttribute(k_skinny_stream<MT, GC, NCH>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
         if (e != cudaSuccess) { set_cuda_error(e, "cudaFuncSetAttribute(k_skinny_stream)"); return LQ_ECUDA; }
         attr_done[dev] = true;
     }
-    launch_pdl(k_skinny_stream<MT, GC, NC4>, dim3(grid), RB_WARPS * 32, smem, st, p, x_stride);
+    launch_pdl(k_skinny_stream<MT, GC, NCH>, dim3(grid), RB_WARPS * 32, smem, st, p, x_stride);
     return check_launch("k_skinny_stream");
 }
 
@@ -682,7 +745,9 @@ static int launch_skinny_stream(const SkinnyParams& p, cudaStream_t st) {
     // K = 4096 with groups of 128: the written-out loop (scales / zeros are read as 8-byte words there)
     const bool nc4 = gc == 1 && p.K == 4096 && LQ_GEMV_PF == 4 && !getenv("LQ_SKINNY_NO_NC4") &&
                      (reinterpret_cast<uintptr_t>(p.scales) & 7) == 0 && (reinterpret_cast<uintptr_t>(p.zeros) & 7) == 0;
-    if (nc4) return mt == 1 ? launch_skinny_stream_v<1, 1, true>(p, x_stride, smem, grid, st) : launch_skinny_stream_v<2, 1, true>(p, x_stride, smem, grid, st);
+    if (nc4) return mt == 1 ? launch_skinny_stream_v<1, 1, 4>(p, x_stride, smem, grid, st) : launch_skinny_stream_v<2, 1, 4>(p, x_stride, smem, grid, st);
+    if (gc == 1 && p.K == 11008 && LQ_GEMV_PF == 4 && !getenv("LQ_SKINNY_NO_NC4"))      // eleven chunks per warp, written out
+        return mt == 1 ? launch_skinny_stream_v<1, 1, 11>(p, x_stride, smem, grid, st) : launch_skinny_stream_v<2, 1, 11>(p, x_stride, smem, grid, st);
     if (mt == 1) return gc == 1 ? launch_skinny_stream_v<1, 1>(p, x_stride, smem, grid, st) : launch_skinny_stream_v<1, 2>(p, x_stride, smem, grid, st);
     return gc == 1 ? launch_skinny_stream_v<2, 1>(p, x_stride, smem, grid, st) : launch_skinny_stream_v<2, 2>(p, x_stride, smem, grid, st);
 }
@@ -702,8 +767,13 @@ int launch_skinny_rows(const SkinnyParams& p, cudaStream_t st) {
     const bool nc4 = g128 && p.K == 4096 && !getenv("LQ_SKINNY_NO_NC4") &&
                      (reinterpret_cast<uintptr_t>(p.scales) & 7) == 0 && (reinterpret_cast<uintptr_t>(p.zeros) & 7) == 0;
     if (nc4) {
-        if (p.M <= 8) launch_pdl(k_skinny_rows<1, 1, true>, dim3(grid), RB_WARPS * 32, 0, st, p);
-        else launch_pdl(k_skinny_rows<2, 1, true>, dim3(grid), RB_WARPS * 32, 0, st, p);
+        if (p.M <= 8) launch_pdl(k_skinny_rows<1, 1, 4>, dim3(grid), RB_WARPS * 32, 0, st, p);
+        else launch_pdl(k_skinny_rows<2, 1, 4>, dim3(grid), RB_WARPS * 32, 0, st, p);
+        return check_launch("k_skinny_rows");
+    }
+    if (g128 && p.K == 11008 && !getenv("LQ_SKINNY_NO_NC4")) {          // eleven chunks per warp, written out
+        if (p.M <= 8) launch_pdl(k_skinny_rows<1, 1, 11>, dim3(grid), RB_WARPS * 32, 0, st, p);
+        else launch_pdl(k_skinny_rows<2, 1, 11>, dim3(grid), RB_WARPS * 32, 0, st, p);
         return check_launch("k_skinny_rows");
     }
     if (p.M <= 8) { if (g128) launch_pdl(k_skinny_rows<1, 1>, dim3(grid), RB_WARPS * 32, 0, st, p); else launch_pdl(k_skinny_rows<1, 2>, dim3(grid), RB_WARPS * 32, 0, st, p); }

@@ -323,14 +323,15 @@ def test_mma_issue_rate_probe_runs_and_rejects_bad_arguments():
     assert lib.lq_mma_issue_rate(_lib.GEMM_A8W8, 1, 256, 1, 1024, 4, C.byref(cyc), None) == _lib.LQ_EINVAL          # int8 has no tensor-memory A here
 
 
+@pytest.mark.parametrize("K", [4096, 11008])
 @pytest.mark.parametrize("M,N,force_stream", [(1, 4096, True), (2, 12288, True), (1, 1088, True), (12, 4160, True),
                                               (5, 4096, False), (16, 12288, False), (9, 1088, False), (3, 4160, False)])
-def test_a16w4_decode_kernels_written_out_loop_equals_general_loop(ops, monkeypatch, M, N, force_stream):
+def test_a16w4_decode_kernels_written_out_loop_equals_general_loop(ops, monkeypatch, M, N, force_stream, K):
     """K = 4096 with groups of 128 runs the decode kernels' written-out loops (four chunks per warp, group parameters
     as 8-byte loads, constant offsets): the streaming kernel (one or two tokens, or forced) and the row-block kernel.
     Same operations in the same order as the general loops: identical bits, with bias, for more and for fewer row
-    blocks than persistent CTAs, one and two token groups; the fused gate|up + silu epilogue included."""
-    K = 4096
+    blocks than persistent CTAs, one and two token groups; the fused gate|up + silu epilogue included.  K = 11008 (eleven
+    chunks per warp, nine in the last one) has written-out loops of its own."""
     codes, sb, zb = make_w4_layer(ops, N, K, seed=11)
     g = torch.Generator(device="cuda").manual_seed(N + M)
     x = torch.randn(M, K, device="cuda", generator=g).to(torch.bfloat16)

@@ -77,6 +77,7 @@ struct GemmParams {
     int sk_q, sk_r;                // tail units / helpers and tail units % helpers (helper h starts at unit h * q + h * r / helpers)
     int sk_pmax;                   // partial-sum slots per shared tile
     int accumulate;                // weight gradient: out += product (rounded once from the fp32 sum) instead of out = product
+    const uint4* qpt;              // QPT kernels: per-column group parameters, packed for the dequant (see k_w4_qp_transpose)
 };
 
 // One CTA's share of the work as a sequence of segments (a tile and a range of its k-blocks).
@@ -226,13 +227,100 @@ __device__ __forceinline__ uint4 dequant8(uint32_t w, __nv_bfloat162 z128, __nv_
     return o;
 }
 
+// The same with a scale and a zero point of its own for every code: sp / zp hold (s, z + 128) of the pairs
+// (c0,c4) (c1,c5) (c2,c6) (c3,c7) in x, y, z, w - the order the extraction produces.
+__device__ __forceinline__ uint4 dequant8t(uint32_t w, const uint4& zp, const uint4& sp) {
+    const uint32_t MAGIC = 0x43004300u, MASK = 0x000F000Fu;
+    uint32_t p15 = (w & MASK) | MAGIC;           // (c1, c5)
+    uint32_t p04 = ((w >> 4) & MASK) | MAGIC;    // (c0, c4)
+    uint32_t p37 = ((w >> 8) & MASK) | MAGIC;    // (c3, c7)
+    uint32_t p26 = ((w >> 12) & MASK) | MAGIC;   // (c2, c6)
+    uint32_t d15 = bf2_as_u32(__hmul2_rn(__hsub2_rn(u32_as_bf2(p15), u32_as_bf2(zp.y)), u32_as_bf2(sp.y)));
+    uint32_t d04 = bf2_as_u32(__hmul2_rn(__hsub2_rn(u32_as_bf2(p04), u32_as_bf2(zp.x)), u32_as_bf2(sp.x)));
+    uint32_t d37 = bf2_as_u32(__hmul2_rn(__hsub2_rn(u32_as_bf2(p37), u32_as_bf2(zp.w)), u32_as_bf2(sp.w)));
+    uint32_t d26 = bf2_as_u32(__hmul2_rn(__hsub2_rn(u32_as_bf2(p26), u32_as_bf2(zp.z)), u32_as_bf2(sp.z)));
+    uint4 o;
+    o.x = __byte_perm(d04, d15, 0x5410);   // (c0, c1)
+    o.y = __byte_perm(d26, d37, 0x5410);   // (c2, c3)
+    o.z = __byte_perm(d04, d15, 0x7632);   // (c4, c5)
+    o.w = __byte_perm(d26, d37, 0x7632);   // (c6, c7)
+    return o;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Transposed copy of a packed A16W4 weight for the grad-input GEMM.
+//   dx[M,K] = dy[M,N] . W[N,K] contracts over the weight's ROWS.  With the weight as stored, the tensor-memory
+//   placement of the dequantised tile would need a nibble-wise gather over 64 rows per thread, and the
+//   shared-memory placement is bound by the shared-memory port (171 instead of 138 cycles per MMA).  With a
+//   transposed copy Wt[K, N] (codes packed along n) the grad-input IS the forward kernel: dx = dy . Wt^T.  Scales
+//   and zero points then differ per contraction element (they belong to (n, k / group)), so they are laid out
+//   per (k group, 8 n) in exactly the order dequant8t consumes: 32 bytes = (s04 s15 s26 s37)(z04 z15 z26 z37), z
+//   already offset by 128.  Both kernels run once per grad-input call (the weights may have changed since the last).
+// ---------------------------------------------------------------------------------------------
+// One CTA transposes a tile of 64 n x 256 k: codes go to shared memory as words of four consecutive k (one byte per
+// code), a thread then owns four k and sixteen n: (even n << 4 | odd n) byte-wise gives the packed output bytes of all
+// four k at once, three byte permutes per output word sort them into the four rows it writes (8 bytes each; the four
+// threads of a k share a 32-byte segment).
+__global__ void __launch_bounds__(256) k_w4_transpose(const uint8_t* __restrict__ in, uint8_t* __restrict__ out, int N, int K) {
+    __shared__ uint32_t t[64][65];                        // [n][k / 4], one word of padding
+    const int n0 = blockIdx.y * 64, k0 = blockIdx.x * 256, i = threadIdx.x;
+    {
+        const int n = i >> 2, seg = i & 3;                // 32 bytes = 64 codes of row n0 + n, k = k0 + seg * 64 ..
+        const uint4* src = reinterpret_cast<const uint4*>(in + (size_t)(n0 + n) * (K / 2) + (k0 / 2) + seg * 32);
+        const uint4 v0 = src[0], v1 = src[1];
+        const uint32_t w[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+#pragma unroll
+        for (int h = 0; h < 8; ++h) {                     // byte j of the word: codes 2j (high nibble), 2j + 1 (low)
+            const uint32_t hi = (w[h] >> 4) & 0x0F0F0F0Fu, lo = w[h] & 0x0F0F0F0Fu;
+            t[n][seg * 16 + h * 2 + 0] = __byte_perm(hi, lo, 0x5140);      // c0 c1 c2 c3 = hi.b0 lo.b0 hi.b1 lo.b1
+            t[n][seg * 16 + h * 2 + 1] = __byte_perm(hi, lo, 0x7362);      // c4 c5 c6 c7
+        }
+    }
+    __syncthreads();
+    {
+        const int k4 = i >> 2, seg = i & 3;               // k = k0 + 4 k4 .. + 3, n = n0 + seg * 16 ..
+        uint32_t v[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[j] = (t[seg * 16 + 2 * j][k4] << 4) | t[seg * 16 + 2 * j + 1][k4];
+        const uint32_t a01 = __byte_perm(v[0], v[1], 0x5140), b01 = __byte_perm(v[0], v[1], 0x7362);   // bytes (k0 k0 k1 k1) / (k2 k2 k3 k3) of v0, v1
+        const uint32_t a23 = __byte_perm(v[2], v[3], 0x5140), b23 = __byte_perm(v[2], v[3], 0x7362);
+        const uint32_t a45 = __byte_perm(v[4], v[5], 0x5140), b45 = __byte_perm(v[4], v[5], 0x7362);
+        const uint32_t a67 = __byte_perm(v[6], v[7], 0x5140), b67 = __byte_perm(v[6], v[7], 0x7362);
+        uint8_t* dst = out + (size_t)(k0 + 4 * k4) * (N / 2) + (n0 / 2) + seg * 8;
+        const size_t pitch = (size_t)(N / 2);
+        *reinterpret_cast<uint2*>(dst) = make_uint2(__byte_perm(a01, a23, 0x5410), __byte_perm(a45, a67, 0x5410));
+        *reinterpret_cast<uint2*>(dst + pitch) = make_uint2(__byte_perm(a01, a23, 0x7632), __byte_perm(a45, a67, 0x7632));
+        *reinterpret_cast<uint2*>(dst + 2 * pitch) = make_uint2(__byte_perm(b01, b23, 0x5410), __byte_perm(b45, b67, 0x5410));
+        *reinterpret_cast<uint2*>(dst + 3 * pitch) = make_uint2(__byte_perm(b01, b23, 0x7632), __byte_perm(b45, b67, 0x7632));
+    }
+}
+// one thread per (8 n, k group); consecutive threads take consecutive groups, so the 2-byte reads of a warp are contiguous
+__global__ void __launch_bounds__(256) k_w4_qp_transpose(const __nv_bfloat16* __restrict__ scales, const __nv_bfloat16* __restrict__ zeros,
+                                                         uint4* __restrict__ qpt, int N, int G) {
+    const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= G * (N / 8)) return;
+    const int n8 = idx / G, g = idx - n8 * G, n = n8 * 8;
+    const unsigned short* sp = reinterpret_cast<const unsigned short*>(scales);
+    uint32_t sv[8], zv[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        sv[j] = sp[(size_t)(n + j) * G + g];
+        const __nv_bfloat16 z = __hadd(zeros[(size_t)(n + j) * G + g], __float2bfloat16_rn(128.0f));
+        zv[j] = *reinterpret_cast<const unsigned short*>(&z);
+    }
+    uint4* dst = qpt + ((size_t)g * (size_t)(N / 8) + (size_t)n8) * 2;
+    dst[0] = make_uint4(sv[0] | sv[4] << 16, sv[1] | sv[5] << 16, sv[2] | sv[6] << 16, sv[3] | sv[7] << 16);
+    dst[1] = make_uint4(zv[0] | zv[4] << 16, zv[1] | zv[5] << 16, zv[2] | zv[6] << 16, zv[3] | zv[7] << 16);
+}
+
 // ---------------------------------------------------------------------------------------------
 // The kernel
 // ---------------------------------------------------------------------------------------------
-template <int KIND, int TN, int RT, bool TA, bool SK>
+template <int KIND, int TN, int RT, bool TA, bool SK, bool QPT = false>
 __global__ void __launch_bounds__(Cfg<KIND, TN, RT, TA, SK>::THREADS, 1)
 k_gemm(const __grid_constant__ CUtensorMap map_tok, const __grid_constant__ CUtensorMap map_w, const GemmParams p) {
     static_assert(!SK || (KIND != KIND_I8 && RT == 1 && TN % FIX_COLS == 0), "balanced mode: A16W4 kinds, one row tile per CTA");
+    static_assert(!QPT || (KIND == KIND_FWD && TA && RT == 1), "per-column group parameters: forward kernel, weight tile in tensor memory");
     using C = Cfg<KIND, TN, RT, TA, SK>;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -661,7 +749,7 @@ k_gemm(const __grid_constant__ CUtensorMap map_tok, const __grid_constant__ CUte
             // (scale | zero << 16) as raw bf16 bits for this thread's two 32-element slots of row tile r at position q
             auto load_qp2 = [&](const Pos& q, int r, uint32_t& a, uint32_t& b) {
                 a = b = 0u;
-                if (!q.valid) return;
+                if (QPT || !q.valid) return;
                 int wrow, k0, k1;
                 if (TA && KIND == KIND_DGRAD) {            // rows n_lane and n_lane+32, one k group per warp
                     wrow = q.kb * 64 + lane; k0 = k1 = q.r_tile * TILE_R + quarter * 32;
@@ -749,7 +837,21 @@ k_gemm(const __grid_constant__ CUtensorMap map_tok, const __grid_constant__ CUte
                             const int raw_off = TA ? (quarter * 32 + lane) * 32 : tt * 32;   // dgrad: (tt/2)*64 + (tt%2)*32 == tt*32
                             const uint4* rp = reinterpret_cast<const uint4*>(raw_tile(stage, r) + raw_off);
                             const uint4 r0 = rp[0], r1 = rp[1];
-                            if (TA) {
+                            if (TA && QPT) {
+                                // group parameters of the stage's 64 contraction elements (the same for every row of the
+                                // tile's k group: the loads of a warp are one broadcast each), one word ahead of their use
+                                const uint32_t dst = ta_addr + (uint32_t)(stage * TA_COLS_PER_STAGE);
+                                const uint4* qp = p.qpt + ((size_t)cur.r_tile * (size_t)(p.C >> 3) + (size_t)cur.kb * 8) * 2;
+                                const uint32_t wq[8] = {r0.x, r0.y, r0.z, r0.w, r1.x, r1.y, r1.z, r1.w};
+                                uint4 sp = __ldg(qp), zp = __ldg(qp + 1);
+#pragma unroll
+                                for (int i = 0; i < 8; i += 2) {
+                                    const uint4 sp1 = __ldg(qp + 2 * i + 2), zp1 = __ldg(qp + 2 * i + 3);
+                                    const uint4 d0 = dequant8t(wq[i], zp, sp);
+                                    if (i + 2 < 8) { sp = __ldg(qp + 2 * i + 4); zp = __ldg(qp + 2 * i + 5); }
+                                    tmem_st8(dst + (uint32_t)(4 * i), d0, dequant8t(wq[i + 1], zp1, sp1));
+                                }
+                            } else if (TA) {
                                 const uint32_t dst = ta_addr + (uint32_t)(stage * TA_COLS_PER_STAGE);
                                 tmem_st8(dst + 0, dequant8(r0.x, za, s2a), dequant8(r0.y, za, s2a));
                                 tmem_st8(dst + 8, dequant8(r0.z, za, s2a), dequant8(r0.w, za, s2a));
@@ -955,14 +1057,14 @@ static int make_map(CUtensorMap* m, const void* base, CUtensorMapDataType dt, in
     return LQ_OK;
 }
 
-template <int KIND, int TN, int RT, bool TA = false, bool SK = false>
+template <int KIND, int TN, int RT, bool TA = false, bool SK = false, bool QPT = false>
 static int launch_tn(const CUtensorMap& mt, const CUtensorMap& mw, const GemmParams& p, cudaStream_t st, int sk_grid = 0) {
     using C = Cfg<KIND, TN, RT, TA, SK>;
     static bool attr_done[64] = {};
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev >= 0 && dev < 64 && !attr_done[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(k_gemm<KIND, TN, RT, TA, SK>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
+        cudaError_t e = cudaFuncSetAttribute(k_gemm<KIND, TN, RT, TA, SK, QPT>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
         if (e != cudaSuccess) { set_cuda_error(e, "cudaFuncSetAttribute"); return LQ_ECUDA; }
         attr_done[dev] = true;
     }
@@ -971,12 +1073,12 @@ static int launch_tn(const CUtensorMap& mt, const CUtensorMap& mw, const GemmPar
         unsigned char* tickets = reinterpret_cast<unsigned char*>(p.partial) + (size_t)p.sk_rem * p.sk_pmax * (size_t)TN * TILE_R * 4;
         cudaError_t e = cudaMemsetAsync(tickets, 0, (size_t)p.sk_rem * 4 * sizeof(unsigned int), st);
         if (e != cudaSuccess) { set_cuda_error(e, "cudaMemsetAsync(hand-over tickets)"); return LQ_ECUDA; }
-        k_gemm<KIND, TN, RT, TA, SK><<<sk_grid, C::THREADS, C::SMEM_BYTES, st>>>(mt, mw, p);
+        k_gemm<KIND, TN, RT, TA, SK, QPT><<<sk_grid, C::THREADS, C::SMEM_BYTES, st>>>(mt, mw, p);
         return check_launch("k_gemm (balanced)");
     }
     const int items = p.r_tiles * p.t_tiles * p.splits;
     const int grid = items < sm_count() ? items : sm_count();
-    k_gemm<KIND, TN, RT, TA, SK><<<grid, C::THREADS, C::SMEM_BYTES, st>>>(mt, mw, p);
+    k_gemm<KIND, TN, RT, TA, SK, QPT><<<grid, C::THREADS, C::SMEM_BYTES, st>>>(mt, mw, p);
     int rc = check_launch("k_gemm");
     if (rc) return rc;
     if (p.splits > 1) {
@@ -1023,10 +1125,26 @@ static int launch_kind(int tn, int rt, const CUtensorMap& mt, const CUtensorMap&
 
 static inline bool al16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
+// Grad-input through a transposed copy of the weight (see k_w4_transpose): bytes of the copy and of its packed group
+// parameters, and the token count from which the two extra passes over the weight pay (they cost about as much as
+// 250 tokens of the GEMM).  LQ_GEMM_DGRAD_TRANSPOSE=0 keeps the shared-memory-A kernel, =1 takes the copy from 256 tokens.
+static size_t dgrad_t_bytes(int64_t N, int64_t K) { return (size_t)N * (size_t)K / 2 + (size_t)N * (size_t)(K / 128) * 4; }
+static bool dgrad_t_wanted(int64_t M, int64_t N, int64_t K, int group) {
+    const char* e = getenv("LQ_GEMM_DGRAD_TRANSPOSE");
+    if (e && e[0] == '0') return false;
+    if (group != 128 || (K % 256) != 0 || (N % 64) != 0 || getenv("LQ_GEMM_A_OPERAND")) return false;
+    return M >= ((e && e[0] == '1') ? 256 : 2048);
+}
+static int run_dgrad_transposed(const void* dy, const void* w, GemmParams p, int64_t M, int64_t N, int64_t K, void* workspace,
+                                cudaStream_t st);
+
 static int run_gemm(int kind, const void* tok, const void* w, GemmParams p, int64_t M, int64_t N, int64_t K,
                     void* workspace, size_t workspace_bytes, cudaStream_t st) {
     if (M == 0) return LQ_OK;
     { int rc_dev = ensure_device_for(tok); if (rc_dev) return rc_dev; }
+    if (kind == KIND_DGRAD && dgrad_t_wanted(M, N, K, p.group) && workspace && workspace_bytes >= dgrad_t_bytes(N, K) &&
+        (reinterpret_cast<uintptr_t>(workspace) & 15) == 0)
+        return run_dgrad_transposed(tok, w, p, M, N, K, workspace, st);
     Plan pl = make_plan(kind, M, N, K, p.group);
     p.M = (int)M; p.R = (int)((kind == KIND_DGRAD) ? K : N); p.C = (int)((kind == KIND_DGRAD) ? N : K);
     // a caller whose workspace is too small for the balanced plan gets the whole-tile plan (which may need less or none)
@@ -1087,6 +1205,30 @@ static int run_gemm(int kind, const void* tok, const void* w, GemmParams p, int6
     return LQ_EINVAL;
 }
 
+static int run_dgrad_transposed(const void* dy, const void* w, GemmParams p, int64_t M, int64_t N, int64_t K, void* workspace,
+                                cudaStream_t st) {
+    uint8_t* wt = reinterpret_cast<uint8_t*>(workspace);                                   // [K][N / 2]
+    uint4* qpt = reinterpret_cast<uint4*>(wt + (size_t)N * (size_t)K / 2);                 // [K / 128][N / 8][2]
+    const int G = (int)(K / 128);
+    k_w4_transpose<<<dim3((unsigned)(K / 256), (unsigned)(N / 64)), 256, 0, st>>>(reinterpret_cast<const uint8_t*>(w), wt, (int)N, (int)K);
+    int rc = check_launch("k_w4_transpose");
+    if (rc) return rc;
+    const int entries = G * (int)(N / 8);
+    k_w4_qp_transpose<<<(entries + 255) / 256, 256, 0, st>>>(p.scales, p.zeros, qpt, (int)N, G);
+    rc = check_launch("k_w4_qp_transpose");
+    if (rc) return rc;
+    // dx[M, K] = dy[M, N] . Wt[K, N]^T: the forward kernel with K output rows and N as the contraction
+    p.M = (int)M; p.R = (int)K; p.C = (int)N; p.wcols = (int)N; p.qpt = qpt;
+    p.t_tiles = (int)((M + 255) / 256); p.r_tiles = (int)((K + TILE_R - 1) / TILE_R); p.splits = 1;
+    p.kb_total = (int)(N / 64); p.kb_per_split = p.kb_total;
+    CUtensorMap mt, mw;
+    rc = make_map(&mt, dy, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)M, (uint64_t)N, 256, 64, true);
+    if (rc) return rc;
+    rc = make_map(&mw, wt, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, (uint64_t)K, (uint64_t)(N / 2), TILE_R, 32, false);
+    if (rc) return rc;
+    return launch_tn<KIND_FWD, 256, 1, true, false, true>(mt, mw, p, st);
+}
+
 }  // namespace lq
 
 using namespace lq;
@@ -1103,6 +1245,7 @@ size_t lq_gemm_workspace_bytes(int kind, int64_t M, int64_t N, int64_t K) {
             const size_t b = plan_workspace_bytes(make_plan(kind, M, N, K, group, balanced), M, R);
             if (b > need) need = b;
         }
+        if (kind == KIND_DGRAD && group == 128 && dgrad_t_wanted(M, N, K, group) && dgrad_t_bytes(N, K) > need) need = dgrad_t_bytes(N, K);
     }
     return need;
 }

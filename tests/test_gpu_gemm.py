@@ -355,3 +355,31 @@ def test_a16w4_decode_kernels_written_out_loop_equals_general_loop(ops, monkeypa
     e_max, e_fro = rel_err(out["written_out"][0], x.float() @ W.float().t() + bias.float())
     assert e_max < RTOL and e_fro < RTOL
     ops._ws_need.clear()
+
+
+@pytest.mark.parametrize("M,N,K,force", [(2048, 4096, 4096, False), (2100, 11008, 4096, False), (4096, 4096, 11008, False),
+                                         (300, 512, 1024, True), (257, 192, 512, True)])
+def test_a16w4_dgrad_through_transposed_copy(ops, monkeypatch, M, N, K, force):
+    """From 2048 tokens on the grad-input GEMM transposes the packed weight (and lays its group parameters out per
+    contraction element) into the workspace and runs the forward kernel on the copy.  Against dequantize + fp32 matmul
+    with the GEMM tolerance, and against the kernel that reads the weight as stored; ragged token tiles, row counts that
+    are not multiples of the 128-row tile, and small shapes with the route forced."""
+    codes, sb, zb = make_w4_layer(ops, N, K, seed=5)
+    g = torch.Generator(device="cuda").manual_seed(M + K)
+    dy = torch.randn(M, N, device="cuda", generator=g).to(torch.bfloat16)
+    W = ops.a16w4_dequant(codes, sb, zb, (N, K), torch.bfloat16)
+    ref = dy.float() @ W.float()
+    out = {}
+    for mode in ("copy", "stored"):
+        monkeypatch.setenv("LQ_GEMM_DGRAD_TRANSPOSE", "0" if mode == "stored" else ("1" if force else ""))
+        if mode == "copy" and not force:
+            monkeypatch.delenv("LQ_GEMM_DGRAD_TRANSPOSE", raising=False)
+        ops._ws_need.clear()
+        out[mode] = ops.gemm_a16w4_dgrad(dy, codes, sb, zb, N, K)
+        e_max, e_fro = rel_err(out[mode], ref)
+        assert e_max < RTOL and e_fro < RTOL, (mode, e_max, e_fro)
+    # both kernels feed the tensor core the same bf16 weights, k-block after k-block: where neither splits the contraction
+    # (the large shapes) the bits agree
+    if not force:
+        assert torch.equal(out["copy"], out["stored"])
+    ops._ws_need.clear()

@@ -1126,14 +1126,15 @@ static int launch_kind(int tn, int rt, const CUtensorMap& mt, const CUtensorMap&
 static inline bool al16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
 // Grad-input through a transposed copy of the weight (see k_w4_transpose): bytes of the copy and of its packed group
-// parameters, and the token count from which the two extra passes over the weight pay (they cost about as much as
-// 250 tokens of the GEMM).  LQ_GEMM_DGRAD_TRANSPOSE=0 keeps the shared-memory-A kernel, =1 takes the copy from 256 tokens.
+// parameters, and the token count from which the two extra passes over the weight pay: they cost 18 us for a
+// 4096 x 11008 weight, the GEMM saves 9 us per 1024 tokens, so the routes break even near 2048 tokens.
+// LQ_GEMM_DGRAD_TRANSPOSE=0 keeps the shared-memory-A kernel, =1 takes the copy from 256 tokens.
 static size_t dgrad_t_bytes(int64_t N, int64_t K) { return (size_t)N * (size_t)K / 2 + (size_t)N * (size_t)(K / 128) * 4; }
 static bool dgrad_t_wanted(int64_t M, int64_t N, int64_t K, int group) {
     const char* e = getenv("LQ_GEMM_DGRAD_TRANSPOSE");
     if (e && e[0] == '0') return false;
     if (group != 128 || (K % 256) != 0 || (N % 64) != 0 || getenv("LQ_GEMM_A_OPERAND")) return false;
-    return M >= ((e && e[0] == '1') ? 256 : 2048);
+    return M >= ((e && e[0] == '1') ? 256 : 3072);
 }
 static int run_dgrad_transposed(const void* dy, const void* w, GemmParams p, int64_t M, int64_t N, int64_t K, void* workspace,
                                 cudaStream_t st);

@@ -357,10 +357,10 @@ def test_a16w4_decode_kernels_written_out_loop_equals_general_loop(ops, monkeypa
     ops._ws_need.clear()
 
 
-@pytest.mark.parametrize("M,N,K,force", [(2048, 4096, 4096, False), (2100, 11008, 4096, False), (4096, 4096, 11008, False),
+@pytest.mark.parametrize("M,N,K,force", [(3072, 4096, 4096, False), (3100, 11008, 4096, False), (4096, 4096, 11008, False),
                                          (300, 512, 1024, True), (257, 192, 512, True)])
 def test_a16w4_dgrad_through_transposed_copy(ops, monkeypatch, M, N, K, force):
-    """From 2048 tokens on the grad-input GEMM transposes the packed weight (and lays its group parameters out per
+    """From 3072 tokens on the grad-input GEMM transposes the packed weight (and lays its group parameters out per
     contraction element) into the workspace and runs the forward kernel on the copy.  Against dequantize + fp32 matmul
     with the GEMM tolerance, and against the kernel that reads the weight as stored; ragged token tiles, row counts that
     are not multiples of the 128-row tile, and small shapes with the route forced."""

@@ -6,7 +6,8 @@
 
 One "step" is one pass of the A16W4 hot path over one batch of synthetic activations: the quantized
 linear forward (y = x·deq(Wq)^T) and grad-input (dx = dy·deq(Wq)) for the four Llama-2-7B linear shapes
-at M = 4096 tokens (8 GEMM launches).  Rank r of N runs an independent replica of the same work on its
+at M = 4096 tokens (8 GEMMs = 16 kernel launches: each grad-input of this size first writes a transposed copy
+of the packed weight and its group parameters with two small kernels, inside the timed region).  Rank r of N runs an independent replica of the same work on its
 own GPU ("replicas only": the kernels have no exchange step), the timed region is bracketed by a
 barrier + synchronize, timed with CUDA events on the launching stream, and the maximum over ranks is
 reported.  One JSON line is printed by rank 0.
@@ -36,8 +37,8 @@ WORKLOAD = "A16W4 dequant-GEMM fwd+grad-input, Llama-2-7B linear shapes (K,N) in
 
 # dram__bytes_read.sum + dram__bytes_write.sum per k_gemm launch from an ncu capture of the (K,N)=(4096,11008),
 # M=4096 launches (a tensor-bound kernel: the figure shows there are no re-reads)
-NCU_TRAFFIC_BYTES_PER_LAUNCH = 128.9e6
-NCU_TRAFFIC_NOTE = ("ncu capture of the (K,N)=(4096,11008), M=4096 launches: forward 115.2 MB, grad-input 142.6 MB, mean 128.9 MB "
+NCU_TRAFFIC_BYTES_PER_LAUNCH = 132.6e6
+NCU_TRAFFIC_NOTE = ("ncu capture of the (K,N)=(4096,11008), M=4096 launches: forward 116.0 MB, grad-input 149.3 MB, mean 132.6 MB "
                     "per launch against 146.8 MB algorithmic bytes of that shape")
 
 
@@ -135,11 +136,18 @@ def build_layers(torch, ops, seed=1234):
     return layers
 
 
+def launches_per_layer(m=M_TOKENS):
+    """Kernel launches of one forward + one grad-input: from 3072 tokens on the grad-input is three launches
+    (weight transpose, group-parameter transpose, GEMM) unless the route is switched off."""
+    transposed = (m >= 3072 and os.environ.get("LQ_GEMM_DGRAD_TRANSPOSE") != "0" and "LQ_GEMM_A_OPERAND" not in os.environ)
+    return 4 if transposed else 2
+
+
 def run_step(ops, layers):
     for L in layers:
         ops.gemm_a16w4_fwd(L["x"], L["codes"], L["s"], L["z"], None, L["N"], L["K"], out=L["y"])
         ops.gemm_a16w4_dgrad(L["dy"], L["codes"], L["s"], L["z"], L["N"], L["K"], out=L["dx"])
-    return 2 * len(layers)
+    return launches_per_layer() * len(layers)
 
 
 def timed(torch, fn, steps, barrier):
@@ -717,7 +725,7 @@ def run_ours(args):
                 with torch.cuda.stream(s_out):
                     host_out.copy_(dev_out, non_blocking=True)
         cur.wait_stream(s_out)                                   # results of this step are on the host before the next GEMM overwrites them
-        return 2 * len(layers)
+        return launches_per_layer() * len(layers)
 
     e2e_step(); torch.cuda.synchronize()
     e2e_steps = max(2, min(args.steps, 10))

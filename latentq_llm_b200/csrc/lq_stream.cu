@@ -160,6 +160,29 @@ __global__ void __launch_bounds__(256) k_unpack_nibbles(const int8_t* __restrict
     }
 }
 
+// 16 codes (one byte each) -> 8 packed bytes per thread and step, and back; the byte-wise kernels above take the tail
+// and unaligned buffers.  Same arithmetic: ((c_even << 4) + c_odd) mod 256.
+__global__ void __launch_bounds__(256) k_pack_nibbles_v(const uint4* __restrict__ codes, uint2* __restrict__ packed, int64_t n_vec) {
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n_vec; i += (int64_t)gridDim.x * blockDim.x) {
+        const uint4 c = __ldg(codes + i);
+        const uint32_t w[4] = {c.x, c.y, c.z, c.w};
+        uint32_t h[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {                                           // bytes (c0 c1 c2 c3) -> (c0 << 4) + c1, (c2 << 4) + c3
+            const uint32_t r = ((((w[j] & 0x000F000Fu) << 4) + ((w[j] >> 8) & 0x00FF00FFu)) & 0x00FF00FFu);
+            h[j] = (r & 0xFFu) | ((r >> 8) & 0xFF00u);
+        }
+        packed[i] = make_uint2(h[0] | (h[1] << 16), h[2] | (h[3] << 16));
+    }
+}
+__global__ void __launch_bounds__(256) k_unpack_nibbles_v(const uint2* __restrict__ packed, uint4* __restrict__ codes, int64_t n_vec) {
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n_vec; i += (int64_t)gridDim.x * blockDim.x) {
+        const uint2 p = __ldg(packed + i);
+        const uint32_t hx = (p.x >> 4) & 0x0F0F0F0Fu, lx = p.x & 0x0F0F0F0Fu, hy = (p.y >> 4) & 0x0F0F0F0Fu, ly = p.y & 0x0F0F0F0Fu;
+        codes[i] = make_uint4(__byte_perm(hx, lx, 0x5140), __byte_perm(hx, lx, 0x7362), __byte_perm(hy, ly, 0x5140), __byte_perm(hy, ly, 0x7362));
+    }
+}
+
 // =================================================================================================
 // Group dequant (DeQfunc_4bit_g)
 // =================================================================================================
@@ -1112,14 +1135,31 @@ int lq_pack_nibbles(const uint8_t* codes, int8_t* packed, int64_t n_codes, lq_st
     if (n_codes == 0) return LQ_OK;
     if (!codes || !packed || n_codes < 0 || (n_codes % 2) || !aligned(codes, 2)) return LQ_EINVAL;
     { int rc_dev = ensure_device_for(codes); if (rc_dev) return rc_dev; }
-    k_pack_nibbles<<<grid_for(n_codes / 2, 256, 8), 256, 0, LQ_ST(stream)>>>(codes, packed, n_codes / 2);
+    const int64_t n_bytes = n_codes / 2;
+    int64_t n_vec = (aligned(codes, 16) && aligned(packed, 8)) ? n_bytes / 8 : 0;
+    if (n_vec > 0) {
+        k_pack_nibbles_v<<<grid_for(n_vec, 256, 8), 256, 0, LQ_ST(stream)>>>(reinterpret_cast<const uint4*>(codes),
+                                                                           reinterpret_cast<uint2*>(packed), n_vec);
+        int rc = check_launch("lq_pack_nibbles");
+        if (rc) return rc;
+    }
+    if (n_bytes > n_vec * 8)
+        k_pack_nibbles<<<grid_for(n_bytes - n_vec * 8, 256, 8), 256, 0, LQ_ST(stream)>>>(codes + n_vec * 16, packed + n_vec * 8, n_bytes - n_vec * 8);
     return check_launch("lq_pack_nibbles");
 }
 int lq_unpack_nibbles(const int8_t* packed, int8_t* codes, int64_t n_bytes, lq_stream_t stream) {
     if (n_bytes == 0) return LQ_OK;
     if (!codes || !packed || n_bytes < 0 || !aligned(codes, 2)) return LQ_EINVAL;
     { int rc_dev = ensure_device_for(codes); if (rc_dev) return rc_dev; }
-    k_unpack_nibbles<<<grid_for(n_bytes, 256, 8), 256, 0, LQ_ST(stream)>>>(packed, codes, n_bytes);
+    int64_t n_vec = (aligned(codes, 16) && aligned(packed, 8)) ? n_bytes / 8 : 0;
+    if (n_vec > 0) {
+        k_unpack_nibbles_v<<<grid_for(n_vec, 256, 8), 256, 0, LQ_ST(stream)>>>(reinterpret_cast<const uint2*>(packed),
+                                                                             reinterpret_cast<uint4*>(codes), n_vec);
+        int rc = check_launch("lq_unpack_nibbles");
+        if (rc) return rc;
+    }
+    if (n_bytes > n_vec * 8)
+        k_unpack_nibbles<<<grid_for(n_bytes - n_vec * 8, 256, 8), 256, 0, LQ_ST(stream)>>>(packed + n_vec * 8, codes + n_vec * 16, n_bytes - n_vec * 8);
     return check_launch("lq_unpack_nibbles");
 }
 

@@ -482,3 +482,24 @@ def test_requant_beyond_2p32_elements(ops):
                                   words=w0.cpu().numpy(), delta=d0.float().cpu().numpy(), codec=orc.CODEC_THREEFOLD,
                                   math_bf16=True, res_round_bf16=True, has_residual=True, mu_enc=2, mu_dec=1, dither=dith)
     assert np.array_equal(codes[a // 2:].cpu().numpy(), co) and np.array_equal(words[a // 8:].cpu().numpy(), wo)
+
+
+@pytest.mark.parametrize("n", [2, 14, 16, 30, 4096 + 6, 1 << 20])
+@pytest.mark.parametrize("offset", [0, 2])
+def test_pack_unpack_vector_and_tail_paths(ops, n, offset):
+    """16 codes per thread where the buffers are aligned, byte-wise for the tail and for unaligned views; codes beyond 15
+    wrap like the reference's int8 arithmetic (python_compress, utils/quant.py:4-11: (a << 4) + b in int8)."""
+    g = torch.Generator(device="cuda").manual_seed(n + offset)
+    raw = torch.randint(0, 256, (n + offset,), device="cuda", generator=g, dtype=torch.uint8)
+    codes = raw[offset:]
+    packed = ops.pack_nibbles(codes)
+    want = ((codes[0::2].to(torch.int32) << 4) + codes[1::2].to(torch.int32)) & 255
+    assert torch.equal(packed.view(torch.uint8).to(torch.int32), want)
+    small = codes & 15
+    packed = ops.pack_nibbles(small)
+    back = ops.unpack_nibbles(packed)
+    assert torch.equal(back.view(torch.uint8), small)
+    if offset:                                      # unpack from an unaligned packed view
+        buf = torch.zeros(packed.numel() + offset, device="cuda", dtype=torch.int8)
+        buf[offset:] = packed
+        assert torch.equal(ops.unpack_nibbles(buf[offset:]).view(torch.uint8), small)

@@ -205,35 +205,42 @@ __global__ void __launch_bounds__(256) k_a16w4_dequant(const uint32_t* __restric
     }
 }
 
-// bf16 qparams, bf16 output, power-of-two group >= 16: two packed words (16 weights) per thread, packed bf16x2 arithmetic
-// (the integers 128 + q are formed by OR-ing the nibble into bf16 128.0; (128+q) - (128+z) and the product with the
-// scale are single bf16 roundings, i.e. exactly bf16((q - z) * s) as the op-by-op chain computes it).
-__global__ void __launch_bounds__(256) k_a16w4_dequant_bf16(const uint2* __restrict__ packed, const unsigned short* __restrict__ scales,
+// bf16 qparams, bf16 output, power-of-two group >= 16: packed bf16x2 arithmetic (the integers 128 + q are formed by
+// OR-ing the nibble into bf16 128.0; (128+q) - (128+z) and the product with the scale are single bf16 roundings, i.e.
+// exactly bf16((q - z) * s) as the op-by-op chain computes it).  A thread converts two packed words a whole grid
+// apart, so that every load (4 bytes per lane) and every store (16 bytes per lane) of a warp is one contiguous run.
+__global__ void __launch_bounds__(256) k_a16w4_dequant_bf16(const uint32_t* __restrict__ packed, const unsigned short* __restrict__ scales,
                                                             const unsigned short* __restrict__ zeros, uint4* __restrict__ out,
-                                                            uint32_t n_pairs, int pair_shift) {
+                                                            uint32_t n_words, int word_shift) {
     const uint32_t c128 = 0x43004300u;
-    for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < n_pairs; i += gridDim.x * blockDim.x) {
-        const uint32_t g = i >> pair_shift;
-        const uint32_t sb = __ldg(scales + g), zb = __ldg(zeros + g);
-        const uint2 pk = __ldg(packed + i);
-        const uint32_t s2u = sb * 0x00010001u, z2u = zb * 0x00010001u;
-        const __nv_bfloat162 s2 = *reinterpret_cast<const __nv_bfloat162*>(&s2u);
-        const __nv_bfloat162 z128 = __hadd2_rn(*reinterpret_cast<const __nv_bfloat162*>(&z2u), *reinterpret_cast<const __nv_bfloat162*>(&c128));
-        uint32_t o[8];
+    const uint32_t T = gridDim.x * blockDim.x;
+    for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < n_words; i += 2 * T) {
+        const uint32_t idx[2] = {i, i + T};
+        uint32_t w[2], sb[2], zb[2];
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
-            const uint32_t w = h ? pk.y : pk.x;
-            const uint32_t lo_n = w & 0x0F0F0F0Fu, hi_n = (w >> 4) & 0x0F0F0F0Fu;       // odd / even elements, one per byte
+            const bool on = idx[h] < n_words;
+            const uint32_t g = idx[h] >> word_shift;
+            w[h] = on ? __ldg(packed + idx[h]) : 0u;
+            sb[h] = on ? (uint32_t)__ldg(scales + g) : 0u; zb[h] = on ? (uint32_t)__ldg(zeros + g) : 0u;
+        }
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            if (idx[h] >= n_words) break;
+            const uint32_t s2u = sb[h] * 0x00010001u, z2u = zb[h] * 0x00010001u;
+            const __nv_bfloat162 s2 = *reinterpret_cast<const __nv_bfloat162*>(&s2u);
+            const __nv_bfloat162 z128 = __hadd2_rn(*reinterpret_cast<const __nv_bfloat162*>(&z2u), *reinterpret_cast<const __nv_bfloat162*>(&c128));
+            const uint32_t lo_n = w[h] & 0x0F0F0F0Fu, hi_n = (w[h] >> 4) & 0x0F0F0F0Fu;       // odd / even elements, one per byte
             const uint32_t c03 = __byte_perm(hi_n, lo_n, 0x5140), c47 = __byte_perm(hi_n, lo_n, 0x7362);
+            uint32_t o[4];
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
                 const uint32_t pair = __byte_perm((j < 2) ? c03 : c47, 0x43434343u, (j & 1) ? 0x4342 : 0x4140);
                 const __nv_bfloat162 v = __hmul2_rn(__hsub2_rn(*reinterpret_cast<const __nv_bfloat162*>(&pair), z128), s2);
-                o[4 * h + j] = *reinterpret_cast<const uint32_t*>(&v);
+                o[j] = *reinterpret_cast<const uint32_t*>(&v);
             }
+            out[idx[h]] = make_uint4(o[0], o[1], o[2], o[3]);
         }
-        out[2 * (size_t)i] = make_uint4(o[0], o[1], o[2], o[3]);
-        out[2 * (size_t)i + 1] = make_uint4(o[4], o[5], o[6], o[7]);
     }
 }
 
@@ -1172,11 +1179,11 @@ int lq_a16w4_dequant(const int8_t* qweight, const void* scales, const void* zero
     { int rc_dev = ensure_device_for(out); if (rc_dev) return rc_dev; }
     if (qp_dtype == LQ_BF16 && out_dtype == LQ_BF16 && group >= 16 && (group & (group - 1)) == 0 && (numel % 16) == 0 &&
         numel < ((int64_t)1 << 34) && aligned(qweight, 8)) {
-        int sh = 0; while ((16 << sh) < group) ++sh;
-        const uint32_t n_pairs = (uint32_t)(numel / 16);
-        k_a16w4_dequant_bf16<<<grid_for(n_pairs, 256, 8), 256, 0, LQ_ST(stream)>>>(
-            reinterpret_cast<const uint2*>(qweight), reinterpret_cast<const unsigned short*>(scales),
-            reinterpret_cast<const unsigned short*>(zeros), reinterpret_cast<uint4*>(out), n_pairs, sh);
+        int sh = 0; while ((8 << sh) < group) ++sh;
+        const uint32_t n_words = (uint32_t)(numel / 8);
+        k_a16w4_dequant_bf16<<<grid_for(n_words / 2, 256, 8), 256, 0, LQ_ST(stream)>>>(
+            reinterpret_cast<const uint32_t*>(qweight), reinterpret_cast<const unsigned short*>(scales),
+            reinterpret_cast<const unsigned short*>(zeros), reinterpret_cast<uint4*>(out), n_words, sh);
         return check_launch("lq_a16w4_dequant");
     }
     int grid = grid_for(numel / 8, 256, 8);

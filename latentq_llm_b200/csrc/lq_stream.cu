@@ -847,16 +847,34 @@ static int launch_requant(const RequantParams& p, const lq_requant_opts* o, cuda
 // =================================================================================================
 // 8-bit optimizer-state codec
 // =================================================================================================
+// One CTA per block of the state.  A thread takes float4 vectors a whole CTA apart (every load of a warp is 512
+// contiguous bytes, every store 128); KEEP vectors per thread stay in registers between the min/max pass and the
+// quantize pass (KEEP * 4 * threads >= block), larger blocks re-read.
+template <int KEEP>
 __global__ void __launch_bounds__(256) k_opt8_quant(const float* __restrict__ x, int block, uint8_t* __restrict__ q,
                                                     float* __restrict__ scale, float* __restrict__ tmax) {
     __shared__ float s_mn[8], s_mx[8];
     const int64_t base = (int64_t)blockIdx.x * block;
+    const float4* xv = reinterpret_cast<const float4*>(x + base);
+    const int n_vec = block / 4;
     float mn = INFINITY, mx = -INFINITY;
-    for (int e = threadIdx.x * 8; e < block; e += blockDim.x * 8) {
-        float v[8];
-        load8(x, LQ_F32, base + e, v);
+    float4 keep[KEEP > 0 ? KEEP : 1];
+    if (KEEP > 0) {
 #pragma unroll
-        for (int k = 0; k < 8; ++k) { mn = fminf(mn, v[k]); mx = fmaxf(mx, v[k]); }
+        for (int u = 0; u < KEEP; ++u) {
+            const int i = threadIdx.x + u * blockDim.x;
+            if (i < n_vec) {
+                keep[u] = __ldg(xv + i);
+                mn = fminf(fminf(mn, keep[u].x), fminf(fminf(keep[u].y, keep[u].z), keep[u].w));
+                mx = fmaxf(fmaxf(mx, keep[u].x), fmaxf(fmaxf(keep[u].y, keep[u].z), keep[u].w));
+            }
+        }
+    } else {
+        for (int i = threadIdx.x; i < n_vec; i += blockDim.x) {
+            const float4 v = __ldg(xv + i);
+            mn = fminf(fminf(mn, v.x), fminf(fminf(v.y, v.z), v.w));
+            mx = fmaxf(fmaxf(mx, v.x), fmaxf(fmaxf(v.y, v.z), v.w));
+        }
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
@@ -871,35 +889,93 @@ __global__ void __launch_bounds__(256) k_opt8_quant(const float* __restrict__ x,
     if (threadIdx.x == 0) { scale[blockIdx.x] = s; tmax[blockIdx.x] = mx; }
     const float rs = __frcp_rn(s);
     const bool ok = fastdiv_ok_scale(s);
-    for (int e = threadIdx.x * 8; e < block; e += blockDim.x * 8) {
-        float v[8];
-        load8(x, LQ_F32, base + e, v);
-        uint32_t b[8];
+    uint32_t* qv = reinterpret_cast<uint32_t*>(q + base);
+    auto quant4 = [&](const float4& v) {
+        const float f[4] = {v.x, v.y, v.z, v.w};
+        uint32_t o = 0;
 #pragma unroll
-        for (int k = 0; k < 8; ++k) {
-            float t = rintf(div_rn(__fsub_rn(mx, v[k]), s, rs, ok));
-            b[k] = (uint32_t)(int)fminf(fmaxf(t, 0.0f), 255.0f);
+        for (int k = 0; k < 4; ++k) {
+            const float t = rintf(div_rn(__fsub_rn(mx, f[k]), s, rs, ok));
+            o |= (uint32_t)(int)fminf(fmaxf(t, 0.0f), 255.0f) << (8 * k);
         }
-        uint2 o2;
-        o2.x = b[0] | (b[1] << 8) | (b[2] << 16) | (b[3] << 24);
-        o2.y = b[4] | (b[5] << 8) | (b[6] << 16) | (b[7] << 24);
-        *reinterpret_cast<uint2*>(q + base + e) = o2;
+        return o;
+    };
+    if (KEEP > 0) {
+#pragma unroll
+        for (int u = 0; u < KEEP; ++u) {
+            const int i = threadIdx.x + u * blockDim.x;
+            if (i < n_vec) qv[i] = quant4(keep[u]);
+        }
+    } else {
+        for (int i = threadIdx.x; i < n_vec; i += blockDim.x) qv[i] = quant4(__ldg(xv + i));
     }
 }
-__global__ void __launch_bounds__(256) k_opt8_dequant(const uint8_t* __restrict__ q, int64_t n_words, int64_t block,
-                                                      const float* __restrict__ scale, const float* __restrict__ tmax,
-                                                      float* __restrict__ x) {
-    for (int64_t w = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; w < n_words; w += (int64_t)gridDim.x * blockDim.x) {
-        int64_t b = (w * 8) / block;
-        float s = __ldg(scale + b), t = __ldg(tmax + b);
-        uint2 pk = __ldg(reinterpret_cast<const uint2*>(q) + w);
-        float v[8];
+// Blocks of up to 2048 values: one WARP per block, the whole block in registers (VW float4 per lane), no shared memory
+// and no CTA barrier between the min/max pass and the quantize pass; a CTA is eight independent warps.
+template <int VW>
+__global__ void __launch_bounds__(256) k_opt8_quant_warp(const float* __restrict__ x, int block, int64_t n_blocks, uint8_t* __restrict__ q,
+                                                         float* __restrict__ scale, float* __restrict__ tmax) {
+    const int lane = threadIdx.x & 31;
+    const int64_t blk = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (blk >= n_blocks) return;
+    const float4* xv = reinterpret_cast<const float4*>(x + blk * block);
+    const int n_vec = block / 4;
+    float4 keep[VW];
+    float mn = INFINITY, mx = -INFINITY;
 #pragma unroll
-        for (int k = 0; k < 8; ++k) {
-            float c = (float)(((k < 4 ? pk.x : pk.y) >> (8 * (k & 3))) & 0xffu);
-            v[k] = __fsub_rn(t, __fmul_rn(c, s));
+    for (int u = 0; u < VW; ++u) {
+        const int i = lane + u * 32;
+        if (i < n_vec) {
+            keep[u] = __ldg(xv + i);
+            mn = fminf(fminf(mn, keep[u].x), fminf(fminf(keep[u].y, keep[u].z), keep[u].w));
+            mx = fmaxf(fmaxf(mx, keep[u].x), fmaxf(fmaxf(keep[u].y, keep[u].z), keep[u].w));
         }
-        store8(x, LQ_F32, w * 8, v);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        mn = fminf(mn, __shfl_xor_sync(0xffffffffu, mn, o));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    }
+    const float s = __fadd_rn(__fdiv_rn(__fsub_rn(mx, mn), 255.0f), 1e-10f);
+    if (lane == 0) { scale[blk] = s; tmax[blk] = mx; }
+    const float rs = __frcp_rn(s);
+    const bool ok = fastdiv_ok_scale(s);
+    uint32_t* qv = reinterpret_cast<uint32_t*>(q + blk * block);
+#pragma unroll
+    for (int u = 0; u < VW; ++u) {
+        const int i = lane + u * 32;
+        if (i < n_vec) {
+            const float f[4] = {keep[u].x, keep[u].y, keep[u].z, keep[u].w};
+            uint32_t o = 0;
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const float t = rintf(div_rn(__fsub_rn(mx, f[k]), s, rs, ok));
+                o |= (uint32_t)(int)fminf(fmaxf(t, 0.0f), 255.0f) << (8 * k);
+            }
+            qv[i] = o;
+        }
+    }
+}
+// four codes (one 32-bit word) per lane and step -> one float4 store; two words a grid apart per thread
+__global__ void __launch_bounds__(256) k_opt8_dequant(const uint32_t* __restrict__ q, int64_t n_words, int64_t block, int block_shift,
+                                                      const float* __restrict__ scale, const float* __restrict__ tmax,
+                                                      float4* __restrict__ x) {
+    const int64_t T = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t w0 = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; w0 < n_words; w0 += 2 * T) {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const int64_t w = w0 + h * T;
+            if (w >= n_words) break;
+            const int64_t b = block_shift >= 0 ? ((w * 4) >> block_shift) : (w * 4) / block;
+            const float s = __ldg(scale + b), t = __ldg(tmax + b);
+            const uint32_t pk = __ldg(q + w);
+            float4 v;
+            v.x = __fsub_rn(t, __fmul_rn((float)(pk & 0xffu), s));
+            v.y = __fsub_rn(t, __fmul_rn((float)((pk >> 8) & 0xffu), s));
+            v.z = __fsub_rn(t, __fmul_rn((float)((pk >> 16) & 0xffu), s));
+            v.w = __fsub_rn(t, __fmul_rn((float)(pk >> 24), s));
+            x[w] = v;
+        }
     }
 }
 
@@ -1315,8 +1391,20 @@ int lq_opt8_quant(const float* x, int64_t n, int block, uint8_t* q, float* scale
     if (!x || !q || !scale || !tmax || n < 0 || block <= 0 || (block % 8) || (n % block) || !aligned(x, 16) || !aligned(q, 8))
         return LQ_EINVAL;
     { int rc_dev = ensure_device_for(x); if (rc_dev) return rc_dev; }
-    int threads = block / 8 >= 256 ? 256 : ((block / 8 + 31) / 32) * 32;
-    k_opt8_quant<<<(unsigned)(n / block), threads, 0, LQ_ST(stream)>>>(x, block, q, scale, tmax);
+    if (block <= 2048) {                        // one warp per block
+        const int64_t nb = n / block;
+        const unsigned gridw = (unsigned)((nb + 7) / 8);
+        if (block <= 512) k_opt8_quant_warp<4><<<gridw, 256, 0, LQ_ST(stream)>>>(x, block, nb, q, scale, tmax);
+        else if (block <= 1024) k_opt8_quant_warp<8><<<gridw, 256, 0, LQ_ST(stream)>>>(x, block, nb, q, scale, tmax);
+        else k_opt8_quant_warp<16><<<gridw, 256, 0, LQ_ST(stream)>>>(x, block, nb, q, scale, tmax);
+        return check_launch("lq_opt8_quant");
+    }
+    int threads = block / 4 >= 256 ? 256 : ((block / 4 + 31) / 32) * 32;
+    const unsigned grid = (unsigned)(n / block);
+    if (block <= 4 * threads) k_opt8_quant<1><<<grid, threads, 0, LQ_ST(stream)>>>(x, block, q, scale, tmax);
+    else if (block <= 8 * threads) k_opt8_quant<2><<<grid, threads, 0, LQ_ST(stream)>>>(x, block, q, scale, tmax);
+    else if (block <= 16 * threads) k_opt8_quant<4><<<grid, threads, 0, LQ_ST(stream)>>>(x, block, q, scale, tmax);
+    else k_opt8_quant<0><<<grid, threads, 0, LQ_ST(stream)>>>(x, block, q, scale, tmax);
     return check_launch("lq_opt8_quant");
 }
 int lq_opt8_dequant(const uint8_t* q, int64_t n, int block, const float* scale, const float* tmax, float* x, lq_stream_t stream) {
@@ -1324,7 +1412,10 @@ int lq_opt8_dequant(const uint8_t* q, int64_t n, int block, const float* scale, 
     if (!x || !q || !scale || !tmax || n < 0 || block <= 0 || (block % 8) || (n % block) || !aligned(x, 16) || !aligned(q, 8))
         return LQ_EINVAL;
     { int rc_dev = ensure_device_for(x); if (rc_dev) return rc_dev; }
-    k_opt8_dequant<<<grid_for(n / 8, 256, 8), 256, 0, LQ_ST(stream)>>>(q, n / 8, block, scale, tmax, x);
+    int sh = -1;
+    if ((block & (block - 1)) == 0) { sh = 0; while ((1 << sh) < block) ++sh; }
+    k_opt8_dequant<<<grid_for(n / 8, 256, 8), 256, 0, LQ_ST(stream)>>>(reinterpret_cast<const uint32_t*>(q), n / 4, block, sh, scale, tmax,
+                                                                      reinterpret_cast<float4*>(x));
     return check_launch("lq_opt8_dequant");
 }
 

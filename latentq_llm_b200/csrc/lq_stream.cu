@@ -983,7 +983,7 @@ __global__ void __launch_bounds__(256) k_opt8_dequant(const uint32_t* __restrict
 // Activation quantizers
 // =================================================================================================
 // One CTA per token.  VPT = 16-byte vectors per thread kept in registers between the absmax pass and the quantize pass
-// (VPT * 2048 >= K); larger rows re-read from L2.
+// (VPT * 8 * blockDim.x >= K); larger rows re-read from L2.
 template <int VPT>
 __global__ void __launch_bounds__(256) k_act_quant_per_token(const __nv_bfloat16* __restrict__ x, int64_t K,
                                                              int8_t* __restrict__ x8, float* __restrict__ a_scale) {
@@ -996,13 +996,13 @@ __global__ void __launch_bounds__(256) k_act_quant_per_token(const __nv_bfloat16
     if (VPT > 0) {
 #pragma unroll
         for (int u = 0; u < VPT; ++u) {
-            const int i = threadIdx.x + u * 256;
+            const int i = threadIdx.x + u * (int)blockDim.x;
             keep[u] = (i < n_vec) ? __ldg(xv + i) : make_uint4(0, 0, 0, 0);
             const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&keep[u]);
             am2 = __hmax2(am2, __hmax2(__hmax2(__habs2(h[0]), __habs2(h[1])), __hmax2(__habs2(h[2]), __habs2(h[3]))));
         }
     } else {
-        for (int i = threadIdx.x; i < n_vec; i += 256) {
+        for (int i = threadIdx.x; i < n_vec; i += (int)blockDim.x) {
             const uint4 v = __ldg(xv + i);
             const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
             am2 = __hmax2(am2, __hmax2(__hmax2(__habs2(h[0]), __habs2(h[1])), __hmax2(__habs2(h[2]), __habs2(h[3]))));
@@ -1049,11 +1049,11 @@ __global__ void __launch_bounds__(256) k_act_quant_per_token(const __nv_bfloat16
     if (VPT > 0) {
 #pragma unroll
         for (int u = 0; u < VPT; ++u) {
-            const int i = threadIdx.x + u * 256;
+            const int i = threadIdx.x + u * (int)blockDim.x;
             if (i < n_vec) ov[i] = quant8(keep[u]);
         }
     } else {
-        for (int i = threadIdx.x; i < n_vec; i += 256) ov[i] = quant8(__ldg(xv + i));
+        for (int i = threadIdx.x; i < n_vec; i += (int)blockDim.x) ov[i] = quant8(__ldg(xv + i));
     }
 }
 
@@ -1424,10 +1424,15 @@ int lq_act_quant_per_token(const void* x, int64_t M, int64_t K, int8_t* x8, floa
     if (!x || !x8 || !a_scale || M < 0 || K <= 0 || (K % 8) || !aligned(x, 16) || !aligned(x8, 8)) return LQ_EINVAL;
     { int rc_dev = ensure_device_for(x); if (rc_dev) return rc_dev; }
     const __nv_bfloat16* xb = reinterpret_cast<const __nv_bfloat16*>(x);
-    if (K <= 2048) k_act_quant_per_token<1><<<(unsigned)M, 256, 0, LQ_ST(stream)>>>(xb, K, x8, a_scale);
-    else if (K <= 4096) k_act_quant_per_token<2><<<(unsigned)M, 256, 0, LQ_ST(stream)>>>(xb, K, x8, a_scale);
-    else if (K <= 8192) k_act_quant_per_token<4><<<(unsigned)M, 256, 0, LQ_ST(stream)>>>(xb, K, x8, a_scale);
-    else k_act_quant_per_token<0><<<(unsigned)M, 256, 0, LQ_ST(stream)>>>(xb, K, x8, a_scale);
+    // 128 threads per token (measured: 0.85 of HBM at K = 4096 against 0.74 with 256 and 0.81 with 64); the row stays in
+    // registers between the absmax pass and the quantize pass up to 16 vectors per thread
+    const unsigned grid = (unsigned)M;
+    if (K <= 1024) k_act_quant_per_token<1><<<grid, 128, 0, LQ_ST(stream)>>>(xb, K, x8, a_scale);
+    else if (K <= 2048) k_act_quant_per_token<2><<<grid, 128, 0, LQ_ST(stream)>>>(xb, K, x8, a_scale);
+    else if (K <= 4096) k_act_quant_per_token<4><<<grid, 128, 0, LQ_ST(stream)>>>(xb, K, x8, a_scale);
+    else if (K <= 8192) k_act_quant_per_token<8><<<grid, 128, 0, LQ_ST(stream)>>>(xb, K, x8, a_scale);
+    else if (K <= 16384) k_act_quant_per_token<16><<<grid, 128, 0, LQ_ST(stream)>>>(xb, K, x8, a_scale);
+    else k_act_quant_per_token<0><<<grid, 256, 0, LQ_ST(stream)>>>(xb, K, x8, a_scale);
     return check_launch("lq_act_quant_per_token");
 }
 int lq_act_quant_per_tensor(const void* x, int64_t n, float* clampv_out, int8_t* x8, lq_stream_t stream) {

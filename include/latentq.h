@@ -241,6 +241,16 @@ LQ_API int lq_gemm_a8w8(const int8_t* x8, const int8_t* w8, const float* row_sca
                         int64_t M, int64_t N, int64_t K, void* workspace, size_t workspace_bytes,
                         lq_stream_t stream);
 
+/* Decode-sized forward (M <= 2, K = 4096, group 128) with the residual add and the RMSNorm in front of it folded into the
+ * kernel's token staging (PTQ/quant/triton_norm.py:7-39 followed by the int4 matmul of PTQ/quant/fused_attn.py:164-204 /
+ * fused_mlp.py:84-168): x = RMSNorm(h + delta) * gamma computed as lq_add_rmsnorm computes it (bit for bit), then
+ * y[M,N] = x . deq(qweight)^T, or with silu_pair != 0 (qweight = gate | up, N = 2 I rows) y[M,I] = silu(gate) * up.
+ * delta may be NULL (then h_out is not written); otherwise h_out receives h + delta and must be a buffer other than h
+ * (every CTA reads h).  Returns LQ_EUNSUPPORTED for other shapes: run lq_add_rmsnorm and the GEMM separately. */
+LQ_API int lq_gemm_a16w4_fwd_rmsnorm(const void* h, const void* delta, const void* gamma, float eps, int hf_rounding, void* h_out,
+                                     const int8_t* qweight, const void* scales, const void* zeros, void* y, int64_t M, int64_t N,
+                                     int64_t K, int group, int silu_pair, lq_stream_t stream);
+
 /* QLinearFunctionW4.backward grad_weight (utils/quant.py:141-142) and its accumulation over micro-batches by the
  * backward hook (:408-411): dw[N,K] (+)= dy[M,N]^T · x[M,K], all bf16 row-major, fp32 accumulation in tensor memory.
  * accumulate != 0: dw = bf16(fp32(dw) + product), one rounding, what a GEMM with beta = 1 computes; 0: dw = bf16(product).

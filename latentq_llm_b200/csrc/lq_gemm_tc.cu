@@ -1303,6 +1303,24 @@ int lq_gemm_a16w4_fwd_silu(const void* x, const int8_t* qweight, const void* sca
     return launch_skinny_rows(sp, (cudaStream_t)stream);
 }
 
+int lq_gemm_a16w4_fwd_rmsnorm(const void* h, const void* delta, const void* gamma, float eps, int hf_rounding, void* h_out,
+                              const int8_t* qweight, const void* scales, const void* zeros, void* y, int64_t M, int64_t N,
+                              int64_t K, int group, int silu_pair, lq_stream_t stream) {
+    if (!h || !gamma || !qweight || !scales || !zeros || !y || !al16(h) || !al16(gamma) || !al16(qweight) || !al16(y)) return LQ_EINVAL;
+    if (delta && (!h_out || h_out == h || !al16(delta) || !al16(h_out))) return LQ_EINVAL;
+    if (!shape_ok_w4(M, N, K, group) || (silu_pair && (N % 16) != 0)) return LQ_EUNSUPPORTED;
+    if (!skinny_norm_supported(M, K, group) || (reinterpret_cast<uintptr_t>(scales) & 7) || (reinterpret_cast<uintptr_t>(zeros) & 7))
+        return LQ_EUNSUPPORTED;
+    { int rc_dev = ensure_device_for(h); if (rc_dev) return rc_dev; }
+    SkinnyParams sp{};
+    sp.qweight = (const uint8_t*)qweight; sp.scales = (const __nv_bfloat16*)scales; sp.zeros = (const __nv_bfloat16*)zeros;
+    sp.out = (__nv_bfloat16*)y; sp.M = (int)M; sp.K = (int)K; sp.group = group; sp.splits = 1; sp.chunks_per_split = (int)(K / 64);
+    sp.N = silu_pair ? (int)(N / 2) : (int)N; sp.pair_stride = silu_pair ? (int)(N / 2) : 0; sp.hf_rounding = hf_rounding;
+    sp.norm_h = (const __nv_bfloat16*)h; sp.norm_delta = (const __nv_bfloat16*)delta; sp.norm_gamma = (const __nv_bfloat16*)gamma;
+    sp.norm_h_out = (__nv_bfloat16*)h_out; sp.norm_eps = eps; sp.norm_hf = hf_rounding;
+    return launch_skinny_rows(sp, (cudaStream_t)stream);
+}
+
 int lq_gemm_wgrad(const void* dy, const void* x, void* dw, int64_t M, int64_t N, int64_t K, int accumulate, lq_stream_t stream) {
     if (!dy || !x || !dw || !al16(dy) || !al16(x) || !al16(dw)) return LQ_EINVAL;
     if (M < 0 || N <= 0 || K <= 0 || M >= (1 << 30) || N >= (1 << 30) || K >= (1 << 30) || (N % 8) != 0 || (K % 8) != 0) return LQ_EUNSUPPORTED;

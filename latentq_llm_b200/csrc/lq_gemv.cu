@@ -420,7 +420,8 @@ __global__ void __launch_bounds__(RB_WARPS * 32, 2) k_skinny_rows(const SkinnyPa
 // about half of the general loop's instructions.
 // NCH = 11: K = 11008 (eleven chunks per warp, nine in the last): written out the same way with every chunk guarded by
 // the warp's own count and 2-byte group-parameter loads at constant offsets.
-template <int MT, int GC, int NCH>
+// NORM: the tokens are RMSNorm(h + delta) * gamma, computed in the staging phase (see SkinnyParams).
+template <int MT, int GC, int NCH, bool NORM = false>
 __global__ void __launch_bounds__(RB_WARPS * 32, LQ_GEMV_MINB) k_skinny_stream(const SkinnyParams p, const int x_stride) {
     constexpr int PF = LQ_GEMV_PF;
     constexpr bool NC4 = NCH == 4;
@@ -474,12 +475,91 @@ __global__ void __launch_bounds__(RB_WARPS * 32, LQ_GEMV_MINB) k_skinny_stream(c
 #pragma unroll
     for (int m = 0; m < MT; ++m) xrow[m] = min(m * 8 + g, p.M - 1);
 
+    // gamma is a parameter: requested before the dependency wait (NORM)
+    uint4 ng[2] = {make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0)};
+    if (NORM) {
+#pragma unroll
+        for (int u = 0; u < 2; ++u) ng[u] = __ldg(reinterpret_cast<const uint4*>(p.norm_gamma) + tid + u * (RB_WARPS * 32));
+    }
     pdl_launch_dependents();        // weight and group-parameter loads are issued: the next launch may start
     // ---- once per CTA, while the first weight loads are in flight: token fragments and per-group token sums
     for (int i = tid; i < gpr * 8 * MT; i += RB_WARPS * 32) sxs[i] = 0.0f;
     __syncthreads();
     pdl_wait();                     // the tokens may be the previous launch's output
-    {
+    // one staged vector: 8 tokens' worth of k of token `tok` (word kw of its row), permuted into B-fragment order, and
+    // its contribution to the token sum of its group
+    auto stage_item = [&](const uint4& v, const int tok, const int kw, const bool on) {
+        const uint32_t r[4] = {v.x, v.y, v.z, v.w};
+        float part = 0.0f;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) part += __uint_as_float(r[j] << 16) + __uint_as_float(r[j] & 0xffff0000u);
+        if (on) {
+            uint4 f;
+            f.x = __byte_perm(v.x, v.z, 0x5410); f.y = __byte_perm(v.x, v.z, 0x7632);
+            f.z = __byte_perm(v.y, v.w, 0x5410); f.w = __byte_perm(v.y, v.w, 0x7632);
+            // word kw = chunk * 16 + t * 4 + w is stored at chunk * 16 + w * 4 + t: the four t of a word index are adjacent
+            xs[(size_t)tok * x_stride + (kw & ~15) + ((kw & 3) << 2) + ((kw >> 2) & 3)] = f;
+        }
+#pragma unroll
+        for (int o = 8 * GC; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
+        if (on && (lane & (16 * GC - 1)) == 0) sxs[(kw / (16 * GC)) * (8 * MT) + tok] = part;
+    };
+    if constexpr (NORM) {
+        // K = 4096: 512 vectors per token, two per thread (vector tid + u * 256, as in k_add_rmsnorm_r<2>)
+        float* nred = &red[0][0][0][0];
+        for (int tk = 0; tk < p.M; ++tk) {
+            const size_t row = (size_t)tk * 4096;
+            uint4 a[2], d[2];
+#pragma unroll
+            for (int u = 0; u < 2; ++u) {
+                const int i = tid + u * (RB_WARPS * 32);
+                a[u] = __ldg(reinterpret_cast<const uint4*>(p.norm_h + row) + i);
+                d[u] = p.norm_delta ? __ldg(reinterpret_cast<const uint4*>(p.norm_delta + row) + i) : make_uint4(0, 0, 0, 0);
+            }
+            float ss = 0.0f;
+#pragma unroll
+            for (int u = 0; u < 2; ++u) {
+                uint32_t* w = reinterpret_cast<uint32_t*>(&a[u]);
+                const uint32_t* e = reinterpret_cast<const uint32_t*>(&d[u]);
+                if (p.norm_delta) {                    // residual + hidden_states: one bf16 rounding of the fp32 sum
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const __nv_bfloat162 sum = __floats2bfloat162_rn(__fadd_rn(__uint_as_float(w[j] << 16), __uint_as_float(e[j] << 16)),
+                                                                         __fadd_rn(__uint_as_float(w[j] & 0xffff0000u), __uint_as_float(e[j] & 0xffff0000u)));
+                        w[j] = sk_bf2(sum);
+                    }
+                    if (blockIdx.x == 0) reinterpret_cast<uint4*>(p.norm_h_out + row)[tid + u * (RB_WARPS * 32)] = a[u];
+                }
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const float lo = __uint_as_float(w[j] << 16), hi = __uint_as_float(w[j] & 0xffff0000u);
+                    ss = fmaf(lo, lo, ss); ss = fmaf(hi, hi, ss);
+                }
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+            if (lane == 0) nred[warp] = ss;
+            __syncthreads();
+            float tot = 0.0f;
+#pragma unroll
+            for (int wv = 0; wv < RB_WARPS; ++wv) tot += nred[wv];                 // same order in every thread
+            const float rstd = p.norm_hf ? rsqrtf(tot / 4096.0f + p.norm_eps) : 1.0f / sqrtf(tot / 4096.0f + p.norm_eps);
+#pragma unroll
+            for (int u = 0; u < 2; ++u) {
+                const uint32_t* w = reinterpret_cast<const uint32_t*>(&a[u]);
+                const uint32_t* gw = reinterpret_cast<const uint32_t*>(&ng[u]);
+                uint32_t o[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    float lo = __fmul_rn(__uint_as_float(w[j] << 16), rstd), hi = __fmul_rn(__uint_as_float(w[j] & 0xffff0000u), rstd);
+                    if (p.norm_hf) { lo = bf16r(lo); hi = bf16r(hi); }
+                    o[j] = sk_bf2(__floats2bfloat162_rn(__fmul_rn(lo, __uint_as_float(gw[j] << 16)), __fmul_rn(hi, __uint_as_float(gw[j] & 0xffff0000u))));
+                }
+                stage_item(make_uint4(o[0], o[1], o[2], o[3]), tk, tid + u * (RB_WARPS * 32), true);
+            }
+            __syncthreads();                                                       // nred is reused by the next token
+        }
+    } else {
         const int kw_per_tok = p.K / 8, items = p.M * kw_per_tok;
         for (int base = 0; base < items; base += 2 * RB_WARPS * 32) {
             uint4 v[2];
@@ -493,22 +573,7 @@ __global__ void __launch_bounds__(RB_WARPS * 32, LQ_GEMV_MINB) k_skinny_stream(c
                 v[h] = on[h] ? reinterpret_cast<const uint4*>(p.x + (size_t)tok[h] * p.K)[kw[h]] : make_uint4(0, 0, 0, 0);
             }
 #pragma unroll
-            for (int h = 0; h < 2; ++h) {
-                const uint32_t r[4] = {v[h].x, v[h].y, v[h].z, v[h].w};
-                float part = 0.0f;
-#pragma unroll
-                for (int j = 0; j < 4; ++j) part += __uint_as_float(r[j] << 16) + __uint_as_float(r[j] & 0xffff0000u);
-                if (on[h]) {
-                    uint4 f;
-                    f.x = __byte_perm(v[h].x, v[h].z, 0x5410); f.y = __byte_perm(v[h].x, v[h].z, 0x7632);
-                    f.z = __byte_perm(v[h].y, v[h].w, 0x5410); f.w = __byte_perm(v[h].y, v[h].w, 0x7632);
-                    // word kw = chunk * 16 + t * 4 + w is stored at chunk * 16 + w * 4 + t: the four t of a word index are adjacent
-                    xs[(size_t)tok[h] * x_stride + (kw[h] & ~15) + ((kw[h] & 3) << 2) + ((kw[h] >> 2) & 3)] = f;
-                }
-#pragma unroll
-                for (int o = 8 * GC; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
-                if (on[h] && (lane & (16 * GC - 1)) == 0) sxs[(kw[h] / (16 * GC)) * (8 * MT) + tok[h]] = part;
-            }
+            for (int h = 0; h < 2; ++h) stage_item(v[h], tok[h], kw[h], on[h]);
         }
     }
     __syncthreads();
@@ -705,6 +770,9 @@ __global__ void __launch_bounds__(RB_WARPS * 32, LQ_GEMV_MINB) k_skinny_stream(c
     }
 }
 
+bool skinny_norm_supported(int64_t M, int64_t K, int group) {
+    return M >= 1 && M <= 2 && K == 4096 && group == 128 && LQ_GEMV_PF == 4 && !getenv("LQ_SKINNY_NO_NC4") && !getenv("LQ_SKINNY_NO_STREAM");
+}
 bool skinny_rows_supported(int64_t K, int group) { return (group == 128 || group == 256) && K % group == 0; }
 
 // every warp of the streaming kernel needs at least two whole groups of the row
@@ -714,18 +782,18 @@ static bool skinny_stream_supported(int64_t K, int group) {
     return gpr - (RB_WARPS - 1) * gper >= 2;
 }
 
-template <int MT, int GC, int NCH = 0>
+template <int MT, int GC, int NCH = 0, bool NORM = false>
 static int launch_skinny_stream_v(const SkinnyParams& p, int x_stride, size_t smem, unsigned grid, cudaStream_t st) {
     static bool attr_done[64] = {};
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev < 0 || dev >= 64) return LQ_EUNSUPPORTED;
     if (!attr_done[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(k_skinny_stream<MT, GC, NCH>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
+        cudaError_t e = cudaFuncSetAttribute(k_skinny_stream<MT, GC, NCH, NORM>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
         if (e != cudaSuccess) { set_cuda_error(e, "cudaFuncSetAttribute(k_skinny_stream)"); return LQ_ECUDA; }
         attr_done[dev] = true;
     }
-    launch_pdl(k_skinny_stream<MT, GC, NCH>, dim3(grid), RB_WARPS * 32, smem, st, p, x_stride);
+    launch_pdl(k_skinny_stream<MT, GC, NCH, NORM>, dim3(grid), RB_WARPS * 32, smem, st, p, x_stride);
     return check_launch("k_skinny_stream");
 }
 
@@ -745,6 +813,10 @@ static int launch_skinny_stream(const SkinnyParams& p, cudaStream_t st) {
     // K = 4096 with groups of 128: the written-out loop (scales / zeros are read as 8-byte words there)
     const bool nc4 = gc == 1 && p.K == 4096 && LQ_GEMV_PF == 4 && !getenv("LQ_SKINNY_NO_NC4") &&
                      (reinterpret_cast<uintptr_t>(p.scales) & 7) == 0 && (reinterpret_cast<uintptr_t>(p.zeros) & 7) == 0;
+    if (p.norm_gamma) {                             // fused-norm staging exists for the written-out K = 4096 loop, up to 8 tokens
+        if (!nc4 || mt != 1) return LQ_EUNSUPPORTED;
+        return launch_skinny_stream_v<1, 1, 4, true>(p, x_stride, smem, grid, st);
+    }
     if (nc4) return mt == 1 ? launch_skinny_stream_v<1, 1, 4>(p, x_stride, smem, grid, st) : launch_skinny_stream_v<2, 1, 4>(p, x_stride, smem, grid, st);
     if (gc == 1 && p.K == 11008 && LQ_GEMV_PF == 4 && !getenv("LQ_SKINNY_NO_NC4"))      // eleven chunks per warp, written out
         return mt == 1 ? launch_skinny_stream_v<1, 1, 11>(p, x_stride, smem, grid, st) : launch_skinny_stream_v<2, 1, 11>(p, x_stride, smem, grid, st);
@@ -760,6 +832,7 @@ int launch_skinny_rows(const SkinnyParams& p, cudaStream_t st) {
     if ((p.M <= 2 || getenv("LQ_SKINNY_STREAM_ALL")) && skinny_stream_supported(p.K, p.group) &&
         skinny_stream_smem(p.M, p.K, p.group) <= 96 * 1024)
         return launch_skinny_stream(p, st);
+    if (p.norm_gamma) return LQ_EUNSUPPORTED;       // the fused-norm staging exists in the streaming kernel only
     const int rpb = p.pair_stride > 0 ? 8 : 16;
     const unsigned grid = (unsigned)((p.N + rpb - 1) / rpb);
     const bool g128 = p.group == 128;

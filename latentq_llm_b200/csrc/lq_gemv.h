@@ -20,6 +20,16 @@ struct SkinnyParams {
     // gate[f] and up[f] of a token; the output is act[M, N] = silu(gate) * up with N = pair_stride features.
     int pair_stride;
     int hf_rounding;               // pair epilogue: round silu(gate) to bf16 before the product (eager-module chain)
+    // Fused residual add + RMSNorm in front (streaming kernel, K = 4096 only): when norm_gamma is set the tokens are not
+    // read from x but computed by every CTA as RMSNorm(norm_h + norm_delta) * norm_gamma, exactly as lq_add_rmsnorm
+    // computes them (same thread-to-element mapping, same order of the sum of squares); CTA 0 also writes the updated
+    // residual norm_h + norm_delta to norm_h_out (a buffer other than norm_h: the other CTAs still read norm_h).
+    const __nv_bfloat16* norm_h;
+    const __nv_bfloat16* norm_delta;   // or null
+    const __nv_bfloat16* norm_gamma;
+    __nv_bfloat16* norm_h_out;         // or null when norm_delta is null
+    float norm_eps;
+    int norm_hf;
 };
 
 // split-K plan of the skinny kernel: returns 64-k chunks per split and writes the number of splits
@@ -28,5 +38,7 @@ int launch_skinny_fwd(const SkinnyParams& p, cudaStream_t st);
 // row-block variant: one launch, no workspace (splits / chunks_per_split / partial are ignored)
 bool skinny_rows_supported(int64_t K, int group);
 int launch_skinny_rows(const SkinnyParams& p, cudaStream_t st);
+// true when launch_skinny_rows would take the streaming kernel with the fused-norm staging for this shape
+bool skinny_norm_supported(int64_t M, int64_t K, int group);
 
 }  // namespace lq

@@ -8,6 +8,8 @@ device buffers that the captured step itself advances, so a replay needs no host
 """
 from __future__ import annotations
 
+import os
+
 import torch
 from torch.nn.attention import SDPBackend, sdpa_kernel
 
@@ -129,6 +131,8 @@ class FusedLlamaGreedyDecoder:
         self.qkv = torch.zeros((batch, (self.Hq + 2 * self.Hkv) * self.hd), **bf)
         self.att = torch.zeros((batch, self.Hq * self.hd), **bf)
         self.tmp = torch.zeros((batch, self.D), **bf)
+        self.h2 = torch.zeros((batch, self.D), **bf)
+        self.fuse_norm = batch <= 2 and not os.environ.get("LQ_DECODE_NO_FUSED_NORM")
         self.gu = torch.zeros((batch, 2 * self.I), **bf)
         self.act = torch.zeros((batch, self.I), **bf)
         self.tok = torch.zeros((batch,), dtype=torch.long, device=dev)
@@ -145,18 +149,30 @@ class FusedLlamaGreedyDecoder:
         D, I, Hq, Hkv, hd = self.D, self.I, self.Hq, self.Hkv, self.hd
         self.h.copy_(torch.nn.functional.embedding(self.tok, self.model.model.embed_tokens.weight))
         delta = None
+        h, h_alt = self.h, self.h2          # the residual stream alternates between two buffers where the norm is fused
         for li, L in enumerate(self.layers):
             kc, vc = self.cache.layers[li].keys, self.cache.layers[li].values
-            ops.add_rmsnorm(self.h, delta, L["ln1"], self.eps, out=self.xn, hf_rounding=self.hf)
-            ops.gemm_a16w4_fwd(self.xn, *L["qkv"], None, (Hq + 2 * Hkv) * hd, D, out=self.qkv)
+            # one or two sequences: residual add + RMSNorm happen inside the projection's launch (None: no fused kernel)
+            fused = self.fuse_norm and ops.gemm_a16w4_fwd_rmsnorm(h, delta, L["ln1"], self.eps, h_alt, *L["qkv"],
+                                                                 (Hq + 2 * Hkv) * hd, D, out=self.qkv, hf_rounding=self.hf)
+            if fused is None or fused is False:
+                ops.add_rmsnorm(h, delta, L["ln1"], self.eps, out=self.xn, hf_rounding=self.hf)
+                ops.gemm_a16w4_fwd(self.xn, *L["qkv"], None, (Hq + 2 * Hkv) * hd, D, out=self.qkv)
+            elif delta is not None:
+                h, h_alt = h_alt, h
             ops.rope_kv_store(self.qkv, self.pos, self.inv_freq, kc, vc, Hq, Hkv, hd, hf_rounding=self.hf)
             ops.decode_attention(self.qkv, self.pos, kc, vc, Hq, Hkv, hd, out=self.att)
             ops.gemm_a16w4_fwd(self.att, *L["o"], None, D, Hq * hd, out=self.tmp)
-            ops.add_rmsnorm(self.h, self.tmp, L["ln2"], self.eps, out=self.xn, hf_rounding=self.hf)
-            ops.gemm_a16w4_fwd_silu(self.xn, *L["gu"], I, D, out=self.act, gate_up=self.gu, hf_rounding=self.hf)
+            fused = self.fuse_norm and ops.gemm_a16w4_fwd_rmsnorm(h, self.tmp, L["ln2"], self.eps, h_alt, *L["gu"], 2 * I, D,
+                                                                 out=self.act, silu_pair=True, hf_rounding=self.hf)
+            if fused is None or fused is False:
+                ops.add_rmsnorm(h, self.tmp, L["ln2"], self.eps, out=self.xn, hf_rounding=self.hf)
+                ops.gemm_a16w4_fwd_silu(self.xn, *L["gu"], I, D, out=self.act, gate_up=self.gu, hf_rounding=self.hf)
+            else:
+                h, h_alt = h_alt, h
             ops.gemm_a16w4_fwd(self.act, *L["down"], None, D, I, out=self.tmp)
             delta = self.tmp
-        ops.add_rmsnorm(self.h, delta, self.model.model.norm.weight.detach(), self.eps, out=self.xn, hf_rounding=self.hf)
+        ops.add_rmsnorm(h, delta, self.model.model.norm.weight.detach(), self.eps, out=self.xn, hf_rounding=self.hf)
         self.logits = torch.nn.functional.linear(self.xn, self.model.lm_head.weight)
         self.tok.copy_(self.logits.argmax(-1))
         self.pos.add_(1)

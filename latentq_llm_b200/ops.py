@@ -426,6 +426,29 @@ def add_rmsnorm(h, delta, gamma, eps, out=None, hf_rounding=True):
     return y
 
 
+def gemm_a16w4_fwd_rmsnorm(h, delta, gamma, eps, h_out, qweight, scales, zeros, N, K, group=128, out=None, silu_pair=False,
+                           hf_rounding=True):
+    """y = (RMSNorm(h + delta) * gamma) · deq(Wq)^T in ONE launch for decode-sized token counts (at most two tokens,
+    K = 4096, group 128): the residual add and the norm happen in the GEMM kernel's token staging, bit for bit as
+    `add_rmsnorm` computes them.  `h_out` (a buffer other than `h`) receives h + delta when `delta` is given.  With
+    `silu_pair` the weight holds gate | up (N = 2 I rows) and the result is silu(gate) * up [M, I].
+    Returns None when the shape has no fused kernel: call `add_rmsnorm` and the GEMM separately then."""
+    _chk(h, "h", torch.bfloat16); _chk(gamma, "gamma", torch.bfloat16); _chk(qweight, "qweight", torch.int8)
+    M = h.shape[0]
+    if delta is not None:
+        _chk(delta, "delta", torch.bfloat16); _chk(h_out, "h_out", torch.bfloat16)
+        assert delta.shape == h.shape == h_out.shape and h_out.data_ptr() != h.data_ptr()
+    n_out = N // 2 if silu_pair else N
+    y = out if out is not None else torch.empty((M, n_out), dtype=torch.bfloat16, device=h.device)
+    rc = L.lib.lq_gemm_a16w4_fwd_rmsnorm(_ptr(h), _ptr(delta), _ptr(gamma), float(eps), int(hf_rounding), _ptr(h_out),
+                                         _ptr(qweight), _ptr(scales), _ptr(zeros), _ptr(y), M, N, K, group, int(silu_pair),
+                                         _stream())
+    if rc == L.LQ_EUNSUPPORTED:
+        return None
+    L.check("lq_gemm_a16w4_fwd_rmsnorm", rc)
+    return y
+
+
 def rope_kv_store(qkv, positions, inv_freq, k_cache, v_cache, Hq, Hkv, hd, tokens_per_seq=1, hf_rounding=True):
     """RoPE on the q and k heads of qkv [M, (Hq + 2 Hkv) hd] (q in place); rotated k and v go into the caches
     [batch, Hkv, max_len, hd] at positions[m] (PTQ/quant/fused_attn.py:8-58)."""

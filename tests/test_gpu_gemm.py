@@ -383,3 +383,48 @@ def test_a16w4_dgrad_through_transposed_copy(ops, monkeypatch, M, N, K, force):
     if not force:
         assert torch.equal(out["copy"], out["stored"])
     ops._ws_need.clear()
+
+
+@pytest.mark.parametrize("hf", [1, 0])
+@pytest.mark.parametrize("with_delta", [True, False])
+@pytest.mark.parametrize("M,N", [(1, 12288), (2, 12288), (1, 22016), (2, 22016), (2, 4160)])
+def test_a16w4_decode_forward_with_residual_add_and_rmsnorm_in_the_launch(ops, M, N, with_delta, hf):
+    """One or two tokens at K = 4096: the streaming decode kernel computes RMSNorm(h + delta) * gamma while it stages
+    its tokens.  The new residual stream and the projection are bit for bit those of `add_rmsnorm` followed by the
+    GEMM (plain and gate|up + silu), with and without a delta, in both rounding modes of the norm; other shapes
+    answer LQ_EUNSUPPORTED (None) and write nothing."""
+    K = 4096
+    codes, sb, zb = make_w4_layer(ops, N, K, seed=23)
+    g = torch.Generator(device="cuda").manual_seed(N + M + hf)
+    h = (torch.randn(M, K, device="cuda", generator=g) * 2).to(torch.bfloat16)
+    delta = torch.randn(M, K, device="cuda", generator=g).to(torch.bfloat16) if with_delta else None
+    gamma = (1 + 0.1 * torch.randn(K, device="cuda", generator=g)).to(torch.bfloat16)
+    eps = 1e-5
+    for silu in (False, True):
+        if silu and N % 16:
+            continue
+        h_ref = h.clone()
+        xn = ops.add_rmsnorm(h_ref, delta, gamma, eps, hf_rounding=hf)          # h_ref += delta in place
+        if silu:
+            want = ops.gemm_a16w4_fwd_silu(xn, codes, sb, zb, N // 2, K, hf_rounding=hf)
+        else:
+            want = ops.gemm_a16w4_fwd(xn, codes, sb, zb, None, N, K)
+        h_in, h_out = h.clone(), torch.full_like(h, 7.0)
+        got = ops.gemm_a16w4_fwd_rmsnorm(h_in, delta, gamma, eps, h_out, codes, sb, zb, N, K, silu_pair=silu, hf_rounding=hf)
+        assert got is not None
+        assert torch.equal(got, want)
+        assert torch.equal(h_in, h)                                              # the input stream is left alone
+        if with_delta:
+            assert torch.equal(h_out, h_ref)
+        else:
+            assert torch.equal(h_out, torch.full_like(h, 7.0))                   # nothing to add: nothing written
+
+
+def test_a16w4_rmsnorm_forward_refuses_shapes_without_a_fused_kernel(ops):
+    for M, N, K in [(3, 4096, 4096), (1, 4096, 2048), (16, 12288, 4096), (1, 4096, 11008)]:
+        codes, sb, zb = make_w4_layer(ops, N, K, seed=3)
+        h = torch.randn(M, K, device="cuda").to(torch.bfloat16)
+        gamma = torch.ones(K, device="cuda", dtype=torch.bfloat16)
+        y = torch.full((M, N), 3.0, device="cuda", dtype=torch.bfloat16)
+        assert ops.gemm_a16w4_fwd_rmsnorm(h, None, gamma, 1e-5, None, codes, sb, zb, N, K, out=y) is None
+        assert torch.equal(y, torch.full_like(y, 3.0))

@@ -64,3 +64,33 @@ def test_fused_llama_decoder_against_the_eager_modules():
     # a second prompt replays the captured graph
     prompt2 = torch.randint(0, 1024, (B, P + 8), device="cuda", generator=g)
     assert torch.equal(fused.generate(prompt2, T, use_graph=True), fused.generate(prompt2, T, use_graph=False))
+
+
+@pytest.mark.parametrize("B", [1, 2])
+def test_fused_decoder_with_the_norm_inside_the_projections_decodes_the_same_tokens(monkeypatch, B):
+    """One or two sequences at hidden size 4096: the residual add and both RMSNorms of a layer run inside the q|k|v and
+    gate|up launches, the residual stream alternating between two buffers.  Same bits as the chain with separate norm
+    launches: logits and tokens identical, eager chain and graph replay alike."""
+    from latentq_llm_b200 import finetune as ft, ops
+    from latentq_llm_b200.generate import FusedLlamaGreedyDecoder
+    model = ft.build_model("llama-wide-tiny", "cuda", seed=5)
+    ft.quantize_decoder(model, lbit=4, gbit=16)
+    model.eval()
+    P, T = 24, 8
+    g = torch.Generator(device="cuda").manual_seed(B)
+    prompt = torch.randint(0, 1024, (B, P), device="cuda", generator=g)
+    monkeypatch.setenv("LQ_DECODE_NO_FUSED_NORM", "1")
+    plain = FusedLlamaGreedyDecoder(model, batch=B, max_len=64)
+    assert not plain.fuse_norm
+    want = plain.generate(prompt, T, use_graph=False)
+    want_logits = plain.logits.clone()
+    monkeypatch.delenv("LQ_DECODE_NO_FUSED_NORM")
+    fused = FusedLlamaGreedyDecoder(model, batch=B, max_len=64)
+    assert fused.fuse_norm
+    calls = []
+    real = ops.gemm_a16w4_fwd_rmsnorm
+    monkeypatch.setattr(ops, "gemm_a16w4_fwd_rmsnorm", lambda *a, **k: (calls.append(1), real(*a, **k))[1])
+    got = fused.generate(prompt, T, use_graph=False)
+    assert calls and torch.equal(got, want) and torch.equal(fused.logits, want_logits)
+    assert torch.equal(fused.generate(prompt, T, use_graph=True), want)
+    assert torch.equal(fused.logits, want_logits)

@@ -251,6 +251,21 @@ LQ_API int lq_gemm_a16w4_fwd_rmsnorm(const void* h, const void* delta, const voi
                                      const int8_t* qweight, const void* scales, const void* zeros, void* y, int64_t M, int64_t N,
                                      int64_t K, int group, int silu_pair, lq_stream_t stream);
 
+/* Decode-sized q|k|v projection (M <= 16) with the rotary embedding and the KV-cache write as its epilogue
+ * (fused QuantLinear of PTQ/quant/fused_attn.py:164-204, triton_rotate_half_ fused_attn.py:8-58 and the cache append
+ * fused_attn.py:124-140): one launch leaves what lq_gemm_a16w4_fwd followed by lq_rope_kv_store leaves, bit for bit -
+ * qkv[M, (Hq + 2 Hkv) hd] with q rotated and k, v as projected, rotated k and v in the caches
+ * [batch, kv head, max_len, hd] at positions[m] (batch = m / tokens_per_seq).  The kernel pairs weight row i of a head
+ * with row i + hd/2 in one MMA block so that a thread holds both halves of a rotation.
+ * Tokens: x[M,K] when gamma is NULL; otherwise RMSNorm(h + delta) * gamma computed in the token staging exactly as
+ * lq_gemm_a16w4_fwd_rmsnorm does (same arguments, same shape limits).  LQ_EUNSUPPORTED for M > 16, hd not a multiple of
+ * 16, or K / group the row-block decode kernels do not serve: run the GEMM and lq_rope_kv_store then. */
+LQ_API int lq_gemm_a16w4_fwd_qkv_rope(const void* x, const void* h, const void* delta, const void* gamma, float eps,
+                                      void* h_out, const int8_t* qweight, const void* scales, const void* zeros, void* qkv,
+                                      const int64_t* positions, const float* inv_freq, void* k_cache, void* v_cache,
+                                      int64_t M, int Hq, int Hkv, int hd, int64_t K, int group, int64_t max_len,
+                                      int tokens_per_seq, int hf_rounding, lq_stream_t stream);
+
 /* QLinearFunctionW4.backward grad_weight (utils/quant.py:141-142) and its accumulation over micro-batches by the
  * backward hook (:408-411): dw[N,K] (+)= dy[M,N]^T · x[M,K], all bf16 row-major, fp32 accumulation in tensor memory.
  * accumulate != 0: dw = bf16(fp32(dw) + product), one rounding, what a GEMM with beta = 1 computes; 0: dw = bf16(product).

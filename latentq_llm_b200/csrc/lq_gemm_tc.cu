@@ -1321,6 +1321,38 @@ int lq_gemm_a16w4_fwd_rmsnorm(const void* h, const void* delta, const void* gamm
     return launch_skinny_rows(sp, (cudaStream_t)stream);
 }
 
+int lq_gemm_a16w4_fwd_qkv_rope(const void* x, const void* h, const void* delta, const void* gamma, float eps, void* h_out,
+                               const int8_t* qweight, const void* scales, const void* zeros, void* qkv, const int64_t* positions,
+                               const float* inv_freq, void* k_cache, void* v_cache, int64_t M, int Hq, int Hkv, int hd, int64_t K,
+                               int group, int64_t max_len, int tokens_per_seq, int hf_rounding, lq_stream_t stream) {
+    if (!qweight || !scales || !zeros || !qkv || !positions || !inv_freq || !k_cache || !v_cache || !al16(qweight) || !al16(qkv))
+        return LQ_EINVAL;
+    if (gamma ? (!h || !al16(h) || !al16(gamma) || (delta && (!h_out || h_out == h || !al16(delta) || !al16(h_out)))) : (!x || !al16(x)))
+        return LQ_EINVAL;
+    if (Hq < 1 || Hkv < 1 || (Hq % Hkv) != 0 || hd < 16 || hd > 512 || (hd % 16) != 0 || tokens_per_seq < 1 || max_len < 1 ||
+        max_len >= (1ll << 31) || Hq + 2 * Hkv > 65535)
+        return LQ_EUNSUPPORTED;
+    const int64_t N = (int64_t)(Hq + 2 * Hkv) * hd;
+    if (!shape_ok_w4(M, N, K, group) || M > 16 || !skinny_rows_supported(K, group) || getenv("LQ_SKINNY_SPLIT")) return LQ_EUNSUPPORTED;
+    if (gamma && (!skinny_norm_supported(M, K, group) || (reinterpret_cast<uintptr_t>(scales) & 7) || (reinterpret_cast<uintptr_t>(zeros) & 7)))
+        return LQ_EUNSUPPORTED;
+    if (M == 0) return LQ_OK;
+    { int rc_dev = ensure_device_for(qkv); if (rc_dev) return rc_dev; }
+    SkinnyParams sp{};
+    sp.x = (const __nv_bfloat16*)x; sp.qweight = (const uint8_t*)qweight; sp.scales = (const __nv_bfloat16*)scales;
+    sp.zeros = (const __nv_bfloat16*)zeros; sp.out = (__nv_bfloat16*)qkv; sp.M = (int)M; sp.K = (int)K; sp.group = group;
+    sp.splits = 1; sp.chunks_per_split = (int)(K / 64);
+    sp.N = (int)(N / 2); sp.pair_stride = hd / 2; sp.hf_rounding = hf_rounding;       // N counts rotation pairs
+    sp.rope_pos = (const long long*)positions; sp.rope_inv_freq = inv_freq; sp.rope_k = (__nv_bfloat16*)k_cache;
+    sp.rope_v = (__nv_bfloat16*)v_cache; sp.rope_hd = hd; sp.rope_hq = Hq; sp.rope_hkv = Hkv; sp.rope_max_len = (int)max_len;
+    sp.rope_tps = tokens_per_seq;
+    if (gamma) {
+        sp.norm_h = (const __nv_bfloat16*)h; sp.norm_delta = (const __nv_bfloat16*)delta; sp.norm_gamma = (const __nv_bfloat16*)gamma;
+        sp.norm_h_out = (__nv_bfloat16*)h_out; sp.norm_eps = eps; sp.norm_hf = hf_rounding;
+    }
+    return launch_skinny_rows(sp, (cudaStream_t)stream);
+}
+
 int lq_gemm_wgrad(const void* dy, const void* x, void* dw, int64_t M, int64_t N, int64_t K, int accumulate, lq_stream_t stream) {
     if (!dy || !x || !dw || !al16(dy) || !al16(x) || !al16(dw)) return LQ_EINVAL;
     if (M < 0 || N <= 0 || K <= 0 || M >= (1 << 30) || N >= (1 << 30) || K >= (1 << 30) || (N % 8) != 0 || (K % 8) != 0) return LQ_EUNSUPPORTED;

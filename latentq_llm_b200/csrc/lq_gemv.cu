@@ -42,6 +42,44 @@ __device__ __forceinline__ void mma_16816_start(float (&d)[4], const uint32_t (&
         : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "f"(0.0f));
 }
 
+// Rotary embedding + cache write for one (token, rotation pair) of a q|k|v projection block (see SkinnyParams):
+// x / yv are the bf16-rounded projections of elements i and i + hd/2 of the head that pair block `blk` belongs to.
+__device__ __forceinline__ void rope_store(const SkinnyParams& p, int blk, int fi, int tok, float x, float yv) {
+    const int hd = p.rope_hd, half = hd >> 1, bph = hd >> 4;
+    const int head = blk / bph, i = (blk - head * bph) * 8 + fi;
+    const long long pos = p.rope_pos[tok];
+    const bool pos_ok = pos >= 0 && pos < p.rope_max_len;
+    const int b = tok / p.rope_tps;
+    __nv_bfloat16* dst = p.out + (size_t)tok * (size_t)(2 * p.N) + (size_t)head * hd;
+    const __nv_bfloat16 rx = __float2bfloat16_rn(x), ry = __float2bfloat16_rn(yv);
+    if (head >= p.rope_hq + p.rope_hkv) {                     // v: as projected, into the buffer and the cache
+        dst[i] = rx; dst[i + half] = ry;
+        if (pos_ok) {
+            __nv_bfloat16* c = p.rope_v + (((size_t)b * p.rope_hkv + (head - p.rope_hq - p.rope_hkv)) * p.rope_max_len + (size_t)pos) * hd;
+            c[i] = rx; c[i + half] = ry;
+        }
+        return;
+    }
+    float sn, cs;
+    sincosf((float)pos * p.rope_inv_freq[i], &sn, &cs);
+    float ox, oy;
+    if (p.hf_rounding) {      // cos / sin cast to bf16, then q*cos + rotate_half(q)*sin as bf16 tensor ops
+        cs = bf16r(cs); sn = bf16r(sn);
+        ox = __fadd_rn(bf16r(__fmul_rn(x, cs)), bf16r(__fmul_rn(-yv, sn)));
+        oy = __fadd_rn(bf16r(__fmul_rn(yv, cs)), bf16r(__fmul_rn(x, sn)));
+    } else {
+        ox = __fsub_rn(__fmul_rn(x, cs), __fmul_rn(yv, sn));
+        oy = __fadd_rn(__fmul_rn(x, sn), __fmul_rn(yv, cs));
+    }
+    const __nv_bfloat16 bx = __float2bfloat16_rn(ox), by = __float2bfloat16_rn(oy);
+    if (head < p.rope_hq) { dst[i] = bx; dst[i + half] = by; return; }               // q: rotated in the buffer
+    dst[i] = rx; dst[i + half] = ry;                                                  // k: as projected in the buffer
+    if (pos_ok) {
+        __nv_bfloat16* c = p.rope_k + (((size_t)b * p.rope_hkv + (head - p.rope_hq)) * p.rope_max_len + (size_t)pos) * hd;
+        c[i] = bx; c[i + half] = by;
+    }
+}
+
 // 8 codes of one packed word -> 4 bf16 pairs (128 + c_k, 128 + c_{k+4}) for k = 0..3 (OR into the mantissa of 128.0)
 __device__ __forceinline__ void extract_word(uint32_t w, uint32_t* p) {
     const uint32_t MAGIC = 0x43004300u, MASK = 0x000F000Fu;
@@ -224,7 +262,9 @@ __global__ void __launch_bounds__(RB_WARPS * 32, 2) k_skinny_rows(const SkinnyPa
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
     const bool pair = p.pair_stride > 0;
     const int row0 = blockIdx.x * (pair ? 8 : 16);
-    const int ra = min(row0 + g, p.N - 1);                                          // clamped loads, guarded stores
+    const int rope_bph = p.rope_hd >> 4;                                            // pair blocks per head (rope mode)
+    const int ra = p.rope_hd ? ((int)blockIdx.x / rope_bph) * p.rope_hd + ((int)blockIdx.x % rope_bph) * 8 + g
+                             : min(row0 + g, p.N - 1);                              // clamped loads, guarded stores
     const int rb = pair ? p.pair_stride + ra : min(row0 + g + 8, p.N - 1);
     const int gpr = NC4 ? 32 : p.K / (RB_CHUNK * GC);                               // groups per weight row
     const int gper = NC4 ? 4 : (gpr + RB_WARPS - 1) / RB_WARPS;
@@ -381,6 +421,7 @@ __global__ void __launch_bounds__(RB_WARPS * 32, 2) k_skinny_rows(const SkinnyPa
             float ag = 0.0f, au = 0.0f;
 #pragma unroll
             for (int w = 0; w < RB_WARPS; ++w) { ag = __fadd_rn(ag, red[w][m][idx]); au = __fadd_rn(au, red[w][m][idx + 2]); }
+            if (p.rope_hd) { rope_store(p, (int)blockIdx.x, ln >> 2, tok, bf16r(ag), bf16r(au)); continue; }
             p.out[(size_t)tok * p.N + f] = __float2bfloat16_rn(silu_mul_bf16(bf16r(ag), bf16r(au), p.hf_rounding));
             continue;
         }
@@ -443,6 +484,7 @@ __global__ void __launch_bounds__(RB_WARPS * 32, LQ_GEMV_MINB) k_skinny_stream(c
     const unsigned short* sc_all = reinterpret_cast<const unsigned short*>(p.scales);
     const unsigned short* zp_all = reinterpret_cast<const unsigned short*>(p.zeros);
     auto row_of = [&](int b, int half) {                                                           // clamped loads, guarded stores
+        if (p.rope_hd) { const int bph = p.rope_hd >> 4; return (b / bph) * p.rope_hd + (b % bph) * 8 + g + half * p.pair_stride; }
         return pair ? half * p.pair_stride + min(b * 8 + g, p.N - 1) : min(b * 16 + g + half * 8, p.N - 1);
     };
     auto wptr = [&](int row) { return reinterpret_cast<const uint4*>(p.qweight + (size_t)row * (p.K / 2) + (size_t)g_begin * GC * (RB_CHUNK / 2)) + t; };
@@ -754,6 +796,7 @@ __global__ void __launch_bounds__(RB_WARPS * 32, LQ_GEMV_MINB) k_skinny_stream(c
                 float ag = 0.0f, au = 0.0f;
 #pragma unroll
                 for (int w = 0; w < RB_WARPS; ++w) { ag = __fadd_rn(ag, red[buf][w][m][idx]); au = __fadd_rn(au, red[buf][w][m][idx + 2]); }
+                if (p.rope_hd) { rope_store(p, blk, ln >> 2, tok, bf16r(ag), bf16r(au)); continue; }
                 p.out[(size_t)tok * p.N + f] = __float2bfloat16_rn(silu_mul_bf16(bf16r(ag), bf16r(au), p.hf_rounding));
                 continue;
             }

@@ -30,6 +30,16 @@ struct SkinnyParams {
     __nv_bfloat16* norm_h_out;         // or null when norm_delta is null
     float norm_eps;
     int norm_hf;
+    // Fused rotary embedding + KV-cache write behind a q|k|v projection (row-block kernels): rope_hd > 0 pairs weight
+    // row i of a head with row i + hd/2 of the same head in one MMA block (pair_stride = hd/2, N = pairs), so that one
+    // thread holds both halves of a rotation.  out is the [M, (Hq + 2 Hkv) hd] projection buffer: q is written rotated,
+    // k and v as projected; rotated k and v also go to the caches [batch, kv head, max_len, hd] at the token's
+    // position.  Same arithmetic as lq_rope_kv_store on the bf16 projection.
+    const long long* rope_pos;         // [M]
+    const float* rope_inv_freq;        // [hd / 2]
+    __nv_bfloat16* rope_k;
+    __nv_bfloat16* rope_v;
+    int rope_hd, rope_hq, rope_hkv, rope_max_len, rope_tps;
 };
 
 // split-K plan of the skinny kernel: returns 64-k chunks per split and writes the number of splits

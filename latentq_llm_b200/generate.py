@@ -133,6 +133,7 @@ class FusedLlamaGreedyDecoder:
         self.tmp = torch.zeros((batch, self.D), **bf)
         self.h2 = torch.zeros((batch, self.D), **bf)
         self.fuse_norm = batch <= 2 and not os.environ.get("LQ_DECODE_NO_FUSED_NORM")
+        self.fuse_rope = batch <= 16 and not os.environ.get("LQ_DECODE_NO_FUSED_ROPE")
         self.gu = torch.zeros((batch, 2 * self.I), **bf)
         self.act = torch.zeros((batch, self.I), **bf)
         self.tok = torch.zeros((batch,), dtype=torch.long, device=dev)
@@ -145,6 +146,26 @@ class FusedLlamaGreedyDecoder:
         with ops.decode_chain():          # launches may start while their predecessor runs (weights are constant here)
             self._step_kernels(ops)
 
+    def _qkv(self, ops, L, h, h_alt, delta, kc, vc) -> bool:
+        """Residual add + RMSNorm + q|k|v projection + RoPE + cache write of one layer in as few launches as the batch
+        allows: one (one or two sequences at hidden size 4096), two (up to 16 sequences: RoPE and the cache write are
+        the projection's epilogue) or three.  True when the residual stream now lives in `h_alt`."""
+        Hq, Hkv, hd, D = self.Hq, self.Hkv, self.hd, self.D
+        N = (Hq + 2 * Hkv) * hd
+        rope = (self.pos, self.inv_freq, kc, vc, Hq, Hkv, hd, D)
+        kw = dict(out=self.qkv, hf_rounding=self.hf)
+        norm = (h, delta, L["ln1"], self.eps, h_alt)
+        if self.fuse_norm and self.fuse_rope and ops.gemm_a16w4_fwd_qkv_rope(None, *L["qkv"], *rope, norm=norm, **kw) is not None:
+            return delta is not None
+        if self.fuse_norm and ops.gemm_a16w4_fwd_rmsnorm(*norm, *L["qkv"], N, D, **kw) is not None:
+            ops.rope_kv_store(self.qkv, self.pos, self.inv_freq, kc, vc, Hq, Hkv, hd, hf_rounding=self.hf)
+            return delta is not None
+        ops.add_rmsnorm(h, delta, L["ln1"], self.eps, out=self.xn, hf_rounding=self.hf)
+        if not (self.fuse_rope and ops.gemm_a16w4_fwd_qkv_rope(self.xn, *L["qkv"], *rope, **kw) is not None):
+            ops.gemm_a16w4_fwd(self.xn, *L["qkv"], None, N, D, out=self.qkv)
+            ops.rope_kv_store(self.qkv, self.pos, self.inv_freq, kc, vc, Hq, Hkv, hd, hf_rounding=self.hf)
+        return False
+
     def _step_kernels(self, ops):
         D, I, Hq, Hkv, hd = self.D, self.I, self.Hq, self.Hkv, self.hd
         self.h.copy_(torch.nn.functional.embedding(self.tok, self.model.model.embed_tokens.weight))
@@ -152,15 +173,8 @@ class FusedLlamaGreedyDecoder:
         h, h_alt = self.h, self.h2          # the residual stream alternates between two buffers where the norm is fused
         for li, L in enumerate(self.layers):
             kc, vc = self.cache.layers[li].keys, self.cache.layers[li].values
-            # one or two sequences: residual add + RMSNorm happen inside the projection's launch (None: no fused kernel)
-            fused = self.fuse_norm and ops.gemm_a16w4_fwd_rmsnorm(h, delta, L["ln1"], self.eps, h_alt, *L["qkv"],
-                                                                 (Hq + 2 * Hkv) * hd, D, out=self.qkv, hf_rounding=self.hf)
-            if fused is None or fused is False:
-                ops.add_rmsnorm(h, delta, L["ln1"], self.eps, out=self.xn, hf_rounding=self.hf)
-                ops.gemm_a16w4_fwd(self.xn, *L["qkv"], None, (Hq + 2 * Hkv) * hd, D, out=self.qkv)
-            elif delta is not None:
+            if self._qkv(ops, L, h, h_alt, delta, kc, vc):
                 h, h_alt = h_alt, h
-            ops.rope_kv_store(self.qkv, self.pos, self.inv_freq, kc, vc, Hq, Hkv, hd, hf_rounding=self.hf)
             ops.decode_attention(self.qkv, self.pos, kc, vc, Hq, Hkv, hd, out=self.att)
             ops.gemm_a16w4_fwd(self.att, *L["o"], None, D, Hq * hd, out=self.tmp)
             fused = self.fuse_norm and ops.gemm_a16w4_fwd_rmsnorm(h, self.tmp, L["ln2"], self.eps, h_alt, *L["gu"], 2 * I, D,

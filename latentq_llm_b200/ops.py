@@ -449,6 +449,41 @@ def gemm_a16w4_fwd_rmsnorm(h, delta, gamma, eps, h_out, qweight, scales, zeros, 
     return y
 
 
+def gemm_a16w4_fwd_qkv_rope(x, qweight, scales, zeros, positions, inv_freq, k_cache, v_cache, Hq, Hkv, hd, K, group=128, out=None,
+                            tokens_per_seq=1, hf_rounding=True, norm=None):
+    """Decode-sized fused q|k|v projection with the rotary embedding and the KV-cache write as its epilogue: leaves what
+    `gemm_a16w4_fwd` followed by `rope_kv_store` leaves (q rotated in the returned [M, (Hq + 2 Hkv) hd] buffer, rotated k
+    and v in the caches), in one launch.  `norm=(h, delta, gamma, eps, h_out)` computes the tokens as
+    RMSNorm(h + delta) * gamma in the same launch (`x` is ignored; see `gemm_a16w4_fwd_rmsnorm`).
+    Returns None when the shape has no fused kernel."""
+    _chk(qweight, "qweight", torch.int8); _chk(positions, "positions", torch.int64); _chk(inv_freq, "inv_freq", torch.float32)
+    _chk(k_cache, "k_cache", torch.bfloat16); _chk(v_cache, "v_cache", torch.bfloat16)
+    h = delta = gamma = h_out = None
+    eps = 0.0
+    if norm is not None:
+        h, delta, gamma, eps, h_out = norm
+        _chk(h, "h", torch.bfloat16); _chk(gamma, "gamma", torch.bfloat16)
+        if delta is not None:
+            _chk(delta, "delta", torch.bfloat16); _chk(h_out, "h_out", torch.bfloat16)
+            assert delta.shape == h.shape == h_out.shape and h_out.data_ptr() != h.data_ptr()
+        M = h.shape[0]
+    else:
+        _chk(x, "x", torch.bfloat16)
+        M = x.shape[0]
+    N = (Hq + 2 * Hkv) * hd
+    max_len = k_cache.shape[2]
+    assert positions.numel() == M and inv_freq.numel() == hd // 2 and k_cache.shape == v_cache.shape and k_cache.shape[3] == hd
+    y = out if out is not None else torch.empty((M, N), dtype=torch.bfloat16, device=qweight.device)
+    rc = L.lib.lq_gemm_a16w4_fwd_qkv_rope(_ptr(None if norm is not None else x), _ptr(h), _ptr(delta), _ptr(gamma), float(eps),
+                                          _ptr(h_out), _ptr(qweight), _ptr(scales), _ptr(zeros), _ptr(y), _ptr(positions),
+                                          _ptr(inv_freq), _ptr(k_cache), _ptr(v_cache), M, Hq, Hkv, hd, K, group, max_len,
+                                          tokens_per_seq, int(hf_rounding), _stream())
+    if rc == L.LQ_EUNSUPPORTED:
+        return None
+    L.check("lq_gemm_a16w4_fwd_qkv_rope", rc)
+    return y
+
+
 def rope_kv_store(qkv, positions, inv_freq, k_cache, v_cache, Hq, Hkv, hd, tokens_per_seq=1, hf_rounding=True):
     """RoPE on the q and k heads of qkv [M, (Hq + 2 Hkv) hd] (q in place); rotated k and v go into the caches
     [batch, Hkv, max_len, hd] at positions[m] (PTQ/quant/fused_attn.py:8-58)."""

@@ -428,3 +428,57 @@ def test_a16w4_rmsnorm_forward_refuses_shapes_without_a_fused_kernel(ops):
         y = torch.full((M, N), 3.0, device="cuda", dtype=torch.bfloat16)
         assert ops.gemm_a16w4_fwd_rmsnorm(h, None, gamma, 1e-5, None, codes, sb, zb, N, K, out=y) is None
         assert torch.equal(y, torch.full_like(y, 3.0))
+
+
+@pytest.mark.parametrize("hf", [1, 0])
+@pytest.mark.parametrize("M,Hq,Hkv,hd,K,with_norm", [(1, 32, 32, 128, 4096, True), (2, 32, 8, 128, 4096, True), (1, 8, 8, 128, 4096, False),
+                                                     (16, 32, 32, 128, 4096, False), (5, 8, 2, 64, 2048, False), (2, 4, 4, 64, 256, False),
+                                                     (9, 8, 4, 128, 11008, False)])
+def test_a16w4_qkv_projection_with_rope_and_cache_write_as_its_epilogue(ops, M, Hq, Hkv, hd, K, with_norm, hf):
+    """Up to 16 tokens: the q|k|v projection pairs rows i and i + hd/2 of a head in one MMA block and finishes with the
+    rotary embedding and the KV-cache write.  The projection buffer (q rotated, k and v as projected) and both caches
+    are bit for bit those of the GEMM followed by `rope_kv_store`, for full and grouped KV heads, head sizes 64 and
+    128, both rounding modes, a position beyond the cache (nothing written), and with the residual add + RMSNorm in the
+    same launch (one or two tokens, K = 4096)."""
+    N, max_len = (Hq + 2 * Hkv) * hd, 80
+    codes, sb, zb = make_w4_layer(ops, N, K, seed=29)
+    g = torch.Generator(device="cuda").manual_seed(N + M + hf)
+    h = torch.randn(M, K, device="cuda", generator=g).to(torch.bfloat16)
+    delta = torch.randn(M, K, device="cuda", generator=g).to(torch.bfloat16)
+    gamma = (1 + 0.1 * torch.randn(K, device="cuda", generator=g)).to(torch.bfloat16)
+    pos = torch.randint(0, max_len, (M,), device="cuda", generator=g)
+    if M > 1:
+        pos[M - 1] = max_len + 3                     # beyond the cache: the caches stay untouched for that token
+    inv_freq = (1.0 / (10000.0 ** (torch.arange(0, hd, 2, dtype=torch.float32) / hd))).cuda()
+    kc = (torch.randn(M, Hkv, max_len, hd, device="cuda", generator=g)).to(torch.bfloat16)
+    vc = (torch.randn(M, Hkv, max_len, hd, device="cuda", generator=g)).to(torch.bfloat16)
+    eps = 1e-5
+    # two launches (three with the norm)
+    h_ref, kc_ref, vc_ref = h.clone(), kc.clone(), vc.clone()
+    x = ops.add_rmsnorm(h_ref, delta, gamma, eps, hf_rounding=hf) if with_norm else h
+    want = ops.gemm_a16w4_fwd(x, codes, sb, zb, None, N, K)
+    ops.rope_kv_store(want, pos, inv_freq, kc_ref, vc_ref, Hq, Hkv, hd, hf_rounding=hf)
+    # one launch
+    kc_got, vc_got, h_out = kc.clone(), vc.clone(), torch.zeros_like(h)
+    norm = (h.clone(), delta, gamma, eps, h_out) if with_norm else None
+    got = ops.gemm_a16w4_fwd_qkv_rope(None if with_norm else h, codes, sb, zb, pos, inv_freq, kc_got, vc_got, Hq, Hkv, hd, K,
+                                      hf_rounding=hf, norm=norm)
+    assert got is not None
+    assert torch.equal(got, want)
+    assert torch.equal(kc_got, kc_ref) and torch.equal(vc_got, vc_ref)
+    assert not torch.equal(kc_got, kc)               # the caches did receive the in-range tokens
+    if with_norm:
+        assert torch.equal(h_out, h_ref)
+
+
+def test_a16w4_qkv_rope_projection_refuses_what_it_does_not_serve(ops):
+    Hq = Hkv = 4
+    for M, hd, K in [(17, 128, 4096), (2, 24, 1024)]:
+        codes, sb, zb = make_w4_layer(ops, 64, K, seed=3)            # refused before anything is read
+        x = torch.randn(M, K, device="cuda").to(torch.bfloat16)
+        pos = torch.zeros(M, dtype=torch.long, device="cuda")
+        inv_freq = torch.ones(hd // 2, device="cuda")
+        kc = torch.zeros(M, Hkv, 8, hd, dtype=torch.bfloat16, device="cuda")
+        vc = torch.zeros_like(kc)
+        assert ops.gemm_a16w4_fwd_qkv_rope(x, codes, sb, zb, pos, inv_freq, kc, vc, Hq, Hkv, hd, K) is None
+        assert not kc.any() and not vc.any()

@@ -345,6 +345,12 @@ LQ_API int lq_decode_attention(const void* q, int64_t q_row_stride, const void* 
  * other shapes return LQ_EUNSUPPORTED: use lq_gemm_a16w4_fwd into [M, 2I] and lq_silu_mul. */
 LQ_API int lq_gemm_a16w4_fwd_silu(const void* x, const int8_t* qweight, const void* scales, const void* zeros, void* act,
                                   int64_t M, int64_t I, int64_t K, int group, int hf_rounding, lq_stream_t stream);
+/* End of a greedy decode step (the argmax + embedding look-up of HF generate's loop that the reference drives,
+ * generate.py:150-190) in one launch: tok[b] = argmax over logits[b, 0..V) (bf16, row stride logits_stride elements; the
+ * first maximum, NaN counted as the largest value, as torch.argmax); positions[b] += 1 when positions is not NULL;
+ * h[b, 0..D) = embed[tok[b], 0..D) when embed is not NULL (D a multiple of 8, both 16-byte aligned). */
+LQ_API int lq_argmax_embed(const void* logits, int64_t logits_stride, int64_t B, int64_t V, const void* embed, int64_t D,
+                           int64_t* tok, int64_t* positions, void* h, lq_stream_t stream);
 /* act[M, I] = silu(gate_up[M, 0:I]) * gate_up[M, I:2I] (epilogue of PTQ/quant/fused_mlp.py:84-168; LlamaMLP). */
 LQ_API int lq_silu_mul(const void* gate_up, void* act, int64_t M, int64_t I, int hf_rounding, lq_stream_t stream);
 

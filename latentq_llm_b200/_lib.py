@@ -103,6 +103,7 @@ SIGNATURES = {
     "lq_gemm_a16w4_fwd_rmsnorm": [_p, _p, _p, _f, _i, _p, _p, _p, _p, _p, _i64, _i64, _i64, _i, _i, _p],
     "lq_gemm_a16w4_fwd_qkv_rope": [_p, _p, _p, _p, _f, _p, _p, _p, _p, _p, _p, _p, _p, _p, _i64, _i, _i, _i, _i64, _i, _i64, _i, _i, _p],
     "lq_gemm_wgrad": [_p, _p, _p, _i64, _i64, _i64, _i, _p],
+    "lq_argmax_embed": [_p, _i64, _i64, _i64, _p, _i64, _p, _p, _p, _p],
     "lq_add_rmsnorm": [_p, _p, _p, _f, _p, _i64, _i64, _i, _p],
     "lq_rope_kv_store": [_p, _p, _p, _p, _p, _i64, _i, _i, _i, _i, _i64, _i, _p],
     "lq_decode_attention_workspace_bytes": [_i64, _i, _i, _i64],

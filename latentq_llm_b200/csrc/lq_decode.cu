@@ -351,6 +351,78 @@ __global__ void __launch_bounds__(256) k_silu_mul(const __nv_bfloat16* __restric
     }
 }
 
+// ---------------------------------------------------------------------------------------------
+// End of a greedy decode step in one launch: tok[b] = argmax_v logits[b, v] (the first maximum, NaN counts as the
+// largest value, as torch.argmax), positions[b] += 1, h[b, :] = embed[tok[b], :] (the next step's input row).
+// One CTA per sequence; a thread walks its vectors in ascending order, so "first" survives the reduction by
+// preferring the smaller index among equal values.
+// ---------------------------------------------------------------------------------------------
+constexpr int AM_THREADS = 1024;
+__device__ __forceinline__ bool am_better(float v, int i, float bv, int bi) {
+    const bool vn = v != v, bn = bv != bv;
+    if (vn != bn) return vn;
+    if (!vn && v != bv) return v > bv;
+    return i < bi;
+}
+__global__ void __launch_bounds__(AM_THREADS) k_argmax_embed(const __nv_bfloat16* __restrict__ logits, int64_t logits_stride, int V,
+                                                             int vec, const __nv_bfloat16* __restrict__ embed, int D,
+                                                             long long* __restrict__ tok, long long* __restrict__ positions,
+                                                             __nv_bfloat16* __restrict__ h) {
+    __shared__ float sv[AM_THREADS / 32];
+    __shared__ int si[AM_THREADS / 32];
+    __shared__ int winner;
+    const int b = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    pdl_launch_dependents();
+    pdl_wait();                                       // the logits are the predecessor's output
+    const __nv_bfloat16* row = logits + (size_t)b * logits_stride;
+    float bv = -INFINITY;
+    int bi = 0x7fffffff;
+    if (vec) {                                        // rows start on 16-byte boundaries and hold whole vectors
+        for (int v = tid; v < V / 8; v += AM_THREADS) {
+            const uint4 q = __ldg(reinterpret_cast<const uint4*>(row) + v);
+            const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float lo = bf_lo(w[j]), hi = bf_hi(w[j]);
+                if (am_better(lo, v * 8 + 2 * j, bv, bi)) { bv = lo; bi = v * 8 + 2 * j; }
+                if (am_better(hi, v * 8 + 2 * j + 1, bv, bi)) { bv = hi; bi = v * 8 + 2 * j + 1; }
+            }
+        }
+    } else {
+        for (int v = tid; v < V; v += AM_THREADS) {
+            const float x = __bfloat162float(row[v]);
+            if (am_better(x, v, bv, bi)) { bv = x; bi = v; }
+        }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (am_better(ov, oi, bv, bi)) { bv = ov; bi = oi; }
+    }
+    if (lane == 0) { sv[warp] = bv; si[warp] = bi; }
+    __syncthreads();
+    if (warp == 0) {
+        bv = sv[lane]; bi = si[lane];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (am_better(ov, oi, bv, bi)) { bv = ov; bi = oi; }
+        }
+        if (lane == 0) {
+            winner = bi;
+            tok[b] = bi;
+            if (positions) positions[b] += 1;
+        }
+    }
+    __syncthreads();
+    if (!embed) return;
+    const uint4* src = reinterpret_cast<const uint4*>(embed + (size_t)winner * D);
+    uint4* dst = reinterpret_cast<uint4*>(h + (size_t)b * D);
+    for (int v = tid; v < D / 8; v += AM_THREADS) dst[v] = __ldg(src + v);
+}
+
 static inline bool al16p(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
 }  // namespace lq
@@ -432,6 +504,20 @@ int lq_decode_attention(const void* q, int64_t q_row_stride, const void* k_cache
         launch_pdl(k_decode_attn<64>, grid, (unsigned)ATT_THREADS, 0, st, (const __nv_bfloat16*)q, (int)q_row_stride, (const __nv_bfloat16*)k_cache,
                    (const __nv_bfloat16*)v_cache, (const long long*)positions, (__nv_bfloat16*)out, Hq, Hkv, (int)max_len, scale, part, tickets);
     return check_launch("k_decode_attn");
+}
+
+int lq_argmax_embed(const void* logits, int64_t logits_stride, int64_t B, int64_t V, const void* embed, int64_t D, int64_t* tok,
+                    int64_t* positions, void* h, lq_stream_t stream) {
+    if (!logits || !tok || (embed && (!h || !al16p(embed) || !al16p(h)))) return LQ_EINVAL;
+    if (B < 0 || V < 1 || V >= (1ll << 31) - 8 || B >= (1ll << 31) || logits_stride < V || (embed && (D < 8 || (D % 8) != 0 || D >= (1ll << 31))))
+        return LQ_EUNSUPPORTED;
+    if (B == 0) return LQ_OK;
+    { int rc = ensure_device_for(logits); if (rc) return rc; }
+    const int vec = al16p(logits) && (logits_stride % 8) == 0 && (V % 8) == 0;
+    launch_pdl(k_argmax_embed, dim3((unsigned)B), (unsigned)AM_THREADS, 0, (cudaStream_t)stream, (const __nv_bfloat16*)logits,
+               logits_stride, (int)V, vec, (const __nv_bfloat16*)embed, (int)D, (long long*)tok, (long long*)positions,
+               (__nv_bfloat16*)h);
+    return check_launch("k_argmax_embed");
 }
 
 int lq_silu_mul(const void* gate_up, void* act, int64_t M, int64_t I, int hf_rounding, lq_stream_t stream) {

@@ -168,8 +168,7 @@ class FusedLlamaGreedyDecoder:
 
     def _step_kernels(self, ops):
         D, I, Hq, Hkv, hd = self.D, self.I, self.Hq, self.Hkv, self.hd
-        self.h.copy_(torch.nn.functional.embedding(self.tok, self.model.model.embed_tokens.weight))
-        delta = None
+        delta = None                        # self.h holds the embedding row of self.tok (written by the previous step's end)
         h, h_alt = self.h, self.h2          # the residual stream alternates between two buffers where the norm is fused
         for li, L in enumerate(self.layers):
             kc, vc = self.cache.layers[li].keys, self.cache.layers[li].values
@@ -188,8 +187,12 @@ class FusedLlamaGreedyDecoder:
             delta = self.tmp
         ops.add_rmsnorm(h, delta, self.model.model.norm.weight.detach(), self.eps, out=self.xn, hf_rounding=self.hf)
         self.logits = torch.nn.functional.linear(self.xn, self.model.lm_head.weight)
-        self.tok.copy_(self.logits.argmax(-1))
-        self.pos.add_(1)
+        # argmax, position += 1 and the next step's embedding row in one launch
+        ops.argmax_embed(self.logits, self.tok, self.pos, self.model.model.embed_tokens.weight.detach(), self.h)
+
+    def _seed(self, first, p):
+        self.tok.copy_(first); self.pos.fill_(p)
+        self.h.copy_(torch.nn.functional.embedding(self.tok, self.model.model.embed_tokens.weight))
 
     @torch.no_grad()
     def _prefill(self, prompt):
@@ -205,11 +208,11 @@ class FusedLlamaGreedyDecoder:
         side = torch.cuda.Stream()
         side.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(side):                       # warm-up: lazy initialisations must not be captured
-            self.tok.copy_(first); self.pos.fill_(p)
+            self._seed(first, p)
             self._step(); self._step()
         torch.cuda.current_stream().wait_stream(side)
         self.graph = torch.cuda.CUDAGraph()
-        self.tok.copy_(first); self.pos.fill_(p)
+        self._seed(first, p)
         with torch.cuda.graph(self.graph):
             self._step()
 
@@ -222,7 +225,7 @@ class FusedLlamaGreedyDecoder:
         if use_graph and self.graph is None:
             self._capture(self._prefill(prompt), p)         # throw-away prefill: capture needs an initialised cache
         first = self._prefill(prompt)
-        self.tok.copy_(first); self.pos.fill_(p)
+        self._seed(first, p)
         toks = [first.clone()]
         for _ in range(max_new_tokens - 1):
             if use_graph:

@@ -484,6 +484,23 @@ def gemm_a16w4_fwd_qkv_rope(x, qweight, scales, zeros, positions, inv_freq, k_ca
     return y
 
 
+def argmax_embed(logits, tok, positions=None, embed=None, h=None):
+    """Greedy step end in one launch: tok[b] = argmax(logits[b]) (first maximum, like torch.argmax); positions += 1 and
+    h[b] = embed[tok[b]] when given (generate.py:150-190 drives HF's loop, which does these as separate ops)."""
+    assert logits.dim() == 2 and logits.dtype == torch.bfloat16 and logits.stride(1) == 1
+    _chk(tok, "tok", torch.int64)
+    B, V = logits.shape
+    D = 0
+    if embed is not None:
+        _chk(embed, "embed", torch.bfloat16); _chk(h, "h", torch.bfloat16)
+        D = embed.shape[1]
+        assert h.shape == (B, D)
+    if positions is not None:
+        _chk(positions, "positions", torch.int64)
+    L.call("lq_argmax_embed", _ptr(logits), logits.stride(0), B, V, _ptr(embed), D, _ptr(tok), _ptr(positions), _ptr(h), _stream())
+    return tok
+
+
 def rope_kv_store(qkv, positions, inv_freq, k_cache, v_cache, Hq, Hkv, hd, tokens_per_seq=1, hf_rounding=True):
     """RoPE on the q and k heads of qkv [M, (Hq + 2 Hkv) hd] (q in place); rotated k and v go into the caches
     [batch, Hkv, max_len, hd] at positions[m] (PTQ/quant/fused_attn.py:8-58)."""

@@ -115,3 +115,31 @@ def test_fused_gate_up_silu(ops, M, I, K, hf):
     sep = ops.silu_mul(ops.gemm_a16w4_fwd(_bf(x), torch.from_numpy(codes).cuda(), _bf(s), _bf(z), None, 2 * I, K), hf_rounding=hf)
     if M <= 16:
         assert np.array_equal(got, sep.float().cpu().numpy())
+
+
+@pytest.mark.parametrize("B,V,D", [(1, 32000, 4096), (16, 32000, 4096), (3, 1027, 256), (64, 50272, 2048), (2, 8, 8)])
+def test_argmax_embed(ops, B, V, D):
+    """The end of a greedy step in one launch: the first maximum per row (ties, rows of equal values, a NaN, rows that do
+    not start on 16-byte boundaries), positions advanced by one, the winners' embedding rows copied."""
+    g = torch.Generator(device="cuda").manual_seed(B + V)
+    logits = torch.randn(B, V, device="cuda", generator=g).to(torch.bfloat16)
+    logits[0, V // 3] = logits[0].max()                  # a tie in the first row: the lower index wins
+    logits[0, V - 1] = logits[0].max()
+    if B > 1:
+        logits[1] = 0.5                                  # all equal: index 0
+    if B > 2:
+        logits[2, V // 2] = float("nan")                 # NaN counts as the maximum
+        logits[2, V // 2 + 3] = float("nan")
+    embed = torch.randn(V, D, device="cuda", generator=g).to(torch.bfloat16)
+    tok = torch.full((B,), -1, dtype=torch.long, device="cuda")
+    pos = torch.arange(B, dtype=torch.long, device="cuda") + 5
+    h = torch.zeros(B, D, dtype=torch.bfloat16, device="cuda")
+    ops.argmax_embed(logits, tok, pos, embed, h)
+    want = logits.float().argmax(-1)
+    assert torch.equal(tok, want)
+    assert torch.equal(pos, torch.arange(B, device="cuda") + 6)
+    assert torch.equal(h, embed[want])
+    # argmax alone, on a column slice (row stride != V)
+    tok2 = torch.full((B,), -1, dtype=torch.long, device="cuda")
+    ops.argmax_embed(logits[:, : V - 1], tok2)
+    assert torch.equal(tok2, logits[:, : V - 1].float().argmax(-1))

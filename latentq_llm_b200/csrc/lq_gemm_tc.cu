@@ -209,12 +209,17 @@ static_assert(sizeof(SmemCtl) <= 1024, "barrier block of the shared-memory budge
 // ---------------------------------------------------------------------------------------------
 __device__ __forceinline__ uint32_t bf2_as_u32(__nv_bfloat162 v) { return *reinterpret_cast<uint32_t*>(&v); }
 __device__ __forceinline__ __nv_bfloat162 u32_as_bf2(uint32_t v) { return *reinterpret_cast<__nv_bfloat162*>(&v); }
+// (w & 0x000F000F) | 0x43004300 as ONE three-input logic instruction (spelled out: the C expression compiled to more)
+__device__ __forceinline__ uint32_t lop_nib(uint32_t w) {
+    uint32_t r;
+    asm("lop3.b32 %0, %1, 0x000F000F, 0x43004300, 0xEA;" : "=r"(r) : "r"(w));
+    return r;
+}
 __device__ __forceinline__ uint4 dequant8(uint32_t w, __nv_bfloat162 z128, __nv_bfloat162 s2) {
-    const uint32_t MAGIC = 0x43004300u, MASK = 0x000F000Fu;
-    uint32_t p15 = (w & MASK) | MAGIC;           // (c1, c5)
-    uint32_t p04 = ((w >> 4) & MASK) | MAGIC;    // (c0, c4)
-    uint32_t p37 = ((w >> 8) & MASK) | MAGIC;    // (c3, c7)
-    uint32_t p26 = ((w >> 12) & MASK) | MAGIC;   // (c2, c6)
+    const uint32_t p15 = lop_nib(w);             // (c1, c5)
+    const uint32_t p04 = lop_nib(w >> 4);        // (c0, c4)
+    const uint32_t p37 = lop_nib(w >> 8);        // (c3, c7)
+    const uint32_t p26 = lop_nib(w >> 12);       // (c2, c6)
     uint32_t d15 = bf2_as_u32(__hmul2_rn(__hsub2_rn(u32_as_bf2(p15), z128), s2));
     uint32_t d04 = bf2_as_u32(__hmul2_rn(__hsub2_rn(u32_as_bf2(p04), z128), s2));
     uint32_t d37 = bf2_as_u32(__hmul2_rn(__hsub2_rn(u32_as_bf2(p37), z128), s2));
@@ -230,11 +235,10 @@ __device__ __forceinline__ uint4 dequant8(uint32_t w, __nv_bfloat162 z128, __nv_
 // The same with a scale and a zero point of its own for every code: sp / zp hold (s, z + 128) of the pairs
 // (c0,c4) (c1,c5) (c2,c6) (c3,c7) in x, y, z, w - the order the extraction produces.
 __device__ __forceinline__ uint4 dequant8t(uint32_t w, const uint4& zp, const uint4& sp) {
-    const uint32_t MAGIC = 0x43004300u, MASK = 0x000F000Fu;
-    uint32_t p15 = (w & MASK) | MAGIC;           // (c1, c5)
-    uint32_t p04 = ((w >> 4) & MASK) | MAGIC;    // (c0, c4)
-    uint32_t p37 = ((w >> 8) & MASK) | MAGIC;    // (c3, c7)
-    uint32_t p26 = ((w >> 12) & MASK) | MAGIC;   // (c2, c6)
+    const uint32_t p15 = lop_nib(w);             // (c1, c5)
+    const uint32_t p04 = lop_nib(w >> 4);        // (c0, c4)
+    const uint32_t p37 = lop_nib(w >> 8);        // (c3, c7)
+    const uint32_t p26 = lop_nib(w >> 12);       // (c2, c6)
     uint32_t d15 = bf2_as_u32(__hmul2_rn(__hsub2_rn(u32_as_bf2(p15), u32_as_bf2(zp.y)), u32_as_bf2(sp.y)));
     uint32_t d04 = bf2_as_u32(__hmul2_rn(__hsub2_rn(u32_as_bf2(p04), u32_as_bf2(zp.x)), u32_as_bf2(sp.x)));
     uint32_t d37 = bf2_as_u32(__hmul2_rn(__hsub2_rn(u32_as_bf2(p37), u32_as_bf2(zp.w)), u32_as_bf2(sp.w)));

@@ -34,14 +34,6 @@ __device__ __forceinline__ float silu_mul_bf16(float gate, float up, int hf_roun
     return __fmul_rn(s, up);
 }
 
-// d = a * b (no accumulator input: starts a new group sum without clearing registers first)
-__device__ __forceinline__ void mma_16816_start(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
-    asm volatile(
-        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
-        : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
-        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "f"(0.0f));
-}
-
 // Rotary embedding + cache write for one (token, rotation pair) of a q|k|v projection block (see SkinnyParams):
 // x / yv are the bf16-rounded projections of elements i and i + hd/2 of the head that pair block `blk` belongs to.
 __device__ __forceinline__ void rope_store(const SkinnyParams& p, int blk, int fi, int tok, float x, float yv) {
@@ -80,13 +72,32 @@ __device__ __forceinline__ void rope_store(const SkinnyParams& p, int blk, int f
     }
 }
 
-// 8 codes of one packed word -> 4 bf16 pairs (128 + c_k, 128 + c_{k+4}) for k = 0..3 (OR into the mantissa of 128.0)
-__device__ __forceinline__ void extract_word(uint32_t w, uint32_t* p) {
-    const uint32_t MAGIC = 0x43004300u, MASK = 0x000F000Fu;
-    p[0] = ((w >> 4) & MASK) | MAGIC;     // (c0, c4)
-    p[1] = (w & MASK) | MAGIC;            // (c1, c5)
-    p[2] = ((w >> 12) & MASK) | MAGIC;    // (c2, c6)
-    p[3] = ((w >> 8) & MASK) | MAGIC;     // (c3, c7)
+// 8 codes of one packed word -> 4 bf16 pairs (128 + c_k, 128 + c_{k+4}) for k = 0..3: a nibble pair is OR-ed into the
+// mantissas of two bf16 128.0 by ONE three-input logic instruction.  Written as inline PTX on scalars: the same
+// expression on arrays (`((w >> 4) & MASK) | MAGIC` into p[0..3], fragments gathered into a0[4] / a1[4]) compiled to
+// 9.6 integer-pipe instructions per word instead of 7 (ncu counters), and that pipe bounds these kernels.
+__device__ __forceinline__ uint32_t lop_nib(uint32_t w) {
+    uint32_t r;
+    asm("lop3.b32 %0, %1, 0x000F000F, 0x43004300, 0xEA;" : "=r"(r) : "r"(w));
+    return r;
+}
+// A fragments of the two k-steps (16 k each) that one packed word of row a (va) and of row b (vb) covers:
+// {a00, a01, a02, a03} = (row a: c0 c4 | row b: c0 c4 | row a: c1 c5 | row b: c1 c5), {a10..a13} the same for c2 c6 | c3 c7
+#define LQ_WORD_FRAGS(va, vb)                                                                                          \
+    const uint32_t a00 = lop_nib((va) >> 4), a01 = lop_nib((vb) >> 4), a02 = lop_nib(va), a03 = lop_nib(vb);            \
+    const uint32_t a10 = lop_nib((va) >> 12), a11 = lop_nib((vb) >> 12), a12 = lop_nib((va) >> 8), a13 = lop_nib((vb) >> 8)
+__device__ __forceinline__ void mma_s(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+// d = a * b (no accumulator input: starts a new group sum without clearing registers first)
+__device__ __forceinline__ void mma_s_start(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+        : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(0.0f));
 }
 
 constexpr int SK_THREADS = 256;       // 8 warps x 16 weight rows = 128 rows per CTA
@@ -182,19 +193,17 @@ __global__ void __launch_bounds__(SK_THREADS) k_skinny_fwd(const SkinnyParams p)
 #pragma unroll
                 for (int q = 0; q < PF; ++q) if (u == q) ring[q] = nx;
             }
-            uint32_t pa[8], pb[8];
-            extract_word(ck.qa.x, pa); extract_word(ck.qa.y, pa + 4);
-            extract_word(ck.qb.x, pb); extract_word(ck.qb.y, pb + 4);
 #pragma unroll
-            for (int m = 0; m < MT; ++m) {
-                const __nv_bfloat16* xr = xs + (size_t)(m * 8 + g) * xstride + c * SK_CHUNK + t * 16;
-                const uint4 x0 = *reinterpret_cast<const uint4*>(xr), x1 = *reinterpret_cast<const uint4*>(xr + 8);
-                const uint32_t xb[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
+            for (int half = 0; half < 2; ++half) {          // the chunk's two packed words per row: 2 x 2 k-steps
+                LQ_WORD_FRAGS(half ? ck.qa.y : ck.qa.x, half ? ck.qb.y : ck.qb.x);
 #pragma unroll
-                for (int s4 = 0; s4 < 4; ++s4) {
-                    const uint32_t a[4] = {pa[2 * s4], pb[2 * s4], pa[2 * s4 + 1], pb[2 * s4 + 1]};
-                    mma_16816(acc[m], a, xb[2 * s4], xb[2 * s4 + 1]);
-                    mma_16816(sx[m], ones, xb[2 * s4], xb[2 * s4 + 1]);
+                for (int m = 0; m < MT; ++m) {
+                    const __nv_bfloat16* xr = xs + (size_t)(m * 8 + g) * xstride + c * SK_CHUNK + t * 16 + half * 8;
+                    const uint4 xv = *reinterpret_cast<const uint4*>(xr);
+                    mma_s(acc[m], a00, a01, a02, a03, xv.x, xv.y);
+                    mma_16816(sx[m], ones, xv.x, xv.y);
+                    mma_s(acc[m], a10, a11, a12, a13, xv.z, xv.w);
+                    mma_16816(sx[m], ones, xv.z, xv.w);
                 }
             }
         }
@@ -365,18 +374,19 @@ __global__ void __launch_bounds__(RB_WARPS * 32, 2) k_skinny_rows(const SkinnyPa
         const uint32_t wsa[4] = {ca.x, ca.y, ca.z, ca.w}, wsb[4] = {cq.x, cq.y, cq.z, cq.w};
 #pragma unroll
         for (int w = 0; w < 4; ++w) {      // one packed word = 8 k of each row = two MMA k-steps
-            uint32_t pa[4], pb[4];
-            extract_word(wsa[w], pa); extract_word(wsb[w], pb);
-#pragma unroll
-            for (int i = 0; i < 4; ++i) { pa[i] = sk_bf2(__hsub2_rn(sk_u2(pa[i]), zp2a)); pb[i] = sk_bf2(__hsub2_rn(sk_u2(pb[i]), zp2b)); }
+            LQ_WORD_FRAGS(wsa[w], wsb[w]);
+            // minus (128 + z): exact in bf16, so the MMAs sum x (q - z) and no token sums are needed
+            const uint32_t d00 = sk_bf2(__hsub2_rn(sk_u2(a00), zp2a)), d01 = sk_bf2(__hsub2_rn(sk_u2(a01), zp2b));
+            const uint32_t d02 = sk_bf2(__hsub2_rn(sk_u2(a02), zp2a)), d03 = sk_bf2(__hsub2_rn(sk_u2(a03), zp2b));
+            const uint32_t d10 = sk_bf2(__hsub2_rn(sk_u2(a10), zp2a)), d11 = sk_bf2(__hsub2_rn(sk_u2(a11), zp2b));
+            const uint32_t d12 = sk_bf2(__hsub2_rn(sk_u2(a12), zp2a)), d13 = sk_bf2(__hsub2_rn(sk_u2(a13), zp2b));
 #pragma unroll
             for (int m = 0; m < MT; ++m) {
                 const uint4 v = xc[m][w];  // (k0,k1)(k2,k3)(k4,k5)(k6,k7) -> (k0,k4)(k1,k5)(k2,k6)(k3,k7)
                 const uint32_t x0 = __byte_perm(v.x, v.z, 0x5410), x1 = __byte_perm(v.x, v.z, 0x7632);
                 const uint32_t x2 = __byte_perm(v.y, v.w, 0x5410), x3 = __byte_perm(v.y, v.w, 0x7632);
-                const uint32_t a0[4] = {pa[0], pb[0], pa[1], pb[1]}, a1[4] = {pa[2], pb[2], pa[3], pb[3]};
-                mma_16816(acc[m][0], a0, x0, x1);
-                mma_16816(acc[m][1], a1, x2, x3);
+                mma_s(acc[m][0], d00, d01, d02, d03, x0, x1);
+                mma_s(acc[m][1], d10, d11, d12, d13, x2, x3);
             }
         }
         if ((u + 1) % GC == 0) {
@@ -646,18 +656,16 @@ __global__ void __launch_bounds__(RB_WARPS * 32, LQ_GEMV_MINB) k_skinny_stream(c
                 const uint32_t wsa[4] = {ca.x, ca.y, ca.z, ca.w}, wsb[4] = {cq.x, cq.y, cq.z, cq.w};
 #pragma unroll
                 for (int w = 0; w < 4; ++w) {
-                    uint32_t pa[4], pb[4];
-                    extract_word(wsa[w], pa); extract_word(wsb[w], pb);
-                    const uint32_t a0[4] = {pa[0], pb[0], pa[1], pb[1]}, a1[4] = {pa[2], pb[2], pa[3], pb[3]};
+                    LQ_WORD_FRAGS(wsa[w], wsb[w]);
 #pragma unroll
                     for (int m = 0; m < MT; ++m) {
                         const uint4 f = xbase[m][u * 16 + w * 4];
                         if (w == 0) {
-                            mma_16816_start(acc[m][0], a0, f.x, f.y);
-                            mma_16816_start(acc[m][1], a1, f.z, f.w);
+                            mma_s_start(acc[m][0], a00, a01, a02, a03, f.x, f.y);
+                            mma_s_start(acc[m][1], a10, a11, a12, a13, f.z, f.w);
                         } else {
-                            mma_16816(acc[m][0], a0, f.x, f.y);
-                            mma_16816(acc[m][1], a1, f.z, f.w);
+                            mma_s(acc[m][0], a00, a01, a02, a03, f.x, f.y);
+                            mma_s(acc[m][1], a10, a11, a12, a13, f.z, f.w);
                         }
                     }
                 }
@@ -703,18 +711,16 @@ __global__ void __launch_bounds__(RB_WARPS * 32, LQ_GEMV_MINB) k_skinny_stream(c
                     const uint32_t wsa[4] = {ca.x, ca.y, ca.z, ca.w}, wsb[4] = {cq.x, cq.y, cq.z, cq.w};
 #pragma unroll
                     for (int w = 0; w < 4; ++w) {
-                        uint32_t pa[4], pb[4];
-                        extract_word(wsa[w], pa); extract_word(wsb[w], pb);
-                        const uint32_t a0[4] = {pa[0], pb[0], pa[1], pb[1]}, a1[4] = {pa[2], pb[2], pa[3], pb[3]};
+                        LQ_WORD_FRAGS(wsa[w], wsb[w]);
 #pragma unroll
                         for (int m = 0; m < MT; ++m) {
                             const uint4 f = xbase[m][c * 16 + w * 4];
                             if (w == 0) {
-                                mma_16816_start(acc[m][0], a0, f.x, f.y);
-                                mma_16816_start(acc[m][1], a1, f.z, f.w);
+                                mma_s_start(acc[m][0], a00, a01, a02, a03, f.x, f.y);
+                                mma_s_start(acc[m][1], a10, a11, a12, a13, f.z, f.w);
                             } else {
-                                mma_16816(acc[m][0], a0, f.x, f.y);
-                                mma_16816(acc[m][1], a1, f.z, f.w);
+                                mma_s(acc[m][0], a00, a01, a02, a03, f.x, f.y);
+                                mma_s(acc[m][1], a10, a11, a12, a13, f.z, f.w);
                             }
                         }
                     }
@@ -750,18 +756,16 @@ __global__ void __launch_bounds__(RB_WARPS * 32, LQ_GEMV_MINB) k_skinny_stream(c
                     const int cg = g_begin * GC + c;                                              // chunk index within the row
 #pragma unroll
                     for (int w = 0; w < 4; ++w) {
-                        uint32_t pa[4], pb[4];
-                        extract_word(wsa[w], pa); extract_word(wsb[w], pb);
-                        const uint32_t a0[4] = {pa[0], pb[0], pa[1], pb[1]}, a1[4] = {pa[2], pb[2], pa[3], pb[3]};
+                        LQ_WORD_FRAGS(wsa[w], wsb[w]);
 #pragma unroll
                         for (int m = 0; m < MT; ++m) {
                             const uint4 f = xs[(size_t)xrow[m] * x_stride + cg * 16 + w * 4 + t];
                             if (w == 0 && u % GC == 0) {            // first word of a group: no accumulator input
-                                mma_16816_start(acc[m][0], a0, f.x, f.y);
-                                mma_16816_start(acc[m][1], a1, f.z, f.w);
+                                mma_s_start(acc[m][0], a00, a01, a02, a03, f.x, f.y);
+                                mma_s_start(acc[m][1], a10, a11, a12, a13, f.z, f.w);
                             } else {
-                                mma_16816(acc[m][0], a0, f.x, f.y);
-                                mma_16816(acc[m][1], a1, f.z, f.w);
+                                mma_s(acc[m][0], a00, a01, a02, a03, f.x, f.y);
+                                mma_s(acc[m][1], a10, a11, a12, a13, f.z, f.w);
                             }
                         }
                     }

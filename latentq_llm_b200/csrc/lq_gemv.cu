@@ -473,7 +473,7 @@ __global__ void __launch_bounds__(RB_WARPS * 32, 2) k_skinny_rows(const SkinnyPa
 // the warp's own count and 2-byte group-parameter loads at constant offsets.
 // NORM: the tokens are RMSNorm(h + delta) * gamma, computed in the staging phase (see SkinnyParams).
 template <int MT, int GC, int NCH, bool NORM = false>
-__global__ void __launch_bounds__(RB_WARPS * 32, LQ_GEMV_MINB) k_skinny_stream(const SkinnyParams p, const int x_stride) {
+__global__ void __launch_bounds__(RB_WARPS * 32, MT == 2 ? 1 : LQ_GEMV_MINB) k_skinny_stream(const SkinnyParams p, const int x_stride) {
     constexpr int PF = LQ_GEMV_PF;
     constexpr bool NC4 = NCH == 4;
     static_assert(NCH == 0 || (GC == 1 && PF == 4), "the written-out loops are for group 128 and a ring of four chunks");
@@ -612,20 +612,23 @@ __global__ void __launch_bounds__(RB_WARPS * 32, LQ_GEMV_MINB) k_skinny_stream(c
             __syncthreads();                                                       // nred is reused by the next token
         }
     } else {
-        const int kw_per_tok = p.K / 8, items = p.M * kw_per_tok;
-        for (int base = 0; base < items; base += 2 * RB_WARPS * 32) {
-            uint4 v[2];
-            int tok[2], kw[2];
-            bool on[2];
+        // SB vectors per thread and round trip to L2: staging is a chain of such round trips (16 tokens of K = 4096 are
+        // 32 vectors per thread)
+        constexpr int SB = MT == 2 ? 8 : 4;
+        const int kw_per_tok = NC4 ? 512 : p.K / 8, items = p.M * kw_per_tok;
+        for (int base = 0; base < items; base += SB * RB_WARPS * 32) {
+            uint4 v[SB];
+            int tok[SB], kw[SB];
+            bool on[SB];
 #pragma unroll
-            for (int h = 0; h < 2; ++h) {                 // both loads first
+            for (int h = 0; h < SB; ++h) {                // all loads first
                 const int idx = base + h * RB_WARPS * 32 + tid;
                 on[h] = idx < items;
                 tok[h] = on[h] ? idx / kw_per_tok : 0; kw[h] = on[h] ? idx - tok[h] * kw_per_tok : 0;
                 v[h] = on[h] ? reinterpret_cast<const uint4*>(p.x + (size_t)tok[h] * p.K)[kw[h]] : make_uint4(0, 0, 0, 0);
             }
 #pragma unroll
-            for (int h = 0; h < 2; ++h) stage_item(v[h], tok[h], kw[h], on[h]);
+            for (int h = 0; h < SB; ++h) stage_item(v[h], tok[h], kw[h], on[h]);
         }
     }
     __syncthreads();
@@ -836,7 +839,7 @@ static int launch_skinny_stream_v(const SkinnyParams& p, int x_stride, size_t sm
     cudaGetDevice(&dev);
     if (dev < 0 || dev >= 64) return LQ_EUNSUPPORTED;
     if (!attr_done[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(k_skinny_stream<MT, GC, NCH, NORM>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
+        cudaError_t e = cudaFuncSetAttribute(k_skinny_stream<MT, GC, NCH, NORM>, cudaFuncAttributeMaxDynamicSharedMemorySize, (MT == 2 ? 144 : 96) * 1024);
         if (e != cudaSuccess) { set_cuda_error(e, "cudaFuncSetAttribute(k_skinny_stream)"); return LQ_ECUDA; }
         attr_done[dev] = true;
     }
@@ -856,7 +859,7 @@ static int launch_skinny_stream(const SkinnyParams& p, cudaStream_t st) {
     const size_t smem = skinny_stream_smem(p.M, p.K, p.group);
     const int rpb = p.pair_stride > 0 ? 8 : 16;
     const int n_blocks = (p.N + rpb - 1) / rpb;
-    const unsigned grid = (unsigned)std::min(n_blocks, LQ_GEMV_MINB * sm_count());
+    const unsigned grid = (unsigned)std::min(n_blocks, (mt == 2 ? 1 : LQ_GEMV_MINB) * sm_count());   // 9-16 tokens: one CTA per SM
     // K = 4096 with groups of 128: the written-out loop (scales / zeros are read as 8-byte words there)
     const bool nc4 = gc == 1 && p.K == 4096 && LQ_GEMV_PF == 4 && !getenv("LQ_SKINNY_NO_NC4") &&
                      (reinterpret_cast<uintptr_t>(p.scales) & 7) == 0 && (reinterpret_cast<uintptr_t>(p.zeros) & 7) == 0;
@@ -876,8 +879,15 @@ int launch_skinny_rows(const SkinnyParams& p, cudaStream_t st) {
     // two CTAs per SM must fit: staged tokens + sums + 8-16 KB of static shared memory each
     // Measured on the Llama-2-7B shapes: 3 % faster than the kernel below for one token, slower from about eight tokens
     // on (staging the tokens costs every CTA M x K / 2048 loop steps), so it serves batch 1-2 decode only.
-    if ((p.M <= 2 || getenv("LQ_SKINNY_STREAM_ALL")) && skinny_stream_supported(p.K, p.group) &&
-        skinny_stream_smem(p.M, p.K, p.group) <= 96 * 1024)
+    // 9-16 tokens at K = 4096: the same kernel with one CTA per SM (its 16 staged tokens take 130 KB); the row-block
+    // kernel below re-reads every token from L2 in every CTA (128 KB per 32 KB of weights) and permutes it per use.
+    // Staging the tokens is a fixed cost per CTA, so from three tokens on the kernel pays only for launches with many row
+    // blocks per CTA (measured: the q|k|v and gate|up projections of the 7B shapes, not the 4096-row ones).
+    const int n_row_blocks = (p.N + (p.pair_stride > 0 ? 8 : 16) - 1) / (p.pair_stride > 0 ? 8 : 16);
+    const int wide_min = getenv("LQ_SKINNY_WIDE_MIN") ? atoi(getenv("LQ_SKINNY_WIDE_MIN")) : 768;
+    const bool wide = p.M > 2 && p.K == 4096 && p.group == 128 && n_row_blocks >= wide_min && !getenv("LQ_SKINNY_NO_STREAM16");
+    if ((p.M <= 2 || wide || getenv("LQ_SKINNY_STREAM_ALL")) && skinny_stream_supported(p.K, p.group) &&
+        skinny_stream_smem(p.M, p.K, p.group) <= (size_t)(p.M > 8 ? 144 : 96) * 1024)
         return launch_skinny_stream(p, st);
     if (p.norm_gamma) return LQ_EUNSUPPORTED;       // the fused-norm staging exists in the streaming kernel only
     const int rpb = p.pair_stride > 0 ? 8 : 16;

@@ -139,10 +139,11 @@ def test_a16w4_tmem_and_smem_operand_paths_agree_bitwise(ops, monkeypatch, M, N,
 
 @pytest.mark.parametrize("group", [64, 128, 256])
 @pytest.mark.parametrize("M,N,K", [(1, 320, 1024), (5, 4096, 2816), (8, 192, 768), (9, 1088, 2048), (16, 4096, 4096),
-                                   (3, 960, 4096), (2, 576, 11008), (8, 4992, 11008), (12, 8960, 2048)])
+                                   (3, 960, 4096), (2, 576, 11008), (8, 4992, 11008), (12, 8960, 2048), (13, 12288, 4096)])
 def test_a16w4_decode_sized_forward_all_routes(ops, monkeypatch, M, N, K, group):
     """M <= 16: the streaming row-block kernel (group 128 / 256, at least two groups per warp, tokens staged in shared
-    memory; default for M <= 2, forced for the rest), the one-block-per-CTA row kernel (default for M > 2 and other K),
+    memory; default for M <= 2 and, one CTA per SM, for 9-16 tokens at K = 4096; forced for the rest), the
+    one-block-per-CTA row kernel (default otherwise),
     the split-K kernel (group 64, or forced) and the tensor-core kernel (forced) against dequantize + fp32 matmul,
     with bias; ragged row blocks, uneven K slices and more row blocks than persistent CTAs included."""
     if K % group:
@@ -153,8 +154,9 @@ def test_a16w4_decode_sized_forward_all_routes(ops, monkeypatch, M, N, K, group)
     bias = (torch.randn(N, device="cuda", generator=g) * 0.1).to(torch.bfloat16)
     W = ops.a16w4_dequant(codes, sb, zb, (N, K), torch.bfloat16, group)
     ref = x.float() @ W.float().t() + bias.float()
-    for env in ({}, {"LQ_SKINNY_NO_STREAM": "1"}, {"LQ_SKINNY_STREAM_ALL": "1"}, {"LQ_SKINNY_SPLIT": "1"}, {"LQ_GEMM_NO_SKINNY": "1"}):
-        for k in ("LQ_SKINNY_SPLIT", "LQ_GEMM_NO_SKINNY", "LQ_SKINNY_NO_STREAM", "LQ_SKINNY_STREAM_ALL"):
+    for env in ({}, {"LQ_SKINNY_NO_STREAM": "1"}, {"LQ_SKINNY_NO_STREAM16": "1"}, {"LQ_SKINNY_STREAM_ALL": "1"}, {"LQ_SKINNY_SPLIT": "1"},
+                {"LQ_GEMM_NO_SKINNY": "1"}):
+        for k in ("LQ_SKINNY_SPLIT", "LQ_GEMM_NO_SKINNY", "LQ_SKINNY_NO_STREAM", "LQ_SKINNY_STREAM_ALL", "LQ_SKINNY_NO_STREAM16"):
             monkeypatch.delenv(k, raising=False)
         for k, v in env.items():
             monkeypatch.setenv(k, v)

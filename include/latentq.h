@@ -246,7 +246,8 @@ LQ_API int lq_gemm_a8w8(const int8_t* x8, const int8_t* w8, const float* row_sca
  * fused_mlp.py:84-168): x = RMSNorm(h + delta) * gamma computed as lq_add_rmsnorm computes it (bit for bit), then
  * y[M,N] = x . deq(qweight)^T, or with silu_pair != 0 (qweight = gate | up, N = 2 I rows) y[M,I] = silu(gate) * up.
  * delta may be NULL (then h_out is not written); otherwise h_out receives h + delta and must be a buffer other than h
- * (every CTA reads h).  Returns LQ_EUNSUPPORTED for other shapes: run lq_add_rmsnorm and the GEMM separately. */
+ * (every CTA reads h).  Returns LQ_EUNSUPPORTED for other shapes, and for launches with no more 16-row blocks than
+ * persistent CTAs (two per SM), which another kernel serves: run lq_add_rmsnorm and the GEMM separately. */
 LQ_API int lq_gemm_a16w4_fwd_rmsnorm(const void* h, const void* delta, const void* gamma, float eps, int hf_rounding, void* h_out,
                                      const int8_t* qweight, const void* scales, const void* zeros, void* y, int64_t M, int64_t N,
                                      int64_t K, int group, int silu_pair, lq_stream_t stream);

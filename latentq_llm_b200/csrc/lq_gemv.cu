@@ -877,8 +877,6 @@ static int launch_skinny_stream(const SkinnyParams& p, cudaStream_t st) {
 int launch_skinny_rows(const SkinnyParams& p, cudaStream_t st) {
     if (!skinny_rows_supported(p.K, p.group)) return LQ_EUNSUPPORTED;
     // two CTAs per SM must fit: staged tokens + sums + 8-16 KB of static shared memory each
-    // Measured on the Llama-2-7B shapes: 3 % faster than the kernel below for one token, slower from about eight tokens
-    // on (staging the tokens costs every CTA M x K / 2048 loop steps), so it serves batch 1-2 decode only.
     // 9-16 tokens at K = 4096: the same kernel with one CTA per SM (its 16 staged tokens take 130 KB); the row-block
     // kernel below re-reads every token from L2 in every CTA (128 KB per 32 KB of weights) and permutes it per use.
     // Staging the tokens is a fixed cost per CTA, so from three tokens on the kernel pays only for launches with many row
@@ -886,7 +884,12 @@ int launch_skinny_rows(const SkinnyParams& p, cudaStream_t st) {
     const int n_row_blocks = (p.N + (p.pair_stride > 0 ? 8 : 16) - 1) / (p.pair_stride > 0 ? 8 : 16);
     const int wide_min = getenv("LQ_SKINNY_WIDE_MIN") ? atoi(getenv("LQ_SKINNY_WIDE_MIN")) : 768;
     const bool wide = p.M > 2 && p.K == 4096 && p.group == 128 && n_row_blocks >= wide_min && !getenv("LQ_SKINNY_NO_STREAM16");
-    if ((p.M <= 2 || wide || getenv("LQ_SKINNY_STREAM_ALL")) && skinny_stream_supported(p.K, p.group) &&
+    // One or two tokens: the streaming kernel when there are more row blocks than persistent CTAs; a launch of one row
+    // block per CTA is the kernel below's case (measured at one token: 3.9 against 4.2 us for 4096 x 4096, 9.0 against
+    // 11.2 us for the 11008 -> 4096 down projection).  A fused norm follows the same rule, so that it always computes
+    // the bits of the two-launch sequence.
+    const bool small = p.M <= 2 && n_row_blocks > LQ_GEMV_MINB * sm_count();
+    if ((small || wide || getenv("LQ_SKINNY_STREAM_ALL")) && skinny_stream_supported(p.K, p.group) &&
         skinny_stream_smem(p.M, p.K, p.group) <= (size_t)(p.M > 8 ? 144 : 96) * 1024)
         return launch_skinny_stream(p, st);
     if (p.norm_gamma) return LQ_EUNSUPPORTED;       // the fused-norm staging exists in the streaming kernel only

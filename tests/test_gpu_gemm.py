@@ -389,7 +389,7 @@ def test_a16w4_dgrad_through_transposed_copy(ops, monkeypatch, M, N, K, force):
 
 @pytest.mark.parametrize("hf", [1, 0])
 @pytest.mark.parametrize("with_delta", [True, False])
-@pytest.mark.parametrize("M,N", [(1, 12288), (2, 12288), (1, 22016), (2, 22016), (2, 4160)])
+@pytest.mark.parametrize("M,N", [(1, 12288), (2, 12288), (1, 22016), (2, 22016), (2, 9600)])
 def test_a16w4_decode_forward_with_residual_add_and_rmsnorm_in_the_launch(ops, M, N, with_delta, hf):
     """One or two tokens at K = 4096: the streaming decode kernel computes RMSNorm(h + delta) * gamma while it stages
     its tokens.  The new residual stream and the projection are bit for bit those of `add_rmsnorm` followed by the
@@ -423,7 +423,7 @@ def test_a16w4_decode_forward_with_residual_add_and_rmsnorm_in_the_launch(ops, M
 
 
 def test_a16w4_rmsnorm_forward_refuses_shapes_without_a_fused_kernel(ops):
-    for M, N, K in [(3, 4096, 4096), (1, 4096, 2048), (16, 12288, 4096), (1, 4096, 11008)]:
+    for M, N, K in [(3, 12288, 4096), (1, 12288, 2048), (16, 12288, 4096), (1, 12288, 11008), (1, 4096, 4096)]:   # the last: one row block per CTA
         codes, sb, zb = make_w4_layer(ops, N, K, seed=3)
         h = torch.randn(M, K, device="cuda").to(torch.bfloat16)
         gamma = torch.ones(K, device="cuda", dtype=torch.bfloat16)

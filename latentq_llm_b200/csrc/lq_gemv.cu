@@ -34,14 +34,21 @@ __device__ __forceinline__ float silu_mul_bf16(float gate, float up, int hf_roun
     return __fmul_rn(s, up);
 }
 
+// pair block -> (head, block within the head); hd / 16 blocks per head, a power of two for the usual head sizes
+__device__ __forceinline__ void rope_split(int blk, int bph, int& head, int& rem) {
+    if ((bph & (bph - 1)) == 0) { head = blk >> (__ffs(bph) - 1); rem = blk & (bph - 1); }
+    else { head = blk / bph; rem = blk - head * bph; }
+}
 // Rotary embedding + cache write for one (token, rotation pair) of a q|k|v projection block (see SkinnyParams):
 // x / yv are the bf16-rounded projections of elements i and i + hd/2 of the head that pair block `blk` belongs to.
 __device__ __forceinline__ void rope_store(const SkinnyParams& p, int blk, int fi, int tok, float x, float yv) {
-    const int hd = p.rope_hd, half = hd >> 1, bph = hd >> 4;
-    const int head = blk / bph, i = (blk - head * bph) * 8 + fi;
+    const int hd = p.rope_hd, half = hd >> 1;
+    int head, rem;
+    rope_split(blk, hd >> 4, head, rem);
+    const int i = rem * 8 + fi;
     const long long pos = p.rope_pos[tok];
     const bool pos_ok = pos >= 0 && pos < p.rope_max_len;
-    const int b = tok / p.rope_tps;
+    const int b = p.rope_tps == 1 ? tok : tok / p.rope_tps;
     __nv_bfloat16* dst = p.out + (size_t)tok * (size_t)(2 * p.N) + (size_t)head * hd;
     const __nv_bfloat16 rx = __float2bfloat16_rn(x), ry = __float2bfloat16_rn(yv);
     if (head >= p.rope_hq + p.rope_hkv) {                     // v: as projected, into the buffer and the cache
@@ -271,8 +278,9 @@ __global__ void __launch_bounds__(RB_WARPS * 32, 2) k_skinny_rows(const SkinnyPa
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
     const bool pair = p.pair_stride > 0;
     const int row0 = blockIdx.x * (pair ? 8 : 16);
-    const int rope_bph = p.rope_hd >> 4;                                            // pair blocks per head (rope mode)
-    const int ra = p.rope_hd ? ((int)blockIdx.x / rope_bph) * p.rope_hd + ((int)blockIdx.x % rope_bph) * 8 + g
+    int rope_head = 0, rope_rem = 0;                                                // rope mode: hd / 16 pair blocks per head
+    if (p.rope_hd) rope_split((int)blockIdx.x, p.rope_hd >> 4, rope_head, rope_rem);
+    const int ra = p.rope_hd ? rope_head * p.rope_hd + rope_rem * 8 + g
                              : min(row0 + g, p.N - 1);                              // clamped loads, guarded stores
     const int rb = pair ? p.pair_stride + ra : min(row0 + g + 8, p.N - 1);
     const int gpr = NC4 ? 32 : p.K / (RB_CHUNK * GC);                               // groups per weight row
@@ -489,12 +497,12 @@ __global__ void __launch_bounds__(RB_WARPS * 32, MT == 2 ? 1 : LQ_GEMV_MINB) k_s
     const int n_chunks = n_groups * GC;
     const bool pair = p.pair_stride > 0;
     const int rows_per_blk = pair ? 8 : 16;
-    const int n_blocks = (p.N + rows_per_blk - 1) / rows_per_blk;
+    const int n_blocks = (p.N + rows_per_blk - 1) >> (pair ? 3 : 4);
     int blk = blockIdx.x;                                  // grid <= n_blocks
     const unsigned short* sc_all = reinterpret_cast<const unsigned short*>(p.scales);
     const unsigned short* zp_all = reinterpret_cast<const unsigned short*>(p.zeros);
     auto row_of = [&](int b, int half) {                                                           // clamped loads, guarded stores
-        if (p.rope_hd) { const int bph = p.rope_hd >> 4; return (b / bph) * p.rope_hd + (b % bph) * 8 + g + half * p.pair_stride; }
+        if (p.rope_hd) { int head, rem; rope_split(b, p.rope_hd >> 4, head, rem); return head * p.rope_hd + rem * 8 + g + half * p.pair_stride; }
         return pair ? half * p.pair_stride + min(b * 8 + g, p.N - 1) : min(b * 16 + g + half * 8, p.N - 1);
     };
     auto wptr = [&](int row) { return reinterpret_cast<const uint4*>(p.qweight + (size_t)row * (p.K / 2) + (size_t)g_begin * GC * (RB_CHUNK / 2)) + t; };

@@ -33,6 +33,9 @@ ARCHS = {
                      vocab_size=1024, max_position_embeddings=256, word_embed_proj_dim=256),
     "llama-tiny": dict(kind="llama", hidden_size=256, intermediate_size=512, num_hidden_layers=2, num_attention_heads=4,
                        num_key_value_heads=4, vocab_size=1024, max_position_embeddings=256),
+    # grouped KV heads (8 query heads on 2 KV heads, head size 64)
+    "llama-gqa-tiny": dict(kind="llama", hidden_size=512, intermediate_size=1024, num_hidden_layers=2, num_attention_heads=8,
+                           num_key_value_heads=2, vocab_size=1024, max_position_embeddings=256),
     # the 7B hidden size (the decode kernels' written-out K = 4096 paths) with two thin layers
     "llama-wide-tiny": dict(kind="llama", hidden_size=4096, intermediate_size=1024, num_hidden_layers=2,
                             num_attention_heads=32, num_key_value_heads=32, vocab_size=1024, max_position_embeddings=256),

@@ -23,7 +23,8 @@ def test_graphed_greedy_decode_equals_eager_loop():
         dec.generate(torch.zeros((2, 90), dtype=torch.long, device="cuda"), 12)
 
 
-def test_fused_llama_decoder_against_the_eager_modules():
+@pytest.mark.parametrize("arch", ["llama-tiny", "llama-gqa-tiny"])
+def test_fused_llama_decoder_against_the_eager_modules(arch):
     """The decode step as a chain of this library's kernels (fused q|k|v and gate|up projections, RMSNorm, RoPE with
     the KV-cache write, single-query attention, silu*up) against the model's own eager modules on the same prompt:
     logits of the first decode step agree closely, greedy tokens agree wherever the eager loop's choice was not a
@@ -31,7 +32,7 @@ def test_fused_llama_decoder_against_the_eager_modules():
     from latentq_llm_b200 import finetune as ft
     from latentq_llm_b200.generate import FusedLlamaGreedyDecoder, GraphedGreedyDecoder, _SDPA
     from torch.nn.attention import sdpa_kernel
-    model = ft.build_model("llama-tiny", "cuda", seed=3)
+    model = ft.build_model(arch, "cuda", seed=3)
     ft.quantize_decoder(model, lbit=4, gbit=16)
     model.eval()
     B, P, T = 2, 40, 10

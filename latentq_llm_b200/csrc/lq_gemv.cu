@@ -34,21 +34,14 @@ __device__ __forceinline__ float silu_mul_bf16(float gate, float up, int hf_roun
     return __fmul_rn(s, up);
 }
 
-// pair block -> (head, block within the head); hd / 16 blocks per head, a power of two for the usual head sizes
-__device__ __forceinline__ void rope_split(int blk, int bph, int& head, int& rem) {
-    if ((bph & (bph - 1)) == 0) { head = blk >> (__ffs(bph) - 1); rem = blk & (bph - 1); }
-    else { head = blk / bph; rem = blk - head * bph; }
-}
 // Rotary embedding + cache write for one (token, rotation pair) of a q|k|v projection block (see SkinnyParams):
 // x / yv are the bf16-rounded projections of elements i and i + hd/2 of the head that pair block `blk` belongs to.
 __device__ __forceinline__ void rope_store(const SkinnyParams& p, int blk, int fi, int tok, float x, float yv) {
-    const int hd = p.rope_hd, half = hd >> 1;
-    int head, rem;
-    rope_split(blk, hd >> 4, head, rem);
-    const int i = rem * 8 + fi;
+    const int hd = p.rope_hd, half = hd >> 1, bph = hd >> 4;
+    const int head = blk / bph, i = (blk - head * bph) * 8 + fi;
     const long long pos = p.rope_pos[tok];
     const bool pos_ok = pos >= 0 && pos < p.rope_max_len;
-    const int b = p.rope_tps == 1 ? tok : tok / p.rope_tps;
+    const int b = tok / p.rope_tps;
     __nv_bfloat16* dst = p.out + (size_t)tok * (size_t)(2 * p.N) + (size_t)head * hd;
     const __nv_bfloat16 rx = __float2bfloat16_rn(x), ry = __float2bfloat16_rn(yv);
     if (head >= p.rope_hq + p.rope_hkv) {                     // v: as projected, into the buffer and the cache
@@ -278,9 +271,8 @@ __global__ void __launch_bounds__(RB_WARPS * 32, 2) k_skinny_rows(const SkinnyPa
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
     const bool pair = p.pair_stride > 0;
     const int row0 = blockIdx.x * (pair ? 8 : 16);
-    int rope_head = 0, rope_rem = 0;                                                // rope mode: hd / 16 pair blocks per head
-    if (p.rope_hd) rope_split((int)blockIdx.x, p.rope_hd >> 4, rope_head, rope_rem);
-    const int ra = p.rope_hd ? rope_head * p.rope_hd + rope_rem * 8 + g
+    const int rope_bph = p.rope_hd >> 4;                                            // pair blocks per head (rope mode)
+    const int ra = p.rope_hd ? ((int)blockIdx.x / rope_bph) * p.rope_hd + ((int)blockIdx.x % rope_bph) * 8 + g
                              : min(row0 + g, p.N - 1);                              // clamped loads, guarded stores
     const int rb = pair ? p.pair_stride + ra : min(row0 + g + 8, p.N - 1);
     const int gpr = NC4 ? 32 : p.K / (RB_CHUNK * GC);                               // groups per weight row
@@ -497,12 +489,12 @@ __global__ void __launch_bounds__(RB_WARPS * 32, MT == 2 ? 1 : LQ_GEMV_MINB) k_s
     const int n_chunks = n_groups * GC;
     const bool pair = p.pair_stride > 0;
     const int rows_per_blk = pair ? 8 : 16;
-    const int n_blocks = (p.N + rows_per_blk - 1) >> (pair ? 3 : 4);
+    const int n_blocks = (p.N + rows_per_blk - 1) / rows_per_blk;
     int blk = blockIdx.x;                                  // grid <= n_blocks
     const unsigned short* sc_all = reinterpret_cast<const unsigned short*>(p.scales);
     const unsigned short* zp_all = reinterpret_cast<const unsigned short*>(p.zeros);
     auto row_of = [&](int b, int half) {                                                           // clamped loads, guarded stores
-        if (p.rope_hd) { int head, rem; rope_split(b, p.rope_hd >> 4, head, rem); return head * p.rope_hd + rem * 8 + g + half * p.pair_stride; }
+        if (p.rope_hd) { const int bph = p.rope_hd >> 4; return (b / bph) * p.rope_hd + (b % bph) * 8 + g + half * p.pair_stride; }
         return pair ? half * p.pair_stride + min(b * 8 + g, p.N - 1) : min(b * 16 + g + half * 8, p.N - 1);
     };
     auto wptr = [&](int row) { return reinterpret_cast<const uint4*>(p.qweight + (size_t)row * (p.K / 2) + (size_t)g_begin * GC * (RB_CHUNK / 2)) + t; };
@@ -548,8 +540,21 @@ __global__ void __launch_bounds__(RB_WARPS * 32, MT == 2 ? 1 : LQ_GEMV_MINB) k_s
     pdl_wait();                     // the tokens may be the previous launch's output
     // one staged vector: 8 tokens' worth of k of token `tok` (word kw of its row), permuted into B-fragment order, and
     // its contribution to the token sum of its group
+    // With 9-16 tokens the per-group token sums are not gathered here (26 of the 45 instructions per vector) but
+    // computed after staging by each warp for its own groups: the staged fragments against an all-ones tile, 8 MMAs per
+    // group and 8 tokens, whose D fragment is exactly the pair of sums the thread needs.
+    constexpr bool mma_sums = MT == 2 && !NORM;
     auto stage_item = [&](const uint4& v, const int tok, const int kw, const bool on) {
         const uint32_t r[4] = {v.x, v.y, v.z, v.w};
+        if constexpr (mma_sums) {
+            if (on) {
+                uint4 f;
+                f.x = __byte_perm(v.x, v.z, 0x5410); f.y = __byte_perm(v.x, v.z, 0x7632);
+                f.z = __byte_perm(v.y, v.w, 0x5410); f.w = __byte_perm(v.y, v.w, 0x7632);
+                xs[(size_t)tok * x_stride + (kw & ~15) + ((kw & 3) << 2) + ((kw >> 2) & 3)] = f;
+            }
+            return;
+        }
         float part = 0.0f;
 #pragma unroll
         for (int j = 0; j < 4; ++j) part += __uint_as_float(r[j] << 16) + __uint_as_float(r[j] & 0xffff0000u);
@@ -640,6 +645,30 @@ __global__ void __launch_bounds__(RB_WARPS * 32, MT == 2 ? 1 : LQ_GEMV_MINB) k_s
         }
     }
     __syncthreads();
+    if constexpr (mma_sums) {
+        const uint32_t ones[4] = {0x3f803f80u, 0x3f803f80u, 0x3f803f80u, 0x3f803f80u};
+        for (int gi = 0; gi < n_groups; ++gi) {
+            float sacc[MT][4];
+#pragma unroll
+            for (int m = 0; m < MT; ++m) sacc[m][0] = sacc[m][1] = sacc[m][2] = sacc[m][3] = 0.0f;
+#pragma unroll
+            for (int c = 0; c < GC; ++c)
+#pragma unroll
+                for (int w = 0; w < 4; ++w)
+#pragma unroll
+                    for (int m = 0; m < MT; ++m) {
+                        const uint4 f = xs[(size_t)xrow[m] * x_stride + ((g_begin + gi) * GC + c) * 16 + w * 4 + t];
+                        mma_16816(sacc[m], ones, f.x, f.y);
+                        mma_16816(sacc[m], ones, f.z, f.w);
+                    }
+            if (g == 0) {                                 // every row of the D fragment holds the same sums
+#pragma unroll
+                for (int m = 0; m < MT; ++m)
+                    *reinterpret_cast<float2*>(&sxs[(g_begin + gi) * (8 * MT) + m * 8 + 2 * t]) = make_float2(sacc[m][0], sacc[m][1]);
+            }
+        }
+        __syncwarp();                                     // a warp reads only the sums of its own groups
+    }
 
     int buf = 0;
     // NC4: per-warp bases of the staged tokens and token sums (everything else is a compile-time offset)
